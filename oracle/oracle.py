@@ -1,0 +1,317 @@
+"""numpy front-end of the CPU oracle (TEST INFRASTRUCTURE — only tests/, the smoke check and the
+CPU-baseline leg of bench.py may import this module; the shipped package never does).
+
+Every function mirrors one reference operator and returns numpy arrays in the reference's tuple
+order: slicing / sampling → (sub_indptr, coo_col | None, sub_indices, select_index)
+(src/cuda/slicing.cu:167, src/cuda/sampling.cu:153); fused slice+sample → (sub_indptr,
+sub_indices, select_index) (src/cuda/fusion/slice_sampling.cu:142).
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+I64 = np.int64
+F32 = np.float32
+
+OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "copy_lhs": 4, "copy_rhs": 5, "dot": 6}
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libgs_oracle.so")
+        if not os.path.exists(path):
+            from . import build as _b  # type: ignore
+            _b.build()
+        _LIB = ctypes.CDLL(path)
+        _LIB.gso_col_slice_count.restype = ctypes.c_int64
+        _LIB.gso_sample_uniform_count.restype = ctypes.c_int64
+        _LIB.gso_list_sample.restype = ctypes.c_int64
+        _LIB.gso_unique_relabel.restype = ctypes.c_int64
+        _LIB.gso_row_slice_csc.restype = ctypes.c_int64
+        _LIB.gso_row_slice_coo.restype = ctypes.c_int64
+        _LIB.gso_sage_batch.restype = ctypes.c_int64
+        _LIB.gso_rand_word.restype = ctypes.c_uint32
+        _LIB.gso_ares_key_of.restype = ctypes.c_float
+        _LIB.gso_num_threads.restype = ctypes.c_int
+    return _LIB
+
+
+def _p(a):
+    if a is None:
+        return ctypes.c_void_p(0)
+    assert a.flags["C_CONTIGUOUS"]
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+def _i64(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=I64)
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=F32)
+
+
+def _c(v):
+    return ctypes.c_int64(int(v))
+
+
+def _u(v):
+    return ctypes.c_uint64(int(v) & 0xFFFFFFFFFFFFFFFF)
+
+
+def num_threads():
+    return int(lib().gso_num_threads())
+
+
+def set_num_threads(n):
+    lib().gso_set_num_threads(ctypes.c_int(int(n)))
+
+
+def philox_block(ctr, key):
+    c = np.asarray(ctr, dtype=np.uint32)
+    k = np.asarray(key, dtype=np.uint32)
+    out = np.zeros(4, dtype=np.uint32)
+    lib().gso_philox_block(_p(c), _p(k), _p(out))
+    return out
+
+
+def rand_word(seed, item, slot, stream):
+    return int(lib().gso_rand_word(_u(seed), _u(item), _u(slot), ctypes.c_uint32(stream)))
+
+
+def ares_key(r, w):
+    return float(lib().gso_ares_key_of(ctypes.c_uint32(r), ctypes.c_float(w)))
+
+
+def col_slice(indptr, indices, seeds, with_coo=True):
+    indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
+    S = len(seeds) if seeds is not None else len(indptr) - 1
+    sub_indptr = np.empty(S + 1, dtype=I64)
+    nnz = lib().gso_col_slice_count(_p(indptr), _p(seeds), _c(S), _p(sub_indptr))
+    out_i = np.empty(nnz, dtype=I64)
+    out_s = np.empty(nnz, dtype=I64)
+    out_c = np.empty(nnz, dtype=I64) if with_coo else None
+    lib().gso_col_slice_fill(_p(indptr), _p(indices), _p(seeds), _c(S), _p(sub_indptr), _p(out_i), _p(out_s),
+                             _p(out_c))
+    return sub_indptr, out_c, out_i, out_s
+
+
+def sample_uniform(indptr, indices, seeds, k, replace, seed=0, algo=0, with_coo=False):
+    """seeds=None → plain Sampling over every column; else fused slice+sample."""
+    indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
+    S = len(seeds) if seeds is not None else len(indptr) - 1
+    sub_indptr = np.empty(S + 1, dtype=I64)
+    nnz = lib().gso_sample_uniform_count(_p(indptr), _p(seeds), _c(S), _c(k), ctypes.c_int(int(replace)),
+                                         _p(sub_indptr))
+    out_i = np.empty(nnz, dtype=I64)
+    out_s = np.empty(nnz, dtype=I64)
+    out_c = np.empty(nnz, dtype=I64) if with_coo else None
+    lib().gso_sample_uniform_fill(_p(indptr), _p(indices), _p(seeds), _c(S), _c(k), ctypes.c_int(int(replace)),
+                                  _u(seed), ctypes.c_int(algo), _p(sub_indptr), _p(out_i), _p(out_s), _p(out_c))
+    return sub_indptr, out_c, out_i, out_s
+
+
+def sample_one_keepdim(indptr, indices, seeds, seed=0):
+    indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
+    S = len(seeds)
+    sub_indptr = np.empty(S + 1, dtype=I64)
+    out_i = np.empty(S, dtype=I64)
+    out_s = np.empty(S, dtype=I64)
+    lib().gso_sample_one_keepdim(_p(indptr), _p(indices), _p(seeds), _c(S), _u(seed), _p(sub_indptr), _p(out_i),
+                                 _p(out_s))
+    return sub_indptr, out_i, out_s
+
+
+def sample_weighted(indptr, indices, probs, seeds, k, replace, seed=0, with_coo=False):
+    indptr, indices, seeds, probs = _i64(indptr), _i64(indices), _i64(seeds), _f32(probs)
+    S = len(seeds) if seeds is not None else len(indptr) - 1
+    sub_indptr = np.empty(S + 1, dtype=I64)
+    nnz = lib().gso_sample_uniform_count(_p(indptr), _p(seeds), _c(S), _c(k), ctypes.c_int(int(replace)),
+                                         _p(sub_indptr))
+    out_i = np.empty(nnz, dtype=I64)
+    out_s = np.empty(nnz, dtype=I64)
+    out_c = np.empty(nnz, dtype=I64) if with_coo else None
+    lib().gso_sample_weighted_fill(_p(indptr), _p(indices), _p(probs), _p(seeds), _c(S), _c(k),
+                                   ctypes.c_int(int(replace)), _u(seed), _p(sub_indptr), _p(out_i), _p(out_s),
+                                   _p(out_c))
+    return sub_indptr, out_c, out_i, out_s
+
+
+def list_sample(data, probs, k, replace, seed=0):
+    data, probs = _i64(data), _f32(probs)
+    N = len(data)
+    cap = max(N, k)
+    out_d = np.empty(cap, dtype=I64)
+    out_x = np.empty(cap, dtype=I64)
+    n = lib().gso_list_sample(_p(data), _p(probs), _c(N), _c(k), ctypes.c_int(int(replace)), _u(seed), _p(out_d),
+                              _p(out_x))
+    return out_d[:n].copy(), out_x[:n].copy()
+
+
+def unique_relabel(mapping, to_relabel=None):
+    """mapping: list of arrays (concatenated in order) → (frontier, [relabeled arrays])."""
+    items = _i64(np.concatenate([np.asarray(m, dtype=I64) for m in mapping])) if len(mapping) else np.empty(0, I64)
+    N = len(items)
+    uniq = np.empty(N, dtype=I64)
+    if to_relabel is None:
+        U = lib().gso_unique_relabel(_p(items), _c(N), _p(uniq), _p(None), _c(0), _p(None))
+        return uniq[:U].copy(), []
+    sizes = [len(t) for t in to_relabel]
+    rel_in = _i64(np.concatenate([np.asarray(t, dtype=I64) for t in to_relabel])) if sizes else np.empty(0, I64)
+    rel_out = np.empty(len(rel_in), dtype=I64)
+    U = lib().gso_unique_relabel(_p(items), _c(N), _p(uniq), _p(rel_in), _c(len(rel_in)), _p(rel_out))
+    outs, o = [], 0
+    for s in sizes:
+        outs.append(rel_out[o:o + s].copy())
+        o += s
+    return uniq[:U].copy(), outs
+
+
+def random_walk(indptr, indices, seeds, length, seed=0, layout=0, walker_offset=0):
+    indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
+    W = len(seeds)
+    out = np.empty(W * (length + 1), dtype=I64)
+    lib().gso_random_walk(_p(indptr), _p(indices), _p(seeds), _c(W), _c(length), _u(seed), ctypes.c_int(layout),
+                          _c(walker_offset), _p(out))
+    # the reference returns the step-major memory reshaped to [W, L+1] without a transpose
+    return out.reshape(W, length + 1)
+
+
+def calc_bcast(op, lhs_shape, rhs_shape):
+    """Restates CalcBcastOff (src/bcast.cc:24-76) on shapes. Returns dict with lhs_len, rhs_len,
+    out_len, reduce_size, lhs_off, rhs_off (None when no broadcasting)."""
+    lhs_len = int(np.prod(lhs_shape[1:])) if len(lhs_shape) > 1 else 1
+    rhs_len = int(np.prod(rhs_shape[1:])) if len(rhs_shape) > 1 else 1
+    use_bcast = False
+    if op not in ("copy_lhs", "copy_rhs"):
+        if len(lhs_shape) != len(rhs_shape):
+            use_bcast = True
+        else:
+            use_bcast = any(lhs_shape[i] != rhs_shape[i] for i in range(1, len(lhs_shape)))
+    reduce_size = 1
+    lhs_off = rhs_off = None
+    if use_bcast:
+        max_ndim = max(len(lhs_shape), len(rhs_shape)) - 1
+        out_len, j = 1, 0
+        if op == "dot":
+            reduce_size = lhs_shape[-1]
+            j = 1
+        stride_l = stride_r = 1
+        lhs_off, rhs_off = [0], [0]
+        while j < max_ndim:
+            dl = 1 if len(lhs_shape) - 1 - j < 1 else lhs_shape[len(lhs_shape) - 1 - j]
+            dr = 1 if len(rhs_shape) - 1 - j < 1 else rhs_shape[len(rhs_shape) - 1 - j]
+            for i in range(1, max(dl, dr)):
+                for k in range(out_len):
+                    lhs_off.append(lhs_off[k] + i * (1 if i < dl else 0) * stride_l)
+                    rhs_off.append(rhs_off[k] + i * (1 if i < dr else 0) * stride_r)
+            out_len *= max(dl, dr)
+            stride_l *= dl
+            stride_r *= dr
+            j += 1
+    else:
+        out_len = rhs_len if op == "copy_rhs" else lhs_len
+        if op == "dot":
+            reduce_size = lhs_shape[-1]
+            out_len //= reduce_size
+    return dict(lhs_len=lhs_len, rhs_len=rhs_len, out_len=out_len, reduce_size=reduce_size, lhs_off=lhs_off,
+                rhs_off=rhs_off)
+
+
+def sddmm_coo(op, row, col, lhs, rhs, lhs_target=0, rhs_target=2, e_ids=None):
+    row, col, e_ids = _i64(row), _i64(col), _i64(e_ids)
+    lhs, rhs = _f32(lhs), _f32(rhs)
+    E = len(row)
+    bc = calc_bcast(op, lhs.shape if lhs is not None else rhs.shape, rhs.shape if rhs is not None else lhs.shape)
+    out = np.zeros((E, bc["out_len"]), dtype=F32)
+    lo = _i64(np.asarray(bc["lhs_off"])) if bc["lhs_off"] is not None else None
+    ro = _i64(np.asarray(bc["rhs_off"])) if bc["rhs_off"] is not None else None
+    lib().gso_sddmm_coo(ctypes.c_int(OPS[op]), _p(row), _p(col), _p(e_ids), _c(E), _p(lhs), _p(rhs), _p(out),
+                        ctypes.c_int(lhs_target), ctypes.c_int(rhs_target), _c(bc["lhs_len"]), _c(bc["rhs_len"]),
+                        _c(bc["out_len"]), _c(bc["reduce_size"]), _p(lo), _p(ro))
+    return out
+
+
+def segment_sum_csc(indptr, data, powk=1, e_ids=None):
+    indptr, data, e_ids = _i64(indptr), _f32(data), _i64(e_ids)
+    n = len(indptr) - 1
+    out = np.zeros(n, dtype=F32)
+    lib().gso_segment_sum_csc(_p(indptr), _c(n), _p(e_ids), _p(data), _c(powk), _p(out))
+    return out
+
+
+def segment_sum_coo(target, num_out, data, powk=1, e_ids=None):
+    target, data, e_ids = _i64(target), _f32(data), _i64(e_ids)
+    out = np.zeros(num_out, dtype=F32)
+    lib().gso_segment_sum_coo(_p(target), _c(len(target)), _p(e_ids), _p(data), _c(powk), _p(out))
+    return out
+
+
+def segment_normalize_csc(indptr, data, e_ids=None):
+    indptr, data, e_ids = _i64(indptr), _f32(data), _i64(e_ids)
+    out = np.empty_like(data)
+    lib().gso_segment_normalize_csc(_p(indptr), _c(len(indptr) - 1), _p(e_ids), _p(data), _p(out))
+    return out
+
+
+def row_slice_csc(indptr, indices, row_ids, with_coo=False):
+    indptr, indices, row_ids = _i64(indptr), _i64(indices), _i64(row_ids)
+    nc = len(indptr) - 1
+    out_indptr = np.empty(nc + 1, dtype=I64)
+    oi = np.empty(len(indices), dtype=I64)
+    os_ = np.empty(len(indices), dtype=I64)
+    oc = np.empty(len(indices), dtype=I64) if with_coo else None
+    n = lib().gso_row_slice_csc(_p(indptr), _p(indices), _c(nc), _p(row_ids), _c(len(row_ids)), _p(out_indptr),
+                                _p(oi), _p(os_), _p(oc))
+    return out_indptr, (oc[:n].copy() if with_coo else None), oi[:n].copy(), os_[:n].copy()
+
+
+def row_slice_coo(coo_row, coo_col, row_ids):
+    coo_row, coo_col, row_ids = _i64(coo_row), _i64(coo_col), _i64(row_ids)
+    E = len(coo_row)
+    o_r, o_c, o_s = (np.empty(E, dtype=I64) for _ in range(3))
+    n = lib().gso_row_slice_coo(_p(coo_row), _p(coo_col), _c(E), _p(row_ids), _c(len(row_ids)), _p(o_r), _p(o_c),
+                                _p(o_s))
+    return o_r[:n].copy(), o_c[:n].copy(), o_s[:n].copy()
+
+
+def csc2coo(indptr, indices):
+    indptr = _i64(indptr)
+    col = np.empty(len(indices), dtype=I64)
+    lib().gso_csc2coo(_p(indptr), _c(len(indptr) - 1), _p(col))
+    return _i64(indices), col
+
+
+def coo2csc(row, col, num_cols, col_sorted=False):
+    """→ (indptr, sorted_row, perm | None); pass (col, row) swapped for CSR."""
+    row, col = _i64(row), _i64(col)
+    E = len(row)
+    indptr = np.empty(num_cols + 1, dtype=I64)
+    out_row = np.empty(E, dtype=I64)
+    perm = None if col_sorted else np.empty(E, dtype=I64)
+    lib().gso_coo2csc(_p(col), _p(row), _c(E), _c(num_cols), ctypes.c_int(int(col_sorted)), _p(indptr),
+                      _p(out_row), _p(perm))
+    return indptr, out_row, perm
+
+
+def sage_batch(indptr, indices, seeds, fanouts, seed=0, want_frontier=False):
+    indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
+    f = _i64(np.asarray(fanouts))
+    flen = ctypes.c_int64(0)
+    cap = 0
+    fr = None
+    if want_frontier:
+        cap = len(seeds)
+        for k in fanouts:
+            cap = cap * (1 + int(k))
+        fr = np.empty(cap, dtype=I64)
+    e = lib().gso_sage_batch(_p(indptr), _p(indices), _p(seeds), _c(len(seeds)), _p(f), ctypes.c_int(len(fanouts)),
+                             _u(seed), _p(fr), _c(cap), ctypes.byref(flen))
+    if want_frontier:
+        return int(e), fr[:flen.value].copy()
+    return int(e)
