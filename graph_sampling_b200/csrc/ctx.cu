@@ -1,0 +1,191 @@
+// Context: scratch arena, look-back tile state, device counters and pinned read-back buffer.
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+struct gsb_ctx {
+  int device;
+  void* workspace;
+  size_t workspace_bytes;
+  u64* tile_words;
+  i64 tile_capacity;
+  uint32_t epoch;
+  i64* counters;  // device, CNT_NUM entries
+  i64* pinned;    // host pinned, CNT_NUM entries
+  i64 launches;
+  char message[512];
+};
+
+namespace gsb {
+
+int cuda_fail(gsb_ctx* ctx, cudaError_t e, const char* file, int line) {
+  if (ctx) snprintf(ctx->message, sizeof(ctx->message), "%s (%s:%d)", cudaGetErrorString(e), file, line);
+  return e == cudaErrorMemoryAllocation ? GSB_ERR_OUT_OF_MEMORY : GSB_ERR_CUDA;
+}
+
+int ctx_reserve_workspace(gsb_ctx* ctx, size_t bytes, void** out) {
+  if (bytes > ctx->workspace_bytes) {
+    // Growing synchronises the device; it only happens the first time a size is seen.
+    GSB_CUDA_OK(cudaDeviceSynchronize());
+    if (ctx->workspace) GSB_CUDA_OK(cudaFree(ctx->workspace));
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    size_t want = bytes + bytes / 4;
+    want = (want + 255) & ~(size_t)255;
+    cudaError_t e = cudaMalloc(&ctx->workspace, want);
+    if (e != cudaSuccess) {
+      want = (bytes + 255) & ~(size_t)255;
+      e = cudaMalloc(&ctx->workspace, want);
+    }
+    if (e != cudaSuccess) return cuda_fail(ctx, e, __FILE__, __LINE__);
+    ctx->workspace_bytes = want;
+  }
+  *out = ctx->workspace;
+  return GSB_OK;
+}
+
+int ctx_tile_state(gsb_ctx* ctx, i64 num_tiles, cudaStream_t stream, TileState* out) {
+  if (num_tiles > ctx->tile_capacity) {
+    GSB_CUDA_OK(cudaDeviceSynchronize());
+    if (ctx->tile_words) GSB_CUDA_OK(cudaFree(ctx->tile_words));
+    ctx->tile_words = nullptr;
+    i64 cap = ctx->tile_capacity > 0 ? ctx->tile_capacity : (1 << 16);
+    while (cap < num_tiles) cap <<= 1;
+    GSB_CUDA_OK(cudaMalloc((void**)&ctx->tile_words, sizeof(u64) * (size_t)cap));
+    GSB_CUDA_OK(cudaMemset(ctx->tile_words, 0, sizeof(u64) * (size_t)cap));
+    ctx->tile_capacity = cap;
+    ctx->epoch = 0;
+  }
+  ctx->epoch += 1;
+  if (ctx->epoch > kEpochMask) {
+    // 22-bit epoch wrapped: stale words could alias, clear them (stream-ordered).
+    GSB_CUDA_OK(cudaMemsetAsync(ctx->tile_words, 0, sizeof(u64) * (size_t)ctx->tile_capacity, stream));
+    ctx->epoch = 1;
+  }
+  out->words = ctx->tile_words;
+  out->epoch = ctx->epoch;
+  out->counters = ctx->counters;
+  return GSB_OK;
+}
+
+i64* ctx_counters(gsb_ctx* ctx) { return ctx->counters; }
+i64* ctx_pinned(gsb_ctx* ctx) { return ctx->pinned; }
+int ctx_device(gsb_ctx* ctx) { return ctx->device; }
+
+int ctx_fetch_counters(gsb_ctx* ctx, cudaStream_t stream, int first, int n, const i64** out) {
+  GSB_CUDA_OK(cudaMemcpyAsync(ctx->pinned + first, ctx->counters + first, sizeof(i64) * (size_t)n,
+                              cudaMemcpyDeviceToHost, stream));
+  GSB_CUDA_OK(cudaStreamSynchronize(stream));
+  *out = ctx->pinned + first;
+  return GSB_OK;
+}
+
+int ctx_check_device_error(gsb_ctx* ctx, cudaStream_t stream) {
+  const i64* c;
+  int st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 2, &c);
+  if (st != GSB_OK) return st;
+  if (c[0] != 0) {
+    int code = (int)c[0];
+    snprintf(ctx->message, sizeof(ctx->message), "device-side error %d (%s), detail %lld", code,
+             gsb_status_string(code), (long long)c[1]);
+    GSB_CUDA_OK(cudaMemsetAsync(ctx->counters + CNT_ERROR, 0, 2 * sizeof(i64), stream));
+    GSB_CUDA_OK(cudaStreamSynchronize(stream));
+    return code;
+  }
+  return GSB_OK;
+}
+
+void ctx_count_launches(gsb_ctx* ctx, int n) { ctx->launches += n; }
+
+}  // namespace gsb
+
+extern "C" {
+
+int gsb_ctx_create(int device, gsb_ctx** out_ctx) {
+  if (!out_ctx) return GSB_ERR_INVALID_ARGUMENT;
+  *out_ctx = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || device < 0 || device >= count) return e != cudaSuccess ? GSB_ERR_CUDA : GSB_ERR_INVALID_ARGUMENT;
+  gsb_ctx* ctx = new (std::nothrow) gsb_ctx();
+  if (!ctx) return GSB_ERR_OUT_OF_MEMORY;
+  memset(ctx, 0, sizeof(*ctx));
+  ctx->device = device;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  int st = GSB_OK;
+  do {
+    if ((e = cudaSetDevice(device)) != cudaSuccess) break;
+    if ((e = cudaMalloc((void**)&ctx->counters, sizeof(i64) * gsb::CNT_NUM)) != cudaSuccess) break;
+    if ((e = cudaMemset(ctx->counters, 0, sizeof(i64) * gsb::CNT_NUM)) != cudaSuccess) break;
+    if ((e = cudaMallocHost((void**)&ctx->pinned, sizeof(i64) * gsb::CNT_NUM)) != cudaSuccess) break;
+    memset(ctx->pinned, 0, sizeof(i64) * gsb::CNT_NUM);
+  } while (0);
+  if (e != cudaSuccess) {
+    st = gsb::cuda_fail(nullptr, e, __FILE__, __LINE__);
+    if (ctx->counters) cudaFree(ctx->counters);
+    if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    delete ctx;
+    cudaSetDevice(prev);
+    return st;
+  }
+  cudaSetDevice(prev);
+  *out_ctx = ctx;
+  return GSB_OK;
+}
+
+int gsb_ctx_destroy(gsb_ctx* ctx) {
+  if (!ctx) return GSB_OK;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  if (ctx->workspace) cudaFree(ctx->workspace);
+  if (ctx->tile_words) cudaFree(ctx->tile_words);
+  if (ctx->counters) cudaFree(ctx->counters);
+  if (ctx->pinned) cudaFreeHost(ctx->pinned);
+  cudaSetDevice(prev);
+  delete ctx;
+  return GSB_OK;
+}
+
+const char* gsb_status_string(int status) {
+  switch (status) {
+    case GSB_OK: return "ok";
+    case GSB_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case GSB_ERR_CUDA: return "CUDA runtime error";
+    case GSB_ERR_OUT_OF_MEMORY: return "out of device memory";
+    case GSB_ERR_CAPACITY: return "output capacity too small";
+    case GSB_ERR_LOOKBACK_TIMEOUT: return "bounded device-side wait expired";
+    case GSB_ERR_TABLE_FULL: return "hash table full";
+    case GSB_ERR_UNSUPPORTED: return "unsupported argument combination";
+    case GSB_ERR_INDEX_RANGE: return "index out of range";
+    default: return "unknown status";
+  }
+}
+
+const char* gsb_last_error_message(gsb_ctx* ctx) { return ctx ? ctx->message : ""; }
+
+int gsb_check_device_status(gsb_ctx* ctx, void* stream) {
+  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  return gsb::ctx_check_device_error(ctx, (cudaStream_t)stream);
+}
+
+const char* gsb_version(void) { return "gsb200 0.1 sm_100a"; }
+
+int64_t gsb_launch_count(gsb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int gsb_read_counts(gsb_ctx* ctx, void* stream, int64_t* nnz_host, int64_t* unique_host) {
+  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  const i64* c;
+  int st = gsb::ctx_fetch_counters(ctx, (cudaStream_t)stream, gsb::CNT_NNZ, 2, &c);
+  if (st != GSB_OK) return st;
+  if (nnz_host) *nnz_host = c[0];
+  if (unique_host) *unique_host = c[1];
+  return GSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,100 @@
+// Uniform random walk: one thread per walker, the current node lives in a register for the whole
+// walk (the reference re-reads the previous trace element from global memory at every step:
+// src/cuda/fusion/random_walk.cu:32), one Philox block feeds four steps.
+//
+// Per step the walker does two dependent gathers (the indptr pair of the current node, then one
+// entry of indices) and one trace store.  Step-major stores (layout 0, the reference's memory
+// order) are coalesced across the warp as they are.  Walker-major stores (layout 1) are staged
+// per warp in shared memory, kChunk steps at a time, and written as 128-byte row segments.
+#include "common.cuh"
+#include "philox.cuh"
+
+namespace gsb {
+
+constexpr int kWalkThreads = 256;
+constexpr int kChunk = 16;
+
+// Degrees are clamped to 2^32 - 1 for the draw (one 32-bit word per step); a column with more
+// entries than that cannot exist in a graph that fits one GPU.
+__device__ __forceinline__ i64 walk_step(const i64* __restrict__ indptr, const i64* __restrict__ indices, i64 cur,
+                                         uint32_t word) {
+  if (cur < 0) return -1;
+  const i64 b = __ldg(indptr + cur);
+  const i64 d = __ldg(indptr + cur + 1) - b;
+  if (d <= 0) return -1;
+  const u64 dd = d > 0xFFFFFFFFll ? 0xFFFFFFFFull : (u64)d;
+  return __ldg(indices + b + (i64)bounded_from_word(word, dd));
+}
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(kWalkThreads, 4) k_random_walk(const i64* __restrict__ indptr,
+                                                              const i64* __restrict__ indices,
+                                                              const i64* __restrict__ seeds, i64 W, i64 L, u64 seed,
+                                                              i64 walker_offset, i64* __restrict__ out) {
+  __shared__ i64 s_buf[LAYOUT == 1 ? (kWalkThreads / 32) * 32 * (kChunk + 1) : 1];
+  const i64 w = (i64)blockIdx.x * kWalkThreads + threadIdx.x;
+  const bool active = w < W;
+  i64 cur = active ? seeds[w] : -1;
+  const u64 item = (u64)(w + walker_offset);
+  if (LAYOUT == 0) {
+    if (!active) return;
+    out[w] = cur;
+    U32x4 blk;
+    for (i64 s = 0; s < L; ++s) {
+      if ((s & 3) == 0) blk = rand_block(seed, item, (u64)(s >> 2), STREAM_WALK);
+      const uint32_t word = (s & 3) == 0 ? blk.v[0] : (s & 3) == 1 ? blk.v[1] : (s & 3) == 2 ? blk.v[2] : blk.v[3];
+      cur = walk_step(indptr, indices, cur, word);
+      out[(s + 1) * W + w] = cur;
+    }
+  } else {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    i64* buf = s_buf + warp * 32 * (kChunk + 1);
+    const i64 warp_w0 = (i64)blockIdx.x * kWalkThreads + warp * 32;
+    const i64 row_len = L + 1;
+    U32x4 blk;
+    // trace position t holds the node after t steps; chunk c covers positions [c*kChunk, (c+1)*kChunk)
+    for (i64 t0 = 0; t0 < row_len; t0 += kChunk) {
+      const int cnt = (int)min((i64)kChunk, row_len - t0);
+      for (int q = 0; q < cnt; ++q) {
+        const i64 t = t0 + q;
+        if (t > 0) {
+          const i64 s = t - 1;
+          if ((s & 3) == 0) blk = rand_block(seed, item, (u64)(s >> 2), STREAM_WALK);
+          const uint32_t word =
+              (s & 3) == 0 ? blk.v[0] : (s & 3) == 1 ? blk.v[1] : (s & 3) == 2 ? blk.v[2] : blk.v[3];
+          if (active) cur = walk_step(indptr, indices, cur, word);
+        }
+        buf[lane * (kChunk + 1) + q] = cur;
+      }
+      __syncwarp();
+      // two walkers per pass: lanes 0-15 write one row segment, lanes 16-31 the next
+      const int sub = lane >> 4, col = lane & 15;
+      for (int r = 0; r < 32; r += 2) {
+        const i64 ww = warp_w0 + r + sub;
+        if (ww < W && col < cnt) out[ww * row_len + t0 + col] = buf[(r + sub) * (kChunk + 1) + col];
+      }
+      __syncwarp();
+    }
+  }
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" int gsb_random_walk(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+                               const int64_t* seeds, int64_t W, int64_t L, uint64_t seed, int layout,
+                               int64_t walker_offset, int64_t* out) {
+  GSB_REQUIRE(ctx && indptr && indices && W >= 0 && L >= 0 && (layout == 0 || layout == 1), GSB_ERR_INVALID_ARGUMENT);
+  if (W == 0) return GSB_OK;
+  GSB_REQUIRE(seeds && out, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int grid = grid_for(W, kWalkThreads);
+  if (layout == 0)
+    k_random_walk<0><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+  else
+    k_random_walk<1><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  return GSB_OK;
+}

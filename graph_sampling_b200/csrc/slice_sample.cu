@@ -1,0 +1,336 @@
+// Column slicing and uniform per-column sampling (plain and fused with slicing).
+//
+// Data layout: the graph is CSC in HBM (int64 indptr[n+1], int64 indices[nnz]); a call works on a
+// list of S seed columns.  Columns are grouped into tiles of kTileCols consecutive seeds, one CTA
+// per tile.  A CTA (1) stages the tile's (start, degree, count) triples in shared memory with one
+// coalesced read of the seed list and one gathered read of the indptr pairs, (2) scans the counts
+// in shared memory and obtains the tile's output offset by decoupled look-back, (3) produces the
+// outputs.  Slicing copies by OUTPUT position (each thread finds its column by binary search in
+// the shared offsets), so hub columns are spread over the whole CTA; sampling gives each column a
+// group of G lanes, G = smallest power of two >= fanout, and needs O(fanout) draws per column
+// whatever its degree (Floyd's k-subset), instead of the reference's O(degree) reservoir pass
+// (src/cuda/fusion/slice_sampling.cu:62-75).
+#include "common.cuh"
+#include "philox.cuh"
+#include "scan.cuh"
+
+namespace gsb {
+
+constexpr int kThreads = 256;
+constexpr int kTileCols = 128;  // columns per CTA in the fill / sample kernels
+
+enum CountMode { COUNT_DEGREE = 0, COUNT_WOR = 1, COUNT_WR = 2 };
+
+__device__ __forceinline__ i64 column_count(i64 d, i64 k, int mode) {
+  if (mode == COUNT_DEGREE) return d;
+  if (mode == COUNT_WOR) return d < k ? d : k;
+  return d > 0 ? k : 0;
+}
+
+// ---- count + scan only (one column per thread) -------------------------------------------------
+__global__ void __launch_bounds__(kThreads) k_count_scan(const i64* __restrict__ indptr,
+                                                         const i64* __restrict__ seeds, i64 S, i64 k, int mode,
+                                                         i64* __restrict__ out_indptr, i64* counters, TileState ts) {
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_base;
+  const int tile = blockIdx.x;
+  const i64 i = (i64)tile * kThreads + threadIdx.x;
+  if ((i64)tile * kThreads >= S && !(S == 0 && tile == 0)) return;
+  i64 f = 0;
+  if (i < S) {
+    const i64 col = seeds ? seeds[i] : i;
+    const i64 b = indptr[col];
+    f = column_count(indptr[col + 1] - b, k, mode);
+  }
+  i64 total;
+  const i64 excl = block_exclusive_scan<kThreads>(f, s_scan, &total);
+  if (threadIdx.x < 32) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, total);
+    if (threadIdx.x == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const i64 tile_base = s_base;
+  if (i < S) out_indptr[i] = tile_base + excl;
+  if ((i64)(tile + 1) * kThreads >= S && threadIdx.x == 0) {
+    out_indptr[S] = tile_base + total;
+    counters[CNT_NNZ] = tile_base + total;
+  }
+}
+
+// ---- slice fill ---------------------------------------------------------------------------------
+struct FillParams {
+  const i64* indptr;
+  const i64* indices;
+  const i64* seeds;
+  i64 S;
+  const i64* out_indptr;
+  i64* out_indices;
+  i64* out_select;
+  i64* out_coo_col;
+  const float* data;
+  const i64* e_ids;
+  float* out_data;
+};
+
+__global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
+  __shared__ i64 s_in[kTileCols];
+  __shared__ i64 s_off[kTileCols + 1];
+  const i64 base = (i64)blockIdx.x * kTileCols;
+  if (base >= p.S) return;
+  const int ncol = (int)min((i64)kTileCols, p.S - base);
+  const int tid = threadIdx.x;
+  if (tid <= ncol) s_off[tid] = p.out_indptr[base + tid];
+  if (tid < ncol) {
+    const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
+    s_in[tid] = p.indptr[col];
+  }
+  __syncthreads();
+  const i64 tile_base = s_off[0];
+  const i64 tile_sum = s_off[ncol] - tile_base;
+  for (i64 q = tid; q < tile_sum; q += kThreads) {
+    const i64 pos = tile_base + q;
+    // largest c with s_off[c] <= pos
+    int lo = 0, hi = ncol;  // invariant: s_off[lo] <= pos < s_off[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_off[mid] <= pos) lo = mid;
+      else hi = mid;
+    }
+    const i64 in_pos = s_in[lo] + (pos - s_off[lo]);
+    p.out_indices[pos] = __ldg(p.indices + in_pos);
+    p.out_select[pos] = in_pos;
+    if (p.out_coo_col) p.out_coo_col[pos] = base + lo;
+    if (p.out_data) p.out_data[pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+  }
+}
+
+// ---- fused count + scan + uniform sampling -------------------------------------------------------
+struct SampleParams {
+  const i64* indptr;
+  const i64* indices;
+  const i64* seeds;
+  i64 S;
+  i64 k;
+  int replace;
+  u64 seed;
+  i64* out_indptr;
+  i64* out_indices;
+  i64* out_select;
+  i64* out_coo_col;
+  const float* data;
+  const i64* e_ids;
+  float* out_data;
+  i64 capacity;
+  i64* counters;
+  TileState ts;
+};
+
+__device__ __forceinline__ void emit_pick(const SampleParams& p, i64 out_pos, i64 in_pos, i64 column_pos) {
+  p.out_indices[out_pos] = __ldg(p.indices + in_pos);
+  p.out_select[out_pos] = in_pos;
+  if (p.out_coo_col) p.out_coo_col[out_pos] = column_pos;
+  if (p.out_data) p.out_data[out_pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+}
+
+template <int G>
+__global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
+  __shared__ i64 s_in[kTileCols];
+  __shared__ i64 s_deg[kTileCols];
+  __shared__ i64 s_off[kTileCols];
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_base;
+  const int tile = blockIdx.x;
+  const int tid = threadIdx.x;
+  const i64 S = p.S;
+  const i64 base = (i64)tile * kTileCols;
+  if (base >= S && !(S == 0 && tile == 0)) return;
+  const int ncol = (int)max((i64)0, min((i64)kTileCols, S - base));
+  const i64 k = p.k;
+
+  i64 f = 0;
+  if (tid < ncol) {
+    const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
+    const i64 b = p.indptr[col];
+    const i64 d = p.indptr[col + 1] - b;
+    f = column_count(d, k, p.replace ? COUNT_WR : COUNT_WOR);
+    s_in[tid] = b;
+    s_deg[tid] = d;
+  }
+  i64 total;
+  const i64 excl = block_exclusive_scan<kThreads>(f, s_scan, &total);
+  if (tid < kTileCols) s_off[tid] = excl;
+  if (tid < 32) {
+    const i64 prefix = tile_exclusive_prefix(p.ts, tile, total);
+    if (tid == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const i64 tile_base = s_base;
+  if (tid < ncol) p.out_indptr[base + tid] = tile_base + excl;
+  if (base + kTileCols >= S && tid == 0) {
+    p.out_indptr[S] = tile_base + total;
+    p.counters[CNT_NNZ] = tile_base + total;
+  }
+  if (tile_base + total > p.capacity) {
+    if (tid == 0) raise_error(p.counters, GSB_ERR_CAPACITY, tile_base + total);
+    return;
+  }
+
+  constexpr int kGroups = kThreads / G;
+  const int lane = tid % G;
+  const int grp = tid / G;
+  const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
+
+  for (int c = grp; c < ncol; c += kGroups) {
+    const i64 d = s_deg[c];
+    const i64 b = s_in[c];
+    const i64 o = tile_base + s_off[c];
+    const i64 col_pos = base + c;
+    if (p.replace) {
+      if (d == 0) continue;
+      for (i64 j = lane; j < k; j += G)
+        emit_pick(p, o + j, b + (i64)rand_bounded(p.seed, (u64)col_pos, (u64)j, STREAM_UNIFORM, (u64)d), col_pos);
+    } else if (d <= k) {
+      for (i64 j = lane; j < d; j += G) emit_pick(p, o + j, b + j, col_pos);
+    } else if (k <= G) {
+      // Floyd's k-subset inside the lane group: lane j draws t_j in [0, d-k+j]; the draws are
+      // resolved in slot order (a repeated value is replaced by d-k+j).
+      const i64 m = d - k + lane;
+      i64 t = 0;
+      if (lane < k) t = (i64)rand_bounded(p.seed, (u64)col_pos, (u64)lane, STREAM_UNIFORM, (u64)(m + 1));
+      i64 pick = -1;
+      for (int j = 0; j < (int)k; ++j) {
+        const i64 tj = __shfl_sync(gmask, t, j, G);
+        const bool dup = (lane < j) && (pick == tj);
+        const unsigned any = __ballot_sync(gmask, dup);
+        if (lane == j) pick = any ? m : tj;
+      }
+      if (lane < k) emit_pick(p, o + lane, b + pick, col_pos);
+    } else {
+      // fanout > 32 (G == 32 here): same procedure with the chosen positions kept in the output
+      // buffer; membership is checked by the whole warp.
+      for (i64 j = 0; j < k; ++j) {
+        const i64 m = d - k + j;
+        const i64 tj = b + (i64)rand_bounded(p.seed, (u64)col_pos, (u64)j, STREAM_UNIFORM, (u64)(m + 1));
+        bool dup = false;
+        for (i64 q = lane; q < j; q += G) dup |= (p.out_select[o + q] == tj);
+        const unsigned any = __ballot_sync(gmask, dup);
+        if (lane == 0) p.out_select[o + j] = any ? (b + m) : tj;
+        __syncwarp(gmask);
+      }
+      for (i64 j = lane; j < k; j += G) emit_pick(p, o + j, p.out_select[o + j], col_pos);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) k_sample_one_keepdim(const i64* __restrict__ indptr,
+                                                                 const i64* __restrict__ indices,
+                                                                 const i64* __restrict__ seeds, i64 S, u64 seed,
+                                                                 i64* __restrict__ out_indptr,
+                                                                 i64* __restrict__ out_indices,
+                                                                 i64* __restrict__ out_select) {
+  const i64 i = (i64)blockIdx.x * kThreads + threadIdx.x;
+  if (i > S) return;
+  out_indptr[i] = i;
+  if (i == S) return;
+  const i64 col = seeds[i];
+  const i64 b = indptr[col];
+  const i64 d = indptr[col + 1] - b;
+  if (d == 0) {
+    out_indices[i] = -1;
+    out_select[i] = -1;
+  } else {
+    const i64 pos = b + (i64)rand_bounded(seed, (u64)i, 0, STREAM_UNIFORM, (u64)d);
+    out_indices[i] = indices[pos];
+    out_select[i] = pos;
+  }
+}
+
+template <int G>
+static void launch_sample(const SampleParams& p, int grid, cudaStream_t stream) {
+  k_sample_uniform<G><<<grid, kThreads, 0, stream>>>(p);
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" {
+
+int gsb_col_slice_count(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* seeds, int64_t S,
+                        int64_t* out_indptr, int64_t* nnz_host) {
+  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int grid = grid_for(S, kThreads);
+  TileState ts;
+  int st = ctx_tile_state(ctx, grid, stream, &ts);
+  if (st != GSB_OK) return st;
+  k_count_scan<<<grid, kThreads, 0, stream>>>(indptr, seeds, S, 0, COUNT_DEGREE, out_indptr, ctx_counters(ctx), ts);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  if (nnz_host) {
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_NNZ, 1, &c);
+    if (st != GSB_OK) return st;
+    *nnz_host = c[0];
+  }
+  return GSB_OK;
+}
+
+int gsb_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+                       const int64_t* seeds, int64_t S, const int64_t* out_indptr, int64_t* out_indices,
+                       int64_t* out_select, int64_t* out_coo_col, const float* data, const int64_t* e_ids,
+                       float* out_data) {
+  GSB_REQUIRE(ctx && indptr && indices && out_indptr && out_indices && out_select && S >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE((out_data == nullptr) == (data == nullptr), GSB_ERR_INVALID_ARGUMENT);
+  if (S == 0) return GSB_OK;
+  FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data};
+  k_slice_fill<<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  return GSB_OK;
+}
+
+int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+                       const int64_t* seeds, int64_t S, int64_t k, int replace, uint64_t seed, int64_t* out_indptr,
+                       int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col, const float* data,
+                       const int64_t* e_ids, float* out_data, int64_t capacity, int64_t* nnz_host) {
+  GSB_REQUIRE(ctx && indptr && indices && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE((out_data == nullptr) == (data == nullptr), GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int grid = grid_for(S, kTileCols);
+  TileState ts;
+  int st = ctx_tile_state(ctx, grid, stream, &ts);
+  if (st != GSB_OK) return st;
+  SampleParams p{indptr, indices, seeds,  S,        k,        replace,         (u64)seed, out_indptr, out_indices,
+                 out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts};
+  if (k <= 4) launch_sample<4>(p, grid, stream);
+  else if (k <= 8) launch_sample<8>(p, grid, stream);
+  else if (k <= 16) launch_sample<16>(p, grid, stream);
+  else launch_sample<32>(p, grid, stream);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  if (nnz_host) {
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);
+    if (st != GSB_OK) return st;
+    *nnz_host = c[CNT_NNZ];
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  }
+  return GSB_OK;
+}
+
+int gsb_sample_one_keepdim(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+                           const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
+                           int64_t* out_indices, int64_t* out_select) {
+  GSB_REQUIRE(ctx && indptr && indices && seeds && out_indptr && out_indices && out_select && S >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  k_sample_one_keepdim<<<grid_for(S + 1, kThreads), kThreads, 0, (cudaStream_t)stream_>>>(
+      indptr, indices, seeds, S, (u64)seed, out_indptr, out_indices, out_select);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  return GSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,198 @@
+// Unique in first-occurrence order + relabel.
+//
+//   pass 1  k_insert          every item records its position in the table (min per id)
+//   pass 2  k_first_compact   an item is a "first occurrence" iff the table holds its own position;
+//                             flags are scanned (block scan + look-back) and the first occurrences
+//                             are written in order -> stable compaction = order of first occurrence;
+//                             the slot's value is replaced by the compacted position
+//   pass 3  k_relabel         every element to relabel reads its id's compacted position
+//
+// This is the three-pass structure of the reference (Unique / Relabel, src/cuda/unique_reindex.cu:80-172)
+// with its separate flag array, cub scan, blocking size read and value table folded away.
+#include "common.cuh"
+#include "hash_table.cuh"
+#include "scan.cuh"
+
+namespace gsb {
+
+constexpr int kThreads = 256;
+constexpr int kItemsPerThread = 4;
+constexpr int kTileItems = kThreads * kItemsPerThread;
+
+struct Segments {
+  const i64* ptr[GSB_MAX_SEGMENTS];
+  i64* out[GSB_MAX_SEGMENTS];
+  i64 start[GSB_MAX_SEGMENTS + 1];  // start[n] = total
+  int n;
+};
+
+// Static indexing only (after unrolling), so the by-value parameter struct stays in constant memory.
+__device__ __forceinline__ i64 load_item(const Segments& s, i64 i) {
+  const i64* p = s.ptr[0];
+  i64 st = 0;
+#pragma unroll
+  for (int q = 1; q < GSB_MAX_SEGMENTS; ++q)
+    if (q < s.n && i >= s.start[q]) {
+      p = s.ptr[q];
+      st = s.start[q];
+    }
+  return p[i - st];
+}
+
+__device__ __forceinline__ i64* out_slot(const Segments& s, i64 i) {
+  i64* p = s.out[0];
+  i64 st = 0;
+#pragma unroll
+  for (int q = 1; q < GSB_MAX_SEGMENTS; ++q)
+    if (q < s.n && i >= s.start[q]) {
+      p = s.out[q];
+      st = s.start[q];
+    }
+  return p + (i - st);
+}
+
+__global__ void __launch_bounds__(kThreads) k_insert(Segments items, Table table, i64* counters) {
+  const i64 n = items.start[items.n];
+  for (i64 i = (i64)blockIdx.x * kThreads + threadIdx.x; i < n; i += (i64)gridDim.x * kThreads) {
+    const i64 key = load_item(items, i);
+    if (key < 0) {
+      raise_error(counters, GSB_ERR_INDEX_RANGE, i);
+      continue;
+    }
+    if (!table_insert_min(table, key, (u64)i)) raise_error(counters, GSB_ERR_TABLE_FULL, i);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) k_first_compact(Segments items, Table table, i64* __restrict__ out_unique,
+                                                            i64* counters, TileState ts) {
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_base;
+  const i64 n = items.start[items.n];
+  const int tile = blockIdx.x;
+  const i64 base = (i64)tile * kTileItems;
+  if (base >= n && !(n == 0 && tile == 0)) return;
+  i64 key[kItemsPerThread];
+  Slot* slot[kItemsPerThread];
+  int first[kItemsPerThread];
+  int mine = 0;
+#pragma unroll
+  for (int q = 0; q < kItemsPerThread; ++q) {
+    const i64 i = base + (i64)threadIdx.x * kItemsPerThread + q;
+    first[q] = 0;
+    slot[q] = nullptr;
+    key[q] = 0;
+    if (i < n) {
+      key[q] = load_item(items, i);
+      slot[q] = key[q] >= 0 ? table_find(table, key[q]) : nullptr;
+      first[q] = (slot[q] != nullptr && slot[q]->val == (u64)i) ? 1 : 0;
+      mine += first[q];
+    }
+  }
+  i64 total;
+  i64 excl = block_exclusive_scan<kThreads>((i64)mine, s_scan, &total);
+  if (threadIdx.x < 32) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, total);
+    if (threadIdx.x == 0) s_base = prefix;
+  }
+  __syncthreads();
+  i64 pos = s_base + excl;
+#pragma unroll
+  for (int q = 0; q < kItemsPerThread; ++q) {
+    if (first[q]) {
+      out_unique[pos] = key[q];
+      // Safe in place: only the first occurrence writes its slot, and every other occurrence of the
+      // id sits at a larger position than both the old and the new value, so its test stays false.
+      slot[q]->val = (u64)pos;
+      ++pos;
+    }
+  }
+  if (base + kTileItems >= n && threadIdx.x == 0) counters[CNT_UNIQUE] = s_base + total;
+}
+
+__global__ void __launch_bounds__(kThreads) k_relabel(Segments rel, Table table) {
+  const i64 n = rel.start[rel.n];
+  for (i64 i = (i64)blockIdx.x * kThreads + threadIdx.x; i < n; i += (i64)gridDim.x * kThreads) {
+    const i64 key = load_item(rel, i);
+    const Slot* s = key >= 0 ? table_find(table, key) : nullptr;
+    *out_slot(rel, i) = s ? (i64)s->val : -1;
+  }
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+static int fill_segments(Segments* s, const int64_t* const* ptrs, const int64_t* lens, int64_t* const* outs, int n) {
+  if (n < 0 || n > GSB_MAX_SEGMENTS) return GSB_ERR_INVALID_ARGUMENT;
+  s->n = n > 0 ? n : 1;
+  i64 run = 0;
+  for (int q = 0; q < GSB_MAX_SEGMENTS; ++q) {
+    s->ptr[q] = nullptr;
+    s->out[q] = nullptr;
+    s->start[q] = run;
+    if (q < n) {
+      if (lens[q] < 0 || (lens[q] > 0 && !ptrs[q])) return GSB_ERR_INVALID_ARGUMENT;
+      s->ptr[q] = ptrs[q];
+      if (outs) s->out[q] = outs[q];
+      run += lens[q];
+    }
+  }
+  s->start[GSB_MAX_SEGMENTS] = run;
+  for (int q = n; q <= GSB_MAX_SEGMENTS; ++q) s->start[q] = run;
+  return GSB_OK;
+}
+
+extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* const* item_ptrs_host,
+                                  const int64_t* item_lens_host, int num_item_arrays, int64_t* out_unique,
+                                  const int64_t* const* relabel_ptrs_host, const int64_t* relabel_lens_host,
+                                  int64_t* const* out_relabel_ptrs_host, int num_relabel, int64_t* unique_host) {
+  GSB_REQUIRE(ctx && num_item_arrays >= 1 && item_ptrs_host && item_lens_host, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(num_relabel == 0 || (relabel_ptrs_host && relabel_lens_host && out_relabel_ptrs_host),
+              GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  Segments items, rel;
+  int st = fill_segments(&items, item_ptrs_host, item_lens_host, nullptr, num_item_arrays);
+  if (st != GSB_OK) return st;
+  st = fill_segments(&rel, relabel_ptrs_host, relabel_lens_host, out_relabel_ptrs_host, num_relabel);
+  if (st != GSB_OK) return st;
+  const i64 n = items.start[items.n];
+  const i64 m = num_relabel > 0 ? rel.start[rel.n] : 0;
+  GSB_REQUIRE(n == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(n < (1ll << 40), GSB_ERR_UNSUPPORTED);
+
+  Table table;
+  u64 cap;
+  table_geometry(n, &cap, &table.shift);
+  table.mask = cap - 1;
+  void* ws;
+  st = ctx_reserve_workspace(ctx, cap * sizeof(Slot), &ws);
+  if (st != GSB_OK) return st;
+  table.slots = (Slot*)ws;
+  GSB_CUDA_OK(cudaMemsetAsync(table.slots, 0xFF, cap * sizeof(Slot), stream));
+
+  const int tiles = grid_for(n, kTileItems);
+  TileState ts;
+  st = ctx_tile_state(ctx, tiles, stream, &ts);
+  if (st != GSB_OK) return st;
+  const int sm_grid = kNumSMs * 8;
+  if (n > 0) {
+    k_insert<<<min(grid_for(n, kThreads), sm_grid), kThreads, 0, stream>>>(items, table, ctx_counters(ctx));
+    GSB_LAUNCH_OK();
+  }
+  k_first_compact<<<tiles, kThreads, 0, stream>>>(items, table, out_unique, ctx_counters(ctx), ts);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, n > 0 ? 3 : 2);
+  if (m > 0) {
+    k_relabel<<<min(grid_for(m, kThreads), sm_grid), kThreads, 0, stream>>>(rel, table);
+    GSB_LAUNCH_OK();
+    ctx_count_launches(ctx, 1);
+  }
+  if (unique_host) {
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
+    if (st != GSB_OK) return st;
+    *unique_host = c[CNT_UNIQUE];
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  }
+  return GSB_OK;
+}

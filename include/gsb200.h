@@ -1,0 +1,150 @@
+/*
+ * gsb200 — C ABI of the B200-native (sm_100a) graph-sampling kernels.
+ *
+ * This is the boundary a gSampler-style host layer binds: plain pointers, sizes and a CUDA stream,
+ * no torch types.  Each entry point names the reference interface it replaces (paths are relative
+ * to the czkkkkkk/graph_sampling tree).  Conventions:
+ *
+ *  - every pointer is a DEVICE pointer unless its name ends in `_host`;
+ *  - ids and offsets are int64, weights / features / edge data are float (the only instantiation
+ *    of the reference: src/cuda/slicing.cu:176, src/cuda/sampling_probs.cu:274);
+ *  - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns
+ *    without waiting, except where a size has to be reported to the host (documented per call);
+ *  - the return value is a status code (0 = GSB_OK); nothing aborts the process (the reference
+ *    LOG(FATAL)s: src/cuda/cuda_common.h:15-28);
+ *  - inputs are borrowed and never modified; outputs are caller-allocated;
+ *  - a gsb_ctx owns scratch memory and device-side counters for ONE stream of work at a time:
+ *    calls sharing a context must be ordered on one stream (use one context per stream/thread).
+ *    Scratch grows on demand with cudaMalloc the first time a size is seen (this synchronises the
+ *    device once); steady-state calls allocate nothing;
+ *  - there is no CPU fallback: without a CUDA device gsb_ctx_create fails.
+ */
+#ifndef GSB200_H_
+#define GSB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GSB_API __attribute__((visibility("default")))
+#else
+#define GSB_API
+#endif
+
+enum gsb_status {
+  GSB_OK = 0,
+  GSB_ERR_INVALID_ARGUMENT = -1,
+  GSB_ERR_CUDA = -2,             /* a CUDA runtime call failed; see gsb_last_error_message */
+  GSB_ERR_OUT_OF_MEMORY = -3,
+  GSB_ERR_CAPACITY = -4,         /* an output buffer or table was too small for the result */
+  GSB_ERR_LOOKBACK_TIMEOUT = -5, /* a bounded device-side wait expired */
+  GSB_ERR_TABLE_FULL = -6,       /* hash-table probe sequence exhausted */
+  GSB_ERR_UNSUPPORTED = -7,
+  GSB_ERR_INDEX_RANGE = -8       /* an id was outside the graph (checked builds / debug mode) */
+};
+
+typedef struct gsb_ctx gsb_ctx;
+
+/* ---- context ------------------------------------------------------------------------------- */
+
+/* Creates a context on CUDA device `device`.  No counterpart in the reference (it uses the
+ * legacy default stream and torch's caching allocator: src/cuda/cuda_common.h:22-28,
+ * src/cuda/utils.h:17-28). */
+GSB_API int gsb_ctx_create(int device, gsb_ctx** out_ctx);
+GSB_API int gsb_ctx_destroy(gsb_ctx* ctx);
+GSB_API const char* gsb_status_string(int status);
+/* Message of the last failing CUDA call seen by this context (empty string if none). */
+GSB_API const char* gsb_last_error_message(gsb_ctx* ctx);
+/* Waits for `stream` and returns the first device-side error recorded by kernels of this context
+ * since the last check (GSB_OK if none), then clears it. */
+GSB_API int gsb_check_device_status(gsb_ctx* ctx, void* stream);
+/* Library build information: "gsb200 <version> sm_100a". */
+GSB_API const char* gsb_version(void);
+/* Number of kernel launches issued through this context so far (all entry points). */
+GSB_API int64_t gsb_launch_count(gsb_ctx* ctx);
+/* Copies counters written by the last kernels (total outputs, distinct ids) to the host after
+ * waiting for `stream`. */
+GSB_API int gsb_read_counts(gsb_ctx* ctx, void* stream, int64_t* nnz_host, int64_t* unique_host);
+
+/* ---- column slicing -------------------------------------------------------------------------
+ * Replaces gs::impl::CSCColSlicingCUDA / _OnIndptrSlicing / _GetSubIndicesKernel
+ * (src/cuda/slicing.cu:100-182; dispatcher gs::CSCColSlicing, src/graph_ops.cc:141-154).
+ *
+ * gsb_col_slice_count: out_indptr[i] = sum of the degrees of seeds[0..i) (S+1 entries), computed
+ *   by one kernel; waits for the stream and returns the total in *nnz_host.  seeds == NULL means
+ *   "every column 0..S-1".
+ * gsb_col_slice_fill: for each seed column copies its index segment in order:
+ *   out_indices = GLOBAL row ids, out_select = position in `indices`, out_coo_col (optional) =
+ *   position of the seed in `seeds`.  If `data` is given, out_data[j] = data[e_ids ? e_ids[sel] :
+ *   sel] (the edge-data gather gs::Graph::Slicing performs afterwards, src/graph.cc:295-308).
+ */
+GSB_API int gsb_col_slice_count(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* seeds, int64_t S,
+                                int64_t* out_indptr, int64_t* nnz_host);
+GSB_API int gsb_col_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                               const int64_t* seeds, int64_t S, const int64_t* out_indptr, int64_t* out_indices,
+                               int64_t* out_select, int64_t* out_coo_col, const float* data, const int64_t* e_ids,
+                               float* out_data);
+
+/* ---- uniform per-column sampling ------------------------------------------------------------
+ * Replaces gs::impl::CSCColSamplingCUDA (src/cuda/sampling.cu:12-167; seeds == NULL: all S columns
+ * of the operand) and gs::impl::fusion::FusedCSCColSlicingSamplingCUDA
+ * (src/cuda/fusion/slice_sampling.cu:13-151; seeds given: slice + sample without materialising
+ * the slice, select index into the ORIGINAL indices).
+ *
+ * One kernel computes the per-column counts (without replacement min(deg,k); with replacement k if
+ * deg > 0 else 0), their exclusive scan (out_indptr, S+1 entries) and the samples.  Columns with
+ * deg <= k (without replacement) are copied in order.  Otherwise a uniform k-subset is drawn with
+ * Floyd's algorithm from the Philox stream keyed by (seed, position of the column in the call,
+ * slot).  Output buffers must hold S*k entries (`capacity`); the exact total is left in the
+ * context (gsb_read_counts) and, if nnz_host != NULL, the call waits and returns it there.
+ * Optional: out_coo_col (position of the column), data/e_ids/out_data as in gsb_col_slice_fill.
+ */
+GSB_API int gsb_sample_uniform(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                               const int64_t* seeds, int64_t S, int64_t k, int replace, uint64_t seed,
+                               int64_t* out_indptr, int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col,
+                               const float* data, const int64_t* e_ids, float* out_data, int64_t capacity,
+                               int64_t* nnz_host);
+
+/* Keep-dimension walk step: exactly one draw per seed, -1 / -1 for an isolated seed.  Replaces
+ * gs::impl::fusion::FusedCSCColSlicingSamplingOneKeepDimCUDA (src/cuda/fusion/slice_sampling.cu:156-200). */
+GSB_API int gsb_sample_one_keepdim(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                                   const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
+                                   int64_t* out_indices, int64_t* out_select);
+
+/* ---- unique (first-occurrence order) + relabel ------------------------------------------------
+ * Replaces gs::impl::TensorUniqueCUDA and gs::impl::RelabelCUDA (src/cuda/unique_reindex.cu:80-199;
+ * dispatchers gs::TensorUnique / gs::BatchTensorRelabel, src/graph_ops.cc:249-270).
+ *
+ * The items are the concatenation of up to GSB_MAX_SEGMENTS arrays (the reference torch::cat's
+ * them).  out_unique receives the distinct ids in order of first occurrence (capacity = total
+ * items).  If num_relabel > 0 the concatenation of relabel_ptrs is mapped to positions in
+ * out_unique and written to the matching out_relabel_ptrs (-1 for an id that is not among the
+ * items).  Ids must be >= 0.  Waits for the stream when unique_host != NULL.
+ */
+#define GSB_MAX_SEGMENTS 4
+GSB_API int gsb_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* const* item_ptrs_host,
+                               const int64_t* item_lens_host, int num_item_arrays, int64_t* out_unique,
+                               const int64_t* const* relabel_ptrs_host, const int64_t* relabel_lens_host,
+                               int64_t* const* out_relabel_ptrs_host, int num_relabel, int64_t* unique_host);
+
+/* ---- uniform random walk ----------------------------------------------------------------------
+ * Replaces gs::impl::fusion::FusedRandomWalkCUDA / _RandomWalkKernel
+ * (src/cuda/fusion/random_walk.cu:11-68; gs::Graph::RandomWalk, src/graph.cc:646-648).
+ * trace[0] = seed; each step moves to a uniformly drawn in-neighbour, or to -1 for a node without
+ * any; -1 is absorbing.  layout 0 = the reference's memory order out[step * W + walker]
+ * (which it returns shaped [W, L+1] without transposing); layout 1 = walker-major
+ * out[walker * (L+1) + step].  The draw for (walker w, step s) is keyed by
+ * (seed, walker_offset + w, s), so a sharded run reproduces the unsharded one.
+ */
+GSB_API int gsb_random_walk(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                            const int64_t* seeds, int64_t W, int64_t L, uint64_t seed, int layout,
+                            int64_t walker_offset, int64_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GSB200_H_ */

@@ -472,9 +472,12 @@ GSO_API void gso_random_walk(const i64* indptr, const i64* indices, const i64* s
       if (s == L) break;
       if (cur != -1) {
         i64 b = indptr[cur], d = indptr[cur + 1] - b;
-        if (d > 0)
-          cur = indices[b + (i64)gso_bounded(seed, (uint64_t)(w + walker_offset), (uint64_t)s,
-                                             GSO_STREAM_WALK, (uint64_t)d)];
+        if (d > 0) {
+          /* one 32-bit word per step; degrees are clamped to 2^32-1 for the draw */
+          uint64_t dd = d > 0xFFFFFFFFll ? 0xFFFFFFFFull : (uint64_t)d;
+          uint32_t r = gso_rand_u32(seed, (uint64_t)(w + walker_offset), (uint64_t)s, GSO_STREAM_WALK);
+          cur = indices[b + (i64)(((uint64_t)r * dd) >> 32)];
+        }
         else
           cur = -1;
       }

@@ -1,0 +1,57 @@
+"""CPU-side checks of the C-ABI library: it is built, loads, and exports every symbol the public
+header declares (no kernel is launched here)."""
+import ctypes
+import os
+
+import pytest
+
+from graph_sampling_b200 import build as gsb_build
+from graph_sampling_b200 import cabi
+
+
+@pytest.fixture(scope="module")
+def lib():
+    gsb_build.build()
+    return cabi.load()
+
+
+def test_header_declares_entry_points():
+    syms = cabi.declared_symbols()
+    for must in ["gsb_ctx_create", "gsb_col_slice_count", "gsb_col_slice_fill", "gsb_sample_uniform",
+                 "gsb_unique_relabel", "gsb_random_walk"]:
+        assert must in syms
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for s in cabi.declared_symbols():
+        assert hasattr(lib, s), s
+
+
+def test_status_strings_and_version(lib):
+    assert cabi.status_string(0) == "ok"
+    assert "capacity" in cabi.status_string(-4)
+    assert "sm_100a" in cabi.version()
+
+
+def test_no_torch_dependency_in_kernel_library():
+    # the boundary is plain C: the kernel library must not link against torch / c10
+    out = os.popen(f"ldd {cabi.LIB_PATH}").read()
+    assert "torch" not in out and "c10" not in out
+
+
+def test_ctx_create_fails_cleanly_without_gpu(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    h = ctypes.c_void_p()
+    st = lib.gsb_ctx_create(0, ctypes.byref(h))
+    assert st != 0 and not h.value
+
+
+def test_package_has_no_cpu_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    from graph_sampling_b200 import ops
+    with pytest.raises(RuntimeError):
+        ops.Context()
