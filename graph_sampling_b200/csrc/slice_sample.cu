@@ -280,9 +280,8 @@ int gsb_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
                        const int64_t* seeds, int64_t S, const int64_t* out_indptr, int64_t* out_indices,
                        int64_t* out_select, int64_t* out_coo_col, const float* data, const int64_t* e_ids,
                        float* out_data) {
-  GSB_REQUIRE(ctx && indptr && indices && out_indptr && out_indices && out_select && S >= 0,
-              GSB_ERR_INVALID_ARGUMENT);
-  GSB_REQUIRE((out_data == nullptr) == (data == nullptr), GSB_ERR_INVALID_ARGUMENT);
+  // out_indices / out_select may be null only when the slice is empty (nothing is written then)
+  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (S == 0) return GSB_OK;
   FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data};
   k_slice_fill<<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
@@ -295,9 +294,8 @@ int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
                        const int64_t* seeds, int64_t S, int64_t k, int replace, uint64_t seed, int64_t* out_indptr,
                        int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col, const float* data,
                        const int64_t* e_ids, float* out_data, int64_t capacity, int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && indptr && indices && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
-  GSB_REQUIRE((out_data == nullptr) == (data == nullptr), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   const int grid = grid_for(S, kTileCols);
   TileState ts;
@@ -324,8 +322,7 @@ int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
 int gsb_sample_one_keepdim(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
                            const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
                            int64_t* out_indices, int64_t* out_select) {
-  GSB_REQUIRE(ctx && indptr && indices && seeds && out_indptr && out_indices && out_select && S >= 0,
-              GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
   k_sample_one_keepdim<<<grid_for(S + 1, kThreads), kThreads, 0, (cudaStream_t)stream_>>>(
       indptr, indices, seeds, S, (u64)seed, out_indptr, out_indices, out_select);
   GSB_LAUNCH_OK();
