@@ -45,7 +45,7 @@ def hub_graph():
     rng = np.random.default_rng(5)
     n = 5000
     deg = np.zeros(n, dtype=np.int64)
-    deg[:50] = rng.integers(2000, 6000, 50)       # hubs
+    deg[:50] = rng.integers(2000, 4500, 50)       # hubs
     deg[50:1000] = rng.integers(0, 40, 950)
     deg[1000:1100] = 1
     deg[1100:1200] = 0
