@@ -1,0 +1,203 @@
+// Probability-weighted per-column sampling.
+//
+// Without replacement: Efraimidis-Spirakis A-Res.  Every edge of a column gets the key
+// log2(u) / w (a monotone transform of the reference's u^(1/w), src/cuda/sampling_probs.cu:70-72)
+// from the Philox word keyed by (seed, column position, edge position); the k largest keys win.
+// One warp per column keeps the running top-k as a sorted list, one entry per lane (k <= 32, the
+// reference's own limit: sampling_probs.cu:32).  A new key enters the list only if it beats the
+// current k-th entry, which after the first few dozen edges is rare, so a hub column costs one
+// key evaluation per edge plus O(k log(deg/k)) list insertions — no merge network, no shared
+// memory.  Ties rank the smaller edge position first; the output is in descending key order.
+//
+// With replacement: k inverse-CDF draws over max(w, 0), the CDF being the fp32 running sum in
+// edge order (sampling_probs.cu:137-186 builds it with a warp scan into a temporary buffer; here
+// each drawing lane walks the column, so no scratch memory is needed).
+//
+// Counts, their scan and the selection run in one kernel (tile of columns per CTA, look-back
+// prefix), like the uniform sampler.
+#include "common.cuh"
+#include "philox.cuh"
+#include "scan.cuh"
+
+namespace gsb {
+
+constexpr int kWThreads = 256;
+constexpr int kWTileCols = 64;  // 8 warps x 8 columns each
+
+struct WeightedParams {
+  const i64* indptr;
+  const i64* indices;
+  const float* probs;
+  const i64* seeds;
+  i64 S;
+  i64 k;
+  int replace;
+  u64 seed;
+  i64* out_indptr;
+  i64* out_indices;
+  i64* out_select;
+  i64* out_coo_col;
+  const float* data;
+  const i64* e_ids;
+  float* out_data;
+  i64 capacity;
+  i64* counters;
+  TileState ts;
+};
+
+__device__ __forceinline__ bool ranks_before(float ka, i64 ia, float kb, i64 ib) {
+  return ka > kb || (ka == kb && ia < ib);
+}
+
+__device__ __forceinline__ void emit_weighted(const WeightedParams& p, i64 out_pos, i64 in_pos, i64 col_pos) {
+  p.out_indices[out_pos] = __ldg(p.indices + in_pos);
+  p.out_select[out_pos] = in_pos;
+  if (p.out_coo_col) p.out_coo_col[out_pos] = col_pos;
+  if (p.out_data) p.out_data[out_pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+}
+
+__global__ void __launch_bounds__(kWThreads) k_sample_weighted(WeightedParams p) {
+  __shared__ i64 s_in[kWTileCols];
+  __shared__ i64 s_deg[kWTileCols];
+  __shared__ i64 s_off[kWTileCols];
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_base;
+  const int tile = blockIdx.x, tid = threadIdx.x;
+  const i64 S = p.S, k = p.k;
+  const i64 base = (i64)tile * kWTileCols;
+  if (base >= S && !(S == 0 && tile == 0)) return;
+  const int ncol = (int)max((i64)0, min((i64)kWTileCols, S - base));
+
+  i64 f = 0;
+  if (tid < ncol) {
+    const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
+    const i64 b = p.indptr[col];
+    const i64 d = p.indptr[col + 1] - b;
+    f = p.replace ? (d > 0 ? k : 0) : (d < k ? d : k);
+    s_in[tid] = b;
+    s_deg[tid] = d;
+  }
+  i64 total;
+  const i64 excl = block_exclusive_scan<kWThreads>(f, s_scan, &total);
+  if (tid < kWTileCols) s_off[tid] = excl;
+  if (tid < 32) {
+    const i64 prefix = tile_exclusive_prefix(p.ts, tile, total);
+    if (tid == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const i64 tile_base = s_base;
+  if (tid < ncol) p.out_indptr[base + tid] = tile_base + excl;
+  if (base + kWTileCols >= S && tid == 0) {
+    p.out_indptr[S] = tile_base + total;
+    p.counters[CNT_NNZ] = tile_base + total;
+  }
+  if (tile_base + total > p.capacity) {
+    if (tid == 0) raise_error(p.counters, GSB_ERR_CAPACITY, tile_base + total);
+    return;
+  }
+
+  const int lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = kWThreads / 32;
+  const unsigned kmask = k >= 32 ? 0xffffffffu : ((1u << (int)k) - 1u);
+  const float neg_inf = __uint_as_float(0xFF800000u);
+
+  for (int c = warp; c < ncol; c += kWarps) {
+    const i64 d = s_deg[c], b = s_in[c], o = tile_base + s_off[c], col_pos = base + c;
+    if (p.replace) {
+      if (d == 0) continue;
+      // every drawing lane walks the column: total first, then the first prefix above its draw
+      for (i64 j0 = 0; j0 < k; j0 += 32) {
+        const i64 j = j0 + lane;
+        if (j < k) {
+          float run = 0.f;
+          for (i64 e = 0; e < d; ++e) run = __fadd_rn(run, fmaxf(__ldg(p.probs + b + e), 0.0f));
+          const float r = __fmul_rn(uniform01(rand_u32(p.seed, (u64)col_pos, (u64)j, STREAM_WEIGHTED)), run);
+          float acc = 0.f;
+          i64 pos = d - 1;
+          for (i64 e = 0; e < d; ++e) {
+            acc = __fadd_rn(acc, fmaxf(__ldg(p.probs + b + e), 0.0f));
+            if (acc > r) {
+              pos = e;
+              break;
+            }
+          }
+          emit_weighted(p, o + j, b + pos, col_pos);
+        }
+      }
+      continue;
+    }
+    if (d <= k) {
+      for (i64 j = lane; j < d; j += 32) emit_weighted(p, o + j, b + j, col_pos);
+      continue;
+    }
+    // running top-k: lane j holds the j-th best (key, edge); empty entries rank last
+    float my_key = neg_inf;
+    i64 my_idx = 0x7fffffffffffffffll;
+    float thr_key = neg_inf;
+    i64 thr_idx = 0x7fffffffffffffffll;
+    for (i64 e0 = 0; e0 < d; e0 += 32) {
+      const i64 e = e0 + lane;
+      float ck = neg_inf;
+      bool want = false;
+      if (e < d) {
+        ck = ares_key(rand_u32(p.seed, (u64)col_pos, (u64)e, STREAM_WEIGHTED), __ldg(p.probs + b + e));
+        want = ranks_before(ck, e, thr_key, thr_idx);
+      }
+      unsigned pending = __ballot_sync(0xffffffffu, want);
+      while (pending) {
+        const int src = __ffs(pending) - 1;
+        pending &= pending - 1;
+        const float nk = __shfl_sync(0xffffffffu, ck, src);
+        const i64 ni = e0 + src;
+        if (!ranks_before(nk, ni, thr_key, thr_idx)) continue;  // threshold moved past it
+        // position = number of list entries that rank before the newcomer
+        const bool mine_first = ranks_before(my_key, my_idx, nk, ni);
+        const int pos = __popc(__ballot_sync(0xffffffffu, mine_first) & kmask);
+        const float up_key = __shfl_up_sync(0xffffffffu, my_key, 1);
+        const i64 up_idx = __shfl_up_sync(0xffffffffu, my_idx, 1);
+        if (lane > pos) {
+          my_key = up_key;
+          my_idx = up_idx;
+        } else if (lane == pos) {
+          my_key = nk;
+          my_idx = ni;
+        }
+        thr_key = __shfl_sync(0xffffffffu, my_key, (int)k - 1);
+        thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
+      }
+    }
+    if (lane < k) emit_weighted(p, o + lane, b + my_idx, col_pos);
+  }
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+                                   const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
+                                   uint64_t seed, int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
+                                   int64_t* out_coo_col, const float* data, const int64_t* e_ids, float* out_data,
+                                   int64_t capacity, int64_t* nnz_host) {
+  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(replace || k <= 32, GSB_ERR_UNSUPPORTED);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int grid = grid_for(S, kWTileCols);
+  TileState ts;
+  int st = ctx_tile_state(ctx, grid, stream, &ts);
+  if (st != GSB_OK) return st;
+  WeightedParams p{indptr, indices,    probs,       seeds, S,     k,        replace,  (u64)seed,         out_indptr,
+                   out_indices, out_select, out_coo_col, data,  e_ids, out_data, capacity, ctx_counters(ctx), ts};
+  k_sample_weighted<<<grid, kWThreads, 0, stream>>>(p);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  if (nnz_host) {
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);
+    if (st != GSB_OK) return st;
+    *nnz_host = c[CNT_NNZ];
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  }
+  return GSB_OK;
+}

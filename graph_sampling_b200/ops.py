@@ -246,3 +246,204 @@ def fused_random_walk(seeds, walk_length, indices, indptr, seed=None, layout=0, 
                                       c_u64(next_seed(seed)), c_int(int(layout)), c_i64(int(walker_offset)), _p(out)),
               "gsb_random_walk")
     return out.reshape(W, L + 1)
+
+
+# ---------------------------------------------------------------------------------------------
+def csc_col_sampling_probs(indptr, indices, probs, fanout, replace, with_coo=True, seed=None, column_ids=None,
+                           data=None, e_ids=None, ctx=None):
+    """CSCColSamplingProbsCUDA (src/cuda/sampling_probs.cu:267-282) → (sub_indptr, coo_col | None,
+    sub_indices, select_index[, data]).  `probs[j]` pairs with `indices[j]`.  `column_ids` (not in the
+    reference) fuses a column slice in front."""
+    indptr, indices, probs = _i64(indptr, "indptr"), _i64(indices, "indices"), _f32(probs, "probs")
+    column_ids = _i64(column_ids, "column_ids", allow_none=True)
+    data, e_ids = _f32(data, "data", True), _i64(e_ids, "e_ids", True)
+    if probs.numel() != indices.numel():
+        raise ValueError("probs must have one entry per edge of the operand")
+    ctx = ctx or default_context(indptr.device)
+    S = column_ids.numel() if column_ids is not None else indptr.numel() - 1
+    cap = S * int(fanout)
+    sub_indptr = _empty(S + 1, indptr)
+    sub_indices, select = _empty(cap, indptr), _empty(cap, indptr)
+    coo_col = _empty(cap, indptr) if with_coo else None
+    out_data = _empty(cap, indptr, torch.float32) if data is not None else None
+    nnz = c_i64(0)
+    ctx.check(ctx.lib.gsb_sample_weighted(ctx.handle, _stream(), _p(indptr), _p(indices), _p(probs), _p(column_ids),
+                                          c_i64(S), c_i64(int(fanout)), c_int(int(bool(replace))),
+                                          c_u64(next_seed(seed)), _p(sub_indptr), _p(sub_indices), _p(select),
+                                          _p(coo_col), _p(data), _p(e_ids), _p(out_data), c_i64(cap),
+                                          ctypes.byref(nnz)), "gsb_sample_weighted")
+    n = nnz.value
+    out = [sub_indptr, coo_col[:n] if with_coo else None, sub_indices[:n], select[:n]]
+    if data is not None:
+        out.append(out_data[:n])
+    return tuple(out)
+
+
+def list_sampling(data, num_picks, replace, probs=None, seed=None, ctx=None):
+    """ListSamplingCUDA (src/cuda/list_sampling.cu:76-83) / ListSamplingProbsCUDA
+    (src/cuda/list_sampling_probs.cu:185-191) → (selected_data, selected_index)."""
+    data = _i64(data, "data")
+    probs = _f32(probs, "probs", allow_none=True)
+    if probs is not None and probs.numel() != data.numel():
+        raise ValueError("probs must have one entry per item")
+    ctx = ctx or default_context(data.device)
+    N, k = data.numel(), int(num_picks)
+    cap = max(N if (not replace and N <= k) else k, 1)
+    out_d, out_i = _empty(cap, data), _empty(cap, data)
+    n_out = c_i64(0)
+    ctx.check(ctx.lib.gsb_list_sample(ctx.handle, _stream(), _p(data), _p(probs), c_i64(N), c_i64(k),
+                                      c_int(int(bool(replace))), c_u64(next_seed(seed)), _p(out_d), _p(out_i),
+                                      ctypes.byref(n_out)), "gsb_list_sample")
+    return out_d[:n_out.value], out_i[:n_out.value]
+
+
+SDDMM_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "copy_lhs": 4, "copy_rhs": 5, "dot": 6}
+
+
+def calc_bcast_off(op, lhs, rhs):
+    """CalcBcastOff (src/bcast.cc:24-76) on tensor shapes → dict(lhs_len, rhs_len, out_len, reduce_size,
+    lhs_off, rhs_off); the offset lists are None when no broadcasting is needed."""
+    ls, rs = list(lhs.shape), list(rhs.shape)
+    lhs_len = 1
+    for d in ls[1:]:
+        lhs_len *= d
+    rhs_len = 1
+    for d in rs[1:]:
+        rhs_len *= d
+    use_bcast = False
+    if op not in ("copy_lhs", "copy_rhs"):
+        use_bcast = len(ls) != len(rs) or any(ls[i] != rs[i] for i in range(1, len(ls)))
+    reduce_size, lhs_off, rhs_off = 1, None, None
+    if use_bcast:
+        max_ndim = max(len(ls), len(rs)) - 1
+        out_len, j = 1, 0
+        if op == "dot":
+            reduce_size = ls[-1]
+            j = 1
+        stride_l = stride_r = 1
+        lhs_off, rhs_off = [0], [0]
+        while j < max_ndim:
+            dl = 1 if len(ls) - 1 - j < 1 else ls[len(ls) - 1 - j]
+            dr = 1 if len(rs) - 1 - j < 1 else rs[len(rs) - 1 - j]
+            for i in range(1, max(dl, dr)):
+                for q in range(out_len):
+                    lhs_off.append(lhs_off[q] + i * (1 if i < dl else 0) * stride_l)
+                    rhs_off.append(rhs_off[q] + i * (1 if i < dr else 0) * stride_r)
+            out_len *= max(dl, dr)
+            stride_l *= dl
+            stride_r *= dr
+            j += 1
+    else:
+        out_len = rhs_len if op == "copy_rhs" else lhs_len
+        if op == "dot":
+            reduce_size = ls[-1]
+            out_len //= reduce_size
+    return dict(lhs_len=lhs_len, rhs_len=rhs_len, out_len=out_len, reduce_size=reduce_size, lhs_off=lhs_off,
+                rhs_off=rhs_off)
+
+
+def sddmm(op, lhs, rhs, out, lhs_target, rhs_target, row, col=None, indptr=None, e_ids=None, ctx=None):
+    """SDDMMCOO (col given) / SDDMMCSC (col=None, indptr given) (src/cuda/sddmm.cu:255-291): writes
+    op(lhs[target], rhs[target]) per edge into the caller's `out` ([E, out_len], fp32)."""
+    if op not in SDDMM_OPS:
+        raise ValueError(f"unknown SDDMM op {op!r}")
+    row = _i64(row, "row")
+    col, indptr, e_ids = _i64(col, "col", True), _i64(indptr, "indptr", True), _i64(e_ids, "e_ids", True)
+    lhs, rhs = _f32(lhs, "lhs", op == "copy_rhs"), _f32(rhs, "rhs", op == "copy_lhs")
+    if not (isinstance(out, torch.Tensor) and out.is_cuda and out.dtype == torch.float32 and out.is_contiguous()):
+        raise TypeError("out must be a contiguous float32 CUDA tensor")
+    ctx = ctx or default_context(row.device)
+    bc = calc_bcast_off(op, lhs if lhs is not None else rhs, rhs if rhs is not None else lhs)
+    E = row.numel()
+    if out.numel() != E * bc["out_len"]:
+        raise ValueError(f"out has {out.numel()} elements, expected {E} x {bc['out_len']}")
+    lo = torch.tensor(bc["lhs_off"], dtype=torch.int64, device=row.device) if bc["lhs_off"] is not None else None
+    ro = torch.tensor(bc["rhs_off"], dtype=torch.int64, device=row.device) if bc["rhs_off"] is not None else None
+    num_cols = indptr.numel() - 1 if indptr is not None else 0
+    ctx.check(ctx.lib.gsb_sddmm(ctx.handle, _stream(), c_int(SDDMM_OPS[op]), _p(row), _p(col), _p(indptr),
+                                c_i64(num_cols), _p(e_ids), c_i64(E), _p(lhs), _p(rhs), _p(out), c_int(int(lhs_target)),
+                                c_int(int(rhs_target)), c_i64(bc["lhs_len"]), c_i64(bc["rhs_len"]), c_i64(bc["out_len"]),
+                                c_i64(bc["reduce_size"]), _p(lo), _p(ro)), "gsb_sddmm")
+    return out
+
+
+def csc_sum(indptr, e_ids, data, out, powk, ctx=None):
+    """CSCSumCUDA (src/cuda/graph_ops.cu:66-96): out[s] = sum over segment s of data^powk (data=None → ones)."""
+    indptr, e_ids, data = _i64(indptr, "indptr"), _i64(e_ids, "e_ids", True), _f32(data, "data", True)
+    ctx = ctx or default_context(indptr.device)
+    ctx.check(ctx.lib.gsb_segment_sum_csc(ctx.handle, _stream(), _p(indptr), c_i64(indptr.numel() - 1), _p(e_ids),
+                                          _p(data), c_i64(int(powk)), _p(out)), "gsb_segment_sum_csc")
+    return out
+
+
+def coo_sum(target, e_ids, data, out, powk, ctx=None):
+    """COOSumCUDA (src/cuda/graph_ops.cu:98-125): out[target[e]] += data[e]^powk; `out` must be zeroed."""
+    target, e_ids, data = _i64(target, "target"), _i64(e_ids, "e_ids", True), _f32(data, "data", True)
+    ctx = ctx or default_context(target.device)
+    ctx.check(ctx.lib.gsb_segment_sum_coo(ctx.handle, _stream(), _p(target), c_i64(target.numel()), _p(e_ids),
+                                          _p(data), c_i64(int(powk)), _p(out)), "gsb_segment_sum_coo")
+    return out
+
+
+def csc_normalize(indptr, e_ids, data, out, ctx=None):
+    """CSCNormalizeCUDA (src/cuda/graph_ops.cu:160-188): out[e] = data[e] / (sum of its segment)."""
+    indptr, e_ids, data = _i64(indptr, "indptr"), _i64(e_ids, "e_ids", True), _f32(data, "data")
+    ctx = ctx or default_context(indptr.device)
+    ctx.check(ctx.lib.gsb_segment_normalize_csc(ctx.handle, _stream(), _p(indptr), c_i64(indptr.numel() - 1),
+                                                _p(e_ids), _p(data), _p(out)), "gsb_segment_normalize_csc")
+    return out
+
+
+def csc_row_slicing(indptr, indices, row_ids, with_coo=True, ctx=None):
+    """CSCRowSlicingCUDA (src/cuda/slicing.cu:528-539) → (out_indptr, coo_col | None, out_indices,
+    select_index); kept row ids are renumbered to their position in row_ids."""
+    indptr, indices, row_ids = _i64(indptr, "indptr"), _i64(indices, "indices"), _i64(row_ids, "row_ids")
+    ctx = ctx or default_context(indptr.device)
+    nc, E = indptr.numel() - 1, indices.numel()
+    out_indptr = _empty(nc + 1, indptr)
+    oi, osel = _empty(E, indptr), _empty(E, indptr)
+    oc = _empty(E, indptr) if with_coo else None
+    nnz = c_i64(0)
+    ctx.check(ctx.lib.gsb_row_slice_csc(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(nc), c_i64(E),
+                                        _p(row_ids), c_i64(row_ids.numel()), _p(out_indptr), _p(oi), _p(osel), _p(oc),
+                                        ctypes.byref(nnz)), "gsb_row_slice_csc")
+    n = nnz.value
+    return out_indptr, (oc[:n] if with_coo else None), oi[:n], osel[:n]
+
+
+def coo_row_slicing(coo_row, coo_col, row_ids, ctx=None):
+    """COORowSlicingCUDA (src/cuda/slicing.cu:768-771) → (renumbered_row, col, select_index)."""
+    coo_row, coo_col, row_ids = _i64(coo_row, "coo_row"), _i64(coo_col, "coo_col"), _i64(row_ids, "row_ids")
+    ctx = ctx or default_context(coo_row.device)
+    E = coo_row.numel()
+    o_r, o_c, o_s = _empty(E, coo_row), _empty(E, coo_row), _empty(E, coo_row)
+    nnz = c_i64(0)
+    ctx.check(ctx.lib.gsb_row_slice_coo(ctx.handle, _stream(), _p(coo_row), _p(coo_col), c_i64(E), _p(row_ids),
+                                        c_i64(row_ids.numel()), _p(o_r), _p(o_c), _p(o_s), ctypes.byref(nnz)),
+              "gsb_row_slice_coo")
+    n = nnz.value
+    return o_r[:n], o_c[:n], o_s[:n]
+
+
+def csc2coo(indptr, indices, ctx=None):
+    """CSC2COOCUDA (src/cuda/format_transform.cu:35-46) → (row = indices, col)."""
+    indptr, indices = _i64(indptr, "indptr"), _i64(indices, "indices")
+    ctx = ctx or default_context(indptr.device)
+    col = _empty(indices.numel(), indptr)
+    ctx.check(ctx.lib.gsb_csc2coo(ctx.handle, _stream(), _p(indptr), c_i64(indptr.numel() - 1), _p(col)),
+              "gsb_csc2coo")
+    return indices, col
+
+
+def coo2csc(row, col, num_cols, col_sorted, ctx=None):
+    """COO2CSCCUDA (src/cuda/format_transform.cu:135-156) → (indptr, sorted_row, sort_index | None).
+    For CSR pass (col, row, num_rows, row_sorted)."""
+    row, col = _i64(row, "row"), _i64(col, "col")
+    ctx = ctx or default_context(row.device)
+    E = row.numel()
+    indptr = _empty(int(num_cols) + 1, row)
+    out_row = _empty(E, row)
+    perm = None if col_sorted else _empty(E, row)
+    ctx.check(ctx.lib.gsb_coo2csc(ctx.handle, _stream(), _p(col), _p(row), c_i64(E), c_i64(int(num_cols)),
+                                  c_int(int(bool(col_sorted))), _p(indptr), _p(out_row), _p(perm)), "gsb_coo2csc")
+    return indptr, out_row, perm

@@ -144,6 +144,95 @@ GSB_API int gsb_random_walk(gsb_ctx* ctx, void* stream, const int64_t* indptr, c
                             const int64_t* seeds, int64_t W, int64_t L, uint64_t seed, int layout,
                             int64_t walker_offset, int64_t* out);
 
+/* ---- weighted per-column sampling -------------------------------------------------------------
+ * Replaces gs::impl::CSCColSamplingProbsCUDA (src/cuda/sampling_probs.cu:23-282; dispatcher
+ * gs::CSCColSamplingProbs, src/graph_ops.cc:207-221).  `probs[j]` pairs with `indices[j]` of the
+ * operand.  Without replacement: A-Res (Efraimidis-Spirakis), the k entries with the largest
+ * u^(1/w) win (ranked through log2(u)/w), k <= 32 like the reference (sampling_probs.cu:32,
+ * GSB_ERR_UNSUPPORTED above that); columns with deg <= k are copied; output per column in
+ * descending key order; weights <= 0 rank below every positive weight.  With replacement: k
+ * inverse-CDF draws over max(w, 0).  seeds == NULL samples all S columns of the operand; seeds
+ * given fuses the column slice (no reference counterpart for the fused form).  Buffers, counts
+ * and optional outputs as in gsb_sample_uniform.
+ */
+GSB_API int gsb_sample_weighted(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                                const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
+                                uint64_t seed, int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
+                                int64_t* out_coo_col, const float* data, const int64_t* e_ids, float* out_data,
+                                int64_t capacity, int64_t* nnz_host);
+
+/* ---- list sampling ------------------------------------------------------------------------------
+ * Replaces gs::impl::ListSamplingCUDA (src/cuda/list_sampling.cu:20-83) when probs == NULL and
+ * gs::impl::ListSamplingProbsCUDA (src/cuda/list_sampling_probs.cu:11-91, 185-191) otherwise;
+ * front ends gs::ListSampling / gs::ListSamplingProbs (src/tensor_ops.cc:5-16).
+ * Picks k of the N items: out_data[j] = data[out_index[j]].  Without replacement and N <= k the
+ * result is the whole list in order.  Without replacement otherwise: the k best ranking keys
+ * (uniform: a random word per item; weighted: A-Res key, p <= 0 never ahead of a positive p),
+ * output in descending key order.  With replacement: k draws, uniform or by inverse CDF of
+ * max(p, 0).  Output buffers must hold max(k, N <= k ? N : k) entries; the number written is
+ * returned in *n_out_host (known on the host without waiting).  N must be below 2^32 - 1.
+ */
+GSB_API int gsb_list_sample(gsb_ctx* ctx, void* stream, const int64_t* data, const float* probs, int64_t N,
+                            int64_t k, int replace, uint64_t seed, int64_t* out_data, int64_t* out_index,
+                            int64_t* n_out_host);
+
+/* ---- SDDMM ------------------------------------------------------------------------------------------
+ * Replaces gs::impl::SDDMMCOO / SDDMMCSC (src/cuda/sddmm.cu:164-291; gs::Graph::SDDMM,
+ * src/graph.cc:967-985).  out[eid, t] = op(lhs[sel_l, lhs_off[t]*R ..], rhs[sel_r, rhs_off[t]*R ..])
+ * for every edge; op: 0 add, 1 sub, 2 mul, 3 div, 4 copy_lhs, 5 copy_rhs, 6 dot (src/cuda/functor.h:9-140);
+ * targets 0 = row (source), 1 = edge, 2 = column (destination) (src/cuda/selector.h); R =
+ * reduce_size (1 unless dot); lhs_len / rhs_len = elements per lhs / rhs row; lhs_off / rhs_off =
+ * broadcast offset tables of CalcBcastOff (src/bcast.cc:24-76) or NULL for the identity.
+ * COO form: row + col per edge.  CSC form: col == NULL, `indptr` (num_cols + 1 entries) locates the
+ * column of each edge.  e_ids (optional) maps edge position to the output / edge-feature row.
+ * `out` is caller-allocated [E, out_len].
+ */
+GSB_API int gsb_sddmm(gsb_ctx* ctx, void* stream, int op, const int64_t* row, const int64_t* col,
+                      const int64_t* indptr, int64_t num_cols, const int64_t* e_ids, int64_t E, const float* lhs,
+                      const float* rhs, float* out, int lhs_target, int rhs_target, int64_t lhs_len, int64_t rhs_len,
+                      int64_t out_len, int64_t reduce_size, const int64_t* lhs_off, const int64_t* rhs_off);
+
+/* ---- segment sum / normalise ---------------------------------------------------------------------
+ * Replace gs::impl::CSCSumCUDA, COOSumCUDA, CSCNormalizeCUDA (src/cuda/graph_ops.cu:15-188; used by
+ * gs::Graph::Sum / Normalize, src/graph.cc:650-702).  sum: out[s] = sum over the segment of
+ * data[e]^powk (data == NULL means ones; exact integer power); the COO form accumulates into a
+ * caller-zeroed dense vector indexed by target[e].  normalize: out[e] = data[e] / segment sum.
+ * e_ids maps segment position to data position when present.
+ */
+GSB_API int gsb_segment_sum_csc(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64_t num_seg,
+                                const int64_t* e_ids, const float* data, int64_t powk, float* out);
+GSB_API int gsb_segment_sum_coo(gsb_ctx* ctx, void* stream, const int64_t* target, int64_t E, const int64_t* e_ids,
+                                const float* data, int64_t powk, float* out_zeroed);
+GSB_API int gsb_segment_normalize_csc(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64_t num_seg,
+                                      const int64_t* e_ids, const float* data, float* out);
+
+/* ---- row slicing -------------------------------------------------------------------------------------
+ * Replace gs::impl::CSCRowSlicingCUDA (src/cuda/slicing.cu:416-539) and COORowSlicingCUDA
+ * (:543-563, 727-771); dispatchers gs::CSCRowSlicing / gs::COOColSlicing (src/graph_ops.cc:127-139,
+ * 173-190).  Keeps the edges whose row id occurs in row_ids; the kept row id becomes its position
+ * in row_ids; edge order is preserved; out_select = kept edge positions.  CSC form: out_indptr has
+ * num_cols + 1 entries (all operand columns), out_coo_col (optional) = column of each kept edge.
+ * Output buffers must hold E entries; the kept count is returned in *nnz_host (waits).
+ */
+GSB_API int gsb_row_slice_csc(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                              int64_t num_cols, int64_t E, const int64_t* row_ids, int64_t R, int64_t* out_indptr,
+                              int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col, int64_t* nnz_host);
+GSB_API int gsb_row_slice_coo(gsb_ctx* ctx, void* stream, const int64_t* coo_row, const int64_t* coo_col, int64_t E,
+                              const int64_t* row_ids, int64_t R, int64_t* out_row, int64_t* out_col,
+                              int64_t* out_select, int64_t* nnz_host);
+
+/* ---- format conversion ---------------------------------------------------------------------------------
+ * gsb_csc2coo replaces gs::impl::CSC2COOCUDA (src/cuda/format_transform.cu:35-46): out_col[e] = the
+ * column whose offset range contains edge e.
+ * gsb_coo2csc replaces gs::impl::COO2CSCCUDA + COOSort (:80-156; gs::GraphCOO2CSC,
+ * src/graph_ops.cc:32-60): offsets over num_keys keys (out_indptr, num_keys + 1 entries) and, unless
+ * key_sorted, a STABLE sort of the edges by key: out_perm = the permutation, out_other = other[perm].
+ * Pass (col, row) for CSC and (row, col) for CSR.
+ */
+GSB_API int gsb_csc2coo(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64_t num_cols, int64_t* out_col);
+GSB_API int gsb_coo2csc(gsb_ctx* ctx, void* stream, const int64_t* key, const int64_t* other, int64_t E,
+                        int64_t num_keys, int key_sorted, int64_t* out_indptr, int64_t* out_other, int64_t* out_perm);
+
 #ifdef __cplusplus
 }
 #endif
