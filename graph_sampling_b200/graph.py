@@ -1,0 +1,579 @@
+"""`Graph`: the host-side mirror of the reference's `gs::Graph` (src/graph.h:13-126, src/graph.cc) for
+the sampling hot path.  It keeps the same state (CSC / CSR / COO views created lazily, optional
+edge data, row / column id maps), the same method names, argument meaning and result layout, and
+forwards every piece of arithmetic to the sm_100a kernels through the C ABI (graph_sampling_b200.ops).
+
+Differences kept on purpose:
+  * errors raise Python exceptions where the reference LOG(FATAL)s and aborts the process;
+  * the edge-data gather that follows slicing / sampling is fused into the kernel;
+  * stochastic methods take their seed from `ops.set_seed` / an optional `seed=` argument (the
+    reference hard-codes 7777 and returns the same sample on every call);
+  * DCSC / DCSR (compact id) layouts, batched ("super-batch") methods and pinned-host graphs are
+    not part of this path and raise NotImplementedError.
+Every method is registered under the CamelCase name of src/pybind.cc and under the snake_case name
+the reference's Python layer calls (python/gs/matrix_api/matrix.py).
+"""
+import torch
+
+from . import ops
+
+_COO, _CSC, _CSR, _DCSC, _DCSR = 1, 2, 4, 8, 16
+
+
+class CSC:
+    """struct CSC / CSR (src/graph_storage.h:9-15)."""
+    __slots__ = ("indptr", "indices", "e_ids")
+
+    def __init__(self, indptr, indices, e_ids=None):
+        self.indptr, self.indices, self.e_ids = indptr, indices, e_ids
+
+
+class COO:
+    """struct COO (src/graph_storage.h:17-23)."""
+    __slots__ = ("row", "col", "e_ids", "row_sorted", "col_sorted")
+
+    def __init__(self, row, col, e_ids=None, row_sorted=False, col_sorted=False):
+        self.row, self.col, self.e_ids = row, col, e_ids
+        self.row_sorted, self.col_sorted = row_sorted, col_sorted
+
+
+def _fatal(msg):
+    raise RuntimeError(msg)
+
+
+class Graph:
+    def __init__(self, is_subgraph=False, col_ids=None, row_ids=None, num_cols=0, num_rows=0):
+        self.is_subgraph_ = bool(is_subgraph)
+        self.num_cols_, self.num_rows_, self.num_edges_ = int(num_cols), int(num_rows), 0
+        self.csc_ = self.csr_ = self.coo_ = None
+        self.data_ = None
+        self.col_ids_, self.row_ids_ = col_ids, row_ids
+        self.val_col_ids_ = self.val_row_ids_ = None
+
+    # ---- loading (src/graph.cc:14-60) -------------------------------------------------------------
+    def LoadCSC(self, indptr, indices):
+        self.csc_ = CSC(indptr, indices)
+        self.num_cols_ = self.num_rows_ = indptr.numel() - 1
+        self.num_edges_ = indices.numel()
+
+    def LoadCSR(self, indptr, indices):
+        self.csr_ = CSC(indptr, indices)
+        self.num_cols_ = self.num_rows_ = indptr.numel() - 1
+        self.num_edges_ = indices.numel()
+
+    def LoadCOO(self, row, col):
+        self.coo_ = COO(row, col)
+        n = max(torch.unique(row).numel(), torch.unique(col).numel())
+        self.num_cols_ = self.num_rows_ = n
+        self.num_edges_ = row.numel()
+
+    def LoadCSCWithColIds(self, column_ids, indptr, indices):
+        if column_ids.numel() != indptr.numel() - 1:
+            _fatal("length of column_ids is not aligned with indptr")
+        self.csc_ = CSC(indptr, indices)
+        self.col_ids_ = column_ids
+        self.num_cols_ = column_ids.numel()
+        self.num_rows_ = int(indices.max().item()) + 1 if indices.numel() else 0
+        self.num_edges_ = indices.numel()
+
+    def SetMetaData(self, col_ids, row_ids, num_cols, num_rows):
+        self.col_ids_, self.row_ids_ = col_ids, row_ids
+        self.num_cols_, self.num_rows_ = int(num_cols), int(num_rows)
+
+    def SetCOOByTensor(self, row, col, e_ids, row_sorted, col_sorted):
+        self.coo_ = COO(row, col, e_ids, bool(row_sorted), bool(col_sorted))
+
+    def SetData(self, data):
+        self.data_ = data
+
+    def SetNumEdges(self, n):
+        self.num_edges_ = int(n)
+
+    def GetNumRows(self):
+        return self.num_rows_
+
+    def GetNumCols(self):
+        return self.num_cols_
+
+    def GetNumEdges(self):
+        return self.num_edges_
+
+    def _device(self):
+        for f in (self.csc_, self.csr_):
+            if f is not None:
+                return f.indptr.device
+        return self.coo_.row.device
+
+    def _data_or_ones(self):
+        if self.data_ is not None:
+            return self.data_
+        return torch.ones(self.num_edges_, dtype=torch.float32, device=self._device())
+
+    def GetData(self, order="default"):
+        """src/graph.cc:68-90."""
+        data = self._data_or_ones()
+        idx = None
+        if order == "col":
+            self.CreateSparseFormat(_CSC)
+            idx = self.csc_.e_ids
+        elif order == "row":
+            self.CreateSparseFormat(_CSR)
+            idx = self.csr_.e_ids
+        return data[idx] if idx is not None else data
+
+    # ---- lazy format creation (src/graph.cc:585-644, src/graph_ops.cc:13-60) ---------------------------
+    def _csc2coo(self, csc, is_csc):
+        expanded = ops.csc2coo(csc.indptr, csc.indices)[1]
+        if is_csc:
+            return COO(csc.indices, expanded, csc.e_ids, False, True)
+        return COO(expanded, csc.indices, csc.e_ids, True, False)
+
+    def _coo2csc(self, coo, num_items, to_csc):
+        if to_csc:
+            indptr, indices, sort_index = ops.coo2csc(coo.row, coo.col, num_items, coo.col_sorted)
+        else:
+            indptr, indices, sort_index = ops.coo2csc(coo.col, coo.row, num_items, coo.row_sorted)
+        if coo.e_ids is not None:
+            e_ids = coo.e_ids[sort_index] if sort_index is not None else coo.e_ids
+        else:
+            e_ids = sort_index
+        return CSC(indptr, indices, e_ids)
+
+    def CreateSparseFormat(self, fmt):
+        if fmt == _COO:
+            if self.coo_ is not None:
+                return
+            if self.csc_ is not None:
+                self.coo_ = self._csc2coo(self.csc_, True)
+            else:
+                self.coo_ = self._csc2coo(self.csr_, False)
+        elif fmt == _CSC:
+            if self.csc_ is not None:
+                return
+            if self.coo_ is None:
+                self.coo_ = self._csc2coo(self.csr_, False)
+            self.csc_ = self._coo2csc(self.coo_, self.num_cols_, True)
+        elif fmt == _CSR:
+            if self.csr_ is not None:
+                return
+            if self.coo_ is None:
+                self.coo_ = self._csc2coo(self.csc_, True)
+            self.csr_ = self._coo2csc(self.coo_, self.num_rows_, False)
+        elif fmt in (_DCSC, _DCSR):
+            raise NotImplementedError("compact-id (DCSC / DCSR) layouts are outside the sampling hot path")
+        else:
+            _fatal("unknown sparse format")
+
+    # ---- helpers -----------------------------------------------------------------------------------------
+    def _child(self, col_ids, row_ids, num_cols, num_rows):
+        return Graph(True, col_ids, row_ids, num_cols, num_rows)
+
+    def _gather_args(self, fmt_struct):
+        """(data, e_ids) handed to a kernel so that it emits data_[e_ids?[select_index]] itself."""
+        if self.data_ is None:
+            return None, None
+        return self.data_, fmt_struct.e_ids
+
+    # ---- Slicing (src/graph.cc:173-310) ----------------------------------------------------------------------
+    def Slicing(self, n_ids, axis, on_format, output_format, relabel=False):
+        self.CreateSparseFormat(on_format)
+        with_coo = bool(output_format & _COO)
+        if axis == 0:
+            new_col_ids = self.col_ids_[n_ids] if self.col_ids_ is not None else n_ids
+            new_row_ids, new_num_cols, new_num_rows = self.row_ids_, n_ids.numel(), self.num_rows_
+        else:
+            new_col_ids = self.col_ids_
+            new_row_ids = self.row_ids_[n_ids] if self.row_ids_ is not None else n_ids
+            new_num_cols, new_num_rows = self.num_cols_, n_ids.numel()
+        csc_ptr = csr_ptr = coo_ptr = None
+        out_data = None
+
+        if on_format == _COO:
+            coo = self.coo_
+            if axis == 0:   # keep edges whose column is in n_ids (COOColSlicing, src/graph_ops.cc:173-190)
+                new_col, new_row, select = ops.coo_row_slicing(coo.col, coo.row, n_ids)
+            else:
+                new_row, new_col, select = ops.coo_row_slicing(coo.row, coo.col, n_ids)
+            coo_ptr = COO(new_row, new_col, None, coo.row_sorted, coo.col_sorted)
+            new_num_edges = new_row.numel()
+            e_ids = coo.e_ids
+            if self.data_ is not None:
+                out_data = self.data_[e_ids[select] if e_ids is not None else select]
+        elif on_format == _CSC:
+            if output_format == _CSR:
+                _fatal("Error in Slicing, Not implementation [on_format = CSC, output_forat = CSR]")
+            data, e_ids = self._gather_args(self.csc_)
+            if axis == 0:
+                r = ops.csc_col_slicing(self.csc_.indptr, self.csc_.indices, n_ids, with_coo, data=data, e_ids=e_ids)
+                indptr, coo_col, indices = r[0], r[1], r[2]
+                out_data = r[4] if data is not None else None
+                if relabel:
+                    frontier, (indices,) = ops.relabel([indices], [indices])
+                    new_row_ids, new_num_rows = frontier, frontier.numel()
+            else:
+                if relabel:
+                    _fatal("Not implemented warning")
+                indptr, coo_col, indices, select = ops.csc_row_slicing(self.csc_.indptr, self.csc_.indices, n_ids,
+                                                                       with_coo)
+                if data is not None:
+                    out_data = data[e_ids[select] if e_ids is not None else select]
+            if output_format & _CSC:
+                csc_ptr = CSC(indptr, indices)
+            if output_format & _COO:
+                coo_ptr = COO(indices, coo_col, None, False, True)
+            new_num_edges = indices.numel()
+        elif on_format == _CSR:
+            if output_format == _CSC:
+                _fatal("Error in Slicing, Not implementation [on_format = CSR, output_forat = CSC]")
+            data, e_ids = self._gather_args(self.csr_)
+            if axis == 0:
+                if relabel:
+                    _fatal("Not implemented warning")
+                indptr, coo_row, indices, select = ops.csc_row_slicing(self.csr_.indptr, self.csr_.indices, n_ids,
+                                                                       with_coo)
+                if data is not None:
+                    out_data = data[e_ids[select] if e_ids is not None else select]
+            else:
+                r = ops.csc_col_slicing(self.csr_.indptr, self.csr_.indices, n_ids, with_coo, data=data, e_ids=e_ids)
+                indptr, coo_row, indices = r[0], r[1], r[2]
+                out_data = r[4] if data is not None else None
+                if relabel:
+                    frontier, (indices,) = ops.relabel([indices], [indices])
+                    new_col_ids, new_num_cols = frontier, frontier.numel()
+            if output_format & _CSR:
+                csr_ptr = CSC(indptr, indices)
+            if output_format & _COO:
+                coo_ptr = COO(coo_row, indices, None, True, False)
+            new_num_edges = indices.numel()
+        else:
+            raise NotImplementedError("Slicing on DCSC / DCSR is outside the sampling hot path")
+
+        ret = self._child(new_col_ids, new_row_ids, new_num_cols, new_num_rows)
+        ret.num_edges_ = new_num_edges
+        ret.coo_, ret.csc_, ret.csr_ = coo_ptr, csc_ptr, csr_ptr
+        if out_data is not None:
+            ret.data_ = out_data
+        return ret
+
+    # ---- Sampling / SamplingProbs (src/graph.cc:393-529) ---------------------------------------------------
+    def _sampling_impl(self, axis, fanout, replace, on_format, output_format, probs, seed):
+        self.CreateSparseFormat(on_format)
+        with_coo = bool(output_format & _COO)
+        ret = self._child(self.col_ids_, self.row_ids_, self.num_cols_, self.num_rows_)
+        if axis == 0 and on_format == _CSC:
+            if output_format == _CSR:
+                _fatal("Error in Sampling, Not implementation [on_format = CSC, output_forat = CSR]")
+            fmt = self.csc_
+        elif axis == 1 and on_format == _CSR:
+            if output_format == _CSC:
+                _fatal("Error in Sampling, Not implementation [on_format = CSR, output_forat = CSC]")
+            fmt = self.csr_
+        else:
+            _fatal("No implementation!")
+        data, e_ids = self._gather_args(fmt)
+        if probs is None:
+            r = ops.csc_col_sampling(fmt.indptr, fmt.indices, fanout, replace, with_coo, seed=seed, data=data,
+                                     e_ids=e_ids)
+        else:
+            r = ops.csc_col_sampling_probs(fmt.indptr, fmt.indices, probs, fanout, replace, with_coo, seed=seed,
+                                           data=data, e_ids=e_ids)
+        indptr, coo_other, indices = r[0], r[1], r[2]
+        if axis == 0:
+            if output_format & _CSC:
+                ret.csc_ = CSC(indptr, indices)
+            if output_format & _COO:
+                ret.coo_ = COO(indices, coo_other, None, False, True)
+        else:
+            if output_format & _CSR:
+                ret.csr_ = CSC(indptr, indices)
+            if output_format & _COO:
+                ret.coo_ = COO(coo_other, indices, None, True, False)
+        ret.num_edges_ = indices.numel()
+        if data is not None:
+            ret.data_ = r[4]
+        return ret
+
+    def Sampling(self, axis, fanout, replace, on_format, output_format, seed=None):
+        return self._sampling_impl(axis, fanout, replace, on_format, output_format, None, seed)
+
+    def SamplingProbs(self, axis, edge_probs, fanout, replace, on_format, output_format, seed=None):
+        return self._sampling_impl(axis, fanout, replace, on_format, output_format, edge_probs, seed)
+
+    def ColumnwiseFusedSlicingAndSampling(self, column_index, fanout, replace, seed=None):
+        """src/graph.cc:531-559 (+ keep-dim variant chosen like src/graph_ops.cc:223-247)."""
+        col_ids = self.col_ids_[column_index] if self.col_ids_ is not None else column_index
+        ret = self._child(col_ids, self.row_ids_, col_ids.numel(), self.num_rows_)
+        csc = self.csc_
+        if csc is None:
+            _fatal("ColumnwiseFusedSlicingAndSampling needs a CSC graph")
+        data, e_ids = self._gather_args(csc)
+        if fanout == 1 and replace:
+            indptr, indices, select = ops.fused_csc_col_slicing_sampling_one_keepdim(csc.indptr, csc.indices,
+                                                                                     column_index, seed=seed)
+            out_data = None
+            if data is not None:
+                safe = select.clamp(min=0)
+                out_data = data[e_ids[safe] if e_ids is not None else safe]
+        else:
+            r = ops.fused_csc_col_slicing_sampling(csc.indptr, csc.indices, column_index, fanout, replace, seed=seed,
+                                                   data=data, e_ids=e_ids)
+            indptr, indices = r[0], r[1]
+            out_data = r[3] if data is not None else None
+        ret.csc_ = CSC(indptr, indices)
+        ret.num_edges_ = indices.numel()
+        if out_data is not None:
+            ret.data_ = out_data
+        return ret
+
+    # ---- AllValidNode / Relabel (src/graph.cc:757-839) ----------------------------------------------------------
+    def _require_col_ids(self):
+        if self.col_ids_ is None:
+            raise RuntimeError("For sampling, col_ids_ is necessary!")
+        return self.col_ids_
+
+    def AllValidNode(self):
+        col_ids = self._require_col_ids()
+        if self.csc_ is not None:
+            rows = self.row_ids_ if self.row_ids_ is not None else self.csc_.indices
+        elif self.coo_ is not None:
+            rows = self.row_ids_ if self.row_ids_ is not None else self.coo_.row
+        elif self.csr_ is not None:
+            self.coo_ = self._csc2coo(self.csr_, False)
+            rows = self.row_ids_ if self.row_ids_ is not None else self.coo_.row
+        else:
+            _fatal("Error in AllValidNode!")
+        return ops.relabel([col_ids, rows], [])[0]
+
+    def Relabel(self):
+        col_ids = self._require_col_ids()
+        if self.csc_ is not None:
+            if self.val_col_ids_ is not None:
+                col_ids = col_ids[self.val_col_ids_]
+            row_indices = self.row_ids_[self.csc_.indices] if self.row_ids_ is not None else self.csc_.indices
+            frontier, (relabeled,) = ops.relabel([col_ids, row_indices], [row_indices])
+            return (frontier, frontier.numel(), col_ids.numel(), self.csc_.indptr.clone(), relabeled, self.csc_.e_ids,
+                    "csc")
+        if self.csr_ is not None or self.coo_ is not None:
+            if self.coo_ is None:
+                self.coo_ = self._csc2coo(self.csr_, False)
+            coo_col = col_ids[self.coo_.col]
+            coo_row = self.row_ids_[self.coo_.row] if self.row_ids_ is not None else self.coo_.row
+            frontier, (rel_col, rel_row) = ops.relabel([col_ids, coo_row], [coo_col, coo_row])
+            return (frontier, frontier.numel(), col_ids.numel(), rel_row, rel_col, self.coo_.e_ids, "coo")
+        _fatal("Error in Relabel!")
+
+    # ---- RandomWalk (src/graph.cc:646-648) -------------------------------------------------------------------------
+    def RandomWalk(self, seeds, walk_length, seed=None, layout=0):
+        """layout=0 reproduces the reference: step-major memory viewed as [len(seeds), walk_length+1]
+        (undo with `.reshape(-1, len(seeds))`, as the reference's own tests do); layout=1 returns the
+        walker-major trace."""
+        if self.csc_ is None:
+            _fatal("RandomWalk needs a CSC graph")
+        return ops.fused_random_walk(seeds, walk_length, self.csc_.indices, self.csc_.indptr, seed=seed, layout=layout)
+
+    # ---- SDDMM (src/graph.cc:967-985) ------------------------------------------------------------------------------------
+    def SDDMM(self, op, lhs, rhs, out, lhs_target, rhs_target, on_format):
+        self.CreateSparseFormat(on_format)
+        if on_format == _COO:
+            ops.sddmm(op, lhs, rhs, out, lhs_target, rhs_target, self.coo_.row, self.coo_.col, e_ids=self.coo_.e_ids)
+        elif on_format == _CSR:
+            lt = lhs_target if lhs_target == 1 else 2 - lhs_target
+            rt = rhs_target if rhs_target == 1 else 2 - rhs_target
+            ops.sddmm(op, lhs, rhs, out, lt, rt, self.csr_.indices, None, indptr=self.csr_.indptr,
+                      e_ids=self.csr_.e_ids)
+        elif on_format == _CSC:
+            ops.sddmm(op, lhs, rhs, out, lhs_target, rhs_target, self.csc_.indices, None, indptr=self.csc_.indptr,
+                      e_ids=self.csc_.e_ids)
+        else:
+            _fatal("SDDMM only supports CSR and COO formats")
+
+    # ---- Sum / Normalize / Divide (src/graph.cc:650-730) --------------------------------------------------------------------
+    def Sum(self, axis, powk, on_format):
+        self.CreateSparseFormat(on_format)
+        data = self.data_
+        out_size = self.num_cols_ if axis == 0 else self.num_rows_
+        out = torch.zeros(out_size, dtype=torch.float32, device=self._device())
+        if on_format == _COO:
+            target = self.coo_.row if (1 - axis) == 0 else self.coo_.col
+            ops.coo_sum(target, self.coo_.e_ids, data, out, powk)
+        elif axis == 0 and on_format == _CSC:
+            ops.csc_sum(self.csc_.indptr, self.csc_.e_ids, data, out, powk)
+        elif axis == 1 and on_format == _CSR:
+            ops.csc_sum(self.csr_.indptr, self.csr_.e_ids, data, out, powk)
+        else:
+            _fatal("axis should be 0 or 1? on_format and axis do not match?")
+        return out
+
+    def _same_structure_child(self, data):
+        ret = Graph(self.is_subgraph_, self.col_ids_, self.row_ids_, self.num_cols_, self.num_rows_)
+        ret.csc_, ret.csr_, ret.coo_ = self.csc_, self.csr_, self.coo_
+        ret.num_edges_ = self.num_edges_
+        ret.data_ = data
+        ret.val_col_ids_, ret.val_row_ids_ = self.val_col_ids_, self.val_row_ids_
+        return ret
+
+    def Normalize(self, axis, on_format):
+        self.CreateSparseFormat(on_format)
+        in_data = self._data_or_ones()
+        out = torch.empty_like(in_data)
+        if axis == 0 and on_format == _CSC:
+            ops.csc_normalize(self.csc_.indptr, self.csc_.e_ids, in_data, out)
+        elif axis == 1 and on_format == _CSR:
+            ops.csc_normalize(self.csr_.indptr, self.csr_.e_ids, in_data, out)
+        else:
+            _fatal("Not Implementation Error")
+        return self._same_structure_child(out)
+
+    def Divide(self, divisor, axis, on_format):
+        self.CreateSparseFormat(on_format)
+        in_data = self._data_or_ones()
+        out = torch.zeros(self.num_edges_, dtype=torch.float32, device=in_data.device)
+        if on_format == _COO:
+            rhs_target = 0 if (1 - axis) == 0 else 2
+            ops.sddmm("div", in_data, divisor, out, 1, rhs_target, self.coo_.row, self.coo_.col,
+                      e_ids=self.coo_.e_ids)
+        elif axis == 0 and on_format == _CSC:
+            ops.sddmm("div", in_data, divisor, out, 1, 2, self.csc_.indices, None, indptr=self.csc_.indptr,
+                      e_ids=self.csc_.e_ids)
+        elif axis == 1 and on_format == _CSR:
+            ops.sddmm("div", in_data, divisor, out, 1, 2, self.csr_.indices, None, indptr=self.csr_.indptr,
+                      e_ids=self.csr_.e_ids)
+        return self._same_structure_child(out)
+
+    # ---- getters (src/graph.cc:841-965) ------------------------------------------------------------------------------------
+    def GetRows(self):
+        if self.row_ids_ is not None:
+            return self.row_ids_
+        return torch.arange(self.num_rows_, dtype=torch.int64, device=self._device())
+
+    def GetCols(self):
+        if self.col_ids_ is not None:
+            return self.col_ids_
+        return torch.arange(self.num_cols_, dtype=torch.int64, device=self._device())
+
+    def GetCOORows(self, is_original):
+        if self.coo_ is not None:
+            rows = self.coo_.row
+        elif self.csc_ is not None and self.csc_.e_ids is None:
+            rows = self.csc_.indices
+        elif self.csr_ is not None and self.csr_.e_ids is None:
+            self.coo_ = self._csc2coo(self.csr_, False)
+            rows = self.coo_.row
+        else:
+            _fatal("Error in GetCOORows!")
+        return self.row_ids_[rows] if (is_original and self.row_ids_ is not None) else rows
+
+    def GetCOOCols(self, is_original):
+        if self.coo_ is not None:
+            cols = self.coo_.col
+        elif self.csc_ is not None and self.csc_.e_ids is None:
+            self.coo_ = self._csc2coo(self.csc_, True)
+            cols = self.coo_.col
+        elif self.csr_ is not None and self.csr_.e_ids is None:
+            cols = self.csr_.indices
+        else:
+            _fatal("Error in GetCOOCols!")
+        return self.col_ids_[cols] if (is_original and self.col_ids_ is not None) else cols
+
+    def GetValidRows(self):
+        local = self.val_row_ids_ if self.val_row_ids_ is not None else torch.unique(self.GetCOORows(False))
+        return self.row_ids_[local] if self.row_ids_ is not None else local
+
+    def GetValidCols(self):
+        local = self.val_col_ids_ if self.val_col_ids_ is not None else torch.unique(self.GetCOOCols(False))
+        return self.col_ids_[local] if self.col_ids_ is not None else local
+
+    def MetaData(self):
+        if self.csc_ is not None:
+            return [self.col_ids_, self.row_ids_, self._data_or_ones(), self.csc_.indptr, self.csc_.indices]
+        if self.csr_ is not None:
+            return [self.col_ids_, self.row_ids_, self._data_or_ones(), self.csr_.indptr, self.csr_.indices]
+        return [self.coo_.row, self.coo_.col]
+
+    def COOMetaData(self):
+        if self.coo_ is None:
+            return []
+        return [self.col_ids_, self.row_ids_, self.data_, self.coo_.row, self.coo_.col]
+
+    def CSCMetaData(self):
+        if self.csc_ is None:
+            return []
+        return [self.col_ids_, self.row_ids_, self.data_, self.csc_.indptr, self.csc_.indices]
+
+    def GetCSCTensor(self):
+        self.CreateSparseFormat(_CSC)
+        return [self.csc_.indptr, self.csc_.indices, self.csc_.e_ids]
+
+    def GetCOOTensor(self):
+        self.CreateSparseFormat(_COO)
+        if not self.coo_.col_sorted:
+            _fatal("Check failed: coo_->col_sorted == true")
+        return [self.coo_.row, self.coo_.col, self.coo_.e_ids]
+
+    # ---- outside the hot path ------------------------------------------------------------------------------------------------------
+    def _out_of_scope(self, *a, **k):
+        raise NotImplementedError("batched / induced-subgraph / compact-id methods are outside the sampling hot path")
+
+    FusedBidirSlicing = BatchFusedBidirSlicing = BatchSlicing = Split = Decode = EDivUSum = _out_of_scope
+
+
+# Registered names: src/pybind.cc:14-52 (CamelCase) and the spelling used by python/gs + examples.
+_NAME_MAP = {
+    "SetData": ("_CAPI_SetData", "_CAPI_set_data"),
+    "GetData": ("_CAPI_GetData", "_CAPI_get_data"),
+    "GetNumRows": ("_CAPI_GetNumRows", "_CAPI_get_num_rows"),
+    "GetNumCols": ("_CAPI_GetNumCols", "_CAPI_get_num_cols"),
+    "GetNumEdges": ("_CAPI_GetNumEdges", "_CAPI_get_num_edges"),
+    "Slicing": ("_CAPI_Slicing", "_CAPI_slicing"),
+    "Sampling": ("_CAPI_Sampling", "_CAPI_sampling"),
+    "SamplingProbs": ("_CAPI_SamplingWithProbs", "_CAPI_sampling_with_probs"),
+    "ColumnwiseFusedSlicingAndSampling": ("_CAPI_FusedColumnwiseSlicingSampling",
+                                          "_CAPI_fused_columnwise_slicing_sampling"),
+    "LoadCSC": ("_CAPI_LoadCSC", "_CAPI_load_csc", "load_csc"),
+    "LoadCOO": ("_CAPI_LoadCOO", "_CAPI_load_coo"),
+    "LoadCSCWithColIds": ("_CAPI_LoadCSCWithColIds", "_CAPI_load_csc_with_col_ids"),
+    "AllValidNode": ("_CAPI_AllValidNode", "_CAPI_all_valid_node", "_CAPI_all_indices"),
+    "GetRows": ("_CAPI_GetRows", "_CAPI_get_rows"),
+    "GetCols": ("_CAPI_GetCols", "_CAPI_get_cols"),
+    "GetValidRows": ("_CAPI_GetValidRows", "_CAPI_get_valid_rows"),
+    "GetValidCols": ("_CAPI_GetValidCols", "_CAPI_get_valid_cols"),
+    "GetCOORows": ("_CAPI_GetCOORows", "_CAPI_get_coo_rows"),
+    "GetCOOCols": ("_CAPI_GetCooCols", "_CAPI_get_coo_cols"),
+    "Relabel": ("_CAPI_Relabel", "_CAPI_relabel"),
+    "Sum": ("_CAPI_Sum", "_CAPI_sum"),
+    "Normalize": ("_CAPI_Normalize", "_CAPI_normalize"),
+    "Divide": ("_CAPI_Divide", "_CAPI_divide"),
+    "MetaData": ("_CAPI_Metadata", "_CAPI_metadata"),
+    "COOMetaData": ("_CAPI_COOMetadata", "_CAPI_coo_metadata"),
+    "CSCMetaData": ("_CAPI_CSCMetadata", "_CAPI_csc_metadata"),
+    "RandomWalk": ("_CAPI_RandomWalk", "_CAPI_random_walk"),
+    "SDDMM": ("_CAPI_SDDMM", "_CAPI_sddmm"),
+    "GetCSCTensor": ("_CAPI_GetCSC", "_CAPI_get_csc"),
+    "GetCOOTensor": ("_CAPI_GetCOO", "_CAPI_get_coo"),
+    "SetCOOByTensor": ("_CAPI_SetCOO", "_CAPI_set_coo"),
+    "SetMetaData": ("_CAPI_SetMetadata", "_CAPI_set_metadata"),
+    "FusedBidirSlicing": ("_CAPI_FusionSlicing", "_CAPI_fusion_slicing"),
+    "BatchSlicing": ("_CAPI_BatchSlicing",),
+    "BatchFusedBidirSlicing": ("_CAPI_BatchFusionSlicing",),
+    "Split": ("_CAPI_Split",),
+    "Decode": ("_CAPI_Decode",),
+    "EDivUSum": ("_CAPI_EDivUSum",),
+}
+for _method, _aliases in _NAME_MAP.items():
+    for _alias in _aliases:
+        setattr(Graph, _alias, getattr(Graph, _method))
+
+
+def ListSampling(data, num_picks, replace, seed=None):
+    """gs::ListSampling (src/tensor_ops.cc:5-9); registered as gs_ops._CAPI_ListSampling / list_sampling."""
+    return ops.list_sampling(data, num_picks, replace, seed=seed)
+
+
+def ListSamplingProbs(data, probs, num_picks, replace, seed=None):
+    """gs::ListSamplingProbs (src/tensor_ops.cc:11-16); gs_ops._CAPI_ListSamplingWithProbs / list_sampling_with_probs."""
+    return ops.list_sampling(data, num_picks, replace, probs=probs, seed=seed)
+
+
+def Unique(node_ids):
+    """gs_ops._CAPI_Unique = gs::impl::TensorUniqueCUDA (src/pybind.cc:85)."""
+    return ops.tensor_unique(node_ids)
