@@ -1,0 +1,351 @@
+#!/usr/bin/env python
+"""Benchmark of the sampling hot path: sampled edges/s on products-scale 3-hop GraphSAGE sampling.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (config "products-scale GraphSAGE 3-hop"): symmetric R-MAT graph, 2,450,000 nodes,
+123,700,000 directed edges, int64 CSC, hub degrees thinned to about 17k; train split = 8% of the
+nodes; one STEP = one minibatch of 1,024 seeds per GPU: per hop (fanouts 15, 10, 5) fused column
+slice + uniform sampling without replacement, then unique + relabel; the frontier is the next hop's
+seeds.  The graph is replicated on every GPU and batches are dealt round-robin to the ranks, so the
+per-GPU work is fixed as N grows (weak scaling); NCCL only reduces the run statistics.
+
+Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` goes through the
+public `Graph` API with seeds in pinned host memory and the per-batch edge count read back.
+`--impl reference` times the reference's own implementation of the same loop: its CUDA library
+compiled unmodified for sm_100 (oracle/_ref/libgs_ref.so) if it is present, because the reference has
+no CPU path; otherwise the CPU restatement on the host cores.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FANOUTS = [15, 10, 5]
+BATCH = 1024
+NUM_NODES = 2_450_000
+NUM_EDGES = 123_700_000
+MAX_DEGREE = 17_000
+TRAIN_FRACTION = 0.08
+GRAPH_SEED = 0x5EED + 2
+METRIC = "sampled_edges_per_second"
+UNIT = "edges/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
+    ap.add_argument("--edges", type=int, default=NUM_EDGES)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region is timed."""
+
+    def __init__(self, index, period=0.1):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def physical_gpu_index(local_index):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def make_inputs(args, device, world, rank):
+    import torch
+    from graph_sampling_b200.synthetic import rmat_csc, seed_batches
+    t0 = time.time()
+    indptr, indices = rmat_csc(args.nodes, args.edges, seed=GRAPH_SEED, symmetric=True, max_degree=MAX_DEGREE,
+                               device=device)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()  # the generator's temporaries are several GB; keep only the graph resident
+    deg = indptr[1:] - indptr[:-1]
+    info = {"nodes": int(args.nodes), "edges": int(indices.numel()), "max_degree": int(deg.max().item()),
+            "gen_seconds": round(time.time() - t0, 2)}
+    total_batches = (args.steps + args.warmup) * world
+    allb = seed_batches(args.nodes, BATCH, total_batches, seed=GRAPH_SEED + 1, train_fraction=TRAIN_FRACTION,
+                        device="cpu")
+    mine = allb[rank::world].contiguous()  # batch b -> rank b mod world
+    return indptr, indices, mine, info
+
+
+def sage_batch_api(graph, seeds, fused_name, relabel_name):
+    """The reference's per-batch loop (examples/graphsage/unbatching_training.py:19-28)."""
+    fused = getattr(graph, fused_name)
+    edges = 0
+    shapes = []
+    for k in FANOUTS:
+        sub = fused(seeds, k, False)
+        frontier, n_row, n_col, indptr, indices, e_ids, fmt = getattr(sub, relabel_name)()
+        shapes.append((int(seeds.numel()), int(indices.numel()), int(n_row)))
+        edges += int(indices.numel())
+        seeds = frontier
+    return edges, shapes
+
+
+def algorithmic_bytes_sample(shapes):
+    # fused slice + uniform sample: 32 B per seed (seed, indptr pair, out offset) + 8 + 24 B per sampled edge
+    return sum(32 * s + 8 + 24 * e for s, e, _ in shapes)
+
+
+def timed_loop(torch, fn, batches_iter, warmup, steps, barrier):
+    for _ in range(warmup):
+        fn(next(batches_iter))
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    edges = 0
+    all_shapes = []
+    for _ in range(steps):
+        e, shapes = fn(next(batches_iter))
+        edges += e
+        all_shapes.append(shapes)
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return ev0.elapsed_time(ev1) / 1e3, edges, all_shapes
+
+
+def reduce_stats(torch, dist, world, seconds, edges, device):
+    if world == 1:
+        return seconds, edges
+    t = torch.tensor([seconds], dtype=torch.float64, device=device)
+    e = torch.tensor([edges], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(e, op=dist.ReduceOp.SUM)
+    return float(t.item()), int(e.item())
+
+
+def cpu_baseline(indptr, indices, batches, budget_s=15.0):
+    """Times the CPU restatement of the same batch loop on all host cores, on a bounded sample."""
+    from oracle import build as obuild
+    obuild.build()
+    from oracle import oracle as o
+    ip, ix = indptr.cpu().numpy(), indices.cpu().numpy()
+    o.sage_batch(ip, ix, batches[0].numpy(), FANOUTS, seed=1)  # warm
+    t0, edges, n = time.time(), 0, 0
+    while n < len(batches) and (time.time() - t0) < budget_s:
+        edges += o.sage_batch(ip, ix, batches[n].numpy(), FANOUTS, seed=n)
+        n += 1
+    dt = time.time() - t0
+    return {"value": edges / dt, "unit": UNIT, "cores": o.num_threads(), "kind": "port",
+            "sample": f"{n} batches of {BATCH} seeds of the same workload ({dt:.1f} s)"}
+
+
+def run_ours(args):
+    import torch
+    rank, world, local = dist_env()
+    dist = None
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+
+    import graph_sampling_b200.gs as gs
+    from graph_sampling_b200 import ops
+    indptr, indices, batches, info = make_inputs(args, device, world, rank)
+    A = gs.Graph(False)
+    A._CAPI_load_csc(indptr, indices)
+    ctx = ops.default_context(device)
+    ops.set_seed(2024 + rank)
+
+    # ---- value: seeds resident in HBM --------------------------------------------------------------
+    dev_batches = batches.to(device)
+    it = iter(dev_batches)
+    sampler = ClockSampler(physical_gpu_index(local))
+    fn = lambda s: sage_batch_api(A, s, "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
+    for _ in range(min(3, args.warmup)):  # size scratch before anything is timed
+        fn(dev_batches[0])
+    ctx.profile_reset()
+    launches0 = ctx.launch_count()
+    sampler.start()
+    ctx.profile_enable(True)
+    seconds, edges, shapes = timed_loop(torch, fn, it, args.warmup, args.steps, barrier)
+    ctx.profile_enable(False)
+    clocks = sampler.stop()
+    prof = ctx.profile_read()
+    launches = ctx.launch_count() - launches0
+    seconds_all, edges_all = reduce_stats(torch, dist, world, seconds, edges, device)
+
+    # ---- e2e: pinned host seeds -> device, public API, edge count back on the host -------------------
+    pinned = batches.pin_memory()
+    h2d_bytes = BATCH * 8
+    d2h_bytes = 8 * 3 * len(FANOUTS)
+
+    def fn_e2e(host_seeds):
+        s = host_seeds.to(device, non_blocking=True)
+        return sage_batch_api(A, s, "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
+
+    e2e_seconds, e2e_edges, _ = timed_loop(torch, fn_e2e, iter(pinned), args.warmup, args.steps, barrier)
+    e2e_seconds_all, e2e_edges_all = reduce_stats(torch, dist, world, e2e_seconds, e2e_edges, device)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    # ---- roofline of the dominant kernel (largest share of timed device time) ---------------------------
+    import json as _json
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(_json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    timed = {k: v for k, v in prof.items()}
+    sample_ms, sample_n = timed.get("sample_uniform", (0.0, 0))
+    # the profile covers warm-up + timed steps; algorithmic bytes are averaged per launch over the timed steps
+    n_hops = len(FANOUTS)
+    bytes_per_launch = sum(algorithmic_bytes_sample(s) for s in shapes) / max(1, len(shapes) * n_hops)
+    avg_launch_s = (sample_ms / 1e3) / max(1, sample_n)
+    achieved = bytes_per_launch / avg_launch_s / 1e9 if avg_launch_s > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": "k_sample_uniform (fused count + scan + sample)",
+                "achieved": round(achieved, 2), "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                "frac": round(achieved / peak, 5), "traffic": None,
+                "bytes_per_launch": round(bytes_per_launch), "avg_launch_us": round(avg_launch_s * 1e6, 2),
+                "kernel_ms": {k: round(v[0], 3) for k, v in timed.items()},
+                "kernel_launches": {k: v[1] for k, v in timed.items()}}
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(indptr, indices, batches)
+    line = {
+        "metric": METRIC, "value": edges_all / seconds_all, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": seconds_all / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, "
+                               "relabel per hop (BASELINE config 2)",
+                   "graph": info, "batch": BATCH, "fanouts": FANOUTS, "parallelism": f"replicated graph, dp{world}",
+                   "l2": "inputs larger than L2: 1 GB of indices gathered at random, no flush",
+                   "path": "Graph API per hop (fused slice+sample, relabel)"},
+        "edges_per_step": edges_all / args.steps / world,
+        "e2e": {"value": e2e_edges_all / e2e_seconds_all, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_seconds_all / args.steps * 1e3},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """Reference arm.  The reference implements this path in CUDA only (every dispatcher aborts off-GPU),
+    so its own implementation is timed on the GPU through its TorchScript classes; if the compiled
+    library is absent the CPU restatement is timed on the host cores instead."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    import torch
+    lib = os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    indptr, indices, batches, info = make_inputs(args, device, 1, 0)
+    base = {"metric": METRIC, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "impl": "reference",
+            "config": {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, "
+                                   "relabel per hop (BASELINE config 2)", "graph": info, "batch": BATCH,
+                       "fanouts": FANOUTS}}
+    if os.path.exists(lib):
+        torch.classes.load_library(lib)
+        G = torch.classes.gs_classes.Graph(False)
+        G._CAPI_LoadCSC(indptr, indices)
+        pinned = batches.pin_memory()
+
+        def fn(host_seeds):
+            s = host_seeds.to(device, non_blocking=True)
+            return sage_batch_api(G, s, "_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_Relabel")
+
+        sampler = ClockSampler(physical_gpu_index(local))
+        sampler.start()
+        seconds, edges, _ = timed_loop(torch, fn, iter(pinned), args.warmup, args.steps, lambda: None)
+        clocks = sampler.stop()
+        v = edges / seconds
+        base.update({"value": v, "ms_per_step": seconds / args.steps * 1e3, "clocks": clocks,
+                     "cpu_baseline": {"value": v, "unit": UNIT, "cores": 0, "kind": "reference",
+                                      "sample": "the reference has no CPU path; this is its own CUDA library "
+                                                "(unmodified sources compiled for sm_100) on the same GPU, "
+                                                f"{args.steps} batches"},
+                     "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    else:
+        cpu = cpu_baseline(indptr, indices, batches, budget_s=60.0)
+        base.update({"value": cpu["value"], "ms_per_step": None, "cpu_baseline": cpu,
+                     "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    print(json.dumps(base))
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -53,6 +53,30 @@ constexpr u64 kValueMask = (1ull << 40) - 1;
 
 int cuda_fail(gsb_ctx* ctx, cudaError_t e, const char* file, int line);
 
+// Kernels that can be timed individually (gsb_profile_*).
+enum KernelId {
+  KID_COUNT_SCAN = 0,
+  KID_SLICE_FILL,
+  KID_SAMPLE_UNIFORM,
+  KID_SAMPLE_KEEPDIM,
+  KID_SAMPLE_WEIGHTED,
+  KID_TABLE_CLEAR,
+  KID_TABLE_INSERT,
+  KID_FIRST_COMPACT,
+  KID_RELABEL,
+  KID_RANDOM_WALK,
+  KID_SDDMM_DOT,
+  KID_SDDMM_GENERIC,
+  KID_SEGMENT,
+  KID_ROW_FILTER,
+  KID_LIST_SAMPLE,
+  KID_SORT,
+  KID_FORMAT,
+  KID_SAGE_SAMPLE_INSERT,
+  KID_OTHER,
+  KID_NUM
+};
+
 // Context internals (defined in ctx.cu).
 struct Workspace {
   void* ptr;
@@ -68,6 +92,18 @@ int ctx_check_device_error(gsb_ctx* ctx, cudaStream_t stream);
 // the pinned pointer.
 int ctx_fetch_counters(gsb_ctx* ctx, cudaStream_t stream, int first, int n, const i64** out);
 void ctx_count_launches(gsb_ctx* ctx, int n);
+// When profiling is enabled (gsb_profile_enable) these bracket a launch with CUDA events on the
+// launching stream; otherwise they only count the launch.
+void ctx_prof_begin(gsb_ctx* ctx, int kid, cudaStream_t stream);
+void ctx_prof_end(gsb_ctx* ctx, int kid, cudaStream_t stream);
+
+struct ScopedKernelTimer {
+  gsb_ctx* ctx;
+  int kid;
+  cudaStream_t stream;
+  ScopedKernelTimer(gsb_ctx* c, int k, cudaStream_t s) : ctx(c), kid(k), stream(s) { ctx_prof_begin(c, k, s); }
+  ~ScopedKernelTimer() { ctx_prof_end(ctx, kid, stream); }
+};
 
 static inline int grid_for(i64 work_items, int per_block) {
   i64 g = (work_items + per_block - 1) / per_block;

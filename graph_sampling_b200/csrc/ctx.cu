@@ -3,6 +3,7 @@
 #include <string.h>
 
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 
@@ -17,6 +18,14 @@ struct gsb_ctx {
   i64* pinned;    // host pinned, CNT_NUM entries
   i64 launches;
   char message[512];
+  // per-kernel event timing (off by default)
+  bool profiling;
+  std::vector<cudaEvent_t>* ev_begin;
+  std::vector<cudaEvent_t>* ev_end;
+  std::vector<int>* ev_kid;
+  size_t ev_used;
+  double prof_ms[gsb::KID_NUM];
+  i64 prof_launches[gsb::KID_NUM];
 };
 
 namespace gsb {
@@ -100,6 +109,41 @@ int ctx_check_device_error(gsb_ctx* ctx, cudaStream_t stream) {
 
 void ctx_count_launches(gsb_ctx* ctx, int n) { ctx->launches += n; }
 
+void ctx_prof_begin(gsb_ctx* ctx, int kid, cudaStream_t stream) {
+  ctx->launches += 1;
+  if (!ctx->profiling) return;
+  if (ctx->ev_used == ctx->ev_begin->size()) {
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    ctx->ev_begin->push_back(a);
+    ctx->ev_end->push_back(b);
+    ctx->ev_kid->push_back(kid);
+  }
+  (*ctx->ev_kid)[ctx->ev_used] = kid;
+  cudaEventRecord((*ctx->ev_begin)[ctx->ev_used], stream);
+}
+
+void ctx_prof_end(gsb_ctx* ctx, int kid, cudaStream_t stream) {
+  (void)kid;
+  if (!ctx->profiling || ctx->ev_used >= ctx->ev_begin->size()) return;
+  cudaEventRecord((*ctx->ev_end)[ctx->ev_used], stream);
+  ctx->ev_used += 1;
+}
+
+// Folds the recorded event pairs into the per-kernel totals (waits for the events).
+static void prof_collect(gsb_ctx* ctx) {
+  for (size_t i = 0; i < ctx->ev_used; ++i) {
+    float ms = 0.f;
+    if (cudaEventSynchronize((*ctx->ev_end)[i]) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, (*ctx->ev_begin)[i], (*ctx->ev_end)[i]) == cudaSuccess) {
+      const int k = (*ctx->ev_kid)[i];
+      ctx->prof_ms[k] += ms;
+      ctx->prof_launches[k] += 1;
+    }
+  }
+  ctx->ev_used = 0;
+}
+
 }  // namespace gsb
 
 extern "C" {
@@ -114,6 +158,9 @@ int gsb_ctx_create(int device, gsb_ctx** out_ctx) {
   if (!ctx) return GSB_ERR_OUT_OF_MEMORY;
   memset(ctx, 0, sizeof(*ctx));
   ctx->device = device;
+  ctx->ev_begin = new std::vector<cudaEvent_t>();
+  ctx->ev_end = new std::vector<cudaEvent_t>();
+  ctx->ev_kid = new std::vector<int>();
   int prev = 0;
   cudaGetDevice(&prev);
   int st = GSB_OK;
@@ -128,6 +175,9 @@ int gsb_ctx_create(int device, gsb_ctx** out_ctx) {
     st = gsb::cuda_fail(nullptr, e, __FILE__, __LINE__);
     if (ctx->counters) cudaFree(ctx->counters);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    delete ctx->ev_begin;
+    delete ctx->ev_end;
+    delete ctx->ev_kid;
     delete ctx;
     cudaSetDevice(prev);
     return st;
@@ -147,6 +197,13 @@ int gsb_ctx_destroy(gsb_ctx* ctx) {
   if (ctx->tile_words) cudaFree(ctx->tile_words);
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
+  for (size_t i = 0; i < ctx->ev_begin->size(); ++i) {
+    cudaEventDestroy((*ctx->ev_begin)[i]);
+    cudaEventDestroy((*ctx->ev_end)[i]);
+  }
+  delete ctx->ev_begin;
+  delete ctx->ev_end;
+  delete ctx->ev_kid;
   cudaSetDevice(prev);
   delete ctx;
   return GSB_OK;
@@ -185,6 +242,42 @@ int gsb_read_counts(gsb_ctx* ctx, void* stream, int64_t* nnz_host, int64_t* uniq
   if (st != GSB_OK) return st;
   if (nnz_host) *nnz_host = c[0];
   if (unique_host) *unique_host = c[1];
+  return GSB_OK;
+}
+
+int gsb_profile_enable(gsb_ctx* ctx, int on) {
+  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  if (!on && ctx->profiling) gsb::prof_collect(ctx);
+  ctx->profiling = on != 0;
+  return GSB_OK;
+}
+
+int gsb_profile_reset(gsb_ctx* ctx) {
+  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  gsb::prof_collect(ctx);
+  for (int k = 0; k < gsb::KID_NUM; ++k) {
+    ctx->prof_ms[k] = 0.0;
+    ctx->prof_launches[k] = 0;
+  }
+  return GSB_OK;
+}
+
+int gsb_profile_num_kernels(void) { return gsb::KID_NUM; }
+
+const char* gsb_profile_kernel_name(int kid) {
+  static const char* names[gsb::KID_NUM] = {
+      "count_scan",     "slice_fill",   "sample_uniform", "sample_keepdim", "sample_weighted", "table_clear",
+      "table_insert",   "first_compact", "relabel",       "random_walk",    "sddmm_dot",       "sddmm_generic",
+      "segment",        "row_filter",   "list_sample",    "sort",           "format",          "sage_sample_insert",
+      "other"};
+  return (kid >= 0 && kid < gsb::KID_NUM) ? names[kid] : "";
+}
+
+int gsb_profile_read(gsb_ctx* ctx, int kid, double* total_ms, int64_t* launches) {
+  if (!ctx || kid < 0 || kid >= gsb::KID_NUM) return GSB_ERR_INVALID_ARGUMENT;
+  gsb::prof_collect(ctx);
+  if (total_ms) *total_ms = ctx->prof_ms[kid];
+  if (launches) *launches = ctx->prof_launches[kid];
   return GSB_OK;
 }
 

@@ -90,11 +90,13 @@ extern "C" int gsb_random_walk(gsb_ctx* ctx, void* stream_, const int64_t* indpt
   GSB_REQUIRE(seeds && out, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   const int grid = grid_for(W, kWalkThreads);
-  if (layout == 0)
-    k_random_walk<0><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
-  else
-    k_random_walk<1><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+  {
+    ScopedKernelTimer timer(ctx, KID_RANDOM_WALK, stream);
+    if (layout == 0)
+      k_random_walk<0><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+    else
+      k_random_walk<1><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   return GSB_OK;
 }

@@ -138,13 +138,14 @@ extern "C" int gsb_sddmm(gsb_ctx* ctx, void* stream_, int op, const int64_t* row
     const int grid = (int)min((i64)kNumSMs * 16, (E * 32 + kSddmmThreads - 1) / kSddmmThreads);
     const bool vec = (reduce_size % 4 == 0) && (lhs_len % 4 == 0) && (rhs_len % 4 == 0) &&
                      (((uintptr_t)lhs | (uintptr_t)rhs) % 16 == 0);
+    ScopedKernelTimer timer(ctx, KID_SDDMM_DOT, stream);
     if (vec) k_sddmm_dot_warp<true><<<grid, kSddmmThreads, 0, stream>>>(p);
     else k_sddmm_dot_warp<false><<<grid, kSddmmThreads, 0, stream>>>(p);
   } else {
     const int grid = (int)min((i64)kNumSMs * 16, (E * out_len + kSddmmThreads - 1) / kSddmmThreads);
+    ScopedKernelTimer timer(ctx, KID_SDDMM_GENERIC, stream);
     k_sddmm_generic<<<grid, kSddmmThreads, 0, stream>>>(p);
   }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   return GSB_OK;
 }

@@ -264,9 +264,11 @@ int gsb_col_slice_count(gsb_ctx* ctx, void* stream_, const int64_t* indptr, cons
   TileState ts;
   int st = ctx_tile_state(ctx, grid, stream, &ts);
   if (st != GSB_OK) return st;
-  k_count_scan<<<grid, kThreads, 0, stream>>>(indptr, seeds, S, 0, COUNT_DEGREE, out_indptr, ctx_counters(ctx), ts);
+  {
+    ScopedKernelTimer timer(ctx, KID_COUNT_SCAN, stream);
+    k_count_scan<<<grid, kThreads, 0, stream>>>(indptr, seeds, S, 0, COUNT_DEGREE, out_indptr, ctx_counters(ctx), ts);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   if (nnz_host) {
     const i64* c;
     st = ctx_fetch_counters(ctx, stream, CNT_NNZ, 1, &c);
@@ -284,9 +286,11 @@ int gsb_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
   GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (S == 0) return GSB_OK;
   FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data};
-  k_slice_fill<<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
+  {
+    ScopedKernelTimer timer(ctx, KID_SLICE_FILL, (cudaStream_t)stream_);
+    k_slice_fill<<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   return GSB_OK;
 }
 
@@ -303,12 +307,14 @@ int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
   if (st != GSB_OK) return st;
   SampleParams p{indptr, indices, seeds,  S,        k,        replace,         (u64)seed, out_indptr, out_indices,
                  out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts};
-  if (k <= 4) launch_sample<4>(p, grid, stream);
-  else if (k <= 8) launch_sample<8>(p, grid, stream);
-  else if (k <= 16) launch_sample<16>(p, grid, stream);
-  else launch_sample<32>(p, grid, stream);
+  {
+    ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
+    if (k <= 4) launch_sample<4>(p, grid, stream);
+    else if (k <= 8) launch_sample<8>(p, grid, stream);
+    else if (k <= 16) launch_sample<16>(p, grid, stream);
+    else launch_sample<32>(p, grid, stream);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   if (nnz_host) {
     const i64* c;
     st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);
@@ -323,10 +329,12 @@ int gsb_sample_one_keepdim(gsb_ctx* ctx, void* stream_, const int64_t* indptr, c
                            const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
                            int64_t* out_indices, int64_t* out_select) {
   GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
-  k_sample_one_keepdim<<<grid_for(S + 1, kThreads), kThreads, 0, (cudaStream_t)stream_>>>(
-      indptr, indices, seeds, S, (u64)seed, out_indptr, out_indices, out_select);
+  {
+    ScopedKernelTimer timer(ctx, KID_SAMPLE_KEEPDIM, (cudaStream_t)stream_);
+    k_sample_one_keepdim<<<grid_for(S + 1, kThreads), kThreads, 0, (cudaStream_t)stream_>>>(
+        indptr, indices, seeds, S, (u64)seed, out_indptr, out_indices, out_select);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   return GSB_OK;
 }
 

@@ -168,7 +168,10 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
   st = ctx_reserve_workspace(ctx, cap * sizeof(Slot), &ws);
   if (st != GSB_OK) return st;
   table.slots = (Slot*)ws;
-  GSB_CUDA_OK(cudaMemsetAsync(table.slots, 0xFF, cap * sizeof(Slot), stream));
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
+    GSB_CUDA_OK(cudaMemsetAsync(table.slots, 0xFF, cap * sizeof(Slot), stream));
+  }
 
   const int tiles = grid_for(n, kTileItems);
   TileState ts;
@@ -176,17 +179,20 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
   if (st != GSB_OK) return st;
   const int sm_grid = kNumSMs * 8;
   if (n > 0) {
+    ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
     k_insert<<<min(grid_for(n, kThreads), sm_grid), kThreads, 0, stream>>>(items, table, ctx_counters(ctx));
-    GSB_LAUNCH_OK();
   }
-  k_first_compact<<<tiles, kThreads, 0, stream>>>(items, table, out_unique, ctx_counters(ctx), ts);
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, n > 0 ? 3 : 2);
-  if (m > 0) {
-    k_relabel<<<min(grid_for(m, kThreads), sm_grid), kThreads, 0, stream>>>(rel, table);
-    GSB_LAUNCH_OK();
-    ctx_count_launches(ctx, 1);
+  {
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_first_compact<<<tiles, kThreads, 0, stream>>>(items, table, out_unique, ctx_counters(ctx), ts);
   }
+  GSB_LAUNCH_OK();
+  if (m > 0) {
+    ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
+    k_relabel<<<min(grid_for(m, kThreads), sm_grid), kThreads, 0, stream>>>(rel, table);
+  }
+  GSB_LAUNCH_OK();
   if (unique_host) {
     const i64* c;
     st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);

@@ -189,9 +189,11 @@ extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* i
   if (st != GSB_OK) return st;
   WeightedParams p{indptr, indices,    probs,       seeds, S,     k,        replace,  (u64)seed,         out_indptr,
                    out_indices, out_select, out_coo_col, data,  e_ids, out_data, capacity, ctx_counters(ctx), ts};
-  k_sample_weighted<<<grid, kWThreads, 0, stream>>>(p);
+  {
+    ScopedKernelTimer timer(ctx, KID_SAMPLE_WEIGHTED, stream);
+    k_sample_weighted<<<grid, kWThreads, 0, stream>>>(p);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   if (nnz_host) {
     const i64* c;
     st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);

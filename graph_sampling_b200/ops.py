@@ -73,6 +73,25 @@ class Context:
     def launch_count(self):
         return int(self.lib.gsb_launch_count(self.handle))
 
+    # ---- per-kernel timing (gsb_profile_*) ----
+    def profile_enable(self, on=True):
+        self.check(self.lib.gsb_profile_enable(self.handle, c_int(int(bool(on)))), "gsb_profile_enable")
+
+    def profile_reset(self):
+        self.check(self.lib.gsb_profile_reset(self.handle), "gsb_profile_reset")
+
+    def profile_read(self):
+        """{kernel class name: (total device ms, launches)} for classes with at least one timed launch."""
+        self.lib.gsb_profile_kernel_name.restype = ctypes.c_char_p
+        out = {}
+        for kid in range(int(self.lib.gsb_profile_num_kernels())):
+            ms, n = ctypes.c_double(0), c_i64(0)
+            self.check(self.lib.gsb_profile_read(self.handle, c_int(kid), ctypes.byref(ms), ctypes.byref(n)),
+                       "gsb_profile_read")
+            if n.value:
+                out[self.lib.gsb_profile_kernel_name(kid).decode()] = (ms.value, n.value)
+        return out
+
     def read_counts(self):
         a, b = c_i64(0), c_i64(0)
         self.check(self.lib.gsb_read_counts(self.handle, _stream(), ctypes.byref(a), ctypes.byref(b)), "gsb_read_counts")

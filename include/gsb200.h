@@ -70,6 +70,17 @@ GSB_API int64_t gsb_launch_count(gsb_ctx* ctx);
  * waiting for `stream`. */
 GSB_API int gsb_read_counts(gsb_ctx* ctx, void* stream, int64_t* nnz_host, int64_t* unique_host);
 
+/* Per-kernel timing (no counterpart in the reference, whose examples bracket calls with NVTX
+ * ranges: examples/shadowgnn/shadowgnn_benchmark.py:29-37).  While enabled, every kernel launch of
+ * this context is bracketed by CUDA events on the launching stream; gsb_profile_read waits for the
+ * recorded events and returns the accumulated device time and launch count of kernel class `kid`
+ * (0 <= kid < gsb_profile_num_kernels(), named by gsb_profile_kernel_name). */
+GSB_API int gsb_profile_enable(gsb_ctx* ctx, int on);
+GSB_API int gsb_profile_reset(gsb_ctx* ctx);
+GSB_API int gsb_profile_num_kernels(void);
+GSB_API const char* gsb_profile_kernel_name(int kid);
+GSB_API int gsb_profile_read(gsb_ctx* ctx, int kid, double* total_ms, int64_t* launches);
+
 /* ---- column slicing -------------------------------------------------------------------------
  * Replaces gs::impl::CSCColSlicingCUDA / _OnIndptrSlicing / _GetSubIndicesKernel
  * (src/cuda/slicing.cu:100-182; dispatcher gs::CSCColSlicing, src/graph_ops.cc:141-154).
