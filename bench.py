@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--group", type=int, default=64,
+                    help="minibatches handed to one call of the batched sampler (1 = per-batch Graph API)")
     return ap.parse_args()
 
 
@@ -147,6 +149,55 @@ def sage_batch_api(graph, seeds, fused_name, relabel_name):
     return edges, shapes
 
 
+def sage_group(ops, indptr, indices, seeds_2d, ptr_cache):
+    """G minibatches through the batched sampler (one fused sample + one batched relabel per hop)."""
+    G, S0 = seeds_2d.shape
+    ptr = ptr_cache.get(G)
+    if ptr is None:
+        import torch
+        ptr = torch.arange(G + 1, dtype=torch.int64, device=indptr.device) * S0
+        ptr_cache[G] = ptr
+    hops = ops.sage_sample_batches(indptr, indices, seeds_2d.reshape(-1), ptr, FANOUTS, replace=False)
+    shapes = [(int(h["seeds"].numel()), int(h["indices"].numel()), int(h["frontier"].numel())) for h in hops]
+    return sum(e for _, e, _ in shapes), shapes
+
+
+def grouped(batches, group):
+    """Yields consecutive groups of up to `group` batches forever (wraps around)."""
+    n = batches.shape[0]
+    i = 0
+    while True:
+        j = min(n, i + group)
+        yield batches[i:j]
+        i = 0 if j >= n else j
+
+
+def timed_group_loop(torch, fn, batches, warmup, steps, group, barrier):
+    """Times exactly `steps` minibatches, processed `group` at a time, after `warmup` untimed ones."""
+    done = 0
+    while done < warmup:
+        g = min(group, warmup - done)
+        fn(batches[done:done + g])
+        done += g
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    edges, all_shapes, at = 0, [], warmup
+    end = warmup + steps
+    while at < end:
+        g = min(group, end - at)
+        e, shapes = fn(batches[at:at + g])
+        edges += e
+        all_shapes.append(shapes)
+        at += g
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return ev0.elapsed_time(ev1) / 1e3, edges, all_shapes
+
+
 def algorithmic_bytes_sample(shapes):
     # fused slice + uniform sample: 32 B per seed (seed, indptr pair, out offset) + 8 + 24 B per sampled edge
     return sum(32 * s + 8 + 24 * e for s, e, _ in shapes)
@@ -219,16 +270,20 @@ def run_ours(args):
 
     # ---- value: seeds resident in HBM --------------------------------------------------------------
     dev_batches = batches.to(device)
-    it = iter(dev_batches)
     sampler = ClockSampler(physical_gpu_index(local))
-    fn = lambda s: sage_batch_api(A, s, "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
-    for _ in range(min(3, args.warmup)):  # size scratch before anything is timed
-        fn(dev_batches[0])
+    group = max(1, min(args.group, args.steps))
+    ptr_cache = {}
+    if group > 1:
+        fn = lambda sb: sage_group(ops, indptr, indices, sb, ptr_cache)
+    else:
+        fn = lambda sb: sage_batch_api(A, sb[0], "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
+    for _ in range(3):  # size scratch before anything is timed
+        fn(dev_batches[:group])
     ctx.profile_reset()
     launches0 = ctx.launch_count()
     sampler.start()
     ctx.profile_enable(True)
-    seconds, edges, shapes = timed_loop(torch, fn, it, args.warmup, args.steps, barrier)
+    seconds, edges, shapes = timed_group_loop(torch, fn, dev_batches, args.warmup, args.steps, group, barrier)
     ctx.profile_enable(False)
     clocks = sampler.stop()
     prof = ctx.profile_read()
@@ -238,13 +293,13 @@ def run_ours(args):
     # ---- e2e: pinned host seeds -> device, public API, edge count back on the host -------------------
     pinned = batches.pin_memory()
     h2d_bytes = BATCH * 8
-    d2h_bytes = 8 * 3 * len(FANOUTS)
+    d2h_bytes = 8 * 4 * len(FANOUTS)  # per call: the status + size counters read back at each hop
 
     def fn_e2e(host_seeds):
         s = host_seeds.to(device, non_blocking=True)
-        return sage_batch_api(A, s, "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
+        return fn(s)
 
-    e2e_seconds, e2e_edges, _ = timed_loop(torch, fn_e2e, iter(pinned), args.warmup, args.steps, barrier)
+    e2e_seconds, e2e_edges, _ = timed_group_loop(torch, fn_e2e, pinned, args.warmup, args.steps, group, barrier)
     e2e_seconds_all, e2e_edges_all = reduce_stats(torch, dist, world, e2e_seconds, e2e_edges, device)
 
     if rank != 0:
@@ -263,6 +318,7 @@ def run_ours(args):
     # the profile covers warm-up + timed steps; algorithmic bytes are averaged per launch over the timed steps
     n_hops = len(FANOUTS)
     bytes_per_launch = sum(algorithmic_bytes_sample(s) for s in shapes) / max(1, len(shapes) * n_hops)
+    timed_launches = len(shapes) * n_hops
     avg_launch_s = (sample_ms / 1e3) / max(1, sample_n)
     achieved = bytes_per_launch / avg_launch_s / 1e9 if avg_launch_s > 0 else 0.0
     roofline = {"bound": "hbm", "kernel": "k_sample_uniform (fused count + scan + sample)",
@@ -282,10 +338,13 @@ def run_ours(args):
                                "relabel per hop (BASELINE config 2)",
                    "graph": info, "batch": BATCH, "fanouts": FANOUTS, "parallelism": f"replicated graph, dp{world}",
                    "l2": "inputs larger than L2: 1 GB of indices gathered at random, no flush",
-                   "path": "Graph API per hop (fused slice+sample, relabel)"},
+                   "group": group,
+                   "path": ("batched sampler: %d minibatches per call, per hop one fused slice+sample launch and one "
+                            "batched unique+relabel" % group) if group > 1 else
+                           "Graph API per batch and hop (fused slice+sample, relabel)"},
         "edges_per_step": edges_all / args.steps / world,
         "e2e": {"value": e2e_edges_all / e2e_seconds_all, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
-                "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_seconds_all / args.steps * 1e3},
+                "d2h_bytes_per_step": d2h_bytes / group, "ms_per_step": e2e_seconds_all / args.steps * 1e3},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roofline,

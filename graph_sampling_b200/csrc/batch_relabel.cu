@@ -1,0 +1,329 @@
+// Batched ("super-batch") unique + relabel: many minibatches in one launch sequence.
+//
+// Input: G batches.  Batch b owns the seed ids seeds[seeds_ptr[b] .. seeds_ptr[b+1]) and the sampled
+// neighbour ids indices[indices_ptr[b] .. indices_ptr[b+1]).  Per batch the result is what
+// unique + relabel gives on cat(seeds_b, indices_b): the distinct ids in first-occurrence order
+// (the frontier, seeds first) and every neighbour id replaced by its position in that frontier.
+// All frontiers are stored back to back (unique_ptr[b] .. unique_ptr[b+1]).
+//
+// One launch handles all batches.  Items are numbered batch-major (seeds of batch 0, neighbours of
+// batch 0, seeds of batch 1, ...), so a CTA's tile of consecutive items belongs to one or two
+// batches, and each batch has its own hash-table region sized from its own item count: the regions
+// that are live at any moment are the few batches the resident CTAs are working on, a few MB that
+// stay in L2, instead of one table for everything.  A slot is one 64-bit word (id << 32 | position)
+// claimed with a CAS and lowered with atomicMin, so ids must be below 2^32 - 1 and a call may hold
+// at most 2^31 items.  Sizes are read from device memory (the edge total of the preceding sampling
+// kernel never has to visit the host); grids are sized from the caller's upper bound.
+//
+// Replaces gs::impl::BatchCSRRelabelCUDA (src/cuda/batch_relabel.cu:90-320), which keeps two int64
+// arrays per table, three passes with separate prefix-sum calls and a host round trip per pass.
+#include "common.cuh"
+#include "scan.cuh"
+
+namespace gsb {
+
+constexpr int kBThreads = 256;
+constexpr int kBPerThread = 4;
+constexpr int kBTile = kBThreads * kBPerThread;
+constexpr u64 kEmptyWord = 0xFFFFFFFFFFFFFFFFull;
+constexpr uint32_t kFinalBit = 0x80000000u;
+
+struct BatchLayout {
+  const i64* seeds;
+  const i64* seeds_ptr;    // [G + 1]
+  const i64* indices;
+  const i64* indices_ptr;  // [G + 1]
+  i64 G;
+  i64* item_off;    // [G + 1]  seeds_ptr[b] + indices_ptr[b]
+  i64* region_off;  // [G + 1]  slot offsets
+  u64* slots;
+  i64 slot_capacity;
+};
+
+__device__ __forceinline__ i64 region_size_for(i64 items) { return items + (items >> 2) + 32; }
+
+// One CTA: per-batch item offsets and table regions (exclusive scan over the G region sizes).
+__global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters) {
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (i64 b0 = 0; b0 < L.G; b0 += kBThreads) {
+    const i64 b = b0 + threadIdx.x;
+    i64 size = 0;
+    if (b < L.G) {
+      const i64 io = L.seeds_ptr[b] + L.indices_ptr[b];
+      L.item_off[b] = io;
+      size = region_size_for(L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - io);
+    }
+    i64 total;
+    const i64 excl = block_exclusive_scan<kBThreads>(size, s_scan, &total);
+    const i64 carry = s_carry;
+    if (b < L.G) L.region_off[b] = carry + excl;
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry = carry + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    L.item_off[L.G] = L.seeds_ptr[L.G] + L.indices_ptr[L.G];
+    L.region_off[L.G] = s_carry;
+    if (s_carry > L.slot_capacity) raise_error(counters, GSB_ERR_CAPACITY, s_carry);
+  }
+}
+
+// Largest b with off[b] <= g  (off has G + 1 non-decreasing entries, off[0] = 0 <= g < off[G]).
+__device__ __forceinline__ i64 batch_of(const i64* __restrict__ off, i64 G, i64 g) {
+  i64 lo = 0, hi = G;
+  while (hi - lo > 1) {
+    const i64 mid = (lo + hi) >> 1;
+    if (__ldg(off + mid) <= g) lo = mid;
+    else hi = mid;
+  }
+  return lo;
+}
+
+struct ItemRef {
+  i64 batch;
+  i64 local;   // position among the batch's items (seeds first)
+  i64 node;
+  u64* region;
+  i64 size;
+};
+
+__device__ __forceinline__ ItemRef resolve_item(const BatchLayout& L, i64 g) {
+  ItemRef r;
+  r.batch = batch_of(L.item_off, L.G, g);
+  const i64 s0 = __ldg(L.seeds_ptr + r.batch), s1 = __ldg(L.seeds_ptr + r.batch + 1);
+  r.local = g - __ldg(L.item_off + r.batch);
+  const i64 ns = s1 - s0;
+  r.node = r.local < ns ? __ldg(L.seeds + s0 + r.local)
+                        : __ldg(L.indices + __ldg(L.indices_ptr + r.batch) + (r.local - ns));
+  const i64 ro = __ldg(L.region_off + r.batch);
+  r.region = L.slots + ro;
+  r.size = __ldg(L.region_off + r.batch + 1) - ro;
+  return r;
+}
+
+__device__ __forceinline__ i64 home_slot(i64 node, i64 size) {
+  const uint32_t h = (uint32_t)(((u64)node * 0x9E3779B97F4A7C15ull) >> 32);
+  return (i64)(((u64)h * (u64)size) >> 32);
+}
+
+__global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
+  const i64 n = L.item_off[L.G];
+  for (i64 g = (i64)blockIdx.x * kBThreads + threadIdx.x; g < n; g += (i64)gridDim.x * kBThreads) {
+    const ItemRef it = resolve_item(L, g);
+    if (it.node < 0 || it.node >= 0xFFFFFFFFll) {
+      raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+      continue;
+    }
+    const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.local;
+    i64 h = home_slot(it.node, it.size);
+    bool done = false;
+    for (i64 probe = 0; probe < it.size; ++probe) {
+      u64* s = it.region + h;
+      u64 w = __ldcg(s);
+      if (w == kEmptyWord) {
+        const u64 old = atomicCAS(s, kEmptyWord, mine);
+        if (old == kEmptyWord) {
+          done = true;
+          break;
+        }
+        w = old;
+      }
+      if ((w >> 32) == (u64)it.node) {
+        if ((uint32_t)w > (uint32_t)it.local) atomicMin(s, mine);
+        done = true;
+        break;
+      }
+      h = (h + 1 == it.size) ? 0 : h + 1;
+    }
+    if (!done) raise_error(counters, GSB_ERR_TABLE_FULL, g);
+  }
+}
+
+__device__ __forceinline__ u64* find_slot(const ItemRef& it) {
+  i64 h = home_slot(it.node, it.size);
+  for (i64 probe = 0; probe < it.size; ++probe) {
+    u64* s = it.region + h;
+    const u64 w = *s;
+    if ((w >> 32) == (u64)it.node) return s;
+    if (w == kEmptyWord) return nullptr;
+    h = (h + 1 == it.size) ? 0 : h + 1;
+  }
+  return nullptr;
+}
+
+struct CompactOut {
+  i64* unique;      // all frontiers back to back
+  i64* unique_ptr;  // [G + 1]
+};
+
+__global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, CompactOut out, i64* counters,
+                                                             TileState ts) {
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_base;
+  const i64 n = L.item_off[L.G];
+  const int tile = blockIdx.x;
+  const i64 base = (i64)tile * kBTile;
+  if (base >= n && !(n == 0 && tile == 0)) return;
+  ItemRef it[kBPerThread];
+  u64* slot[kBPerThread];
+  int first[kBPerThread];
+  int mine = 0;
+#pragma unroll
+  for (int q = 0; q < kBPerThread; ++q) {
+    const i64 g = base + (i64)threadIdx.x * kBPerThread + q;
+    first[q] = 0;
+    slot[q] = nullptr;
+    if (g < n) {
+      it[q] = resolve_item(L, g);
+      slot[q] = find_slot(it[q]);
+      first[q] = (slot[q] != nullptr && (uint32_t)(*slot[q]) == (uint32_t)it[q].local) ? 1 : 0;
+      mine += first[q];
+    }
+  }
+  i64 total;
+  const i64 excl = block_exclusive_scan<kBThreads>((i64)mine, s_scan, &total);
+  if (threadIdx.x < 32) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, total);
+    if (threadIdx.x == 0) s_base = prefix;
+  }
+  __syncthreads();
+  i64 pos = s_base + excl;
+#pragma unroll
+  for (int q = 0; q < kBPerThread; ++q) {
+    const i64 g = base + (i64)threadIdx.x * kBPerThread + q;
+    if (g < n) {
+      // the first item of a batch is always a first occurrence: its prefix is the batch's frontier offset
+      if (it[q].local == 0) {
+        out.unique_ptr[it[q].batch] = pos;
+        // batches without any item in front of this one start (and end) at the same offset
+        for (i64 e = it[q].batch - 1; e >= 0 && __ldg(L.item_off + e) == g; --e) out.unique_ptr[e] = pos;
+      }
+      if (first[q]) {
+        out.unique[pos] = it[q].node;
+        // final value: compacted position with the top bit set, so that it can never equal the
+        // position of a later duplicate that is still being tested in this launch
+        *slot[q] = ((u64)it[q].node << 32) | (u64)(kFinalBit | (uint32_t)pos);
+        ++pos;
+      }
+    }
+  }
+  if (base + kBTile >= n && threadIdx.x == kBThreads - 1) {
+    out.unique_ptr[L.G] = s_base + total;
+    for (i64 e = L.G - 1; e >= 0 && __ldg(L.item_off + e) == n; --e) out.unique_ptr[e] = s_base + total;
+    counters[CNT_UNIQUE] = s_base + total;
+    counters[CNT_NNZ] = L.indices_ptr[L.G];
+  }
+}
+
+__global__ void __launch_bounds__(kBThreads) k_batch_relabel(BatchLayout L, const i64* __restrict__ unique_ptr,
+                                                             i64* __restrict__ out_relabeled) {
+  const i64 E = L.indices_ptr[L.G];
+  for (i64 p = (i64)blockIdx.x * kBThreads + threadIdx.x; p < E; p += (i64)gridDim.x * kBThreads) {
+    ItemRef it;
+    it.batch = batch_of(L.indices_ptr, L.G, p);
+    it.node = __ldg(L.indices + p);
+    const i64 ro = __ldg(L.region_off + it.batch);
+    it.region = L.slots + ro;
+    it.size = __ldg(L.region_off + it.batch + 1) - ro;
+    it.local = 0;
+    const u64* s = find_slot(it);
+    out_relabeled[p] = s ? (i64)((uint32_t)(*s) & ~kFinalBit) - __ldg(unique_ptr + it.batch) : -1;
+  }
+}
+
+__global__ void __launch_bounds__(kBThreads) k_gather_offsets(const i64* __restrict__ sub_indptr,
+                                                              const i64* __restrict__ seeds_ptr, i64 G,
+                                                              i64* __restrict__ out) {
+  const i64 b = (i64)blockIdx.x * kBThreads + threadIdx.x;
+  if (b <= G) out[b] = sub_indptr[seeds_ptr[b]];
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" {
+
+int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream_, const int64_t* sub_indptr, const int64_t* seeds_ptr,
+                           int64_t G, int64_t* out_indices_ptr) {
+  GSB_REQUIRE(ctx && sub_indptr && seeds_ptr && out_indices_ptr && G >= 0, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+  k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(sub_indptr, seeds_ptr, G, out_indices_ptr);
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, const int64_t* seeds_ptr,
+                             int64_t num_seeds, const int64_t* indices, const int64_t* indices_ptr,
+                             int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
+                             int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host) {
+  GSB_REQUIRE(ctx && seeds_ptr && indices_ptr && out_unique_ptr && G >= 1 && num_seeds >= 0 && indices_capacity >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  const i64 n_cap = num_seeds + indices_capacity;
+  GSB_REQUIRE(n_cap < (1ll << 31), GSB_ERR_UNSUPPORTED);
+  GSB_REQUIRE(n_cap == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 * G + 64;
+  const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
+  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, slots_bytes + 2 * off_bytes, &ws);
+  if (st != GSB_OK) return st;
+  BatchLayout L;
+  L.seeds = seeds;
+  L.seeds_ptr = seeds_ptr;
+  L.indices = indices;
+  L.indices_ptr = indices_ptr;
+  L.G = G;
+  L.slots = (u64*)ws;
+  L.item_off = (i64*)((char*)ws + slots_bytes);
+  L.region_off = (i64*)((char*)ws + slots_bytes + off_bytes);
+  L.slot_capacity = slot_cap;
+  i64* counters = ctx_counters(ctx);
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
+    GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
+  }
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters);
+  }
+  GSB_LAUNCH_OK();
+  const int wide = kNumSMs * 8;
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
+    k_batch_insert<<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
+  }
+  GSB_LAUNCH_OK();
+  const int tiles = grid_for(n_cap, kBTile);
+  TileState ts;
+  st = ctx_tile_state(ctx, tiles, stream, &ts);
+  if (st != GSB_OK) return st;
+  CompactOut out{out_unique, out_unique_ptr};
+  {
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_batch_compact<<<tiles, kBThreads, 0, stream>>>(L, out, counters, ts);
+  }
+  GSB_LAUNCH_OK();
+  if (indices_capacity > 0 && out_relabeled) {
+    ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
+    k_batch_relabel<<<max(1, min(grid_for(indices_capacity, kBThreads), wide)), kBThreads, 0, stream>>>(
+        L, out_unique_ptr, out_relabeled);
+  }
+  GSB_LAUNCH_OK();
+  if (unique_total_host || edges_total_host) {
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
+    if (st != GSB_OK) return st;
+    if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
+    if (edges_total_host) *edges_total_host = c[CNT_NNZ];
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  }
+  return GSB_OK;
+}
+
+}  // extern "C"

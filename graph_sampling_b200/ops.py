@@ -466,3 +466,78 @@ def coo2csc(row, col, num_cols, col_sorted, ctx=None):
     ctx.check(ctx.lib.gsb_coo2csc(ctx.handle, _stream(), _p(col), _p(row), c_i64(E), c_i64(int(num_cols)),
                                   c_int(int(bool(col_sorted))), _p(indptr), _p(out_row), _p(perm)), "gsb_coo2csc")
     return indptr, out_row, perm
+
+
+# ---- batched ("super-batch") operators --------------------------------------------------------------
+def batch_csr_relabel(seeds, seeds_ptr, indices, indices_ptr, indices_count=None, ctx=None, sync=True):
+    """BatchCSRRelabelCUDA (src/cuda/batch_relabel.cu, gs_ops._CAPI_BatchCSRRelabel) →
+    (unique_tensor, unique_tensor_ptr, relabeled_indices, indices_ptr): per batch b, the distinct ids of
+    cat(seeds[seeds_ptr[b]:seeds_ptr[b+1]], indices[indices_ptr[b]:indices_ptr[b+1]]) in first-occurrence
+    order and the batch-local positions of its indices.  `indices` may be longer than the valid edge
+    count (indices_ptr[-1]); with sync=False the outputs keep their upper-bound length and the exact
+    sizes stay on the device."""
+    seeds, seeds_ptr = _i64(seeds, "seeds"), _i64(seeds_ptr, "seeds_ptr")
+    indices, indices_ptr = _i64(indices, "indices"), _i64(indices_ptr, "indices_ptr")
+    ctx = ctx or default_context(seeds.device)
+    G = seeds_ptr.numel() - 1
+    cap = indices.numel() if indices_count is None else int(indices_count)
+    uniq = _empty(seeds.numel() + cap, seeds)
+    uniq_ptr = _empty(G + 1, seeds)
+    rel = _empty(cap, seeds)
+    nu, ne = c_i64(0), c_i64(0)
+    ctx.check(ctx.lib.gsb_batch_unique_relabel(ctx.handle, _stream(), _p(seeds), _p(seeds_ptr), c_i64(seeds.numel()),
+                                               _p(indices), _p(indices_ptr), c_i64(cap), c_i64(G), _p(uniq),
+                                               _p(uniq_ptr), _p(rel), ctypes.byref(nu) if sync else None,
+                                               ctypes.byref(ne) if sync else None), "gsb_batch_unique_relabel")
+    if sync:
+        return uniq[:nu.value], uniq_ptr, rel[:ne.value], indices_ptr
+    return uniq, uniq_ptr, rel, indices_ptr
+
+
+def batch_edge_offsets(sub_indptr, seeds_ptr, ctx=None):
+    """indices_ptr[b] = sub_indptr[seeds_ptr[b]] (what GetBatchCSC derives, examples/graphsage/batching.py:66)."""
+    sub_indptr, seeds_ptr = _i64(sub_indptr, "sub_indptr"), _i64(seeds_ptr, "seeds_ptr")
+    ctx = ctx or default_context(sub_indptr.device)
+    out = _empty(seeds_ptr.numel(), seeds_ptr)
+    ctx.check(ctx.lib.gsb_batch_edge_offsets(ctx.handle, _stream(), _p(sub_indptr), _p(seeds_ptr),
+                                             c_i64(seeds_ptr.numel() - 1), _p(out)), "gsb_batch_edge_offsets")
+    return out
+
+
+def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None):
+    """Multi-hop GraphSAGE sampling of G minibatches at once (the loop of
+    examples/graphsage/batching.py:56-90): per hop one fused slice+sample over the seeds of all batches,
+    then one batched unique + relabel; each batch's frontier becomes its seeds for the next hop.
+
+    Returns a list (one entry per hop) of dicts with: seeds, seeds_ptr (columns of the hop and their
+    per-batch offsets), sub_indptr (offsets over all columns), indices (global ids), relabeled
+    (batch-local ids), select_index, indices_ptr, frontier, frontier_ptr.  One host synchronisation
+    per hop (to learn the frontier size that sizes the next hop)."""
+    ctx = ctx or default_context(indptr.device)
+    out = []
+    base_seed = next_seed(seed)
+    for hop, k in enumerate(fanouts):
+        S = seeds.numel()
+        cap = S * int(k)
+        sub_indptr = _empty(S + 1, indptr)
+        sub_indices, select = _empty(cap, indptr), _empty(cap, indptr)
+        ctx.check(ctx.lib.gsb_sample_uniform(ctx.handle, _stream(), _p(indptr), _p(indices), _p(seeds), c_i64(S),
+                                             c_i64(int(k)), c_int(int(bool(replace))), c_u64((base_seed + hop) & (2**64 - 1)),
+                                             _p(sub_indptr), _p(sub_indices), _p(select), _p(None), _p(None), _p(None),
+                                             _p(None), c_i64(cap), None), "gsb_sample_uniform")
+        indices_ptr = batch_edge_offsets(sub_indptr, seeds_ptr, ctx)
+        G = seeds_ptr.numel() - 1
+        uniq = _empty(S + cap, indptr)
+        uniq_ptr = _empty(G + 1, indptr)
+        rel = _empty(cap, indptr)
+        nu, ne = c_i64(0), c_i64(0)
+        ctx.check(ctx.lib.gsb_batch_unique_relabel(ctx.handle, _stream(), _p(seeds), _p(seeds_ptr), c_i64(S),
+                                                   _p(sub_indices), _p(indices_ptr), c_i64(cap), c_i64(G), _p(uniq),
+                                                   _p(uniq_ptr), _p(rel), ctypes.byref(nu), ctypes.byref(ne)),
+                  "gsb_batch_unique_relabel")
+        E, U = ne.value, nu.value
+        out.append(dict(seeds=seeds, seeds_ptr=seeds_ptr, sub_indptr=sub_indptr, indices=sub_indices[:E],
+                        relabeled=rel[:E], select_index=select[:E], indices_ptr=indices_ptr, frontier=uniq[:U],
+                        frontier_ptr=uniq_ptr))
+        seeds, seeds_ptr = uniq[:U], uniq_ptr
+    return out

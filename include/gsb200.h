@@ -244,6 +244,27 @@ GSB_API int gsb_csc2coo(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64
 GSB_API int gsb_coo2csc(gsb_ctx* ctx, void* stream, const int64_t* key, const int64_t* other, int64_t E,
                         int64_t num_keys, int key_sorted, int64_t* out_indptr, int64_t* out_other, int64_t* out_perm);
 
+/* ---- batched ("super-batch") unique + relabel -------------------------------------------------------
+ * Replaces gs::impl::BatchCSRRelabelCUDA (src/cuda/batch_relabel.cu:90-320, registered as
+ * gs_ops._CAPI_BatchCSRRelabel, src/pybind.cc:76) and the GetBatchCSC offset gather used with it
+ * (examples/graphsage/batching.py:64-69): G minibatches are relabelled by one launch sequence.
+ * Batch b owns seeds[seeds_ptr[b] .. seeds_ptr[b+1]) and indices[indices_ptr[b] .. indices_ptr[b+1]);
+ * per batch: out_unique[out_unique_ptr[b] .. out_unique_ptr[b+1]) = distinct ids of
+ * cat(seeds_b, indices_b) in first-occurrence order, out_relabeled[p] = position of indices[p] in its
+ * batch's frontier.  seeds_ptr / indices_ptr / out_unique_ptr are DEVICE arrays of G + 1 entries; the
+ * number of edges is read from indices_ptr[G] on the device, so the call can follow a sampling call
+ * without a host round trip; `indices_capacity` is an upper bound on it used to size scratch and grids.
+ * Ids must be below 2^32 - 1 and num_seeds + indices_capacity below 2^31.  Waits for the stream only if
+ * a *_host pointer is given.
+ * gsb_batch_edge_offsets: out_indices_ptr[b] = sub_indptr[seeds_ptr[b]] for b in [0, G].
+ */
+GSB_API int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream, const int64_t* sub_indptr, const int64_t* seeds_ptr,
+                                   int64_t G, int64_t* out_indices_ptr);
+GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* seeds, const int64_t* seeds_ptr,
+                                     int64_t num_seeds, const int64_t* indices, const int64_t* indices_ptr,
+                                     int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
+                                     int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
+
 #ifdef __cplusplus
 }
 #endif
