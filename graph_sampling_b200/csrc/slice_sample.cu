@@ -222,6 +222,100 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
   }
 }
 
+
+// ---- thread-per-column sampler for small fanouts --------------------------------------------------
+// One lane owns one column: it draws all k picks itself (Floyd's k-subset in registers, one Philox
+// block per four picks), issues the k gathers back to back and then stores.  A warp is a tile of 32
+// columns: counts are scanned with shuffles and the tile prefix comes from the same look-back chain,
+// so the kernel has no CTA-wide barrier at all and every lane keeps k independent loads in flight.
+constexpr int kTpcThreads = 128;
+
+template <int KMAX>
+__global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams p) {
+  const int lane = threadIdx.x & 31;
+  const i64 tile = (i64)blockIdx.x * (kTpcThreads / 32) + (threadIdx.x >> 5);
+  const i64 S = p.S;
+  if (tile * 32 >= S && !(S == 0 && tile == 0)) return;
+  const i64 i = tile * 32 + lane;
+  const bool valid = i < S;
+  const int k = (int)p.k;
+  i64 b = 0, d = 0, f = 0;
+  if (valid) {
+    const i64 col = p.seeds ? __ldg(p.seeds + i) : i;
+    b = __ldg(p.indptr + col);
+    d = __ldg(p.indptr + col + 1) - b;
+    f = column_count(d, k, p.replace ? COUNT_WR : COUNT_WOR);
+  }
+  i64 inc = f;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const i64 t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  const i64 total = __shfl_sync(0xffffffffu, inc, 31);
+  const i64 prefix = __shfl_sync(0xffffffffu, tile_exclusive_prefix(p.ts, (int)tile, total), 0);
+  const i64 o = prefix + inc - f;
+  if (valid) {
+    p.out_indptr[i] = o;
+    if (i == S - 1) {
+      p.out_indptr[S] = o + f;
+      p.counters[CNT_NNZ] = o + f;
+    }
+  } else if (S == 0 && lane == 0) {
+    p.out_indptr[0] = 0;
+    p.counters[CNT_NNZ] = 0;
+  }
+  if (prefix + total > p.capacity) {
+    if (lane == 0) raise_error(p.counters, GSB_ERR_CAPACITY, prefix + total);
+    return;
+  }
+  if (!valid || f == 0) return;
+  if (d > 0xFFFFFFFFll) {
+    raise_error(p.counters, GSB_ERR_UNSUPPORTED, i);
+    return;
+  }
+  uint32_t pick[KMAX];
+  const int n = (int)f;
+  if (p.replace || d > k) {
+    U32x4 blk;
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      if (j < k) {
+        if ((j & 3) == 0) blk = rand_block(p.seed, (u64)i, (u64)(j >> 2), STREAM_UNIFORM);
+        const uint32_t word = (j & 3) == 0 ? blk.v[0] : (j & 3) == 1 ? blk.v[1] : (j & 3) == 2 ? blk.v[2] : blk.v[3];
+        if (p.replace) {
+          pick[j] = (uint32_t)bounded_from_word(word, (u64)d);
+        } else {
+          const uint32_t m = (uint32_t)(d - k + j);
+          const uint32_t t = (uint32_t)bounded_from_word(word, (u64)m + 1);
+          bool dup = false;
+#pragma unroll
+          for (int q = 0; q < KMAX; ++q)
+            if (q < j) dup |= (pick[q] == t);
+          pick[j] = dup ? m : t;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) pick[j] = (uint32_t)j;
+  }
+  i64 val[KMAX];
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j)
+    if (j < n) val[j] = __ldg(p.indices + b + pick[j]);
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    if (j < n) {
+      const i64 in_pos = b + pick[j];
+      p.out_indices[o + j] = val[j];
+      p.out_select[o + j] = in_pos;
+      if (p.out_coo_col) p.out_coo_col[o + j] = i;
+      if (p.out_data) p.out_data[o + j] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) k_sample_one_keepdim(const i64* __restrict__ indptr,
                                                                  const i64* __restrict__ indices,
                                                                  const i64* __restrict__ seeds, i64 S, u64 seed,
@@ -301,17 +395,18 @@ int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
   GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const int grid = grid_for(S, kTileCols);
+  const bool per_thread = k <= 16;  // small fanouts: one lane per column, one warp per tile of 32 columns
+  const int grid = per_thread ? grid_for(S, kTpcThreads) : grid_for(S, kTileCols);
   TileState ts;
-  int st = ctx_tile_state(ctx, grid, stream, &ts);
+  int st = ctx_tile_state(ctx, per_thread ? (S + 31) / 32 + 1 : grid, stream, &ts);
   if (st != GSB_OK) return st;
   SampleParams p{indptr, indices, seeds,  S,        k,        replace,         (u64)seed, out_indptr, out_indices,
                  out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts};
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
-    if (k <= 4) launch_sample<4>(p, grid, stream);
-    else if (k <= 8) launch_sample<8>(p, grid, stream);
-    else if (k <= 16) launch_sample<16>(p, grid, stream);
+    if (k <= 4) k_sample_uniform_tpc<4><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 8) k_sample_uniform_tpc<8><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 16) k_sample_uniform_tpc<16><<<grid, kTpcThreads, 0, stream>>>(p);
     else launch_sample<32>(p, grid, stream);
   }
   GSB_LAUNCH_OK();
