@@ -202,3 +202,110 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
   }
   return GSB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of unique + relabel.
+//
+// Some hosts of this library are not allowed to allocate device memory while they run: code that
+// executes inside a memory pool owned by another runtime with a fixed budget, plug-ins loaded into
+// a serving process after its arena has been carved up, or callers holding a lock under which
+// cudaMalloc (which synchronises the whole device) is forbidden.  gsb_unique_relabel needs a context,
+// and the context grows its scratch with cudaMalloc the first time a size is seen.  The entry point
+// below needs neither: its hash table, look-back words and counters live in file-scope __device__
+// arrays that every GPU loading the library carries until the process exits (about 8.1 MB), which
+// bounds the problem size (GSB_STATIC_MAX_ITEMS items per call).
+//
+// All calls share these arrays and the arrays keep the previous call's contents, so each call first
+// clears (stream-ordered) everything that must start empty.  Two calls that overlap on the GPU —
+// different streams, or different host threads — would race on the shared scratch.
+namespace gsb {
+
+constexpr i64 kStaticMaxItems = GSB_STATIC_MAX_ITEMS;
+constexpr u64 kStaticSlots = 2 * (u64)kStaticMaxItems;  // power of two, load factor <= 0.5
+constexpr int kStaticTiles = (int)(kStaticMaxItems / kTileItems) + 2;
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) Slot g_static_slots[kStaticSlots];
+static __device__ __align__(256) u64 g_static_tile_words[kStaticTiles];
+static __device__ __align__(256) i64 g_static_counters[CNT_NUM];
+
+struct StaticScratch {
+  Slot* slots;
+  u64* tile_words;
+  i64* counters;
+  bool ready;
+};
+// Host-side table of the device addresses of the arrays above, one entry per device.  In host code
+// the array names are only stand-ins for the symbols; the addresses a kernel can use come from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static StaticScratch s_static[kMaxDevices];
+
+static int static_scratch_for_current_device(StaticScratch** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return GSB_ERR_CUDA;
+  StaticScratch* s = &s_static[dev];
+  if (!s->ready) {
+    void *a = nullptr, *b = nullptr, *c = nullptr;
+    if (cudaGetSymbolAddress(&a, g_static_slots) != cudaSuccess) return GSB_ERR_CUDA;
+    if (cudaGetSymbolAddress(&b, g_static_tile_words) != cudaSuccess) return GSB_ERR_CUDA;
+    if (cudaGetSymbolAddress(&c, g_static_counters) != cudaSuccess) return GSB_ERR_CUDA;
+    s->slots = (Slot*)a;
+    s->tile_words = (u64*)b;
+    s->counters = (i64*)c;
+    s->ready = true;
+  }
+  *out = s;
+  return GSB_OK;
+}
+
+}  // namespace gsb
+
+extern "C" int64_t gsb_static_max_items(void) { return gsb::kStaticMaxItems; }
+
+extern "C" int gsb_unique_relabel_static(void* stream_, const int64_t* items, int64_t n, int64_t* out_unique,
+                                         const int64_t* to_relabel, int64_t m, int64_t* out_relabeled,
+                                         int64_t* out_counts) {
+  if (n < 0 || m < 0 || !out_counts) return GSB_ERR_INVALID_ARGUMENT;
+  if (n > kStaticMaxItems) return GSB_ERR_CAPACITY;  // more items than the built-in table can hold
+  if ((n > 0 && (!items || !out_unique)) || (m > 0 && (!to_relabel || !out_relabeled))) return GSB_ERR_INVALID_ARGUMENT;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  StaticScratch* sc = nullptr;
+  int st = static_scratch_for_current_device(&sc);
+  if (st != GSB_OK) return st;
+
+  Segments seg_items, seg_rel;
+  const int64_t* ip[1] = {items};
+  const int64_t il[1] = {n};
+  st = fill_segments(&seg_items, ip, il, nullptr, 1);
+  if (st != GSB_OK) return st;
+  const int64_t* rp[1] = {to_relabel};
+  const int64_t rl[1] = {m};
+  int64_t* ro[1] = {out_relabeled};
+  st = fill_segments(&seg_rel, rp, rl, ro, m > 0 ? 1 : 0);
+  if (st != GSB_OK) return st;
+
+  Table table;
+  u64 cap;
+  table_geometry(n, &cap, &table.shift);  // power of two >= 2n, never above kStaticSlots
+  table.mask = cap - 1;
+  table.slots = sc->slots;
+  // the shared arrays still hold the previous call's state: empty the table, the look-back words
+  // and the counters before use
+  if (cudaMemsetAsync(sc->slots, 0xFF, cap * sizeof(Slot), stream) != cudaSuccess) return GSB_ERR_CUDA;
+  if (cudaMemsetAsync(sc->tile_words, 0, sizeof(u64) * kStaticTiles, stream) != cudaSuccess) return GSB_ERR_CUDA;
+  if (cudaMemsetAsync(sc->counters, 0, sizeof(i64) * CNT_NUM, stream) != cudaSuccess) return GSB_ERR_CUDA;
+  TileState ts{sc->tile_words, 1u, sc->counters};
+  const int sm_grid = kNumSMs * 8;
+  if (n > 0) k_insert<<<min(grid_for(n, kThreads), sm_grid), kThreads, 0, stream>>>(seg_items, table, sc->counters);
+  k_first_compact<<<grid_for(n, kTileItems), kThreads, 0, stream>>>(seg_items, table, out_unique, sc->counters, ts);
+  if (m > 0) k_relabel<<<min(grid_for(m, kThreads), sm_grid), kThreads, 0, stream>>>(seg_rel, table);
+  if (cudaGetLastError() != cudaSuccess) return GSB_ERR_CUDA;
+  // results stay on the device: [0] = number of distinct ids, [1] = first device-side error code (0 = none)
+  if (cudaMemcpyAsync(out_counts, sc->counters + CNT_UNIQUE, sizeof(i64), cudaMemcpyDeviceToDevice, stream) !=
+      cudaSuccess)
+    return GSB_ERR_CUDA;
+  if (cudaMemcpyAsync(out_counts + 1, sc->counters + CNT_ERROR, sizeof(i64), cudaMemcpyDeviceToDevice, stream) !=
+      cudaSuccess)
+    return GSB_ERR_CUDA;
+  return GSB_OK;
+}

@@ -265,6 +265,31 @@ GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* 
                                      int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
                                      int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
 
+/* ---- unique + relabel without any allocation ----------------------------------------------------------
+ * No counterpart in the reference.  For callers that must not allocate device memory while they
+ * run (a host process whose memory budget is fixed up front, a plug-in running under a lock that
+ * forbids the device-wide synchronisation cudaMalloc implies): the same result as gsb_unique_relabel
+ * for ONE item array, computed with scratch that is compiled into the library as device arrays
+ * (about 8.1 MB per GPU, held from library load to process exit) instead of a context's arena.
+ *   - at most GSB_STATIC_MAX_ITEMS items per call; a larger `n` returns GSB_ERR_CAPACITY and
+ *     launches nothing;
+ *   - no gsb_ctx; nothing is allocated or freed, on the host or the device;
+ *   - the first call on a device looks up the device addresses of the built-in arrays (it must be
+ *     made with that device current, and it should come before any stream capture begins);
+ *   - all calls share the built-in scratch, which still holds the previous call's state; every call
+ *     clears what it needs on `stream` first.  Calls whose GPU work overlaps (other streams, other
+ *     threads) race on it: order them on one stream;
+ *   - nothing is read back: out_counts (DEVICE, 2 entries) receives the number of distinct ids and
+ *     the first device-side error code (0 = none) in stream order.
+ * out_unique must hold n entries; ids must be >= 0; out_relabeled[j] = position of to_relabel[j] in
+ * out_unique, or -1 if the id is not among the items.
+ */
+#define GSB_STATIC_MAX_ITEMS 262144
+GSB_API int64_t gsb_static_max_items(void);
+GSB_API int gsb_unique_relabel_static(void* stream, const int64_t* items, int64_t n, int64_t* out_unique,
+                                      const int64_t* to_relabel, int64_t m, int64_t* out_relabeled,
+                                      int64_t* out_counts);
+
 #ifdef __cplusplus
 }
 #endif
