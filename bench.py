@@ -40,13 +40,13 @@ UNIT = "edges/s"
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=128)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--group", type=int, default=64,
+    ap.add_argument("--group", type=int, default=256,
                     help="minibatches handed to one call of the batched sampler (1 = per-batch Graph API)")
     return ap.parse_args()
 
@@ -172,8 +172,9 @@ def grouped(batches, group):
         i = 0 if j >= n else j
 
 
-def timed_group_loop(torch, fn, batches, warmup, steps, group, barrier):
-    """Times exactly `steps` minibatches, processed `group` at a time, after `warmup` untimed ones."""
+def timed_group_loop(torch, fn, batches, warmup, steps, group, barrier, ctx=None):
+    """Times exactly `steps` minibatches, processed `group` at a time, after `warmup` untimed ones.  With `ctx`,
+    per-kernel event timing and the launch counter cover exactly the timed region."""
     done = 0
     while done < warmup:
         g = min(group, warmup - done)
@@ -182,6 +183,11 @@ def timed_group_loop(torch, fn, batches, warmup, steps, group, barrier):
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
+    launches0 = 0
+    if ctx is not None:
+        ctx.profile_reset()
+        ctx.profile_enable(True)
+        launches0 = ctx.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     edges, all_shapes, at = 0, [], warmup
@@ -194,6 +200,9 @@ def timed_group_loop(torch, fn, batches, warmup, steps, group, barrier):
         at += g
     ev1.record()
     torch.cuda.synchronize()
+    if ctx is not None:
+        ctx.profile_enable(False)
+        timed_group_loop.launches = ctx.launch_count() - launches0
     barrier()
     return ev0.elapsed_time(ev1) / 1e3, edges, all_shapes
 
@@ -279,15 +288,11 @@ def run_ours(args):
         fn = lambda sb: sage_batch_api(A, sb[0], "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
     for _ in range(3):  # size scratch before anything is timed
         fn(dev_batches[:group])
-    ctx.profile_reset()
-    launches0 = ctx.launch_count()
     sampler.start()
-    ctx.profile_enable(True)
-    seconds, edges, shapes = timed_group_loop(torch, fn, dev_batches, args.warmup, args.steps, group, barrier)
-    ctx.profile_enable(False)
+    seconds, edges, shapes = timed_group_loop(torch, fn, dev_batches, args.warmup, args.steps, group, barrier, ctx)
     clocks = sampler.stop()
     prof = ctx.profile_read()
-    launches = ctx.launch_count() - launches0
+    launches = timed_group_loop.launches
     seconds_all, edges_all = reduce_stats(torch, dist, world, seconds, edges, device)
 
     # ---- e2e: pinned host seeds -> device, public API, edge count back on the host -------------------
@@ -313,20 +318,43 @@ def run_ours(args):
         peak, peak_src = float(_json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = 6650.0, "fallback"
-    timed = {k: v for k, v in prof.items()}
-    sample_ms, sample_n = timed.get("sample_uniform", (0.0, 0))
-    # the profile covers warm-up + timed steps; algorithmic bytes are averaged per launch over the timed steps
-    n_hops = len(FANOUTS)
-    bytes_per_launch = sum(algorithmic_bytes_sample(s) for s in shapes) / max(1, len(shapes) * n_hops)
-    timed_launches = len(shapes) * n_hops
-    avg_launch_s = (sample_ms / 1e3) / max(1, sample_n)
-    achieved = bytes_per_launch / avg_launch_s / 1e9 if avg_launch_s > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "k_sample_uniform (fused count + scan + sample)",
-                "achieved": round(achieved, 2), "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                "frac": round(achieved / peak, 5), "traffic": None,
-                "bytes_per_launch": round(bytes_per_launch), "avg_launch_us": round(avg_launch_s * 1e6, 2),
-                "kernel_ms": {k: round(v[0], 3) for k, v in timed.items()},
-                "kernel_launches": {k: v[1] for k, v in timed.items()}}
+    # Algorithmic bytes per launch of each hot kernel, from the shapes of the timed calls: (S, E, U) per hop.
+    # sample: 32 B per seed column (seed id, indptr pair, output offset) + 24 B per sampled edge (8 read, 16 written);
+    # unique + relabel is three passes over N = S + E items: insert reads 8 N; first-occurrence compaction reads 8 N
+    # and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead, not counted).
+    hop_shapes = [h for call in shapes for h in call]
+    n_launch = max(1, len(hop_shapes))
+    alg = {
+        "sample_uniform": sum(32 * s_ + 8 + 24 * e_ for s_, e_, _ in hop_shapes) / n_launch,
+        "table_insert": sum(8 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
+        "first_compact": sum(8 * (s_ + e_) + 8 * u_ for s_, e_, u_ in hop_shapes) / n_launch,
+        "relabel": sum(16 * e_ for s_, e_, _ in hop_shapes) / n_launch,
+    }
+    kernel_names = {"sample_uniform": "k_sample_uniform_tpc (fused count + scan + uniform sample)",
+                    "table_insert": "k_batch_insert / k_insert (position-min hash insert)",
+                    "first_compact": "k_batch_compact / k_first_compact (first-occurrence scan + compaction)",
+                    "relabel": "k_batch_relabel / k_relabel (lookup)"}
+    total_ms = sum(v[0] for v in prof.values()) or 1.0
+    per_kernel = {}
+    for name, (ms, n) in prof.items():
+        entry = {"ms": round(ms, 3), "launches": n, "share": round(ms / total_ms, 4)}
+        if name in alg and n:
+            avg_s = ms / 1e3 / n
+            entry["avg_launch_us"] = round(avg_s * 1e6, 2)
+            entry["bytes_per_launch"] = round(alg[name])
+            entry["achieved_gbs"] = round(alg[name] / avg_s / 1e9, 2)
+            entry["frac"] = round(alg[name] / avg_s / 1e9 / peak, 5)
+        per_kernel[name] = entry
+    top = max((k for k in per_kernel if k in alg), key=lambda k: per_kernel[k]["ms"], default=None)
+    if top is not None:
+        t = per_kernel[top]
+        roofline = {"bound": "hbm", "kernel": kernel_names[top], "achieved": t["achieved_gbs"], "peak": peak,
+                    "peak_source": peak_src, "unit": "GB/s", "frac": t["frac"], "traffic": None,
+                    "bytes_per_launch": t["bytes_per_launch"], "avg_launch_us": t["avg_launch_us"],
+                    "share_of_device_time": t["share"], "kernels": per_kernel}
+    else:
+        roofline = {"bound": "hbm", "kernel": None, "achieved": None, "peak": peak, "peak_source": peak_src,
+                    "unit": "GB/s", "frac": None, "traffic": None, "kernels": per_kernel}
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(indptr, indices, batches)
