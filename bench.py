@@ -40,8 +40,8 @@ UNIT = "edges/s"
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=8192)
+    ap.add_argument("--warmup", type=int, default=256)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
@@ -54,7 +54,7 @@ def parse():
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while a region is timed."""
 
-    def __init__(self, index, period=0.1):
+    def __init__(self, index, period=0.02):
         super().__init__(daemon=True)
         self.index, self.period = index, period
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -131,7 +131,8 @@ def make_inputs(args, device, world, rank):
     total_batches = (args.steps + args.warmup) * world
     allb = seed_batches(args.nodes, BATCH, total_batches, seed=GRAPH_SEED + 1, train_fraction=TRAIN_FRACTION,
                         device="cpu")
-    mine = allb[rank::world].contiguous()  # batch b -> rank b mod world
+    from graph_sampling_b200.sharding import shard_batches
+    mine = shard_batches(allb, rank, world)  # batch b -> rank b mod world
     return indptr, indices, mine, info
 
 
@@ -233,13 +234,8 @@ def timed_loop(torch, fn, batches_iter, warmup, steps, barrier):
 
 
 def reduce_stats(torch, dist, world, seconds, edges, device):
-    if world == 1:
-        return seconds, edges
-    t = torch.tensor([seconds], dtype=torch.float64, device=device)
-    e = torch.tensor([edges], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dist.all_reduce(e, op=dist.ReduceOp.SUM)
-    return float(t.item()), int(e.item())
+    from graph_sampling_b200.sharding import reduce_run_stats
+    return reduce_run_stats(seconds, edges, device=device)
 
 
 def cpu_baseline(indptr, indices, batches, budget_s=15.0):

@@ -109,49 +109,129 @@ __device__ __forceinline__ i64 home_slot(i64 node, i64 size) {
   return (i64)(((u64)h * (u64)size) >> 32);
 }
 
-__global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
-  const i64 n = L.item_off[L.G];
-  for (i64 g = (i64)blockIdx.x * kBThreads + threadIdx.x; g < n; g += (i64)gridDim.x * kBThreads) {
-    const ItemRef it = resolve_item(L, g);
-    if (it.node < 0 || it.node >= 0xFFFFFFFFll) {
-      raise_error(counters, GSB_ERR_INDEX_RANGE, g);
-      continue;
-    }
-    const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.local;
-    i64 h = home_slot(it.node, it.size);
-    bool done = false;
-    for (i64 probe = 0; probe < it.size; ++probe) {
-      u64* s = it.region + h;
-      u64 w = __ldcg(s);
-      if (w == kEmptyWord) {
-        const u64 old = atomicCAS(s, kEmptyWord, mine);
-        if (old == kEmptyWord) {
-          done = true;
-          break;
-        }
-        w = old;
-      }
-      if ((w >> 32) == (u64)it.node) {
-        if ((uint32_t)w > (uint32_t)it.local) atomicMin(s, mine);
-        done = true;
-        break;
-      }
-      h = (h + 1 == it.size) ? 0 : h + 1;
-    }
-    if (!done) raise_error(counters, GSB_ERR_TABLE_FULL, g);
-  }
+// ---- traversal by warp tiles ------------------------------------------------------------------------
+// A warp owns kWarpItems consecutive items, lane-strided so that loads coalesce.  Items are batch-major,
+// so almost every tile lies inside ONE batch: the batch is found once per tile (one binary search per
+// 128 items instead of one per item) and its parameters stay in warp-uniform registers.  The rare tile
+// that straddles a batch boundary resolves each item on its own (resolve_item).  Each lane first issues
+// the loads of its four ids, then the four home-slot probes, so four independent memory round trips are
+// in flight per lane; only a collision enters the probing loop.
+constexpr int kLaneItems = 4;
+constexpr int kWarpItems = 32 * kLaneItems;
+
+struct BatchUniform {
+  i64 batch, begin, next_begin, seeds_begin, num_seeds, edges_begin;
+  u64* region;
+  i64 size;
+};
+
+__device__ __forceinline__ BatchUniform load_batch(const BatchLayout& L, const i64* __restrict__ off, i64 b) {
+  BatchUniform u;
+  u.batch = b;
+  u.begin = __ldg(off + b);
+  u.next_begin = __ldg(off + b + 1);
+  u.seeds_begin = __ldg(L.seeds_ptr + b);
+  u.num_seeds = __ldg(L.seeds_ptr + b + 1) - u.seeds_begin;
+  u.edges_begin = __ldg(L.indices_ptr + b);
+  const i64 ro = __ldg(L.region_off + b);
+  u.region = L.slots + ro;
+  u.size = __ldg(L.region_off + b + 1) - ro;
+  return u;
 }
 
-__device__ __forceinline__ u64* find_slot(const ItemRef& it) {
-  i64 h = home_slot(it.node, it.size);
-  for (i64 probe = 0; probe < it.size; ++probe) {
-    u64* s = it.region + h;
-    const u64 w = *s;
-    if ((w >> 32) == (u64)it.node) return s;
+__device__ __forceinline__ bool valid_id(i64 node) { return node >= 0 && node < 0xFFFFFFFFll; }
+
+// Insert with the home slot's current word already loaded (`w`): plain loads suffice when the id is
+// present with a smaller position; otherwise CAS / atomicMin, then linear probing.
+__device__ __forceinline__ bool insert_from(u64* region, i64 size, i64 h, u64 w, i64 node, u64 mine) {
+  for (i64 probe = 0; probe < size; ++probe) {
+    u64* s = region + h;
+    if (probe > 0) w = __ldcg(s);
+    if (w == kEmptyWord) {
+      const u64 old = atomicCAS(s, kEmptyWord, mine);
+      if (old == kEmptyWord) return true;
+      w = old;
+    }
+    if ((w >> 32) == (u64)node) {
+      if ((uint32_t)w > (uint32_t)mine) atomicMin(s, mine);
+      return true;
+    }
+    h = (h + 1 == size) ? 0 : h + 1;
+  }
+  return false;
+}
+
+// Lookup with the home slot's word already loaded.  Returns the slot or nullptr; *word receives its value.
+__device__ __forceinline__ u64* find_from(u64* region, i64 size, i64 h, u64 w, i64 node, u64* word) {
+  for (i64 probe = 0; probe < size; ++probe) {
+    u64* s = region + h;
+    if (probe > 0) w = *s;
+    if ((w >> 32) == (u64)node) {
+      *word = w;
+      return s;
+    }
     if (w == kEmptyWord) return nullptr;
-    h = (h + 1 == it.size) ? 0 : h + 1;
+    h = (h + 1 == size) ? 0 : h + 1;
   }
   return nullptr;
+}
+
+template <int ITEMS>
+__global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
+  constexpr int kTileI = 32 * ITEMS;
+  const int lane = threadIdx.x & 31;
+  const i64 n = L.item_off[L.G];
+  const i64 warps = (i64)gridDim.x * (kBThreads / 32);
+  for (i64 tile = (i64)blockIdx.x * (kBThreads / 32) + (threadIdx.x >> 5); tile * kTileI < n; tile += warps) {
+    const i64 base = tile * kTileI;
+    const i64 end = min(n, base + kTileI);
+    const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, base));
+    if (end <= u.next_begin) {
+      i64 node[ITEMS];
+      u64 w[ITEMS];
+#pragma unroll
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        const i64 local = g - u.begin;
+        node[q] = g < end ? (local < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + local)
+                                                 : __ldg(L.indices + u.edges_begin + (local - u.num_seeds)))
+                          : -1;
+      }
+#pragma unroll
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        w[q] = 0;
+        if (g < end && valid_id(node[q])) w[q] = __ldcg(u.region + home_slot(node[q], u.size));
+      }
+#pragma unroll
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        if (g >= end) continue;
+        if (!valid_id(node[q])) {
+          raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+          continue;
+        }
+        const u64 mine = ((u64)node[q] << 32) | (u64)(uint32_t)(g - u.begin);
+        if ((w[q] >> 32) == (u64)node[q] && (uint32_t)w[q] <= (uint32_t)mine) continue;  // already there, earlier
+        if (!insert_from(u.region, u.size, home_slot(node[q], u.size), w[q], node[q], mine))
+          raise_error(counters, GSB_ERR_TABLE_FULL, g);
+      }
+    } else {
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        if (g >= end) continue;
+        const ItemRef it = resolve_item(L, g);
+        if (!valid_id(it.node)) {
+          raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+          continue;
+        }
+        const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.local;
+        const i64 h = home_slot(it.node, it.size);
+        if (!insert_from(it.region, it.size, h, __ldcg(it.region + h), it.node, mine))
+          raise_error(counters, GSB_ERR_TABLE_FULL, g);
+      }
+    }
+  }
 }
 
 struct CompactOut {
@@ -159,78 +239,181 @@ struct CompactOut {
   i64* unique_ptr;  // [G + 1]
 };
 
+// One CTA per tile of kBTile items; each of its 8 warps covers kWarpItems consecutive items.  First-
+// occurrence flags are ranked with ballots, the 8 warp totals are combined through shared memory (one
+// barrier) and warp 0 fetches the tile prefix from the look-back chain.
 __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, CompactOut out, i64* counters,
                                                              TileState ts) {
-  __shared__ i64 s_scan[33];
+  static_assert(kBTile == (kBThreads / 32) * kWarpItems, "tile geometry");
+  __shared__ i64 s_warp_total[kBThreads / 32];
   __shared__ i64 s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const i64 n = L.item_off[L.G];
   const int tile = blockIdx.x;
-  const i64 base = (i64)tile * kBTile;
-  if (base >= n && !(n == 0 && tile == 0)) return;
-  ItemRef it[kBPerThread];
-  u64* slot[kBPerThread];
-  int first[kBPerThread];
-  int mine = 0;
+  const i64 tile_base = (i64)tile * kBTile;
+  if (tile_base >= n && !(n == 0 && tile == 0)) return;
+  const i64 base = tile_base + (i64)warp * kWarpItems;
+  const i64 end = min(n, base + kWarpItems);
+  i64 node[kLaneItems], batch[kLaneItems];
+  uint32_t local[kLaneItems];
+  u64* slot[kLaneItems];
+  u64 w[kLaneItems];
 #pragma unroll
-  for (int q = 0; q < kBPerThread; ++q) {
-    const i64 g = base + (i64)threadIdx.x * kBPerThread + q;
-    first[q] = 0;
+  for (int q = 0; q < kLaneItems; ++q) {
     slot[q] = nullptr;
-    if (g < n) {
-      it[q] = resolve_item(L, g);
-      slot[q] = find_slot(it[q]);
-      first[q] = (slot[q] != nullptr && (uint32_t)(*slot[q]) == (uint32_t)it[q].local) ? 1 : 0;
-      mine += first[q];
+    w[q] = 0;
+    node[q] = -1;
+    batch[q] = 0;
+    local[q] = 0xFFFFFFFFu;
+  }
+  if (base < end) {
+    const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, base));
+    if (end <= u.next_begin) {
+#pragma unroll
+      for (int q = 0; q < kLaneItems; ++q) {
+        const i64 g = base + q * 32 + lane;
+        const i64 lc = g - u.begin;
+        if (g < end) {
+          node[q] = lc < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + lc)
+                                     : __ldg(L.indices + u.edges_begin + (lc - u.num_seeds));
+          local[q] = (uint32_t)lc;
+          batch[q] = u.batch;
+        }
+      }
+      i64 h[kLaneItems];
+#pragma unroll
+      for (int q = 0; q < kLaneItems; ++q) {
+        h[q] = 0;
+        if (valid_id(node[q])) {
+          h[q] = home_slot(node[q], u.size);
+          w[q] = u.region[h[q]];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kLaneItems; ++q)
+        if (valid_id(node[q])) slot[q] = find_from(u.region, u.size, h[q], w[q], node[q], &w[q]);
+    } else {
+      for (int q = 0; q < kLaneItems; ++q) {
+        const i64 g = base + q * 32 + lane;
+        if (g >= end) continue;
+        const ItemRef it = resolve_item(L, g);
+        node[q] = it.node;
+        local[q] = (uint32_t)it.local;
+        batch[q] = it.batch;
+        if (valid_id(it.node)) {
+          const i64 h = home_slot(it.node, it.size);
+          slot[q] = find_from(it.region, it.size, h, it.region[h], it.node, &w[q]);
+        }
+      }
     }
   }
-  i64 total;
-  const i64 excl = block_exclusive_scan<kBThreads>((i64)mine, s_scan, &total);
-  if (threadIdx.x < 32) {
-    const i64 prefix = tile_exclusive_prefix(ts, tile, total);
-    if (threadIdx.x == 0) s_base = prefix;
+  const unsigned lt = (1u << lane) - 1u;
+  unsigned rank[kLaneItems];
+  bool first[kLaneItems];
+  unsigned run = 0;
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    first[q] = slot[q] != nullptr && (uint32_t)w[q] == local[q];
+    const unsigned bal = __ballot_sync(0xffffffffu, first[q]);
+    rank[q] = run + __popc(bal & lt);
+    run += __popc(bal);
+  }
+  if (lane == 0) s_warp_total[warp] = run;
+  __syncthreads();
+  i64 warp_excl = 0, tile_total = 0;
+#pragma unroll
+  for (int x = 0; x < kBThreads / 32; ++x) {
+    const i64 t = s_warp_total[x];
+    if (x < warp) warp_excl += t;
+    tile_total += t;
+  }
+  if (warp == 0) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, tile_total);
+    if (lane == 0) s_base = prefix;
   }
   __syncthreads();
-  i64 pos = s_base + excl;
+  const i64 warp_pos = s_base + warp_excl;
 #pragma unroll
-  for (int q = 0; q < kBPerThread; ++q) {
-    const i64 g = base + (i64)threadIdx.x * kBPerThread + q;
-    if (g < n) {
-      // the first item of a batch is always a first occurrence: its prefix is the batch's frontier offset
-      if (it[q].local == 0) {
-        out.unique_ptr[it[q].batch] = pos;
+  for (int q = 0; q < kLaneItems; ++q) {
+    const i64 g = base + q * 32 + lane;
+    if (g < end) {
+      const i64 pos = warp_pos + rank[q];
+      // the first item of a batch is always a first occurrence: its position is the batch's frontier offset
+      if (local[q] == 0) {
+        out.unique_ptr[batch[q]] = pos;
         // batches without any item in front of this one start (and end) at the same offset
-        for (i64 e = it[q].batch - 1; e >= 0 && __ldg(L.item_off + e) == g; --e) out.unique_ptr[e] = pos;
+        for (i64 e = batch[q] - 1; e >= 0 && __ldg(L.item_off + e) == g; --e) out.unique_ptr[e] = pos;
       }
       if (first[q]) {
-        out.unique[pos] = it[q].node;
+        out.unique[pos] = node[q];
         // final value: compacted position with the top bit set, so that it can never equal the
         // position of a later duplicate that is still being tested in this launch
-        *slot[q] = ((u64)it[q].node << 32) | (u64)(kFinalBit | (uint32_t)pos);
-        ++pos;
+        *slot[q] = ((u64)node[q] << 32) | (u64)(kFinalBit | (uint32_t)pos);
       }
     }
   }
-  if (base + kBTile >= n && threadIdx.x == kBThreads - 1) {
-    out.unique_ptr[L.G] = s_base + total;
-    for (i64 e = L.G - 1; e >= 0 && __ldg(L.item_off + e) == n; --e) out.unique_ptr[e] = s_base + total;
-    counters[CNT_UNIQUE] = s_base + total;
+  if (tile_base + kBTile >= n && threadIdx.x == 0) {
+    const i64 total = s_base + tile_total;
+    out.unique_ptr[L.G] = total;
+    for (i64 e = L.G - 1; e >= 0 && __ldg(L.item_off + e) == n; --e) out.unique_ptr[e] = total;
+    counters[CNT_UNIQUE] = total;
     counters[CNT_NNZ] = L.indices_ptr[L.G];
   }
 }
 
 __global__ void __launch_bounds__(kBThreads) k_batch_relabel(BatchLayout L, const i64* __restrict__ unique_ptr,
                                                              i64* __restrict__ out_relabeled) {
+  const int lane = threadIdx.x & 31;
   const i64 E = L.indices_ptr[L.G];
-  for (i64 p = (i64)blockIdx.x * kBThreads + threadIdx.x; p < E; p += (i64)gridDim.x * kBThreads) {
-    ItemRef it;
-    it.batch = batch_of(L.indices_ptr, L.G, p);
-    it.node = __ldg(L.indices + p);
-    const i64 ro = __ldg(L.region_off + it.batch);
-    it.region = L.slots + ro;
-    it.size = __ldg(L.region_off + it.batch + 1) - ro;
-    it.local = 0;
-    const u64* s = find_slot(it);
-    out_relabeled[p] = s ? (i64)((uint32_t)(*s) & ~kFinalBit) - __ldg(unique_ptr + it.batch) : -1;
+  const i64 warps = (i64)gridDim.x * (kBThreads / 32);
+  for (i64 tile = (i64)blockIdx.x * (kBThreads / 32) + (threadIdx.x >> 5); tile * kWarpItems < E; tile += warps) {
+    const i64 base = tile * kWarpItems;
+    const i64 end = min(E, base + kWarpItems);
+    const BatchUniform u = load_batch(L, L.indices_ptr, batch_of(L.indices_ptr, L.G, base));
+    if (end <= u.next_begin) {
+      const i64 front = __ldg(unique_ptr + u.batch);
+      i64 node[kLaneItems], h[kLaneItems];
+      u64 w[kLaneItems];
+#pragma unroll
+      for (int q = 0; q < kLaneItems; ++q) {
+        const i64 p = base + q * 32 + lane;
+        node[q] = p < end ? __ldg(L.indices + p) : -1;
+      }
+#pragma unroll
+      for (int q = 0; q < kLaneItems; ++q) {
+        h[q] = 0;
+        w[q] = kEmptyWord;
+        if (valid_id(node[q])) {
+          h[q] = home_slot(node[q], u.size);
+          w[q] = u.region[h[q]];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kLaneItems; ++q) {
+        const i64 p = base + q * 32 + lane;
+        if (p < end) {
+          const u64* s = valid_id(node[q]) ? find_from(u.region, u.size, h[q], w[q], node[q], &w[q]) : nullptr;
+          out_relabeled[p] = s ? (i64)((uint32_t)w[q] & ~kFinalBit) - front : -1;
+        }
+      }
+    } else {
+      for (int q = 0; q < kLaneItems; ++q) {
+        const i64 p = base + q * 32 + lane;
+        if (p >= end) continue;
+        const i64 b = batch_of(L.indices_ptr, L.G, p);
+        const i64 node = __ldg(L.indices + p);
+        const i64 ro = __ldg(L.region_off + b);
+        u64* region = L.slots + ro;
+        const i64 size = __ldg(L.region_off + b + 1) - ro;
+        u64 word = 0;
+        const u64* s = nullptr;
+        if (valid_id(node)) {
+          const i64 h = home_slot(node, size);
+          s = find_from(region, size, h, region[h], node, &word);
+        }
+        out_relabeled[p] = s ? (i64)((uint32_t)word & ~kFinalBit) - __ldg(unique_ptr + b) : -1;
+      }
+    }
   }
 }
 
@@ -296,7 +479,9 @@ int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, 
   const int wide = kNumSMs * 8;
   {
     ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
-    k_batch_insert<<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
+    // one item per lane measured fastest for the insert (more items in flight per lane only add contention
+    // on the slots of frequent ids)
+    k_batch_insert<1><<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
   }
   GSB_LAUNCH_OK();
   const int tiles = grid_for(n_cap, kBTile);
@@ -311,7 +496,7 @@ int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, 
   GSB_LAUNCH_OK();
   if (indices_capacity > 0 && out_relabeled) {
     ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
-    k_batch_relabel<<<max(1, min(grid_for(indices_capacity, kBThreads), wide)), kBThreads, 0, stream>>>(
+    k_batch_relabel<<<max(1, min(grid_for(indices_capacity, kBTile), wide)), kBThreads, 0, stream>>>(
         L, out_unique_ptr, out_relabeled);
   }
   GSB_LAUNCH_OK();
