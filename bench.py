@@ -46,6 +46,12 @@ def parse():
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="sage", choices=["sage", "walk"],
+                    help="sage = the headline (BASELINE config 2); walk = uniform random walk (BASELINE config 4 shape)")
+    ap.add_argument("--walkers", type=int, default=10_000_000)
+    ap.add_argument("--walk-length", type=int, default=80)
+    ap.add_argument("--walk-nodes", type=int, default=111_000_000)
+    ap.add_argument("--walk-edges", type=int, default=1_600_000_000)
     ap.add_argument("--group", type=int, default=256,
                     help="minibatches handed to one call of the batched sampler (1 = per-batch Graph API)")
     return ap.parse_args()
@@ -317,16 +323,19 @@ def run_ours(args):
     # Algorithmic bytes per launch of each hot kernel, from the shapes of the timed calls: (S, E, U) per hop.
     # sample: 32 B per seed column (seed id, indptr pair, output offset) + 24 B per sampled edge (8 read, 16 written);
     # unique + relabel is three passes over N = S + E items: insert reads 8 N; first-occurrence compaction reads 8 N
-    # and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead, not counted).
+    # and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead, not counted).  The sampler that
+    # also records the ids in the tables is charged the sampling bytes only.
     hop_shapes = [h for call in shapes for h in call]
     n_launch = max(1, len(hop_shapes))
     alg = {
         "sample_uniform": sum(32 * s_ + 8 + 24 * e_ for s_, e_, _ in hop_shapes) / n_launch,
+        "sage_sample_insert": sum(32 * s_ + 8 + 24 * e_ for s_, e_, _ in hop_shapes) / n_launch,
         "table_insert": sum(8 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
         "first_compact": sum(8 * (s_ + e_) + 8 * u_ for s_, e_, u_ in hop_shapes) / n_launch,
         "relabel": sum(16 * e_ for s_, e_, _ in hop_shapes) / n_launch,
     }
     kernel_names = {"sample_uniform": "k_sample_uniform_tpc (fused count + scan + uniform sample)",
+                    "sage_sample_insert": "k_sample_uniform_tpc<K, fused> (count + scan + uniform sample + table insert)",
                     "table_insert": "k_batch_insert / k_insert (position-min hash insert)",
                     "first_compact": "k_batch_compact / k_first_compact (first-occurrence scan + compaction)",
                     "relabel": "k_batch_relabel / k_relabel (lookup)"}
@@ -363,8 +372,8 @@ def run_ours(args):
                    "graph": info, "batch": BATCH, "fanouts": FANOUTS, "parallelism": f"replicated graph, dp{world}",
                    "l2": "inputs larger than L2: 1 GB of indices gathered at random, no flush",
                    "group": group,
-                   "path": ("batched sampler: %d minibatches per call, per hop one fused slice+sample launch and one "
-                            "batched unique+relabel" % group) if group > 1 else
+                   "path": ("batched sampler (gsb_sage_hop): %d minibatches per call; per hop one fused slice+sample launch "
+                            "and a batched unique+relabel (insert, compaction, lookup)" % group) if group > 1 else
                            "Graph API per batch and hop (fused slice+sample, relabel)"},
         "edges_per_step": edges_all / args.steps / world,
         "e2e": {"value": e2e_edges_all / e2e_seconds_all, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
@@ -426,9 +435,80 @@ def run_reference(args):
     print(json.dumps(base))
 
 
+def run_walk(args):
+    """Uniform random walk (BASELINE config 4 shape): one walker per distinct start node, walkers split into
+    contiguous ranges over the ranks, int64 trace [walkers, length + 1].  A step here is one full pass over
+    this rank's walkers.  Secondary workload: prints its own JSON line (metric walker_steps_per_second)."""
+    import torch
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    from graph_sampling_b200.synthetic import rmat_csc, distinct_starts
+    from graph_sampling_b200.sharding import shard_walkers, reduce_run_stats
+    t0 = time.time()
+    indptr, indices = rmat_csc(args.walk_nodes, args.walk_edges, seed=GRAPH_SEED + 4, device=device, permute=True)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    info = {"nodes": args.walk_nodes, "edges": int(indices.numel()), "gen_seconds": round(time.time() - t0, 1)}
+    starts = distinct_starts(args.walk_nodes, args.walkers, seed=7, device=device)
+    off, cnt = shard_walkers(args.walkers, rank, world)
+    mine = starts[off:off + cnt].contiguous()
+    L = args.walk_length
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    if args.impl == "reference":
+        torch.classes.load_library(os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so"))
+        G = torch.classes.gs_classes.Graph(False)
+        G._CAPI_LoadCSC(indptr, indices)
+        fn = lambda: G._CAPI_RandomWalk(mine, L)
+        layout = "step-major memory (the reference's own)"
+    else:
+        from graph_sampling_b200 import ops
+        ctx = ops.default_context(device)
+        layout_id = 1
+        fn = lambda: ops.fused_random_walk(mine, L, indices, indptr, layout=layout_id, walker_offset=off)
+        layout = "walker-major [walkers, length+1]"
+    for _ in range(warmup):
+        out = fn()
+    torch.cuda.synchronize()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        out = fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    seconds = ev0.elapsed_time(ev1) / 1e3
+    units = cnt * L * steps
+    seconds_all, units_all = reduce_run_stats(seconds, units, device=device)
+    alive = float((out >= 0).float().mean().item()) if out.numel() < (1 << 31) else None
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+        alg = (16 * cnt + 32 * cnt * L)  # per pass on this rank
+        ach = alg * steps / seconds / 1e9
+        print(json.dumps({"metric": "walker_steps_per_second", "value": units_all / seconds_all, "unit": "steps/s",
+                          "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": seconds_all / steps * 1e3,
+                          "higher_is_better": True, "scaling": "strong", "dtype": "int64", "data": "synthetic",
+                          "impl": args.impl,
+                          "config": {"workload": "uniform random walk (BASELINE config 4 shape)", "graph": info,
+                                     "walkers": args.walkers, "length": L, "layout": layout,
+                                     "fraction_of_trace_alive": alive},
+                          "roofline": {"bound": "hbm", "kernel": "k_random_walk", "achieved": round(ach, 2), "peak": peak,
+                                       "unit": "GB/s", "frac": round(ach / peak, 5), "traffic": None}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     a = parse()
-    if a.impl == "reference":
+    if a.workload == "walk":
+        run_walk(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

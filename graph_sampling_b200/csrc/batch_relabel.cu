@@ -17,6 +17,7 @@
 //
 // Replaces gs::impl::BatchCSRRelabelCUDA (src/cuda/batch_relabel.cu:90-320), which keeps two int64
 // arrays per table, three passes with separate prefix-sum calls and a host round trip per pass.
+#include "batch_table.cuh"
 #include "common.cuh"
 #include "scan.cuh"
 
@@ -25,8 +26,6 @@ namespace gsb {
 constexpr int kBThreads = 256;
 constexpr int kBPerThread = 4;
 constexpr int kBTile = kBThreads * kBPerThread;
-constexpr u64 kEmptyWord = 0xFFFFFFFFFFFFFFFFull;
-constexpr uint32_t kFinalBit = 0x80000000u;
 
 struct BatchLayout {
   const i64* seeds;
@@ -40,10 +39,12 @@ struct BatchLayout {
   i64 slot_capacity;
 };
 
-__device__ __forceinline__ i64 region_size_for(i64 items) { return items + (items >> 2) + 32; }
 
-// One CTA: per-batch item offsets and table regions (exclusive scan over the G region sizes).
-__global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters) {
+// One CTA: per-batch item offsets and / or table regions (exclusive scan over the G region sizes).
+// bound_k < 0: regions sized from the batches' actual item counts (needs indices_ptr); bound_k >= 0:
+// regions sized from the upper bound seeds * (1 + bound_k), which is known before sampling.
+// what & 1: write region_off; what & 2: write item_off.
+__global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters, i64 bound_k, int what) {
   __shared__ i64 s_scan[33];
   __shared__ i64 s_carry;
   if (threadIdx.x == 0) s_carry = 0;
@@ -52,39 +53,31 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
     const i64 b = b0 + threadIdx.x;
     i64 size = 0;
     if (b < L.G) {
-      const i64 io = L.seeds_ptr[b] + L.indices_ptr[b];
-      L.item_off[b] = io;
-      size = region_size_for(L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - io);
+      if (what & 2) L.item_off[b] = L.seeds_ptr[b] + L.indices_ptr[b];
+      if (bound_k >= 0) size = region_size_for((L.seeds_ptr[b + 1] - L.seeds_ptr[b]) * (1 + bound_k));
+      else size = region_size_for(L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - L.seeds_ptr[b] - L.indices_ptr[b]);
     }
     i64 total;
     const i64 excl = block_exclusive_scan<kBThreads>(size, s_scan, &total);
     const i64 carry = s_carry;
-    if (b < L.G) L.region_off[b] = carry + excl;
+    if (b < L.G && (what & 1)) L.region_off[b] = carry + excl;
     __syncthreads();
     if (threadIdx.x == 0) s_carry = carry + total;
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    L.item_off[L.G] = L.seeds_ptr[L.G] + L.indices_ptr[L.G];
-    L.region_off[L.G] = s_carry;
-    if (s_carry > L.slot_capacity) raise_error(counters, GSB_ERR_CAPACITY, s_carry);
+    if (what & 2) L.item_off[L.G] = L.seeds_ptr[L.G] + L.indices_ptr[L.G];
+    if (what & 1) {
+      L.region_off[L.G] = s_carry;
+      if (s_carry > L.slot_capacity) raise_error(counters, GSB_ERR_CAPACITY, s_carry);
+    }
   }
-}
-
-// Largest b with off[b] <= g  (off has G + 1 non-decreasing entries, off[0] = 0 <= g < off[G]).
-__device__ __forceinline__ i64 batch_of(const i64* __restrict__ off, i64 G, i64 g) {
-  i64 lo = 0, hi = G;
-  while (hi - lo > 1) {
-    const i64 mid = (lo + hi) >> 1;
-    if (__ldg(off + mid) <= g) lo = mid;
-    else hi = mid;
-  }
-  return lo;
 }
 
 struct ItemRef {
   i64 batch;
   i64 local;   // position among the batch's items (seeds first)
+  i64 key;     // position key stored in the table: local for a seed, edges_begin + local for a neighbour
   i64 node;
   u64* region;
   i64 size;
@@ -96,17 +89,13 @@ __device__ __forceinline__ ItemRef resolve_item(const BatchLayout& L, i64 g) {
   const i64 s0 = __ldg(L.seeds_ptr + r.batch), s1 = __ldg(L.seeds_ptr + r.batch + 1);
   r.local = g - __ldg(L.item_off + r.batch);
   const i64 ns = s1 - s0;
-  r.node = r.local < ns ? __ldg(L.seeds + s0 + r.local)
-                        : __ldg(L.indices + __ldg(L.indices_ptr + r.batch) + (r.local - ns));
+  const i64 eb = __ldg(L.indices_ptr + r.batch);
+  r.node = r.local < ns ? __ldg(L.seeds + s0 + r.local) : __ldg(L.indices + eb + (r.local - ns));
+  r.key = r.local < ns ? r.local : eb + r.local;
   const i64 ro = __ldg(L.region_off + r.batch);
   r.region = L.slots + ro;
   r.size = __ldg(L.region_off + r.batch + 1) - ro;
   return r;
-}
-
-__device__ __forceinline__ i64 home_slot(i64 node, i64 size) {
-  const uint32_t h = (uint32_t)(((u64)node * 0x9E3779B97F4A7C15ull) >> 32);
-  return (i64)(((u64)h * (u64)size) >> 32);
 }
 
 // ---- traversal by warp tiles ------------------------------------------------------------------------
@@ -137,43 +126,6 @@ __device__ __forceinline__ BatchUniform load_batch(const BatchLayout& L, const i
   u.region = L.slots + ro;
   u.size = __ldg(L.region_off + b + 1) - ro;
   return u;
-}
-
-__device__ __forceinline__ bool valid_id(i64 node) { return node >= 0 && node < 0xFFFFFFFFll; }
-
-// Insert with the home slot's current word already loaded (`w`): plain loads suffice when the id is
-// present with a smaller position; otherwise CAS / atomicMin, then linear probing.
-__device__ __forceinline__ bool insert_from(u64* region, i64 size, i64 h, u64 w, i64 node, u64 mine) {
-  for (i64 probe = 0; probe < size; ++probe) {
-    u64* s = region + h;
-    if (probe > 0) w = __ldcg(s);
-    if (w == kEmptyWord) {
-      const u64 old = atomicCAS(s, kEmptyWord, mine);
-      if (old == kEmptyWord) return true;
-      w = old;
-    }
-    if ((w >> 32) == (u64)node) {
-      if ((uint32_t)w > (uint32_t)mine) atomicMin(s, mine);
-      return true;
-    }
-    h = (h + 1 == size) ? 0 : h + 1;
-  }
-  return false;
-}
-
-// Lookup with the home slot's word already loaded.  Returns the slot or nullptr; *word receives its value.
-__device__ __forceinline__ u64* find_from(u64* region, i64 size, i64 h, u64 w, i64 node, u64* word) {
-  for (i64 probe = 0; probe < size; ++probe) {
-    u64* s = region + h;
-    if (probe > 0) w = *s;
-    if ((w >> 32) == (u64)node) {
-      *word = w;
-      return s;
-    }
-    if (w == kEmptyWord) return nullptr;
-    h = (h + 1 == size) ? 0 : h + 1;
-  }
-  return nullptr;
 }
 
 template <int ITEMS>
@@ -211,7 +163,8 @@ __global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* 
           raise_error(counters, GSB_ERR_INDEX_RANGE, g);
           continue;
         }
-        const u64 mine = ((u64)node[q] << 32) | (u64)(uint32_t)(g - u.begin);
+        const i64 lc = g - u.begin;
+        const u64 mine = ((u64)node[q] << 32) | (u64)(uint32_t)(lc < u.num_seeds ? lc : u.edges_begin + lc);
         if ((w[q] >> 32) == (u64)node[q] && (uint32_t)w[q] <= (uint32_t)mine) continue;  // already there, earlier
         if (!insert_from(u.region, u.size, home_slot(node[q], u.size), w[q], node[q], mine))
           raise_error(counters, GSB_ERR_TABLE_FULL, g);
@@ -225,7 +178,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* 
           raise_error(counters, GSB_ERR_INDEX_RANGE, g);
           continue;
         }
-        const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.local;
+        const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.key;
         const i64 h = home_slot(it.node, it.size);
         if (!insert_from(it.region, it.size, h, __ldcg(it.region + h), it.node, mine))
           raise_error(counters, GSB_ERR_TABLE_FULL, g);
@@ -255,7 +208,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
   const i64 base = tile_base + (i64)warp * kWarpItems;
   const i64 end = min(n, base + kWarpItems);
   i64 node[kLaneItems], batch[kLaneItems];
-  uint32_t local[kLaneItems];
+  uint32_t local[kLaneItems], key[kLaneItems];
   u64* slot[kLaneItems];
   u64 w[kLaneItems];
 #pragma unroll
@@ -265,6 +218,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
     node[q] = -1;
     batch[q] = 0;
     local[q] = 0xFFFFFFFFu;
+    key[q] = 0xFFFFFFFFu;
   }
   if (base < end) {
     const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, base));
@@ -277,6 +231,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
           node[q] = lc < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + lc)
                                      : __ldg(L.indices + u.edges_begin + (lc - u.num_seeds));
           local[q] = (uint32_t)lc;
+          key[q] = (uint32_t)(lc < u.num_seeds ? lc : u.edges_begin + lc);
           batch[q] = u.batch;
         }
       }
@@ -299,6 +254,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
         const ItemRef it = resolve_item(L, g);
         node[q] = it.node;
         local[q] = (uint32_t)it.local;
+        key[q] = (uint32_t)it.key;
         batch[q] = it.batch;
         if (valid_id(it.node)) {
           const i64 h = home_slot(it.node, it.size);
@@ -313,7 +269,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
   unsigned run = 0;
 #pragma unroll
   for (int q = 0; q < kLaneItems; ++q) {
-    first[q] = slot[q] != nullptr && (uint32_t)w[q] == local[q];
+    first[q] = slot[q] != nullptr && (uint32_t)w[q] == key[q];
     const unsigned bal = __ballot_sync(0xffffffffu, first[q]);
     rank[q] = run + __popc(bal & lt);
     run += __popc(bal);
@@ -473,7 +429,7 @@ int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, 
   }
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
   }
   GSB_LAUNCH_OK();
   const int wide = kNumSMs * 8;
@@ -498,6 +454,86 @@ int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, 
     ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
     k_batch_relabel<<<max(1, min(grid_for(indices_capacity, kBTile), wide)), kBThreads, 0, stream>>>(
         L, out_unique_ptr, out_relabeled);
+  }
+  GSB_LAUNCH_OK();
+  if (unique_total_host || edges_total_host) {
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
+    if (st != GSB_OK) return st;
+    if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
+    if (edges_total_host) *edges_total_host = c[CNT_NNZ];
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  }
+  return GSB_OK;
+}
+
+int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, const int64_t* seeds,
+                 const int64_t* seeds_ptr, int64_t G, int64_t S, int64_t k, int replace, uint64_t seed,
+                 int64_t* out_indptr, int64_t* out_indices, int64_t* out_select, int64_t* out_indices_ptr,
+                 int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_relabeled, int64_t* unique_total_host,
+                 int64_t* edges_total_host) {
+  GSB_REQUIRE(ctx && indptr && seeds_ptr && out_indptr && out_indices_ptr && out_unique_ptr && G >= 1 && S >= 0 &&
+                  k >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  const i64 cap = S * k;
+  const i64 n_cap = S + cap;
+  GSB_REQUIRE(n_cap < (1ll << 30), GSB_ERR_UNSUPPORTED);
+  GSB_REQUIRE(n_cap == 0 || (seeds && out_unique), GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(cap == 0 || (indices && out_indices && out_select && out_relabeled), GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 * G + 64;
+  const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
+  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, slots_bytes + 2 * off_bytes, &ws);
+  if (st != GSB_OK) return st;
+  BatchLayout L;
+  L.seeds = seeds;
+  L.seeds_ptr = seeds_ptr;
+  L.indices = out_indices;
+  L.indices_ptr = out_indices_ptr;
+  L.G = G;
+  L.slots = (u64*)ws;
+  L.item_off = (i64*)((char*)ws + slots_bytes);
+  L.region_off = (i64*)((char*)ws + slots_bytes + off_bytes);
+  L.slot_capacity = slot_cap;
+  i64* counters = ctx_counters(ctx);
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
+    GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
+  }
+  st = sample_uniform_launch(ctx, stream, indptr, indices, seeds, S, k, replace, (u64)seed, out_indptr, out_indices,
+                             out_select, nullptr, nullptr, nullptr, nullptr, cap);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(out_indptr, seeds_ptr, G, out_indices_ptr);
+  }
+  GSB_LAUNCH_OK();
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
+  }
+  GSB_LAUNCH_OK();
+  const int wide = kNumSMs * 8;
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
+    k_batch_insert<1><<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
+  }
+  GSB_LAUNCH_OK();
+  const int tiles = grid_for(n_cap, kBTile);
+  TileState ts;
+  st = ctx_tile_state(ctx, tiles, stream, &ts);
+  if (st != GSB_OK) return st;
+  CompactOut out{out_unique, out_unique_ptr};
+  {
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_batch_compact<<<tiles, kBThreads, 0, stream>>>(L, out, counters, ts);
+  }
+  GSB_LAUNCH_OK();
+  if (cap > 0) {
+    ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
+    k_batch_relabel<<<max(1, min(grid_for(cap, kBTile), wide)), kBThreads, 0, stream>>>(L, out_unique_ptr, out_relabeled);
   }
   GSB_LAUNCH_OK();
   if (unique_total_host || edges_total_host) {

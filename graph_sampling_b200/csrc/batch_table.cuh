@@ -1,0 +1,71 @@
+// Per-minibatch hash-table regions of the batched unique + relabel: one 64-bit word per slot
+// (id << 32 | position), empty = all ones, multiplicative hashing, linear probing inside the region.
+#pragma once
+#include "common.cuh"
+
+namespace gsb {
+
+constexpr u64 kEmptyWord = 0xFFFFFFFFFFFFFFFFull;
+constexpr uint32_t kFinalBit = 0x80000000u;
+
+__host__ __device__ __forceinline__ i64 region_size_for(i64 items) { return items + (items >> 2) + 32; }
+
+__device__ __forceinline__ i64 home_slot(i64 node, i64 size) {
+  const uint32_t h = (uint32_t)(((u64)node * 0x9E3779B97F4A7C15ull) >> 32);
+  return (i64)(((u64)h * (u64)size) >> 32);
+}
+
+__device__ __forceinline__ bool valid_id(i64 node) { return node >= 0 && node < 0xFFFFFFFFll; }
+
+// Insert with the home slot's current word already loaded (`w`): plain loads suffice when the id is
+// present with a smaller position; otherwise CAS / atomicMin, then linear probing.
+__device__ __forceinline__ bool insert_from(u64* region, i64 size, i64 h, u64 w, i64 node, u64 mine) {
+  for (i64 probe = 0; probe < size; ++probe) {
+    u64* s = region + h;
+    if (probe > 0) w = __ldcg(s);
+    if (w == kEmptyWord) {
+      const u64 old = atomicCAS(s, kEmptyWord, mine);
+      if (old == kEmptyWord) return true;
+      w = old;
+    }
+    if ((w >> 32) == (u64)node) {
+      if ((uint32_t)w > (uint32_t)mine) atomicMin(s, mine);
+      return true;
+    }
+    h = (h + 1 == size) ? 0 : h + 1;
+  }
+  return false;
+}
+
+// Lookup with the home slot's word already loaded.  Returns the slot or nullptr; *word receives its value.
+__device__ __forceinline__ u64* find_from(u64* region, i64 size, i64 h, u64 w, i64 node, u64* word) {
+  for (i64 probe = 0; probe < size; ++probe) {
+    u64* s = region + h;
+    if (probe > 0) w = *s;
+    if ((w >> 32) == (u64)node) {
+      *word = w;
+      return s;
+    }
+    if (w == kEmptyWord) return nullptr;
+    h = (h + 1 == size) ? 0 : h + 1;
+  }
+  return nullptr;
+}
+
+// Largest b with off[b] <= g  (off has G + 1 non-decreasing entries, off[0] <= g < off[G]).
+__device__ __forceinline__ i64 batch_of(const i64* __restrict__ off, i64 G, i64 g) {
+  i64 lo = 0, hi = G;
+  while (hi - lo > 1) {
+    const i64 mid = (lo + hi) >> 1;
+    if (__ldg(off + mid) <= g) lo = mid;
+    else hi = mid;
+  }
+  return lo;
+}
+
+// Uniform sampler shared by gsb_sample_uniform and the batched hop (defined in slice_sample.cu).
+int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
+                          i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,
+                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity);
+
+}  // namespace gsb

@@ -10,6 +10,7 @@
 // group of G lanes, G = smallest power of two >= fanout, and needs O(fanout) draws per column
 // whatever its degree (Floyd's k-subset), instead of the reference's O(degree) reservoir pass
 // (src/cuda/fusion/slice_sampling.cu:62-75).
+#include "batch_table.cuh"
 #include "common.cuh"
 #include "philox.cuh"
 #include "scan.cuh"
@@ -239,9 +240,9 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
   const i64 i = tile * 32 + lane;
   const bool valid = i < S;
   const int k = (int)p.k;
-  i64 b = 0, d = 0, f = 0;
+  i64 b = 0, d = 0, f = 0, col = 0;
   if (valid) {
-    const i64 col = p.seeds ? __ldg(p.seeds + i) : i;
+    col = p.seeds ? __ldg(p.seeds + i) : i;
     b = __ldg(p.indptr + col);
     d = __ldg(p.indptr + col + 1) - b;
     f = column_count(d, k, p.replace ? COUNT_WR : COUNT_WOR);
@@ -269,36 +270,38 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
     if (lane == 0) raise_error(p.counters, GSB_ERR_CAPACITY, prefix + total);
     return;
   }
-  if (!valid || f == 0) return;
-  if (d > 0xFFFFFFFFll) {
+  if (valid && d > 0xFFFFFFFFll) {
     raise_error(p.counters, GSB_ERR_UNSUPPORTED, i);
     return;
   }
+  const int n = valid ? (int)f : 0;
   uint32_t pick[KMAX];
-  const int n = (int)f;
-  if (p.replace || d > k) {
-    U32x4 blk;
+  if (n > 0) {
+    if (p.replace || d > k) {
+      U32x4 blk;
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) {
-      if (j < k) {
-        if ((j & 3) == 0) blk = rand_block(p.seed, (u64)i, (u64)(j >> 2), STREAM_UNIFORM);
-        const uint32_t word = (j & 3) == 0 ? blk.v[0] : (j & 3) == 1 ? blk.v[1] : (j & 3) == 2 ? blk.v[2] : blk.v[3];
-        if (p.replace) {
-          pick[j] = (uint32_t)bounded_from_word(word, (u64)d);
-        } else {
-          const uint32_t m = (uint32_t)(d - k + j);
-          const uint32_t t = (uint32_t)bounded_from_word(word, (u64)m + 1);
-          bool dup = false;
+      for (int j = 0; j < KMAX; ++j) {
+        if (j < k) {
+          if ((j & 3) == 0) blk = rand_block(p.seed, (u64)i, (u64)(j >> 2), STREAM_UNIFORM);
+          const uint32_t word =
+              (j & 3) == 0 ? blk.v[0] : (j & 3) == 1 ? blk.v[1] : (j & 3) == 2 ? blk.v[2] : blk.v[3];
+          if (p.replace) {
+            pick[j] = (uint32_t)bounded_from_word(word, (u64)d);
+          } else {
+            const uint32_t m = (uint32_t)(d - k + j);
+            const uint32_t t = (uint32_t)bounded_from_word(word, (u64)m + 1);
+            bool dup = false;
 #pragma unroll
-          for (int q = 0; q < KMAX; ++q)
-            if (q < j) dup |= (pick[q] == t);
-          pick[j] = dup ? m : t;
+            for (int q = 0; q < KMAX; ++q)
+              if (q < j) dup |= (pick[q] == t);
+            pick[j] = dup ? m : t;
+          }
         }
       }
-    }
-  } else {
+    } else {
 #pragma unroll
-    for (int j = 0; j < KMAX; ++j) pick[j] = (uint32_t)j;
+      for (int j = 0; j < KMAX; ++j) pick[j] = (uint32_t)j;
+    }
   }
   i64 val[KMAX];
 #pragma unroll
@@ -342,6 +345,28 @@ __global__ void __launch_bounds__(kThreads) k_sample_one_keepdim(const i64* __re
 template <int G>
 static void launch_sample(const SampleParams& p, int grid, cudaStream_t stream) {
   k_sample_uniform<G><<<grid, kThreads, 0, stream>>>(p);
+}
+
+
+int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
+                          i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,
+                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity) {
+  const bool per_thread = k <= 16;  // small fanouts: one lane per column, one warp per tile of 32 columns
+  const int grid = per_thread ? grid_for(S, kTpcThreads) : grid_for(S, kTileCols);
+  TileState ts;
+  int st = ctx_tile_state(ctx, per_thread ? (S + 31) / 32 + 1 : grid, stream, &ts);
+  if (st != GSB_OK) return st;
+  SampleParams p{indptr, indices, seeds,  S,        k,        replace,         seed, out_indptr, out_indices,
+                 out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts};
+  {
+    ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
+    if (k <= 4) k_sample_uniform_tpc<4><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 8) k_sample_uniform_tpc<8><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 16) k_sample_uniform_tpc<16><<<grid, kTpcThreads, 0, stream>>>(p);
+    else launch_sample<32>(p, grid, stream);
+  }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
 }
 
 }  // namespace gsb
@@ -395,21 +420,9 @@ int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
   GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const bool per_thread = k <= 16;  // small fanouts: one lane per column, one warp per tile of 32 columns
-  const int grid = per_thread ? grid_for(S, kTpcThreads) : grid_for(S, kTileCols);
-  TileState ts;
-  int st = ctx_tile_state(ctx, per_thread ? (S + 31) / 32 + 1 : grid, stream, &ts);
+  int st = sample_uniform_launch(ctx, stream, indptr, indices, seeds, S, k, replace, (u64)seed, out_indptr,
+                                 out_indices, out_select, out_coo_col, data, e_ids, out_data, capacity);
   if (st != GSB_OK) return st;
-  SampleParams p{indptr, indices, seeds,  S,        k,        replace,         (u64)seed, out_indptr, out_indices,
-                 out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts};
-  {
-    ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
-    if (k <= 4) k_sample_uniform_tpc<4><<<grid, kTpcThreads, 0, stream>>>(p);
-    else if (k <= 8) k_sample_uniform_tpc<8><<<grid, kTpcThreads, 0, stream>>>(p);
-    else if (k <= 16) k_sample_uniform_tpc<16><<<grid, kTpcThreads, 0, stream>>>(p);
-    else launch_sample<32>(p, grid, stream);
-  }
-  GSB_LAUNCH_OK();
   if (nnz_host) {
     const i64* c;
     st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);

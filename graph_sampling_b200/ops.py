@@ -518,23 +518,18 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
     base_seed = next_seed(seed)
     for hop, k in enumerate(fanouts):
         S = seeds.numel()
+        G = seeds_ptr.numel() - 1
         cap = S * int(k)
         sub_indptr = _empty(S + 1, indptr)
-        sub_indices, select = _empty(cap, indptr), _empty(cap, indptr)
-        ctx.check(ctx.lib.gsb_sample_uniform(ctx.handle, _stream(), _p(indptr), _p(indices), _p(seeds), c_i64(S),
-                                             c_i64(int(k)), c_int(int(bool(replace))), c_u64((base_seed + hop) & (2**64 - 1)),
-                                             _p(sub_indptr), _p(sub_indices), _p(select), _p(None), _p(None), _p(None),
-                                             _p(None), c_i64(cap), None), "gsb_sample_uniform")
-        indices_ptr = batch_edge_offsets(sub_indptr, seeds_ptr, ctx)
-        G = seeds_ptr.numel() - 1
+        sub_indices, select, rel = _empty(cap, indptr), _empty(cap, indptr), _empty(cap, indptr)
+        indices_ptr, uniq_ptr = _empty(G + 1, indptr), _empty(G + 1, indptr)
         uniq = _empty(S + cap, indptr)
-        uniq_ptr = _empty(G + 1, indptr)
-        rel = _empty(cap, indptr)
         nu, ne = c_i64(0), c_i64(0)
-        ctx.check(ctx.lib.gsb_batch_unique_relabel(ctx.handle, _stream(), _p(seeds), _p(seeds_ptr), c_i64(S),
-                                                   _p(sub_indices), _p(indices_ptr), c_i64(cap), c_i64(G), _p(uniq),
-                                                   _p(uniq_ptr), _p(rel), ctypes.byref(nu), ctypes.byref(ne)),
-                  "gsb_batch_unique_relabel")
+        ctx.check(ctx.lib.gsb_sage_hop(ctx.handle, _stream(), _p(indptr), _p(indices), _p(seeds), _p(seeds_ptr),
+                                       c_i64(G), c_i64(S), c_i64(int(k)), c_int(int(bool(replace))),
+                                       c_u64((base_seed + hop) & (2**64 - 1)), _p(sub_indptr), _p(sub_indices),
+                                       _p(select), _p(indices_ptr), _p(uniq), _p(uniq_ptr), _p(rel),
+                                       ctypes.byref(nu), ctypes.byref(ne)), "gsb_sage_hop")
         E, U = ne.value, nu.value
         out.append(dict(seeds=seeds, seeds_ptr=seeds_ptr, sub_indptr=sub_indptr, indices=sub_indices[:E],
                         relabeled=rel[:E], select_index=select[:E], indices_ptr=indices_ptr, frontier=uniq[:U],

@@ -265,6 +265,25 @@ GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* 
                                      int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
                                      int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
 
+/* ---- one hop of multi-batch GraphSAGE sampling ------------------------------------------------------------
+ * The per-hop body of the reference's super-batch loop (examples/graphsage/batching.py:56-90:
+ * _CAPI_fused_columnwise_slicing_sampling over the seeds of all batches, GetBatchCSC,
+ * gs_ops.BatchCSRRelabel) as ONE call: fused slice + uniform sample over the S seed columns of G
+ * minibatches (seeds_ptr: DEVICE, G + 1 offsets), then per batch unique(cat(seeds_b, sampled_b)) in
+ * first-occurrence order and batch-local relabelling.  (Recording the ids in the tables from inside the
+ * sampling kernel was measured slower than a separate insert pass and is not done.)
+ * Outputs: out_indptr[S + 1] (offsets over all columns), out_indices / out_select / out_relabeled
+ * (S * k entries each; global ids, positions in `indices`, batch-local ids), out_indices_ptr[G + 1]
+ * (per-batch edge offsets), out_unique (S + S * k entries; all frontiers back to back) and
+ * out_unique_ptr[G + 1].  The frontier of a batch becomes its seed list for the next hop.
+ * Ids below 2^32 - 1; S * (1 + k) below 2^30.  Waits for the stream only if a *_host pointer is given.
+ */
+GSB_API int gsb_sage_hop(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                         const int64_t* seeds, const int64_t* seeds_ptr, int64_t G, int64_t S, int64_t k, int replace,
+                         uint64_t seed, int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
+                         int64_t* out_indices_ptr, int64_t* out_unique, int64_t* out_unique_ptr,
+                         int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
+
 /* ---- unique + relabel without any allocation ----------------------------------------------------------
  * No counterpart in the reference.  For callers that must not allocate device memory while they
  * run (a host process whose memory budget is fixed up front, a plug-in running under a lock that

@@ -58,18 +58,19 @@ def test_batch_with_empty_batches(ops, oracle):
     assert host(rel).tolist() == [1, 3, 3, 0, 2, 0]
 
 
-def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph):
+@pytest.mark.parametrize("fanouts", [[10, 5], [20, 3], [1, 16, 2]])
+def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, fanouts):
     """BASELINE config 1 shape, 16 batches of 1,024 seeds at once: sampling equals the oracle's fused
     sampler over the concatenated seeds (same Philox stream), relabel equals the per-batch oracle."""
     indptr, indices = cfg1_graph
     n = len(indptr) - 1
-    G, S0 = 16, 1024
+    G, S0 = (16, 1024) if fanouts[0] != 20 else (5, 300)
     rng = np.random.default_rng(0)
     seeds0 = np.concatenate([rng.choice(n, S0, replace=False) for _ in range(G)]).astype(np.int64)
     ptr0 = (np.arange(G + 1) * S0).astype(np.int64)
-    hops = ops.sage_sample_batches(dev(indptr), dev(indices), dev(seeds0), dev(ptr0), [10, 5], seed=77)
+    hops = ops.sage_sample_batches(dev(indptr), dev(indices), dev(seeds0), dev(ptr0), fanouts, seed=77)
     cur, cur_ptr = seeds0, ptr0
-    for hop, (k, h) in enumerate(zip([10, 5], hops)):
+    for hop, (k, h) in enumerate(zip(fanouts, hops)):
         w_indptr, _, w_idx, w_sel = oracle.sample_uniform(indptr, indices, cur, k, False, seed=77 + hop)
         assert np.array_equal(host(h["sub_indptr"]), w_indptr)
         assert np.array_equal(host(h["indices"]), w_idx)
