@@ -37,6 +37,12 @@ METRIC = "sampled_edges_per_second"
 UNIT = "edges/s"
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) divided by algorithmic bytes, from one ncu capture
+# per kernel on a 64-minibatch call of this workload (profiles/k_*_sage3hop_group64.md).  Traffic grows in
+# proportion to the units a launch processes, so a full launch's traffic is this ratio times its algorithmic bytes.
+TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.1, "table_insert": 3.0, "first_compact": 2.2, "relabel": 1.8}
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -349,12 +355,15 @@ def run_ours(args):
             entry["bytes_per_launch"] = round(alg[name])
             entry["achieved_gbs"] = round(alg[name] / avg_s / 1e9, 2)
             entry["frac"] = round(alg[name] / avg_s / 1e9 / peak, 5)
+            if name in TRAFFIC_OVER_ALGORITHMIC:
+                entry["traffic"] = round(alg[name] * TRAFFIC_OVER_ALGORITHMIC[name])
         per_kernel[name] = entry
     top = max((k for k in per_kernel if k in alg), key=lambda k: per_kernel[k]["ms"], default=None)
     if top is not None:
         t = per_kernel[top]
         roofline = {"bound": "hbm", "kernel": kernel_names[top], "achieved": t["achieved_gbs"], "peak": peak,
-                    "peak_source": peak_src, "unit": "GB/s", "frac": t["frac"], "traffic": None,
+                    "peak_source": peak_src, "unit": "GB/s", "frac": t["frac"], "traffic": t.get("traffic"),
+                    "traffic_source": "ncu capture of a 64-minibatch call, scaled by algorithmic bytes",
                     "bytes_per_launch": t["bytes_per_launch"], "avg_launch_us": t["avg_launch_us"],
                     "share_of_device_time": t["share"], "kernels": per_kernel}
     else:
