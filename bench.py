@@ -478,9 +478,9 @@ def run_walk(args):
     else:
         from graph_sampling_b200 import ops
         ctx = ops.default_context(device)
-        layout_id = 1
+        layout_id = 0  # the reference's own memory order, so both arms write the same layout
         fn = lambda: ops.fused_random_walk(mine, L, indices, indptr, layout=layout_id, walker_offset=off)
-        layout = "walker-major [walkers, length+1]"
+        layout = "walker-major [walkers, length+1]" if layout_id == 1 else "step-major memory (the reference's own)"
     for _ in range(warmup):
         out = fn()
     torch.cuda.synchronize()

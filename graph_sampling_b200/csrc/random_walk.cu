@@ -2,6 +2,10 @@
 // walk (the reference re-reads the previous trace element from global memory at every step:
 // src/cuda/fusion/random_walk.cu:32), one Philox block feeds four steps.
 //
+// Several walkers per thread (more independent chains in flight) were measured and do not help: at
+// papers scale the walk is bound by the throughput of random 64-byte DRAM accesses (two per live step), not
+// by latency.
+//
 // Per step the walker does two dependent gathers (the indptr pair of the current node, then one
 // entry of indices) and one trace store.  Step-major stores (layout 0, the reference's memory
 // order) are coalesced across the warp as they are.  Walker-major stores (layout 1) are staged
