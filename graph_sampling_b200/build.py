@@ -58,5 +58,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+GLUE_SRC = os.path.join(CSRC, "glue", "gs_glue.cc")
+GLUE_LIB = os.path.join(LIBDIR, "libgs.so")
+
+
+def build_glue(force: bool = False) -> str:
+    """Builds lib/libgs.so: the TorchScript front end (gs_classes.Graph, gs_ops.*) over the C ABI.  Needs the
+    torch headers; links against libgsb200.so (found next to it through $ORIGIN) and torch."""
+    build(force=False)
+    deps = [GLUE_SRC, os.path.join(os.path.dirname(PKG), "include", "gsb200.h")]
+    if not force and os.path.exists(GLUE_LIB) and all(os.path.getmtime(GLUE_LIB) >= os.path.getmtime(d) for d in deps):
+        return GLUE_LIB
+    import sysconfig
+    import torch
+    tdir = os.path.dirname(torch.__file__)
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-w",
+           "-I", os.path.join(tdir, "include"), "-I", os.path.join(tdir, "include", "torch", "csrc", "api", "include"),
+           "-I", sysconfig.get_paths()["include"], "-I", "/usr/local/cuda/include", GLUE_SRC, "-o", GLUE_LIB,
+           "-L", LIBDIR, "-lgsb200", "-Wl,-rpath,$ORIGIN", "-L", os.path.join(tdir, "lib"), "-ltorch", "-ltorch_cpu",
+           "-ltorch_cuda", "-lc10", "-lc10_cuda", "-Wl,-rpath," + os.path.join(tdir, "lib"),
+           "-L", "/usr/local/cuda/lib64", "-lcudart"]
+    subprocess.check_call(cmd)
+    return GLUE_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--glue" in sys.argv:
+        print(build_glue(force="--force" in sys.argv))

@@ -1,0 +1,780 @@
+// TorchScript front end of the sampler: registers `gs_classes.Graph` and the `gs_ops` free operators with
+// the method names of the reference's registry (src/pybind.cc:11-86) — CamelCase as registered there and the
+// snake_case spelling its Python layer calls (python/gs/matrix_api/matrix.py) — so that
+// `torch.classes.load_library("libgs.so")` gives the same object a user of the reference drives.
+//
+// This file holds only bookkeeping: which sparse formats a graph owns, its id maps, edge data, tuple orders.
+// Every piece of arithmetic goes through the C ABI of gsb200.h with raw device pointers and torch's current
+// stream.  The state kept per graph and the effect of each method on it follow gs::Graph
+// (src/graph.h:113-126, src/graph.cc).  Where the reference aborts the process (LOG(FATAL)), TORCH_CHECK
+// raises instead.  Compact-id (DCSC/DCSR), batched and induced-subgraph methods are not provided.
+#include <c10/cuda/CUDAStream.h>
+#include <torch/custom_class.h>
+#include <torch/script.h>
+
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "../../../include/gsb200.h"
+
+namespace gsglue {
+
+using torch::Tensor;
+using OptTensor = torch::optional<Tensor>;
+
+constexpr int64_t kCOO = 1, kCSC = 2, kCSR = 4, kDCSC = 8, kDCSR = 16;
+
+// ---- C ABI plumbing ---------------------------------------------------------------------------------------
+static gsb_ctx* Ctx() {
+  static thread_local gsb_ctx* ctx[64] = {nullptr};
+  const int dev = c10::cuda::current_device();
+  TORCH_CHECK(dev >= 0 && dev < 64, "unsupported device index ", dev);
+  if (!ctx[dev]) {
+    const int st = gsb_ctx_create(dev, &ctx[dev]);
+    TORCH_CHECK(st == GSB_OK, "gsb_ctx_create failed: ", gsb_status_string(st), " (a CUDA device is required)");
+  }
+  return ctx[dev];
+}
+static void* Stream() { return (void*)c10::cuda::getCurrentCUDAStream().stream(); }
+static void Check(int st, const char* what) {
+  TORCH_CHECK(st == GSB_OK, what, ": ", gsb_status_string(st), " ", gsb_last_error_message(Ctx()));
+}
+static const int64_t* IP(const Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<int64_t>() : nullptr; }
+static int64_t* MP(Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<int64_t>() : nullptr; }
+static const float* FP(const Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<float>() : nullptr; }
+static Tensor Ids(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt64, name, " must be an int64 CUDA tensor");
+  return t.contiguous();
+}
+static Tensor Floats(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32, name, " must be a float32 CUDA tensor");
+  return t.contiguous();
+}
+static Tensor EmptyIds(int64_t n, const Tensor& like) { return torch::empty({n}, like.options().dtype(torch::kInt64)); }
+
+static std::atomic<uint64_t> g_seed_base{7777};
+static std::atomic<uint64_t> g_seed_counter{0};
+static uint64_t NextSeed() { return g_seed_base.load() * 0x9E3779B97F4A7C15ull + g_seed_counter.fetch_add(1); }
+
+// ---- storage (src/graph_storage.h:9-30) ------------------------------------------------------------------------
+struct CSC {
+  Tensor indptr, indices;
+  OptTensor e_ids;
+};
+struct COO {
+  Tensor row, col;
+  OptTensor e_ids;
+  bool row_sorted = false, col_sorted = false;
+};
+struct Sliced {  // {sub_indptr, other coordinate per edge (optional), sub_indices, select_index, gathered data (optional)}
+  Tensor indptr, coo_other, indices, select, data;
+};
+
+// ---- operator wrappers ------------------------------------------------------------------------------------------
+static Sliced ColSlice(const CSC& g, const Tensor& ids, bool with_coo, const OptTensor& data) {
+  Tensor n_ids = Ids(ids, "node ids");
+  const int64_t S = n_ids.numel();
+  Sliced r;
+  r.indptr = EmptyIds(S + 1, g.indptr);
+  int64_t nnz = 0;
+  Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), IP(n_ids), S, MP(r.indptr), &nnz), "gsb_col_slice_count");
+  r.indices = EmptyIds(nnz, g.indptr);
+  r.select = EmptyIds(nnz, g.indptr);
+  if (with_coo) r.coo_other = EmptyIds(nnz, g.indptr);
+  Tensor d, e;
+  if (data.has_value()) {
+    d = Floats(data.value(), "edge data");
+    r.data = torch::empty({nnz}, d.options());
+    if (g.e_ids.has_value()) e = g.e_ids.value();
+  }
+  Check(gsb_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(n_ids), S, IP(r.indptr), MP(r.indices),
+                           MP(r.select), with_coo ? MP(r.coo_other) : nullptr, FP(d), IP(e),
+                           r.data.defined() && nnz ? r.data.data_ptr<float>() : nullptr),
+        "gsb_col_slice_fill");
+  return r;
+}
+
+static Sliced Sample(const CSC& g, const Tensor* seeds, int64_t fanout, bool replace, bool with_coo,
+                     const Tensor* probs, const OptTensor& data) {
+  Tensor s;
+  if (seeds) s = Ids(*seeds, "column ids");
+  const int64_t S = seeds ? s.numel() : g.indptr.numel() - 1;
+  const int64_t cap = S * fanout;
+  Sliced r;
+  r.indptr = EmptyIds(S + 1, g.indptr);
+  r.indices = EmptyIds(cap, g.indptr);
+  r.select = EmptyIds(cap, g.indptr);
+  if (with_coo) r.coo_other = EmptyIds(cap, g.indptr);
+  Tensor d, e, out_d, p;
+  if (data.has_value()) {
+    d = Floats(data.value(), "edge data");
+    out_d = torch::empty({cap}, d.options());
+    if (g.e_ids.has_value()) e = g.e_ids.value();
+  }
+  int64_t nnz = 0;
+  if (probs) {
+    p = Floats(*probs, "edge probabilities");
+    TORCH_CHECK(p.numel() == g.indices.numel(), "edge_probs must have one entry per edge of the operand");
+    Check(gsb_sample_weighted(Ctx(), Stream(), IP(g.indptr), IP(g.indices), FP(p), seeds ? IP(s) : nullptr, S, fanout,
+                              replace, NextSeed(), MP(r.indptr), MP(r.indices), MP(r.select),
+                              with_coo ? MP(r.coo_other) : nullptr, FP(d), IP(e),
+                              out_d.defined() && cap ? out_d.data_ptr<float>() : nullptr, cap, &nnz),
+          "gsb_sample_weighted");
+  } else {
+    Check(gsb_sample_uniform(Ctx(), Stream(), IP(g.indptr), IP(g.indices), seeds ? IP(s) : nullptr, S, fanout, replace,
+                             NextSeed(), MP(r.indptr), MP(r.indices), MP(r.select),
+                             with_coo ? MP(r.coo_other) : nullptr, FP(d), IP(e),
+                             out_d.defined() && cap ? out_d.data_ptr<float>() : nullptr, cap, &nnz),
+          "gsb_sample_uniform");
+  }
+  r.indices = r.indices.narrow(0, 0, nnz);
+  r.select = r.select.narrow(0, 0, nnz);
+  if (with_coo) r.coo_other = r.coo_other.narrow(0, 0, nnz);
+  if (out_d.defined()) r.data = out_d.narrow(0, 0, nnz);
+  return r;
+}
+
+static std::tuple<Tensor, std::vector<Tensor>> Relabel(const std::vector<Tensor>& mapping,
+                                                       const std::vector<Tensor>& to_relabel) {
+  TORCH_CHECK(!mapping.empty() && mapping.size() <= GSB_MAX_SEGMENTS && to_relabel.size() <= GSB_MAX_SEGMENTS,
+              "relabel takes 1..", GSB_MAX_SEGMENTS, " mapping tensors and at most ", GSB_MAX_SEGMENTS, " tensors to relabel");
+  std::vector<Tensor> maps, rels, outs;
+  const int64_t* ip[GSB_MAX_SEGMENTS] = {nullptr};
+  int64_t il[GSB_MAX_SEGMENTS] = {0};
+  const int64_t* rp[GSB_MAX_SEGMENTS] = {nullptr};
+  int64_t rl[GSB_MAX_SEGMENTS] = {0};
+  int64_t* ro[GSB_MAX_SEGMENTS] = {nullptr};
+  int64_t n = 0;
+  for (size_t i = 0; i < mapping.size(); ++i) {
+    maps.push_back(Ids(mapping[i], "mapping tensor"));
+    ip[i] = IP(maps[i]);
+    il[i] = maps[i].numel();
+    n += il[i];
+  }
+  for (size_t i = 0; i < to_relabel.size(); ++i) {
+    rels.push_back(Ids(to_relabel[i], "tensor to relabel"));
+    outs.push_back(torch::empty_like(rels[i]));
+    rp[i] = IP(rels[i]);
+    rl[i] = rels[i].numel();
+    ro[i] = MP(outs[i]);
+  }
+  Tensor unique = EmptyIds(n, maps[0]);
+  int64_t nu = 0;
+  Check(gsb_unique_relabel(Ctx(), Stream(), ip, il, (int)maps.size(), MP(unique), rp, rl, ro, (int)rels.size(), &nu),
+        "gsb_unique_relabel");
+  return {unique.narrow(0, 0, nu), outs};
+}
+
+static std::tuple<Tensor, Tensor, Tensor, Tensor> RowSliceCSC(const CSC& g, const Tensor& ids, bool with_coo) {
+  Tensor rows = Ids(ids, "row ids");
+  const int64_t nc = g.indptr.numel() - 1, E = g.indices.numel();
+  Tensor out_indptr = EmptyIds(nc + 1, g.indptr), oi = EmptyIds(E, g.indptr), os = EmptyIds(E, g.indptr), oc;
+  if (with_coo) oc = EmptyIds(E, g.indptr);
+  int64_t nnz = 0;
+  Check(gsb_row_slice_csc(Ctx(), Stream(), IP(g.indptr), IP(g.indices), nc, E, IP(rows), rows.numel(), MP(out_indptr),
+                          MP(oi), MP(os), with_coo ? MP(oc) : nullptr, &nnz),
+        "gsb_row_slice_csc");
+  if (with_coo) oc = oc.narrow(0, 0, nnz);
+  return {out_indptr, oc, oi.narrow(0, 0, nnz), os.narrow(0, 0, nnz)};
+}
+
+static std::tuple<Tensor, Tensor, Tensor> RowSliceCOO(const Tensor& key, const Tensor& other, const Tensor& ids) {
+  Tensor rows = Ids(ids, "ids");
+  const int64_t E = key.numel();
+  Tensor o_k = EmptyIds(E, key), o_o = EmptyIds(E, key), o_s = EmptyIds(E, key);
+  int64_t nnz = 0;
+  Check(gsb_row_slice_coo(Ctx(), Stream(), IP(key), IP(other), E, IP(rows), rows.numel(), MP(o_k), MP(o_o), MP(o_s),
+                          &nnz),
+        "gsb_row_slice_coo");
+  return {o_k.narrow(0, 0, nnz), o_o.narrow(0, 0, nnz), o_s.narrow(0, 0, nnz)};
+}
+
+static Tensor ExpandOffsets(const CSC& g) {
+  Tensor col = EmptyIds(g.indices.numel(), g.indptr);
+  Check(gsb_csc2coo(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, MP(col)), "gsb_csc2coo");
+  return col;
+}
+
+// (indptr, other sorted by key, permutation or nullopt): src/cuda/format_transform.cu:135-156
+static std::tuple<Tensor, Tensor, OptTensor> SortByKey(const Tensor& key, const Tensor& other, int64_t num_keys,
+                                                       bool sorted) {
+  const int64_t E = key.numel();
+  Tensor indptr = EmptyIds(num_keys + 1, key), out = EmptyIds(E, key), perm;
+  if (!sorted) perm = EmptyIds(E, key);
+  Check(gsb_coo2csc(Ctx(), Stream(), IP(key), IP(other), E, num_keys, sorted, MP(indptr), MP(out),
+                    sorted ? nullptr : MP(perm)),
+        "gsb_coo2csc");
+  return {indptr, out, sorted ? OptTensor() : OptTensor(perm)};
+}
+
+struct Bcast {  // CalcBcastOff, src/bcast.cc:24-76
+  int64_t lhs_len = 1, rhs_len = 1, out_len = 1, reduce_size = 1;
+  std::vector<int64_t> lhs_off, rhs_off;
+  bool use = false;
+};
+static Bcast CalcBcast(const std::string& op, const Tensor& lhs, const Tensor& rhs) {
+  Bcast b;
+  for (int64_t i = 1; i < lhs.dim(); ++i) b.lhs_len *= lhs.size(i);
+  for (int64_t i = 1; i < rhs.dim(); ++i) b.rhs_len *= rhs.size(i);
+  if (op != "copy_lhs" && op != "copy_rhs") {
+    b.use = lhs.dim() != rhs.dim();
+    for (int64_t i = 1; !b.use && i < lhs.dim(); ++i) b.use = lhs.size(i) != rhs.size(i);
+  }
+  if (b.use) {
+    const int64_t max_ndim = std::max(lhs.dim(), rhs.dim()) - 1;
+    int64_t out_len = 1, j = 0, stride_l = 1, stride_r = 1;
+    if (op == "dot") {
+      b.reduce_size = lhs.size(lhs.dim() - 1);
+      j = 1;
+    }
+    b.lhs_off.push_back(0);
+    b.rhs_off.push_back(0);
+    for (; j < max_ndim; ++j) {
+      const int64_t dl = (lhs.dim() - 1 - j < 1) ? 1 : lhs.size(lhs.dim() - 1 - j);
+      const int64_t dr = (rhs.dim() - 1 - j < 1) ? 1 : rhs.size(rhs.dim() - 1 - j);
+      for (int64_t i = 1; i < std::max(dl, dr); ++i)
+        for (int64_t q = 0; q < out_len; ++q) {
+          b.lhs_off.push_back(b.lhs_off[q] + i * (i < dl ? 1 : 0) * stride_l);
+          b.rhs_off.push_back(b.rhs_off[q] + i * (i < dr ? 1 : 0) * stride_r);
+        }
+      out_len *= std::max(dl, dr);
+      stride_l *= dl;
+      stride_r *= dr;
+    }
+    b.out_len = out_len;
+  } else {
+    b.out_len = (op == "copy_rhs") ? b.rhs_len : b.lhs_len;
+    if (op == "dot") {
+      b.reduce_size = lhs.size(lhs.dim() - 1);
+      b.out_len /= b.reduce_size;
+    }
+  }
+  return b;
+}
+
+static void Sddmm(const std::string& op, const Tensor& row, const Tensor* col, const Tensor* indptr,
+                  const OptTensor& e_ids, const Tensor& lhs_in, const Tensor& rhs_in, Tensor out, int64_t lt,
+                  int64_t rt) {
+  static const char* names[] = {"add", "sub", "mul", "div", "copy_lhs", "copy_rhs", "dot"};
+  int code = -1;
+  for (int i = 0; i < 7; ++i)
+    if (op == names[i]) code = i;
+  TORCH_CHECK(code >= 0, "unknown SDDMM op ", op);
+  Tensor lhs = Floats(lhs_in, "lhs"), rhs = Floats(rhs_in, "rhs");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kFloat32 && out.is_contiguous(),
+              "out must be a contiguous float32 CUDA tensor");
+  const Bcast b = CalcBcast(op, lhs, rhs);
+  const int64_t E = row.numel();
+  TORCH_CHECK(out.numel() == E * b.out_len, "out has ", out.numel(), " elements, expected ", E * b.out_len);
+  Tensor lo, ro, e;
+  if (b.use) {
+    lo = torch::tensor(b.lhs_off, torch::dtype(torch::kInt64)).to(row.device());
+    ro = torch::tensor(b.rhs_off, torch::dtype(torch::kInt64)).to(row.device());
+  }
+  if (e_ids.has_value()) e = e_ids.value();
+  Check(gsb_sddmm(Ctx(), Stream(), code, IP(row), col ? IP(*col) : nullptr, indptr ? IP(*indptr) : nullptr,
+                  indptr ? indptr->numel() - 1 : 0, IP(e), E, FP(lhs), FP(rhs), out.numel() ? out.data_ptr<float>() : nullptr,
+                  (int)lt, (int)rt, b.lhs_len, b.rhs_len, b.out_len, b.reduce_size, IP(lo), IP(ro)),
+        "gsb_sddmm");
+}
+
+// ---- Graph -----------------------------------------------------------------------------------------------------
+class Graph : public torch::CustomClassHolder {
+ public:
+  explicit Graph(bool is_subgraph) : is_subgraph_(is_subgraph) {}
+  Graph(bool is_subgraph, OptTensor col_ids, OptTensor row_ids, int64_t num_cols, int64_t num_rows)
+      : is_subgraph_(is_subgraph), num_cols_(num_cols), num_rows_(num_rows), col_ids_(col_ids), row_ids_(row_ids) {}
+
+  // loading (src/graph.cc:14-60)
+  void LoadCSC(Tensor indptr, Tensor indices) {
+    csc_ = std::make_shared<CSC>(CSC{Ids(indptr, "indptr"), Ids(indices, "indices"), torch::nullopt});
+    num_cols_ = num_rows_ = indptr.numel() - 1;
+    num_edges_ = indices.numel();
+  }
+  void LoadCOO(Tensor row, Tensor col) {
+    coo_ = std::make_shared<COO>(COO{Ids(row, "row"), Ids(col, "col"), torch::nullopt, false, false});
+    const int64_t n = std::max(std::get<0>(torch::_unique(row)).numel(), std::get<0>(torch::_unique(col)).numel());
+    num_cols_ = num_rows_ = n;
+    num_edges_ = row.numel();
+  }
+  void LoadCSCWithColIds(Tensor column_ids, Tensor indptr, Tensor indices) {
+    TORCH_CHECK(column_ids.numel() == indptr.numel() - 1, "length of column_ids is not aligned with indptr");
+    csc_ = std::make_shared<CSC>(CSC{Ids(indptr, "indptr"), Ids(indices, "indices"), torch::nullopt});
+    col_ids_ = column_ids;
+    num_cols_ = column_ids.numel();
+    num_rows_ = indices.numel() ? indices.max().item<int64_t>() + 1 : 0;
+    num_edges_ = indices.numel();
+  }
+  void SetMetaData(OptTensor col_ids, OptTensor row_ids, int64_t num_cols, int64_t num_rows) {
+    col_ids_ = col_ids;
+    row_ids_ = row_ids;
+    num_cols_ = num_cols;
+    num_rows_ = num_rows;
+  }
+  void SetCOOByTensor(Tensor row, Tensor col, OptTensor e_ids, bool row_sorted, bool col_sorted) {
+    coo_ = std::make_shared<COO>(COO{row, col, e_ids, row_sorted, col_sorted});
+  }
+  void SetData(Tensor data) { data_ = data; }
+  int64_t GetNumRows() { return num_rows_; }
+  int64_t GetNumCols() { return num_cols_; }
+  int64_t GetNumEdges() { return num_edges_; }
+
+  OptTensor GetData(std::string order) {
+    Tensor data = DataOrOnes();
+    if (order == "col") {
+      CreateSparseFormat(kCSC);
+      if (csc_->e_ids.has_value()) return data.index({csc_->e_ids.value()});
+    } else if (order == "row") {
+      CreateSparseFormat(kCSR);
+      if (csr_->e_ids.has_value()) return data.index({csr_->e_ids.value()});
+    }
+    return data;
+  }
+
+  // lazy formats (src/graph.cc:585-644, src/graph_ops.cc:13-60)
+  void CreateSparseFormat(int64_t format) {
+    if (format == kCOO) {
+      if (coo_) return;
+      coo_ = csc_ ? ToCOO(*csc_, true) : ToCOO(*csr_, false);
+    } else if (format == kCSC) {
+      if (csc_) return;
+      if (!coo_) coo_ = ToCOO(*csr_, false);
+      csc_ = FromCOO(*coo_, num_cols_, true);
+    } else if (format == kCSR) {
+      if (csr_) return;
+      if (!coo_) coo_ = ToCOO(*csc_, true);
+      csr_ = FromCOO(*coo_, num_rows_, false);
+    } else {
+      TORCH_CHECK(false, "compact-id (DCSC / DCSR) layouts are not provided by this library");
+    }
+  }
+
+  // Slicing (src/graph.cc:173-310)
+  c10::intrusive_ptr<Graph> Slicing(Tensor n_ids, int64_t axis, int64_t on_format, int64_t output_format,
+                                    bool relabel) {
+    CreateSparseFormat(on_format);
+    const bool with_coo = output_format & kCOO;
+    OptTensor new_col_ids, new_row_ids;
+    int64_t new_cols, new_rows, new_edges = 0;
+    if (axis == 0) {
+      new_col_ids = col_ids_.has_value() ? col_ids_.value().index({n_ids}) : n_ids;
+      new_row_ids = row_ids_;
+      new_cols = n_ids.numel();
+      new_rows = num_rows_;
+    } else {
+      new_col_ids = col_ids_;
+      new_row_ids = row_ids_.has_value() ? row_ids_.value().index({n_ids}) : n_ids;
+      new_cols = num_cols_;
+      new_rows = n_ids.numel();
+    }
+    std::shared_ptr<CSC> csc, csr;
+    std::shared_ptr<COO> coo;
+    Tensor out_data;
+    auto gather = [&](const OptTensor& e_ids, const Tensor& select) {
+      if (!data_.has_value()) return;
+      Tensor idx = e_ids.has_value() ? e_ids.value().index({select}) : select;
+      out_data = data_.value().index({idx});
+    };
+    if (on_format == kCOO) {
+      Tensor nr, nc, sel;
+      if (axis == 1) std::tie(nr, nc, sel) = RowSliceCOO(coo_->row, coo_->col, n_ids);
+      else std::tie(nc, nr, sel) = RowSliceCOO(coo_->col, coo_->row, n_ids);
+      coo = std::make_shared<COO>(COO{nr, nc, torch::nullopt, coo_->row_sorted, coo_->col_sorted});
+      new_edges = nr.numel();
+      gather(coo_->e_ids, sel);
+    } else if (on_format == kCSC || on_format == kCSR) {
+      const bool on_csc = on_format == kCSC;
+      TORCH_CHECK(output_format != (on_csc ? kCSR : kCSC), "Error in Slicing, Not implementation [on_format = ",
+                  on_csc ? "CSC, output_forat = CSR]" : "CSR, output_forat = CSC]");
+      const CSC& g = on_csc ? *csc_ : *csr_;
+      const bool slice_segments = (axis == 0) == on_csc;  // slicing along the format's own axis
+      Tensor indptr, other, indices;
+      if (slice_segments) {
+        Sliced r = ColSlice(g, n_ids, with_coo, data_);
+        indptr = r.indptr, other = r.coo_other, indices = r.indices, out_data = r.data;
+        if (relabel) {
+          auto res = Relabel({indices}, {indices});
+          indices = std::get<1>(res)[0];
+          if (on_csc) new_row_ids = std::get<0>(res), new_rows = std::get<0>(res).numel();
+          else new_col_ids = std::get<0>(res), new_cols = std::get<0>(res).numel();
+        }
+      } else {
+        TORCH_CHECK(!relabel, "Not implemented warning");
+        Tensor sel;
+        std::tie(indptr, other, indices, sel) = RowSliceCSC(g, n_ids, with_coo);
+        gather(g.e_ids, sel);
+      }
+      if (output_format & (on_csc ? kCSC : kCSR))
+        (on_csc ? csc : csr) = std::make_shared<CSC>(CSC{indptr, indices, torch::nullopt});
+      if (with_coo)
+        coo = on_csc ? std::make_shared<COO>(COO{indices, other, torch::nullopt, false, true})
+                     : std::make_shared<COO>(COO{other, indices, torch::nullopt, true, false});
+      new_edges = indices.numel();
+    } else {
+      TORCH_CHECK(false, "Slicing on DCSC / DCSR is not provided by this library");
+    }
+    auto ret = c10::make_intrusive<Graph>(true, new_col_ids, new_row_ids, new_cols, new_rows);
+    ret->num_edges_ = new_edges;
+    ret->csc_ = csc, ret->csr_ = csr, ret->coo_ = coo;
+    if (out_data.defined()) ret->data_ = out_data;
+    return ret;
+  }
+
+  // Sampling / SamplingProbs (src/graph.cc:393-529)
+  c10::intrusive_ptr<Graph> SampleImpl(int64_t axis, const Tensor* probs, int64_t fanout, bool replace,
+                                       int64_t on_format, int64_t output_format) {
+    CreateSparseFormat(on_format);
+    const bool with_coo = output_format & kCOO;
+    const bool on_csc = axis == 0 && on_format == kCSC;
+    TORCH_CHECK(on_csc || (axis == 1 && on_format == kCSR), "No implementation!");
+    TORCH_CHECK(output_format != (on_csc ? kCSR : kCSC), "Error in Sampling, Not implementation [on_format / output_format]");
+    const CSC& g = on_csc ? *csc_ : *csr_;
+    Sliced r = Sample(g, nullptr, fanout, replace, with_coo, probs, data_);
+    auto ret = c10::make_intrusive<Graph>(true, col_ids_, row_ids_, num_cols_, num_rows_);
+    if (output_format & (on_csc ? kCSC : kCSR))
+      (on_csc ? ret->csc_ : ret->csr_) = std::make_shared<CSC>(CSC{r.indptr, r.indices, torch::nullopt});
+    if (with_coo)
+      ret->coo_ = on_csc ? std::make_shared<COO>(COO{r.indices, r.coo_other, torch::nullopt, false, true})
+                         : std::make_shared<COO>(COO{r.coo_other, r.indices, torch::nullopt, true, false});
+    ret->num_edges_ = r.indices.numel();
+    if (r.data.defined()) ret->data_ = r.data;
+    return ret;
+  }
+  c10::intrusive_ptr<Graph> Sampling(int64_t axis, int64_t fanout, bool replace, int64_t on_format,
+                                     int64_t output_format) {
+    return SampleImpl(axis, nullptr, fanout, replace, on_format, output_format);
+  }
+  c10::intrusive_ptr<Graph> SamplingProbs(int64_t axis, Tensor edge_probs, int64_t fanout, bool replace,
+                                          int64_t on_format, int64_t output_format) {
+    return SampleImpl(axis, &edge_probs, fanout, replace, on_format, output_format);
+  }
+
+  // src/graph.cc:531-559 (keep-dim variant chosen like src/graph_ops.cc:223-247)
+  c10::intrusive_ptr<Graph> ColumnwiseFusedSlicingAndSampling(Tensor column_index, int64_t fanout, bool replace) {
+    TORCH_CHECK(csc_ != nullptr, "ColumnwiseFusedSlicingAndSampling needs a CSC graph");
+    Tensor col_ids = col_ids_.has_value() ? col_ids_.value().index({column_index}) : column_index;
+    auto ret = c10::make_intrusive<Graph>(true, col_ids, row_ids_, col_ids.numel(), num_rows_);
+    if (fanout == 1 && replace) {
+      Tensor seeds = Ids(column_index, "column ids");
+      const int64_t S = seeds.numel();
+      Tensor indptr = EmptyIds(S + 1, seeds), indices = EmptyIds(S, seeds), select = EmptyIds(S, seeds);
+      Check(gsb_sample_one_keepdim(Ctx(), Stream(), IP(csc_->indptr), IP(csc_->indices), IP(seeds), S, NextSeed(),
+                                   MP(indptr), MP(indices), MP(select)),
+            "gsb_sample_one_keepdim");
+      ret->csc_ = std::make_shared<CSC>(CSC{indptr, indices, torch::nullopt});
+      ret->num_edges_ = S;
+      if (data_.has_value()) {
+        Tensor safe = select.clamp_min(0);
+        ret->data_ = data_.value().index({csc_->e_ids.has_value() ? csc_->e_ids.value().index({safe}) : safe});
+      }
+      return ret;
+    }
+    Sliced r = Sample(*csc_, &column_index, fanout, replace, false, nullptr, data_);
+    ret->csc_ = std::make_shared<CSC>(CSC{r.indptr, r.indices, torch::nullopt});
+    ret->num_edges_ = r.indices.numel();
+    if (r.data.defined()) ret->data_ = r.data;
+    return ret;
+  }
+
+  // src/graph.cc:757-839
+  Tensor AllValidNode() {
+    TORCH_CHECK(col_ids_.has_value(), "For sampling, col_ids_ is necessary!");
+    Tensor rows;
+    if (csc_) rows = row_ids_.has_value() ? row_ids_.value() : csc_->indices;
+    else {
+      if (!coo_) coo_ = ToCOO(*csr_, false);
+      rows = row_ids_.has_value() ? row_ids_.value() : coo_->row;
+    }
+    return std::get<0>(Relabel({col_ids_.value(), rows}, {}));
+  }
+  std::tuple<Tensor, int64_t, int64_t, Tensor, Tensor, OptTensor, std::string> Relabel_() {
+    TORCH_CHECK(col_ids_.has_value(), "For sampling, col_ids_ is necessary!");
+    Tensor col_ids = col_ids_.value();
+    if (csc_) {
+      Tensor rows = row_ids_.has_value() ? row_ids_.value().index({csc_->indices}) : csc_->indices;
+      auto res = Relabel({col_ids, rows}, {rows});
+      Tensor frontier = std::get<0>(res);
+      return {frontier, frontier.numel(), col_ids.numel(), csc_->indptr.clone(), std::get<1>(res)[0], csc_->e_ids, "csc"};
+    }
+    TORCH_CHECK(csr_ || coo_, "Error in Relabel!");
+    if (!coo_) coo_ = ToCOO(*csr_, false);
+    Tensor coo_col = col_ids.index({coo_->col});
+    Tensor coo_row = row_ids_.has_value() ? row_ids_.value().index({coo_->row}) : coo_->row;
+    auto res = Relabel({col_ids, coo_row}, {coo_col, coo_row});
+    Tensor frontier = std::get<0>(res);
+    return {frontier, frontier.numel(), col_ids.numel(), std::get<1>(res)[1], std::get<1>(res)[0], coo_->e_ids, "coo"};
+  }
+
+  // src/graph.cc:646-648: the reference's step-major memory viewed as [seeds, length + 1]
+  Tensor RandomWalk(Tensor seeds, int64_t walk_length) {
+    TORCH_CHECK(csc_ != nullptr, "RandomWalk needs a CSC graph");
+    Tensor s = Ids(seeds, "seeds");
+    Tensor out = EmptyIds(s.numel() * (walk_length + 1), s);
+    Check(gsb_random_walk(Ctx(), Stream(), IP(csc_->indptr), IP(csc_->indices), IP(s), s.numel(), walk_length,
+                          NextSeed(), 0, 0, MP(out)),
+          "gsb_random_walk");
+    return out.reshape({s.numel(), walk_length + 1});
+  }
+
+  // src/graph.cc:967-985
+  void SDDMM(const std::string& op, Tensor lhs, Tensor rhs, Tensor out, int64_t lhs_target, int64_t rhs_target,
+             int64_t on_format) {
+    CreateSparseFormat(on_format);
+    if (on_format == kCOO) {
+      Sddmm(op, coo_->row, &coo_->col, nullptr, coo_->e_ids, lhs, rhs, out, lhs_target, rhs_target);
+    } else if (on_format == kCSR) {
+      const int64_t lt = lhs_target == 1 ? 1 : 2 - lhs_target, rt = rhs_target == 1 ? 1 : 2 - rhs_target;
+      Sddmm(op, csr_->indices, nullptr, &csr_->indptr, csr_->e_ids, lhs, rhs, out, lt, rt);
+    } else if (on_format == kCSC) {
+      Sddmm(op, csc_->indices, nullptr, &csc_->indptr, csc_->e_ids, lhs, rhs, out, lhs_target, rhs_target);
+    } else {
+      TORCH_CHECK(false, "SDDMM only supports CSR and COO formats");
+    }
+  }
+
+  // src/graph.cc:650-730
+  Tensor Sum(int64_t axis, int64_t powk, int64_t on_format) {
+    CreateSparseFormat(on_format);
+    Tensor data;
+    if (data_.has_value()) data = Floats(data_.value(), "edge data");
+    Tensor out = torch::zeros({axis == 0 ? num_cols_ : num_rows_},
+                              torch::dtype(torch::kFloat32).device(Device()));
+    float* o = out.numel() ? out.data_ptr<float>() : nullptr;
+    if (on_format == kCOO) {
+      const Tensor& target = (1 - axis) == 0 ? coo_->row : coo_->col;
+      Tensor e = coo_->e_ids.has_value() ? coo_->e_ids.value() : Tensor();
+      Check(gsb_segment_sum_coo(Ctx(), Stream(), IP(target), target.numel(), IP(e), FP(data), powk, o), "gsb_segment_sum_coo");
+    } else if ((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR)) {
+      const CSC& g = axis == 0 ? *csc_ : *csr_;
+      Tensor e = g.e_ids.has_value() ? g.e_ids.value() : Tensor();
+      Check(gsb_segment_sum_csc(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(e), FP(data), powk, o),
+            "gsb_segment_sum_csc");
+    } else {
+      TORCH_CHECK(false, "axis should be 0 or 1? on_format and axis do not match?");
+    }
+    return out;
+  }
+  c10::intrusive_ptr<Graph> Normalize(int64_t axis, int64_t on_format) {
+    CreateSparseFormat(on_format);
+    TORCH_CHECK((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR), "Not Implementation Error");
+    const CSC& g = axis == 0 ? *csc_ : *csr_;
+    Tensor in = Floats(DataOrOnes(), "edge data");
+    Tensor out = torch::empty_like(in);
+    Tensor e = g.e_ids.has_value() ? g.e_ids.value() : Tensor();
+    Check(gsb_segment_normalize_csc(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(e), FP(in),
+                                    out.numel() ? out.data_ptr<float>() : nullptr),
+          "gsb_segment_normalize_csc");
+    return SameStructure(out);
+  }
+  c10::intrusive_ptr<Graph> Divide(Tensor divisor, int64_t axis, int64_t on_format) {
+    CreateSparseFormat(on_format);
+    Tensor in = DataOrOnes();
+    Tensor out = torch::zeros({num_edges_}, in.options());
+    if (on_format == kCOO) {
+      Sddmm("div", coo_->row, &coo_->col, nullptr, coo_->e_ids, in, divisor, out, 1, (1 - axis) == 0 ? 0 : 2);
+    } else if ((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR)) {
+      const CSC& g = axis == 0 ? *csc_ : *csr_;
+      Sddmm("div", g.indices, nullptr, &g.indptr, g.e_ids, in, divisor, out, 1, 2);
+    }
+    return SameStructure(out);
+  }
+
+  // getters (src/graph.cc:841-965)
+  Tensor GetRows() {
+    return row_ids_.has_value() ? row_ids_.value() : torch::arange(num_rows_, torch::dtype(torch::kInt64).device(Device()));
+  }
+  Tensor GetCols() {
+    return col_ids_.has_value() ? col_ids_.value() : torch::arange(num_cols_, torch::dtype(torch::kInt64).device(Device()));
+  }
+  Tensor GetCOORows(bool is_original) {
+    Tensor rows;
+    if (coo_) rows = coo_->row;
+    else if (csc_ && !csc_->e_ids.has_value()) rows = csc_->indices;
+    else {
+      TORCH_CHECK(csr_ && !csr_->e_ids.has_value(), "Error in GetCOORows!");
+      coo_ = ToCOO(*csr_, false);
+      rows = coo_->row;
+    }
+    return (is_original && row_ids_.has_value()) ? row_ids_.value().index({rows}) : rows;
+  }
+  Tensor GetCOOCols(bool is_original) {
+    Tensor cols;
+    if (coo_) cols = coo_->col;
+    else if (csc_ && !csc_->e_ids.has_value()) {
+      coo_ = ToCOO(*csc_, true);
+      cols = coo_->col;
+    } else {
+      TORCH_CHECK(csr_ && !csr_->e_ids.has_value(), "Error in GetCOOCols!");
+      cols = csr_->indices;
+    }
+    return (is_original && col_ids_.has_value()) ? col_ids_.value().index({cols}) : cols;
+  }
+  Tensor GetValidRows() {
+    Tensor local = std::get<0>(torch::_unique(GetCOORows(false)));
+    return row_ids_.has_value() ? row_ids_.value().index({local}) : local;
+  }
+  Tensor GetValidCols() {
+    Tensor local = std::get<0>(torch::_unique(GetCOOCols(false)));
+    return col_ids_.has_value() ? col_ids_.value().index({local}) : local;
+  }
+  std::vector<Tensor> MetaData() {
+    Tensor c = col_ids_.value_or(Tensor()), r = row_ids_.value_or(Tensor());
+    if (csc_) return {c, r, DataOrOnes(), csc_->indptr, csc_->indices};
+    if (csr_) return {c, r, DataOrOnes(), csr_->indptr, csr_->indices};
+    return {coo_->row, coo_->col};
+  }
+  std::vector<Tensor> COOMetaData() {
+    if (!coo_) return {};
+    return {col_ids_.value_or(Tensor()), row_ids_.value_or(Tensor()), data_.value_or(Tensor()), coo_->row, coo_->col};
+  }
+  std::vector<Tensor> CSCMetaData() {
+    if (!csc_) return {};
+    return {col_ids_.value_or(Tensor()), row_ids_.value_or(Tensor()), data_.value_or(Tensor()), csc_->indptr, csc_->indices};
+  }
+  std::vector<Tensor> GetCSCTensor() {
+    CreateSparseFormat(kCSC);
+    return {csc_->indptr, csc_->indices, csc_->e_ids.value_or(Tensor())};
+  }
+  std::vector<Tensor> GetCOOTensor() {
+    CreateSparseFormat(kCOO);
+    TORCH_CHECK(coo_->col_sorted, "Check failed: coo_->col_sorted == true");
+    return {coo_->row, coo_->col, coo_->e_ids.value_or(Tensor())};
+  }
+
+ private:
+  torch::Device Device() const {
+    if (csc_) return csc_->indptr.device();
+    if (csr_) return csr_->indptr.device();
+    return coo_->row.device();
+  }
+  Tensor DataOrOnes() {
+    return data_.has_value() ? data_.value()
+                             : torch::ones({num_edges_}, torch::dtype(torch::kFloat32).device(Device()));
+  }
+  static std::shared_ptr<COO> ToCOO(const CSC& g, bool is_csc) {
+    Tensor expanded = ExpandOffsets(g);
+    return is_csc ? std::make_shared<COO>(COO{g.indices, expanded, g.e_ids, false, true})
+                  : std::make_shared<COO>(COO{expanded, g.indices, g.e_ids, true, false});
+  }
+  static std::shared_ptr<CSC> FromCOO(const COO& c, int64_t num_items, bool to_csc) {
+    Tensor indptr, indices;
+    OptTensor perm;
+    if (to_csc) std::tie(indptr, indices, perm) = SortByKey(c.col, c.row, num_items, c.col_sorted);
+    else std::tie(indptr, indices, perm) = SortByKey(c.row, c.col, num_items, c.row_sorted);
+    OptTensor e_ids = perm;
+    if (c.e_ids.has_value()) e_ids = perm.has_value() ? c.e_ids.value().index({perm.value()}) : c.e_ids.value();
+    return std::make_shared<CSC>(CSC{indptr, indices, e_ids});
+  }
+  c10::intrusive_ptr<Graph> SameStructure(Tensor data) {
+    auto ret = c10::make_intrusive<Graph>(is_subgraph_, col_ids_, row_ids_, num_cols_, num_rows_);
+    ret->csc_ = csc_, ret->csr_ = csr_, ret->coo_ = coo_;
+    ret->num_edges_ = num_edges_;
+    ret->data_ = data;
+    return ret;
+  }
+
+  bool is_subgraph_ = false;
+  int64_t num_cols_ = 0, num_rows_ = 0, num_edges_ = 0;
+  std::shared_ptr<CSC> csc_, csr_;
+  std::shared_ptr<COO> coo_;
+  OptTensor data_, col_ids_, row_ids_;
+};
+
+// ---- free operators (src/tensor_ops.cc:5-16, src/pybind.cc:62-85) ---------------------------------------------------
+static std::tuple<Tensor, Tensor> ListSampleImpl(const Tensor& data_in, const Tensor* probs, int64_t k, bool replace) {
+  Tensor data = Ids(data_in, "data"), p;
+  if (probs) {
+    p = Floats(*probs, "probs");
+    TORCH_CHECK(p.numel() == data.numel(), "probs must have one entry per item");
+  }
+  const int64_t N = data.numel();
+  const int64_t cap = std::max<int64_t>((!replace && N <= k) ? N : k, 1);
+  Tensor out_d = EmptyIds(cap, data), out_i = EmptyIds(cap, data);
+  int64_t n = 0;
+  Check(gsb_list_sample(Ctx(), Stream(), IP(data), FP(p), N, k, replace, NextSeed(), MP(out_d), MP(out_i), &n),
+        "gsb_list_sample");
+  return {out_d.narrow(0, 0, n), out_i.narrow(0, 0, n)};
+}
+static std::tuple<Tensor, Tensor> ListSampling(Tensor data, int64_t num_picks, bool replace) {
+  return ListSampleImpl(data, nullptr, num_picks, replace);
+}
+static std::tuple<Tensor, Tensor> ListSamplingProbs(Tensor data, Tensor probs, int64_t num_picks, bool replace) {
+  return ListSampleImpl(data, &probs, num_picks, replace);
+}
+static Tensor Unique(Tensor node_ids) { return std::get<0>(Relabel({node_ids}, {})); }
+static std::tuple<Tensor, Tensor, Tensor, Tensor> BatchCSRRelabel(Tensor seeds, Tensor seeds_ptr, Tensor indices,
+                                                                  Tensor indices_ptr) {
+  Tensor s = Ids(seeds, "seeds"), sp = Ids(seeds_ptr, "seeds_ptr"), ix = Ids(indices, "indices"),
+         ixp = Ids(indices_ptr, "indices_ptr");
+  const int64_t G = sp.numel() - 1;
+  Tensor uniq = EmptyIds(s.numel() + ix.numel(), s), uniq_ptr = EmptyIds(G + 1, s), rel = EmptyIds(ix.numel(), s);
+  int64_t nu = 0, ne = 0;
+  Check(gsb_batch_unique_relabel(Ctx(), Stream(), IP(s), IP(sp), s.numel(), IP(ix), IP(ixp), ix.numel(), G, MP(uniq),
+                                 MP(uniq_ptr), MP(rel), &nu, &ne),
+        "gsb_batch_unique_relabel");
+  return {uniq.narrow(0, 0, nu), uniq_ptr, rel.narrow(0, 0, ne), ixp};
+}
+static void SetSeed(int64_t seed) {
+  g_seed_base.store((uint64_t)seed);
+  g_seed_counter.store(0);
+}
+
+}  // namespace gsglue
+
+using gsglue::Graph;
+
+#define GS_DEF2(camel, snake, fn) .def(camel, fn).def(snake, fn)
+
+TORCH_LIBRARY(gs_classes, m) {
+  m.class_<Graph>("Graph")
+      .def(torch::init<bool>())
+      GS_DEF2("_CAPI_SetData", "_CAPI_set_data", &Graph::SetData)
+      GS_DEF2("_CAPI_GetData", "_CAPI_get_data", &Graph::GetData)
+      GS_DEF2("_CAPI_GetNumRows", "_CAPI_get_num_rows", &Graph::GetNumRows)
+      GS_DEF2("_CAPI_GetNumCols", "_CAPI_get_num_cols", &Graph::GetNumCols)
+      GS_DEF2("_CAPI_GetNumEdges", "_CAPI_get_num_edges", &Graph::GetNumEdges)
+      GS_DEF2("_CAPI_Slicing", "_CAPI_slicing", &Graph::Slicing)
+      GS_DEF2("_CAPI_Sampling", "_CAPI_sampling", &Graph::Sampling)
+      GS_DEF2("_CAPI_SamplingWithProbs", "_CAPI_sampling_with_probs", &Graph::SamplingProbs)
+      GS_DEF2("_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_fused_columnwise_slicing_sampling",
+              &Graph::ColumnwiseFusedSlicingAndSampling)
+      GS_DEF2("_CAPI_LoadCSC", "_CAPI_load_csc", &Graph::LoadCSC)
+      GS_DEF2("_CAPI_LoadCOO", "_CAPI_load_coo", &Graph::LoadCOO)
+      GS_DEF2("_CAPI_LoadCSCWithColIds", "_CAPI_load_csc_with_col_ids", &Graph::LoadCSCWithColIds)
+      GS_DEF2("_CAPI_AllValidNode", "_CAPI_all_valid_node", &Graph::AllValidNode)
+      .def("_CAPI_all_indices", &Graph::AllValidNode)
+      GS_DEF2("_CAPI_GetRows", "_CAPI_get_rows", &Graph::GetRows)
+      GS_DEF2("_CAPI_GetCols", "_CAPI_get_cols", &Graph::GetCols)
+      GS_DEF2("_CAPI_GetValidRows", "_CAPI_get_valid_rows", &Graph::GetValidRows)
+      GS_DEF2("_CAPI_GetValidCols", "_CAPI_get_valid_cols", &Graph::GetValidCols)
+      GS_DEF2("_CAPI_GetCOORows", "_CAPI_get_coo_rows", &Graph::GetCOORows)
+      GS_DEF2("_CAPI_GetCooCols", "_CAPI_get_coo_cols", &Graph::GetCOOCols)
+      GS_DEF2("_CAPI_Relabel", "_CAPI_relabel", &Graph::Relabel_)
+      GS_DEF2("_CAPI_Sum", "_CAPI_sum", &Graph::Sum)
+      GS_DEF2("_CAPI_Normalize", "_CAPI_normalize", &Graph::Normalize)
+      GS_DEF2("_CAPI_Divide", "_CAPI_divide", &Graph::Divide)
+      GS_DEF2("_CAPI_Metadata", "_CAPI_metadata", &Graph::MetaData)
+      GS_DEF2("_CAPI_COOMetadata", "_CAPI_coo_metadata", &Graph::COOMetaData)
+      GS_DEF2("_CAPI_CSCMetadata", "_CAPI_csc_metadata", &Graph::CSCMetaData)
+      GS_DEF2("_CAPI_RandomWalk", "_CAPI_random_walk", &Graph::RandomWalk)
+      GS_DEF2("_CAPI_SDDMM", "_CAPI_sddmm", &Graph::SDDMM)
+      GS_DEF2("_CAPI_GetCSC", "_CAPI_get_csc", &Graph::GetCSCTensor)
+      GS_DEF2("_CAPI_GetCOO", "_CAPI_get_coo", &Graph::GetCOOTensor)
+      GS_DEF2("_CAPI_SetCOO", "_CAPI_set_coo", &Graph::SetCOOByTensor)
+      GS_DEF2("_CAPI_SetMetadata", "_CAPI_set_metadata", &Graph::SetMetaData);
+}
+
+TORCH_LIBRARY(gs_ops, m) {
+  m.def("_CAPI_ListSampling", &gsglue::ListSampling);
+  m.def("list_sampling", &gsglue::ListSampling);
+  m.def("_CAPI_ListSamplingWithProbs", &gsglue::ListSamplingProbs);
+  m.def("list_sampling_with_probs", &gsglue::ListSamplingProbs);
+  m.def("_CAPI_Unique", &gsglue::Unique);
+  m.def("_CAPI_BatchCSRRelabel", &gsglue::BatchCSRRelabel);
+  m.def("BatchCSRRelabel", &gsglue::BatchCSRRelabel);
+  m.def("_CAPI_SetSeed", &gsglue::SetSeed);
+}

@@ -55,3 +55,23 @@ def test_package_has_no_cpu_fallback():
     from graph_sampling_b200 import ops
     with pytest.raises(RuntimeError):
         ops.Context()
+
+
+def test_torchscript_glue_registers_reference_names():
+    """lib/libgs.so loads in torch and registers gs_classes.Graph / gs_ops with the reference's method names
+    (src/pybind.cc) in both spellings; without a GPU a call fails with an exception, not an abort."""
+    import torch
+    torch.classes.load_library(gsb_build.build_glue())
+    g = torch.classes.gs_classes.Graph(False)
+    for name in ["_CAPI_LoadCSC", "_CAPI_load_csc", "_CAPI_Slicing", "_CAPI_slicing", "_CAPI_Sampling",
+                 "_CAPI_SamplingWithProbs", "_CAPI_FusedColumnwiseSlicingSampling",
+                 "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_AllValidNode", "_CAPI_all_indices", "_CAPI_Relabel",
+                 "_CAPI_relabel", "_CAPI_RandomWalk", "_CAPI_SDDMM", "_CAPI_Sum", "_CAPI_Normalize", "_CAPI_Divide",
+                 "_CAPI_Metadata", "_CAPI_GetCooCols", "_CAPI_GetCSC", "_CAPI_GetCOO"]:
+        assert hasattr(g, name), name
+    for op in ["_CAPI_ListSampling", "_CAPI_ListSamplingWithProbs", "_CAPI_Unique", "list_sampling",
+               "list_sampling_with_probs", "_CAPI_BatchCSRRelabel"]:
+        assert hasattr(torch.ops.gs_ops, op), op
+    if not torch.cuda.is_available():
+        with pytest.raises(Exception):
+            g._CAPI_LoadCSC(torch.arange(3), torch.arange(2))

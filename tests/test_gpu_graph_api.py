@@ -20,8 +20,30 @@ def host(t):
     return t.cpu().numpy()
 
 
+class _TorchScriptFace:
+    """The TorchScript registration (lib/libgs.so: torch.classes.gs_classes.Graph, torch.ops.gs_ops.*), given the
+    attribute names of the Python `gs` package so that the same call sequences run against both."""
+    _COO, _CSC, _CSR = 1, 2, 4
+
+    def __init__(self):
+        from graph_sampling_b200 import build as b
+        torch.classes.load_library(b.build_glue())
+        self.Graph = torch.classes.gs_classes.Graph
+        self.Unique = torch.ops.gs_ops._CAPI_Unique
+        self.ListSampling = torch.ops.gs_ops._CAPI_ListSampling
+        self.ListSamplingProbs = torch.ops.gs_ops._CAPI_ListSamplingWithProbs
+
+
+@pytest.fixture(scope="module", params=["python", "torchscript"])
+def gs(request):
+    if request.param == "torchscript":
+        return _TorchScriptFace()
+    import graph_sampling_b200.gs as _gs
+    return _gs
+
+
 @pytest.fixture(scope="module")
-def gs():
+def gs_py():
     import graph_sampling_b200.gs as _gs
     return _gs
 
@@ -156,7 +178,8 @@ def test_full_fixture_call_sequence(gs, gold):
     assert np.array_equal(host(sel), gold["listp_identity_data"]) and np.array_equal(host(idx), gold["listp_identity_index"])
 
 
-def test_graphsage_loop_matches_oracle(gs, oracle, cfg1_graph):
+def test_graphsage_loop_matches_oracle(gs_py, oracle, cfg1_graph):
+    gs = gs_py
     """BASELINE config 1: 1,024 seeds, fanouts [10, 5], fused slice+sample then relabel per hop
     (examples/graphsage/unbatching_training.py:19-28).  Same Philox seeds => identical frontiers."""
     indptr, indices = cfg1_graph
@@ -181,7 +204,8 @@ def test_graphsage_loop_matches_oracle(gs, oracle, cfg1_graph):
     assert total > 0
 
 
-def test_matrix_api_ladies_layer(gs, oracle, cfg1_graph):
+def test_matrix_api_ladies_layer(gs_py, oracle, cfg1_graph):
+    gs = gs_py
     """One LADIES layer through gs.Matrix (examples/ladies/train_minibatch.py:43-59): column slice,
     row probability = sum of squared weights, weighted list sampling, row slice, divide, normalize."""
     indptr, indices = cfg1_graph
@@ -217,7 +241,8 @@ def test_matrix_api_ladies_layer(gs, oracle, cfg1_graph):
     assert blk.format in ("coo", "csc") and blk.num_dst == 512
 
 
-def test_adaptive_sampling_hop(gs, oracle, cfg1_graph):
+def test_adaptive_sampling_hop(gs_py, oracle, cfg1_graph):
+    gs = gs_py
     """AS-GCN style hop (BASELINE config 5 at small scale): slice, u_dot_v / 16, per-column softmax,
     weighted sampling without replacement (fanout 10), relabel."""
     indptr, indices = cfg1_graph
