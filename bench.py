@@ -66,12 +66,15 @@ def parse():
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while a region is timed."""
 
-    def __init__(self, index, period=0.02):
+    def __init__(self, index, period=0.05, enabled=True):
         super().__init__(daemon=True)
         self.index, self.period = index, period
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop_evt = threading.Event()
         self.ok = False
+        if not enabled:  # only rank 0 polls NVML: concurrent polling from every rank slows the launch threads
+            self.nv = None
+            return
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -287,7 +290,7 @@ def run_ours(args):
 
     # ---- value: seeds resident in HBM --------------------------------------------------------------
     dev_batches = batches.to(device)
-    sampler = ClockSampler(physical_gpu_index(local))
+    sampler = ClockSampler(physical_gpu_index(local), enabled=(rank == 0))
     group = max(1, min(args.group, args.steps))
     ptr_cache = {}
     if group > 1:

@@ -380,11 +380,39 @@ __global__ void __launch_bounds__(kBThreads) k_gather_offsets(const i64* __restr
   if (b <= G) out[b] = sub_indptr[seeds_ptr[b]];
 }
 
+// Per-batch offset arrays cut out of one offset array: batch b receives indptr[offsets[b] .. offsets[b+1]]
+// rebased to start at 0, stored at out[offsets[b] + b ..] (each batch has one more entry than columns).
+__global__ void __launch_bounds__(kBThreads) k_split_indptr(const i64* __restrict__ indptr,
+                                                            const i64* __restrict__ offsets, i64 G, i64 uniform_size,
+                                                            i64* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const i64 warps = (i64)gridDim.x * (kBThreads / 32);
+  for (i64 b = (i64)blockIdx.x * (kBThreads / 32) + (threadIdx.x >> 5); b < G; b += warps) {
+    const i64 in_begin = offsets ? __ldg(offsets + b) : b * uniform_size;
+    const i64 in_end = offsets ? __ldg(offsets + b + 1) : (b + 1) * uniform_size;
+    const i64 prefix = __ldg(indptr + in_begin);
+    for (i64 j = lane; j <= in_end - in_begin; j += 32) out[in_begin + b + j] = __ldg(indptr + in_begin + j) - prefix;
+  }
+}
+
 }  // namespace gsb
 
 using namespace gsb;
 
 extern "C" {
+
+int gsb_split_indptr(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* offsets, int64_t G,
+                     int64_t uniform_size, int64_t* out) {
+  GSB_REQUIRE(ctx && G >= 0 && (offsets || uniform_size >= 0), GSB_ERR_INVALID_ARGUMENT);
+  if (G == 0) return GSB_OK;
+  GSB_REQUIRE(indptr && out, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+  k_split_indptr<<<max(1, min(grid_for(G * 32, kBThreads), kNumSMs * 8)), kBThreads, 0, stream>>>(indptr, offsets, G,
+                                                                                                  uniform_size, out);
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
 
 int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream_, const int64_t* sub_indptr, const int64_t* seeds_ptr,
                            int64_t G, int64_t* out_indices_ptr) {

@@ -718,6 +718,30 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor> BatchCSRRelabel(Tensor seeds, 
         "gsb_batch_unique_relabel");
   return {uniq.narrow(0, 0, nu), uniq_ptr, rel.narrow(0, 0, ne), ixp};
 }
+static std::vector<Tensor> SplitByOffset(Tensor data, Tensor offset) {  // src/tensor_ops.cc:33-45
+  Tensor sizes = (offset.slice(0, 1, offset.numel()) - offset.slice(0, 0, offset.numel() - 1)).to(torch::kCPU);
+  std::vector<int64_t> split(sizes.data_ptr<int64_t>(), sizes.data_ptr<int64_t>() + sizes.numel());
+  return torch::split_with_sizes(data, split);
+}
+static std::vector<Tensor> IndptrSplitByOffset(Tensor indptr_in, Tensor offsets_in) {  // src/cuda/batch_split.cu:66-97
+  Tensor indptr = Ids(indptr_in, "indptr"), offsets = Ids(offsets_in, "offsets");
+  const int64_t G = offsets.numel() - 1;
+  Tensor host = offsets.to(torch::kCPU);
+  const int64_t* h = host.data_ptr<int64_t>();
+  TORCH_CHECK(G >= 0 && (G == 0 || h[0] == 0), "offsets must start at 0");
+  Tensor out = EmptyIds(G ? h[G] + G : 0, indptr);
+  Check(gsb_split_indptr(Ctx(), Stream(), IP(indptr), IP(offsets), G, 0, MP(out)), "gsb_split_indptr");
+  std::vector<int64_t> split;
+  for (int64_t b = 0; b < G; ++b) split.push_back(h[b + 1] - h[b] + 1);
+  return torch::split_with_sizes(out, split);
+}
+static std::vector<Tensor> IndptrSplitBySize(Tensor indptr_in, int64_t size) {  // src/cuda/batch_split.cu:11-48
+  Tensor indptr = Ids(indptr_in, "indptr");
+  const int64_t G = (indptr.numel() - 1) / size;
+  Tensor out = EmptyIds(G * (size + 1), indptr);
+  Check(gsb_split_indptr(Ctx(), Stream(), IP(indptr), nullptr, G, size, MP(out)), "gsb_split_indptr");
+  return torch::split(out, size + 1);
+}
 static void SetSeed(int64_t seed) {
   g_seed_base.store((uint64_t)seed);
   g_seed_counter.store(0);
@@ -776,5 +800,10 @@ TORCH_LIBRARY(gs_ops, m) {
   m.def("_CAPI_Unique", &gsglue::Unique);
   m.def("_CAPI_BatchCSRRelabel", &gsglue::BatchCSRRelabel);
   m.def("BatchCSRRelabel", &gsglue::BatchCSRRelabel);
+  m.def("_CAPI_SplitByOffset", &gsglue::SplitByOffset);
+  m.def("SplitByOffset", &gsglue::SplitByOffset);
+  m.def("_CAPI_IndptrSplitByOffset", &gsglue::IndptrSplitByOffset);
+  m.def("IndptrSplitByOffset", &gsglue::IndptrSplitByOffset);
+  m.def("_CAPI_IndptrSplitBySize", &gsglue::IndptrSplitBySize);
   m.def("_CAPI_SetSeed", &gsglue::SetSeed);
 }

@@ -504,6 +504,37 @@ def batch_edge_offsets(sub_indptr, seeds_ptr, ctx=None):
     return out
 
 
+def split_by_offset(data, offsets):
+    """gs::SplitByOffset (src/tensor_ops.cc:33-45): views of `data` cut at `offsets` (one host read of the sizes)."""
+    sizes = (offsets[1:] - offsets[:-1]).tolist()
+    return list(torch.split(data, sizes))
+
+
+def indptr_split_by_offset(indptr, offsets, ctx=None):
+    """SplitIndptrByOffsetCUDA (src/cuda/batch_split.cu:66-97): per-batch offset arrays, each rebased to 0."""
+    indptr, offsets = _i64(indptr, "indptr"), _i64(offsets, "offsets")
+    ctx = ctx or default_context(indptr.device)
+    G = offsets.numel() - 1
+    host = offsets.tolist()
+    out = _empty(host[-1] - host[0] + G, indptr)
+    if host[0] != 0:
+        raise ValueError("offsets must start at 0")
+    ctx.check(ctx.lib.gsb_split_indptr(ctx.handle, _stream(), _p(indptr), _p(offsets), c_i64(G), c_i64(0), _p(out)),
+              "gsb_split_indptr")
+    return list(torch.split(out, [host[b + 1] - host[b] + 1 for b in range(G)]))
+
+
+def indptr_split_by_size(indptr, size, ctx=None):
+    """SplitIndptrBySizeCUDA (src/cuda/batch_split.cu:11-48): batches of `size` columns each."""
+    indptr = _i64(indptr, "indptr")
+    ctx = ctx or default_context(indptr.device)
+    G = (indptr.numel() - 1) // int(size)
+    out = _empty(G * (int(size) + 1), indptr)
+    ctx.check(ctx.lib.gsb_split_indptr(ctx.handle, _stream(), _p(indptr), _p(None), c_i64(G), c_i64(int(size)),
+                                       _p(out)), "gsb_split_indptr")
+    return list(torch.split(out, int(size) + 1))
+
+
 def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None):
     """Multi-hop GraphSAGE sampling of G minibatches at once (the loop of
     examples/graphsage/batching.py:56-90): per hop one fused slice+sample over the seeds of all batches,

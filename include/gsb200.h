@@ -258,6 +258,13 @@ GSB_API int gsb_coo2csc(gsb_ctx* ctx, void* stream, const int64_t* key, const in
  * a *_host pointer is given.
  * gsb_batch_edge_offsets: out_indices_ptr[b] = sub_indptr[seeds_ptr[b]] for b in [0, G].
  */
+/* gsb_split_indptr replaces gs::impl::SplitIndptrByOffsetCUDA / SplitIndptrBySizeCUDA
+ * (src/cuda/batch_split.cu:11-104; gs_ops._CAPI_IndptrSplitByOffset / _CAPI_IndptrSplitBySize): cuts one
+ * offset array into per-batch offset arrays that start at 0.  Batch b covers columns
+ * offsets[b] .. offsets[b+1] (offsets: DEVICE, G + 1 entries; NULL means b * uniform_size) and its
+ * (columns + 1) entries are written at out[offsets[b] + b ..]; `out` holds num_columns + G entries. */
+GSB_API int gsb_split_indptr(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* offsets, int64_t G,
+                             int64_t uniform_size, int64_t* out);
 GSB_API int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream, const int64_t* sub_indptr, const int64_t* seeds_ptr,
                                    int64_t G, int64_t* out_indices_ptr);
 GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* seeds, const int64_t* seeds_ptr,

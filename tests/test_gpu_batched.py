@@ -88,3 +88,26 @@ def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, fanouts):
             nxt.append(wu)
             nxt_ptr.append(nxt_ptr[-1] + len(wu))
         cur, cur_ptr = np.concatenate(nxt), np.array(nxt_ptr, dtype=np.int64)
+
+
+def test_split_helpers(ops):
+    """SplitByOffset / IndptrSplitByOffset / IndptrSplitBySize (reference src/tensor_ops.cc:33-45,
+    src/cuda/batch_split.cu): per-batch pieces of a super-batch result."""
+    rng = np.random.default_rng(4)
+    sizes = np.array([3, 0, 5, 1, 64, 33])
+    offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    deg = rng.integers(0, 9, offsets[-1])
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    parts = ops.indptr_split_by_offset(dev(indptr), dev(offsets))
+    assert len(parts) == len(sizes)
+    for b, p in enumerate(parts):
+        want = indptr[offsets[b]:offsets[b + 1] + 1] - indptr[offsets[b]]
+        assert np.array_equal(host(p), want)
+    indptr2 = np.concatenate([[0], np.cumsum(rng.integers(0, 5, 40))]).astype(np.int64)
+    parts = ops.indptr_split_by_size(dev(indptr2), 8)
+    assert len(parts) == 5
+    for b, p in enumerate(parts):
+        assert np.array_equal(host(p), indptr2[8 * b:8 * b + 9] - indptr2[8 * b])
+    data = dev(np.arange(offsets[-1], dtype=np.int64))
+    pieces = ops.split_by_offset(data, dev(offsets))
+    assert [len(x) for x in pieces] == sizes.tolist() and torch.equal(torch.cat(pieces), data)
