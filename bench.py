@@ -53,7 +53,7 @@ def parse():
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="sage", choices=["sage", "walk"],
-                    help="sage = the headline (BASELINE config 2); walk = uniform random walk (BASELINE config 4 shape)")
+                    help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale configuration)")
     ap.add_argument("--walkers", type=int, default=10_000_000)
     ap.add_argument("--walk-length", type=int, default=80)
     ap.add_argument("--walk-nodes", type=int, default=111_000_000)
@@ -380,7 +380,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": seconds_all / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
         "config": {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, "
-                               "relabel per hop (BASELINE config 2)",
+                               "relabel per hop (the products-scale configuration)",
                    "graph": info, "batch": BATCH, "fanouts": FANOUTS, "parallelism": f"replicated graph, dp{world}",
                    "l2": "inputs larger than L2: 1 GB of indices gathered at random, no flush",
                    "group": group,
@@ -417,7 +417,7 @@ def run_reference(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
             "impl": "reference",
             "config": {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, "
-                                   "relabel per hop (BASELINE config 2)", "graph": info, "batch": BATCH,
+                                   "relabel per hop (the products-scale configuration)", "graph": info, "batch": BATCH,
                        "fanouts": FANOUTS}}
     if os.path.exists(lib):
         torch.classes.load_library(lib)
@@ -481,7 +481,7 @@ def run_reference(args):
 
 
 def run_walk(args):
-    """Uniform random walk (BASELINE config 4 shape): one walker per distinct start node, walkers split into
+    """Uniform random walk (papers-scale configuration): one walker per distinct start node, walkers split into
     contiguous ranges over the ranks, int64 trace [walkers, length + 1].  A step here is one full pass over
     this rank's walkers.  Secondary workload: prints its own JSON line (metric walker_steps_per_second)."""
     import torch
@@ -540,7 +540,7 @@ def run_walk(args):
                           "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": seconds_all / steps * 1e3,
                           "higher_is_better": True, "scaling": "strong", "dtype": "int64", "data": "synthetic",
                           "impl": args.impl,
-                          "config": {"workload": "uniform random walk (BASELINE config 4 shape)", "graph": info,
+                          "config": {"workload": "uniform random walk (papers-scale configuration)", "graph": info,
                                      "walkers": args.walkers, "length": L, "layout": layout,
                                      "fraction_of_trace_alive": alive},
                           "roofline": {"bound": "hbm", "kernel": "k_random_walk", "achieved": round(ach, 2), "peak": peak,

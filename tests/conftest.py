@@ -35,7 +35,7 @@ def small_graph():
 
 @pytest.fixture(scope="session")
 def cfg1_graph():
-    """BASELINE config 1: 100,000 nodes, 2,000,000 directed edges."""
+    """Small GraphSAGE configuration: 100,000 nodes, 2,000,000 directed edges."""
     return make_graph(100_000, 2_000_000, seed=0x5EED + 1)
 
 

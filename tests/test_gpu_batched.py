@@ -60,7 +60,7 @@ def test_batch_with_empty_batches(ops, oracle):
 
 @pytest.mark.parametrize("fanouts", [[10, 5], [20, 3], [1, 16, 2]])
 def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, fanouts):
-    """BASELINE config 1 shape, 16 batches of 1,024 seeds at once: sampling equals the oracle's fused
+    """The 100k-node configuration, 16 batches of 1,024 seeds at once: sampling equals the oracle's fused
     sampler over the concatenated seeds (same Philox stream), relabel equals the per-batch oracle."""
     indptr, indices = cfg1_graph
     n = len(indptr) - 1

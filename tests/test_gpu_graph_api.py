@@ -180,7 +180,7 @@ def test_full_fixture_call_sequence(gs, gold):
 
 def test_graphsage_loop_matches_oracle(gs_py, oracle, cfg1_graph):
     gs = gs_py
-    """BASELINE config 1: 1,024 seeds, fanouts [10, 5], fused slice+sample then relabel per hop
+    """The 100k-node configuration: 1,024 seeds, fanouts [10, 5], fused slice+sample then relabel per hop
     (examples/graphsage/unbatching_training.py:19-28).  Same Philox seeds => identical frontiers."""
     indptr, indices = cfg1_graph
     A = gs.Matrix().load_csc(dev(indptr), dev(indices))
@@ -243,7 +243,7 @@ def test_matrix_api_ladies_layer(gs_py, oracle, cfg1_graph):
 
 def test_adaptive_sampling_hop(gs_py, oracle, cfg1_graph):
     gs = gs_py
-    """AS-GCN style hop (BASELINE config 5 at small scale): slice, u_dot_v / 16, per-column softmax,
+    """AS-GCN style hop (the adaptive-sampling configuration at small scale): slice, u_dot_v / 16, per-column softmax,
     weighted sampling without replacement (fanout 10), relabel."""
     indptr, indices = cfg1_graph
     rng = np.random.default_rng(3)
