@@ -52,7 +52,7 @@ def parse():
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="sage", choices=["sage", "walk"],
+    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels"],
                     help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale configuration)")
     ap.add_argument("--walkers", type=int, default=10_000_000)
     ap.add_argument("--walk-length", type=int, default=80)
@@ -549,9 +549,89 @@ def run_walk(args):
         dist.destroy_process_group()
 
 
+def run_kernels(args):
+    """Per-operator throughput on the products-scale graph: every operator of the hot path once, at a size that
+    fills the GPU, timed with CUDA events; achieved = algorithmic bytes / time against the measured HBM peak.
+    Secondary output (one JSON line with a list)."""
+    import torch
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    from graph_sampling_b200 import ops
+    from graph_sampling_b200.synthetic import rmat_csc
+    indptr, indices = rmat_csc(args.nodes, args.edges, seed=GRAPH_SEED, symmetric=True, max_degree=MAX_DEGREE,
+                               device=device)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    n = args.nodes
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+    g = torch.Generator(device=device)
+    g.manual_seed(1)
+    results = []
+
+    def timed(name, fn, alg_bytes, reps=10, note=""):
+        for _ in range(3):
+            out = fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        b = alg_bytes(out) if callable(alg_bytes) else alg_bytes
+        results.append({"op": name, "ms": round(ms, 4), "algorithmic_MB": round(b / 1e6, 1),
+                        "achieved_gbs": round(b / ms / 1e6, 1), "frac": round(b / ms / 1e6 / peak, 4), "note": note})
+        return out
+
+    S = 262_144
+    seeds = torch.randint(0, n, (S,), generator=g, device=device)
+    sl = timed("column slice (count + fill, COO out)", lambda: ops.csc_col_slicing(indptr, indices, seeds, True),
+               lambda o: 32 * S + 8 + 32 * o[2].numel(), note="includes one size read-back")
+    D = sl[2].numel()
+    big = torch.randint(0, n, (2_600_000,), generator=g, device=device)
+    timed("fused slice + uniform sample, fanout 10", lambda: ops.fused_csc_col_slicing_sampling(indptr, indices, big, 10, False),
+          lambda o: 32 * big.numel() + 8 + 24 * o[1].numel(), note="includes one size read-back")
+    sub_indptr, sub_col, sub_row = sl[0], sl[1], sl[2]
+    probs = torch.rand(D, generator=g, device=device) + 0.01
+    timed("weighted per-column sample, fanout 10", lambda: ops.csc_col_sampling_probs(sub_indptr, sub_row, probs, 10, False, with_coo=False),
+          lambda o: 32 * S + 8 + 4 * D + 24 * o[2].numel())
+    items = torch.cat([seeds, sub_row])
+    timed("unique + relabel (single table)", lambda: ops.relabel([seeds, sub_row], [sub_row]),
+          lambda o: 8 * items.numel() + 8 * o[0].numel() + 8 * D)
+    F = 256
+    x = torch.randn(n, F, generator=g, device=device)
+    xd = x[seeds]
+    out = torch.zeros(D, 1, device=device)
+    timed("SDDMM dot, F = 256", lambda: ops.sddmm("dot", x, xd, out, 0, 2, sub_row, sub_col), D * (4 * F + 20) + S * 4 * F)
+    w = torch.rand(D, generator=g, device=device)
+    o1 = torch.zeros(S, device=device)
+    timed("segment sum of squares (CSC)", lambda: ops.csc_sum(sub_indptr, None, w, o1, 2), 12 * D + 4 * S)
+    o2 = torch.zeros(n, device=device)
+    timed("segment sum of squares (COO, atomics)", lambda: ops.coo_sum(sub_row, None, w, o2, 2), 12 * D + 4 * n)
+    o3 = torch.empty(D, device=device)
+    timed("segment normalize (CSC)", lambda: ops.csc_normalize(sub_indptr, None, w, o3), 8 * D + 8 * (S + 1))
+    rows = torch.randperm(n, generator=g, device=device)[:100_000]
+    timed("row slice by membership (CSC)", lambda: ops.csc_row_slicing(sub_indptr, sub_row, rows, True),
+          lambda o: 8 * rows.numel() + 8 * D + 24 * o[2].numel())
+    timed("CSC -> COO", lambda: ops.csc2coo(sub_indptr, sub_row), 8 * (S + 1) + 8 * D)
+    timed("COO -> CSR (stable radix sort)", lambda: ops.coo2csc(sub_col, sub_row, n, False), 32 * D * 3 + 8 * n,
+          note="3 radix passes of 32 B per edge")
+    lp = torch.rand(1_000_000, generator=g, device=device)
+    lp[torch.rand(1_000_000, generator=g, device=device) < 0.5] = 0
+    ld = torch.arange(1_000_000, device=device)
+    timed("list sampling, 512 of 1 M weighted", lambda: ops.list_sampling(ld, 512, False, probs=lp), 12 * 1_000_000 + 16 * 512,
+          note="20 launches; latency bound")
+    print(json.dumps({"metric": "per_operator_roofline", "unit": "GB/s", "peak": peak, "graph": {"nodes": n, "edges": int(indices.numel())},
+                      "operators": results}))
+
+
 if __name__ == "__main__":
     a = parse()
-    if a.workload == "walk":
+    if a.workload == "kernels":
+        run_kernels(a)
+    elif a.workload == "walk":
         run_walk(a)
     elif a.impl == "reference":
         run_reference(a)
