@@ -52,6 +52,9 @@ def parse():
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--face", default="python", choices=["python", "torchscript"],
+                    help="with --group 1: drive the per-batch Graph API through the Python mirror or through the "
+                         "TorchScript library (lib/libgs.so)")
     ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels"],
                     help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale configuration)")
     ap.add_argument("--walkers", type=int, default=10_000_000)
@@ -295,6 +298,12 @@ def run_ours(args):
     ptr_cache = {}
     if group > 1:
         fn = lambda sb: sage_group(ops, indptr, indices, sb, ptr_cache)
+    elif args.face == "torchscript":
+        from graph_sampling_b200 import build as gsb_build
+        torch.classes.load_library(gsb_build.build_glue())
+        TS = torch.classes.gs_classes.Graph(False)
+        TS._CAPI_LoadCSC(indptr, indices)
+        fn = lambda sb: sage_batch_api(TS, sb[0], "_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_Relabel")
     else:
         fn = lambda sb: sage_batch_api(A, sb[0], "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
     for _ in range(3):  # size scratch before anything is timed

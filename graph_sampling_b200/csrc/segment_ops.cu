@@ -11,6 +11,10 @@
 namespace gsb {
 
 constexpr int kSegThreads = 256;
+// Segments longer than this are left to k_segment_long_* (one CTA per segment): with power-law degrees a
+// single hub column would otherwise keep one warp busy for hundreds of iterations while the rest of the
+// grid has long finished.
+constexpr i64 kLongSegment = 2048;
 
 __device__ __forceinline__ float int_pow(float x, i64 powk) {
   if (powk == 1) return x;
@@ -22,12 +26,17 @@ __device__ __forceinline__ float int_pow(float x, i64 powk) {
 __global__ void __launch_bounds__(kSegThreads) k_segment_sum_csc(const i64* __restrict__ indptr, i64 num_seg,
                                                                  const i64* __restrict__ e_ids,
                                                                  const float* __restrict__ data, i64 powk,
-                                                                 float* __restrict__ out) {
+                                                                 float* __restrict__ out, i64* long_list,
+                                                                 i64* long_count) {
   const int lane = threadIdx.x & 31;
   const i64 warp_global = ((i64)blockIdx.x * kSegThreads + threadIdx.x) >> 5;
   const i64 num_warps = ((i64)gridDim.x * kSegThreads) >> 5;
   for (i64 s = warp_global; s < num_seg; s += num_warps) {
     const i64 b = __ldg(indptr + s), e = __ldg(indptr + s + 1);
+    if (e - b > kLongSegment) {
+      if (lane == 0) long_list[atomicAdd((u64*)long_count, 1ull)] = s;
+      continue;
+    }
     float acc = 0.f;
     for (i64 j = b + lane; j < e; j += 32) {
       const float x = data ? __ldg(data + (e_ids ? __ldg(e_ids + j) : j)) : 1.0f;
@@ -49,15 +58,57 @@ __global__ void __launch_bounds__(kSegThreads) k_segment_sum_coo(const i64* __re
   }
 }
 
+// One CTA per long segment (taken from the list the warp kernels filled): strided partial sums, a fixed-order
+// shared-memory reduction (deterministic), then the result / the normalised values.
+template <bool NORMALIZE>
+__global__ void __launch_bounds__(kSegThreads) k_segment_long(const i64* __restrict__ indptr,
+                                                              const i64* __restrict__ e_ids,
+                                                              const float* __restrict__ data, i64 powk,
+                                                              float* __restrict__ out, const i64* __restrict__ long_list,
+                                                              const i64* __restrict__ long_count) {
+  __shared__ float s_part[kSegThreads];
+  const i64 n_long = *long_count;
+  for (i64 q = blockIdx.x; q < n_long; q += gridDim.x) {
+    const i64 s = long_list[q];
+    const i64 b = __ldg(indptr + s), e = __ldg(indptr + s + 1);
+    float acc = 0.f;
+    for (i64 j = b + threadIdx.x; j < e; j += kSegThreads) {
+      const float x = data ? __ldg(data + (e_ids ? __ldg(e_ids + j) : j)) : 1.0f;
+      acc += NORMALIZE ? x : int_pow(x, powk);
+    }
+    s_part[threadIdx.x] = acc;
+    __syncthreads();
+    for (int w = kSegThreads / 2; w > 0; w >>= 1) {
+      if (threadIdx.x < w) s_part[threadIdx.x] += s_part[threadIdx.x + w];
+      __syncthreads();
+    }
+    const float total = s_part[0];
+    if (NORMALIZE) {
+      for (i64 j = b + threadIdx.x; j < e; j += kSegThreads) {
+        const i64 p = e_ids ? __ldg(e_ids + j) : j;
+        out[p] = __ldg(data + p) / total;
+      }
+    } else if (threadIdx.x == 0) {
+      out[s] = total;
+    }
+    __syncthreads();
+  }
+}
+
 __global__ void __launch_bounds__(kSegThreads) k_segment_normalize_csc(const i64* __restrict__ indptr, i64 num_seg,
                                                                        const i64* __restrict__ e_ids,
                                                                        const float* __restrict__ data,
-                                                                       float* __restrict__ out) {
+                                                                       float* __restrict__ out, i64* long_list,
+                                                                       i64* long_count) {
   const int lane = threadIdx.x & 31;
   const i64 warp_global = ((i64)blockIdx.x * kSegThreads + threadIdx.x) >> 5;
   const i64 num_warps = ((i64)gridDim.x * kSegThreads) >> 5;
   for (i64 s = warp_global; s < num_seg; s += num_warps) {
     const i64 b = __ldg(indptr + s), e = __ldg(indptr + s + 1);
+    if (e - b > kLongSegment) {
+      if (lane == 0) long_list[atomicAdd((u64*)long_count, 1ull)] = s;
+      continue;
+    }
     float acc = 0.f;
     for (i64 j = b + lane; j < e; j += 32) acc += __ldg(data + (e_ids ? __ldg(e_ids + j) : j));
 #pragma unroll
@@ -74,6 +125,17 @@ static inline int warp_grid(i64 segments) {
   return (int)max((i64)1, min(blocks, (i64)kNumSMs * 16));
 }
 
+// Scratch for the list of long segments: [count | ids...] in the context arena, count zeroed on the stream.
+static int long_segment_scratch(gsb_ctx* ctx, cudaStream_t stream, i64 num_seg, i64** list, i64** count) {
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, sizeof(i64) * (size_t)(num_seg + 32), &ws);
+  if (st != GSB_OK) return st;
+  *count = (i64*)ws;
+  *list = (i64*)ws + 32;
+  GSB_CUDA_OK(cudaMemsetAsync(*count, 0, sizeof(i64), stream));
+  return GSB_OK;
+}
+
 }  // namespace gsb
 
 using namespace gsb;
@@ -85,10 +147,21 @@ int gsb_segment_sum_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int6
   GSB_REQUIRE(ctx && num_seg >= 0 && powk >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (num_seg == 0) return GSB_OK;
   GSB_REQUIRE(indptr && out, GSB_ERR_INVALID_ARGUMENT);
-  k_segment_sum_csc<<<warp_grid(num_seg), kSegThreads, 0, (cudaStream_t)stream_>>>(indptr, num_seg, e_ids, data, powk,
-                                                                                  out);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  i64 *long_list, *long_count;
+  int st = long_segment_scratch(ctx, stream, num_seg, &long_list, &long_count);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_SEGMENT, stream);
+    k_segment_sum_csc<<<warp_grid(num_seg), kSegThreads, 0, stream>>>(indptr, num_seg, e_ids, data, powk, out,
+                                                                      long_list, long_count);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
+  {
+    ScopedKernelTimer timer(ctx, KID_SEGMENT, stream);
+    k_segment_long<false><<<kNumSMs * 2, kSegThreads, 0, stream>>>(indptr, e_ids, data, powk, out, long_list, long_count);
+  }
+  GSB_LAUNCH_OK();
   return GSB_OK;
 }
 
@@ -109,10 +182,21 @@ int gsb_segment_normalize_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr
   GSB_REQUIRE(ctx && num_seg >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (num_seg == 0) return GSB_OK;
   GSB_REQUIRE(indptr && data && out, GSB_ERR_INVALID_ARGUMENT);
-  k_segment_normalize_csc<<<warp_grid(num_seg), kSegThreads, 0, (cudaStream_t)stream_>>>(indptr, num_seg, e_ids, data,
-                                                                                        out);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  i64 *long_list, *long_count;
+  int st = long_segment_scratch(ctx, stream, num_seg, &long_list, &long_count);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_SEGMENT, stream);
+    k_segment_normalize_csc<<<warp_grid(num_seg), kSegThreads, 0, stream>>>(indptr, num_seg, e_ids, data, out,
+                                                                            long_list, long_count);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
+  {
+    ScopedKernelTimer timer(ctx, KID_SEGMENT, stream);
+    k_segment_long<true><<<kNumSMs * 2, kSegThreads, 0, stream>>>(indptr, e_ids, data, 1, out, long_list, long_count);
+  }
+  GSB_LAUNCH_OK();
   return GSB_OK;
 }
 

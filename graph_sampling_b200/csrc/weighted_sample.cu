@@ -45,6 +45,8 @@ struct WeightedParams {
   TileState ts;
 };
 
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
 __device__ __forceinline__ bool ranks_before(float ka, i64 ia, float kb, i64 ib) {
   return ka > kb || (ka == kb && ia < ib);
 }
@@ -55,6 +57,65 @@ __device__ __forceinline__ void emit_weighted(const WeightedParams& p, i64 out_p
   if (p.out_coo_col) p.out_coo_col[out_pos] = col_pos;
   if (p.out_data) p.out_data[out_pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
 }
+
+// Warp-collective: every lane offers one candidate (key, edge position); the running top-k list (lane j holds
+// the j-th best, empty entries rank last) absorbs the candidates that beat its k-th entry, one at a time.
+__device__ __forceinline__ void topk_offer(float ck, i64 ci, bool valid, int k, unsigned kmask, float& my_key,
+                                           i64& my_idx, float& thr_key, i64& thr_idx) {
+  bool want = valid && ranks_before(ck, ci, thr_key, thr_idx);
+  unsigned pending = __ballot_sync(0xffffffffu, want);
+  while (pending) {
+    const int src = __ffs(pending) - 1;
+    pending &= pending - 1;
+    const float nk = __shfl_sync(0xffffffffu, ck, src);
+    const i64 ni = __shfl_sync(0xffffffffu, ci, src);
+    if (!ranks_before(nk, ni, thr_key, thr_idx)) continue;  // the threshold has moved past it
+    const bool mine_first = ranks_before(my_key, my_idx, nk, ni);
+    const int pos = __popc(__ballot_sync(0xffffffffu, mine_first) & kmask);
+    const float up_key = __shfl_up_sync(0xffffffffu, my_key, 1);
+    const i64 up_idx = __shfl_up_sync(0xffffffffu, my_idx, 1);
+    if (lane_id() > pos) {
+      my_key = up_key;
+      my_idx = up_idx;
+    } else if (lane_id() == pos) {
+      my_key = nk;
+      my_idx = ni;
+    }
+    thr_key = __shfl_sync(0xffffffffu, my_key, k - 1);
+    thr_idx = __shfl_sync(0xffffffffu, my_idx, k - 1);
+  }
+}
+
+// Top-k of the edges [e_begin, e_end) of one column, scanned by one warp.
+__device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, i64 b, i64 e_begin, i64 e_end, int k,
+                                          unsigned kmask, float& my_key, i64& my_idx) {
+  const float neg_inf = __uint_as_float(0xFF800000u);
+  my_key = neg_inf;
+  my_idx = 0x7fffffffffffffffll;
+  float thr_key = neg_inf;
+  i64 thr_idx = 0x7fffffffffffffffll;
+  // 128 edges per iteration: a lane evaluates ONE Philox block and uses its four words for four consecutive
+  // edges (edge e draws word e & 3 of block e >> 2), instead of four lanes computing the same block.
+  const i64 first_block = e_begin >> 2;
+  for (i64 blk0 = first_block; (blk0 << 2) < e_end; blk0 += 32) {
+    const i64 blk = blk0 + lane_id();
+    const i64 e4 = blk << 2;
+    U32x4 r;
+    if (e4 < e_end) r = rand_block(p.seed, (u64)col_pos, (u64)blk, STREAM_WEIGHTED);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const i64 e = e4 + q;
+      const bool valid = e >= e_begin && e < e_end;
+      float ck = neg_inf;
+      if (valid) ck = ares_key(r.v[q], __ldg(p.probs + b + e));
+      topk_offer(ck, e, valid, k, kmask, my_key, my_idx, thr_key, thr_idx);
+    }
+  }
+}
+
+// Columns longer than this are scanned by all warps of the CTA together (each warp a slice, lists merged
+// through shared memory): one hub column would otherwise occupy a single warp for hundreds of iterations.
+constexpr i64 kLongColumn = 2048;
 
 __global__ void __launch_bounds__(kWThreads) k_sample_weighted(WeightedParams p) {
   __shared__ i64 s_in[kWTileCols];
@@ -130,43 +191,38 @@ __global__ void __launch_bounds__(kWThreads) k_sample_weighted(WeightedParams p)
       for (i64 j = lane; j < d; j += 32) emit_weighted(p, o + j, b + j, col_pos);
       continue;
     }
-    // running top-k: lane j holds the j-th best (key, edge); empty entries rank last
-    float my_key = neg_inf;
-    i64 my_idx = 0x7fffffffffffffffll;
-    float thr_key = neg_inf;
-    i64 thr_idx = 0x7fffffffffffffffll;
-    for (i64 e0 = 0; e0 < d; e0 += 32) {
-      const i64 e = e0 + lane;
-      float ck = neg_inf;
-      bool want = false;
-      if (e < d) {
-        ck = ares_key(rand_u32(p.seed, (u64)col_pos, (u64)e, STREAM_WEIGHTED), __ldg(p.probs + b + e));
-        want = ranks_before(ck, e, thr_key, thr_idx);
-      }
-      unsigned pending = __ballot_sync(0xffffffffu, want);
-      while (pending) {
-        const int src = __ffs(pending) - 1;
-        pending &= pending - 1;
-        const float nk = __shfl_sync(0xffffffffu, ck, src);
-        const i64 ni = e0 + src;
-        if (!ranks_before(nk, ni, thr_key, thr_idx)) continue;  // threshold moved past it
-        // position = number of list entries that rank before the newcomer
-        const bool mine_first = ranks_before(my_key, my_idx, nk, ni);
-        const int pos = __popc(__ballot_sync(0xffffffffu, mine_first) & kmask);
-        const float up_key = __shfl_up_sync(0xffffffffu, my_key, 1);
-        const i64 up_idx = __shfl_up_sync(0xffffffffu, my_idx, 1);
-        if (lane > pos) {
-          my_key = up_key;
-          my_idx = up_idx;
-        } else if (lane == pos) {
-          my_key = nk;
-          my_idx = ni;
-        }
-        thr_key = __shfl_sync(0xffffffffu, my_key, (int)k - 1);
-        thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
-      }
-    }
+    if (d > kLongColumn) continue;  // handled by the whole CTA below
+    float my_key;
+    i64 my_idx;
+    topk_scan(p, col_pos, b, 0, d, (int)k, kmask, my_key, my_idx);
     if (lane < k) emit_weighted(p, o + lane, b + my_idx, col_pos);
+  }
+
+  if (p.replace) return;
+  // long columns: every warp scans a slice, warp 0 merges the per-warp lists
+  __shared__ float s_key[kWarps][32];
+  __shared__ i64 s_idx[kWarps][32];
+  for (int c = 0; c < ncol; ++c) {
+    const i64 d = s_deg[c];
+    if (d <= kLongColumn || d <= k) continue;  // uniform across the CTA
+    const i64 b = s_in[c], o = tile_base + s_off[c], col_pos = base + c;
+    const i64 chunk = (((d + kWarps - 1) / kWarps) + 31) & ~(i64)31;
+    const i64 e_begin = min(d, (i64)warp * chunk), e_end = min(d, (i64)(warp + 1) * chunk);
+    float my_key;
+    i64 my_idx;
+    topk_scan(p, col_pos, b, e_begin, e_end, (int)k, kmask, my_key, my_idx);
+    s_key[warp][lane] = my_key;
+    s_idx[warp][lane] = my_idx;
+    __syncthreads();
+    if (warp == 0) {
+      float thr_key = __shfl_sync(0xffffffffu, my_key, (int)k - 1);
+      i64 thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
+      for (int w = 1; w < kWarps; ++w)
+        topk_offer(s_key[w][lane], s_idx[w][lane], lane < k && s_idx[w][lane] != 0x7fffffffffffffffll, (int)k, kmask,
+                   my_key, my_idx, thr_key, thr_idx);
+      if (lane < k) emit_weighted(p, o + lane, b + my_idx, col_pos);
+    }
+    __syncthreads();
   }
 }
 
