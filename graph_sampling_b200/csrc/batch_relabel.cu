@@ -395,6 +395,13 @@ __global__ void __launch_bounds__(kBThreads) k_split_indptr(const i64* __restric
   }
 }
 
+__global__ void k_set_single_batch_ptrs(i64* seeds_ptr, i64* indices_ptr, i64 S, i64 E) {
+  seeds_ptr[0] = 0;
+  seeds_ptr[1] = S;
+  indices_ptr[0] = 0;
+  indices_ptr[1] = E;
+}
+
 }  // namespace gsb
 
 using namespace gsb;
@@ -576,3 +583,75 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
 }
 
 }  // extern "C"
+
+namespace gsb {
+
+// unique(cat(first, second)) + relabel of `second` through the batched kernels with one batch (8-byte
+// slots, warp tiles).  Only valid for ids below 2^32 - 1: a larger id makes the kernels record
+// GSB_ERR_INDEX_RANGE, which the caller sees after the read-back and answers by using the wide-slot path.
+int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i64 S, const i64* second, i64 E,
+                          i64* out_unique, i64* out_relabeled, i64* unique_host) {
+  void* ws;
+  const i64 n_cap = S + E;
+  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 + 64;
+  const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
+  int st = ctx_reserve_workspace(ctx, slots_bytes + 4 * 256, &ws);
+  if (st != GSB_OK) return st;
+  BatchLayout L;
+  L.seeds = first;
+  L.indices = second;
+  L.G = 1;
+  L.slots = (u64*)ws;
+  char* tail = (char*)ws + slots_bytes;
+  L.item_off = (i64*)tail;
+  L.region_off = (i64*)(tail + 256);
+  i64* seeds_ptr = (i64*)(tail + 512);
+  i64* indices_ptr = (i64*)(tail + 768);
+  L.seeds_ptr = seeds_ptr;
+  L.indices_ptr = indices_ptr;
+  L.slot_capacity = slot_cap;
+  i64* counters = ctx_counters(ctx);
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
+    GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
+  }
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_set_single_batch_ptrs<<<1, 1, 0, stream>>>(seeds_ptr, indices_ptr, S, E);
+  }
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
+  }
+  GSB_LAUNCH_OK();
+  const int wide = kNumSMs * 8;
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
+    k_batch_insert<1><<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
+  }
+  GSB_LAUNCH_OK();
+  const int tiles = grid_for(n_cap, kBTile);
+  TileState ts;
+  st = ctx_tile_state(ctx, tiles, stream, &ts);
+  if (st != GSB_OK) return st;
+  // unique_ptr[0..1] lives in scratch: nobody needs it here
+  CompactOut out{out_unique, L.item_off + 8};
+  {
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_batch_compact<<<tiles, kBThreads, 0, stream>>>(L, out, counters, ts);
+  }
+  GSB_LAUNCH_OK();
+  if (E > 0 && out_relabeled) {
+    ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
+    k_batch_relabel<<<max(1, min(grid_for(E, kBTile), wide)), kBThreads, 0, stream>>>(L, L.item_off + 8, out_relabeled);
+  }
+  GSB_LAUNCH_OK();
+  const i64* c;
+  st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
+  if (st != GSB_OK) return st;
+  *unique_host = c[CNT_UNIQUE];
+  if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  return GSB_OK;
+}
+
+}  // namespace gsb

@@ -63,6 +63,10 @@ __device__ __forceinline__ i64 batch_of(const i64* __restrict__ off, i64 G, i64 
   return lo;
 }
 
+// Single-batch unique + relabel through the packed-slot batched kernels (defined in batch_relabel.cu).
+int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i64 S, const i64* second, i64 E,
+                          i64* out_unique, i64* out_relabeled, i64* unique_host);
+
 // Uniform sampler shared by gsb_sample_uniform and the batched hop (defined in slice_sample.cu).
 int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
                           i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,

@@ -9,6 +9,7 @@
 //
 // This is the three-pass structure of the reference (Unique / Relabel, src/cuda/unique_reindex.cu:80-172)
 // with its separate flag array, cub scan, blocking size read and value table folded away.
+#include "batch_table.cuh"
 #include "common.cuh"
 #include "hash_table.cuh"
 #include "scan.cuh"
@@ -159,6 +160,23 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
   const i64 m = num_relabel > 0 ? rel.start[rel.n] : 0;
   GSB_REQUIRE(n == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(n < (1ll << 40), GSB_ERR_UNSUPPORTED);
+
+  // Fast path for the shapes gs::Graph produces — unique(cat(a, b)) with b (or nothing) relabelled, or
+  // unique(a) with a relabelled: 8-byte slots and warp-tile kernels, valid for ids below 2^32 - 1.  It needs
+  // the read-back (to learn whether an id was too large); if one was, the wide-slot path below redoes the call.
+  if (unique_host && n > 0 && n < (1ll << 30) && num_item_arrays <= 2 && num_relabel <= 1) {
+    const i64* last = item_ptrs_host[num_item_arrays - 1];
+    const i64 last_len = item_lens_host[num_item_arrays - 1];
+    const bool rel_ok = num_relabel == 0 || (relabel_ptrs_host[0] == last && relabel_lens_host[0] == last_len);
+    if (rel_ok) {
+      const i64* first = num_item_arrays == 2 ? item_ptrs_host[0] : nullptr;
+      const i64 S = num_item_arrays == 2 ? item_lens_host[0] : 0;
+      st = unique_relabel_packed(ctx, stream, first, S, last, last_len, out_unique,
+                                 num_relabel ? out_relabel_ptrs_host[0] : nullptr, unique_host);
+      if (st != GSB_ERR_INDEX_RANGE) return st;
+      // an id >= 2^32 - 1 (or a negative one, which the wide path reports again): fall through
+    }
+  }
 
   Table table;
   u64 cap;

@@ -175,6 +175,30 @@ def test_unique_large_ids(ops, oracle):
     assert np.array_equal(wu, host(gu)) and np.array_equal(wr, host(gr))
 
 
+@pytest.mark.parametrize("n_items", [1, 127, 128, 129, 4097, 300_000])
+@pytest.mark.parametrize("big", [False, True])
+def test_relabel_graph_shapes(ops, oracle, n_items, big):
+    """The shapes gs::Graph::Relabel produces (the relabelled array IS the last mapping array) take the
+    packed-slot kernels; an id at or above 2^32 - 1 sends the same call to the wide-slot kernels."""
+    rng = np.random.default_rng(n_items + big)
+    hi = max(2, n_items // 2)
+    a = rng.integers(0, hi, max(1, n_items // 5)).astype(np.int64)
+    b = rng.integers(0, hi * 3, n_items).astype(np.int64)
+    if big:
+        b[rng.integers(0, n_items)] = (1 << 32) - 1
+        b[rng.integers(0, n_items)] = 1 << 45
+    da, db = dev(a), dev(b)
+    wu, (wr,) = oracle.unique_relabel([a, b], [b])
+    gu, (gr,) = ops.relabel([da, db], [db])
+    assert np.array_equal(wu, host(gu)) and np.array_equal(wr, host(gr))
+    wu, (wr,) = oracle.unique_relabel([b], [b])
+    gu, (gr,) = ops.relabel([db], [db])
+    assert np.array_equal(wu, host(gu)) and np.array_equal(wr, host(gr))
+    gu, _ = ops.relabel([da, db], [])
+    assert np.array_equal(oracle.unique_relabel([a, b], [])[0], host(gu))
+    assert np.array_equal(oracle.unique_relabel([b], [])[0], host(ops.tensor_unique(db)))
+
+
 @pytest.mark.parametrize("layout", [0, 1])
 @pytest.mark.parametrize("W,L", [(1, 1), (33, 4), (1000, 80), (5000, 17)])
 def test_random_walk_matches_oracle(ops, oracle, layout, W, L):
