@@ -19,6 +19,7 @@
 // arrays per table, three passes with separate prefix-sum calls and a host round trip per pass.
 #include "batch_table.cuh"
 #include "common.cuh"
+#include "radix_sort.cuh"
 #include "scan.cuh"
 
 namespace gsb {
@@ -395,6 +396,125 @@ __global__ void __launch_bounds__(kBThreads) k_split_indptr(const i64* __restric
   }
 }
 
+// ---- kernels of the other table-based super-batch operators ---------------------------------------
+
+// Batch number of every frontier entry (the `key` output of BatchUnique).
+__global__ void __launch_bounds__(kBThreads) k_unique_keys(const i64* __restrict__ unique_ptr, i64 G,
+                                                           i64* __restrict__ out_key) {
+  const i64 u = unique_ptr[G];
+  for (i64 i = (i64)blockIdx.x * kBThreads + threadIdx.x; i < u; i += (i64)gridDim.x * kBThreads)
+    out_key[i] = batch_of(unique_ptr, G, i);
+}
+
+// (batch << 32 | id) sort keys of the frontier entries, for the sorted flavour of BatchUnique.
+__global__ void __launch_bounds__(kBThreads) k_unique_sort_keys(const i64* __restrict__ unique,
+                                                                const i64* __restrict__ unique_ptr, i64 G,
+                                                                u64* __restrict__ keys, i64* __restrict__ vals) {
+  const i64 u = unique_ptr[G];
+  for (i64 i = (i64)blockIdx.x * kBThreads + threadIdx.x; i < u; i += (i64)gridDim.x * kBThreads) {
+    keys[i] = ((u64)batch_of(unique_ptr, G, i) << 32) | (u64)__ldg(unique + i);
+    vals[i] = i;
+  }
+}
+
+__global__ void __launch_bounds__(kBThreads) k_unique_from_keys(const u64* __restrict__ keys, i64 u,
+                                                                i64* __restrict__ unique) {
+  for (i64 i = (i64)blockIdx.x * kBThreads + threadIdx.x; i < u; i += (i64)gridDim.x * kBThreads)
+    unique[i] = (i64)(keys[i] & 0xFFFFFFFFull);
+}
+
+// Per-batch membership filter of COO edges: edge i (batch b by edge_ptr) survives when target[i] is in
+// the table region of batch b.  Survivors keep their order; out_ptr[b] = number of survivors in front of
+// batch b.  Same tile geometry and ranking as k_batch_compact.
+struct FilterParams {
+  const i64* target;
+  const i64* row;
+  const i64* col;
+  const i64* edge_ptr;  // [G + 1]
+  i64 E;
+  i64* out_row;
+  i64* out_col;
+  i64* out_ptr;  // [G + 1]
+};
+
+__global__ void __launch_bounds__(kBThreads) k_batch_filter(BatchLayout L, FilterParams p, i64* counters,
+                                                            TileState ts) {
+  __shared__ i64 s_warp_total[kBThreads / 32];
+  __shared__ i64 s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tile = blockIdx.x;
+  const i64 tile_base = (i64)tile * kBTile;
+  if (tile_base >= p.E && !(p.E == 0 && tile == 0)) return;
+  const i64 base = tile_base + (i64)warp * kWarpItems;
+  const i64 end = min(p.E, base + kWarpItems);
+  bool keep[kLaneItems];
+  i64 batch[kLaneItems];
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    keep[q] = false;
+    batch[q] = 0;
+    const i64 g = base + q * 32 + lane;
+    if (g < end) {
+      const i64 b = batch_of(p.edge_ptr, L.G, g);
+      batch[q] = b;
+      const i64 node = __ldg(p.target + g);
+      if (valid_id(node)) {
+        const i64 ro = __ldg(L.region_off + b);
+        u64* region = L.slots + ro;
+        const i64 size = __ldg(L.region_off + b + 1) - ro;
+        const i64 h = home_slot(node, size);
+        u64 word;
+        keep[q] = find_from(region, size, h, region[h], node, &word) != nullptr;
+      }
+    }
+  }
+  const unsigned lt = (1u << lane) - 1u;
+  unsigned rank[kLaneItems];
+  unsigned run = 0;
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    const unsigned bal = __ballot_sync(0xffffffffu, keep[q]);
+    rank[q] = run + __popc(bal & lt);
+    run += __popc(bal);
+  }
+  if (lane == 0) s_warp_total[warp] = run;
+  __syncthreads();
+  i64 warp_excl = 0, tile_total = 0;
+#pragma unroll
+  for (int x = 0; x < kBThreads / 32; ++x) {
+    const i64 t = s_warp_total[x];
+    if (x < warp) warp_excl += t;
+    tile_total += t;
+  }
+  if (warp == 0) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, tile_total);
+    if (lane == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const i64 warp_pos = s_base + warp_excl;
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    const i64 g = base + q * 32 + lane;
+    if (g < end) {
+      const i64 pos = warp_pos + rank[q];
+      if (g == __ldg(p.edge_ptr + batch[q])) {
+        p.out_ptr[batch[q]] = pos;
+        for (i64 e = batch[q] - 1; e >= 0 && __ldg(p.edge_ptr + e) == g; --e) p.out_ptr[e] = pos;
+      }
+      if (keep[q]) {
+        p.out_row[pos] = __ldg(p.row + g);
+        p.out_col[pos] = __ldg(p.col + g);
+      }
+    }
+  }
+  if (tile_base + kBTile >= p.E && threadIdx.x == 0) {
+    const i64 total = s_base + tile_total;
+    p.out_ptr[L.G] = total;
+    for (i64 e = L.G - 1; e >= 0 && __ldg(p.edge_ptr + e) == p.E; --e) p.out_ptr[e] = total;
+    counters[CNT_NNZ] = total;
+  }
+}
+
 __global__ void k_set_single_batch_ptrs(i64* seeds_ptr, i64* indices_ptr, i64 S, i64 E) {
   seeds_ptr[0] = 0;
   seeds_ptr[1] = S;
@@ -580,6 +700,204 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
     if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
   }
   return GSB_OK;
+}
+
+}  // extern "C"
+
+namespace gsb {
+
+// ---- shared host sequence -------------------------------------------------------------------------
+// clear -> layout -> insert [-> compact]: afterwards the tables stay valid in the context workspace until
+// the next call that reserves it, so the callers below can run their look-up kernels against them.
+// indices_ptr == nullptr means "no second array": a zeroed offset array is placed in the workspace.
+// `extra_bytes` more workspace is returned through `extra` (placed after everything else).
+static int build_batch_tables(gsb_ctx* ctx, cudaStream_t stream, const i64* seeds, const i64* seeds_ptr, i64 num_seeds,
+                              const i64* indices, const i64* indices_ptr, i64 indices_capacity, i64 G,
+                              i64* out_unique, i64* out_unique_ptr, BatchLayout* out_layout, size_t extra_bytes,
+                              void** extra) {
+  const i64 n_cap = num_seeds + indices_capacity;
+  GSB_REQUIRE(n_cap < (1ll << 31), GSB_ERR_UNSUPPORTED);
+  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 * G + 64;
+  const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
+  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, slots_bytes + 3 * off_bytes + 256 + extra_bytes, &ws);
+  if (st != GSB_OK) return st;
+  BatchLayout L;
+  L.seeds = seeds;
+  L.seeds_ptr = seeds_ptr;
+  L.indices = indices;
+  L.G = G;
+  L.slots = (u64*)ws;
+  L.item_off = (i64*)((char*)ws + slots_bytes);
+  L.region_off = (i64*)((char*)ws + slots_bytes + off_bytes);
+  i64* zero_ptr = (i64*)((char*)ws + slots_bytes + 2 * off_bytes);
+  i64* single_ptr = (i64*)((char*)ws + slots_bytes + 3 * off_bytes);
+  if (extra) *extra = (char*)ws + slots_bytes + 3 * off_bytes + 256;
+  L.indices_ptr = indices_ptr ? indices_ptr : zero_ptr;
+  if (!seeds_ptr) {  // one batch holding all seeds
+    GSB_REQUIRE(G == 1, GSB_ERR_INVALID_ARGUMENT);
+    k_set_single_batch_ptrs<<<1, 1, 0, stream>>>(single_ptr, single_ptr + 2, num_seeds, 0);
+    GSB_LAUNCH_OK();
+    ctx_count_launches(ctx, 1);
+    L.seeds_ptr = single_ptr;
+  }
+  L.slot_capacity = slot_cap;
+  i64* counters = ctx_counters(ctx);
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
+    GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
+  }
+  if (!indices_ptr) GSB_CUDA_OK(cudaMemsetAsync(zero_ptr, 0, off_bytes, stream));
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
+  }
+  GSB_LAUNCH_OK();
+  const int wide = kNumSMs * 8;
+  {
+    ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
+    k_batch_insert<1><<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
+  }
+  GSB_LAUNCH_OK();
+  if (out_unique_ptr) {
+    const int tiles = grid_for(n_cap, kBTile);
+    TileState ts;
+    st = ctx_tile_state(ctx, tiles, stream, &ts);
+    if (st != GSB_OK) return st;
+    CompactOut out{out_unique, out_unique_ptr};
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_batch_compact<<<tiles, kBThreads, 0, stream>>>(L, out, counters, ts);
+    GSB_LAUNCH_OK();
+  }
+  *out_layout = L;
+  return GSB_OK;
+}
+
+static int read_totals(gsb_ctx* ctx, cudaStream_t stream, i64* unique_total_host, i64* edges_total_host) {
+  const i64* c;
+  int st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
+  if (st != GSB_OK) return st;
+  if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
+  if (edges_total_host) *edges_total_host = c[CNT_NNZ];
+  if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+  return GSB_OK;
+}
+
+}  // namespace gsb
+
+extern "C" {
+
+int gsb_batch_unique(gsb_ctx* ctx, void* stream_, const int64_t* data, const int64_t* data_ptr, int64_t n, int64_t G,
+                     int sorted, int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_unique_key,
+                     int64_t* unique_total_host) {
+  GSB_REQUIRE(ctx && data_ptr && out_unique_ptr && G >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(n == 0 || (data && out_unique), GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(!sorted || unique_total_host, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  BatchLayout L;
+  const size_t pair_bytes = ((size_t)n * 8 + 255) & ~(size_t)255;
+  const size_t extra = sorted ? 2 * pair_bytes + radix_sort_scratch_bytes(n) : 0;
+  void* extra_ws = nullptr;
+  int st = build_batch_tables(ctx, stream, data, data_ptr, n, nullptr, nullptr, 0, G, out_unique, out_unique_ptr, &L,
+                              extra, &extra_ws);
+  if (st != GSB_OK) return st;
+  const int wide = kNumSMs * 8;
+  const int grid = max(1, min(grid_for(n, kBThreads), wide));
+  if (out_unique_key && n > 0) {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_unique_keys<<<grid, kBThreads, 0, stream>>>(out_unique_ptr, G, out_unique_key);
+    GSB_LAUNCH_OK();
+  }
+  if (!sorted) return unique_total_host ? read_totals(ctx, stream, unique_total_host, nullptr) : GSB_OK;
+  st = read_totals(ctx, stream, unique_total_host, nullptr);
+  if (st != GSB_OK) return st;
+  const i64 u = *unique_total_host;
+  if (u <= 1) return GSB_OK;
+  u64* keys = (u64*)extra_ws;
+  i64* vals = (i64*)((char*)extra_ws + pair_bytes);
+  void* sort_ws = (char*)extra_ws + 2 * pair_bytes;
+  {
+    ScopedKernelTimer timer(ctx, KID_SORT, stream);
+    k_unique_sort_keys<<<grid, kBThreads, 0, stream>>>(out_unique, out_unique_ptr, G, keys, vals);
+  }
+  GSB_LAUNCH_OK();
+  int gbits = 0;
+  while (((i64)1 << gbits) < G) ++gbits;
+  st = radix_sort_pairs(ctx, stream, keys, vals, u, 0, 32 + gbits, sort_ws);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_SORT, stream);
+    k_unique_from_keys<<<grid, kBThreads, 0, stream>>>(keys, u, out_unique);
+  }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int gsb_batch_coo_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, const int64_t* seeds_ptr,
+                          int64_t num_seeds, const int64_t* coo_col, const int64_t* coo_row, const int64_t* coo_ptr,
+                          int64_t num_edges, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_row,
+                          int64_t* out_col, int64_t* unique_total_host) {
+  GSB_REQUIRE(ctx && seeds_ptr && coo_ptr && out_unique_ptr && G >= 1 && num_seeds >= 0 && num_edges >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(num_edges == 0 || (coo_col && coo_row && out_row && out_col), GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(num_seeds + num_edges == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  BatchLayout L;
+  int st = build_batch_tables(ctx, stream, seeds, seeds_ptr, num_seeds, coo_row, coo_ptr, num_edges, G, out_unique,
+                              out_unique_ptr, &L, 0, nullptr);
+  if (st != GSB_OK) return st;
+  if (num_edges > 0) {
+    const int grid = max(1, min(grid_for(num_edges, kBTile), kNumSMs * 8));
+    {
+      ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
+      k_batch_relabel<<<grid, kBThreads, 0, stream>>>(L, out_unique_ptr, out_row);
+    }
+    GSB_LAUNCH_OK();
+    L.indices = coo_col;
+    {
+      ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
+      k_batch_relabel<<<grid, kBThreads, 0, stream>>>(L, out_unique_ptr, out_col);
+    }
+    GSB_LAUNCH_OK();
+  }
+  return unique_total_host ? read_totals(ctx, stream, unique_total_host, nullptr) : GSB_OK;
+}
+
+int gsb_batch_coo_slice(gsb_ctx* ctx, void* stream_, int axis, const int64_t* coo_row, const int64_t* coo_col,
+                        const int64_t* edge_ptr, int64_t num_edges, const int64_t* members, const int64_t* members_ptr,
+                        int64_t num_members, int64_t G, int64_t* out_row, int64_t* out_col, int64_t* out_ptr,
+                        int64_t* n_out_host) {
+  GSB_REQUIRE(ctx && G >= 1 && num_edges >= 0 && num_members >= 0 && out_ptr && (axis == 0 || axis == 1),
+              GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE((edge_ptr && members_ptr) || (G == 1 && !edge_ptr && !members_ptr), GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(num_edges == 0 || (coo_row && coo_col && out_row && out_col), GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(num_members == 0 || members, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  BatchLayout L;
+  void* extra = nullptr;
+  int st = build_batch_tables(ctx, stream, members, members_ptr, num_members, nullptr, nullptr, 0, G, nullptr, nullptr,
+                              &L, 256, &extra);
+  if (st != GSB_OK) return st;
+  i64* counters = ctx_counters(ctx);
+  if (!edge_ptr) {
+    i64* one = (i64*)extra;
+    k_set_single_batch_ptrs<<<1, 1, 0, stream>>>(one, one + 2, num_edges, 0);
+    GSB_LAUNCH_OK();
+    ctx_count_launches(ctx, 1);
+    edge_ptr = one;
+  }
+  FilterParams p{axis == 0 ? coo_col : coo_row, coo_row, coo_col, edge_ptr, num_edges, out_row, out_col, out_ptr};
+  const int tiles = grid_for(num_edges, kBTile);
+  TileState ts;
+  st = ctx_tile_state(ctx, tiles, stream, &ts);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_ROW_FILTER, stream);
+    k_batch_filter<<<tiles, kBThreads, 0, stream>>>(L, p, counters, ts);
+  }
+  GSB_LAUNCH_OK();
+  return n_out_host ? read_totals(ctx, stream, nullptr, n_out_host) : GSB_OK;
 }
 
 }  // extern "C"

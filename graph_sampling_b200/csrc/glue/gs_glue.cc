@@ -7,7 +7,7 @@
 // Every piece of arithmetic goes through the C ABI of gsb200.h with raw device pointers and torch's current
 // stream.  The state kept per graph and the effect of each method on it follow gs::Graph
 // (src/graph.h:113-126, src/graph.cc).  Where the reference aborts the process (LOG(FATAL)), TORCH_CHECK
-// raises instead.  Compact-id (DCSC/DCSR), batched and induced-subgraph methods are not provided.
+// raises instead.  Compact-id (DCSC/DCSR) and induced-subgraph methods are not provided.
 #include <c10/cuda/CUDAStream.h>
 #include <torch/custom_class.h>
 #include <torch/script.h>
@@ -424,6 +424,58 @@ class Graph : public torch::CustomClassHolder {
     return ret;
   }
 
+  // BatchSlicing (src/graph.cc:312-391): column slice for the seeds of many batches at once.
+  std::tuple<c10::intrusive_ptr<Graph>, Tensor> BatchSlicing(Tensor n_ids_in, Tensor nid_ptr_in, int64_t axis,
+                                                             int64_t on_format, int64_t output_format, bool relabel,
+                                                             bool encoding) {
+    TORCH_CHECK(axis == 0, "batch slicing only suppurt column slicing now");
+    TORCH_CHECK(on_format == kCSC, "Not Implementatin Error");
+    CreateSparseFormat(on_format);
+    Tensor n_ids = Ids(n_ids_in, "node ids"), nid_ptr = Ids(nid_ptr_in, "nid_ptr");
+    const bool with_coo = output_format & kCOO;
+    const int64_t S = n_ids.numel(), G = nid_ptr.numel() - 1;
+    OptTensor new_col_ids, new_row_ids = row_ids_;
+    if (col_ids_.has_value()) {
+      new_col_ids = col_ids_.value().index({n_ids});
+    } else {
+      Tensor enc = EmptyIds(S, n_ids);
+      Check(gsb_batch_encode(Ctx(), Stream(), IP(n_ids), IP(nid_ptr), G, S, num_rows_, MP(enc)), "gsb_batch_encode");
+      new_col_ids = enc;
+    }
+    int64_t new_rows = num_rows_ * G;
+    const CSC& g = *csc_;
+    Tensor sub_indptr = EmptyIds(S + 1, g.indptr);
+    int64_t nnz = 0;
+    Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), IP(n_ids), S, MP(sub_indptr), &nnz), "gsb_col_slice_count");
+    Tensor indices = EmptyIds(nnz, g.indptr), select = EmptyIds(nnz, g.indptr), offsets = EmptyIds(G + 1, g.indptr);
+    Tensor coo_col = with_coo ? EmptyIds(nnz, g.indptr) : Tensor();
+    Tensor out_data;
+    const float* data_in = nullptr;
+    float* data_out = nullptr;
+    if (data_.has_value()) {
+      out_data = torch::empty({nnz}, data_.value().options());
+      data_in = FP(data_.value());
+      data_out = nnz ? out_data.data_ptr<float>() : nullptr;
+    }
+    Tensor eids = g.e_ids.value_or(Tensor());
+    Check(gsb_batch_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(n_ids), S, IP(nid_ptr), G,
+                                   encoding ? num_rows_ : 0, IP(sub_indptr), MP(indices), MP(select), MP(coo_col),
+                                   MP(offsets), data_in, IP(eids), data_out),
+          "gsb_batch_col_slice_fill");
+    if (relabel) {
+      auto res = Relabel({indices}, {indices});
+      indices = std::get<1>(res)[0];
+      new_row_ids = std::get<0>(res);
+      new_rows = std::get<0>(res).numel();
+    }
+    auto ret = c10::make_intrusive<Graph>(true, new_col_ids, new_row_ids, S, new_rows);
+    ret->num_edges_ = nnz;
+    if (output_format & kCSC) ret->csc_ = std::make_shared<CSC>(CSC{sub_indptr, indices, torch::nullopt});
+    if (with_coo) ret->coo_ = std::make_shared<COO>(COO{indices, coo_col, torch::nullopt, false, true});
+    if (out_data.defined()) ret->data_ = out_data;
+    return {ret, offsets};
+  }
+
   // Sampling / SamplingProbs (src/graph.cc:393-529)
   c10::intrusive_ptr<Graph> SampleImpl(int64_t axis, const Tensor* probs, int64_t fanout, bool replace,
                                        int64_t on_format, int64_t output_format) {
@@ -742,6 +794,138 @@ static std::vector<Tensor> IndptrSplitBySize(Tensor indptr_in, int64_t size) {  
   Check(gsb_split_indptr(Ctx(), Stream(), IP(indptr), nullptr, G, size, MP(out)), "gsb_split_indptr");
   return torch::split(out, size + 1);
 }
+// ---- the rest of the super-batch family (src/pybind.cc:65-84) ---------------------------------------------------
+static Tensor BatchEncode(Tensor data_in, Tensor ptr_in, int64_t encoding_size) {
+  Tensor data = Ids(data_in, "data"), ptr = Ids(ptr_in, "data_ptr");
+  Tensor out = torch::empty_like(data);
+  Check(gsb_batch_encode(Ctx(), Stream(), IP(data), IP(ptr), ptr.numel() - 1, data.numel(), encoding_size, MP(out)),
+        "gsb_batch_encode");
+  return out;
+}
+static Tensor BatchDecode(Tensor data_in, int64_t encoding_size) {
+  Tensor data = Ids(data_in, "data");
+  Tensor out = torch::empty_like(data);
+  Check(gsb_batch_decode(Ctx(), Stream(), IP(data), data.numel(), encoding_size, MP(out)), "gsb_batch_decode");
+  return out;
+}
+static std::tuple<Tensor, Tensor> GetBatchOffsets(Tensor data_in, int64_t num_batches, int64_t encoding_size) {
+  Tensor data = Ids(data_in, "data");
+  Tensor ptr = EmptyIds(num_batches + 1, data), dec = torch::empty_like(data);
+  Check(gsb_get_batch_offsets(Ctx(), Stream(), IP(data), data.numel(), num_batches, encoding_size, MP(ptr), MP(dec)),
+        "gsb_get_batch_offsets");
+  return {ptr, dec};
+}
+static std::tuple<Tensor, Tensor, Tensor> BatchUniqueImpl(Tensor data_in, Tensor ptr_in, bool sorted) {
+  Tensor data = Ids(data_in, "data"), ptr = Ids(ptr_in, "data_ptr");
+  const int64_t n = data.numel(), G = ptr.numel() - 1;
+  Tensor uniq = EmptyIds(n, data), key = EmptyIds(n, data), uptr = EmptyIds(G + 1, data);
+  int64_t nu = 0;
+  Check(gsb_batch_unique(Ctx(), Stream(), IP(data), IP(ptr), n, G, sorted ? 1 : 0, MP(uniq), MP(uptr), MP(key), &nu),
+        "gsb_batch_unique");
+  return {uniq.narrow(0, 0, nu), uptr, key.narrow(0, 0, nu)};
+}
+static std::tuple<Tensor, Tensor, Tensor> BatchUnique(Tensor data, Tensor ptr) { return BatchUniqueImpl(data, ptr, false); }
+static std::tuple<Tensor, Tensor, Tensor> BatchUnique2(Tensor data, Tensor ptr) { return BatchUniqueImpl(data, ptr, true); }
+// The ...ByKey forms take the batch number of every item as well; it is implied by the offset arrays (the
+// reference derives one from the other with _RepeatKernel, src/cuda/batch_unique.cu:184-206), so it is not read.
+static std::tuple<Tensor, Tensor, Tensor> BatchUniqueByKey(Tensor data, Tensor ptr, Tensor) {
+  return BatchUniqueImpl(data, ptr, false);
+}
+static std::tuple<Tensor, Tensor, Tensor> BatchUniqueByKey2(Tensor data, Tensor ptr, Tensor) {
+  return BatchUniqueImpl(data, ptr, true);
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor> BatchCSRRelabelByKey(Tensor seeds, Tensor seeds_ptr, Tensor,
+                                                                       Tensor indices, Tensor indices_ptr, Tensor) {
+  return BatchCSRRelabel(seeds, seeds_ptr, indices, indices_ptr);
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> BatchCOORelabel(Tensor seeds_in, Tensor seeds_ptr_in,
+                                                                          Tensor coo_col_in, Tensor coo_row_in,
+                                                                          Tensor coo_ptr_in) {
+  Tensor s = Ids(seeds_in, "seeds"), sp = Ids(seeds_ptr_in, "seeds_ptr"), col = Ids(coo_col_in, "coo_col"),
+         row = Ids(coo_row_in, "coo_row"), cp = Ids(coo_ptr_in, "coo_ptr");
+  TORCH_CHECK(col.numel() == row.numel(), "coo_col and coo_row must have the same length");
+  const int64_t G = sp.numel() - 1, E = row.numel();
+  Tensor uniq = EmptyIds(s.numel() + E, s), uptr = EmptyIds(G + 1, s), orow = EmptyIds(E, s), ocol = EmptyIds(E, s);
+  int64_t nu = 0;
+  Check(gsb_batch_coo_relabel(Ctx(), Stream(), IP(s), IP(sp), s.numel(), IP(col), IP(row), IP(cp), E, G, MP(uniq),
+                              MP(uptr), MP(orow), MP(ocol), &nu),
+        "gsb_batch_coo_relabel");
+  return {uniq.narrow(0, 0, nu), uptr, orow, ocol, cp};
+}
+static std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> BatchCOORelabelByKey(Tensor seeds, Tensor seeds_ptr, Tensor,
+                                                                               Tensor coo_col, Tensor coo_row,
+                                                                               Tensor coo_ptr, Tensor) {
+  return BatchCOORelabel(seeds, seeds_ptr, coo_col, coo_row, coo_ptr);
+}
+static std::tuple<Tensor, Tensor, Tensor> CooSliceImpl(int64_t axis, Tensor row_in, Tensor col_in, const Tensor* edge_ptr,
+                                                       Tensor members_in, const Tensor* members_ptr) {
+  Tensor row = Ids(row_in, "coo_row"), col = Ids(col_in, "coo_col"), mem = Ids(members_in, "neighbors");
+  TORCH_CHECK(axis == 0 || axis == 1, "axis must be 0 or 1");
+  Tensor ep = edge_ptr ? Ids(*edge_ptr, "batch_ptr") : Tensor(), mp = members_ptr ? Ids(*members_ptr, "neighbors_ptr") : Tensor();
+  const int64_t G = edge_ptr ? ep.numel() - 1 : 1, E = row.numel();
+  Tensor orow = EmptyIds(E, row), ocol = EmptyIds(E, row), optr = EmptyIds(G + 1, row);
+  int64_t n = 0;
+  Check(gsb_batch_coo_slice(Ctx(), Stream(), (int)axis, IP(row), IP(col), IP(ep), E, IP(mem), IP(mp), mem.numel(), G,
+                            MP(orow), MP(ocol), MP(optr), &n),
+        "gsb_batch_coo_slice");
+  return {orow.narrow(0, 0, n), ocol.narrow(0, 0, n), optr};
+}
+static std::tuple<Tensor, Tensor, Tensor> BatchCOOSlicing(int64_t axis, Tensor coo_row, Tensor coo_col, Tensor batch_ptr,
+                                                          Tensor neighbors, Tensor neighbors_ptr) {
+  return CooSliceImpl(axis, coo_row, coo_col, &batch_ptr, neighbors, &neighbors_ptr);
+}
+static std::tuple<Tensor, Tensor> COORowSlicingGlobalId(Tensor coo_row, Tensor coo_col, Tensor row_ids) {
+  auto r = CooSliceImpl(1, coo_row, coo_col, nullptr, row_ids, nullptr);
+  return {std::get<0>(r), std::get<1>(r)};
+}
+static std::tuple<Tensor, Tensor, Tensor> BatchConcat(std::vector<Tensor> data_tensors, std::vector<Tensor> offset_tensors) {
+  const size_t n = data_tensors.size();
+  TORCH_CHECK(n >= 1 && n == offset_tensors.size() && n <= GSB_MAX_CONCAT, "between 1 and ", GSB_MAX_CONCAT,
+              " (data, offsets) pairs are required");
+  std::vector<Tensor> d, o;
+  const int64_t* dp[GSB_MAX_CONCAT];
+  const int64_t* op[GSB_MAX_CONCAT];
+  int64_t len[GSB_MAX_CONCAT], total = 0;
+  for (size_t i = 0; i < n; ++i) {
+    d.push_back(Ids(data_tensors[i], "data tensor"));
+    o.push_back(Ids(offset_tensors[i], "offset tensor"));
+    dp[i] = IP(d[i]), op[i] = IP(o[i]), len[i] = d[i].numel(), total += len[i];
+  }
+  const int64_t G = o[0].numel() - 1;
+  Tensor out = EmptyIds(total, d[0]), key = EmptyIds(total, d[0]), ptr = EmptyIds(G + 1, d[0]);
+  Check(gsb_batch_concat(Ctx(), Stream(), dp, op, len, (int)n, G, MP(out), MP(key), MP(ptr)), "gsb_batch_concat");
+  return {out, key, ptr};
+}
+static std::tuple<std::vector<Tensor>, std::vector<Tensor>> BatchSplit(Tensor data_in, Tensor data_ptr_in, Tensor,
+                                                                       std::vector<Tensor> out_tensors,
+                                                                       std::vector<Tensor> out_ptr_tensors) {
+  Tensor data = Ids(data_in, "data"), ptr = Ids(data_ptr_in, "data_ptr");
+  const size_t n = out_tensors.size();
+  TORCH_CHECK(n >= 1 && n == out_ptr_tensors.size() && n <= GSB_MAX_CONCAT, "between 1 and ", GSB_MAX_CONCAT,
+              " (output, offsets) pairs are required");
+  std::vector<Tensor> o;
+  int64_t* outp[GSB_MAX_CONCAT];
+  const int64_t* op[GSB_MAX_CONCAT];
+  for (size_t i = 0; i < n; ++i) {
+    TORCH_CHECK(out_tensors[i].is_cuda() && out_tensors[i].scalar_type() == torch::kInt64 && out_tensors[i].is_contiguous(),
+                "output tensors must be contiguous int64 CUDA tensors");
+    o.push_back(Ids(out_ptr_tensors[i], "output offsets"));
+    outp[i] = MP(out_tensors[i]), op[i] = IP(o[i]);
+  }
+  Check(gsb_batch_split(Ctx(), Stream(), IP(data), IP(ptr), data.numel(), ptr.numel() - 1, outp, op, (int)n),
+        "gsb_batch_split");
+  return {out_tensors, out_ptr_tensors};
+}
+static std::tuple<Tensor, Tensor> BatchListSamplingProbs(Tensor probs_in, int64_t num_picks, bool replace, Tensor range_in) {
+  TORCH_CHECK(!replace, "Not implemented warning");  // src/cuda/list_sampling_probs.cu:119-120 aborts as well
+  Tensor probs = Floats(probs_in, "probs"), range = Ids(range_in, "range");
+  const int64_t N = probs.numel(), G = range.numel() - 1;
+  Tensor out = EmptyIds(std::min(N, G * num_picks), range), out_range = EmptyIds(G + 1, range);
+  int64_t n = 0;
+  Check(gsb_batch_list_sample(Ctx(), Stream(), FP(probs), N, IP(range), G, num_picks, NextSeed(), MP(out), MP(out_range), &n),
+        "gsb_batch_list_sample");
+  return {out.narrow(0, 0, n), out_range};
+}
 static void SetSeed(int64_t seed) {
   g_seed_base.store((uint64_t)seed);
   g_seed_counter.store(0);
@@ -762,6 +946,7 @@ TORCH_LIBRARY(gs_classes, m) {
       GS_DEF2("_CAPI_GetNumCols", "_CAPI_get_num_cols", &Graph::GetNumCols)
       GS_DEF2("_CAPI_GetNumEdges", "_CAPI_get_num_edges", &Graph::GetNumEdges)
       GS_DEF2("_CAPI_Slicing", "_CAPI_slicing", &Graph::Slicing)
+      GS_DEF2("_CAPI_BatchSlicing", "_CAPI_batch_slicing", &Graph::BatchSlicing)
       GS_DEF2("_CAPI_Sampling", "_CAPI_sampling", &Graph::Sampling)
       GS_DEF2("_CAPI_SamplingWithProbs", "_CAPI_sampling_with_probs", &Graph::SamplingProbs)
       GS_DEF2("_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_fused_columnwise_slicing_sampling",
@@ -805,5 +990,22 @@ TORCH_LIBRARY(gs_ops, m) {
   m.def("_CAPI_IndptrSplitByOffset", &gsglue::IndptrSplitByOffset);
   m.def("IndptrSplitByOffset", &gsglue::IndptrSplitByOffset);
   m.def("_CAPI_IndptrSplitBySize", &gsglue::IndptrSplitBySize);
+  m.def("_CAPI_BatchListSamplingWithProbs", &gsglue::BatchListSamplingProbs);
+  m.def("_CAPI_BatchConcat", &gsglue::BatchConcat);
+  m.def("_CAPI_BatchUnique", &gsglue::BatchUnique);
+  m.def("_CAPI_BatchUniqueByKey", &gsglue::BatchUniqueByKey);
+  m.def("_CAPI_BatchUnique2", &gsglue::BatchUnique2);
+  m.def("_CAPI_BatchUniqueByKey2", &gsglue::BatchUniqueByKey2);
+  m.def("_CAPI_BatchCSRRelabelByKey", &gsglue::BatchCSRRelabelByKey);
+  m.def("_CAPI_BatchCOORelabelByKey", &gsglue::BatchCOORelabelByKey);
+  m.def("_CAPI_BatchCOORelabel", &gsglue::BatchCOORelabel);
+  m.def("BatchCOORelabel", &gsglue::BatchCOORelabel);
+  m.def("_CAPI_BatchSplit", &gsglue::BatchSplit);
+  m.def("_CAPI_BatchCOOSlicing", &gsglue::BatchCOOSlicing);
+  m.def("_CAPI_BatchEncode", &gsglue::BatchEncode);
+  m.def("_CAPI_BatchDecode", &gsglue::BatchDecode);
+  m.def("_CAPI_GetBatchOffsets", &gsglue::GetBatchOffsets);
+  m.def("_CAPI_COORowSlicingGlobalId", &gsglue::COORowSlicingGlobalId);
+  m.def("COORowSlicingGlobalId", &gsglue::COORowSlicingGlobalId);
   m.def("_CAPI_SetSeed", &gsglue::SetSeed);
 }

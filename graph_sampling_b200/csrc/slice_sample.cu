@@ -71,11 +71,18 @@ struct FillParams {
   const float* data;
   const i64* e_ids;
   float* out_data;
+  // super-batch form (src/cuda/slicing.cu:184-270): seeds of batch b are seeds[nid_ptr[b] .. nid_ptr[b+1]);
+  // with encoding_size > 0 the row id of an edge of batch b is written as id + b * encoding_size
+  const i64* nid_ptr;
+  i64 G;
+  i64 encoding_size;
 };
 
+template <bool ENCODE>
 __global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
   __shared__ i64 s_in[kTileCols];
   __shared__ i64 s_off[kTileCols + 1];
+  __shared__ i64 s_enc[ENCODE ? kTileCols : 1];
   const i64 base = (i64)blockIdx.x * kTileCols;
   if (base >= p.S) return;
   const int ncol = (int)min((i64)kTileCols, p.S - base);
@@ -84,6 +91,7 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
   if (tid < ncol) {
     const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
     s_in[tid] = p.indptr[col];
+    if (ENCODE) s_enc[tid] = batch_of(p.nid_ptr, p.G, base + tid) * p.encoding_size;
   }
   __syncthreads();
   const i64 tile_base = s_off[0];
@@ -98,7 +106,7 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
       else hi = mid;
     }
     const i64 in_pos = s_in[lo] + (pos - s_off[lo]);
-    p.out_indices[pos] = __ldg(p.indices + in_pos);
+    p.out_indices[pos] = __ldg(p.indices + in_pos) + (ENCODE ? s_enc[lo] : 0);
     p.out_select[pos] = in_pos;
     if (p.out_coo_col) p.out_coo_col[pos] = base + lo;
     if (p.out_data) p.out_data[pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
@@ -404,10 +412,35 @@ int gsb_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
   // out_indices / out_select may be null only when the slice is empty (nothing is written then)
   GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (S == 0) return GSB_OK;
-  FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data};
+  FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data,
+               nullptr, 0, 0};
   {
     ScopedKernelTimer timer(ctx, KID_SLICE_FILL, (cudaStream_t)stream_);
-    k_slice_fill<<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
+    k_slice_fill<false><<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
+  }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int gsb_batch_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+                             const int64_t* seeds, int64_t S, const int64_t* nid_ptr, int64_t G,
+                             int64_t encoding_size, const int64_t* out_indptr, int64_t* out_indices,
+                             int64_t* out_select, int64_t* out_coo_col, int64_t* out_coo_offsets, const float* data,
+                             const int64_t* e_ids, float* out_data) {
+  GSB_REQUIRE(ctx && indptr && out_indptr && nid_ptr && S >= 0 && G >= 1 && encoding_size >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (out_coo_offsets) {
+    int st = gsb_batch_edge_offsets(ctx, stream_, out_indptr, nid_ptr, G, out_coo_offsets);
+    if (st != GSB_OK) return st;
+  }
+  if (S == 0) return GSB_OK;
+  FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data,
+               nid_ptr, G, encoding_size};
+  {
+    ScopedKernelTimer timer(ctx, KID_SLICE_FILL, stream);
+    if (encoding_size > 0) k_slice_fill<true><<<grid_for(S, kTileCols), kThreads, 0, stream>>>(p);
+    else k_slice_fill<false><<<grid_for(S, kTileCols), kThreads, 0, stream>>>(p);
   }
   GSB_LAUNCH_OK();
   return GSB_OK;

@@ -255,6 +255,38 @@ class Graph:
             ret.data_ = out_data
         return ret
 
+    # ---- BatchSlicing (src/graph.cc:312-391) --------------------------------------------------------------
+    def BatchSlicing(self, n_ids, nid_ptr, axis, on_format, output_format, relabel=False, encoding=False):
+        """Column slice for the seeds of many batches at once → (Graph, coo_offsets).  The child's column ids are
+        the seeds encoded with their batch number (id + batch * num_rows) and it spans num_rows * batches rows;
+        with `encoding` the row ids of its edges are encoded the same way."""
+        if axis != 0:
+            _fatal("batch slicing only suppurt column slicing now")
+        if on_format != _CSC:
+            _fatal("Not Implementatin Error")
+        self.CreateSparseFormat(on_format)
+        with_coo = bool(output_format & _COO)
+        batch_num = nid_ptr.numel() - 1
+        new_col_ids = self.col_ids_[n_ids] if self.col_ids_ is not None else ops.batch_encode(n_ids, nid_ptr,
+                                                                                               self.num_rows_)
+        new_row_ids, new_num_rows = self.row_ids_, self.num_rows_ * batch_num
+        data, e_ids = self._gather_args(self.csc_)
+        r = ops.batch_csc_col_slicing(self.csc_.indptr, self.csc_.indices, n_ids, nid_ptr, self.num_rows_, with_coo,
+                                      encoding, data=data, e_ids=e_ids)
+        indptr, coo_col, indices, coo_offsets = r[0], r[1], r[2], r[4]
+        if relabel:
+            frontier, (indices,) = ops.relabel([indices], [indices])
+            new_row_ids, new_num_rows = frontier, frontier.numel()
+        ret = self._child(new_col_ids, new_row_ids, n_ids.numel(), new_num_rows)
+        ret.num_edges_ = indices.numel()
+        if output_format & _CSC:
+            ret.csc_ = CSC(indptr, indices)
+        if with_coo:
+            ret.coo_ = COO(indices, coo_col, None, False, True)
+        if data is not None:
+            ret.data_ = r[5]
+        return ret, coo_offsets
+
     # ---- Sampling / SamplingProbs (src/graph.cc:393-529) ---------------------------------------------------
     def _sampling_impl(self, axis, fanout, replace, on_format, output_format, probs, seed):
         self.CreateSparseFormat(on_format)
@@ -512,9 +544,9 @@ class Graph:
 
     # ---- outside the hot path ------------------------------------------------------------------------------------------------------
     def _out_of_scope(self, *a, **k):
-        raise NotImplementedError("batched / induced-subgraph / compact-id methods are outside the sampling hot path")
+        raise NotImplementedError("induced-subgraph / compact-id methods are outside the sampling hot path")
 
-    FusedBidirSlicing = BatchFusedBidirSlicing = BatchSlicing = Split = Decode = EDivUSum = _out_of_scope
+    FusedBidirSlicing = BatchFusedBidirSlicing = Split = Decode = EDivUSum = _out_of_scope
 
 
 # Registered names: src/pybind.cc:14-52 (CamelCase) and the spelling used by python/gs + examples.
@@ -553,7 +585,7 @@ _NAME_MAP = {
     "SetCOOByTensor": ("_CAPI_SetCOO", "_CAPI_set_coo"),
     "SetMetaData": ("_CAPI_SetMetadata", "_CAPI_set_metadata"),
     "FusedBidirSlicing": ("_CAPI_FusionSlicing", "_CAPI_fusion_slicing"),
-    "BatchSlicing": ("_CAPI_BatchSlicing",),
+    "BatchSlicing": ("_CAPI_BatchSlicing", "_CAPI_batch_slicing"),
     "BatchFusedBidirSlicing": ("_CAPI_BatchFusionSlicing",),
     "Split": ("_CAPI_Split",),
     "Decode": ("_CAPI_Decode",),
@@ -572,6 +604,49 @@ def ListSampling(data, num_picks, replace, seed=None):
 def ListSamplingProbs(data, probs, num_picks, replace, seed=None):
     """gs::ListSamplingProbs (src/tensor_ops.cc:11-16); gs_ops._CAPI_ListSamplingWithProbs / list_sampling_with_probs."""
     return ops.list_sampling(data, num_picks, replace, probs=probs, seed=seed)
+
+
+# Free operators of the super-batch family under their registered names (src/pybind.cc:65-84).
+def _batch_ops():
+    o = ops
+    return {
+        "_CAPI_BatchListSamplingWithProbs": o.batch_list_sampling_probs,
+        "_CAPI_SplitByOffset": o.split_by_offset,
+        "_CAPI_IndptrSplitBySize": o.indptr_split_by_size,
+        "_CAPI_IndptrSplitByOffset": o.indptr_split_by_offset,
+        "_CAPI_BatchConcat": o.batch_concat,
+        "_CAPI_BatchUnique": lambda d, p: o.batch_unique(d, p, sort=False),
+        "_CAPI_BatchUniqueByKey": lambda d, p, k: o.batch_unique(d, p, sort=False),
+        "_CAPI_BatchUnique2": lambda d, p: o.batch_unique(d, p, sort=True),
+        "_CAPI_BatchUniqueByKey2": lambda d, p, k: o.batch_unique(d, p, sort=True),
+        "_CAPI_BatchCSRRelabel": o.batch_csr_relabel,
+        "_CAPI_BatchCSRRelabelByKey": lambda s, sp, sk, i, ip, ik: o.batch_csr_relabel(s, sp, i, ip),
+        "_CAPI_BatchCOORelabel": o.batch_coo_relabel,
+        "_CAPI_BatchCOORelabelByKey": lambda s, sp, sk, c, r, p, k: o.batch_coo_relabel(s, sp, c, r, p),
+        "_CAPI_BatchSplit": o.batch_split,
+        "_CAPI_BatchCOOSlicing": o.batch_coo_slicing,
+        "_CAPI_BatchEncode": o.batch_encode,
+        "_CAPI_BatchDecode": o.batch_decode,
+        "_CAPI_GetBatchOffsets": o.get_batch_offsets,
+        "_CAPI_COORowSlicingGlobalId": o.coo_row_slicing_global_id,
+    }
+
+
+class _GsOps:
+    """Stand-in for `torch.ops.gs_ops` in the Python face: gs_ops._CAPI_BatchUnique(...) and so on."""
+
+    def __getattr__(self, name):
+        table = _batch_ops()
+        table.update({"_CAPI_ListSampling": ListSampling, "_CAPI_ListSamplingWithProbs": ListSamplingProbs,
+                      "_CAPI_Unique": Unique, "list_sampling": ListSampling,
+                      "list_sampling_with_probs": ListSamplingProbs})
+        for key in (name, "_CAPI_" + name):
+            if key in table:
+                return table[key]
+        raise AttributeError(f"gs_ops has no operator {name}")
+
+
+gs_ops = _GsOps()
 
 
 def Unique(node_ids):

@@ -504,6 +504,173 @@ def batch_edge_offsets(sub_indptr, seeds_ptr, ctx=None):
     return out
 
 
+# ---- the rest of the super-batch family (gs_ops registry, src/pybind.cc:65-84) ------------------
+def batch_encode(data, data_ptr, encoding_size, ctx=None):
+    """BatchEncodeCUDA (src/cuda/batch_coding.cu:64-85): data[i] + batch(i) * encoding_size."""
+    data, data_ptr = _i64(data, "data"), _i64(data_ptr, "data_ptr")
+    ctx = ctx or default_context(data.device)
+    out = torch.empty_like(data)
+    ctx.check(ctx.lib.gsb_batch_encode(ctx.handle, _stream(), _p(data), _p(data_ptr), c_i64(data_ptr.numel() - 1),
+                                       c_i64(data.numel()), c_i64(int(encoding_size)), _p(out)), "gsb_batch_encode")
+    return out
+
+
+def batch_decode(data, encoding_size, ctx=None):
+    """BatchDecodeCUDA (src/cuda/batch_coding.cu:87-98): data[i] mod encoding_size."""
+    data = _i64(data, "data")
+    ctx = ctx or default_context(data.device)
+    out = torch.empty_like(data)
+    ctx.check(ctx.lib.gsb_batch_decode(ctx.handle, _stream(), _p(data), c_i64(data.numel()),
+                                       c_i64(int(encoding_size)), _p(out)), "gsb_batch_decode")
+    return out
+
+
+def get_batch_offsets(data, num_batches, encoding_size, ctx=None):
+    """GetBatchOffsets (src/cuda/batch_coding.cu:100-121) → (data_ptr[num_batches + 1], decoded ids)."""
+    data = _i64(data, "data")
+    ctx = ctx or default_context(data.device)
+    ptr = _empty(int(num_batches) + 1, data)
+    dec = torch.empty_like(data)
+    ctx.check(ctx.lib.gsb_get_batch_offsets(ctx.handle, _stream(), _p(data), c_i64(data.numel()),
+                                            c_i64(int(num_batches)), c_i64(int(encoding_size)), _p(ptr), _p(dec)),
+              "gsb_get_batch_offsets")
+    return ptr, dec
+
+
+def batch_csc_col_slicing(indptr, indices, column_ids, nid_ptr, encoding_size, with_coo=True, encoding=False,
+                          data=None, e_ids=None, ctx=None):
+    """BatchCSCColSlicingCUDA (src/cuda/slicing.cu:275-295) → (sub_indptr, coo_col | None, sub_indices,
+    select_index, coo_offsets[, sliced_data]).  With `encoding` the row ids of batch b carry b * encoding_size."""
+    indptr, indices = _i64(indptr, "indptr"), _i64(indices, "indices")
+    column_ids, nid_ptr = _i64(column_ids, "column_ids"), _i64(nid_ptr, "nid_ptr")
+    data, e_ids = _f32(data, "data", True), _i64(e_ids, "e_ids", True)
+    ctx = ctx or default_context(indptr.device)
+    S, G = column_ids.numel(), nid_ptr.numel() - 1
+    sub_indptr = _empty(S + 1, indptr)
+    nnz = c_i64(0)
+    ctx.check(ctx.lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), _p(column_ids), c_i64(S), _p(sub_indptr),
+                                          ctypes.byref(nnz)), "gsb_col_slice_count")
+    n = nnz.value
+    sub_indices, select = _empty(n, indptr), _empty(n, indptr)
+    coo_col = _empty(n, indptr) if with_coo else None
+    offsets = _empty(G + 1, indptr)
+    out_data = _empty(n, indptr, torch.float32) if data is not None else None
+    ctx.check(ctx.lib.gsb_batch_col_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+                                               _p(nid_ptr), c_i64(G), c_i64(int(encoding_size) if encoding else 0),
+                                               _p(sub_indptr), _p(sub_indices), _p(select), _p(coo_col), _p(offsets),
+                                               _p(data), _p(e_ids), _p(out_data)), "gsb_batch_col_slice_fill")
+    if data is not None:
+        return sub_indptr, coo_col, sub_indices, select, offsets, out_data
+    return sub_indptr, coo_col, sub_indices, select, offsets
+
+
+def batch_unique(data, data_ptr, sort=False, ctx=None):
+    """BatchUniqueCUDA (first-occurrence order) / BatchUnique2CUDA (sort=True: ascending per batch)
+    (src/cuda/batch_unique.cu:131-278) → (unique, unique_ptr, unique_key)."""
+    data, data_ptr = _i64(data, "data"), _i64(data_ptr, "data_ptr")
+    ctx = ctx or default_context(data.device)
+    n, G = data.numel(), data_ptr.numel() - 1
+    uniq, key, ptr = _empty(n, data), _empty(n, data), _empty(G + 1, data)
+    nu = c_i64(0)
+    ctx.check(ctx.lib.gsb_batch_unique(ctx.handle, _stream(), _p(data), _p(data_ptr), c_i64(n), c_i64(G),
+                                       c_int(1 if sort else 0), _p(uniq), _p(ptr), _p(key), ctypes.byref(nu)),
+              "gsb_batch_unique")
+    return uniq[:nu.value], ptr, key[:nu.value]
+
+
+def batch_coo_relabel(seeds, seeds_ptr, coo_col, coo_row, coo_ptr, ctx=None):
+    """BatchCOORelabelCUDA (src/cuda/batch_relabel.cu:349-497) →
+    (unique_tensor, unique_tensor_ptr, relabeled_row, relabeled_col, coo_ptr)."""
+    seeds, seeds_ptr = _i64(seeds, "seeds"), _i64(seeds_ptr, "seeds_ptr")
+    coo_col, coo_row, coo_ptr = _i64(coo_col, "coo_col"), _i64(coo_row, "coo_row"), _i64(coo_ptr, "coo_ptr")
+    if coo_col.numel() != coo_row.numel():
+        raise ValueError("coo_col and coo_row must have the same length")
+    ctx = ctx or default_context(seeds.device)
+    G, E = seeds_ptr.numel() - 1, coo_row.numel()
+    uniq, ptr = _empty(seeds.numel() + E, seeds), _empty(G + 1, seeds)
+    out_row, out_col = _empty(E, seeds), _empty(E, seeds)
+    nu = c_i64(0)
+    ctx.check(ctx.lib.gsb_batch_coo_relabel(ctx.handle, _stream(), _p(seeds), _p(seeds_ptr), c_i64(seeds.numel()),
+                                            _p(coo_col), _p(coo_row), _p(coo_ptr), c_i64(E), c_i64(G), _p(uniq),
+                                            _p(ptr), _p(out_row), _p(out_col), ctypes.byref(nu)),
+              "gsb_batch_coo_relabel")
+    return uniq[:nu.value], ptr, out_row, out_col, coo_ptr
+
+
+def batch_coo_slicing(axis, coo_row, coo_col, batch_ptr, neighbors, neighbors_ptr, ctx=None):
+    """BatchCOOSlicingCUDA (src/cuda/batch_slicing.cu:166-263) → (sub_coo_row, sub_coo_col, sub_ptr): per batch
+    the edges whose column (axis 0) / row (axis 1) id is among the batch's neighbours; ids unchanged."""
+    coo_row, coo_col = _i64(coo_row, "coo_row"), _i64(coo_col, "coo_col")
+    batch_ptr = _i64(batch_ptr, "batch_ptr", True)
+    neighbors, neighbors_ptr = _i64(neighbors, "neighbors"), _i64(neighbors_ptr, "neighbors_ptr", True)
+    ctx = ctx or default_context(coo_row.device)
+    G = 1 if batch_ptr is None else batch_ptr.numel() - 1
+    E = coo_row.numel()
+    out_row, out_col, out_ptr = _empty(E, coo_row), _empty(E, coo_row), _empty(G + 1, coo_row)
+    n = c_i64(0)
+    ctx.check(ctx.lib.gsb_batch_coo_slice(ctx.handle, _stream(), c_int(int(axis)), _p(coo_row), _p(coo_col),
+                                          _p(batch_ptr), c_i64(E), _p(neighbors), _p(neighbors_ptr),
+                                          c_i64(neighbors.numel()), c_i64(G), _p(out_row), _p(out_col), _p(out_ptr),
+                                          ctypes.byref(n)), "gsb_batch_coo_slice")
+    return out_row[:n.value], out_col[:n.value], out_ptr
+
+
+def coo_row_slicing_global_id(coo_row, coo_col, row_ids, ctx=None):
+    """COORowSlicingGlobalIdCUDA (src/cuda/batch_slicing.cu:265-317) → (coo_row, coo_col) of the edges whose
+    row id is in row_ids; ids unchanged."""
+    r, c, _ = batch_coo_slicing(1, coo_row, coo_col, None, row_ids, None, ctx=ctx)
+    return r, c
+
+
+def batch_concat(data_tensors, offset_tensors, ctx=None):
+    """BatchConcatCUDA (src/cuda/batch_concat.cu:50-121) → (data, key, data_ptr): batch b of the result is
+    batch b of every input in turn."""
+    datas = [_i64(t, "data tensor") for t in data_tensors]
+    offs = [_i64(t, "offset tensor") for t in offset_tensors]
+    if not datas or len(datas) != len(offs) or len(datas) > 8:
+        raise ValueError("between 1 and 8 (data, offsets) pairs are required")
+    ctx = ctx or default_context(datas[0].device)
+    G = offs[0].numel() - 1
+    total = sum(t.numel() for t in datas)
+    out, key, ptr = _empty(total, datas[0]), _empty(total, datas[0]), _empty(G + 1, datas[0])
+    ctx.check(ctx.lib.gsb_batch_concat(ctx.handle, _stream(), _ptr_array(datas), _ptr_array(offs), _len_array(datas),
+                                       c_int(len(datas)), c_i64(G), _p(out), _p(key), _p(ptr)), "gsb_batch_concat")
+    return out, key, ptr
+
+
+def batch_split(data, data_ptr, data_key, out_tensors, out_ptr_tensors, ctx=None):
+    """BatchSplit2CUDA (src/cuda/batch_split2.cu:40-106): the inverse of batch_concat; fills the caller's
+    out_tensors (partitioned by out_ptr_tensors) and returns (out_tensors, out_ptr_tensors).  data_key is
+    accepted for signature compatibility; the batch of an item is derived from data_ptr."""
+    data, data_ptr = _i64(data, "data"), _i64(data_ptr, "data_ptr")
+    outs = [_i64(t, "output tensor") for t in out_tensors]
+    optrs = [_i64(t, "output offsets") for t in out_ptr_tensors]
+    if not outs or len(outs) != len(optrs) or len(outs) > 8:
+        raise ValueError("between 1 and 8 (output, offsets) pairs are required")
+    ctx = ctx or default_context(data.device)
+    ctx.check(ctx.lib.gsb_batch_split(ctx.handle, _stream(), _p(data), _p(data_ptr), c_i64(data.numel()),
+                                      c_i64(data_ptr.numel() - 1), _ptr_array(outs), _ptr_array(optrs),
+                                      c_int(len(outs))), "gsb_batch_split")
+    return outs, optrs
+
+
+def batch_list_sampling_probs(probs, num_picks, replace, range_ptr, seed=None, ctx=None):
+    """BatchListSamplingProbsCUDA (src/cuda/list_sampling_probs.cu:110-183) → (out_idx, out_range): weighted
+    sampling without replacement of min(num_picks, size) positions from every segment of `probs`."""
+    if replace:
+        raise NotImplementedError("segmented list sampling with replacement (the reference aborts as well)")
+    probs, range_ptr = _f32(probs, "probs"), _i64(range_ptr, "range")
+    ctx = ctx or default_context(probs.device)
+    N, G = probs.numel(), range_ptr.numel() - 1
+    out = _empty(min(N, G * int(num_picks)), range_ptr)
+    out_range = _empty(G + 1, range_ptr)
+    n = c_i64(0)
+    ctx.check(ctx.lib.gsb_batch_list_sample(ctx.handle, _stream(), _p(probs), c_i64(N), _p(range_ptr), c_i64(G),
+                                            c_i64(int(num_picks)), c_u64(next_seed(seed)), _p(out), _p(out_range),
+                                            ctypes.byref(n)), "gsb_batch_list_sample")
+    return out[:n.value], out_range
+
+
 def split_by_offset(data, offsets):
     """gs::SplitByOffset (src/tensor_ops.cc:33-45): views of `data` cut at `offsets` (one host read of the sizes)."""
     sizes = (offsets[1:] - offsets[:-1]).tolist()

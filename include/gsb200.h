@@ -272,6 +272,85 @@ GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* 
                                      int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
                                      int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
 
+/* ---- the rest of the super-batch family (gs_ops registry, src/pybind.cc:65-84) ---------------------------
+ * Ids of G minibatches travel in one array plus a DEVICE offset array of G + 1 entries.  All sizes the
+ * caller passes are exact unless called "capacity".  Calls wait for the stream only where a *_host pointer
+ * is given.
+ *
+ * gsb_batch_encode / gsb_batch_decode / gsb_get_batch_offsets replace gs::impl::BatchEncodeCUDA,
+ * BatchDecodeCUDA and GetBatchOffsets (src/cuda/batch_coding.cu:64-121): out[i] = data[i] + b * encoding_size
+ * for item i of batch b; out[i] = data[i] mod encoding_size; out_ptr[b + 1] = number of leading items whose
+ * batch number data[i] / encoding_size is <= b (the batch numbers must be non-decreasing) together with the
+ * decoded ids (out_decoded may be NULL).
+ */
+GSB_API int gsb_batch_encode(gsb_ctx* ctx, void* stream, const int64_t* data, const int64_t* data_ptr, int64_t G,
+                             int64_t n, int64_t encoding_size, int64_t* out);
+GSB_API int gsb_batch_decode(gsb_ctx* ctx, void* stream, const int64_t* data, int64_t n, int64_t encoding_size,
+                             int64_t* out);
+GSB_API int gsb_get_batch_offsets(gsb_ctx* ctx, void* stream, const int64_t* data, int64_t n, int64_t num_batches,
+                                  int64_t encoding_size, int64_t* out_ptr, int64_t* out_decoded);
+
+/* gsb_batch_col_slice_fill replaces gs::impl::BatchCSCColSlicingCUDA (src/cuda/slicing.cu:184-295; the kernel
+ * side of Graph::BatchSlicing, src/graph.cc:312-391): the fill step of a column slice whose seeds belong to
+ * G batches (nid_ptr).  out_indptr comes from gsb_col_slice_count.  encoding_size > 0 writes the row id of an
+ * edge of batch b as id + b * encoding_size; out_coo_offsets[b] = out_indptr[nid_ptr[b]] (may be NULL). */
+GSB_API int gsb_batch_col_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                                     const int64_t* seeds, int64_t S, const int64_t* nid_ptr, int64_t G,
+                                     int64_t encoding_size, const int64_t* out_indptr, int64_t* out_indices,
+                                     int64_t* out_select, int64_t* out_coo_col, int64_t* out_coo_offsets,
+                                     const float* data, const int64_t* e_ids, float* out_data);
+
+/* gsb_batch_unique replaces gs::impl::BatchUniqueCUDA / BatchUniqueByKeyCUDA (first-occurrence order,
+ * src/cuda/batch_unique.cu:131-213) and BatchUnique2CUDA / BatchUniqueByKey2CUDA (sorted != 0: ascending ids
+ * per batch, :215-278).  out_unique (n entries) holds the per-batch distinct ids back to back,
+ * out_unique_ptr[G + 1] their offsets, out_unique_key (n entries, may be NULL) the batch number of every
+ * distinct id.  sorted != 0 requires unique_total_host.  Ids below 2^32 - 1, n below 2^31. */
+GSB_API int gsb_batch_unique(gsb_ctx* ctx, void* stream, const int64_t* data, const int64_t* data_ptr, int64_t n,
+                             int64_t G, int sorted, int64_t* out_unique, int64_t* out_unique_ptr,
+                             int64_t* out_unique_key, int64_t* unique_total_host);
+
+/* gsb_batch_coo_relabel replaces gs::impl::BatchCOORelabelCUDA / BatchCOORelabelByKeyCUDA
+ * (src/cuda/batch_relabel.cu:349-497): per batch the frontier is unique(cat(seeds_b, coo_row_b)) in
+ * first-occurrence order; coo_row and coo_col (both partitioned by coo_ptr) are replaced by positions in
+ * that frontier (-1 for an id that is not in it). */
+GSB_API int gsb_batch_coo_relabel(gsb_ctx* ctx, void* stream, const int64_t* seeds, const int64_t* seeds_ptr,
+                                  int64_t num_seeds, const int64_t* coo_col, const int64_t* coo_row,
+                                  const int64_t* coo_ptr, int64_t num_edges, int64_t G, int64_t* out_unique,
+                                  int64_t* out_unique_ptr, int64_t* out_row, int64_t* out_col,
+                                  int64_t* unique_total_host);
+
+/* gsb_batch_coo_slice replaces gs::impl::BatchCOOSlicingCUDA (src/cuda/batch_slicing.cu:166-263) and, with
+ * G = 1 and edge_ptr = members_ptr = NULL, COORowSlicingGlobalIdCUDA (:265-317): keeps the edges whose
+ * column (axis 0) or row (axis 1) id is one of the batch's `members`; ids are NOT renumbered; survivors keep
+ * their order; out_ptr[G + 1] are the per-batch offsets of the survivors.  out_row / out_col hold num_edges
+ * entries. */
+GSB_API int gsb_batch_coo_slice(gsb_ctx* ctx, void* stream, int axis, const int64_t* coo_row, const int64_t* coo_col,
+                                const int64_t* edge_ptr, int64_t num_edges, const int64_t* members,
+                                const int64_t* members_ptr, int64_t num_members, int64_t G, int64_t* out_row,
+                                int64_t* out_col, int64_t* out_ptr, int64_t* n_out_host);
+
+/* gsb_batch_concat / gsb_batch_split replace gs::impl::BatchConcatCUDA (src/cuda/batch_concat.cu:50-121) and
+ * BatchSplit2CUDA (src/cuda/batch_split2.cu:40-106).  concat: batch b of the output is batch b of array 0,
+ * then batch b of array 1, ...; out_key[i] = batch of output item i (may be NULL); out_ptr[b] = sum of the
+ * arrays' offsets.  split is the inverse: the caller provides the output arrays and their offset arrays.
+ * The pointer tables and lens are HOST arrays of num_arrays (<= GSB_MAX_CONCAT) entries. */
+#define GSB_MAX_CONCAT 8
+GSB_API int gsb_batch_concat(gsb_ctx* ctx, void* stream, const int64_t* const* data_ptrs_host,
+                             const int64_t* const* offset_ptrs_host, const int64_t* lens_host, int num_arrays,
+                             int64_t G, int64_t* out, int64_t* out_key, int64_t* out_ptr);
+GSB_API int gsb_batch_split(gsb_ctx* ctx, void* stream, const int64_t* data, const int64_t* data_ptr, int64_t n,
+                            int64_t G, int64_t* const* out_data_host, const int64_t* const* out_ptr_host,
+                            int num_arrays);
+
+/* gsb_batch_list_sample replaces gs::impl::BatchListSamplingProbsCUDA (src/cuda/list_sampling_probs.cu:110-183;
+ * gs_ops._CAPI_BatchListSamplingWithProbs): weighted sampling without replacement of min(k, size) items from
+ * every segment range[b] .. range[b+1] of probs (A-Res keys, probs <= 0 rank last).  out_idx holds the winners'
+ * positions in probs, per segment in descending key order, out_range[G + 1] their offsets; out_idx needs
+ * min(N, G * k) entries.  N below 2^32 - 1. */
+GSB_API int gsb_batch_list_sample(gsb_ctx* ctx, void* stream, const float* probs, int64_t N, const int64_t* range,
+                                  int64_t G, int64_t k, uint64_t seed, int64_t* out_idx, int64_t* out_range,
+                                  int64_t* n_out_host);
+
 /* ---- one hop of multi-batch GraphSAGE sampling ------------------------------------------------------------
  * The per-hop body of the reference's super-batch loop (examples/graphsage/batching.py:56-90:
  * _CAPI_fused_columnwise_slicing_sampling over the seeds of all batches, GetBatchCSC,

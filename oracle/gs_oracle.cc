@@ -67,6 +67,13 @@ GSO_API uint32_t gso_rand_word(uint64_t seed, uint64_t item, uint64_t slot, uint
 }
 GSO_API float gso_ares_key_of(uint32_t r, float w) { return gso_ares_key(r, w); }
 
+// A-Res ranking key of every list position (the keys list sampling and its segmented form rank by).
+GSO_API void gso_list_keys(const float* probs, i64 N, uint64_t seed, float* out_keys) {
+#pragma omp parallel for schedule(static)
+  for (i64 i = 0; i < N; ++i)
+    out_keys[i] = gso_ares_key(gso_rand_u32(seed, (uint64_t)i, 0, GSO_STREAM_LIST_WEIGHTED), probs[i]);
+}
+
 /* exclusive scan in place over n+1 entries; returns the total (entry n). */
 static i64 exclusive_scan(i64* a, i64 n) {
   i64 run = 0;

@@ -315,3 +315,161 @@ def sage_batch(indptr, indices, seeds, fanouts, seed=0, want_frontier=False):
     if want_frontier:
         return int(e), fr[:flen.value].copy()
     return int(e)
+
+
+# ---- super-batch family (src/pybind.cc:65-84): ids of G batches in one array + an offset array ----------
+def _batch_ids(ptr, n):
+    """Batch number of each of n items partitioned by ptr (src/cuda/batch_unique.cu:184-194 _RepeatKernel)."""
+    ptr = np.asarray(ptr, dtype=I64)
+    return (np.searchsorted(ptr, np.arange(n, dtype=I64), side="right") - 1).astype(I64)
+
+
+def batch_encode(data, data_ptr, encoding_size):
+    """src/cuda/batch_coding.cu:10-28."""
+    data = np.asarray(data, dtype=I64)
+    return data + _batch_ids(data_ptr, len(data)) * encoding_size
+
+
+def batch_decode(data, encoding_size):
+    """src/cuda/batch_coding.cu:87-98."""
+    data = np.asarray(data, dtype=I64)
+    return data - (data // encoding_size) * encoding_size
+
+
+def get_batch_offsets(data, num_batches, encoding_size):
+    """src/cuda/batch_coding.cu:100-121 → (ptr, decoded): ptr[b+1] = upper bound of b among the batch numbers."""
+    data = np.asarray(data, dtype=I64)
+    mask = data // encoding_size
+    ptr = np.zeros(num_batches + 1, dtype=I64)
+    ptr[1:] = np.searchsorted(mask, np.arange(num_batches, dtype=I64), side="right")
+    return ptr, data - mask * encoding_size
+
+
+def batch_col_slice(indptr, indices, seeds, nid_ptr, encoding_size, with_coo=True, encoding=False):
+    """src/cuda/slicing.cu:184-270 → (sub_indptr, coo_col | None, sub_indices, select_index, coo_offsets)."""
+    sub_indptr, coo_col, sub_indices, select = col_slice(indptr, indices, seeds, with_coo=True)
+    nid_ptr = np.asarray(nid_ptr, dtype=I64)
+    if encoding:
+        sub_indices = sub_indices + _batch_ids(nid_ptr, len(seeds))[coo_col] * encoding_size
+    return sub_indptr, (coo_col if with_coo else None), sub_indices, select, sub_indptr[nid_ptr]
+
+
+def batch_unique(data, data_ptr, sort=False):
+    """src/cuda/batch_unique.cu:131-278 → (unique, unique_ptr, unique_key); first-occurrence order per batch,
+    or ascending when sort (the cub segment-sort flavour, :215-260)."""
+    data, data_ptr = np.asarray(data, dtype=I64), np.asarray(data_ptr, dtype=I64)
+    G = len(data_ptr) - 1
+    parts, ptr = [], np.zeros(G + 1, dtype=I64)
+    for b in range(G):
+        u = unique_relabel([data[data_ptr[b]:data_ptr[b + 1]]])[0]
+        if sort:
+            u = np.sort(u)
+        parts.append(u)
+        ptr[b + 1] = ptr[b] + len(u)
+    uniq = np.concatenate(parts) if parts else np.empty(0, I64)
+    return uniq.astype(I64), ptr, _batch_ids(ptr, len(uniq))
+
+
+def batch_csr_relabel(seeds, seeds_ptr, indices, indices_ptr):
+    """src/cuda/batch_relabel.cu:214-320 → (unique, unique_ptr, relabeled_indices)."""
+    seeds, seeds_ptr = np.asarray(seeds, dtype=I64), np.asarray(seeds_ptr, dtype=I64)
+    indices, indices_ptr = np.asarray(indices, dtype=I64), np.asarray(indices_ptr, dtype=I64)
+    G = len(seeds_ptr) - 1
+    us, rels, ptr = [], [], np.zeros(G + 1, dtype=I64)
+    for b in range(G):
+        ind = indices[indices_ptr[b]:indices_ptr[b + 1]]
+        u, (r,) = unique_relabel([seeds[seeds_ptr[b]:seeds_ptr[b + 1]], ind], [ind])
+        us.append(u)
+        rels.append(r)
+        ptr[b + 1] = ptr[b] + len(u)
+    cat = lambda xs: np.concatenate(xs).astype(I64) if xs else np.empty(0, I64)
+    return cat(us), ptr, cat(rels)
+
+
+def batch_coo_relabel(seeds, seeds_ptr, coo_col, coo_row, coo_ptr):
+    """src/cuda/batch_relabel.cu:349-497 → (unique, unique_ptr, relabeled_row, relabeled_col): the frontier of a
+    batch is unique(cat(seeds_b, coo_row_b)); a column id that is not in it maps to -1."""
+    seeds, seeds_ptr = np.asarray(seeds, dtype=I64), np.asarray(seeds_ptr, dtype=I64)
+    coo_col, coo_row, coo_ptr = (np.asarray(a, dtype=I64) for a in (coo_col, coo_row, coo_ptr))
+    G = len(seeds_ptr) - 1
+    us, rows, cols, ptr = [], [], [], np.zeros(G + 1, dtype=I64)
+    for b in range(G):
+        r = coo_row[coo_ptr[b]:coo_ptr[b + 1]]
+        c = coo_col[coo_ptr[b]:coo_ptr[b + 1]]
+        u, (rr, cc) = unique_relabel([seeds[seeds_ptr[b]:seeds_ptr[b + 1]], r], [r, c])
+        us.append(u)
+        rows.append(rr)
+        cols.append(cc)
+        ptr[b + 1] = ptr[b] + len(u)
+    cat = lambda xs: np.concatenate(xs).astype(I64) if xs else np.empty(0, I64)
+    return cat(us), ptr, cat(rows), cat(cols)
+
+
+def batch_coo_slice(axis, coo_row, coo_col, batch_ptr, neighbors, neighbors_ptr):
+    """src/cuda/batch_slicing.cu:166-263 → (sub_row, sub_col, sub_ptr); ids unchanged, order kept."""
+    coo_row, coo_col = np.asarray(coo_row, dtype=I64), np.asarray(coo_col, dtype=I64)
+    batch_ptr, neighbors_ptr = np.asarray(batch_ptr, dtype=I64), np.asarray(neighbors_ptr, dtype=I64)
+    neighbors = np.asarray(neighbors, dtype=I64)
+    target = coo_col if axis == 0 else coo_row
+    G = len(batch_ptr) - 1
+    keep = np.zeros(len(target), dtype=bool)
+    ptr = np.zeros(G + 1, dtype=I64)
+    for b in range(G):
+        sl = slice(batch_ptr[b], batch_ptr[b + 1])
+        keep[sl] = np.isin(target[sl], neighbors[neighbors_ptr[b]:neighbors_ptr[b + 1]])
+        ptr[b + 1] = ptr[b] + keep[sl].sum()
+    return coo_row[keep], coo_col[keep], ptr
+
+
+def batch_concat(datas, ptrs):
+    """src/cuda/batch_concat.cu:11-121 → (data, key, ptr)."""
+    datas = [np.asarray(d, dtype=I64) for d in datas]
+    ptrs = [np.asarray(p, dtype=I64) for p in ptrs]
+    G = len(ptrs[0]) - 1
+    parts, keys = [], []
+    for b in range(G):
+        for d, p in zip(datas, ptrs):
+            parts.append(d[p[b]:p[b + 1]])
+            keys.append(np.full(p[b + 1] - p[b], b, dtype=I64))
+    out_ptr = np.sum(np.stack(ptrs), axis=0).astype(I64)
+    cat = lambda xs: np.concatenate(xs).astype(I64) if xs else np.empty(0, I64)
+    return cat(parts), cat(keys), out_ptr
+
+
+def batch_split(data, data_ptr, out_ptrs):
+    """src/cuda/batch_split2.cu:11-106 → list of arrays: the inverse of batch_concat."""
+    data, data_ptr = np.asarray(data, dtype=I64), np.asarray(data_ptr, dtype=I64)
+    out_ptrs = [np.asarray(p, dtype=I64) for p in out_ptrs]
+    G = len(data_ptr) - 1
+    outs = [np.empty(p[-1], dtype=I64) for p in out_ptrs]
+    for b in range(G):
+        o = data_ptr[b]
+        for out, p in zip(outs, out_ptrs):
+            n = p[b + 1] - p[b]
+            out[p[b]:p[b + 1]] = data[o:o + n]
+            o += n
+    return outs
+
+
+def list_keys(probs, seed=0):
+    probs = _f32(probs)
+    keys = np.empty(len(probs), dtype=np.float32)
+    lib().gso_list_keys(_p(probs), _c(len(probs)), _u(seed), _p(keys))
+    return keys
+
+
+def batch_list_sample(probs, range_ptr, k, seed=0):
+    """src/cuda/list_sampling_probs.cu:110-183 → (out_idx, out_range): per segment the min(k, size) positions
+    with the largest A-Res keys, in descending key order (ties: smaller position first)."""
+    keys = list_keys(probs, seed)
+    range_ptr = np.asarray(range_ptr, dtype=I64)
+    G = len(range_ptr) - 1
+    outs, out_range = [], np.zeros(G + 1, dtype=I64)
+    for b in range(G):
+        lo, hi = range_ptr[b], range_ptr[b + 1]
+        seg = keys[lo:hi]
+        order = np.lexsort((np.arange(hi - lo), -seg.astype(np.float64)))
+        take = order[:min(k, hi - lo)] + lo
+        outs.append(take.astype(I64))
+        out_range[b + 1] = out_range[b] + len(take)
+    return (np.concatenate(outs).astype(I64) if outs else np.empty(0, I64)), out_range
