@@ -7,12 +7,13 @@
 // Every piece of arithmetic goes through the C ABI of gsb200.h with raw device pointers and torch's current
 // stream.  The state kept per graph and the effect of each method on it follow gs::Graph
 // (src/graph.h:113-126, src/graph.cc).  Where the reference aborts the process (LOG(FATAL)), TORCH_CHECK
-// raises instead.  Compact-id (DCSC/DCSR) and induced-subgraph methods are not provided.
+// raises instead.  Compact-id (DCSC/DCSR) layouts are not provided.
 #include <c10/cuda/CUDAStream.h>
 #include <torch/custom_class.h>
 #include <torch/script.h>
 
 #include <atomic>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -476,6 +477,118 @@ class Graph : public torch::CustomClassHolder {
     return {ret, offsets};
   }
 
+  // FusedBidirSlicing / BatchFusedBidirSlicing (src/graph.cc:116-170): seed columns x listed rows in one pass.
+  c10::intrusive_ptr<Graph> ColRowSliceImpl(Tensor column_seeds, const Tensor* col_ptr, Tensor row_seeds,
+                                            const Tensor* row_ptr) {
+    CreateSparseFormat(kCSC);
+    const bool batched = col_ptr != nullptr;
+    Tensor cs = Ids(column_seeds, "column seeds"), rs = Ids(row_seeds, "row seeds");
+    Tensor col_ids = col_ids_.has_value() ? col_ids_.value().index({cs}) : cs;
+    Tensor row_ids = batched ? rs : (row_ids_.has_value() ? row_ids_.value().index({rs}) : rs);
+    Tensor cp = batched ? Ids(*col_ptr, "col_ptr") : Tensor(), rp = batched ? Ids(*row_ptr, "row_ptr") : Tensor();
+    if (batched) TORCH_CHECK(cp.numel() == rp.numel(), "col_ptr and row_ptr must have the same length");
+    const CSC& g = *csc_;
+    const int64_t S = col_ids.numel(), R = row_ids.numel(), G = batched ? cp.numel() - 1 : 1;
+    Tensor sub_indptr = EmptyIds(S + 1, g.indptr);
+    int64_t nnz = 0;
+    Check(gsb_col_row_slice_count(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(col_ids), S, IP(row_ids), R, IP(cp),
+                                  IP(rp), G, num_rows_, MP(sub_indptr), &nnz),
+          "gsb_col_row_slice_count");
+    Tensor indices = EmptyIds(nnz, g.indptr), select = EmptyIds(nnz, g.indptr), out_data;
+    const float* data_in = nullptr;
+    float* data_out = nullptr;
+    if (data_.has_value()) {
+      out_data = torch::empty({nnz}, data_.value().options());
+      data_in = FP(data_.value());
+      data_out = nnz ? out_data.data_ptr<float>() : nullptr;
+    }
+    Tensor eids = g.e_ids.value_or(Tensor());
+    Check(gsb_col_row_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(col_ids), S, IP(row_ids), R, IP(cp),
+                                 IP(rp), G, num_rows_, batched ? 0 : 1, IP(sub_indptr), MP(indices), MP(select),
+                                 data_in, IP(eids), data_out),
+          "gsb_col_row_slice_fill");
+    auto ret = batched ? c10::make_intrusive<Graph>(true, col_ids, row_ids_, S, num_rows_)
+                       : c10::make_intrusive<Graph>(true, col_ids, row_ids, S, R);
+    ret->csc_ = std::make_shared<CSC>(CSC{sub_indptr, indices, torch::nullopt});
+    ret->num_edges_ = nnz;
+    if (out_data.defined()) ret->data_ = out_data;
+    return ret;
+  }
+  c10::intrusive_ptr<Graph> FusedBidirSlicing(Tensor column_seeds, Tensor row_seeds) {
+    return ColRowSliceImpl(column_seeds, nullptr, row_seeds, nullptr);
+  }
+  c10::intrusive_ptr<Graph> BatchFusedBidirSlicing(Tensor column_seeds, Tensor col_ptr, Tensor row_seeds,
+                                                   Tensor row_ptr) {
+    return ColRowSliceImpl(column_seeds, &col_ptr, row_seeds, &row_ptr);
+  }
+
+  // EDivUSum (src/graph.cc:732-755): data / divisor[row] and the per-column sums of the quotient.
+  std::tuple<c10::intrusive_ptr<Graph>, Tensor> EDivUSum(Tensor divisor_in) {
+    CreateSparseFormat(kCOO);
+    Tensor divisor = Floats(divisor_in, "divisor");
+    Tensor in = data_.has_value() ? data_.value() : Tensor();
+    if (in.defined() && coo_->e_ids.has_value()) in = in.index({coo_->e_ids.value()});
+    if (in.defined()) in = Floats(in, "edge data");
+    Tensor out = torch::empty({num_edges_}, divisor.options());
+    Tensor out_sum = torch::zeros({num_cols_}, divisor.options());
+    Check(gsb_edge_div_u_sum(Ctx(), Stream(), IP(coo_->row), IP(coo_->col), num_edges_, FP(in), FP(divisor),
+                             num_edges_ ? out.data_ptr<float>() : nullptr, num_cols_ ? out_sum.data_ptr<float>() : nullptr),
+          "gsb_edge_div_u_sum");
+    if (coo_->e_ids.has_value()) {
+      Tensor full = torch::empty_like(out);
+      full.index_put_({coo_->e_ids.value()}, out);
+      out = full;
+    }
+    return {SameStructure(out), out_sum};
+  }
+
+  // Split (src/graph.cc:987-1017): consecutive chunks of split_size columns as separate graphs.
+  std::vector<c10::intrusive_ptr<Graph>> Split(int64_t split_size) {
+    CreateSparseFormat(kCSC);
+    TORCH_CHECK(split_size > 0, "split_size must be positive");
+    const int64_t n = csc_->indptr.numel() - 1;
+    std::vector<int64_t> bounds;
+    for (int64_t c = 0; c < n; c += split_size) bounds.push_back(c);
+    bounds.push_back(n);
+    const int64_t parts = (int64_t)bounds.size() - 1;
+    Tensor offsets = torch::tensor(bounds, torch::dtype(torch::kInt64)).to(Device());
+    Tensor out = EmptyIds(n + parts, csc_->indptr);
+    Check(gsb_split_indptr(Ctx(), Stream(), IP(csc_->indptr), IP(offsets), parts, 0, MP(out)), "gsb_split_indptr");
+    Tensor edge_bounds = csc_->indptr.index({offsets}).to(torch::kCPU);
+    const int64_t* eb = edge_bounds.data_ptr<int64_t>();
+    std::vector<c10::intrusive_ptr<Graph>> ret;
+    for (int64_t i = 0; i < parts; ++i) {
+      const int64_t cols = bounds[i + 1] - bounds[i];
+      Tensor indptr = out.narrow(0, bounds[i] + i, cols + 1);
+      Tensor indices = csc_->indices.narrow(0, eb[i], eb[i + 1] - eb[i]);
+      OptTensor e_ids;
+      if (csc_->e_ids.has_value()) e_ids = csc_->e_ids.value().narrow(0, eb[i], eb[i + 1] - eb[i]);
+      OptTensor nid;
+      if (col_ids_.has_value()) nid = col_ids_.value().narrow(0, bounds[i], cols);
+      auto g = c10::make_intrusive<Graph>(true, nid, row_ids_, cols, num_rows_);
+      g->csc_ = std::make_shared<CSC>(CSC{indptr, indices, e_ids});
+      g->num_edges_ = indices.numel();
+      ret.push_back(g);
+    }
+    return ret;
+  }
+
+  // Decode: strips the batch encoding from both id maps.  (The reference aborts whenever an id map is present and
+  // dereferences it when it is absent, src/graph.cc:1035-1040; this does what the name says.)
+  void Decode(int64_t encoding_size) {
+    TORCH_CHECK(col_ids_.has_value() && row_ids_.has_value(), "Error: Decoding should have both row and column id");
+    Tensor c = Ids(col_ids_.value(), "col ids"), r = Ids(row_ids_.value(), "row ids");
+    Tensor oc = torch::empty_like(c), orow = torch::empty_like(r);
+    Check(gsb_batch_decode(Ctx(), Stream(), IP(c), c.numel(), encoding_size, MP(oc)), "gsb_batch_decode");
+    Check(gsb_batch_decode(Ctx(), Stream(), IP(r), r.numel(), encoding_size, MP(orow)), "gsb_batch_decode");
+    col_ids_ = oc, row_ids_ = orow;
+  }
+
+  const CSC& CscForWalk() {
+    CreateSparseFormat(kCSC);
+    return *csc_;
+  }
+
   // Sampling / SamplingProbs (src/graph.cc:393-529)
   c10::intrusive_ptr<Graph> SampleImpl(int64_t axis, const Tensor* probs, int64_t fanout, bool replace,
                                        int64_t on_format, int64_t output_format) {
@@ -736,6 +849,55 @@ class Graph : public torch::CustomClassHolder {
   OptTensor data_, col_ids_, row_ids_;
 };
 
+// ---- HeteroGraph (src/hetero_graph.h:38-70, src/hetero_graph.cc:20-75) ----------------------------------------
+class HeteroGraph : public torch::CustomClassHolder {
+ public:
+  HeteroGraph() {}
+  void LoadFromHomo(const std::vector<std::string>& node_types,
+                    const std::vector<std::tuple<std::string, std::string, std::string>>& edge_types,
+                    const std::vector<c10::intrusive_ptr<Graph>>& edge_relations) {
+    TORCH_CHECK(edge_types.size() == edge_relations.size(), "edge_types and edge_relations differ in length");
+    TORCH_CHECK(edge_relations.size() <= GSB_MAX_RELATIONS, "at most ", GSB_MAX_RELATIONS, " relations");
+    node_type_.clear(), edge_type_.clear(), relations_.clear();
+    for (size_t i = 0; i < node_types.size(); ++i) node_type_[node_types[i]] = (int64_t)i;
+    for (size_t i = 0; i < edge_types.size(); ++i) {
+      edge_type_[std::get<1>(edge_types[i])] = (int64_t)i;
+      relations_.push_back(edge_relations[i]);
+    }
+  }
+  c10::intrusive_ptr<Graph> GetHomoGraph(const std::string& edge_type) const {
+    auto it = edge_type_.find(edge_type);
+    TORCH_CHECK(it != edge_type_.end(), "unknown edge type ", edge_type);
+    return relations_[it->second];
+  }
+  Tensor MetapathRandomWalkFused(Tensor seeds, const std::vector<std::string>& metapath) {
+    Tensor s = Ids(seeds, "seeds");
+    const int64_t L = (int64_t)metapath.size();
+    TORCH_CHECK(L <= GSB_MAX_METAPATH, "metapath longer than ", GSB_MAX_METAPATH);
+    std::vector<int64_t> path;
+    for (const auto& name : metapath) {
+      auto it = edge_type_.find(name);
+      TORCH_CHECK(it != edge_type_.end(), "unknown edge type ", name);
+      path.push_back(it->second);
+    }
+    const int64_t* ip[GSB_MAX_RELATIONS];
+    const int64_t* ix[GSB_MAX_RELATIONS];
+    for (size_t i = 0; i < relations_.size(); ++i) {
+      const CSC& g = relations_[i]->CscForWalk();
+      ip[i] = IP(g.indptr), ix[i] = IP(g.indices);
+    }
+    Tensor out = EmptyIds(s.numel() * (L + 1), s);
+    Check(gsb_metapath_random_walk(Ctx(), Stream(), ip, ix, (int)relations_.size(), path.data(), L, IP(s), s.numel(),
+                                   NextSeed(), 0, 0, MP(out)),
+          "gsb_metapath_random_walk");
+    return out.reshape({s.numel(), L + 1});
+  }
+
+ private:
+  std::map<std::string, int64_t> node_type_, edge_type_;
+  std::vector<c10::intrusive_ptr<Graph>> relations_;
+};
+
 // ---- free operators (src/tensor_ops.cc:5-16, src/pybind.cc:62-85) ---------------------------------------------------
 static std::tuple<Tensor, Tensor> ListSampleImpl(const Tensor& data_in, const Tensor* probs, int64_t k, bool replace) {
   Tensor data = Ids(data_in, "data"), p;
@@ -926,6 +1088,12 @@ static std::tuple<Tensor, Tensor> BatchListSamplingProbs(Tensor probs_in, int64_
         "gsb_batch_list_sample");
   return {out.narrow(0, 0, n), out_range};
 }
+static Tensor IndexSearch(Tensor origin_in, Tensor keys_in) {  // src/tensor_ops.cc:23-31
+  Tensor origin = Ids(origin_in, "origin_data"), keys = Ids(keys_in, "keys");
+  Tensor out = torch::empty_like(keys);
+  Check(gsb_index_search(Ctx(), Stream(), IP(origin), origin.numel(), IP(keys), keys.numel(), MP(out)), "gsb_index_search");
+  return out;
+}
 static void SetSeed(int64_t seed) {
   g_seed_base.store((uint64_t)seed);
   g_seed_counter.store(0);
@@ -934,6 +1102,7 @@ static void SetSeed(int64_t seed) {
 }  // namespace gsglue
 
 using gsglue::Graph;
+using gsglue::HeteroGraph;
 
 #define GS_DEF2(camel, snake, fn) .def(camel, fn).def(snake, fn)
 
@@ -947,6 +1116,11 @@ TORCH_LIBRARY(gs_classes, m) {
       GS_DEF2("_CAPI_GetNumEdges", "_CAPI_get_num_edges", &Graph::GetNumEdges)
       GS_DEF2("_CAPI_Slicing", "_CAPI_slicing", &Graph::Slicing)
       GS_DEF2("_CAPI_BatchSlicing", "_CAPI_batch_slicing", &Graph::BatchSlicing)
+      GS_DEF2("_CAPI_FusionSlicing", "_CAPI_fusion_slicing", &Graph::FusedBidirSlicing)
+      GS_DEF2("_CAPI_BatchFusionSlicing", "_CAPI_batch_fusion_slicing", &Graph::BatchFusedBidirSlicing)
+      GS_DEF2("_CAPI_EDivUSum", "_CAPI_e_div_u_sum", &Graph::EDivUSum)
+      GS_DEF2("_CAPI_Split", "_CAPI_split", &Graph::Split)
+      GS_DEF2("_CAPI_Decode", "_CAPI_decode", &Graph::Decode)
       GS_DEF2("_CAPI_Sampling", "_CAPI_sampling", &Graph::Sampling)
       GS_DEF2("_CAPI_SamplingWithProbs", "_CAPI_sampling_with_probs", &Graph::SamplingProbs)
       GS_DEF2("_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_fused_columnwise_slicing_sampling",
@@ -975,6 +1149,13 @@ TORCH_LIBRARY(gs_classes, m) {
       GS_DEF2("_CAPI_GetCOO", "_CAPI_get_coo", &Graph::GetCOOTensor)
       GS_DEF2("_CAPI_SetCOO", "_CAPI_set_coo", &Graph::SetCOOByTensor)
       GS_DEF2("_CAPI_SetMetadata", "_CAPI_set_metadata", &Graph::SetMetaData);
+
+  m.class_<HeteroGraph>("HeteroGraph")
+      .def(torch::init<>())
+      GS_DEF2("_CAPI_LoadFromHomo", "_CAPI_load_from_homo", &HeteroGraph::LoadFromHomo)
+      GS_DEF2("_CAPI_GetHomoGraph", "_CAPI_get_homo_graph", &HeteroGraph::GetHomoGraph)
+      GS_DEF2("_CAPI_MetapathRandomWalkFused", "_CAPI_metapath_random_walk_fused",
+              &HeteroGraph::MetapathRandomWalkFused);
 }
 
 TORCH_LIBRARY(gs_ops, m) {
@@ -1006,6 +1187,7 @@ TORCH_LIBRARY(gs_ops, m) {
   m.def("_CAPI_BatchDecode", &gsglue::BatchDecode);
   m.def("_CAPI_GetBatchOffsets", &gsglue::GetBatchOffsets);
   m.def("_CAPI_COORowSlicingGlobalId", &gsglue::COORowSlicingGlobalId);
+  m.def("_CAPI_IndexSearch", &gsglue::IndexSearch);
   m.def("COORowSlicingGlobalId", &gsglue::COORowSlicingGlobalId);
   m.def("_CAPI_SetSeed", &gsglue::SetSeed);
 }

@@ -30,9 +30,28 @@ __device__ __forceinline__ i64 walk_step(const i64* __restrict__ indptr, const i
   return __ldg(indices + b + (i64)bounded_from_word(word, dd));
 }
 
-template <int LAYOUT>
-__global__ void __launch_bounds__(kWalkThreads, 4) k_random_walk(const i64* __restrict__ indptr,
-                                                              const i64* __restrict__ indices,
+// Which graph a step walks on.  One graph for the homogeneous walk; for a metapath walk
+// (src/cuda/fusion/metapath_random_walk.cu:9-50) step s uses relation path[s] of up to kMaxRelations CSC graphs.
+struct OneGraph {
+  const i64* indptr;
+  const i64* indices;
+  __device__ __forceinline__ const i64* indptr_at(i64) const { return indptr; }
+  __device__ __forceinline__ const i64* indices_at(i64) const { return indices; }
+};
+
+constexpr int kMaxRelations = GSB_MAX_RELATIONS;
+constexpr int kMaxPath = GSB_MAX_METAPATH;
+
+struct Metapath {
+  const i64* indptr[kMaxRelations];
+  const i64* indices[kMaxRelations];
+  unsigned char path[kMaxPath];
+  __device__ __forceinline__ const i64* indptr_at(i64 s) const { return indptr[path[s]]; }
+  __device__ __forceinline__ const i64* indices_at(i64 s) const { return indices[path[s]]; }
+};
+
+template <int LAYOUT, class Graphs>
+__global__ void __launch_bounds__(kWalkThreads, 4) k_random_walk(const __grid_constant__ Graphs g,
                                                               const i64* __restrict__ seeds, i64 W, i64 L, u64 seed,
                                                               i64 walker_offset, i64* __restrict__ out) {
   __shared__ i64 s_buf[LAYOUT == 1 ? (kWalkThreads / 32) * 32 * (kChunk + 1) : 1];
@@ -47,7 +66,7 @@ __global__ void __launch_bounds__(kWalkThreads, 4) k_random_walk(const i64* __re
     for (i64 s = 0; s < L; ++s) {
       if ((s & 3) == 0) blk = rand_block(seed, item, (u64)(s >> 2), STREAM_WALK);
       const uint32_t word = (s & 3) == 0 ? blk.v[0] : (s & 3) == 1 ? blk.v[1] : (s & 3) == 2 ? blk.v[2] : blk.v[3];
-      cur = walk_step(indptr, indices, cur, word);
+      cur = walk_step(g.indptr_at(s), g.indices_at(s), cur, word);
       out[(s + 1) * W + w] = cur;
     }
   } else {
@@ -66,7 +85,7 @@ __global__ void __launch_bounds__(kWalkThreads, 4) k_random_walk(const i64* __re
           if ((s & 3) == 0) blk = rand_block(seed, item, (u64)(s >> 2), STREAM_WALK);
           const uint32_t word =
               (s & 3) == 0 ? blk.v[0] : (s & 3) == 1 ? blk.v[1] : (s & 3) == 2 ? blk.v[2] : blk.v[3];
-          if (active) cur = walk_step(indptr, indices, cur, word);
+          if (active) cur = walk_step(g.indptr_at(s), g.indices_at(s), cur, word);
         }
         buf[lane * (kChunk + 1) + q] = cur;
       }
@@ -96,10 +115,44 @@ extern "C" int gsb_random_walk(gsb_ctx* ctx, void* stream_, const int64_t* indpt
   const int grid = grid_for(W, kWalkThreads);
   {
     ScopedKernelTimer timer(ctx, KID_RANDOM_WALK, stream);
+    const OneGraph g{indptr, indices};
     if (layout == 0)
-      k_random_walk<0><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+      k_random_walk<0, OneGraph><<<grid, kWalkThreads, 0, stream>>>(g, seeds, W, L, (u64)seed, walker_offset, out);
     else
-      k_random_walk<1><<<grid, kWalkThreads, 0, stream>>>(indptr, indices, seeds, W, L, (u64)seed, walker_offset, out);
+      k_random_walk<1, OneGraph><<<grid, kWalkThreads, 0, stream>>>(g, seeds, W, L, (u64)seed, walker_offset, out);
+  }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+extern "C" int gsb_metapath_random_walk(gsb_ctx* ctx, void* stream_, const int64_t* const* indptr_host,
+                                        const int64_t* const* indices_host, int num_relations,
+                                        const int64_t* metapath_host, int64_t L, const int64_t* seeds, int64_t W,
+                                        uint64_t seed, int layout, int64_t walker_offset, int64_t* out) {
+  GSB_REQUIRE(ctx && indptr_host && indices_host && W >= 0 && L >= 0 && (layout == 0 || layout == 1),
+              GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(num_relations >= 1 && num_relations <= kMaxRelations && L <= kMaxPath, GSB_ERR_UNSUPPORTED);
+  GSB_REQUIRE(L == 0 || metapath_host, GSB_ERR_INVALID_ARGUMENT);
+  if (W == 0) return GSB_OK;
+  GSB_REQUIRE(seeds && out, GSB_ERR_INVALID_ARGUMENT);
+  Metapath g{};
+  for (int r = 0; r < num_relations; ++r) {
+    GSB_REQUIRE(indptr_host[r], GSB_ERR_INVALID_ARGUMENT);
+    g.indptr[r] = indptr_host[r];
+    g.indices[r] = indices_host[r];
+  }
+  for (i64 s = 0; s < L; ++s) {
+    GSB_REQUIRE(metapath_host[s] >= 0 && metapath_host[s] < num_relations, GSB_ERR_INVALID_ARGUMENT);
+    g.path[s] = (unsigned char)metapath_host[s];
+  }
+  cudaStream_t stream = (cudaStream_t)stream_;
+  const int grid = grid_for(W, kWalkThreads);
+  {
+    ScopedKernelTimer timer(ctx, KID_RANDOM_WALK, stream);
+    if (layout == 0)
+      k_random_walk<0, Metapath><<<grid, kWalkThreads, 0, stream>>>(g, seeds, W, L, (u64)seed, walker_offset, out);
+    else
+      k_random_walk<1, Metapath><<<grid, kWalkThreads, 0, stream>>>(g, seeds, W, L, (u64)seed, walker_offset, out);
   }
   GSB_LAUNCH_OK();
   return GSB_OK;

@@ -58,6 +58,22 @@ __global__ void __launch_bounds__(kSegThreads) k_segment_sum_coo(const i64* __re
   }
 }
 
+// out_data[e] = data[e] / divisor[row[e]] and out_sum[col[e]] += out_data[e] in one pass over the edges
+// (gs::impl::fusion::COOEDivUSum, src/cuda/fusion/edge_map_reduce.cu:10-24).
+__global__ void __launch_bounds__(kSegThreads) k_edge_div_u_sum(const i64* __restrict__ row,
+                                                                const i64* __restrict__ col, i64 E,
+                                                                const float* __restrict__ data,
+                                                                const float* __restrict__ divisor,
+                                                                float* __restrict__ out_data,
+                                                                float* __restrict__ out_sum) {
+  for (i64 e = (i64)blockIdx.x * kSegThreads + threadIdx.x; e < E; e += (i64)gridDim.x * kSegThreads) {
+    const float x = data ? __ldg(data + e) : 1.0f;
+    const float v = __fdiv_rn(x, __ldg(divisor + __ldg(row + e)));
+    out_data[e] = v;
+    atomicAdd(out_sum + __ldg(col + e), v);
+  }
+}
+
 // One CTA per long segment (taken from the list the warp kernels filled): strided partial sums, a fixed-order
 // shared-memory reduction (deterministic), then the result / the normalised values.
 template <bool NORMALIZE>
@@ -196,6 +212,18 @@ int gsb_segment_normalize_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr
     ScopedKernelTimer timer(ctx, KID_SEGMENT, stream);
     k_segment_long<true><<<kNumSMs * 2, kSegThreads, 0, stream>>>(indptr, e_ids, data, 1, out, long_list, long_count);
   }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int gsb_edge_div_u_sum(gsb_ctx* ctx, void* stream_, const int64_t* coo_row, const int64_t* coo_col, int64_t E,
+                       const float* data, const float* divisor, float* out_data, float* out_sum_zeroed) {
+  GSB_REQUIRE(ctx && E >= 0, GSB_ERR_INVALID_ARGUMENT);
+  if (E == 0) return GSB_OK;
+  GSB_REQUIRE(coo_row && coo_col && divisor && out_data && out_sum_zeroed, GSB_ERR_INVALID_ARGUMENT);
+  ScopedKernelTimer timer(ctx, KID_SEGMENT, (cudaStream_t)stream_);
+  k_edge_div_u_sum<<<min(grid_for(E, kSegThreads), kNumSMs * 16), kSegThreads, 0, (cudaStream_t)stream_>>>(
+      coo_row, coo_col, E, data, divisor, out_data, out_sum_zeroed);
   GSB_LAUNCH_OK();
   return GSB_OK;
 }

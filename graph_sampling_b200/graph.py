@@ -287,6 +287,71 @@ class Graph:
             ret.data_ = r[5]
         return ret, coo_offsets
 
+    # ---- induced subgraph (src/graph.cc:116-170) ----------------------------------------------------------
+    def FusedBidirSlicing(self, column_seeds, row_seeds):
+        """Columns `column_seeds` x rows `row_seeds` of the CSC in one pass; rows are renumbered to their position in
+        row_seeds.  Edge data follows the kept edges (the reference gathers it with positions inside the column
+        slice, src/graph.cc:131-137, which only works when every column is a seed)."""
+        self.CreateSparseFormat(_CSC)
+        col_ids = self.col_ids_[column_seeds] if self.col_ids_ is not None else column_seeds
+        row_ids = self.row_ids_[row_seeds] if self.row_ids_ is not None else row_seeds
+        data, e_ids = self._gather_args(self.csc_)
+        r = ops.csc_col_row_slicing(self.csc_.indptr, self.csc_.indices, col_ids, row_ids, data=data, e_ids=e_ids)
+        ret = self._child(col_ids, row_ids, column_seeds.numel(), row_seeds.numel())
+        ret.csc_ = CSC(r[0], r[1])
+        ret.num_edges_ = r[1].numel()
+        if data is not None:
+            ret.data_ = r[3]
+        return ret
+
+    def BatchFusedBidirSlicing(self, column_seeds, col_ptr, row_seeds, row_ptr):
+        """Super-batch form: a column of batch b keeps the rows listed for batch b; row ids stay global."""
+        self.CreateSparseFormat(_CSC)
+        col_ids = self.col_ids_[column_seeds] if self.col_ids_ is not None else column_seeds
+        data, e_ids = self._gather_args(self.csc_)
+        r = ops.csc_col_row_slicing(self.csc_.indptr, self.csc_.indices, col_ids, row_seeds, col_ptr, row_ptr,
+                                    self.num_rows_, data=data, e_ids=e_ids)
+        ret = self._child(col_ids, self.row_ids_, column_seeds.numel(), self.num_rows_)
+        ret.csc_ = CSC(r[0], r[1])
+        ret.num_edges_ = r[1].numel()
+        if data is not None:
+            ret.data_ = r[3]
+        return ret
+
+    def EDivUSum(self, divisor):
+        """(Graph with data / divisor[row], per-column sums of that) — src/graph.cc:732-755.  Edge data keeps its
+        order; the reference pairs data_[i] with COO edge i and is only right when the COO carries no edge ids."""
+        self.CreateSparseFormat(_COO)
+        e_ids = self.coo_.e_ids
+        data = self.data_ if (self.data_ is None or e_ids is None) else self.data_[e_ids]
+        out, out_sum = ops.coo_e_div_u_sum(self.coo_.row, self.coo_.col, data, divisor, self.num_cols_)
+        if e_ids is not None:
+            full = torch.empty_like(out)
+            full[e_ids] = out
+            out = full
+        return self._same_structure_child(out), out_sum
+
+    def Split(self, split_size):
+        """Consecutive chunks of split_size columns as separate graphs (src/graph.cc:987-1017)."""
+        self.CreateSparseFormat(_CSC)
+        n = self.csc_.indptr.numel() - 1
+        split_size = int(split_size)
+        bounds = list(range(0, n, split_size)) + [n]
+        offsets = torch.tensor(bounds, dtype=torch.int64, device=self.csc_.indptr.device)
+        indptrs = ops.indptr_split_by_offset(self.csc_.indptr, offsets)
+        edge_bounds = self.csc_.indptr[offsets]
+        indices = ops.split_by_offset(self.csc_.indices, edge_bounds)
+        eids = ops.split_by_offset(self.csc_.e_ids, edge_bounds) if self.csc_.e_ids is not None else None
+        nids = torch.split(self.col_ids_, split_size) if self.col_ids_ is not None else None
+        out = []
+        for i in range(len(bounds) - 1):
+            g = self._child(nids[i] if nids is not None else None, self.row_ids_, bounds[i + 1] - bounds[i],
+                            self.num_rows_)
+            g.csc_ = CSC(indptrs[i], indices[i], eids[i] if eids is not None else None)
+            g.num_edges_ = indices[i].numel()
+            out.append(g)
+        return out
+
     # ---- Sampling / SamplingProbs (src/graph.cc:393-529) ---------------------------------------------------
     def _sampling_impl(self, axis, fanout, replace, on_format, output_format, probs, seed):
         self.CreateSparseFormat(on_format)
@@ -546,7 +611,13 @@ class Graph:
     def _out_of_scope(self, *a, **k):
         raise NotImplementedError("induced-subgraph / compact-id methods are outside the sampling hot path")
 
-    FusedBidirSlicing = BatchFusedBidirSlicing = Split = Decode = EDivUSum = _out_of_scope
+    def Decode(self, encoding_size):
+        """Strips the batch encoding from both id maps.  (The reference's version aborts whenever an id map is
+        present and dereferences it when it is absent, src/graph.cc:1035-1040; this one does what its name says.)"""
+        if self.col_ids_ is None or self.row_ids_ is None:
+            _fatal("Error: Decoding should have both row and column id")
+        self.col_ids_ = ops.batch_decode(self.col_ids_, encoding_size)
+        self.row_ids_ = ops.batch_decode(self.row_ids_, encoding_size)
 
 
 # Registered names: src/pybind.cc:14-52 (CamelCase) and the spelling used by python/gs + examples.
@@ -586,7 +657,7 @@ _NAME_MAP = {
     "SetMetaData": ("_CAPI_SetMetadata", "_CAPI_set_metadata"),
     "FusedBidirSlicing": ("_CAPI_FusionSlicing", "_CAPI_fusion_slicing"),
     "BatchSlicing": ("_CAPI_BatchSlicing", "_CAPI_batch_slicing"),
-    "BatchFusedBidirSlicing": ("_CAPI_BatchFusionSlicing",),
+    "BatchFusedBidirSlicing": ("_CAPI_BatchFusionSlicing", "_CAPI_batch_fusion_slicing"),
     "Split": ("_CAPI_Split",),
     "Decode": ("_CAPI_Decode",),
     "EDivUSum": ("_CAPI_EDivUSum",),
@@ -604,6 +675,40 @@ def ListSampling(data, num_picks, replace, seed=None):
 def ListSamplingProbs(data, probs, num_picks, replace, seed=None):
     """gs::ListSamplingProbs (src/tensor_ops.cc:11-16); gs_ops._CAPI_ListSamplingWithProbs / list_sampling_with_probs."""
     return ops.list_sampling(data, num_picks, replace, probs=probs, seed=seed)
+
+
+class HeteroGraph:
+    """gs::HeteroGraph (src/hetero_graph.h:38-70, src/hetero_graph.cc:20-75): named relations, each a homogeneous
+    Graph, and the fused metapath random walk over them."""
+
+    def __init__(self):
+        self.node_type_mapping_, self.edge_type_mapping_ = {}, {}
+        self.hetero_edges_ = {}
+
+    def LoadFromHomo(self, node_types, edge_types, edge_relations):
+        if len(edge_types) != len(edge_relations):
+            _fatal("edge_types and edge_relations differ in length")
+        self.node_type_mapping_ = {name: i for i, name in enumerate(node_types)}
+        self.edge_type_mapping_, self.hetero_edges_ = {}, {}
+        for i, ((src, etype, dst), graph) in enumerate(zip(edge_types, edge_relations)):
+            self.edge_type_mapping_[etype] = i
+            graph.CreateSparseFormat(_CSC)
+            self.hetero_edges_[i] = (self.node_type_mapping_[src], self.node_type_mapping_[dst], graph)
+
+    def GetHomoGraph(self, edge_type):
+        return self.hetero_edges_[self.edge_type_mapping_[edge_type]][2]
+
+    def MetapathRandomWalkFused(self, seeds, metapath, seed=None, layout=0):
+        """Trace of shape [num_seeds, len(metapath) + 1]; layout 0 is the reference's step-major memory viewed
+        with that shape (as Graph.RandomWalk), layout 1 a true walker-major trace."""
+        path = [self.edge_type_mapping_[name] for name in metapath]
+        graphs = [(self.hetero_edges_[i][2].csc_.indptr, self.hetero_edges_[i][2].csc_.indices)
+                  for i in range(len(self.hetero_edges_))]
+        return ops.fused_metapath_random_walk(seeds, path, graphs, seed=seed, layout=layout)
+
+    _CAPI_LoadFromHomo = _CAPI_load_from_homo = LoadFromHomo
+    _CAPI_GetHomoGraph = _CAPI_get_homo_graph = GetHomoGraph
+    _CAPI_MetapathRandomWalkFused = _CAPI_metapath_random_walk_fused = MetapathRandomWalkFused
 
 
 # Free operators of the super-batch family under their registered names (src/pybind.cc:65-84).
@@ -629,6 +734,7 @@ def _batch_ops():
         "_CAPI_BatchDecode": o.batch_decode,
         "_CAPI_GetBatchOffsets": o.get_batch_offsets,
         "_CAPI_COORowSlicingGlobalId": o.coo_row_slicing_global_id,
+        "_CAPI_IndexSearch": o.index_search,
     }
 
 

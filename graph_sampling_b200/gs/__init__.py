@@ -6,7 +6,7 @@
 reference are compiler and framework glue around the hot path and are not provided; `Matrix.to_block`
 returns a plain DGL-free block description instead of a DGL object.
 """
-from ..graph import Graph, ListSampling, ListSamplingProbs, Unique, gs_ops, _COO, _CSC, _CSR, _DCSC, _DCSR
+from ..graph import Graph, HeteroGraph, ListSampling, ListSamplingProbs, Unique, gs_ops, _COO, _CSC, _CSR, _DCSC, _DCSR
 from ..ops import set_seed
 from . import ops, utils
 from .matrix import Block, Matrix
@@ -14,5 +14,5 @@ from .matrix import Block, Matrix
 list_sampling = ListSampling
 list_sampling_with_probs = ListSamplingProbs
 
-__all__ = ["Graph", "Matrix", "Block", "ops", "utils", "gs_ops", "set_seed", "list_sampling", "list_sampling_with_probs",
+__all__ = ["Graph", "HeteroGraph", "Matrix", "Block", "ops", "utils", "gs_ops", "set_seed", "list_sampling", "list_sampling_with_probs",
            "ListSampling", "ListSamplingProbs", "Unique", "_COO", "_CSC", "_CSR", "_DCSC", "_DCSR"]

@@ -267,6 +267,82 @@ def fused_random_walk(seeds, walk_length, indices, indptr, seed=None, layout=0, 
     return out.reshape(W, L + 1)
 
 
+def fused_metapath_random_walk(seeds, metapath, graphs, seed=None, layout=0, walker_offset=0, ctx=None):
+    """FusedMetapathRandomWalkCUDA (src/cuda/fusion/metapath_random_walk.cu:52-67): `graphs` is a list of
+    (indptr, indices) CSC pairs, `metapath` the relation index of every step.  Layouts as in fused_random_walk."""
+    seeds = _i64(seeds, "seeds")
+    pairs = [(_i64(a, "indptr"), _i64(b, "indices")) for a, b in graphs]
+    path = [int(r) for r in metapath]
+    ctx = ctx or default_context(seeds.device)
+    W, L = seeds.numel(), len(path)
+    out = _empty(W * (L + 1), seeds)
+    ip = (c_vp * max(1, len(pairs)))(*[a.data_ptr() for a, _ in pairs])
+    ix = (c_vp * max(1, len(pairs)))(*[b.data_ptr() for _, b in pairs])
+    mp = (c_i64 * max(1, L))(*path)
+    ctx.check(ctx.lib.gsb_metapath_random_walk(ctx.handle, _stream(), ip, ix, c_int(len(pairs)), mp, c_i64(L),
+                                               _p(seeds), c_i64(W), c_u64(next_seed(seed)), c_int(int(layout)),
+                                               c_i64(int(walker_offset)), _p(out)), "gsb_metapath_random_walk")
+    return out.reshape(W, L + 1)
+
+
+def csc_col_row_slicing(indptr, indices, column_ids, row_ids, col_ptr=None, row_ptr=None, encoding_size=0,
+                        data=None, e_ids=None, ctx=None):
+    """CSCColRowSlicingCUDA / BatchCSCColRowSlicingCUDA (src/cuda/fusion/column_row_slicing.cu:101-365) →
+    (sub_indptr, sub_indices, select_index[, sliced_data]).  Without col_ptr / row_ptr the kept row ids are
+    renumbered to their position in row_ids; with them (the super-batch form) a column of batch b is matched
+    against batch b's rows and row ids stay as they are.  select_index points into `indices`."""
+    indptr, indices = _i64(indptr, "indptr"), _i64(indices, "indices")
+    column_ids, row_ids = _i64(column_ids, "column_ids"), _i64(row_ids, "row_ids")
+    col_ptr, row_ptr = _i64(col_ptr, "col_ptr", True), _i64(row_ptr, "row_ptr", True)
+    data, e_ids = _f32(data, "data", True), _i64(e_ids, "e_ids", True)
+    if (col_ptr is None) != (row_ptr is None):
+        raise ValueError("col_ptr and row_ptr go together")
+    ctx = ctx or default_context(indptr.device)
+    S, R = column_ids.numel(), row_ids.numel()
+    G = 1 if col_ptr is None else col_ptr.numel() - 1
+    sub_indptr = _empty(S + 1, indptr)
+    nnz = c_i64(0)
+    ctx.check(ctx.lib.gsb_col_row_slice_count(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+                                              _p(row_ids), c_i64(R), _p(col_ptr), _p(row_ptr), c_i64(G),
+                                              c_i64(int(encoding_size)), _p(sub_indptr), ctypes.byref(nnz)),
+              "gsb_col_row_slice_count")
+    n = nnz.value
+    sub_indices, select = _empty(n, indptr), _empty(n, indptr)
+    out_data = _empty(n, indptr, torch.float32) if data is not None else None
+    ctx.check(ctx.lib.gsb_col_row_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+                                             _p(row_ids), c_i64(R), _p(col_ptr), _p(row_ptr), c_i64(G),
+                                             c_i64(int(encoding_size)), c_int(1 if col_ptr is None else 0),
+                                             _p(sub_indptr), _p(sub_indices), _p(select), _p(data), _p(e_ids),
+                                             _p(out_data)), "gsb_col_row_slice_fill")
+    if data is not None:
+        return sub_indptr, sub_indices, select, out_data
+    return sub_indptr, sub_indices, select
+
+
+def index_search(origin_data, keys, ctx=None):
+    """gs::IndexSearch (src/tensor_ops.cc:23-31): position of every key in origin_data, -1 if absent."""
+    origin_data, keys = _i64(origin_data, "origin_data"), _i64(keys, "keys")
+    ctx = ctx or default_context(keys.device)
+    out = torch.empty_like(keys)
+    ctx.check(ctx.lib.gsb_index_search(ctx.handle, _stream(), _p(origin_data), c_i64(origin_data.numel()), _p(keys),
+                                       c_i64(keys.numel()), _p(out)), "gsb_index_search")
+    return out
+
+
+def coo_e_div_u_sum(coo_row, coo_col, data, divisor, num_cols, ctx=None):
+    """COOEDivUSum (src/cuda/fusion/edge_map_reduce.cu:10-24) → (out_data, out_sum): edge data divided by the
+    divisor of the edge's row node, and the per-column sums of the result."""
+    coo_row, coo_col = _i64(coo_row, "coo_row"), _i64(coo_col, "coo_col")
+    data, divisor = _f32(data, "data", True), _f32(divisor, "divisor")
+    ctx = ctx or default_context(coo_row.device)
+    E = coo_row.numel()
+    out = _empty(E, coo_row, torch.float32)
+    out_sum = torch.zeros(int(num_cols), dtype=torch.float32, device=coo_row.device)
+    ctx.check(ctx.lib.gsb_edge_div_u_sum(ctx.handle, _stream(), _p(coo_row), _p(coo_col), c_i64(E), _p(data),
+                                         _p(divisor), _p(out), _p(out_sum)), "gsb_edge_div_u_sum")
+    return out, out_sum
+
+
 # ---------------------------------------------------------------------------------------------
 def csc_col_sampling_probs(indptr, indices, probs, fanout, replace, with_coo=True, seed=None, column_ids=None,
                            data=None, e_ids=None, ctx=None):

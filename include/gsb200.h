@@ -272,6 +272,53 @@ GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* 
                                      int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
                                      int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
 
+/* ---- induced-subgraph slicing, index search, fused divide + sum -------------------------------------------
+ * gsb_col_row_slice_count / _fill replace gs::impl::fusion::CSCColRowSlicingCUDA and BatchCSCColRowSlicingCUDA
+ * (src/cuda/fusion/column_row_slicing.cu:101-365; Graph::FusedBidirSlicing / BatchFusedBidirSlicing,
+ * src/graph.cc:116-170): of the seed columns keep the edges whose row id is in row_ids.  count writes the
+ * offsets out_indptr[S + 1] and returns the number of survivors; fill writes them in edge order.
+ * renumber != 0 writes the position of the row id in row_ids (the single-list form), 0 keeps the row id
+ * (the super-batch form).  col_ptr / row_ptr (DEVICE, G + 1 entries, both or neither) partition the columns
+ * and the row list into batches: a column of batch b is matched against the rows of batch b only;
+ * encoding_size must exceed every row id.  out_select holds positions in `indices` (the reference returns
+ * positions inside the unmaterialised column slice, which its own data gather then misuses: src/graph.cc:131-137).
+ * Both calls rebuild the row table, so nothing has to survive between them.
+ */
+GSB_API int gsb_col_row_slice_count(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                                    const int64_t* column_ids, int64_t S, const int64_t* row_ids, int64_t R,
+                                    const int64_t* col_ptr, const int64_t* row_ptr, int64_t G, int64_t encoding_size,
+                                    int64_t* out_indptr, int64_t* nnz_host);
+GSB_API int gsb_col_row_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                                   const int64_t* column_ids, int64_t S, const int64_t* row_ids, int64_t R,
+                                   const int64_t* col_ptr, const int64_t* row_ptr, int64_t G, int64_t encoding_size,
+                                   int renumber, const int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
+                                   const float* data, const int64_t* e_ids, float* out_data);
+
+/* gsb_index_search replaces gs::IndexSearch (src/tensor_ops.cc:23-31; IndexHashMapInsertCUDA + IndexHashMapSearchCUDA,
+ * src/cuda/index_search.cu): out[i] = position of keys[i] in origin (the largest one if the id repeats), -1 if
+ * absent. */
+GSB_API int gsb_index_search(gsb_ctx* ctx, void* stream, const int64_t* origin, int64_t n, const int64_t* keys,
+                             int64_t m, int64_t* out);
+
+/* gsb_edge_div_u_sum replaces gs::impl::fusion::COOEDivUSum (src/cuda/fusion/edge_map_reduce.cu:10-24;
+ * Graph::EDivUSum, src/graph.cc:732-755): out_data[e] = data[e] / divisor[coo_row[e]] (data NULL = ones) and
+ * out_sum[coo_col[e]] += out_data[e] (float atomics; out_sum must be zeroed by the caller). */
+GSB_API int gsb_edge_div_u_sum(gsb_ctx* ctx, void* stream, const int64_t* coo_row, const int64_t* coo_col, int64_t E,
+                               const float* data, const float* divisor, float* out_data, float* out_sum_zeroed);
+
+/* gsb_metapath_random_walk replaces gs::impl::fusion::FusedMetapathRandomWalkCUDA
+ * (src/cuda/fusion/metapath_random_walk.cu:9-67; HeteroGraph::MetapathRandomWalkFused, src/hetero_graph.cc:58-74):
+ * as gsb_random_walk, but step s moves along relation metapath_host[s] — one of num_relations
+ * (<= GSB_MAX_RELATIONS) CSC graphs whose DEVICE indptr / indices pointers are listed in the two HOST arrays.
+ * L (<= GSB_MAX_METAPATH) is the length of metapath_host.  With every entry 0 and one relation the result equals
+ * gsb_random_walk for the same seed. */
+#define GSB_MAX_RELATIONS 16
+#define GSB_MAX_METAPATH 256
+GSB_API int gsb_metapath_random_walk(gsb_ctx* ctx, void* stream, const int64_t* const* indptr_host,
+                                     const int64_t* const* indices_host, int num_relations,
+                                     const int64_t* metapath_host, int64_t L, const int64_t* seeds, int64_t W,
+                                     uint64_t seed, int layout, int64_t walker_offset, int64_t* out);
+
 /* ---- the rest of the super-batch family (gs_ops registry, src/pybind.cc:65-84) ---------------------------
  * Ids of G minibatches travel in one array plus a DEVICE offset array of G + 1 entries.  All sizes the
  * caller passes are exact unless called "capacity".  Calls wait for the stream only where a *_host pointer

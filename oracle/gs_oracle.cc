@@ -492,6 +492,34 @@ GSO_API void gso_random_walk(const i64* indptr, const i64* indices, const i64* s
   }
 }
 
+/* Metapath walk (src/cuda/fusion/metapath_random_walk.cu:9-50): step s moves along relation path[s]; the
+ * draw for (walker, step) is the same word as in gso_random_walk. */
+GSO_API void gso_metapath_random_walk(const i64* const* indptrs, const i64* const* indicess, const i64* path,
+                                      const i64* seeds, i64 W, i64 L, uint64_t seed, int layout,
+                                      i64 walker_offset, i64* out) {
+#pragma omp parallel for schedule(static)
+  for (i64 w = 0; w < W; ++w) {
+    i64 cur = seeds[w];
+    for (i64 s = 0; s <= L; ++s) {
+      if (layout == 0) out[s * W + w] = cur;
+      else out[w * (L + 1) + s] = cur;
+      if (s == L) break;
+      if (cur != -1) {
+        const i64* indptr = indptrs[path[s]];
+        const i64* indices = indicess[path[s]];
+        i64 b = indptr[cur], d = indptr[cur + 1] - b;
+        if (d > 0) {
+          uint64_t dd = d > 0xFFFFFFFFll ? 0xFFFFFFFFull : (uint64_t)d;
+          uint32_t r = gso_rand_u32(seed, (uint64_t)(w + walker_offset), (uint64_t)s, GSO_STREAM_WALK);
+          cur = indices[b + (i64)(((uint64_t)r * dd) >> 32)];
+        } else {
+          cur = -1;
+        }
+      }
+    }
+  }
+}
+
 /* ------------------------------------------------------------------------------------------
  * g-SDDMM over COO.  Reference: SDDMMCooKernel / SDDMMCooTreeReduceKernel,
  * src/cuda/sddmm.cu:18-104, operators src/cuda/functor.h:9-140, targets src/cuda/selector.h

@@ -473,3 +473,69 @@ def batch_list_sample(probs, range_ptr, k, seed=0):
         outs.append(take.astype(I64))
         out_range[b + 1] = out_range[b] + len(take)
     return (np.concatenate(outs).astype(I64) if outs else np.empty(0, I64)), out_range
+
+
+# ---- induced-subgraph slicing, metapath walk, index search, fused divide + sum ----------------------------
+def metapath_random_walk(graphs, path, seeds, seed=0, layout=0, walker_offset=0):
+    """src/cuda/fusion/metapath_random_walk.cu:9-67.  graphs: list of (indptr, indices); path: relation per step."""
+    gs_ = [(_i64(a), _i64(b)) for a, b in graphs]
+    ip = (ctypes.c_void_p * len(gs_))(*[a.ctypes.data for a, _ in gs_])
+    ix = (ctypes.c_void_p * len(gs_))(*[b.ctypes.data for _, b in gs_])
+    path, seeds = _i64(np.asarray(path)), _i64(seeds)
+    W, L = len(seeds), len(path)
+    out = np.empty(W * (L + 1), dtype=I64)
+    lib().gso_metapath_random_walk(ip, ix, _p(path), _p(seeds), _c(W), _c(L), _u(seed), ctypes.c_int(layout),
+                                   _c(walker_offset), _p(out))
+    return out.reshape(W, L + 1)
+
+
+def col_row_slice(indptr, indices, column_ids, row_ids, col_ptr=None, row_ptr=None, renumber=True):
+    """src/cuda/fusion/column_row_slicing.cu:101-365 → (out_indptr, out_indices, select_index into `indices`).
+    Single list: rows renumbered to their position in row_ids (largest position for a repeated id).  Batched
+    (col_ptr / row_ptr): a column of batch b keeps the rows listed for batch b; row ids stay global."""
+    indptr, indices = np.asarray(indptr, dtype=I64), np.asarray(indices, dtype=I64)
+    column_ids, row_ids = np.asarray(column_ids, dtype=I64), np.asarray(row_ids, dtype=I64)
+    S = len(column_ids)
+    if col_ptr is None:
+        col_batch, tables = np.zeros(S, dtype=I64), [{int(r): i for i, r in enumerate(row_ids)}]
+    else:
+        col_batch = _batch_ids(col_ptr, S)
+        tables = [{int(r): int(row_ptr[b]) + i for i, r in enumerate(row_ids[row_ptr[b]:row_ptr[b + 1]])}
+                  for b in range(len(row_ptr) - 1)]
+    out_indptr = np.zeros(S + 1, dtype=I64)
+    out_i, out_s = [], []
+    for c in range(S):
+        t = tables[col_batch[c]]
+        for e in range(indptr[column_ids[c]], indptr[column_ids[c] + 1]):
+            r = int(indices[e])
+            if r in t:
+                out_i.append(t[r] if renumber else r)
+                out_s.append(e)
+        out_indptr[c + 1] = len(out_i)
+    return out_indptr, np.asarray(out_i, dtype=I64), np.asarray(out_s, dtype=I64)
+
+
+def index_search(origin, keys):
+    """src/tensor_ops.cc:23-31: position of each key in origin (largest for a repeated id), -1 if absent."""
+    t = {int(v): i for i, v in enumerate(np.asarray(origin, dtype=I64))}
+    return np.asarray([t.get(int(k), -1) for k in np.asarray(keys, dtype=I64)], dtype=I64)
+
+
+def edge_div_u_sum(coo_row, coo_col, data, divisor, num_cols):
+    """src/cuda/fusion/edge_map_reduce.cu:10-24 → (out_data, out_sum)."""
+    data = np.ones(len(coo_row), dtype=np.float32) if data is None else np.asarray(data, dtype=np.float32)
+    out = (data / np.asarray(divisor, dtype=np.float32)[np.asarray(coo_row, dtype=I64)]).astype(np.float32)
+    s = np.zeros(num_cols, dtype=np.float64)
+    np.add.at(s, np.asarray(coo_col, dtype=I64), out.astype(np.float64))
+    return out, s.astype(np.float32)
+
+
+def csc_split(indptr, indices, split_size):
+    """src/cuda/graph_ops.cu:190-248: consecutive chunks of split_size columns, each with its own offsets."""
+    indptr, indices = np.asarray(indptr, dtype=I64), np.asarray(indices, dtype=I64)
+    n = len(indptr) - 1
+    parts = []
+    for c0 in range(0, n, split_size):
+        c1 = min(n, c0 + split_size)
+        parts.append((indptr[c0:c1 + 1] - indptr[c0], indices[indptr[c0]:indptr[c1]]))
+    return parts

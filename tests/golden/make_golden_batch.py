@@ -120,6 +120,52 @@ def main(out_path):
         rec[tag + "cols"] = npy(sub._CAPI_GetCols())
         rec[tag + "num"] = np.array([sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols(), sub._CAPI_GetNumEdges()])
 
+    # --- induced subgraph: seed columns x listed rows (rows renumbered), and its super-batch form (global row ids)
+    n = g_indptr.numel() - 1
+    cols = rng.choice(n, 40, replace=False).astype(np.int64)
+    rows = rng.choice(n, 120, replace=False).astype(np.int64)
+    rec["in_fs_cols"], rec["in_fs_rows"] = cols, rows
+    sub = g._CAPI_FusionSlicing(t(cols), t(rows))
+    csc = sub._CAPI_GetCSC()
+    rec["fs_indptr"], rec["fs_indices"] = npy(csc[0]), npy(csc[1])
+    rec["fs_num"] = np.array([sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols(), sub._CAPI_GetNumEdges()])
+    bcols, bcp = ragged(3, 5, 20, n)
+    brows = np.concatenate([rng.choice(n, 80, replace=False) for _ in range(3)]).astype(np.int64)
+    brp = np.arange(4, dtype=np.int64) * 80
+    rec["in_bfs_cols"], rec["in_bfs_col_ptr"], rec["in_bfs_rows"], rec["in_bfs_row_ptr"] = bcols, bcp, brows, brp
+    sub = g._CAPI_BatchFusionSlicing(t(bcols), t(bcp), t(brows), t(brp))
+    csc = sub._CAPI_GetCSC()
+    rec["bfs_indptr"], rec["bfs_indices"] = npy(csc[0]), npy(csc[1])
+
+    # --- EDivUSum on a column-sliced graph with data; Split; IndexSearch
+    w = torch.from_numpy((rng.random(g_indices.numel()) + 0.5).astype(np.float32))
+    rec["in_g_weights"] = npy(w)
+    gd = Graph(False)
+    gd._CAPI_LoadCSC(g_indptr.to(dev), g_indices.to(dev))
+    gd._CAPI_SetData(w.to(dev))
+    sl = gd._CAPI_Slicing(t(cols), 0, _CSC, _COO, False)
+    div = torch.from_numpy((rng.random(n) + 1.0).astype(np.float32))
+    rec["in_divisor"] = npy(div)
+    out_g, out_sum = sl._CAPI_EDivUSum(div.to(dev))
+    rec["edivusum_data"], rec["edivusum_sum"] = npy(out_g._CAPI_GetData("default")), npy(out_sum)
+    parts = g._CAPI_Split(64)
+    rec["split_count"] = np.array([len(parts)])
+    rec["split_indptr"] = np.concatenate([npy(p._CAPI_GetCSC()[0]) for p in parts])
+    rec["split_indices"] = np.concatenate([npy(p._CAPI_GetCSC()[1]) for p in parts])
+    origin = rng.choice(5000, 300, replace=False).astype(np.int64)
+    keys = np.concatenate([rng.choice(origin, 100), rng.integers(5000, 6000, 20)]).astype(np.int64)
+    rec["in_search_origin"], rec["in_search_keys"] = origin, keys
+    rec["index_search"] = npy(ops._CAPI_IndexSearch(t(origin), t(keys)))
+
+    # --- metapath walk with a single possible path (tests/test_hetero_random_walk.cc:29-75)
+    HeteroGraph = torch.classes.gs_classes.HeteroGraph
+    g1, g2 = Graph(False), Graph(False)
+    g1._CAPI_LoadCSC(t([0, 0, 1, 2, 3]), t([0, 1, 2]))
+    g2._CAPI_LoadCSC(t([0, 1, 2, 3]), t([0, 1, 2]))
+    hg = HeteroGraph()
+    hg._CAPI_LoadFromHomo(["user", "item"], [("user", "follow", "user"), ("user", "view", "item")], [g1, g2])
+    rec["metapath_trace"] = npy(hg._CAPI_MetapathRandomWalkFused(t([2, 1]), ["view", "follow", "follow"]))
+
     torch.cuda.synchronize()
     np.savez_compressed(out_path, **rec)
     print("wrote", out_path, "with", len(rec), "arrays")

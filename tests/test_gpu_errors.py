@@ -99,4 +99,4 @@ def test_graph_methods_raise_where_the_reference_aborts():
     with pytest.raises(RuntimeError):
         g._CAPI_all_valid_node()  # col_ids missing
     with pytest.raises(NotImplementedError):
-        g._CAPI_BatchFusionSlicing()
+        g._CAPI_slicing(torch.arange(2).cuda(), 0, gs._DCSC, gs._CSC, False)  # compact-id layouts: not provided

@@ -1,0 +1,188 @@
+"""Induced-subgraph slicing, metapath walk, index search, fused divide + sum and column splitting through the C ABI
+against the CPU oracle, plus the Graph / HeteroGraph methods of both faces against the fixture recorded from the
+reference library."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_batch_b200.npz")
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from graph_sampling_b200 import ops as m
+    return m
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    from oracle import oracle as m
+    return m
+
+
+@pytest.mark.parametrize("S,R", [(0, 10), (1, 1), (50, 0), (300, 400), (2000, 1500)])
+def test_col_row_slicing_matches_oracle(ops, oracle, hub_graph, S, R):
+    indptr, indices = hub_graph
+    n = len(indptr) - 1
+    rng = np.random.default_rng(S + R)
+    cols = rng.integers(0, n, S).astype(np.int64)
+    if S:
+        cols[0] = int(np.argmax(np.diff(indptr)))       # the hub column: many 32-edge rounds for one warp
+    rows = rng.choice(n, R, replace=False).astype(np.int64)
+    w = rng.random(len(indices)).astype(np.float32)
+    want = oracle.col_row_slice(indptr, indices, cols, rows)
+    got = ops.csc_col_row_slicing(dev(indptr), dev(indices), dev(cols), dev(rows), data=dev(w))
+    for a, b in zip(want, got[:3]):
+        assert np.array_equal(a, host(b))
+    assert np.array_equal(host(got[3]), w[want[2]])
+    # composition of the two separate slices gives the same graph
+    sub = ops.csc_col_slicing(dev(indptr), dev(indices), dev(cols), with_coo=False)
+    rs = ops.csc_row_slicing(sub[0], sub[2], dev(rows), with_coo=False)
+    assert np.array_equal(host(rs[0]), want[0]) and np.array_equal(host(rs[2]), want[1])
+
+
+def test_batch_col_row_slicing_matches_oracle(ops, oracle, small_graph):
+    indptr, indices = small_graph
+    n = len(indptr) - 1
+    rng = np.random.default_rng(2)
+    G = 7
+    csz, rsz = rng.integers(0, 60, G), rng.integers(0, 300, G)
+    csz[3] = 0
+    rsz[5] = 0
+    cp = np.concatenate([[0], np.cumsum(csz)]).astype(np.int64)
+    rp = np.concatenate([[0], np.cumsum(rsz)]).astype(np.int64)
+    cols = rng.integers(0, n, cp[-1]).astype(np.int64)
+    rows = np.concatenate([rng.choice(n, k, replace=False) for k in rsz]).astype(np.int64)
+    want = oracle.col_row_slice(indptr, indices, cols, rows, cp, rp, renumber=False)
+    got = ops.csc_col_row_slicing(dev(indptr), dev(indices), dev(cols), dev(rows), dev(cp), dev(rp), n)
+    for a, b in zip(want, got):
+        assert np.array_equal(a, host(b))
+
+
+def test_metapath_walk(ops, oracle, small_graph, hub_graph):
+    # known answer of the reference's own test (tests/test_hetero_random_walk.cc:29-75)
+    g1 = (np.array([0, 0, 1, 2, 3]), np.array([0, 1, 2]))
+    g2 = (np.array([0, 1, 2, 3]), np.array([0, 1, 2]))
+    dg = [(dev(a), dev(b)) for a, b in (g1, g2)]
+    t = ops.fused_metapath_random_walk(dev(np.array([2, 1])), [1, 0, 0], dg, seed=9)
+    assert host(t).reshape(-1).tolist() == [2, 1, 2, 1, 1, 0, 0, -1]
+    # two real relations over the same node set, both layouts, against the oracle
+    n = min(len(small_graph[0]), len(hub_graph[0])) - 1
+    rel = []
+    for indptr, indices in (small_graph, hub_graph):
+        ip = indptr[:n + 1].copy()
+        ix = indices[:ip[-1]].copy() % n
+        rel.append((ip, ix))
+    drel = [(dev(a), dev(b)) for a, b in rel]
+    rng = np.random.default_rng(1)
+    seeds = rng.integers(0, n, 3000).astype(np.int64)
+    path = [0, 1, 1, 0, 1, 0, 0, 0, 1]
+    for layout in (0, 1):
+        want = oracle.metapath_random_walk(rel, path, seeds, seed=4, layout=layout, walker_offset=3)
+        got = ops.fused_metapath_random_walk(dev(seeds), path, drel, seed=4, layout=layout, walker_offset=3)
+        assert np.array_equal(want, host(got))
+    # one relation: the homogeneous walk, word for word
+    a = ops.fused_metapath_random_walk(dev(seeds), [0] * 12, drel[:1], seed=8, layout=1)
+    b = ops.fused_random_walk(dev(seeds), 12, drel[0][1], drel[0][0], seed=8, layout=1)
+    assert torch.equal(a, b)
+
+
+def test_index_search_and_edge_div_u_sum(ops, oracle):
+    rng = np.random.default_rng(6)
+    origin = rng.choice(100000, 20000, replace=False).astype(np.int64)
+    keys = np.concatenate([rng.choice(origin, 5000), rng.integers(100000, 200000, 500)]).astype(np.int64)
+    assert np.array_equal(host(ops.index_search(dev(origin), dev(keys))), oracle.index_search(origin, keys))
+    E, nr, nc = 200000, 3000, 500
+    row, col = rng.integers(0, nr, E).astype(np.int64), rng.integers(0, nc, E).astype(np.int64)
+    data, div = rng.random(E).astype(np.float32), (rng.random(nr) + 0.5).astype(np.float32)
+    wd, ws = oracle.edge_div_u_sum(row, col, data, div, nc)
+    gd, gs_ = ops.coo_e_div_u_sum(dev(row), dev(col), dev(data), dev(div), nc)
+    assert np.array_equal(wd, host(gd))                      # one IEEE division per edge: bit-exact
+    assert np.allclose(ws, host(gs_), rtol=1e-4, atol=1e-3)  # float atomics: order-dependent rounding
+    wd, ws = oracle.edge_div_u_sum(row, col, None, div, nc)
+    gd, gs_ = ops.coo_e_div_u_sum(dev(row), dev(col), None, dev(div), nc)
+    assert np.array_equal(wd, host(gd)) and np.allclose(ws, host(gs_), rtol=1e-4, atol=1e-3)
+
+
+# ---- Graph / HeteroGraph methods of both faces against the reference's recorded outputs -----------------------
+class _PythonFace:
+    def __init__(self):
+        import graph_sampling_b200.gs as gs
+        self.Graph, self.HeteroGraph, self.ops = gs.Graph, gs.HeteroGraph, gs.gs_ops
+
+
+class _TorchScriptFace:
+    def __init__(self):
+        from graph_sampling_b200 import build as b
+        torch.classes.load_library(b.build_glue())
+        self.Graph, self.HeteroGraph = torch.classes.gs_classes.Graph, torch.classes.gs_classes.HeteroGraph
+        self.ops = torch.ops.gs_ops
+
+
+@pytest.fixture(scope="module", params=["python", "torchscript"])
+def face(request):
+    return _PythonFace() if request.param == "python" else _TorchScriptFace()
+
+
+@pytest.fixture(scope="module")
+def fx():
+    return dict(np.load(GOLD))
+
+
+def same(t, a):
+    return np.array_equal(host(t), a)
+
+
+def test_fixture_replay_graph_methods(face, fx, oracle):
+    _COO, _CSC = 1, 2
+    g = face.Graph(False)
+    g._CAPI_LoadCSC(dev(fx["in_g_indptr"]), dev(fx["in_g_indices"]))
+    sub = g._CAPI_FusionSlicing(dev(fx["in_fs_cols"]), dev(fx["in_fs_rows"]))
+    csc = sub._CAPI_GetCSC()
+    assert same(csc[0], fx["fs_indptr"]) and same(csc[1], fx["fs_indices"])
+    # the reference leaves the edge count of this child at 0 (src/graph.cc:116-140 never sets it); here it is set
+    assert [sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols()] == fx["fs_num"].tolist()[:2]
+    assert sub._CAPI_GetNumEdges() == len(fx["fs_indices"])
+    sub = g._CAPI_BatchFusionSlicing(dev(fx["in_bfs_cols"]), dev(fx["in_bfs_col_ptr"]), dev(fx["in_bfs_rows"]),
+                                     dev(fx["in_bfs_row_ptr"]))
+    csc = sub._CAPI_GetCSC()
+    assert same(csc[0], fx["bfs_indptr"]) and same(csc[1], fx["bfs_indices"])
+    gd = face.Graph(False)
+    gd._CAPI_LoadCSC(dev(fx["in_g_indptr"]), dev(fx["in_g_indices"]))
+    gd._CAPI_SetData(dev(fx["in_g_weights"]))
+    sl = gd._CAPI_Slicing(dev(fx["in_fs_cols"]), 0, _CSC, _COO, False)
+    out_g, out_sum = sl._CAPI_EDivUSum(dev(fx["in_divisor"]))
+    assert np.allclose(host(out_g._CAPI_GetData("default")), fx["edivusum_data"], rtol=2e-7, atol=0)
+    assert np.allclose(host(out_sum), fx["edivusum_sum"], rtol=1e-5, atol=1e-5)
+    # edge data follows the kept edges of an induced subgraph
+    sub = gd._CAPI_FusionSlicing(dev(fx["in_fs_cols"]), dev(fx["in_fs_rows"]))
+    want = oracle.col_row_slice(fx["in_g_indptr"], fx["in_g_indices"], fx["in_fs_cols"], fx["in_fs_rows"])
+    assert same(sub._CAPI_GetData("default"), fx["in_g_weights"][want[2]])
+    parts = g._CAPI_Split(64)
+    assert len(parts) == int(fx["split_count"][0])
+    assert same(torch.cat([p._CAPI_GetCSC()[0] for p in parts]), fx["split_indptr"])
+    assert same(torch.cat([p._CAPI_GetCSC()[1] for p in parts]), fx["split_indices"])
+    assert same(face.ops._CAPI_IndexSearch(dev(fx["in_search_origin"]), dev(fx["in_search_keys"])), fx["index_search"])
+
+
+def test_fixture_replay_metapath(face, fx):
+    g1, g2 = face.Graph(False), face.Graph(False)
+    g1._CAPI_LoadCSC(dev(np.array([0, 0, 1, 2, 3])), dev(np.array([0, 1, 2])))
+    g2._CAPI_LoadCSC(dev(np.array([0, 1, 2, 3])), dev(np.array([0, 1, 2])))
+    hg = face.HeteroGraph()
+    hg._CAPI_LoadFromHomo(["user", "item"], [("user", "follow", "user"), ("user", "view", "item")], [g1, g2])
+    trace = hg._CAPI_MetapathRandomWalkFused(dev(np.array([2, 1])), ["view", "follow", "follow"])
+    assert same(trace, fx["metapath_trace"])
+    assert host(trace).reshape(-1).tolist() == [2, 1, 2, 1, 1, 0, 0, -1]
+    assert hg._CAPI_GetHomoGraph("view")._CAPI_GetNumEdges() == 3

@@ -86,3 +86,33 @@ def test_batch_slicing(fx, oracle):
         assert eq(offsets, fx[tag + "offsets"])
         assert eq(oracle.batch_encode(seeds, ps, n), fx[tag + "cols"])
         assert fx[tag + "num"].tolist() == [n * (len(ps) - 1), len(seeds), len(sub_indices)]
+
+
+def test_induced_subgraph_and_friends(fx, oracle):
+    indptr, indices = fx["in_g_indptr"], fx["in_g_indices"]
+    ip, ix, sel = oracle.col_row_slice(indptr, indices, fx["in_fs_cols"], fx["in_fs_rows"])
+    assert eq(ip, fx["fs_indptr"]) and eq(ix, fx["fs_indices"])
+    assert eq(indices[sel], fx["in_fs_rows"][ix])         # select_index points at the kept edges
+    ip, ix, _ = oracle.col_row_slice(indptr, indices, fx["in_bfs_cols"], fx["in_bfs_rows"], fx["in_bfs_col_ptr"],
+                                     fx["in_bfs_row_ptr"], renumber=False)
+    assert eq(ip, fx["bfs_indptr"]) and eq(ix, fx["bfs_indices"])
+    assert eq(oracle.index_search(fx["in_search_origin"], fx["in_search_keys"]), fx["index_search"])
+    parts = oracle.csc_split(indptr, indices, 64)
+    assert len(parts) == int(fx["split_count"][0])
+    assert eq(np.concatenate([p[0] for p in parts]), fx["split_indptr"])
+    assert eq(np.concatenate([p[1] for p in parts]), fx["split_indices"])
+
+
+def test_edge_div_u_sum(fx, oracle):
+    indptr, indices, w = fx["in_g_indptr"], fx["in_g_indices"], fx["in_g_weights"]
+    _, coo_col, rows, sel = oracle.col_slice(indptr, indices, fx["in_fs_cols"], with_coo=True)
+    out, s = oracle.edge_div_u_sum(rows, coo_col, w[sel], fx["in_divisor"], len(fx["in_fs_cols"]))
+    assert np.allclose(out, fx["edivusum_data"], rtol=2e-7, atol=0)      # the reference divides with --use_fast_math off
+    assert np.allclose(s, fx["edivusum_sum"], rtol=1e-5, atol=1e-5)
+
+
+def test_metapath_known_answer(fx, oracle):
+    g1 = (np.array([0, 0, 1, 2, 3]), np.array([0, 1, 2]))
+    g2 = (np.array([0, 1, 2, 3]), np.array([0, 1, 2]))
+    t = oracle.metapath_random_walk([g1, g2], [1, 0, 0], np.array([2, 1]), seed=1)
+    assert eq(t, fx["metapath_trace"]) and t.reshape(-1).tolist() == [2, 1, 2, 1, 1, 0, 0, -1]
