@@ -632,6 +632,35 @@ def run_kernels(args):
     ld = torch.arange(1_000_000, device=device)
     timed("list sampling, 512 of 1 M weighted", lambda: ops.list_sampling(ld, 512, False, probs=lp), 12 * 1_000_000 + 16 * 512,
           note="20 launches; latency bound")
+    # ---- feature load, induced subgraph, metapath walk, super-batch operators --------------------------------
+    fr = torch.randint(0, n, (1_000_000,), generator=g, device=device)
+    timed("feature rows gather, F = 256 (1 M rows)", lambda: ops.gather_rows(x, fr), fr.numel() * (8 + 8 * F))
+    timed("edge data gather, F = 1 (13 M of 124 M)", lambda: ops.gather_rows(probs, sub_row % D), D * 16)
+    del x, xd
+    torch.cuda.empty_cache()
+    timed("induced subgraph (262 k columns x 100 k rows)", lambda: ops.csc_col_row_slicing(indptr, indices, seeds, rows),
+          lambda o: 32 * S + 8 * rows.numel() + 8 * D + 16 * o[1].numel(), note="two size read-backs")
+    wseeds = torch.randint(0, n, (4_000_000,), generator=g, device=device)
+    path = [0, 1] * 8
+    timed("metapath walk, 4 M walkers x 16 steps, 2 relations", lambda: ops.fused_metapath_random_walk(wseeds, path, [(indptr, indices), (indptr, indices)]),
+          wseeds.numel() * (16 + 32 * 16))
+    G = 256
+    bptr = torch.arange(G + 1, device=device) * (D // G)
+    bptr[-1] = D
+    sptr = torch.arange(G + 1, device=device) * (S // G)
+    timed("BatchUnique, 256 batches", lambda: ops.batch_unique(sub_row, bptr), lambda o: 8 * D + 16 * o[0].numel())
+    timed("BatchUnique2 (sorted), 256 batches", lambda: ops.batch_unique(sub_row, bptr, sort=True),
+          lambda o: 8 * D + 16 * o[0].numel() + 32 * 5 * o[0].numel(), note="+ 5 radix passes over the distinct ids")
+    bcol = seeds[sub_col]
+    timed("BatchCOORelabel, 256 batches", lambda: ops.batch_coo_relabel(seeds, sptr, bcol, sub_row, bptr),
+          lambda o: 8 * (S + D) + 8 * o[0].numel() + 8 * D + 16 * D)
+    timed("BatchCOOSlicing by membership, 256 batches", lambda: ops.batch_coo_slicing(1, sub_row, sub_col, bptr, rows, torch.arange(G + 1, device=device) * (rows.numel() // G)),
+          lambda o: 8 * rows.numel() + 16 * D + 16 * o[0].numel())
+    enc = timed("BatchEncode", lambda: ops.batch_encode(sub_row, bptr, n), 16 * D)
+    timed("GetBatchOffsets + decode", lambda: ops.get_batch_offsets(enc, G, n), 16 * D)
+    timed("BatchConcat of 2 arrays", lambda: ops.batch_concat([seeds, sub_row], [sptr, bptr]), 24 * (S + D))
+    timed("segmented list sampling, 256 x 4000 of 13 M", lambda: ops.batch_list_sampling_probs(probs, 4000, False, bptr),
+          12 * D + 8 * 4000 * G, note="5 radix passes of 32 B per item")
     print(json.dumps({"metric": "per_operator_roofline", "unit": "GB/s", "peak": peak, "graph": {"nodes": n, "edges": int(indices.numel())},
                       "operators": results}))
 

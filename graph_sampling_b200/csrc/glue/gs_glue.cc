@@ -489,24 +489,24 @@ class Graph : public torch::CustomClassHolder {
     if (batched) TORCH_CHECK(cp.numel() == rp.numel(), "col_ptr and row_ptr must have the same length");
     const CSC& g = *csc_;
     const int64_t S = col_ids.numel(), R = row_ids.numel(), G = batched ? cp.numel() - 1 : 1;
-    Tensor sub_indptr = EmptyIds(S + 1, g.indptr);
-    int64_t nnz = 0;
-    Check(gsb_col_row_slice_count(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(col_ids), S, IP(row_ids), R, IP(cp),
-                                  IP(rp), G, num_rows_, MP(sub_indptr), &nnz),
-          "gsb_col_row_slice_count");
-    Tensor indices = EmptyIds(nnz, g.indptr), select = EmptyIds(nnz, g.indptr), out_data;
+    Tensor slice_indptr = EmptyIds(S + 1, g.indptr), sub_indptr = EmptyIds(S + 1, g.indptr);
+    int64_t D = 0, nnz = 0;
+    Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), IP(col_ids), S, MP(slice_indptr), &D), "gsb_col_slice_count");
+    Tensor indices = EmptyIds(D, g.indptr), select = EmptyIds(D, g.indptr), out_data;
     const float* data_in = nullptr;
     float* data_out = nullptr;
     if (data_.has_value()) {
-      out_data = torch::empty({nnz}, data_.value().options());
+      out_data = torch::empty({D}, data_.value().options());
       data_in = FP(data_.value());
-      data_out = nnz ? out_data.data_ptr<float>() : nullptr;
+      data_out = D ? out_data.data_ptr<float>() : nullptr;
     }
     Tensor eids = g.e_ids.value_or(Tensor());
-    Check(gsb_col_row_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(col_ids), S, IP(row_ids), R, IP(cp),
-                                 IP(rp), G, num_rows_, batched ? 0 : 1, IP(sub_indptr), MP(indices), MP(select),
-                                 data_in, IP(eids), data_out),
-          "gsb_col_row_slice_fill");
+    Check(gsb_col_row_slice(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(col_ids), S, IP(slice_indptr), D,
+                            IP(row_ids), R, IP(cp), IP(rp), G, num_rows_, batched ? 0 : 1, MP(sub_indptr), MP(indices),
+                            MP(select), data_in, IP(eids), data_out, &nnz),
+          "gsb_col_row_slice");
+    indices = indices.narrow(0, 0, nnz);
+    if (out_data.defined()) out_data = out_data.narrow(0, 0, nnz);
     auto ret = batched ? c10::make_intrusive<Graph>(true, col_ids, row_ids_, S, num_rows_)
                        : c10::make_intrusive<Graph>(true, col_ids, row_ids, S, R);
     ret->csc_ = std::make_shared<CSC>(CSC{sub_indptr, indices, torch::nullopt});

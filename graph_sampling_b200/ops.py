@@ -300,23 +300,51 @@ def csc_col_row_slicing(indptr, indices, column_ids, row_ids, col_ptr=None, row_
     ctx = ctx or default_context(indptr.device)
     S, R = column_ids.numel(), row_ids.numel()
     G = 1 if col_ptr is None else col_ptr.numel() - 1
+    slice_indptr = _empty(S + 1, indptr)
+    d = c_i64(0)
+    ctx.check(ctx.lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), _p(column_ids), c_i64(S),
+                                          _p(slice_indptr), ctypes.byref(d)), "gsb_col_slice_count")
+    D = d.value
     sub_indptr = _empty(S + 1, indptr)
+    sub_indices, select = _empty(D, indptr), _empty(D, indptr)
+    out_data = _empty(D, indptr, torch.float32) if data is not None else None
     nnz = c_i64(0)
-    ctx.check(ctx.lib.gsb_col_row_slice_count(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
-                                              _p(row_ids), c_i64(R), _p(col_ptr), _p(row_ptr), c_i64(G),
-                                              c_i64(int(encoding_size)), _p(sub_indptr), ctypes.byref(nnz)),
-              "gsb_col_row_slice_count")
+    ctx.check(ctx.lib.gsb_col_row_slice(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+                                        _p(slice_indptr), c_i64(D), _p(row_ids), c_i64(R), _p(col_ptr), _p(row_ptr),
+                                        c_i64(G), c_i64(int(encoding_size)), c_int(1 if col_ptr is None else 0),
+                                        _p(sub_indptr), _p(sub_indices), _p(select), _p(data), _p(e_ids),
+                                        _p(out_data), ctypes.byref(nnz)), "gsb_col_row_slice")
     n = nnz.value
-    sub_indices, select = _empty(n, indptr), _empty(n, indptr)
-    out_data = _empty(n, indptr, torch.float32) if data is not None else None
-    ctx.check(ctx.lib.gsb_col_row_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
-                                             _p(row_ids), c_i64(R), _p(col_ptr), _p(row_ptr), c_i64(G),
-                                             c_i64(int(encoding_size)), c_int(1 if col_ptr is None else 0),
-                                             _p(sub_indptr), _p(sub_indices), _p(select), _p(data), _p(e_ids),
-                                             _p(out_data)), "gsb_col_row_slice_fill")
+    sub_indices, select = sub_indices[:n], select[:n]
+    if out_data is not None:
+        out_data = out_data[:n]
     if data is not None:
         return sub_indptr, sub_indices, select, out_data
     return sub_indptr, sub_indices, select
+
+
+def gather_rows(src, index, ctx=None):
+    """out[i] = src[index[i]] for a float32 matrix (or vector) `src` that lives on the GPU or in pinned host memory
+    (read in place by the GPU, like IndexSelectCPUFromGPU, src/cuda/index_select_uvm.cu:8-45)."""
+    index = _i64(index, "index")
+    if not (isinstance(src, torch.Tensor) and src.dtype == torch.float32 and src.is_contiguous()):
+        raise TypeError("src must be a contiguous float32 tensor")
+    if not (src.is_cuda or src.is_pinned()):
+        raise TypeError("src must live on the GPU or in pinned host memory")
+    ctx = ctx or default_context(index.device)
+    num_rows = src.shape[0] if src.dim() > 0 else 0
+    row_len = 1
+    for d in src.shape[1:]:
+        row_len *= int(d)
+    out = torch.empty((index.numel(),) + tuple(src.shape[1:]), dtype=torch.float32, device=index.device)
+    if row_len == 0:
+        return out
+    ctx.check(ctx.lib.gsb_gather_rows(ctx.handle, _stream(), c_vp(src.data_ptr()), c_i64(num_rows), c_i64(row_len),
+                                      _p(index), c_i64(index.numel()), _p(out)), "gsb_gather_rows")
+    return out
+
+
+index_select_cpu_from_gpu = gather_rows
 
 
 def index_search(origin_data, keys, ctx=None):

@@ -273,26 +273,24 @@ GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* 
                                      int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
 
 /* ---- induced-subgraph slicing, index search, fused divide + sum -------------------------------------------
- * gsb_col_row_slice_count / _fill replace gs::impl::fusion::CSCColRowSlicingCUDA and BatchCSCColRowSlicingCUDA
+ * gsb_col_row_slice replaces gs::impl::fusion::CSCColRowSlicingCUDA and BatchCSCColRowSlicingCUDA
  * (src/cuda/fusion/column_row_slicing.cu:101-365; Graph::FusedBidirSlicing / BatchFusedBidirSlicing,
- * src/graph.cc:116-170): of the seed columns keep the edges whose row id is in row_ids.  count writes the
- * offsets out_indptr[S + 1] and returns the number of survivors; fill writes them in edge order.
+ * src/graph.cc:116-170): of the seed columns keep the edges whose row id is in row_ids.
+ * sub_indptr[S + 1] and D = sub_indptr[S] come from gsb_col_slice_count on the same seeds (the offsets of
+ * the unfiltered column slice); out_indices / out_select (/ out_data) hold D entries, of which the first
+ * *nnz_host are written, in edge order; out_indptr[S + 1] are the offsets of the survivors.
  * renumber != 0 writes the position of the row id in row_ids (the single-list form), 0 keeps the row id
  * (the super-batch form).  col_ptr / row_ptr (DEVICE, G + 1 entries, both or neither) partition the columns
  * and the row list into batches: a column of batch b is matched against the rows of batch b only;
  * encoding_size must exceed every row id.  out_select holds positions in `indices` (the reference returns
  * positions inside the unmaterialised column slice, which its own data gather then misuses: src/graph.cc:131-137).
- * Both calls rebuild the row table, so nothing has to survive between them.
  */
-GSB_API int gsb_col_row_slice_count(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                                    const int64_t* column_ids, int64_t S, const int64_t* row_ids, int64_t R,
-                                    const int64_t* col_ptr, const int64_t* row_ptr, int64_t G, int64_t encoding_size,
-                                    int64_t* out_indptr, int64_t* nnz_host);
-GSB_API int gsb_col_row_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                                   const int64_t* column_ids, int64_t S, const int64_t* row_ids, int64_t R,
-                                   const int64_t* col_ptr, const int64_t* row_ptr, int64_t G, int64_t encoding_size,
-                                   int renumber, const int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
-                                   const float* data, const int64_t* e_ids, float* out_data);
+GSB_API int gsb_col_row_slice(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
+                              const int64_t* column_ids, int64_t S, const int64_t* sub_indptr, int64_t D,
+                              const int64_t* row_ids, int64_t R, const int64_t* col_ptr, const int64_t* row_ptr,
+                              int64_t G, int64_t encoding_size, int renumber, int64_t* out_indptr,
+                              int64_t* out_indices, int64_t* out_select, const float* data, const int64_t* e_ids,
+                              float* out_data, int64_t* nnz_host);
 
 /* gsb_index_search replaces gs::IndexSearch (src/tensor_ops.cc:23-31; IndexHashMapInsertCUDA + IndexHashMapSearchCUDA,
  * src/cuda/index_search.cu): out[i] = position of keys[i] in origin (the largest one if the id repeats), -1 if
@@ -305,6 +303,15 @@ GSB_API int gsb_index_search(gsb_ctx* ctx, void* stream, const int64_t* origin, 
  * out_sum[coo_col[e]] += out_data[e] (float atomics; out_sum must be zeroed by the caller). */
 GSB_API int gsb_edge_div_u_sum(gsb_ctx* ctx, void* stream, const int64_t* coo_row, const int64_t* coo_col, int64_t E,
                                const float* data, const float* divisor, float* out_data, float* out_sum_zeroed);
+
+/* gsb_gather_rows: out[i, :] = src[index[i], :] for rows of row_len floats — the feature / edge-data load that
+ * follows sampling (features[frontier]) and, when src is page-locked HOST memory that the GPU reads in place,
+ * gs::impl::IndexSelectCPUFromGPU (src/cuda/index_select_uvm.cu:8-45; row_len = 1 there).  src: device memory or
+ * page-locked host memory (pageable host memory returns GSB_ERR_INVALID_ARGUMENT); index, out: device memory.
+ * An index outside [0, num_rows) leaves its output row untouched and records GSB_ERR_INDEX_RANGE, which the next
+ * call that waits for the stream (or gsb_check_device_status) reports. */
+GSB_API int gsb_gather_rows(gsb_ctx* ctx, void* stream, const float* src, int64_t num_rows, int64_t row_len,
+                            const int64_t* index, int64_t n, float* out);
 
 /* gsb_metapath_random_walk replaces gs::impl::fusion::FusedMetapathRandomWalkCUDA
  * (src/cuda/fusion/metapath_random_walk.cu:9-67; HeteroGraph::MetapathRandomWalkFused, src/hetero_graph.cc:58-74):
