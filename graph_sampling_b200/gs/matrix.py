@@ -5,6 +5,7 @@ from dataclasses import dataclass
 from typing import Optional
 
 import torch
+import torch.fx
 
 from ..graph import Graph, _COO, _CSC, _CSR
 
@@ -86,9 +87,9 @@ class Matrix:
     def __getitem__(self, data):
         ret = self._graph
         r_slice, c_slice = data[0], data[1]
-        if isinstance(c_slice, torch.Tensor):
+        if isinstance(c_slice, (torch.Tensor, torch.fx.Proxy)):
             ret = ret._CAPI_slicing(c_slice, 0, _CSC, _COO, False)
-        if isinstance(r_slice, torch.Tensor):
+        if isinstance(r_slice, (torch.Tensor, torch.fx.Proxy)):
             ret = ret._CAPI_slicing(r_slice, 1, _CSR, _COO, False)
         return Matrix(ret)
 
