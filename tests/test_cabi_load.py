@@ -67,11 +67,20 @@ def test_torchscript_glue_registers_reference_names():
                  "_CAPI_SamplingWithProbs", "_CAPI_FusedColumnwiseSlicingSampling",
                  "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_AllValidNode", "_CAPI_all_indices", "_CAPI_Relabel",
                  "_CAPI_relabel", "_CAPI_RandomWalk", "_CAPI_SDDMM", "_CAPI_Sum", "_CAPI_Normalize", "_CAPI_Divide",
-                 "_CAPI_Metadata", "_CAPI_GetCooCols", "_CAPI_GetCSC", "_CAPI_GetCOO"]:
+                 "_CAPI_Metadata", "_CAPI_GetCooCols", "_CAPI_GetCSC", "_CAPI_GetCOO", "_CAPI_BatchSlicing",
+                 "_CAPI_FusionSlicing", "_CAPI_BatchFusionSlicing", "_CAPI_EDivUSum", "_CAPI_Split", "_CAPI_Decode"]:
         assert hasattr(g, name), name
     for op in ["_CAPI_ListSampling", "_CAPI_ListSamplingWithProbs", "_CAPI_Unique", "list_sampling",
-               "list_sampling_with_probs", "_CAPI_BatchCSRRelabel"]:
+               "list_sampling_with_probs", "_CAPI_BatchCSRRelabel", "_CAPI_BatchListSamplingWithProbs", "_CAPI_IndexSearch",
+               "_CAPI_SplitByOffset", "_CAPI_IndptrSplitBySize", "_CAPI_IndptrSplitByOffset", "_CAPI_BatchConcat",
+               "_CAPI_BatchUnique", "_CAPI_BatchUniqueByKey", "_CAPI_BatchUnique2", "_CAPI_BatchUniqueByKey2",
+               "_CAPI_BatchCSRRelabelByKey", "_CAPI_BatchCOORelabelByKey", "_CAPI_BatchCOORelabel", "_CAPI_BatchSplit",
+               "_CAPI_BatchCOOSlicing", "_CAPI_BatchEncode", "_CAPI_BatchDecode", "_CAPI_GetBatchOffsets",
+               "_CAPI_COORowSlicingGlobalId"]:   # every name of the reference's gs_ops registry (src/pybind.cc:62-85)
         assert hasattr(torch.ops.gs_ops, op), op
+    hg = torch.classes.gs_classes.HeteroGraph()
+    for name in ["_CAPI_LoadFromHomo", "_CAPI_GetHomoGraph", "_CAPI_MetapathRandomWalkFused"]:
+        assert hasattr(hg, name), name
     if not torch.cuda.is_available():
         with pytest.raises(Exception):
             g._CAPI_LoadCSC(torch.arange(3), torch.arange(2))
