@@ -522,6 +522,19 @@ __global__ void k_set_single_batch_ptrs(i64* seeds_ptr, i64* indices_ptr, i64 S,
   indices_ptr[1] = E;
 }
 
+// Everything k_batch_layout derives, for exactly one batch: offsets, item count and the one table region.
+__global__ void k_single_batch_setup(i64* seeds_ptr, i64* indices_ptr, i64* item_off, i64* region_off, i64 S, i64 E,
+                                     i64 region_size) {
+  seeds_ptr[0] = 0;
+  seeds_ptr[1] = S;
+  indices_ptr[0] = 0;
+  indices_ptr[1] = E;
+  item_off[0] = 0;
+  item_off[1] = S + E;
+  region_off[0] = 0;
+  region_off[1] = region_size;
+}
+
 }  // namespace gsb
 
 using namespace gsb;
@@ -561,7 +574,7 @@ int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, 
   GSB_REQUIRE(n_cap < (1ll << 31), GSB_ERR_UNSUPPORTED);
   GSB_REQUIRE(n_cap == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 * G + 64;
+  const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
   const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
   void* ws;
@@ -636,7 +649,7 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
   GSB_REQUIRE(n_cap == 0 || (seeds && out_unique), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(cap == 0 || (indices && out_indices && out_select && out_relabeled), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 * G + 64;
+  const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
   const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
   void* ws;
@@ -717,7 +730,7 @@ static int build_batch_tables(gsb_ctx* ctx, cudaStream_t stream, const i64* seed
                               void** extra) {
   const i64 n_cap = num_seeds + indices_capacity;
   GSB_REQUIRE(n_cap < (1ll << 31), GSB_ERR_UNSUPPORTED);
-  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 * G + 64;
+  const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
   const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
   void* ws;
@@ -911,7 +924,8 @@ int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i
                           i64* out_unique, i64* out_relabeled, i64* unique_host) {
   void* ws;
   const i64 n_cap = S + E;
-  const i64 slot_cap = n_cap + (n_cap >> 2) + 32 + 64;
+  const i64 region = region_size_for(n_cap);
+  const i64 slot_cap = region + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
   int st = ctx_reserve_workspace(ctx, slots_bytes + 4 * 256, &ws);
   if (st != GSB_OK) return st;
@@ -935,11 +949,7 @@ int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i
   }
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_set_single_batch_ptrs<<<1, 1, 0, stream>>>(seeds_ptr, indices_ptr, S, E);
-  }
-  {
-    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
+    k_single_batch_setup<<<1, 1, 0, stream>>>(seeds_ptr, indices_ptr, L.item_off, L.region_off, S, E, region);
   }
   GSB_LAUNCH_OK();
   const int wide = kNumSMs * 8;

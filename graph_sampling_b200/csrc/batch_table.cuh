@@ -8,7 +8,10 @@ namespace gsb {
 constexpr u64 kEmptyWord = 0xFFFFFFFFFFFFFFFFull;
 constexpr uint32_t kFinalBit = 0x80000000u;
 
-__host__ __device__ __forceinline__ i64 region_size_for(i64 items) { return items + (items >> 2) + 32; }
+// Slots of a table region for `items` insertions: load <= 0.5.  Denser tables (load 0.8 was tried) cost more than
+// the memset they save: linear probing then has probe runs of hundreds of slots, which set the duration of a
+// small call outright (one warp walks them with dependent loads) and still cost 7 % on a 256-batch call.
+__host__ __device__ __forceinline__ i64 region_size_for(i64 items) { return 2 * items + 32; }
 
 __device__ __forceinline__ i64 home_slot(i64 node, i64 size) {
   const uint32_t h = (uint32_t)(((u64)node * 0x9E3779B97F4A7C15ull) >> 32);
