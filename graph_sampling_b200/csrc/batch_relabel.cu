@@ -670,8 +670,9 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
     ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
     GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
   }
+  // the exact seed count is seeds_ptr[G] on the device; S only has to bound it (grids, scratch and capacities)
   st = sample_uniform_launch(ctx, stream, indptr, indices, seeds, S, k, replace, (u64)seed, out_indptr, out_indices,
-                             out_select, nullptr, nullptr, nullptr, nullptr, cap);
+                             out_select, nullptr, nullptr, nullptr, nullptr, cap, seeds_ptr + G);
   if (st != GSB_OK) return st;
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);

@@ -70,9 +70,11 @@ __device__ __forceinline__ i64 batch_of(const i64* __restrict__ off, i64 G, i64 
 int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i64 S, const i64* second, i64 E,
                           i64* out_unique, i64* out_relabeled, i64* unique_host);
 
-// Uniform sampler shared by gsb_sample_uniform and the batched hop (defined in slice_sample.cu).
+// Uniform sampler shared by gsb_sample_uniform and the batched hop (defined in slice_sample.cu).  With S_dev the
+// exact seed count is read on the device and S is an upper bound that sizes the grid.
 int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
                           i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,
-                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity);
+                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity,
+                          const i64* S_dev = nullptr);
 
 }  // namespace gsb

@@ -132,6 +132,7 @@ struct SampleParams {
   i64 capacity;
   i64* counters;
   TileState ts;
+  const i64* S_dev;  // when set, the exact seed count lives on the device and S above is only an upper bound
 };
 
 __device__ __forceinline__ void emit_pick(const SampleParams& p, i64 out_pos, i64 in_pos, i64 column_pos) {
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
   __shared__ i64 s_base;
   const int tile = blockIdx.x;
   const int tid = threadIdx.x;
-  const i64 S = p.S;
+  const i64 S = p.S_dev ? min(p.S, __ldg(p.S_dev)) : p.S;
   const i64 base = (i64)tile * kTileCols;
   if (base >= S && !(S == 0 && tile == 0)) return;
   const int ncol = (int)max((i64)0, min((i64)kTileCols, S - base));
@@ -243,7 +244,7 @@ template <int KMAX>
 __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams p) {
   const int lane = threadIdx.x & 31;
   const i64 tile = (i64)blockIdx.x * (kTpcThreads / 32) + (threadIdx.x >> 5);
-  const i64 S = p.S;
+  const i64 S = p.S_dev ? min(p.S, __ldg(p.S_dev)) : p.S;
   if (tile * 32 >= S && !(S == 0 && tile == 0)) return;
   const i64 i = tile * 32 + lane;
   const bool valid = i < S;
@@ -358,14 +359,15 @@ static void launch_sample(const SampleParams& p, int grid, cudaStream_t stream) 
 
 int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
                           i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,
-                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity) {
+                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity,
+                          const i64* S_dev) {
   const bool per_thread = k <= 16;  // small fanouts: one lane per column, one warp per tile of 32 columns
   const int grid = per_thread ? grid_for(S, kTpcThreads) : grid_for(S, kTileCols);
   TileState ts;
   int st = ctx_tile_state(ctx, per_thread ? (S + 31) / 32 + 1 : grid, stream, &ts);
   if (st != GSB_OK) return st;
   SampleParams p{indptr, indices, seeds,  S,        k,        replace,         seed, out_indptr, out_indices,
-                 out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts};
+                 out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts, S_dev};
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
     if (k <= 4) k_sample_uniform_tpc<4><<<grid, kTpcThreads, 0, stream>>>(p);

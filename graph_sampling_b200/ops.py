@@ -806,15 +806,19 @@ def indptr_split_by_size(indptr, size, ctx=None):
     return list(torch.split(out, int(size) + 1))
 
 
-def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None):
+def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None, sync=True):
     """Multi-hop GraphSAGE sampling of G minibatches at once (the loop of
     examples/graphsage/batching.py:56-90): per hop one fused slice+sample over the seeds of all batches,
     then one batched unique + relabel; each batch's frontier becomes its seeds for the next hop.
 
     Returns a list (one entry per hop) of dicts with: seeds, seeds_ptr (columns of the hop and their
     per-batch offsets), sub_indptr (offsets over all columns), indices (global ids), relabeled
-    (batch-local ids), select_index, indices_ptr, frontier, frontier_ptr.  One host synchronisation
-    per hop (to learn the frontier size that sizes the next hop)."""
+    (batch-local ids), select_index, indices_ptr, frontier, frontier_ptr.
+
+    sync=True waits once per hop and trims every array to its exact length.  sync=False queues all hops
+    without waiting for the GPU: arrays keep their upper-bound length (S·k edges, S·(1+k) frontier entries
+    per hop, so capacities grow by (1+k) per hop), the valid prefixes are given by the offset arrays, and
+    every dict carries `counts`, a 3-element device tensor (seeds, edges, frontier) to read when convenient."""
     ctx = ctx or default_context(indptr.device)
     out = []
     base_seed = next_seed(seed)
@@ -831,10 +835,18 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
                                        c_i64(G), c_i64(S), c_i64(int(k)), c_int(int(bool(replace))),
                                        c_u64((base_seed + hop) & (2**64 - 1)), _p(sub_indptr), _p(sub_indices),
                                        _p(select), _p(indices_ptr), _p(uniq), _p(uniq_ptr), _p(rel),
-                                       ctypes.byref(nu), ctypes.byref(ne)), "gsb_sage_hop")
-        E, U = ne.value, nu.value
-        out.append(dict(seeds=seeds, seeds_ptr=seeds_ptr, sub_indptr=sub_indptr, indices=sub_indices[:E],
-                        relabeled=rel[:E], select_index=select[:E], indices_ptr=indices_ptr, frontier=uniq[:U],
-                        frontier_ptr=uniq_ptr))
-        seeds, seeds_ptr = uniq[:U], uniq_ptr
+                                       ctypes.byref(nu) if sync else None, ctypes.byref(ne) if sync else None),
+                  "gsb_sage_hop")
+        if sync:
+            E, U = ne.value, nu.value
+            out.append(dict(seeds=seeds, seeds_ptr=seeds_ptr, sub_indptr=sub_indptr, indices=sub_indices[:E],
+                            relabeled=rel[:E], select_index=select[:E], indices_ptr=indices_ptr, frontier=uniq[:U],
+                            frontier_ptr=uniq_ptr))
+            seeds, seeds_ptr = uniq[:U], uniq_ptr
+        else:
+            counts = torch.cat([seeds_ptr[G:], indices_ptr[G:], uniq_ptr[G:]])
+            out.append(dict(seeds=seeds, seeds_ptr=seeds_ptr, sub_indptr=sub_indptr, indices=sub_indices,
+                            relabeled=rel, select_index=select, indices_ptr=indices_ptr, frontier=uniq,
+                            frontier_ptr=uniq_ptr, counts=counts))
+            seeds, seeds_ptr = uniq, uniq_ptr
     return out

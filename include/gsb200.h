@@ -416,6 +416,10 @@ GSB_API int gsb_batch_list_sample(gsb_ctx* ctx, void* stream, const float* probs
  * (S * k entries each; global ids, positions in `indices`, batch-local ids), out_indices_ptr[G + 1]
  * (per-batch edge offsets), out_unique (S + S * k entries; all frontiers back to back) and
  * out_unique_ptr[G + 1].  The frontier of a batch becomes its seed list for the next hop.
+ * S may be an UPPER BOUND of the seed count: the exact count is read from seeds_ptr[G] on the device, S sizes grids,
+ * scratch and the output capacities (S * k, S + S * k).  With the *_host pointers NULL a caller can therefore queue
+ * the next hop right away — seeds = out_unique, seeds_ptr = out_unique_ptr, S = this hop's S * (1 + k) — and read all
+ * counts (out_indices_ptr[G], out_unique_ptr[G] of every hop) after the last one: no host wait between hops.
  * Ids below 2^32 - 1; S * (1 + k) below 2^30.  Waits for the stream only if a *_host pointer is given.
  */
 GSB_API int gsb_sage_hop(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,

@@ -90,6 +90,31 @@ def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, fanouts):
         cur, cur_ptr = np.concatenate(nxt), np.array(nxt_ptr, dtype=np.int64)
 
 
+@pytest.mark.parametrize("fanouts", [[10, 5], [15, 10, 5], [20, 3]])
+def test_sage_sample_batches_without_host_waits(ops, cfg1_graph, fanouts):
+    """All hops queued without waiting for the GPU (seed counts stay on the device, capacities are upper bounds):
+    the valid prefixes equal the hop-by-hop result, word for word."""
+    indptr, indices = cfg1_graph
+    n = len(indptr) - 1
+    G, S0 = 12, 700
+    rng = np.random.default_rng(3)
+    seeds0 = dev(np.concatenate([rng.choice(n, S0, replace=False) for _ in range(G)]).astype(np.int64))
+    ptr0 = dev((np.arange(G + 1) * S0).astype(np.int64))
+    want = ops.sage_sample_batches(dev(indptr), dev(indices), seeds0, ptr0, fanouts, seed=5)
+    got = ops.sage_sample_batches(dev(indptr), dev(indices), seeds0, ptr0, fanouts, seed=5, sync=False)
+    ops.default_context().check_device()
+    for w, g in zip(want, got):
+        S, E, U = g["counts"].tolist()
+        assert (S, E, U) == (w["seeds"].numel(), w["indices"].numel(), w["frontier"].numel())
+        assert g["indices"].numel() >= E and g["frontier"].numel() >= U      # capacities, not sizes
+        assert torch.equal(g["seeds"][:S], w["seeds"]) and torch.equal(g["seeds_ptr"], w["seeds_ptr"])
+        assert torch.equal(g["sub_indptr"][:S + 1], w["sub_indptr"])
+        for key in ("indices", "relabeled", "select_index"):
+            assert torch.equal(g[key][:E], w[key]), key
+        assert torch.equal(g["indices_ptr"], w["indices_ptr"]) and torch.equal(g["frontier_ptr"], w["frontier_ptr"])
+        assert torch.equal(g["frontier"][:U], w["frontier"])
+
+
 def test_split_helpers(ops):
     """SplitByOffset / IndptrSplitByOffset / IndptrSplitBySize (reference src/tensor_ops.cc:33-45,
     src/cuda/batch_split.cu): per-batch pieces of a super-batch result."""
