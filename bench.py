@@ -169,7 +169,8 @@ def sage_batch_api(graph, seeds, fused_name, relabel_name):
 
 
 def sage_group(ops, indptr, indices, seeds_2d, ptr_cache):
-    """G minibatches through the batched sampler (one fused sample + one batched relabel per hop)."""
+    """G minibatches through the batched sampler (one fused sample + one batched relabel per hop).  Outputs come
+    from a reusable arena (ptr_cache["arena"]): the loop allocates only while the arena is still growing."""
     G, S0 = seeds_2d.shape
     ptr = ptr_cache.get(G)
     if ptr is None:
@@ -179,7 +180,10 @@ def sage_group(ops, indptr, indices, seeds_2d, ptr_cache):
     # one host wait per hop: the exact frontier size sizes the next hop.  Queuing all hops on upper bounds
     # (sync=False) was measured slower here: bounds overshoot the real sizes 3.5x, which costs more in table
     # clears and empty CTAs (9.1 G edges/s) than the three waits do (10.0 G).
-    hops = ops.sage_sample_batches(indptr, indices, seeds_2d.reshape(-1), ptr, FANOUTS, replace=False)
+    arena = ptr_cache.get("arena")
+    if arena is None:
+        arena = ptr_cache["arena"] = ops.OutputArena()
+    hops = ops.sage_sample_batches(indptr, indices, seeds_2d.reshape(-1), ptr, FANOUTS, replace=False, arena=arena)
     shapes = [(int(h["seeds"].numel()), int(h["indices"].numel()), int(h["frontier"].numel())) for h in hops]
     return sum(e for _, e, _ in shapes), shapes
 

@@ -806,7 +806,29 @@ def indptr_split_by_size(indptr, size, ctx=None):
     return list(torch.split(out, int(size) + 1))
 
 
-def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None, sync=True):
+class OutputArena:
+    """Reusable output buffers for a loop that calls the same operator again and again (a sampler feeding a
+    trainer): the first calls allocate, with 25 % headroom, and later calls of similar size allocate nothing, so
+    the loop never waits for cudaMalloc — which serialises across the processes of a multi-GPU job.
+    Results handed out from an arena are overwritten by the next call that uses it."""
+
+    def __init__(self):
+        self._buffers = {}
+
+    def get(self, key, n, like, dtype=torch.int64):
+        n = int(n)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n or buf.device != like.device or buf.dtype != dtype:
+            buf = torch.empty(max(16, n + n // 4), dtype=dtype, device=like.device)
+            self._buffers[key] = buf
+        return buf[:n]
+
+    def bytes(self):
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None, sync=True,
+                        arena=None):
     """Multi-hop GraphSAGE sampling of G minibatches at once (the loop of
     examples/graphsage/batching.py:56-90): per hop one fused slice+sample over the seeds of all batches,
     then one batched unique + relabel; each batch's frontier becomes its seeds for the next hop.
@@ -818,18 +840,24 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
     sync=True waits once per hop and trims every array to its exact length.  sync=False queues all hops
     without waiting for the GPU: arrays keep their upper-bound length (S·k edges, S·(1+k) frontier entries
     per hop, so capacities grow by (1+k) per hop), the valid prefixes are given by the offset arrays, and
-    every dict carries `counts`, a 3-element device tensor (seeds, edges, frontier) to read when convenient."""
+    every dict carries `counts`, a 3-element device tensor (seeds, edges, frontier) to read when convenient.
+
+    arena: an OutputArena to take the output arrays from (they are then valid until the next call with it)."""
     ctx = ctx or default_context(indptr.device)
     out = []
     base_seed = next_seed(seed)
+
+    def alloc(name, hop, n):
+        return _empty(n, indptr) if arena is None else arena.get((name, hop), n, indptr)
+
     for hop, k in enumerate(fanouts):
         S = seeds.numel()
         G = seeds_ptr.numel() - 1
         cap = S * int(k)
-        sub_indptr = _empty(S + 1, indptr)
-        sub_indices, select, rel = _empty(cap, indptr), _empty(cap, indptr), _empty(cap, indptr)
-        indices_ptr, uniq_ptr = _empty(G + 1, indptr), _empty(G + 1, indptr)
-        uniq = _empty(S + cap, indptr)
+        sub_indptr = alloc("sub_indptr", hop, S + 1)
+        sub_indices, select, rel = alloc("indices", hop, cap), alloc("select", hop, cap), alloc("relabeled", hop, cap)
+        indices_ptr, uniq_ptr = alloc("indices_ptr", hop, G + 1), alloc("frontier_ptr", hop, G + 1)
+        uniq = alloc("frontier", hop, S + cap)
         nu, ne = c_i64(0), c_i64(0)
         ctx.check(ctx.lib.gsb_sage_hop(ctx.handle, _stream(), _p(indptr), _p(indices), _p(seeds), _p(seeds_ptr),
                                        c_i64(G), c_i64(S), c_i64(int(k)), c_int(int(bool(replace))),
