@@ -661,8 +661,10 @@ def run_kernels(args):
     bcol = seeds[sub_col]
     timed("BatchCOORelabel, 256 batches", lambda: ops.batch_coo_relabel(seeds, sptr, bcol, sub_row, bptr),
           lambda o: 8 * (S + D) + 8 * o[0].numel() + 8 * D + 16 * D)
-    timed("BatchCOOSlicing by membership, 256 batches", lambda: ops.batch_coo_slicing(1, sub_row, sub_col, bptr, rows, torch.arange(G + 1, device=device) * (rows.numel() // G)),
-          lambda o: 8 * rows.numel() + 16 * D + 16 * o[0].numel())
+    rptr = torch.arange(G + 1, device=device) * (rows.numel() // G)
+    rows_m = rows[:int(rows.numel() // G) * G].contiguous()   # the offsets must cover the whole member array
+    timed("BatchCOOSlicing by membership, 256 batches", lambda: ops.batch_coo_slicing(1, sub_row, sub_col, bptr, rows_m, rptr),
+          lambda o: 8 * rows_m.numel() + 16 * D + 16 * o[0].numel())
     enc = timed("BatchEncode", lambda: ops.batch_encode(sub_row, bptr, n), 16 * D)
     timed("GetBatchOffsets + decode", lambda: ops.get_batch_offsets(enc, G, n), 16 * D)
     timed("BatchConcat of 2 arrays", lambda: ops.batch_concat([seeds, sub_row], [sptr, bptr]), 24 * (S + D))
@@ -672,10 +674,105 @@ def run_kernels(args):
                       "operators": results}))
 
 
+def run_kernels_reference(args):
+    """The reference's own CUDA operators (unmodified sources compiled for sm_100) on the inputs of run_kernels,
+    timed the same way: the per-operator counterpart of `--impl reference`.  Secondary output."""
+    import torch
+    lib = os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so")
+    if not os.path.exists(lib):
+        print(json.dumps({"metric": "per_operator_time", "impl": "reference",
+                          "unavailable": "oracle/_ref/libgs_ref.so is not built (oracle/build_ref.sh)"}))
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    from graph_sampling_b200.synthetic import rmat_csc
+    torch.classes.load_library(lib)
+    Graph, ops = torch.classes.gs_classes.Graph, torch.ops.gs_ops
+    indptr, indices = rmat_csc(args.nodes, args.edges, seed=GRAPH_SEED, symmetric=True, max_degree=MAX_DEGREE,
+                               device=device)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    n = args.nodes
+    _COO, _CSC, _CSR = 1, 2, 4
+    g = torch.Generator(device=device)
+    g.manual_seed(1)
+    results = []
+
+    def timed(name, fn, reps=10):
+        try:
+            for _ in range(3):
+                out = fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                out = fn()
+            e1.record()
+            torch.cuda.synchronize()
+            results.append({"op": name, "ms": round(e0.elapsed_time(e1) / reps, 4)})
+            return out
+        except Exception as exc:  # an operator the reference cannot run at this size is reported, not fatal
+            results.append({"op": name, "ms": None, "error": str(exc).splitlines()[0][:120]})
+            return None
+
+    A = Graph(False)
+    A._CAPI_LoadCSC(indptr, indices)
+    S = 262_144
+    seeds = torch.randint(0, n, (S,), generator=g, device=device)
+    sub = timed("column slice (count + fill, COO out)", lambda: A._CAPI_Slicing(seeds, 0, _CSC, _CSC + _COO, False))
+    big = torch.randint(0, n, (2_600_000,), generator=g, device=device)
+    timed("fused slice + uniform sample, fanout 10", lambda: A._CAPI_FusedColumnwiseSlicingSampling(big, 10, False))
+    sub_indptr, sub_row, _ = sub._CAPI_GetCSC()
+    sub_col = sub._CAPI_GetCOO()[1]
+    D = sub_row.numel()
+    probs = torch.rand(D, generator=g, device=device) + 0.01
+    timed("weighted per-column sample, fanout 10", lambda: sub._CAPI_SamplingWithProbs(0, probs, 10, False, _CSC, _CSC))
+    timed("unique + relabel (single table)", lambda: sub._CAPI_Relabel())
+    F = 256
+    x = torch.randn(n, F, generator=g, device=device)
+    xd = x[seeds]
+    out = torch.zeros(D, 1, device=device)
+    timed("SDDMM dot, F = 256", lambda: sub._CAPI_SDDMM("dot", x, xd, out, 0, 2, _COO))
+    w = torch.rand(D, generator=g, device=device)
+    sub._CAPI_SetData(w)
+    timed("segment sum of squares (CSC)", lambda: sub._CAPI_Sum(0, 2, _CSC))
+    timed("segment sum of squares (COO, atomics)", lambda: sub._CAPI_Sum(1, 2, _COO))
+    timed("segment normalize (CSC)", lambda: sub._CAPI_Normalize(0, _CSC))
+    rows = torch.randperm(n, generator=g, device=device)[:100_000]
+    timed("row slice by membership (CSC)", lambda: sub._CAPI_Slicing(rows, 1, _CSC, _CSC + _COO, False))
+    lp = torch.rand(1_000_000, generator=g, device=device)
+    lp[torch.rand(1_000_000, generator=g, device=device) < 0.5] = 0
+    ld = torch.arange(1_000_000, device=device)
+    timed("list sampling, 512 of 1 M weighted", lambda: ops._CAPI_ListSamplingWithProbs(ld, lp, 512, False))
+    fr = torch.randint(0, n, (1_000_000,), generator=g, device=device)
+    timed("feature rows gather, F = 256 (1 M rows)", lambda: x[fr])    # the reference indexes with torch here
+    del x, xd
+    torch.cuda.empty_cache()
+    timed("induced subgraph (262 k columns x 100 k rows)", lambda: A._CAPI_FusionSlicing(seeds, rows))
+    G = 256
+    bptr = torch.arange(G + 1, device=device) * (D // G)
+    bptr[-1] = D
+    sptr = torch.arange(G + 1, device=device) * (S // G)
+    timed("BatchUnique, 256 batches", lambda: ops._CAPI_BatchUnique(sub_row, bptr))
+    timed("BatchUnique2 (sorted), 256 batches", lambda: ops._CAPI_BatchUnique2(sub_row, bptr))
+    bcol = seeds[sub_col]
+    timed("BatchCOORelabel, 256 batches", lambda: ops._CAPI_BatchCOORelabel(seeds, sptr, bcol, sub_row, bptr))
+    rptr = torch.arange(G + 1, device=device) * (rows.numel() // G)
+    rows_m = rows[:int(rows.numel() // G) * G].contiguous()   # the offsets must cover the whole member array
+    timed("BatchCOOSlicing by membership, 256 batches", lambda: ops._CAPI_BatchCOOSlicing(1, sub_row, sub_col, bptr, rows_m, rptr))
+    enc = timed("BatchEncode", lambda: ops._CAPI_BatchEncode(sub_row, bptr, n))
+    if enc is not None:
+        timed("GetBatchOffsets + decode", lambda: ops._CAPI_GetBatchOffsets(enc, G, n))
+    timed("BatchConcat of 2 arrays", lambda: ops._CAPI_BatchConcat([seeds, sub_row], [sptr, bptr]))
+    timed("segmented list sampling, 256 x 4000 of 13 M", lambda: ops._CAPI_BatchListSamplingWithProbs(probs, 4000, False, bptr))
+    print(json.dumps({"metric": "per_operator_time", "unit": "ms", "impl": "reference",
+                      "graph": {"nodes": n, "edges": int(indices.numel())}, "operators": results}))
+
+
 if __name__ == "__main__":
     a = parse()
     if a.workload == "kernels":
-        run_kernels(a)
+        run_kernels_reference(a) if a.impl == "reference" else run_kernels(a)
     elif a.workload == "walk":
         run_walk(a)
     elif a.impl == "reference":

@@ -6,15 +6,17 @@
 //   split                       the inverse of concat                          src/cuda/batch_split2.cu:11-106
 //   list sampling               weighted k-of-segment without replacement      src/cuda/list_sampling_probs.cu:92-183
 //
-// All of them are one pass over the items: each thread finds the batch of its item with a binary search
-// over the offset array (G + 1 entries, a few KB that stay in L1) where the reference materialises a key
-// array per item first.  Segmented list sampling ranks every item by (segment, A-Res key) with the
-// stable radix sort and keeps the first min(k, size) of each segment; the reference runs a segmented
-// sort of all keys as well (cub_segmentedSortPairsDescending).
+// All of them are one pass over the items: a warp finds the batch of the first of its 256 consecutive items with
+// a binary search over the offset array (G + 1 entries, a few KB that stay in L1) and walks forward from there,
+// where the reference materialises a key array per item first.  Segmented list sampling ranks by (segment,
+// A-Res key): two per-segment histogram passes over the top 16 bits of the ranking word find a threshold that
+// keeps a few more than min(k, size) candidates per segment, and only the candidates are sorted (stable radix
+// sort); the reference segment-sorts every key (cub_segmentedSortPairsDescending).
 #include "batch_table.cuh"
 #include "common.cuh"
 #include "philox.cuh"
 #include "radix_sort.cuh"
+#include "scan.cuh"
 
 namespace gsb {
 
@@ -30,8 +32,7 @@ struct PtrTable {
 __global__ void __launch_bounds__(kOpThreads) k_batch_encode(const i64* __restrict__ data,
                                                              const i64* __restrict__ data_ptr, i64 G, i64 n,
                                                              i64 encoding_size, i64* __restrict__ out) {
-  for (i64 i = (i64)blockIdx.x * kOpThreads + threadIdx.x; i < n; i += (i64)gridDim.x * kOpThreads)
-    out[i] = __ldg(data + i) + batch_of(data_ptr, G, i) * encoding_size;
+  for_each_item_with_batch(data_ptr, G, n, [&](i64 i, i64 b) { out[i] = __ldg(data + i) + b * encoding_size; });
 }
 
 __global__ void __launch_bounds__(kOpThreads) k_batch_decode(const i64* __restrict__ data, i64 n, i64 encoding_size,
@@ -73,20 +74,18 @@ __global__ void __launch_bounds__(kOpThreads) k_batch_concat(PtrTable t, int seg
                                                              i64* __restrict__ out_key) {
   const i64* __restrict__ data = t.data[seg];
   const i64* __restrict__ ptr = t.ptr[seg];
-  for (i64 i = (i64)blockIdx.x * kOpThreads + threadIdx.x; i < len; i += (i64)gridDim.x * kOpThreads) {
-    const i64 b = batch_of(ptr, G, i);
+  for_each_item_with_batch(ptr, G, len, [&](i64 i, i64 b) {
     i64 dst = __ldg(out_ptr + b) + (i - __ldg(ptr + b));
     for (int s = 0; s < seg; ++s) dst += __ldg(t.ptr[s] + b + 1) - __ldg(t.ptr[s] + b);
     out[dst] = __ldg(data + i);
     if (out_key) out_key[dst] = b;
-  }
+  });
 }
 
 __global__ void __launch_bounds__(kOpThreads) k_batch_split(const i64* __restrict__ data,
                                                             const i64* __restrict__ data_ptr, i64 n, i64 G,
                                                             PtrTable t) {
-  for (i64 i = (i64)blockIdx.x * kOpThreads + threadIdx.x; i < n; i += (i64)gridDim.x * kOpThreads) {
-    const i64 b = batch_of(data_ptr, G, i);
+  for_each_item_with_batch(data_ptr, G, n, [&](i64 i, i64 b) {
     i64 local = i - __ldg(data_ptr + b);
     for (int s = 0; s < t.n; ++s) {
       const i64 begin = __ldg(t.ptr[s] + b);
@@ -97,7 +96,7 @@ __global__ void __launch_bounds__(kOpThreads) k_batch_split(const i64* __restric
       }
       local -= len;
     }
-  }
+  });
 }
 
 // ---- segmented weighted list sampling ----------------------------------------------------------------
@@ -107,33 +106,168 @@ __device__ __forceinline__ uint32_t orderable_desc_f32(float f) {
   return ~((u & 0x80000000u) ? ~u : (u | 0x80000000u));
 }
 
+// Pass 1: the 32-bit ranking word of every item (smaller = better) and, per segment, how many items fall into
+// each value of its top byte.  Lanes of a warp that hit the same counter add once (__match_any_sync).
+__device__ __forceinline__ void count_bin(unsigned* __restrict__ hist, i64 segment, unsigned bin) {
+  const unsigned slot = (unsigned)segment * 256u + bin;
+  const unsigned active = __activemask();
+  const unsigned peers = __match_any_sync(active, slot);
+  if ((int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(hist + slot, (unsigned)__popc(peers));
+}
+
 __global__ void __launch_bounds__(kOpThreads) k_blist_keys(const float* __restrict__ probs, i64 N,
                                                            const i64* __restrict__ range, i64 G, u64 seed,
-                                                           u64* __restrict__ keys, i64* __restrict__ vals) {
-  for (i64 i = (i64)blockIdx.x * kOpThreads + threadIdx.x; i < N; i += (i64)gridDim.x * kOpThreads) {
+                                                           uint32_t* __restrict__ key32, unsigned* __restrict__ hist_a) {
+  for_each_item_with_batch(range, G, N, [&](i64 i, i64 b) {
     const float key = ares_key(rand_u32(seed, (u64)i, 0, STREAM_LIST_WEIGHTED), __ldg(probs + i));
-    keys[i] = ((u64)batch_of(range, G, i) << 32) | (u64)orderable_desc_f32(key);
-    vals[i] = i;
-  }
+    const uint32_t w = orderable_desc_f32(key);
+    key32[i] = w;
+    count_bin(hist_a, b, w >> 24);
+  });
 }
 
-__global__ void __launch_bounds__(kOpThreads) k_blist_counts(const i64* __restrict__ range, i64 G, i64 k,
-                                                             i64* __restrict__ out_range) {
+// Per segment: out_range[b] = min(k, size); the top-byte value in which the k-th best item lies and how many items
+// are strictly better than that byte (pass 2), then the same one byte further down (pass 4): afterwards every item
+// whose top 16 bits are <= threshold16[b] is a candidate, and at least min(k, size) items are.
+struct ListSelect {
+  unsigned bin_a;     // top byte of the k-th best word
+  unsigned need;      // how many winners must still come from inside bin_a (after pass 2) / bin_a:bin_b (after pass 4)
+  unsigned thresh16;  // candidates: (word >> 16) <= thresh16
+  unsigned pad;
+};
+
+__global__ void __launch_bounds__(kOpThreads) k_blist_select(const i64* __restrict__ range, i64 G, i64 k,
+                                                             const unsigned* __restrict__ hist, int second,
+                                                             ListSelect* __restrict__ sel, i64* __restrict__ out_range) {
   const i64 b = (i64)blockIdx.x * kOpThreads + threadIdx.x;
   if (b > G) return;
-  out_range[b] = b < G ? min(k, __ldg(range + b + 1) - __ldg(range + b)) : 0;
+  if (b == G) {
+    if (!second) out_range[G] = 0;
+    return;
+  }
+  const i64 size = __ldg(range + b + 1) - __ldg(range + b);
+  const i64 want = min(k, size);
+  if (!second) out_range[b] = want;
+  if (size <= k) {  // everything wins
+    if (!second) sel[b] = ListSelect{0xFFFFFFFFu, 0u, 0xFFFFu, 0u};
+    return;
+  }
+  unsigned need = second ? sel[b].need : (unsigned)want;
+  const unsigned* h = hist + b * 256;
+  unsigned bin = 0;
+  for (; bin < 255u; ++bin) {
+    const unsigned c = h[bin];
+    if (c >= need) break;
+    need -= c;
+  }
+  if (!second) sel[b] = ListSelect{bin, need, 0u, 0u};
+  else sel[b].thresh16 = (sel[b].bin_a << 8) | bin;
 }
 
-__global__ void __launch_bounds__(kOpThreads) k_blist_emit(const i64* __restrict__ sorted_vals, i64 N,
-                                                           const i64* __restrict__ range, i64 G,
+// Pass 3: inside the selected top byte, the histogram of the next byte.
+__global__ void __launch_bounds__(kOpThreads) k_blist_hist_b(const uint32_t* __restrict__ key32, i64 N,
+                                                             const i64* __restrict__ range, i64 G,
+                                                             const ListSelect* __restrict__ sel,
+                                                             unsigned* __restrict__ hist_b) {
+  for_each_item_with_batch(range, G, N, [&](i64 i, i64 b) {
+    const uint32_t w = key32[i];
+    if ((w >> 24) == sel[b].bin_a) count_bin(hist_b, b, (w >> 16) & 0xFFu);
+  });
+}
+
+// Pass 5: candidates in input order (ballot ranking + look-back), as (segment << 32 | word, position) pairs, and
+// the candidate offset of every segment.
+__global__ void __launch_bounds__(kOpThreads) k_blist_compact(const uint32_t* __restrict__ key32, i64 N,
+                                                              const i64* __restrict__ range, i64 G,
+                                                              const ListSelect* __restrict__ sel,
+                                                              u64* __restrict__ cand_keys, i64* __restrict__ cand_vals,
+                                                              i64* __restrict__ cand_ptr, i64* counters, TileState ts) {
+  constexpr int kLane = 4, kWarp = 32 * kLane, kTile = (kOpThreads / 32) * kWarp;
+  __shared__ i64 s_warp_total[kOpThreads / 32];
+  __shared__ i64 s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tile = blockIdx.x;
+  const i64 tile_base = (i64)tile * kTile;
+  const i64 base = tile_base + (i64)warp * kWarp;
+  const i64 end = min(N, base + kWarp);
+  bool keep[kLane];
+  i64 seg[kLane];
+  uint32_t word[kLane];
+  i64 b = base < N ? batch_of(range, G, base) : 0;
+  i64 next = base < N ? __ldg(range + b + 1) : 0;
+#pragma unroll
+  for (int q = 0; q < kLane; ++q) {
+    const i64 i = base + q * 32 + lane;
+    keep[q] = false;
+    seg[q] = 0;
+    word[q] = 0;
+    if (i < end) {
+      while (i >= next && b + 1 < G) {
+        ++b;
+        next = __ldg(range + b + 1);
+      }
+      seg[q] = b;
+      word[q] = key32[i];
+      keep[q] = (word[q] >> 16) <= sel[b].thresh16;
+    }
+  }
+  const unsigned lt = (1u << lane) - 1u;
+  unsigned rank[kLane];
+  unsigned run = 0;
+#pragma unroll
+  for (int q = 0; q < kLane; ++q) {
+    const unsigned bal = __ballot_sync(0xffffffffu, keep[q]);
+    rank[q] = run + __popc(bal & lt);
+    run += __popc(bal);
+  }
+  if (lane == 0) s_warp_total[warp] = run;
+  __syncthreads();
+  i64 warp_excl = 0, tile_total = 0;
+#pragma unroll
+  for (int x = 0; x < kOpThreads / 32; ++x) {
+    const i64 t = s_warp_total[x];
+    if (x < warp) warp_excl += t;
+    tile_total += t;
+  }
+  if (warp == 0) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, tile_total);
+    if (lane == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const i64 warp_pos = s_base + warp_excl;
+#pragma unroll
+  for (int q = 0; q < kLane; ++q) {
+    const i64 i = base + q * 32 + lane;
+    if (i < end) {
+      const i64 pos = warp_pos + rank[q];
+      if (i == __ldg(range + seg[q])) {  // first item of its segment (and of the empty segments right before it)
+        cand_ptr[seg[q]] = pos;
+        for (i64 e = seg[q] - 1; e >= 0 && __ldg(range + e) == i; --e) cand_ptr[e] = pos;
+      }
+      if (keep[q]) {
+        cand_keys[pos] = ((u64)seg[q] << 32) | (u64)word[q];
+        cand_vals[pos] = i;
+      }
+    }
+  }
+  if (tile_base + kTile >= N && threadIdx.x == 0) {
+    const i64 total = s_base + tile_total;
+    cand_ptr[G] = total;
+    for (i64 e = G - 1; e >= 0 && __ldg(range + e) == N; --e) cand_ptr[e] = total;
+    counters[CNT_AUX0] = total;
+  }
+}
+
+// Pass 7: the first min(k, size) sorted candidates of every segment are the sample.
+__global__ void __launch_bounds__(kOpThreads) k_blist_emit(const i64* __restrict__ sorted_vals,
+                                                           const i64* __restrict__ cand_ptr, i64 G,
                                                            const i64* __restrict__ out_range,
                                                            i64* __restrict__ out_idx, i64* counters) {
-  for (i64 i = (i64)blockIdx.x * kOpThreads + threadIdx.x; i < N; i += (i64)gridDim.x * kOpThreads) {
-    const i64 b = batch_of(range, G, i);
-    const i64 r = i - __ldg(range + b);
+  for_each_item_with_batch(cand_ptr, G, cand_ptr[G], [&](i64 p, i64 b) {
+    const i64 r = p - __ldg(cand_ptr + b);
     const i64 o = __ldg(out_range + b);
-    if (r < __ldg(out_range + b + 1) - o) out_idx[o + r] = __ldg(sorted_vals + i);
-  }
+    if (r < __ldg(out_range + b + 1) - o) out_idx[o + r] = __ldg(sorted_vals + p);
+  });
   if (blockIdx.x == 0 && threadIdx.x == 0) counters[CNT_NNZ] = out_range[G];
 }
 
@@ -244,38 +378,71 @@ int gsb_batch_list_sample(gsb_ctx* ctx, void* stream_, const float* probs, int64
                           int64_t G, int64_t k, uint64_t seed, int64_t* out_idx, int64_t* out_range,
                           int64_t* n_out_host) {
   GSB_REQUIRE(ctx && range && out_range && N >= 0 && G >= 1 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
-  GSB_REQUIRE(N < 0xFFFFFFFFll && G < (1ll << 31), GSB_ERR_UNSUPPORTED);
+  GSB_REQUIRE(N < 0xFFFFFFFFll && G < (1ll << 23), GSB_ERR_UNSUPPORTED);
   GSB_REQUIRE(N == 0 || (probs && out_idx), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   const int wide = kNumSMs * 8;
-  k_blist_counts<<<grid_for(G + 1, kOpThreads), kOpThreads, 0, stream>>>(range, G, k, out_range);
-  GSB_LAUNCH_OK();
-  int st = exclusive_scan_i64(ctx, stream, out_range, G + 1);
-  if (st != GSB_OK) return st;
-  ctx_count_launches(ctx, 1);
+  const int grid_n = min(grid_for(N, kOpThreads), wide);
+  const int grid_g = grid_for(G + 1, kOpThreads);
   i64* counters = ctx_counters(ctx);
+  // workspace: 32-bit words, two histograms, the per-segment selection state, candidate offsets
+  const size_t key_bytes = ((size_t)N * 4 + 255) & ~(size_t)255;
+  const size_t hist_bytes = (size_t)G * 256 * sizeof(unsigned);
+  const size_t sel_bytes = ((size_t)G * sizeof(ListSelect) + 255) & ~(size_t)255;
+  const size_t ptr_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
+  const size_t fixed = key_bytes + 2 * hist_bytes + sel_bytes + ptr_bytes;
+  // candidates: at most N; they are sorted in a second reservation once their number is known, so the first part
+  // of the workspace (which a larger reservation would move) is copied nowhere: the candidate arrays come first
+  const size_t pair_bytes = ((size_t)N * 8 + 255) & ~(size_t)255;
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, 2 * pair_bytes + radix_sort_scratch_bytes(N) + fixed, &ws);
+  if (st != GSB_OK) return st;
+  u64* cand_keys = (u64*)ws;
+  i64* cand_vals = (i64*)((char*)ws + pair_bytes);
+  void* sort_ws = (char*)ws + 2 * pair_bytes;
+  char* tail = (char*)sort_ws + radix_sort_scratch_bytes(N);
+  uint32_t* key32 = (uint32_t*)tail;
+  unsigned* hist_a = (unsigned*)(tail + key_bytes);
+  unsigned* hist_b = hist_a + (size_t)G * 256;
+  ListSelect* sel = (ListSelect*)(tail + key_bytes + 2 * hist_bytes);
+  i64* cand_ptr = (i64*)(tail + key_bytes + 2 * hist_bytes + sel_bytes);
+  GSB_CUDA_OK(cudaMemsetAsync(hist_a, 0, 2 * hist_bytes, stream));
+  ScopedKernelTimer timer(ctx, KID_LIST_SAMPLE, stream);
   if (N > 0) {
-    const size_t pair_bytes = ((size_t)N * 8 + 255) & ~(size_t)255;
-    void* ws;
-    st = ctx_reserve_workspace(ctx, 2 * pair_bytes + radix_sort_scratch_bytes(N), &ws);
-    if (st != GSB_OK) return st;
-    u64* keys = (u64*)ws;
-    i64* vals = (i64*)((char*)ws + pair_bytes);
-    void* sort_ws = (char*)ws + 2 * pair_bytes;
-    {
-      ScopedKernelTimer timer(ctx, KID_LIST_SAMPLE, stream);
-      k_blist_keys<<<min(grid_for(N, kOpThreads), wide), kOpThreads, 0, stream>>>(probs, N, range, G, (u64)seed, keys,
-                                                                                 vals);
-    }
+    k_blist_keys<<<grid_n, kOpThreads, 0, stream>>>(probs, N, range, G, (u64)seed, key32, hist_a);
     GSB_LAUNCH_OK();
-    st = radix_sort_pairs(ctx, stream, keys, vals, N, 0, 32 + bits_for(G), sort_ws);
+  }
+  k_blist_select<<<grid_g, kOpThreads, 0, stream>>>(range, G, k, hist_a, 0, sel, out_range);
+  GSB_LAUNCH_OK();
+  st = exclusive_scan_i64(ctx, stream, out_range, G + 1);
+  if (st != GSB_OK) return st;
+  if (N > 0) {
+    k_blist_hist_b<<<grid_n, kOpThreads, 0, stream>>>(key32, N, range, G, sel, hist_b);
+    GSB_LAUNCH_OK();
+    k_blist_select<<<grid_g, kOpThreads, 0, stream>>>(range, G, k, hist_b, 1, sel, out_range);
+    GSB_LAUNCH_OK();
+    const int tiles = grid_for(N, (kOpThreads / 32) * 128);
+    TileState ts;
+    st = ctx_tile_state(ctx, tiles, stream, &ts);
     if (st != GSB_OK) return st;
-    {
-      ScopedKernelTimer timer(ctx, KID_LIST_SAMPLE, stream);
-      k_blist_emit<<<min(grid_for(N, kOpThreads), wide), kOpThreads, 0, stream>>>(vals, N, range, G, out_range,
+    k_blist_compact<<<tiles, kOpThreads, 0, stream>>>(key32, N, range, G, sel, cand_keys, cand_vals, cand_ptr,
+                                                     counters, ts);
+    GSB_LAUNCH_OK();
+    ctx_count_launches(ctx, 6);
+    const i64* c;
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, CNT_AUX0 + 1, &c);  // the number of candidates sizes the sort
+    if (st != GSB_OK) return st;
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+    const i64 M = c[CNT_AUX0];
+    st = radix_sort_pairs(ctx, stream, cand_keys, cand_vals, M, 0, 32 + bits_for(G), sort_ws);
+    if (st != GSB_OK) return st;
+    if (M > 0) {
+      k_blist_emit<<<min(grid_for(M, kOpThreads), wide), kOpThreads, 0, stream>>>(cand_vals, cand_ptr, G, out_range,
                                                                                  out_idx, counters);
+      GSB_LAUNCH_OK();
+    } else {
+      GSB_CUDA_OK(cudaMemsetAsync(counters + CNT_NNZ, 0, sizeof(i64), stream));
     }
-    GSB_LAUNCH_OK();
   } else {
     GSB_CUDA_OK(cudaMemsetAsync(counters + CNT_NNZ, 0, sizeof(i64), stream));
   }

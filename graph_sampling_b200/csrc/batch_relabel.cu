@@ -401,26 +401,7 @@ __global__ void __launch_bounds__(kBThreads) k_split_indptr(const i64* __restric
 // Batch number of every frontier entry (the `key` output of BatchUnique).
 __global__ void __launch_bounds__(kBThreads) k_unique_keys(const i64* __restrict__ unique_ptr, i64 G,
                                                            i64* __restrict__ out_key) {
-  const i64 u = unique_ptr[G];
-  for (i64 i = (i64)blockIdx.x * kBThreads + threadIdx.x; i < u; i += (i64)gridDim.x * kBThreads)
-    out_key[i] = batch_of(unique_ptr, G, i);
-}
-
-// (batch << 32 | id) sort keys of the frontier entries, for the sorted flavour of BatchUnique.
-__global__ void __launch_bounds__(kBThreads) k_unique_sort_keys(const i64* __restrict__ unique,
-                                                                const i64* __restrict__ unique_ptr, i64 G,
-                                                                u64* __restrict__ keys, i64* __restrict__ vals) {
-  const i64 u = unique_ptr[G];
-  for (i64 i = (i64)blockIdx.x * kBThreads + threadIdx.x; i < u; i += (i64)gridDim.x * kBThreads) {
-    keys[i] = ((u64)batch_of(unique_ptr, G, i) << 32) | (u64)__ldg(unique + i);
-    vals[i] = i;
-  }
-}
-
-__global__ void __launch_bounds__(kBThreads) k_unique_from_keys(const u64* __restrict__ keys, i64 u,
-                                                                i64* __restrict__ unique) {
-  for (i64 i = (i64)blockIdx.x * kBThreads + threadIdx.x; i < u; i += (i64)gridDim.x * kBThreads)
-    unique[i] = (i64)(keys[i] & 0xFFFFFFFFull);
+  for_each_item_with_batch(unique_ptr, G, unique_ptr[G], [&](i64 i, i64 b) { out_key[i] = b; });
 }
 
 // Per-batch membership filter of COO edges: edge i (batch b by edge_ptr) survives when target[i] is in
@@ -512,6 +493,91 @@ __global__ void __launch_bounds__(kBThreads) k_batch_filter(BatchLayout L, Filte
     p.out_ptr[L.G] = total;
     for (i64 e = L.G - 1; e >= 0 && __ldg(p.edge_ptr + e) == p.E; --e) p.out_ptr[e] = total;
     counters[CNT_NNZ] = total;
+  }
+}
+
+// ---- sorted flavour of BatchUnique: sort (batch << 32 | id) keys, keep each key's first copy ------------------
+__global__ void __launch_bounds__(kBThreads) k_batch_sort_keys(const i64* __restrict__ data,
+                                                               const i64* __restrict__ data_ptr, i64 G, i64 n,
+                                                               u64* __restrict__ keys, i64* counters) {
+  for_each_item_with_batch(data_ptr, G, n, [&](i64 i, i64 b) {
+    const i64 id = __ldg(data + i);
+    if (!valid_id(id)) {
+      raise_error(counters, GSB_ERR_INDEX_RANGE, i);
+      keys[i] = ((u64)b << 32) | 0xFFFFFFFFull;
+    } else {
+      keys[i] = ((u64)b << 32) | (u64)id;
+    }
+  });
+}
+
+__global__ void __launch_bounds__(kBThreads) k_sorted_unique_compact(const u64* __restrict__ keys, i64 n, i64 G,
+                                                                     i64* __restrict__ out_unique,
+                                                                     i64* __restrict__ out_key,
+                                                                     i64* __restrict__ out_ptr, i64* counters,
+                                                                     TileState ts) {
+  __shared__ i64 s_warp_total[kBThreads / 32];
+  __shared__ i64 s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tile = blockIdx.x;
+  const i64 tile_base = (i64)tile * kBTile;
+  if (tile_base >= n && !(n == 0 && tile == 0)) return;
+  const i64 base = tile_base + (i64)warp * kWarpItems;
+  const i64 end = min(n, base + kWarpItems);
+  u64 key[kLaneItems], prev[kLaneItems];
+  bool first[kLaneItems];
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    const i64 i = base + q * 32 + lane;
+    first[q] = false;
+    key[q] = prev[q] = 0;
+    if (i < end) {
+      key[q] = keys[i];
+      prev[q] = i > 0 ? keys[i - 1] : ~key[q];
+      first[q] = key[q] != prev[q];
+    }
+  }
+  const unsigned lt = (1u << lane) - 1u;
+  unsigned rank[kLaneItems];
+  unsigned run = 0;
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    const unsigned bal = __ballot_sync(0xffffffffu, first[q]);
+    rank[q] = run + __popc(bal & lt);
+    run += __popc(bal);
+  }
+  if (lane == 0) s_warp_total[warp] = run;
+  __syncthreads();
+  i64 warp_excl = 0, tile_total = 0;
+#pragma unroll
+  for (int x = 0; x < kBThreads / 32; ++x) {
+    const i64 t = s_warp_total[x];
+    if (x < warp) warp_excl += t;
+    tile_total += t;
+  }
+  if (warp == 0) {
+    const i64 prefix = tile_exclusive_prefix(ts, tile, tile_total);
+    if (lane == 0) s_base = prefix;
+  }
+  __syncthreads();
+  const i64 warp_pos = s_base + warp_excl;
+#pragma unroll
+  for (int q = 0; q < kLaneItems; ++q) {
+    const i64 i = base + q * 32 + lane;
+    if (i < end && first[q]) {
+      const i64 pos = warp_pos + rank[q];
+      const i64 b = (i64)(key[q] >> 32);
+      out_unique[pos] = (i64)(key[q] & 0xFFFFFFFFull);
+      if (out_key) out_key[pos] = b;
+      const i64 pb = i > 0 ? (i64)(prev[q] >> 32) : -1;
+      for (i64 e = pb + 1; e <= b; ++e) out_ptr[e] = pos;  // batch b starts here; the batches skipped were empty
+    }
+  }
+  if (tile_base + kBTile >= n && threadIdx.x == 0) {
+    const i64 total = s_base + tile_total;
+    const i64 last = n > 0 ? (i64)(keys[n - 1] >> 32) : -1;
+    for (i64 e = last + 1; e <= G; ++e) out_ptr[e] = total;
+    counters[CNT_UNIQUE] = total;
   }
 }
 
@@ -807,45 +873,53 @@ int gsb_batch_unique(gsb_ctx* ctx, void* stream_, const int64_t* data, const int
                      int64_t* unique_total_host) {
   GSB_REQUIRE(ctx && data_ptr && out_unique_ptr && G >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(n == 0 || (data && out_unique), GSB_ERR_INVALID_ARGUMENT);
-  GSB_REQUIRE(!sorted || unique_total_host, GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(n < (1ll << 31) && G < (1ll << 31), GSB_ERR_UNSUPPORTED);
   cudaStream_t stream = (cudaStream_t)stream_;
-  BatchLayout L;
-  const size_t pair_bytes = ((size_t)n * 8 + 255) & ~(size_t)255;
-  const size_t extra = sorted ? 2 * pair_bytes + radix_sort_scratch_bytes(n) : 0;
-  void* extra_ws = nullptr;
-  int st = build_batch_tables(ctx, stream, data, data_ptr, n, nullptr, nullptr, 0, G, out_unique, out_unique_ptr, &L,
-                              extra, &extra_ws);
-  if (st != GSB_OK) return st;
   const int wide = kNumSMs * 8;
   const int grid = max(1, min(grid_for(n, kBThreads), wide));
-  if (out_unique_key && n > 0) {
-    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_unique_keys<<<grid, kBThreads, 0, stream>>>(out_unique_ptr, G, out_unique_key);
+  if (!sorted) {
+    BatchLayout L;
+    int st = build_batch_tables(ctx, stream, data, data_ptr, n, nullptr, nullptr, 0, G, out_unique, out_unique_ptr, &L,
+                                0, nullptr);
+    if (st != GSB_OK) return st;
+    if (out_unique_key && n > 0) {
+      ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+      k_unique_keys<<<grid, kBThreads, 0, stream>>>(out_unique_ptr, G, out_unique_key);
+      GSB_LAUNCH_OK();
+    }
+    return unique_total_host ? read_totals(ctx, stream, unique_total_host, nullptr) : GSB_OK;
+  }
+  // sorted: no table at all — (batch << 32 | id) keys, a keys-only radix sort over the bits in use, then the
+  // first copy of every key (the reference segment-sorts and runs unique-by-key: src/cuda/batch_unique.cu:215-260)
+  const size_t key_bytes = ((size_t)n * 8 + 255) & ~(size_t)255;
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, key_bytes + radix_sort_scratch_bytes(n) + 256, &ws);
+  if (st != GSB_OK) return st;
+  u64* keys = (u64*)ws;
+  void* sort_ws = (char*)ws + key_bytes;
+  i64* counters = ctx_counters(ctx);
+  if (n > 0) {
+    {
+      ScopedKernelTimer timer(ctx, KID_SORT, stream);
+      k_batch_sort_keys<<<grid, kBThreads, 0, stream>>>(data, data_ptr, G, n, keys, counters);
+    }
     GSB_LAUNCH_OK();
+    int gbits = 0;
+    while (((i64)1 << gbits) < G) ++gbits;
+    st = radix_sort_pairs(ctx, stream, keys, nullptr, n, 0, 32 + gbits, sort_ws);
+    if (st != GSB_OK) return st;
   }
-  if (!sorted) return unique_total_host ? read_totals(ctx, stream, unique_total_host, nullptr) : GSB_OK;
-  st = read_totals(ctx, stream, unique_total_host, nullptr);
-  if (st != GSB_OK) return st;
-  const i64 u = *unique_total_host;
-  if (u <= 1) return GSB_OK;
-  u64* keys = (u64*)extra_ws;
-  i64* vals = (i64*)((char*)extra_ws + pair_bytes);
-  void* sort_ws = (char*)extra_ws + 2 * pair_bytes;
-  {
-    ScopedKernelTimer timer(ctx, KID_SORT, stream);
-    k_unique_sort_keys<<<grid, kBThreads, 0, stream>>>(out_unique, out_unique_ptr, G, keys, vals);
-  }
-  GSB_LAUNCH_OK();
-  int gbits = 0;
-  while (((i64)1 << gbits) < G) ++gbits;
-  st = radix_sort_pairs(ctx, stream, keys, vals, u, 0, 32 + gbits, sort_ws);
+  const int tiles = grid_for(n, kBTile);
+  TileState ts;
+  st = ctx_tile_state(ctx, tiles, stream, &ts);
   if (st != GSB_OK) return st;
   {
-    ScopedKernelTimer timer(ctx, KID_SORT, stream);
-    k_unique_from_keys<<<grid, kBThreads, 0, stream>>>(keys, u, out_unique);
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_sorted_unique_compact<<<tiles, kBThreads, 0, stream>>>(keys, n, G, out_unique, out_unique_key, out_unique_ptr,
+                                                            counters, ts);
   }
   GSB_LAUNCH_OK();
-  return GSB_OK;
+  return unique_total_host ? read_totals(ctx, stream, unique_total_host, nullptr) : GSB_OK;
 }
 
 int gsb_batch_coo_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, const int64_t* seeds_ptr,

@@ -66,6 +66,31 @@ __device__ __forceinline__ i64 batch_of(const i64* __restrict__ off, i64 G, i64 
   return lo;
 }
 
+// Calls f(i, b) for every item i in [0, n) with b = its batch (off: G + 1 offsets).  A warp takes 256 consecutive
+// items: one binary search for the first of them, then the batch number only walks forward — one search per 256
+// items instead of one per item (a search is 8 dependent loads whichever lanes take part).
+template <class F>
+__device__ __forceinline__ void for_each_item_with_batch(const i64* __restrict__ off, i64 G, i64 n, F f) {
+  constexpr int kPerLane = 8;
+  const int lane = threadIdx.x & 31;
+  const i64 warps = (i64)gridDim.x * (blockDim.x >> 5);
+  for (i64 base = ((i64)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 * kPerLane); base < n;
+       base += warps * (32 * kPerLane)) {
+    i64 b = batch_of(off, G, base);
+    i64 next = __ldg(off + b + 1);
+#pragma unroll
+    for (int q = 0; q < kPerLane; ++q) {
+      const i64 i = base + q * 32 + lane;
+      if (i >= n) break;
+      while (i >= next && b + 1 < G) {  // (the bound only matters for offsets that do not cover n)
+        ++b;
+        next = __ldg(off + b + 1);
+      }
+      f(i, b);
+    }
+  }
+}
+
 // Single-batch unique + relabel through the packed-slot batched kernels (defined in batch_relabel.cu).
 int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i64 S, const i64* second, i64 E,
                           i64* out_unique, i64* out_relabeled, i64* unique_host);

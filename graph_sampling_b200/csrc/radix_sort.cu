@@ -50,6 +50,11 @@ __global__ void __launch_bounds__(kSortThreads) k_radix_histogram(const u64* __r
   hist[(i64)threadIdx.x * num_tiles + tile] = s_count[threadIdx.x];
 }
 
+// Scatter of one pass.  Items are ranked inside the tile (stable: warps own consecutive ranges, a warp ranks 32
+// items at a time with __match_any_sync), staged in shared memory in digit order, and then written out so that
+// consecutive threads write consecutive addresses of a bin's run — full sectors instead of one 8-byte store
+// per item.  HAS_VALS = false sorts keys only (half the traffic).
+template <bool HAS_VALS>
 __global__ void __launch_bounds__(kSortThreads) k_radix_scatter(const u64* __restrict__ keys_in,
                                                                const i64* __restrict__ vals_in,
                                                                u64* __restrict__ keys_out, i64* __restrict__ vals_out,
@@ -58,11 +63,17 @@ __global__ void __launch_bounds__(kSortThreads) k_radix_scatter(const u64* __res
   constexpr int kWarps = kSortThreads / 32;
   constexpr int kRounds = kSortItemsPerThread;  // each warp owns kRounds * 32 consecutive items
   __shared__ unsigned s_warp_count[kWarps][kRadix];
+  __shared__ unsigned s_tile_start[kRadix];
   __shared__ i64 s_bin_base[kRadix];
+  __shared__ unsigned s_scan[kWarps];
+  __shared__ u64 s_keys[kSortTile];
+  __shared__ i64 s_vals[HAS_VALS ? kSortTile : 1];
   const int tile = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int q = threadIdx.x; q < kWarps * kRadix; q += kSortThreads) (&s_warp_count[0][0])[q] = 0;
   __syncthreads();
-  const i64 warp_base = (i64)tile * kSortTile + (i64)warp * (kRounds * 32);
+  const i64 tile_base = (i64)tile * kSortTile;
+  const int tile_items = (int)min((i64)kSortTile, n - tile_base);
+  const i64 warp_base = tile_base + (i64)warp * (kRounds * 32);
   u64 key[kRounds];
   i64 val[kRounds];
   unsigned rank[kRounds];
@@ -72,7 +83,7 @@ __global__ void __launch_bounds__(kSortThreads) k_radix_scatter(const u64* __res
     const i64 i = warp_base + r * 32 + lane;
     const bool valid = i < n;
     key[r] = valid ? keys_in[i] : 0;
-    val[r] = valid ? vals_in[i] : 0;
+    if (HAS_VALS) val[r] = valid ? vals_in[i] : 0;
     const unsigned digit = valid ? ((unsigned)(key[r] >> shift) & 0xFFu) : 0x1000u;
     const unsigned peers = __match_any_sync(0xffffffffu, digit);
     const unsigned before = __popc(peers & lt_mask);
@@ -84,6 +95,8 @@ __global__ void __launch_bounds__(kSortThreads) k_radix_scatter(const u64* __res
     rank[r] = base + before;
   }
   __syncthreads();
+  // per digit: exclusive prefix over the warps, the tile's count, and the bin's global base for this tile
+  unsigned count;
   {
     const int d = threadIdx.x;  // kSortThreads == kRadix
     unsigned run = 0;
@@ -93,18 +106,41 @@ __global__ void __launch_bounds__(kSortThreads) k_radix_scatter(const u64* __res
       s_warp_count[w][d] = run;
       run += c;
     }
+    count = run;
     s_bin_base[d] = hist[(i64)d * num_tiles + tile];
   }
+  // exclusive scan of the 256 digit counts -> where each digit's run starts inside the staged tile
+  unsigned inc = count;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) s_scan[warp] = inc;
+  __syncthreads();
+  unsigned warp_off = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w)
+    if (w < warp) warp_off += s_scan[w];
+  s_tile_start[threadIdx.x] = warp_off + inc - count;
   __syncthreads();
 #pragma unroll
   for (int r = 0; r < kRounds; ++r) {
     const i64 i = warp_base + r * 32 + lane;
     if (i < n) {
       const unsigned digit = (unsigned)(key[r] >> shift) & 0xFFu;
-      const i64 dst = s_bin_base[digit] + s_warp_count[warp][digit] + rank[r];
-      keys_out[dst] = key[r];
-      vals_out[dst] = val[r];
+      const unsigned pos = s_tile_start[digit] + s_warp_count[warp][digit] + rank[r];
+      s_keys[pos] = key[r];
+      if (HAS_VALS) s_vals[pos] = val[r];
     }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < tile_items; j += kSortThreads) {
+    const u64 k = s_keys[j];
+    const unsigned digit = (unsigned)(k >> shift) & 0xFFu;
+    const i64 dst = s_bin_base[digit] + (i64)(j - s_tile_start[digit]);
+    keys_out[dst] = k;
+    if (HAS_VALS) vals_out[dst] = s_vals[j];
   }
 }
 
@@ -141,7 +177,8 @@ int radix_sort_pairs(gsb_ctx* ctx, cudaStream_t stream, u64* keys, i64* vals, i6
     GSB_LAUNCH_OK();
     int st = exclusive_scan_i64(ctx, stream, hist, (i64)kRadix * tiles);
     if (st != GSB_OK) return st;
-    k_radix_scatter<<<tiles, kSortThreads, 0, stream>>>(kin, vin, kout, vout, n, shift, hist, tiles);
+    if (vals) k_radix_scatter<true><<<tiles, kSortThreads, 0, stream>>>(kin, vin, kout, vout, n, shift, hist, tiles);
+    else k_radix_scatter<false><<<tiles, kSortThreads, 0, stream>>>(kin, nullptr, kout, nullptr, n, shift, hist, tiles);
     GSB_LAUNCH_OK();
     ctx_count_launches(ctx, 2);
     u64* tk = kin; kin = kout; kout = tk;
@@ -149,7 +186,7 @@ int radix_sort_pairs(gsb_ctx* ctx, cudaStream_t stream, u64* keys, i64* vals, i6
   }
   if (kin != keys) {
     GSB_CUDA_OK(cudaMemcpyAsync(keys, kin, sizeof(u64) * (size_t)n, cudaMemcpyDeviceToDevice, stream));
-    GSB_CUDA_OK(cudaMemcpyAsync(vals, vin, sizeof(i64) * (size_t)n, cudaMemcpyDeviceToDevice, stream));
+    if (vals) GSB_CUDA_OK(cudaMemcpyAsync(vals, vin, sizeof(i64) * (size_t)n, cudaMemcpyDeviceToDevice, stream));
   }
   return GSB_OK;
 }

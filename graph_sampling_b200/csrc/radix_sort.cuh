@@ -22,7 +22,7 @@ constexpr int kRadix = 256;
 size_t radix_sort_scratch_bytes(i64 n);
 
 // Sorts by bits [begin_bit, end_bit) of the key, ascending, stable.  keys/vals are overwritten with
-// the sorted result.  `scratch` must hold radix_sort_scratch_bytes(n).
+// the sorted result; vals == nullptr sorts the keys alone.  `scratch` must hold radix_sort_scratch_bytes(n).
 int radix_sort_pairs(gsb_ctx* ctx, cudaStream_t stream, u64* keys, i64* vals, i64 n, int begin_bit, int end_bit,
                      void* scratch);
 

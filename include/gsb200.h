@@ -358,7 +358,7 @@ GSB_API int gsb_batch_col_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* 
  * src/cuda/batch_unique.cu:131-213) and BatchUnique2CUDA / BatchUniqueByKey2CUDA (sorted != 0: ascending ids
  * per batch, :215-278).  out_unique (n entries) holds the per-batch distinct ids back to back,
  * out_unique_ptr[G + 1] their offsets, out_unique_key (n entries, may be NULL) the batch number of every
- * distinct id.  sorted != 0 requires unique_total_host.  Ids below 2^32 - 1, n below 2^31. */
+ * distinct id.  Ids below 2^32 - 1, n below 2^31. */
 GSB_API int gsb_batch_unique(gsb_ctx* ctx, void* stream, const int64_t* data, const int64_t* data_ptr, int64_t n,
                              int64_t G, int sorted, int64_t* out_unique, int64_t* out_unique_ptr,
                              int64_t* out_unique_key, int64_t* unique_total_host);
