@@ -657,7 +657,7 @@ def run_kernels(args):
     sptr = torch.arange(G + 1, device=device) * (S // G)
     timed("BatchUnique, 256 batches", lambda: ops.batch_unique(sub_row, bptr), lambda o: 8 * D + 16 * o[0].numel())
     timed("BatchUnique2 (sorted), 256 batches", lambda: ops.batch_unique(sub_row, bptr, sort=True),
-          lambda o: 8 * D + 16 * o[0].numel() + 32 * 5 * o[0].numel(), note="+ 5 radix passes over the distinct ids")
+          lambda o: 8 * D + 16 * o[0].numel() + 5 * 24 * D, note="5 keys-only radix passes of 24 B per item")
     bcol = seeds[sub_col]
     timed("BatchCOORelabel, 256 batches", lambda: ops.batch_coo_relabel(seeds, sptr, bcol, sub_row, bptr),
           lambda o: 8 * (S + D) + 8 * o[0].numel() + 8 * D + 16 * D)
@@ -669,7 +669,7 @@ def run_kernels(args):
     timed("GetBatchOffsets + decode", lambda: ops.get_batch_offsets(enc, G, n), 16 * D)
     timed("BatchConcat of 2 arrays", lambda: ops.batch_concat([seeds, sub_row], [sptr, bptr]), 24 * (S + D))
     timed("segmented list sampling, 256 x 4000 of 13 M", lambda: ops.batch_list_sampling_probs(probs, 4000, False, bptr),
-          12 * D + 8 * 4000 * G, note="5 radix passes of 32 B per item")
+          12 * D + 8 * 4000 * G, note="two histogram passes, then only the candidates are sorted")
     print(json.dumps({"metric": "per_operator_roofline", "unit": "GB/s", "peak": peak, "graph": {"nodes": n, "edges": int(indices.numel())},
                       "operators": results}))
 
