@@ -40,7 +40,7 @@ UNIT = "edges/s"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) divided by algorithmic bytes, from one ncu capture
 # per kernel on a 64-minibatch call of this workload (profiles/k_*_sage3hop_group64.md).  Traffic grows in
 # proportion to the units a launch processes, so a full launch's traffic is this ratio times its algorithmic bytes.
-TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.1, "table_insert": 3.0, "first_compact": 2.2, "relabel": 1.8}
+TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.1, "table_insert": 4.0, "first_compact": 2.9, "relabel": 2.3}
 
 
 def parse():
