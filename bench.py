@@ -263,7 +263,7 @@ def reduce_stats(torch, dist, world, seconds, edges, device):
     return reduce_run_stats(seconds, edges, device=device)
 
 
-def cpu_baseline(indptr, indices, batches, budget_s=15.0):
+def cpu_baseline(indptr, indices, batches, limit_s=15.0):
     """Times the CPU restatement of the same batch loop on all host cores, on a bounded sample."""
     from oracle import build as obuild
     obuild.build()
@@ -271,7 +271,7 @@ def cpu_baseline(indptr, indices, batches, budget_s=15.0):
     ip, ix = indptr.cpu().numpy(), indices.cpu().numpy()
     o.sage_batch(ip, ix, batches[0].numpy(), FANOUTS, seed=1)  # warm
     t0, edges, n = time.time(), 0, 0
-    while n < len(batches) and (time.time() - t0) < budget_s:
+    while n < len(batches) and (time.time() - t0) < limit_s:
         edges += o.sage_batch(ip, ix, batches[n].numpy(), FANOUTS, seed=n)
         n += 1
     dt = time.time() - t0
@@ -490,7 +490,7 @@ def run_reference(args):
                                                 f"{args.steps} batches"},
                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
     else:
-        cpu = cpu_baseline(indptr, indices, batches, budget_s=60.0)
+        cpu = cpu_baseline(indptr, indices, batches, limit_s=60.0)
         base.update({"value": cpu["value"], "ms_per_step": None, "cpu_baseline": cpu,
                      "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
     print(json.dumps(base))
