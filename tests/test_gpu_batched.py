@@ -115,6 +115,25 @@ def test_sage_sample_batches_without_host_waits(ops, cfg1_graph, fanouts):
         assert torch.equal(g["frontier"][:U], w["frontier"])
 
 
+def test_output_arena_reuses_buffers_and_keeps_results_equal(ops, cfg1_graph):
+    indptr, indices = cfg1_graph
+    n = len(indptr) - 1
+    rng = np.random.default_rng(8)
+    arena = ops.OutputArena()
+    sizes = []
+    for trial in range(4):
+        G, S0 = 6, 500 + 40 * trial          # later calls are a little larger: they fit the head-room
+        seeds0 = dev(np.concatenate([rng.choice(n, S0, replace=False) for _ in range(G)]).astype(np.int64))
+        ptr0 = dev((np.arange(G + 1) * S0).astype(np.int64))
+        want = ops.sage_sample_batches(dev(indptr), dev(indices), seeds0, ptr0, [10, 5], seed=trial)
+        got = ops.sage_sample_batches(dev(indptr), dev(indices), seeds0, ptr0, [10, 5], seed=trial, arena=arena)
+        for w, g in zip(want, got):
+            for key in ("sub_indptr", "indices", "relabeled", "select_index", "indices_ptr", "frontier", "frontier_ptr"):
+                assert torch.equal(w[key], g[key]), key
+        sizes.append(arena.bytes())
+    assert sizes[0] > 0 and sizes[-1] == sizes[1]   # grew at most once after the first call
+
+
 def test_split_helpers(ops):
     """SplitByOffset / IndptrSplitByOffset / IndptrSplitBySize (reference src/tensor_ops.cc:33-45,
     src/cuda/batch_split.cu): per-batch pieces of a super-batch result."""
