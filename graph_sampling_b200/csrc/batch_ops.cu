@@ -379,7 +379,7 @@ int gsb_batch_list_sample(gsb_ctx* ctx, void* stream_, const float* probs, int64
                           int64_t* n_out_host) {
   GSB_REQUIRE(ctx && range && out_range && N >= 0 && G >= 1 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(N < 0xFFFFFFFFll && G < (1ll << 23), GSB_ERR_UNSUPPORTED);
-  GSB_REQUIRE(N == 0 || (probs && out_idx), GSB_ERR_INVALID_ARGUMENT);
+  GSB_REQUIRE(N == 0 || (probs && (out_idx || k == 0)), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   const int wide = kNumSMs * 8;
   const int grid_n = min(grid_for(N, kOpThreads), wide);

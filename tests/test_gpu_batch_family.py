@@ -260,3 +260,50 @@ def test_fixture_replay_batch_slicing(face, fx):
         assert same(coo[0], fx[tag + "coo_row"]) and same(coo[1], fx[tag + "coo_col"])
         assert same(offs, fx[tag + "offsets"]) and same(sub._CAPI_GetCols(), fx[tag + "cols"])
         assert [sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols(), sub._CAPI_GetNumEdges()] == fx[tag + "num"].tolist()
+
+
+# ---- edge cases ---------------------------------------------------------------------------------------
+def test_batch_list_sampling_edges(ops, oracle):
+    # nothing to pick from, nothing to pick, every segment smaller than k, all weights zero
+    ptr = dev(np.array([0, 0, 0], dtype=np.int64))
+    idx, rng_ = ops.batch_list_sampling_probs(torch.empty(0, device="cuda"), 5, False, ptr)
+    assert idx.numel() == 0 and host(rng_).tolist() == [0, 0, 0]
+    probs = np.random.default_rng(0).random(50).astype(np.float32)
+    ptr = np.array([0, 10, 10, 37, 50], dtype=np.int64)
+    idx, rng_ = ops.batch_list_sampling_probs(dev(probs), 0, False, dev(ptr))
+    assert idx.numel() == 0 and host(rng_).tolist() == [0, 0, 0, 0, 0]
+    for k in (1, 13, 27, 1000):
+        want = oracle.batch_list_sample(probs, ptr, k, seed=9)
+        got = ops.batch_list_sampling_probs(dev(probs), k, False, dev(ptr), seed=9)
+        assert np.array_equal(want[0], host(got[0])) and np.array_equal(want[1], host(got[1]))
+    zeros = np.zeros(50, dtype=np.float32)
+    want = oracle.batch_list_sample(zeros, ptr, 4, seed=9)
+    got = ops.batch_list_sampling_probs(dev(zeros), 4, False, dev(ptr), seed=9)
+    assert np.array_equal(want[0], host(got[0]))      # ties at -inf: smallest positions first
+    assert host(got[0]).tolist() == [0, 1, 2, 3, 10, 11, 12, 13, 37, 38, 39, 40]
+    with pytest.raises(NotImplementedError):
+        ops.batch_list_sampling_probs(dev(probs), 3, True, dev(ptr))
+
+
+def test_batch_list_sampling_many_equal_keys(ops, oracle):
+    """Equal weights and a seed-independent tie structure: thousands of items share the top 16 bits of the ranking
+    word, so the candidate threshold lands inside a crowded bin."""
+    rng = np.random.default_rng(5)
+    ptr = np.array([0, 30000, 30001, 90000], dtype=np.int64)
+    probs = np.full(90000, 0.25, dtype=np.float32)
+    probs[rng.integers(0, 90000, 5000)] = 3.0
+    for k in (1, 100, 5000, 29999, 30000, 70000):
+        want = oracle.batch_list_sample(probs, ptr, k, seed=k)
+        got = ops.batch_list_sampling_probs(dev(probs), k, False, dev(ptr), seed=k)
+        assert np.array_equal(want[1], host(got[1])) and np.array_equal(want[0], host(got[0])), k
+
+
+def test_batch_unique_sorted_with_invalid_id_is_reported(ops):
+    from graph_sampling_b200.cabi import GsbError
+    data = dev(np.array([3, 1 << 35, 2], dtype=np.int64))
+    ptr = dev(np.array([0, 3], dtype=np.int64))
+    with pytest.raises(GsbError) as e:
+        ops.batch_unique(data, ptr, sort=True)
+    assert e.value.status == -8
+    u, p, k = ops.batch_unique(dev(np.array([3, 1, 3], dtype=np.int64)), ptr, sort=True)
+    assert host(u).tolist() == [1, 3] and host(p).tolist() == [0, 2] and host(k).tolist() == [0, 0]

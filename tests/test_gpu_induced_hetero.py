@@ -186,3 +186,35 @@ def test_fixture_replay_metapath(face, fx):
     assert same(trace, fx["metapath_trace"])
     assert host(trace).reshape(-1).tolist() == [2, 1, 2, 1, 1, 0, 0, -1]
     assert hg._CAPI_GetHomoGraph("view")._CAPI_GetNumEdges() == 3
+
+
+def test_col_row_slicing_repeated_ids_and_empty_inputs(ops, oracle, small_graph):
+    indptr, indices = small_graph
+    n = len(indptr) - 1
+    cols = np.array([5, 5, 7, 5], dtype=np.int64)                    # a column may be asked for twice
+    rows = np.array([indices[indptr[5]], 3, indices[indptr[5]], 9], dtype=np.int64)   # a row id listed twice: last wins
+    want = oracle.col_row_slice(indptr, indices, cols, rows)
+    got = ops.csc_col_row_slicing(dev(indptr), dev(indices), dev(cols), dev(rows))
+    for a, b in zip(want, got):
+        assert np.array_equal(a, host(b))
+    empty = np.empty(0, dtype=np.int64)
+    got = ops.csc_col_row_slicing(dev(indptr), dev(indices), dev(empty), dev(rows))
+    assert host(got[0]).tolist() == [0] and got[1].numel() == 0
+    got = ops.csc_col_row_slicing(dev(indptr), dev(indices), dev(cols), dev(empty))
+    assert host(got[0]).tolist() == [0] * 5 and got[1].numel() == 0
+    isolated = np.flatnonzero(np.diff(indptr) == 0)[:3].astype(np.int64)   # columns without edges
+    if len(isolated):
+        got = ops.csc_col_row_slicing(dev(indptr), dev(indices), dev(isolated), dev(np.arange(n, dtype=np.int64)))
+        assert host(got[0]).tolist() == [0] * (len(isolated) + 1)
+
+
+def test_metapath_walk_edges(ops):
+    g = [(dev(np.array([0, 1, 2])), dev(np.array([1, 0])))]
+    t = ops.fused_metapath_random_walk(dev(np.array([0, 1, -1])), [], g)          # no steps: the seeds themselves
+    assert host(t).tolist() == [[0], [1], [-1]]
+    t = ops.fused_metapath_random_walk(dev(np.array([0, -1])), [0, 0, 0], g, layout=1)
+    assert host(t).tolist() == [[0, 1, 0, 1], [-1, -1, -1, -1]]
+    with pytest.raises(Exception):
+        ops.fused_metapath_random_walk(dev(np.array([0])), [1], g)                 # relation index out of range
+    with pytest.raises(Exception):
+        ops.fused_metapath_random_walk(dev(np.array([0])), [0] * 300, g)           # longer than the supported path
