@@ -86,6 +86,42 @@ __device__ __forceinline__ void topk_offer(float ck, i64 ci, bool valid, int k, 
   }
 }
 
+// Warp-collective: the first 32 candidates of a column.  The list is empty, so every one of them would be inserted
+// one at a time; a bitonic sort of the 32 (key, position) pairs across the lanes (15 exchange steps) builds the
+// same list directly.  (key, position) is a total order — positions are distinct — so the result does not depend
+// on how it was reached.
+__device__ __forceinline__ void topk_init(float ck, i64 ci, bool valid, int k, float& my_key, i64& my_idx,
+                                          float& thr_key, i64& thr_idx) {
+  const float neg_inf = __uint_as_float(0xFF800000u);
+  const i64 no_idx = 0x7fffffffffffffffll;
+  my_key = valid ? ck : neg_inf;
+  my_idx = valid ? ci : no_idx;
+  const int lane = lane_id();
+#pragma unroll
+  for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+    for (int j = size >> 1; j > 0; j >>= 1) {
+      const float ok = __shfl_xor_sync(0xffffffffu, my_key, j);
+      const i64 oi = __shfl_xor_sync(0xffffffffu, my_idx, j);
+      const bool descending = (lane & size) == 0;   // direction of this lane's block (the last pass: all descending)
+      const bool lower = (lane & j) == 0;
+      const bool mine_first = ranks_before(my_key, my_idx, ok, oi);
+      // in a descending block the lower lane keeps the entry that ranks first
+      const bool keep = (mine_first == (lower == descending)) || (my_key == ok && my_idx == oi);
+      if (!keep) {
+        my_key = ok;
+        my_idx = oi;
+      }
+    }
+  }
+  if (lane >= k) {
+    my_key = neg_inf;
+    my_idx = no_idx;
+  }
+  thr_key = __shfl_sync(0xffffffffu, my_key, k - 1);
+  thr_idx = __shfl_sync(0xffffffffu, my_idx, k - 1);
+}
+
 // Top-k of the edges [e_begin, e_end) of one column, scanned by one warp.
 __device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, i64 b, i64 e_begin, i64 e_end, int k,
                                           unsigned kmask, float& my_key, i64& my_idx) {
@@ -97,6 +133,7 @@ __device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, 
   // 128 edges per iteration: a lane evaluates ONE Philox block and uses its four words for four consecutive
   // edges (edge e draws word e & 3 of block e >> 2), instead of four lanes computing the same block.
   const i64 first_block = e_begin >> 2;
+  bool empty_list = true;
   for (i64 blk0 = first_block; (blk0 << 2) < e_end; blk0 += 32) {
     const i64 blk = blk0 + lane_id();
     const i64 e4 = blk << 2;
@@ -108,7 +145,12 @@ __device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, 
       const bool valid = e >= e_begin && e < e_end;
       float ck = neg_inf;
       if (valid) ck = ares_key(r.v[q], __ldg(p.probs + b + e));
-      topk_offer(ck, e, valid, k, kmask, my_key, my_idx, thr_key, thr_idx);
+      if (empty_list) {
+        topk_init(ck, e, valid, k, my_key, my_idx, thr_key, thr_idx);
+        empty_list = false;
+      } else {
+        topk_offer(ck, e, valid, k, kmask, my_key, my_idx, thr_key, thr_idx);
+      }
     }
   }
 }
@@ -117,16 +159,18 @@ __device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, 
 // through shared memory): one hub column would otherwise occupy a single warp for hundreds of iterations.
 constexpr i64 kLongColumn = 2048;
 
-__global__ void __launch_bounds__(kWThreads) k_sample_weighted(WeightedParams p) {
+__global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams p) {
   __shared__ i64 s_in[kWTileCols];
   __shared__ i64 s_deg[kWTileCols];
   __shared__ i64 s_off[kWTileCols];
   __shared__ i64 s_scan[33];
   __shared__ i64 s_base;
+  __shared__ int s_next;  // next column of the tile that no warp has taken yet
   const int tile = blockIdx.x, tid = threadIdx.x;
   const i64 S = p.S, k = p.k;
   const i64 base = (i64)tile * kWTileCols;
   if (base >= S && !(S == 0 && tile == 0)) return;
+  if (tid == 0) s_next = 0;
   const int ncol = (int)max((i64)0, min((i64)kWTileCols, S - base));
 
   i64 f = 0;
@@ -162,7 +206,12 @@ __global__ void __launch_bounds__(kWThreads) k_sample_weighted(WeightedParams p)
   const unsigned kmask = k >= 32 ? 0xffffffffu : ((1u << (int)k) - 1u);
   const float neg_inf = __uint_as_float(0xFF800000u);
 
-  for (int c = warp; c < ncol; c += kWarps) {
+  // warps take columns as they become free: degrees inside a tile differ by orders of magnitude
+  for (;;) {
+    int c = 0;
+    if (lane == 0) c = atomicAdd(&s_next, 1);
+    c = __shfl_sync(0xffffffffu, c, 0);
+    if (c >= ncol) break;
     const i64 d = s_deg[c], b = s_in[c], o = tile_base + s_off[c], col_pos = base + c;
     if (p.replace) {
       if (d == 0) continue;
