@@ -96,20 +96,48 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
   __syncthreads();
   const i64 tile_base = s_off[0];
   const i64 tile_sum = s_off[ncol] - tile_base;
-  for (i64 q = tid; q < tile_sum; q += kThreads) {
-    const i64 pos = tile_base + q;
-    // largest c with s_off[c] <= pos
-    int lo = 0, hi = ncol;  // invariant: s_off[lo] <= pos < s_off[hi]
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (s_off[mid] <= pos) lo = mid;
-      else hi = mid;
+  // A warp copies 256 consecutive output positions at a time (lanes on consecutive positions): the column of the
+  // first one is found by binary search in the shared tile offsets, after that the column index only walks
+  // forward — a hub column is spread over the whole CTA, and no position pays for its own search.
+  constexpr int kChunk = 32 * 8;
+  const int lane = tid & 31, warp = tid >> 5;
+  for (i64 chunk = (i64)warp * kChunk; chunk < tile_sum; chunk += (i64)(kThreads / 32) * kChunk) {
+    int c = 0;
+    {
+      const i64 first = tile_base + chunk;
+      int lo = 0, hi = ncol;  // invariant: s_off[lo] <= first < s_off[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_off[mid] <= first) lo = mid;
+        else hi = mid;
+      }
+      c = lo;
     }
-    const i64 in_pos = s_in[lo] + (pos - s_off[lo]);
-    p.out_indices[pos] = __ldg(p.indices + in_pos) + (ENCODE ? s_enc[lo] : 0);
-    p.out_select[pos] = in_pos;
-    if (p.out_coo_col) p.out_coo_col[pos] = base + lo;
-    if (p.out_data) p.out_data[pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+    // all eight loads first, then the stores: the compiler may not move a load above a store it cannot prove
+    // independent, and eight dependent DRAM round trips per chunk would set the pace
+    i64 in_pos[8], val[8];
+    int col_of[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const i64 q = chunk + r * 32 + lane;
+      in_pos[r] = -1;
+      if (q < tile_sum) {
+        const i64 pos = tile_base + q;
+        while (s_off[c + 1] <= pos) ++c;  // empty columns are stepped over; pos < s_off[ncol] bounds the walk
+        col_of[r] = c;
+        in_pos[r] = s_in[c] + (pos - s_off[c]);
+        val[r] = __ldg(p.indices + in_pos[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (in_pos[r] < 0) continue;
+      const i64 pos = tile_base + chunk + r * 32 + lane;
+      p.out_indices[pos] = val[r] + (ENCODE ? s_enc[col_of[r]] : 0);
+      p.out_select[pos] = in_pos[r];
+      if (p.out_coo_col) p.out_coo_col[pos] = base + col_of[r];
+      if (p.out_data) p.out_data[pos] = p.data[p.e_ids ? p.e_ids[in_pos[r]] : in_pos[r]];
+    }
   }
 }
 
