@@ -8,9 +8,9 @@ namespace gsb {
 constexpr int kFmtThreads = 256;
 constexpr int kFmtTileCols = 256;
 
-// One CTA per tile of columns; threads walk the tile's contiguous edge range and find the column of
-// each edge by binary search in the shared copy of the tile's offsets (the reference searches the
-// whole indptr in global memory per edge: src/cuda/format_transform.cu:23-33).
+// One CTA per tile of columns; warps walk the tile's contiguous edge range 256 edges at a time and find the
+// column of the first edge by binary search in the shared copy of the tile's offsets, then step forward (the
+// reference searches the whole indptr in global memory per edge: src/cuda/format_transform.cu:23-33).
 __global__ void __launch_bounds__(kFmtThreads) k_csc2coo(const i64* __restrict__ indptr, i64 num_cols,
                                                          i64* __restrict__ out_col) {
   __shared__ i64 s_off[kFmtTileCols + 1];
@@ -20,14 +20,24 @@ __global__ void __launch_bounds__(kFmtThreads) k_csc2coo(const i64* __restrict__
   for (int q = threadIdx.x; q <= ncol; q += kFmtThreads) s_off[q] = indptr[base + q];
   __syncthreads();
   const i64 lo_e = s_off[0], hi_e = s_off[ncol];
-  for (i64 e = lo_e + threadIdx.x; e < hi_e; e += kFmtThreads) {
-    int lo = 0, hi = ncol;
+  // a warp writes 256 consecutive edges at a time: one binary search for the first, then the column only walks on
+  constexpr int kChunk = 32 * 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (i64 chunk = lo_e + (i64)warp * kChunk; chunk < hi_e; chunk += (i64)(kFmtThreads / 32) * kChunk) {
+    int lo = 0, hi = ncol;  // invariant: s_off[lo] <= chunk < s_off[hi]
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (s_off[mid] <= e) lo = mid;
+      if (s_off[mid] <= chunk) lo = mid;
       else hi = mid;
     }
-    out_col[e] = base + lo;
+    int c = lo;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const i64 e = chunk + r * 32 + lane;
+      if (e >= hi_e) break;
+      while (s_off[c + 1] <= e) ++c;
+      out_col[e] = base + c;
+    }
   }
 }
 

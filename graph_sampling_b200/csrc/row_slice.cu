@@ -177,6 +177,23 @@ __device__ __forceinline__ i64 column_at(const i64* __restrict__ sub_indptr, i64
   return lo;
 }
 
+// The same search done by a whole warp: 32 pivots per step, so a search over a few hundred thousand columns takes
+// four dependent loads instead of eighteen.  Needs sub_indptr[0] <= pos < sub_indptr[S].
+__device__ __forceinline__ i64 warp_column_at(const i64* __restrict__ sub_indptr, i64 S, i64 pos) {
+  const int lane = threadIdx.x & 31;
+  i64 lo = 0, hi = S;
+  while (hi - lo > 1) {
+    const i64 step = (hi - lo + 31) / 32;
+    const i64 idx = lo + (i64)(lane + 1) * step;
+    const bool le = idx < hi && __ldg(sub_indptr + idx) <= pos;   // true for a prefix of the lanes
+    const int n = __popc(__ballot_sync(0xffffffffu, le));
+    const i64 new_hi = min(hi, lo + (i64)(n + 1) * step);
+    lo += (i64)n * step;
+    hi = new_hi;
+  }
+  return lo;
+}
+
 __global__ void __launch_bounds__(kRowThreads) k_col_row_filter(ColRowParams p) {
   __shared__ i64 s_warp_total[kRowThreads / 32];
   __shared__ i64 s_base, s_clo, s_chi;
@@ -184,34 +201,56 @@ __global__ void __launch_bounds__(kRowThreads) k_col_row_filter(ColRowParams p) 
   const int tile = blockIdx.x;
   const i64 tile_base = (i64)tile * kCrTile;
   const i64 tile_end = min(p.D, tile_base + kCrTile);
-  if (threadIdx.x == 0) {
-    s_clo = column_at(p.sub_indptr, 0, p.S, tile_base);
-    s_chi = column_at(p.sub_indptr, 0, p.S, tile_end - 1);
+  // the tile's column range: two warp-wide searches side by side (one thread doing both binary searches over the
+  // global offsets was 36 dependent loads with the rest of the CTA waiting at the barrier — most of the kernel's time)
+  if (warp < 2) {
+    const i64 c = warp_column_at(p.sub_indptr, p.S, warp == 0 ? tile_base : tile_end - 1);
+    if (lane == 0) (warp == 0 ? s_clo : s_chi) = c;
   }
   __syncthreads();
   const i64 clo = s_clo, chi = s_chi;
   const i64 base = tile_base + (i64)warp * kCrWarp;
   bool keep[kCrLane];
   i64 col_of[kCrLane], edge[kCrLane], value[kCrLane];
+  // the warp's 128 positions are consecutive: search for the first one, then the column only walks forward.
+  // Phases (column -> edge position -> row id -> table probe) run for all four positions of a lane before the next
+  // phase starts, so that four independent loads are in flight per lane in every phase.
+  i64 c = base < tile_end ? column_at(p.sub_indptr, clo, chi, base) : clo;
+  i64 start_of[kCrLane], row_of[kCrLane];
 #pragma unroll
   for (int q = 0; q < kCrLane; ++q) {
     keep[q] = false;
     col_of[q] = -1;
     const i64 pos = base + q * 32 + lane;
     if (pos < tile_end) {
-      const i64 c = column_at(p.sub_indptr, clo, chi, pos);
+      while (c < chi && __ldg(p.sub_indptr + c + 1) <= pos) ++c;
       col_of[q] = c;
-      const i64 col = p.seeds ? __ldg(p.seeds + c) : c;
-      const i64 e = __ldg(p.indptr + col) + (pos - __ldg(p.sub_indptr + c));
-      edge[q] = e;
-      const i64 r = __ldg(p.indices + e);
-      if (r >= 0) {
-        const i64 shift = p.col_ptr ? batch_of(p.col_ptr, p.G, c) * p.encoding_size : 0;
-        const Slot* s = table_find(p.table, r + shift);
-        if (s) {
-          keep[q] = true;
-          value[q] = p.renumber ? (i64)(kMaxFlip - s->val) : r;
-        }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < kCrLane; ++q) {
+    if (col_of[q] >= 0) {
+      const i64 col = p.seeds ? __ldg(p.seeds + col_of[q]) : col_of[q];
+      start_of[q] = __ldg(p.indptr + col);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < kCrLane; ++q) {
+    row_of[q] = -1;
+    if (col_of[q] >= 0) {
+      const i64 pos = base + q * 32 + lane;
+      edge[q] = start_of[q] + (pos - __ldg(p.sub_indptr + col_of[q]));
+      row_of[q] = __ldg(p.indices + edge[q]);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < kCrLane; ++q) {
+    if (row_of[q] >= 0) {
+      const i64 shift = p.col_ptr ? batch_of(p.col_ptr, p.G, col_of[q]) * p.encoding_size : 0;
+      const Slot* s = table_find(p.table, row_of[q] + shift);
+      if (s) {
+        keep[q] = true;
+        value[q] = p.renumber ? (i64)(kMaxFlip - s->val) : row_of[q];
       }
     }
   }
