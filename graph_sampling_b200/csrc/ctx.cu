@@ -248,6 +248,18 @@ int gsb_read_counts(gsb_ctx* ctx, void* stream, int64_t* nnz_host, int64_t* uniq
 int gsb_profile_enable(gsb_ctx* ctx, int on) {
   if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
   if (!on && ctx->profiling) gsb::prof_collect(ctx);
+  if (on) {
+    // Events are created here, not at the first launches that need them: creating an event is a driver call that
+    // several processes on one machine contend for, and it would otherwise land inside the caller's timed region.
+    constexpr size_t kPool = 4096;
+    while (ctx->ev_begin->size() < kPool) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) break;
+      ctx->ev_begin->push_back(a);
+      ctx->ev_end->push_back(b);
+      ctx->ev_kid->push_back(0);
+    }
+  }
   ctx->profiling = on != 0;
   return GSB_OK;
 }
