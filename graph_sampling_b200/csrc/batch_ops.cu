@@ -434,7 +434,9 @@ int gsb_batch_list_sample(gsb_ctx* ctx, void* stream_, const float* probs, int64
     if (st != GSB_OK) return st;
     if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
     const i64 M = c[CNT_AUX0];
-    st = radix_sort_pairs(ctx, stream, cand_keys, cand_vals, M, 0, 32 + bits_for(G), sort_ws);
+    // candidate positions increase with the input order, so (key, position) order is the stable order
+    if (M <= kSmallSortPairs) st = small_sort_pairs(ctx, stream, cand_keys, cand_vals, M);
+    else st = radix_sort_pairs(ctx, stream, cand_keys, cand_vals, M, 0, 32 + bits_for(G), sort_ws);
     if (st != GSB_OK) return st;
     if (M > 0) {
       k_blist_emit<<<min(grid_for(M, kOpThreads), wide), kOpThreads, 0, stream>>>(cand_vals, cand_ptr, G, out_range,

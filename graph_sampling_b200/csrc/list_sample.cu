@@ -4,7 +4,7 @@
 // A-Res key log2(u)/w for the weighted case (w <= 0 can never beat a positive weight) — and the k
 // best keys win; ties go to the smaller position; the output is in descending key order, which is
 // what the reference's descending stable sort yields (src/cuda/list_sampling_probs.cu:56-88).
-// Instead of sorting all N keys to take k of them, the k-th best key is found by an 8-pass
+// Instead of sorting all N keys to take k of them, the k-th best key is found by an 8-pass (one launch each)
 // most-significant-digit radix SELECT over the 64-bit composite (key << 32 | ~position), the k
 // winners are compacted and only they are sorted.  With replacement: k independent draws, uniform
 // or by inverse CDF (src/cuda/list_sampling.cu:35-52, list_sampling_probs.cu:28-55).
@@ -24,6 +24,8 @@ struct SelectState {
   u64 prefix;     // bits decided so far (high digits)
   i64 remaining;  // how many winners must still come from the undecided bin
   i64 hist[256];
+  unsigned done;      // CTAs that have added their counts in the current pass
+  unsigned resolved;  // the selected bin is needed entirely: the threshold is final, later passes have nothing to do
 };
 
 __device__ __forceinline__ uint32_t orderable_f32(float f) {
@@ -45,30 +47,43 @@ __global__ void k_select_init(SelectState* st, i64 k) {
   if (threadIdx.x == 0) {
     st->prefix = 0;
     st->remaining = k;
+    st->done = 0;
+    st->resolved = 0;
   }
   st->hist[threadIdx.x] = 0;
 }
 
-__global__ void __launch_bounds__(kListThreads) k_select_histogram(const u64* __restrict__ composite, i64 N, int shift,
-                                                                   SelectState* st) {
+// One pass of the radix select: every CTA counts, per value of the current digit, the items that still match the
+// decided prefix; the CTA that adds its counts last (a ticket from `done`) walks the 256 bins from the top — the
+// bin in which the running count reaches `remaining` holds the k-th best item — and clears the state for the next
+// pass.  (Counting and picking were two launches per pass; the operator is launch bound.)
+__global__ void __launch_bounds__(kListThreads) k_select_pass(const u64* __restrict__ composite, i64 N, int shift,
+                                                              SelectState* st) {
   __shared__ unsigned s_hist[256];
+  __shared__ bool s_last;
+  if (st->resolved) return;  // uniform over the grid: written by the previous launch
   s_hist[threadIdx.x] = 0;
   __syncthreads();
   const u64 prefix = st->prefix;
   const u64 high_mask = shift >= 56 ? 0ull : (~0ull << (shift + 8));
   for (i64 i = (i64)blockIdx.x * kListThreads + threadIdx.x; i < N; i += (i64)gridDim.x * kListThreads) {
     const u64 c = composite[i];
-    if ((c & high_mask) == prefix) atomicAdd(&s_hist[(unsigned)(c >> shift) & 0xFFu], 1u);
+    // lanes that hit the same bin add once: with many equal keys (all zero-weight items share one) plain
+    // shared-memory atomics on one address serialise the whole CTA
+    const unsigned digit = (c & high_mask) == prefix ? ((unsigned)(c >> shift) & 0xFFu) : 0x100u;
+    const unsigned peers = __match_any_sync(__activemask(), digit);
+    if (digit < 0x100u && (int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&s_hist[digit], (unsigned)__popc(peers));
   }
   __syncthreads();
   if (s_hist[threadIdx.x]) atomicAdd((u64*)&st->hist[threadIdx.x], (u64)s_hist[threadIdx.x]);
-}
-
-// Walks the bins from the top: the bin in which the running count reaches `remaining` holds the
-// k-th best item.  Single warp; also clears the histogram for the next pass.
-__global__ void k_select_pick(SelectState* st, int shift) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&st->done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
   __shared__ i64 s_h[256];
-  s_h[threadIdx.x] = st->hist[threadIdx.x];
+  s_h[threadIdx.x] = ((volatile i64*)st->hist)[threadIdx.x];
   st->hist[threadIdx.x] = 0;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -83,6 +98,11 @@ __global__ void k_select_pick(SelectState* st, int shift) {
     }
     st->prefix |= (u64)bin << shift;
     st->remaining = need;
+    st->done = 0;
+    // every item of the selected bin is needed: all composites >= prefix (lower digits zero) are exactly the k
+    // winners, so the remaining digits need not be examined (the usual case once the key digits are through:
+    // the last passes only split ties)
+    if (s_h[bin] == need) st->resolved = 1;
   }
 }
 
@@ -308,28 +328,36 @@ extern "C" int gsb_list_sample(gsb_ctx* ctx, void* stream_, const int64_t* data,
   void* sort_ws = (char*)ws + comp_bytes + win_bytes;
   SelectState* state = (SelectState*)((char*)sort_ws + sort_bytes);
   const int grid_n = min(grid_for(N, kListThreads), wide);
-  k_list_keys<<<grid_n, kListThreads, 0, stream>>>(probs, N, (u64)seed, composite);
+  {
+    ScopedKernelTimer timer(ctx, KID_LIST_SAMPLE, stream);
+    k_list_keys<<<grid_n, kListThreads, 0, stream>>>(probs, N, (u64)seed, composite);
+  }
   GSB_LAUNCH_OK();
   k_select_init<<<1, 256, 0, stream>>>(state, k);
   GSB_LAUNCH_OK();
+  // few, long-running CTAs for the select passes: every CTA ends with up to 256 global atomics on the same 256
+  // counters and one ticket, and those serialise
+  const int grid_sel = max(1, min(grid_for(N, kListThreads * 16), kNumSMs * 2));
   for (int shift = 56; shift >= 0; shift -= 8) {
-    k_select_histogram<<<grid_n, kListThreads, 0, stream>>>(composite, N, shift, state);
-    GSB_LAUNCH_OK();
-    k_select_pick<<<1, 256, 0, stream>>>(state, shift);
+    ScopedKernelTimer timer(ctx, KID_SORT, stream);
+    k_select_pass<<<grid_sel, kListThreads, 0, stream>>>(composite, N, shift, state);
     GSB_LAUNCH_OK();
   }
   const int tiles = grid_for(N, kListTile);
   TileState ts;
   st = ctx_tile_state(ctx, tiles, stream, &ts);
   if (st != GSB_OK) return st;
-  k_compact_winners<<<tiles, kListThreads, 0, stream>>>(composite, N, state, winners, k, ctx_counters(ctx), ts);
+  {
+    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
+    k_compact_winners<<<tiles, kListThreads, 0, stream>>>(composite, N, state, winners, k, ctx_counters(ctx), ts);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 19);
+  ctx_count_launches(ctx, 1);
   int inverted = 0;
   if (k <= kSmallSort) {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
     k_sort_winners_small<<<1, 1024, 0, stream>>>(winners, k);
     GSB_LAUNCH_OK();
-    ctx_count_launches(ctx, 1);
   } else {
     k_invert_keys<<<min(grid_for(k, kListThreads), wide), kListThreads, 0, stream>>>(winners, win_vals, k);
     GSB_LAUNCH_OK();

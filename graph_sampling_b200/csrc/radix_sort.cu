@@ -144,6 +144,51 @@ __global__ void __launch_bounds__(kSortThreads) k_radix_scatter(const u64* __res
   }
 }
 
+// Ascending bitonic sort by (key, val) of up to kSmallSortPairs pairs in the shared memory of one CTA.
+__global__ void __launch_bounds__(1024) k_small_sort_pairs(u64* __restrict__ keys, i64* __restrict__ vals, int n) {
+  __shared__ u64 s_key[kSmallSortPairs];
+  __shared__ i64 s_val[kSmallSortPairs];
+  int m = 1;
+  while (m < n) m <<= 1;
+  for (int i = threadIdx.x; i < m; i += 1024) {
+    s_key[i] = i < n ? keys[i] : ~0ull;  // padding sorts last
+    s_val[i] = i < n ? vals[i] : 0x7fffffffffffffffll;
+  }
+  __syncthreads();
+  for (int size = 2; size <= m; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = threadIdx.x; i < m / 2; i += 1024) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi = lo + stride;
+        const bool ascending = ((lo & size) == 0);
+        const u64 ka = s_key[lo], kb = s_key[hi];
+        const i64 va = s_val[lo], vb = s_val[hi];
+        const bool a_after_b = ka > kb || (ka == kb && va > vb);
+        if (a_after_b == ascending) {
+          s_key[lo] = kb;
+          s_key[hi] = ka;
+          s_val[lo] = vb;
+          s_val[hi] = va;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < n; i += 1024) {
+    keys[i] = s_key[i];
+    vals[i] = s_val[i];
+  }
+}
+
+int small_sort_pairs(gsb_ctx* ctx, cudaStream_t stream, u64* keys, i64* vals, i64 n) {
+  if (n <= 1) return GSB_OK;
+  if (n > kSmallSortPairs) return GSB_ERR_INVALID_ARGUMENT;
+  k_small_sort_pairs<<<1, 1024, 0, stream>>>(keys, vals, (int)n);
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  return GSB_OK;
+}
+
 size_t radix_sort_scratch_bytes(i64 n) {
   const i64 tiles = (n + kSortTile - 1) / kSortTile;
   size_t b = (size_t)n * 16 + ((size_t)kRadix * (size_t)(tiles > 0 ? tiles : 1) + 8) * 8;

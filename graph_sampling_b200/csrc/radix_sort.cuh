@@ -26,6 +26,11 @@ size_t radix_sort_scratch_bytes(i64 n);
 int radix_sort_pairs(gsb_ctx* ctx, cudaStream_t stream, u64* keys, i64* vals, i64 n, int begin_bit, int end_bit,
                      void* scratch);
 
+// Ascending sort by (key, val) of n <= kSmallSortPairs pairs by one CTA (one launch instead of three per radix
+// pass).  Equal to a stable sort by key whenever vals increase with the input position.
+constexpr int kSmallSortPairs = 2048;
+int small_sort_pairs(gsb_ctx* ctx, cudaStream_t stream, u64* keys, i64* vals, i64 n);
+
 // Generic in-place exclusive scan of n i64 values (a[n] receives the total when with_total).
 int exclusive_scan_i64(gsb_ctx* ctx, cudaStream_t stream, i64* a, i64 n);
 
