@@ -626,6 +626,8 @@ def run_kernels(args):
     timed("segment sum of squares (CSC)", lambda: ops.csc_sum(sub_indptr, None, w, o1, 2), 12 * D + 4 * S)
     o2 = torch.zeros(n, device=device)
     timed("segment sum of squares (COO, atomics)", lambda: ops.coo_sum(sub_row, None, w, o2, 2), 12 * D + 4 * n)
+    timed("segment sum of squares (COO, sorted targets)", lambda: ops.coo_sum(sub_col, None, w, o1, 2, targets_in_runs=True), 12 * D + 4 * S,
+          note="one atomic per distinct target of a warp")
     o3 = torch.empty(D, device=device)
     timed("segment normalize (CSC)", lambda: ops.csc_normalize(sub_indptr, None, w, o3), 8 * D + 8 * (S + 1))
     rows = torch.randperm(n, generator=g, device=device)[:100_000]
@@ -737,6 +739,7 @@ def run_kernels_reference(args):
     sub._CAPI_SetData(w)
     timed("segment sum of squares (CSC)", lambda: sub._CAPI_Sum(0, 2, _CSC))
     timed("segment sum of squares (COO, atomics)", lambda: sub._CAPI_Sum(1, 2, _COO))
+    timed("segment sum of squares (COO, sorted targets)", lambda: sub._CAPI_Sum(0, 2, _COO))
     timed("segment normalize (CSC)", lambda: sub._CAPI_Normalize(0, _CSC))
     rows = torch.randperm(n, generator=g, device=device)[:100_000]
     timed("row slice by membership (CSC)", lambda: sub._CAPI_Slicing(rows, 1, _CSC, _CSC + _COO, False))

@@ -710,9 +710,12 @@ class Graph : public torch::CustomClassHolder {
                               torch::dtype(torch::kFloat32).device(Device()));
     float* o = out.numel() ? out.data_ptr<float>() : nullptr;
     if (on_format == kCOO) {
-      const Tensor& target = (1 - axis) == 0 ? coo_->row : coo_->col;
+      const bool by_row = (1 - axis) == 0;
+      const Tensor& target = by_row ? coo_->row : coo_->col;
       Tensor e = coo_->e_ids.has_value() ? coo_->e_ids.value() : Tensor();
-      Check(gsb_segment_sum_coo(Ctx(), Stream(), IP(target), target.numel(), IP(e), FP(data), powk, o), "gsb_segment_sum_coo");
+      Check(gsb_segment_sum_coo(Ctx(), Stream(), IP(target), target.numel(), IP(e), FP(data), powk,
+                                (by_row ? coo_->row_sorted : coo_->col_sorted) ? 1 : 0, o),
+            "gsb_segment_sum_coo");
     } else if ((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR)) {
       const CSC& g = axis == 0 ? *csc_ : *csr_;
       Tensor e = g.e_ids.has_value() ? g.e_ids.value() : Tensor();

@@ -48,13 +48,39 @@ __global__ void __launch_bounds__(kSegThreads) k_segment_sum_csc(const i64* __re
   }
 }
 
+// FOLD = false: one float atomic per edge (scattered targets).  FOLD = true, for targets that come in runs (a
+// column-sorted COO summed per column has 32 equal targets in a row): lanes with the same target add once, in lane
+// order — one atomic per distinct target of the warp; a warp without a repeat next door skips the fold.
+template <bool FOLD>
 __global__ void __launch_bounds__(kSegThreads) k_segment_sum_coo(const i64* __restrict__ target, i64 E,
                                                                  const i64* __restrict__ e_ids,
                                                                  const float* __restrict__ data, i64 powk,
                                                                  float* __restrict__ out) {
-  for (i64 e = (i64)blockIdx.x * kSegThreads + threadIdx.x; e < E; e += (i64)gridDim.x * kSegThreads) {
-    const float x = data ? __ldg(data + (e_ids ? __ldg(e_ids + e) : e)) : 1.0f;
-    atomicAdd(out + __ldg(target + e), int_pow(x, powk));
+  if (!FOLD) {
+    for (i64 e = (i64)blockIdx.x * kSegThreads + threadIdx.x; e < E; e += (i64)gridDim.x * kSegThreads) {
+      const float x = data ? __ldg(data + (e_ids ? __ldg(e_ids + e) : e)) : 1.0f;
+      atomicAdd(out + __ldg(target + e), int_pow(x, powk));
+    }
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  for (i64 e0 = (i64)blockIdx.x * kSegThreads + threadIdx.x - lane; e0 < E; e0 += (i64)gridDim.x * kSegThreads) {
+    const i64 e = e0 + lane;
+    const bool valid = e < E;
+    const i64 t = valid ? __ldg(target + e) : -1 - lane;  // distinct dummies: lanes past the end pair with nobody
+    const float v = valid ? int_pow(data ? __ldg(data + (e_ids ? __ldg(e_ids + e) : e)) : 1.0f, powk) : 0.0f;
+    const int prev_t = __shfl_up_sync(0xffffffffu, (int)t, 1);  // low words: a false match only takes the fold
+    if (!__any_sync(0xffffffffu, lane > 0 && prev_t == (int)t)) {
+      if (valid) atomicAdd(out + t, v);
+      continue;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, t);
+    float sum = 0.0f;
+    for (int src = 0; src < 32; ++src) {
+      const float other = __shfl_sync(0xffffffffu, v, src);
+      if ((peers >> src) & 1u) sum += other;
+    }
+    if (valid && lane == __ffs(peers) - 1) atomicAdd(out + t, sum);
   }
 }
 
@@ -66,11 +92,33 @@ __global__ void __launch_bounds__(kSegThreads) k_edge_div_u_sum(const i64* __res
                                                                 const float* __restrict__ divisor,
                                                                 float* __restrict__ out_data,
                                                                 float* __restrict__ out_sum) {
-  for (i64 e = (i64)blockIdx.x * kSegThreads + threadIdx.x; e < E; e += (i64)gridDim.x * kSegThreads) {
-    const float x = data ? __ldg(data + e) : 1.0f;
-    const float v = __fdiv_rn(x, __ldg(divisor + __ldg(row + e)));
-    out_data[e] = v;
-    atomicAdd(out_sum + __ldg(col + e), v);
+  const int lane = threadIdx.x & 31;
+  for (i64 e0 = (i64)blockIdx.x * kSegThreads + threadIdx.x - lane; e0 < E; e0 += (i64)gridDim.x * kSegThreads) {
+    const i64 e = e0 + lane;
+    const bool valid = e < E;
+    float v = 0.0f;
+    i64 t = -1 - lane;
+    if (valid) {
+      v = __fdiv_rn(data ? __ldg(data + e) : 1.0f, __ldg(divisor + __ldg(row + e)));
+      out_data[e] = v;
+      t = __ldg(col + e);
+    }
+    // as in k_segment_sum_coo: one atomic per distinct column of the warp when columns repeat next door
+    const int prev_t = __shfl_up_sync(0xffffffffu, (int)t, 1);  // low words: a false match only takes the fold
+    if (!__any_sync(0xffffffffu, lane > 0 && prev_t == (int)t)) {
+      if (valid) atomicAdd(out_sum + t, v);
+      continue;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, t);
+    float sum = v;
+    if (__any_sync(0xffffffffu, valid && __popc(peers) > 1)) {
+      sum = 0.0f;
+      for (int src = 0; src < 32; ++src) {
+        const float other = __shfl_sync(0xffffffffu, v, src);
+        if ((peers >> src) & 1u) sum += other;
+      }
+    }
+    if (valid && lane == __ffs(peers) - 1) atomicAdd(out_sum + t, sum);
   }
 }
 
@@ -182,14 +230,19 @@ int gsb_segment_sum_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int6
 }
 
 int gsb_segment_sum_coo(gsb_ctx* ctx, void* stream_, const int64_t* target, int64_t E, const int64_t* e_ids,
-                        const float* data, int64_t powk, float* out_zeroed) {
+                        const float* data, int64_t powk, int targets_in_runs, float* out_zeroed) {
   GSB_REQUIRE(ctx && E >= 0 && powk >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (E == 0) return GSB_OK;
   GSB_REQUIRE(target && out_zeroed, GSB_ERR_INVALID_ARGUMENT);
-  k_segment_sum_coo<<<min(grid_for(E, kSegThreads), kNumSMs * 16), kSegThreads, 0, (cudaStream_t)stream_>>>(
-      target, E, e_ids, data, powk, out_zeroed);
+  const int grid = min(grid_for(E, kSegThreads), kNumSMs * 16);
+  {
+    ScopedKernelTimer timer(ctx, KID_SEGMENT, (cudaStream_t)stream_);
+    if (targets_in_runs)
+      k_segment_sum_coo<true><<<grid, kSegThreads, 0, (cudaStream_t)stream_>>>(target, E, e_ids, data, powk, out_zeroed);
+    else
+      k_segment_sum_coo<false><<<grid, kSegThreads, 0, (cudaStream_t)stream_>>>(target, E, e_ids, data, powk, out_zeroed);
+  }
   GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
   return GSB_OK;
 }
 

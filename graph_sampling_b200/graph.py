@@ -491,8 +491,10 @@ class Graph:
         out_size = self.num_cols_ if axis == 0 else self.num_rows_
         out = torch.zeros(out_size, dtype=torch.float32, device=self._device())
         if on_format == _COO:
-            target = self.coo_.row if (1 - axis) == 0 else self.coo_.col
-            ops.coo_sum(target, self.coo_.e_ids, data, out, powk)
+            by_row = (1 - axis) == 0
+            target = self.coo_.row if by_row else self.coo_.col
+            ops.coo_sum(target, self.coo_.e_ids, data, out, powk,
+                        targets_in_runs=self.coo_.row_sorted if by_row else self.coo_.col_sorted)
         elif axis == 0 and on_format == _CSC:
             ops.csc_sum(self.csc_.indptr, self.csc_.e_ids, data, out, powk)
         elif axis == 1 and on_format == _CSR:

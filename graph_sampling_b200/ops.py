@@ -499,12 +499,14 @@ def csc_sum(indptr, e_ids, data, out, powk, ctx=None):
     return out
 
 
-def coo_sum(target, e_ids, data, out, powk, ctx=None):
-    """COOSumCUDA (src/cuda/graph_ops.cu:98-125): out[target[e]] += data[e]^powk; `out` must be zeroed."""
+def coo_sum(target, e_ids, data, out, powk, ctx=None, targets_in_runs=False):
+    """COOSumCUDA (src/cuda/graph_ops.cu:98-125): out[target[e]] += data[e]^powk; `out` must be zeroed.
+    targets_in_runs: equal targets are adjacent (the sorted coordinate of a COO) — a hint, not a requirement."""
     target, e_ids, data = _i64(target, "target"), _i64(e_ids, "e_ids", True), _f32(data, "data", True)
     ctx = ctx or default_context(target.device)
     ctx.check(ctx.lib.gsb_segment_sum_coo(ctx.handle, _stream(), _p(target), c_i64(target.numel()), _p(e_ids),
-                                          _p(data), c_i64(int(powk)), _p(out)), "gsb_segment_sum_coo")
+                                          _p(data), c_i64(int(powk)), c_int(int(bool(targets_in_runs))), _p(out)),
+              "gsb_segment_sum_coo")
     return out
 
 

@@ -207,13 +207,15 @@ GSB_API int gsb_sddmm(gsb_ctx* ctx, void* stream, int op, const int64_t* row, co
  * Replace gs::impl::CSCSumCUDA, COOSumCUDA, CSCNormalizeCUDA (src/cuda/graph_ops.cu:15-188; used by
  * gs::Graph::Sum / Normalize, src/graph.cc:650-702).  sum: out[s] = sum over the segment of
  * data[e]^powk (data == NULL means ones; exact integer power); the COO form accumulates into a
- * caller-zeroed dense vector indexed by target[e].  normalize: out[e] = data[e] / segment sum.
+ * caller-zeroed dense vector indexed by target[e]; targets_in_runs != 0 tells it that equal targets are adjacent
+ * (the sorted coordinate of a COO), which lets a warp fold them before it touches memory — results are the same
+ * either way.  normalize: out[e] = data[e] / segment sum.
  * e_ids maps segment position to data position when present.
  */
 GSB_API int gsb_segment_sum_csc(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64_t num_seg,
                                 const int64_t* e_ids, const float* data, int64_t powk, float* out);
 GSB_API int gsb_segment_sum_coo(gsb_ctx* ctx, void* stream, const int64_t* target, int64_t E, const int64_t* e_ids,
-                                const float* data, int64_t powk, float* out_zeroed);
+                                const float* data, int64_t powk, int targets_in_runs, float* out_zeroed);
 GSB_API int gsb_segment_normalize_csc(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64_t num_seg,
                                       const int64_t* e_ids, const float* data, float* out);
 

@@ -260,6 +260,12 @@ def test_segment_ops_against_oracle_and_fixture(ops, oracle, gold, hub_graph):
     out = torch.zeros(len(gold["indptr"]) - 1, device="cuda")
     ops.coo_sum(dev(row), None, dev(w), out, 2)
     assert np.allclose(host(out), gold["sum_axis1_p2_coo"], rtol=1e-4, atol=1e-6)
+    # the folding variant (meant for sorted targets) gives the same sums on any input, sorted or not
+    for target, size, want in ((row, len(gold["indptr"]) - 1, gold["sum_axis1_p2_coo"]),
+                               (col, len(sub_indptr) - 1, gold["sum_axis0_p2"])):
+        out = torch.zeros(size, device="cuda")
+        ops.coo_sum(dev(target), None, dev(w), out, 2, targets_in_runs=True)
+        assert np.allclose(host(out), want, rtol=1e-4, atol=1e-6)
     nz = torch.empty(len(w), device="cuda")
     ops.csc_normalize(dev(sub_indptr), None, dev(w), nz)
     assert np.allclose(host(nz), gold["normalize_axis0"], rtol=1e-5, atol=1e-7)
