@@ -640,7 +640,7 @@ def run_kernels(args):
     lp[torch.rand(1_000_000, generator=g, device=device) < 0.5] = 0
     ld = torch.arange(1_000_000, device=device)
     timed("list sampling, 512 of 1 M weighted", lambda: ops.list_sampling(ld, 512, False, probs=lp), 12 * 1_000_000 + 16 * 512,
-          note="20 launches; latency bound")
+          note="12 launches; bound by host launch time")
     # ---- feature load, induced subgraph, metapath walk, super-batch operators --------------------------------
     fr = torch.randint(0, n, (1_000_000,), generator=g, device=device)
     timed("feature rows gather, F = 256 (1 M rows)", lambda: ops.gather_rows(x, fr), fr.numel() * (8 + 8 * F))
