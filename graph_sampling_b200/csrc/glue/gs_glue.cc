@@ -7,7 +7,7 @@
 // Every piece of arithmetic goes through the C ABI of gsb200.h with raw device pointers and torch's current
 // stream.  The state kept per graph and the effect of each method on it follow gs::Graph
 // (src/graph.h:113-126, src/graph.cc).  Where the reference aborts the process (LOG(FATAL)), TORCH_CHECK
-// raises instead.  Compact-id (DCSC/DCSR) layouts are not provided.
+// raises instead.
 #include <c10/cuda/CUDAStream.h>
 #include <torch/custom_class.h>
 #include <torch/script.h>
@@ -339,19 +339,77 @@ class Graph : public torch::CustomClassHolder {
   // lazy formats (src/graph.cc:585-644, src/graph_ops.cc:13-60)
   void CreateSparseFormat(int64_t format) {
     if (format == kCOO) {
-      if (coo_) return;
-      coo_ = csc_ ? ToCOO(*csc_, true) : ToCOO(*csr_, false);
+      if (!coo_) coo_ = AnyToCOO();
     } else if (format == kCSC) {
-      if (csc_) return;
-      if (!coo_) coo_ = ToCOO(*csr_, false);
+      if (csc_) {
+        TORCH_CHECK(!val_col_ids_.has_value(), "Require CSC, get DCSC instead");
+        return;
+      }
+      if (!coo_) coo_ = AnyToCOO();
       csc_ = FromCOO(*coo_, num_cols_, true);
+    } else if (format == kDCSC) {
+      if (csc_) {
+        TORCH_CHECK(val_col_ids_.has_value(), "Require DCSC, get CSC instead");
+        return;
+      }
+      if (!coo_) coo_ = AnyToCOO();
+      Tensor val;
+      std::tie(csc_, val) = CompactFromCOO(*coo_, num_cols_, true);
+      val_col_ids_ = val;
     } else if (format == kCSR) {
-      if (csr_) return;
-      if (!coo_) coo_ = ToCOO(*csc_, true);
+      if (csr_) {
+        TORCH_CHECK(!val_row_ids_.has_value(), "Require CSR, get DCSR instead");
+        return;
+      }
+      if (!coo_) coo_ = AnyToCOO();
       csr_ = FromCOO(*coo_, num_rows_, false);
+    } else if (format == kDCSR) {
+      if (csr_) {
+        TORCH_CHECK(val_row_ids_.has_value(), "Require DCSR, get CSR instead");
+        return;
+      }
+      if (!coo_) coo_ = AnyToCOO();
+      Tensor val;
+      std::tie(csr_, val) = CompactFromCOO(*coo_, num_rows_, false);
+      val_row_ids_ = val;
     } else {
-      TORCH_CHECK(false, "compact-id (DCSC / DCSR) layouts are not provided by this library");
+      TORCH_CHECK(false, "unknown sparse format");
     }
+  }
+
+  // Doubly compressed forms: offsets only over the columns (rows) that have edges, plus the list of those ids
+  // (src/cuda/format_transform.cu:172-203, src/graph_ops.cc:62-110).
+  static std::pair<std::shared_ptr<CSC>, Tensor> CompactFromCOO(const COO& c, int64_t num_items, bool to_csc) {
+    std::shared_ptr<CSC> dense = FromCOO(c, num_items, to_csc);
+    const int64_t n = dense->indptr.numel() - 1;
+    Tensor degree = dense->indptr.slice(0, 1, n + 1) - dense->indptr.slice(0, 0, n);
+    Tensor val = torch::nonzero(degree > 0).reshape({-1});
+    Tensor indptr = torch::cat({dense->indptr.index({val}), dense->indptr.slice(0, n, n + 1)});
+    return {std::make_shared<CSC>(CSC{indptr, dense->indices, dense->e_ids}), val};
+  }
+  std::shared_ptr<COO> AnyToCOO() {
+    const bool from_csc = csc_ != nullptr;
+    const CSC& g = from_csc ? *csc_ : *csr_;
+    const OptTensor& val = from_csc ? val_col_ids_ : val_row_ids_;
+    Tensor expanded = ExpandOffsets(g);
+    if (val.has_value()) expanded = val.value().index({expanded});
+    return from_csc ? std::make_shared<COO>(COO{g.indices, expanded, g.e_ids, false, true})
+                    : std::make_shared<COO>(COO{expanded, g.indices, g.e_ids, true, false});
+  }
+  // DCSCColSlicingCUDA (src/cuda/slicing.cu:298-413): column slice of a doubly compressed form; a requested id
+  // without edges is absent from val_ids and yields an empty segment.
+  Sliced CompactColSlice(const CSC& g, const Tensor& val_ids, const Tensor& ids, bool with_coo, const OptTensor& data) {
+    Tensor n_ids = Ids(ids, "node ids"), val = Ids(val_ids, "valid ids");
+    Tensor pos = torch::empty_like(n_ids);
+    Check(gsb_index_search(Ctx(), Stream(), IP(val), val.numel(), IP(n_ids), n_ids.numel(), MP(pos)), "gsb_index_search");
+    Tensor present = torch::nonzero(pos >= 0).reshape({-1});
+    Sliced r = ColSlice(g, pos.index({present}).contiguous(), with_coo, data);
+    Tensor counts = torch::zeros({n_ids.numel() + 1}, n_ids.options());
+    const int64_t m = r.indptr.numel() - 1;
+    counts.index_put_({present + 1}, r.indptr.slice(0, 1, m + 1) - r.indptr.slice(0, 0, m));
+    r.indptr = torch::cumsum(counts, 0);
+    if (with_coo) r.coo_other = present.index({r.coo_other});
+    return r;
   }
 
   // Slicing (src/graph.cc:173-310)
@@ -374,6 +432,7 @@ class Graph : public torch::CustomClassHolder {
     }
     std::shared_ptr<CSC> csc, csr;
     std::shared_ptr<COO> coo;
+    OptTensor new_val_cols, new_val_rows;
     Tensor out_data;
     auto gather = [&](const OptTensor& e_ids, const Tensor& select) {
       if (!data_.has_value()) return;
@@ -387,15 +446,17 @@ class Graph : public torch::CustomClassHolder {
       coo = std::make_shared<COO>(COO{nr, nc, torch::nullopt, coo_->row_sorted, coo_->col_sorted});
       new_edges = nr.numel();
       gather(coo_->e_ids, sel);
-    } else if (on_format == kCSC || on_format == kCSR) {
-      const bool on_csc = on_format == kCSC;
+    } else if (on_format == kCSC || on_format == kCSR || on_format == kDCSC || on_format == kDCSR) {
+      const bool on_csc = on_format == kCSC || on_format == kDCSC;
+      const OptTensor& val_ids = on_csc ? val_col_ids_ : val_row_ids_;
       TORCH_CHECK(output_format != (on_csc ? kCSR : kCSC), "Error in Slicing, Not implementation [on_format = ",
                   on_csc ? "CSC, output_forat = CSR]" : "CSR, output_forat = CSC]");
       const CSC& g = on_csc ? *csc_ : *csr_;
       const bool slice_segments = (axis == 0) == on_csc;  // slicing along the format's own axis
       Tensor indptr, other, indices;
       if (slice_segments) {
-        Sliced r = ColSlice(g, n_ids, with_coo, data_);
+        Sliced r = val_ids.has_value() ? CompactColSlice(g, val_ids.value(), n_ids, with_coo, data_)
+                                       : ColSlice(g, n_ids, with_coo, data_);
         indptr = r.indptr, other = r.coo_other, indices = r.indices, out_data = r.data;
         if (relabel) {
           auto res = Relabel({indices}, {indices});
@@ -408,6 +469,7 @@ class Graph : public torch::CustomClassHolder {
         Tensor sel;
         std::tie(indptr, other, indices, sel) = RowSliceCSC(g, n_ids, with_coo);
         gather(g.e_ids, sel);
+        (on_csc ? new_val_cols : new_val_rows) = val_ids;
       }
       if (output_format & (on_csc ? kCSC : kCSR))
         (on_csc ? csc : csr) = std::make_shared<CSC>(CSC{indptr, indices, torch::nullopt});
@@ -416,11 +478,12 @@ class Graph : public torch::CustomClassHolder {
                      : std::make_shared<COO>(COO{other, indices, torch::nullopt, true, false});
       new_edges = indices.numel();
     } else {
-      TORCH_CHECK(false, "Slicing on DCSC / DCSR is not provided by this library");
+      TORCH_CHECK(false, "Not implemented warning");
     }
     auto ret = c10::make_intrusive<Graph>(true, new_col_ids, new_row_ids, new_cols, new_rows);
     ret->num_edges_ = new_edges;
     ret->csc_ = csc, ret->csr_ = csr, ret->coo_ = coo;
+    ret->val_col_ids_ = new_val_cols, ret->val_row_ids_ = new_val_rows;
     if (out_data.defined()) ret->data_ = out_data;
     return ret;
   }
@@ -651,7 +714,7 @@ class Graph : public torch::CustomClassHolder {
     Tensor rows;
     if (csc_) rows = row_ids_.has_value() ? row_ids_.value() : csc_->indices;
     else {
-      if (!coo_) coo_ = ToCOO(*csr_, false);
+      if (!coo_) coo_ = AnyToCOO();
       rows = row_ids_.has_value() ? row_ids_.value() : coo_->row;
     }
     return std::get<0>(Relabel({col_ids_.value(), rows}, {}));
@@ -660,13 +723,14 @@ class Graph : public torch::CustomClassHolder {
     TORCH_CHECK(col_ids_.has_value(), "For sampling, col_ids_ is necessary!");
     Tensor col_ids = col_ids_.value();
     if (csc_) {
+      if (val_col_ids_.has_value()) col_ids = col_ids.index({val_col_ids_.value()});  // src/graph.cc:790-791
       Tensor rows = row_ids_.has_value() ? row_ids_.value().index({csc_->indices}) : csc_->indices;
       auto res = Relabel({col_ids, rows}, {rows});
       Tensor frontier = std::get<0>(res);
       return {frontier, frontier.numel(), col_ids.numel(), csc_->indptr.clone(), std::get<1>(res)[0], csc_->e_ids, "csc"};
     }
     TORCH_CHECK(csr_ || coo_, "Error in Relabel!");
-    if (!coo_) coo_ = ToCOO(*csr_, false);
+    if (!coo_) coo_ = AnyToCOO();
     Tensor coo_col = col_ids.index({coo_->col});
     Tensor coo_row = row_ids_.has_value() ? row_ids_.value().index({coo_->row}) : coo_->row;
     auto res = Relabel({col_ids, coo_row}, {coo_col, coo_row});
@@ -689,6 +753,12 @@ class Graph : public torch::CustomClassHolder {
   void SDDMM(const std::string& op, Tensor lhs, Tensor rhs, Tensor out, int64_t lhs_target, int64_t rhs_target,
              int64_t on_format) {
     CreateSparseFormat(on_format);
+    if (on_format == kDCSC || on_format == kDCSR) {
+      // a compact form numbers its segments by position in val_*_ids_; the COO view has the node ids again and
+      // carries the same edge ids, so the result lands in the same order
+      CreateSparseFormat(kCOO);
+      on_format = kCOO;
+    }
     if (on_format == kCOO) {
       Sddmm(op, coo_->row, &coo_->col, nullptr, coo_->e_ids, lhs, rhs, out, lhs_target, rhs_target);
     } else if (on_format == kCSR) {
@@ -716,11 +786,21 @@ class Graph : public torch::CustomClassHolder {
       Check(gsb_segment_sum_coo(Ctx(), Stream(), IP(target), target.numel(), IP(e), FP(data), powk,
                                 (by_row ? coo_->row_sorted : coo_->col_sorted) ? 1 : 0, o),
             "gsb_segment_sum_coo");
-    } else if ((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR)) {
+    } else if ((axis == 0 && (on_format == kCSC || on_format == kDCSC)) ||
+               (axis == 1 && (on_format == kCSR || on_format == kDCSR))) {
       const CSC& g = axis == 0 ? *csc_ : *csr_;
+      const OptTensor& val = axis == 0 ? val_col_ids_ : val_row_ids_;
       Tensor e = g.e_ids.has_value() ? g.e_ids.value() : Tensor();
-      Check(gsb_segment_sum_csc(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(e), FP(data), powk, o),
-            "gsb_segment_sum_csc");
+      if (!val.has_value()) {
+        Check(gsb_segment_sum_csc(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(e), FP(data), powk, o),
+              "gsb_segment_sum_csc");
+      } else {  // segment c of a compact form belongs to node val[c] (src/cuda/graph_ops.cu:15-39)
+        Tensor compact = torch::zeros({val.value().numel()}, out.options());
+        Check(gsb_segment_sum_csc(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(e), FP(data), powk,
+                                  compact.numel() ? compact.data_ptr<float>() : nullptr),
+              "gsb_segment_sum_csc");
+        out.index_put_({val.value()}, compact);
+      }
     } else {
       TORCH_CHECK(false, "axis should be 0 or 1? on_format and axis do not match?");
     }
@@ -728,7 +808,9 @@ class Graph : public torch::CustomClassHolder {
   }
   c10::intrusive_ptr<Graph> Normalize(int64_t axis, int64_t on_format) {
     CreateSparseFormat(on_format);
-    TORCH_CHECK((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR), "Not Implementation Error");
+    TORCH_CHECK((axis == 0 && (on_format == kCSC || on_format == kDCSC)) ||
+                    (axis == 1 && (on_format == kCSR || on_format == kDCSR)),
+                "Not Implementation Error");
     const CSC& g = axis == 0 ? *csc_ : *csr_;
     Tensor in = Floats(DataOrOnes(), "edge data");
     Tensor out = torch::empty_like(in);
@@ -744,9 +826,12 @@ class Graph : public torch::CustomClassHolder {
     Tensor out = torch::zeros({num_edges_}, in.options());
     if (on_format == kCOO) {
       Sddmm("div", coo_->row, &coo_->col, nullptr, coo_->e_ids, in, divisor, out, 1, (1 - axis) == 0 ? 0 : 2);
-    } else if ((axis == 0 && on_format == kCSC) || (axis == 1 && on_format == kCSR)) {
+    } else if ((axis == 0 && (on_format == kCSC || on_format == kDCSC)) ||
+               (axis == 1 && (on_format == kCSR || on_format == kDCSR))) {
       const CSC& g = axis == 0 ? *csc_ : *csr_;
-      Sddmm("div", g.indices, nullptr, &g.indptr, g.e_ids, in, divisor, out, 1, 2);
+      const OptTensor& val = axis == 0 ? val_col_ids_ : val_row_ids_;
+      Tensor per_segment = val.has_value() ? divisor.index({val.value()}).contiguous() : divisor;
+      Sddmm("div", g.indices, nullptr, &g.indptr, g.e_ids, in, per_segment, out, 1, 2);
     }
     return SameStructure(out);
   }
@@ -764,7 +849,7 @@ class Graph : public torch::CustomClassHolder {
     else if (csc_ && !csc_->e_ids.has_value()) rows = csc_->indices;
     else {
       TORCH_CHECK(csr_ && !csr_->e_ids.has_value(), "Error in GetCOORows!");
-      coo_ = ToCOO(*csr_, false);
+      coo_ = AnyToCOO();
       rows = coo_->row;
     }
     return (is_original && row_ids_.has_value()) ? row_ids_.value().index({rows}) : rows;
@@ -773,7 +858,7 @@ class Graph : public torch::CustomClassHolder {
     Tensor cols;
     if (coo_) cols = coo_->col;
     else if (csc_ && !csc_->e_ids.has_value()) {
-      coo_ = ToCOO(*csc_, true);
+      coo_ = AnyToCOO();
       cols = coo_->col;
     } else {
       TORCH_CHECK(csr_ && !csr_->e_ids.has_value(), "Error in GetCOOCols!");
@@ -782,11 +867,11 @@ class Graph : public torch::CustomClassHolder {
     return (is_original && col_ids_.has_value()) ? col_ids_.value().index({cols}) : cols;
   }
   Tensor GetValidRows() {
-    Tensor local = std::get<0>(torch::_unique(GetCOORows(false)));
+    Tensor local = val_row_ids_.has_value() ? val_row_ids_.value() : std::get<0>(torch::_unique(GetCOORows(false)));
     return row_ids_.has_value() ? row_ids_.value().index({local}) : local;
   }
   Tensor GetValidCols() {
-    Tensor local = std::get<0>(torch::_unique(GetCOOCols(false)));
+    Tensor local = val_col_ids_.has_value() ? val_col_ids_.value() : std::get<0>(torch::_unique(GetCOOCols(false)));
     return col_ids_.has_value() ? col_ids_.value().index({local}) : local;
   }
   std::vector<Tensor> MetaData() {
@@ -842,6 +927,7 @@ class Graph : public torch::CustomClassHolder {
     ret->csc_ = csc_, ret->csr_ = csr_, ret->coo_ = coo_;
     ret->num_edges_ = num_edges_;
     ret->data_ = data;
+    ret->val_col_ids_ = val_col_ids_, ret->val_row_ids_ = val_row_ids_;
     return ret;
   }
 
@@ -850,6 +936,7 @@ class Graph : public torch::CustomClassHolder {
   std::shared_ptr<CSC> csc_, csr_;
   std::shared_ptr<COO> coo_;
   OptTensor data_, col_ids_, row_ids_;
+  OptTensor val_col_ids_, val_row_ids_;  // ids that have edges, when csc_ / csr_ is doubly compressed (DCSC / DCSR)
 };
 
 // ---- HeteroGraph (src/hetero_graph.h:38-70, src/hetero_graph.cc:20-75) ----------------------------------------

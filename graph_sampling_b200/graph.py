@@ -139,30 +139,101 @@ class Graph:
             e_ids = sort_index
         return CSC(indptr, indices, e_ids)
 
+    # Doubly compressed forms (DCSC / DCSR): offsets only over the columns (rows) that have edges, plus the list of
+    # those ids (val_col_ids_ / val_row_ids_) — src/cuda/format_transform.cu:172-203, src/graph_ops.cc:62-110.
+    def _coo2dcsc(self, coo, num_items, to_csc):
+        dense = self._coo2csc(coo, num_items, to_csc)
+        degree = dense.indptr[1:] - dense.indptr[:-1]
+        val_ids = torch.nonzero(degree > 0).reshape(-1)
+        return CSC(torch.cat([dense.indptr[val_ids], dense.indptr[-1:]]), dense.indices, dense.e_ids), val_ids
+
+    def _dcsc2coo(self, csc, val_ids, is_csc):
+        expanded = val_ids[ops.csc2coo(csc.indptr, csc.indices)[1]]
+        if is_csc:
+            return COO(csc.indices, expanded, csc.e_ids, False, True)
+        return COO(expanded, csc.indices, csc.e_ids, True, False)
+
+    def _any2coo(self):
+        if self.csc_ is not None:
+            if self.val_col_ids_ is not None:
+                return self._dcsc2coo(self.csc_, self.val_col_ids_, True)
+            return self._csc2coo(self.csc_, True)
+        if self.val_row_ids_ is not None:
+            return self._dcsc2coo(self.csr_, self.val_row_ids_, False)
+        return self._csc2coo(self.csr_, False)
+
+    def CSC2CSR(self):
+        self.coo_ = self._csc2coo(self.csc_, True)
+        self.csr_ = self._coo2csc(self.coo_, self.num_rows_, False)
+
+    def CSC2DCSR(self):
+        self.coo_ = self._csc2coo(self.csc_, True)
+        self.csr_, self.val_row_ids_ = self._coo2dcsc(self.coo_, self.num_rows_, False)
+
+    def CSR2CSC(self):
+        self.coo_ = self._csc2coo(self.csr_, False)
+        self.csc_ = self._coo2csc(self.coo_, self.num_cols_, True)
+
+    def CSR2DCSC(self):
+        self.coo_ = self._csc2coo(self.csr_, False)
+        self.csc_, self.val_col_ids_ = self._coo2dcsc(self.coo_, self.num_cols_, True)
+
     def CreateSparseFormat(self, fmt):
+        """src/graph.cc:585-644."""
         if fmt == _COO:
-            if self.coo_ is not None:
-                return
-            if self.csc_ is not None:
-                self.coo_ = self._csc2coo(self.csc_, True)
-            else:
-                self.coo_ = self._csc2coo(self.csr_, False)
+            if self.coo_ is None:
+                self.coo_ = self._any2coo()
         elif fmt == _CSC:
             if self.csc_ is not None:
+                if self.val_col_ids_ is not None:
+                    _fatal("Require CSC, get DCSC instead")
                 return
-            if self.coo_ is None:
-                self.coo_ = self._csc2coo(self.csr_, False)
-            self.csc_ = self._coo2csc(self.coo_, self.num_cols_, True)
+            if self.coo_ is not None:
+                self.csc_ = self._coo2csc(self.coo_, self.num_cols_, True)
+            else:
+                self.CSR2CSC()
+        elif fmt == _DCSC:
+            if self.csc_ is not None:
+                if self.val_col_ids_ is None:
+                    _fatal("Require DCSC, get CSC instead")
+                return
+            if self.coo_ is not None:
+                self.csc_, self.val_col_ids_ = self._coo2dcsc(self.coo_, self.num_cols_, True)
+            else:
+                self.CSR2DCSC()
         elif fmt == _CSR:
             if self.csr_ is not None:
+                if self.val_row_ids_ is not None:
+                    _fatal("Require CSR, get DCSR instead")
                 return
-            if self.coo_ is None:
-                self.coo_ = self._csc2coo(self.csc_, True)
-            self.csr_ = self._coo2csc(self.coo_, self.num_rows_, False)
-        elif fmt in (_DCSC, _DCSR):
-            raise NotImplementedError("compact-id (DCSC / DCSR) layouts are outside the sampling hot path")
+            if self.coo_ is not None:
+                self.csr_ = self._coo2csc(self.coo_, self.num_rows_, False)
+            else:
+                self.CSC2CSR()
+        elif fmt == _DCSR:
+            if self.csr_ is not None:
+                if self.val_row_ids_ is None:
+                    _fatal("Require DCSR, get CSR instead")
+                return
+            if self.coo_ is not None:
+                self.csr_, self.val_row_ids_ = self._coo2dcsc(self.coo_, self.num_rows_, False)
+            else:
+                self.CSC2DCSR()
         else:
             _fatal("unknown sparse format")
+
+    def _compact_col_slicing(self, fmt, val_ids, n_ids, with_coo, data, e_ids):
+        """DCSCColSlicingCUDA (src/cuda/slicing.cu:298-413): column slice of a doubly compressed form.  A requested
+        id that has no edges is absent from val_ids and yields an empty segment."""
+        pos = ops.index_search(val_ids, n_ids)
+        present = torch.nonzero(pos >= 0).reshape(-1)
+        r = ops.csc_col_slicing(fmt.indptr, fmt.indices, pos[present].contiguous(), with_coo, data=data, e_ids=e_ids)
+        counts = torch.zeros(n_ids.numel() + 1, dtype=torch.int64, device=n_ids.device)
+        counts[present + 1] = r[0][1:] - r[0][:-1]
+        out = [torch.cumsum(counts, 0), present[r[1]] if with_coo else None, r[2], r[3]]
+        if data is not None:
+            out.append(r[4])
+        return out
 
     # ---- helpers -----------------------------------------------------------------------------------------
     def _child(self, col_ids, row_ids, num_cols, num_rows):
@@ -187,6 +258,7 @@ class Graph:
             new_num_cols, new_num_rows = self.num_cols_, n_ids.numel()
         csc_ptr = csr_ptr = coo_ptr = None
         out_data = None
+        new_val_cols = new_val_rows = None
 
         if on_format == _COO:
             coo = self.coo_
@@ -199,12 +271,16 @@ class Graph:
             e_ids = coo.e_ids
             if self.data_ is not None:
                 out_data = self.data_[e_ids[select] if e_ids is not None else select]
-        elif on_format == _CSC:
+        elif on_format in (_CSC, _DCSC):
             if output_format == _CSR:
                 _fatal("Error in Slicing, Not implementation [on_format = CSC, output_forat = CSR]")
             data, e_ids = self._gather_args(self.csc_)
             if axis == 0:
-                r = ops.csc_col_slicing(self.csc_.indptr, self.csc_.indices, n_ids, with_coo, data=data, e_ids=e_ids)
+                if self.val_col_ids_ is not None:
+                    r = self._compact_col_slicing(self.csc_, self.val_col_ids_, n_ids, with_coo, data, e_ids)
+                else:
+                    r = ops.csc_col_slicing(self.csc_.indptr, self.csc_.indices, n_ids, with_coo, data=data,
+                                            e_ids=e_ids)
                 indptr, coo_col, indices = r[0], r[1], r[2]
                 out_data = r[4] if data is not None else None
                 if relabel:
@@ -215,6 +291,7 @@ class Graph:
                     _fatal("Not implemented warning")
                 indptr, coo_col, indices, select = ops.csc_row_slicing(self.csc_.indptr, self.csc_.indices, n_ids,
                                                                        with_coo)
+                new_val_cols = self.val_col_ids_
                 if data is not None:
                     out_data = data[e_ids[select] if e_ids is not None else select]
             if output_format & _CSC:
@@ -222,7 +299,7 @@ class Graph:
             if output_format & _COO:
                 coo_ptr = COO(indices, coo_col, None, False, True)
             new_num_edges = indices.numel()
-        elif on_format == _CSR:
+        elif on_format in (_CSR, _DCSR):
             if output_format == _CSC:
                 _fatal("Error in Slicing, Not implementation [on_format = CSR, output_forat = CSC]")
             data, e_ids = self._gather_args(self.csr_)
@@ -231,10 +308,15 @@ class Graph:
                     _fatal("Not implemented warning")
                 indptr, coo_row, indices, select = ops.csc_row_slicing(self.csr_.indptr, self.csr_.indices, n_ids,
                                                                        with_coo)
+                new_val_rows = self.val_row_ids_
                 if data is not None:
                     out_data = data[e_ids[select] if e_ids is not None else select]
             else:
-                r = ops.csc_col_slicing(self.csr_.indptr, self.csr_.indices, n_ids, with_coo, data=data, e_ids=e_ids)
+                if self.val_row_ids_ is not None:
+                    r = self._compact_col_slicing(self.csr_, self.val_row_ids_, n_ids, with_coo, data, e_ids)
+                else:
+                    r = ops.csc_col_slicing(self.csr_.indptr, self.csr_.indices, n_ids, with_coo, data=data,
+                                            e_ids=e_ids)
                 indptr, coo_row, indices = r[0], r[1], r[2]
                 out_data = r[4] if data is not None else None
                 if relabel:
@@ -246,11 +328,12 @@ class Graph:
                 coo_ptr = COO(coo_row, indices, None, True, False)
             new_num_edges = indices.numel()
         else:
-            raise NotImplementedError("Slicing on DCSC / DCSR is outside the sampling hot path")
+            _fatal("Not implemented warning")
 
         ret = self._child(new_col_ids, new_row_ids, new_num_cols, new_num_rows)
         ret.num_edges_ = new_num_edges
         ret.coo_, ret.csc_, ret.csr_ = coo_ptr, csc_ptr, csr_ptr
+        ret.val_col_ids_, ret.val_row_ids_ = new_val_cols, new_val_rows
         if out_data is not None:
             ret.data_ = out_data
         return ret
@@ -471,6 +554,11 @@ class Graph:
     # ---- SDDMM (src/graph.cc:967-985) ------------------------------------------------------------------------------------
     def SDDMM(self, op, lhs, rhs, out, lhs_target, rhs_target, on_format):
         self.CreateSparseFormat(on_format)
+        if on_format in (_DCSC, _DCSR):
+            # a compact form numbers its segments by position in val_*_ids_; the COO view has the node ids again and
+            # carries the same edge ids, so the result lands in the same order
+            self.CreateSparseFormat(_COO)
+            on_format = _COO
         if on_format == _COO:
             ops.sddmm(op, lhs, rhs, out, lhs_target, rhs_target, self.coo_.row, self.coo_.col, e_ids=self.coo_.e_ids)
         elif on_format == _CSR:
@@ -495,10 +583,14 @@ class Graph:
             target = self.coo_.row if by_row else self.coo_.col
             ops.coo_sum(target, self.coo_.e_ids, data, out, powk,
                         targets_in_runs=self.coo_.row_sorted if by_row else self.coo_.col_sorted)
-        elif axis == 0 and on_format == _CSC:
-            ops.csc_sum(self.csc_.indptr, self.csc_.e_ids, data, out, powk)
-        elif axis == 1 and on_format == _CSR:
-            ops.csc_sum(self.csr_.indptr, self.csr_.e_ids, data, out, powk)
+        elif (axis == 0 and on_format in (_CSC, _DCSC)) or (axis == 1 and on_format in (_CSR, _DCSR)):
+            fmt, val_ids = (self.csc_, self.val_col_ids_) if axis == 0 else (self.csr_, self.val_row_ids_)
+            if val_ids is None:
+                ops.csc_sum(fmt.indptr, fmt.e_ids, data, out, powk)
+            else:  # segment c of a compact form belongs to node val_ids[c] (src/cuda/graph_ops.cu:15-39)
+                compact = torch.zeros(val_ids.numel(), dtype=torch.float32, device=out.device)
+                ops.csc_sum(fmt.indptr, fmt.e_ids, data, compact, powk)
+                out[val_ids] = compact
         else:
             _fatal("axis should be 0 or 1? on_format and axis do not match?")
         return out
@@ -515,9 +607,9 @@ class Graph:
         self.CreateSparseFormat(on_format)
         in_data = self._data_or_ones()
         out = torch.empty_like(in_data)
-        if axis == 0 and on_format == _CSC:
+        if axis == 0 and on_format in (_CSC, _DCSC):
             ops.csc_normalize(self.csc_.indptr, self.csc_.e_ids, in_data, out)
-        elif axis == 1 and on_format == _CSR:
+        elif axis == 1 and on_format in (_CSR, _DCSR):
             ops.csc_normalize(self.csr_.indptr, self.csr_.e_ids, in_data, out)
         else:
             _fatal("Not Implementation Error")
@@ -531,12 +623,10 @@ class Graph:
             rhs_target = 0 if (1 - axis) == 0 else 2
             ops.sddmm("div", in_data, divisor, out, 1, rhs_target, self.coo_.row, self.coo_.col,
                       e_ids=self.coo_.e_ids)
-        elif axis == 0 and on_format == _CSC:
-            ops.sddmm("div", in_data, divisor, out, 1, 2, self.csc_.indices, None, indptr=self.csc_.indptr,
-                      e_ids=self.csc_.e_ids)
-        elif axis == 1 and on_format == _CSR:
-            ops.sddmm("div", in_data, divisor, out, 1, 2, self.csr_.indices, None, indptr=self.csr_.indptr,
-                      e_ids=self.csr_.e_ids)
+        elif (axis == 0 and on_format in (_CSC, _DCSC)) or (axis == 1 and on_format in (_CSR, _DCSR)):
+            fmt, val_ids = (self.csc_, self.val_col_ids_) if axis == 0 else (self.csr_, self.val_row_ids_)
+            per_segment = divisor if val_ids is None else divisor[val_ids].contiguous()
+            ops.sddmm("div", in_data, per_segment, out, 1, 2, fmt.indices, None, indptr=fmt.indptr, e_ids=fmt.e_ids)
         return self._same_structure_child(out)
 
     # ---- getters (src/graph.cc:841-965) ------------------------------------------------------------------------------------
@@ -609,10 +699,6 @@ class Graph:
             _fatal("Check failed: coo_->col_sorted == true")
         return [self.coo_.row, self.coo_.col, self.coo_.e_ids]
 
-    # ---- outside the hot path ------------------------------------------------------------------------------------------------------
-    def _out_of_scope(self, *a, **k):
-        raise NotImplementedError("induced-subgraph / compact-id methods are outside the sampling hot path")
-
     def Decode(self, encoding_size):
         """Strips the batch encoding from both id maps.  (The reference's version aborts whenever an id map is
         present and dereferences it when it is absent, src/graph.cc:1035-1040; this one does what its name says.)"""
@@ -658,6 +744,8 @@ _NAME_MAP = {
     "SetCOOByTensor": ("_CAPI_SetCOO", "_CAPI_set_coo"),
     "SetMetaData": ("_CAPI_SetMetadata", "_CAPI_set_metadata"),
     "FusedBidirSlicing": ("_CAPI_FusionSlicing", "_CAPI_fusion_slicing"),
+    "CSC2DCSR": ("_CAPI_CSC2DCSR",),
+    "CSR2DCSC": ("_CAPI_CSR2DCSC",),
     "BatchSlicing": ("_CAPI_BatchSlicing", "_CAPI_batch_slicing"),
     "BatchFusedBidirSlicing": ("_CAPI_BatchFusionSlicing", "_CAPI_batch_fusion_slicing"),
     "Split": ("_CAPI_Split",),

@@ -98,5 +98,5 @@ def test_graph_methods_raise_where_the_reference_aborts():
         g._CAPI_slicing(torch.arange(2).cuda(), 0, gs._CSC, gs._CSR, False)  # CSC -> CSR output: not implemented
     with pytest.raises(RuntimeError):
         g._CAPI_all_valid_node()  # col_ids missing
-    with pytest.raises(NotImplementedError):
-        g._CAPI_slicing(torch.arange(2).cuda(), 0, gs._DCSC, gs._CSC, False)  # compact-id layouts: not provided
+    with pytest.raises(RuntimeError, match="Require DCSC, get CSC instead"):
+        g._CAPI_slicing(torch.arange(2).cuda(), 0, gs._DCSC, gs._CSC, False)  # holds a plain CSC (src/graph.cc:609-613)
