@@ -47,15 +47,41 @@ static void Check(int st, const char* what) {
 static const int64_t* IP(const Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<int64_t>() : nullptr; }
 static int64_t* MP(Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<int64_t>() : nullptr; }
 static const float* FP(const Tensor& t) { return t.defined() && t.numel() ? t.data_ptr<float>() : nullptr; }
+// Graph arrays may live in pinned host memory, which the kernels read in place over the unified address space
+// (the reference accepts the same: src/graph_ops.cc:144,226, src/cuda/slicing.cu:128); results are always allocated
+// on the current device.
+static bool Pinned(const Tensor& t) { return !t.is_cuda() && t.is_pinned(); }
 static Tensor Ids(const Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt64, name, " must be an int64 CUDA tensor");
+  TORCH_CHECK((t.is_cuda() || Pinned(t)) && t.scalar_type() == torch::kInt64, name, " must be an int64 CUDA (or pinned host) tensor");
+  TORCH_CHECK(t.is_cuda() || t.is_contiguous(), name, ": a pinned host tensor must be contiguous");
   return t.contiguous();
 }
 static Tensor Floats(const Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32, name, " must be a float32 CUDA tensor");
+  TORCH_CHECK((t.is_cuda() || Pinned(t)) && t.scalar_type() == torch::kFloat32, name, " must be a float32 CUDA (or pinned host) tensor");
+  TORCH_CHECK(t.is_cuda() || t.is_contiguous(), name, ": a pinned host tensor must be contiguous");
   return t.contiguous();
 }
-static Tensor EmptyIds(int64_t n, const Tensor& like) { return torch::empty({n}, like.options().dtype(torch::kInt64)); }
+static torch::Device DeviceOf(const Tensor& t) {
+  return t.is_cuda() ? t.device() : torch::Device(torch::kCUDA, c10::cuda::current_device());
+}
+static c10::TensorOptions OnDevice(const Tensor& like) { return like.options().device(DeviceOf(like)); }
+// src[index] for per-edge arrays that may be pinned (edge data: float32, edge ids: int64, copied as pairs of words):
+// the GPU reads the pinned array in place, as gs::impl::IndexSelectCPUFromGPU does (src/graph.cc:296-306).
+static Tensor Take(const Tensor& src, const Tensor& index);
+static Tensor EmptyIds(int64_t n, const Tensor& like) { return torch::empty({n}, OnDevice(like).dtype(torch::kInt64)); }
+static Tensor Take(const Tensor& src, const Tensor& index) {
+  if (src.is_cuda()) return src.index({index});
+  TORCH_CHECK(Pinned(src) && src.is_contiguous() && src.dim() == 1, "a host-side edge array must be pinned, contiguous and 1-D");
+  const bool ids = src.scalar_type() == torch::kInt64;
+  TORCH_CHECK(ids || src.scalar_type() == torch::kFloat32, "a pinned edge array must be int64 or float32");
+  Tensor idx = Ids(index, "index");
+  const int64_t n = idx.numel(), words = ids ? 2 : 1;
+  Tensor out = torch::empty({n}, OnDevice(src));
+  if (n)
+    Check(gsb_gather_rows(Ctx(), Stream(), (const float*)src.data_ptr(), src.numel(), words, IP(idx), n, (float*)out.data_ptr()),
+          "gsb_gather_rows");
+  return out;
+}
 
 static std::atomic<uint64_t> g_seed_base{7777};
 static std::atomic<uint64_t> g_seed_counter{0};
@@ -89,7 +115,7 @@ static Sliced ColSlice(const CSC& g, const Tensor& ids, bool with_coo, const Opt
   Tensor d, e;
   if (data.has_value()) {
     d = Floats(data.value(), "edge data");
-    r.data = torch::empty({nnz}, d.options());
+    r.data = torch::empty({nnz}, OnDevice(d));
     if (g.e_ids.has_value()) e = g.e_ids.value();
   }
   Check(gsb_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(n_ids), S, IP(r.indptr), MP(r.indices),
@@ -113,7 +139,7 @@ static Sliced Sample(const CSC& g, const Tensor* seeds, int64_t fanout, bool rep
   Tensor d, e, out_d, p;
   if (data.has_value()) {
     d = Floats(data.value(), "edge data");
-    out_d = torch::empty({cap}, d.options());
+    out_d = torch::empty({cap}, OnDevice(d));
     if (g.e_ids.has_value()) e = g.e_ids.value();
   }
   int64_t nnz = 0;
@@ -436,8 +462,8 @@ class Graph : public torch::CustomClassHolder {
     Tensor out_data;
     auto gather = [&](const OptTensor& e_ids, const Tensor& select) {
       if (!data_.has_value()) return;
-      Tensor idx = e_ids.has_value() ? e_ids.value().index({select}) : select;
-      out_data = data_.value().index({idx});
+      Tensor idx = e_ids.has_value() ? Take(e_ids.value(), select) : select;
+      out_data = Take(data_.value(), idx);
     };
     if (on_format == kCOO) {
       Tensor nr, nc, sel;
@@ -517,7 +543,7 @@ class Graph : public torch::CustomClassHolder {
     const float* data_in = nullptr;
     float* data_out = nullptr;
     if (data_.has_value()) {
-      out_data = torch::empty({nnz}, data_.value().options());
+      out_data = torch::empty({nnz}, OnDevice(data_.value()));
       data_in = FP(data_.value());
       data_out = nnz ? out_data.data_ptr<float>() : nullptr;
     }
@@ -559,7 +585,7 @@ class Graph : public torch::CustomClassHolder {
     const float* data_in = nullptr;
     float* data_out = nullptr;
     if (data_.has_value()) {
-      out_data = torch::empty({D}, data_.value().options());
+      out_data = torch::empty({D}, OnDevice(data_.value()));
       data_in = FP(data_.value());
       data_out = D ? out_data.data_ptr<float>() : nullptr;
     }
@@ -697,7 +723,7 @@ class Graph : public torch::CustomClassHolder {
       ret->num_edges_ = S;
       if (data_.has_value()) {
         Tensor safe = select.clamp_min(0);
-        ret->data_ = data_.value().index({csc_->e_ids.has_value() ? csc_->e_ids.value().index({safe}) : safe});
+        ret->data_ = Take(data_.value(), csc_->e_ids.has_value() ? Take(csc_->e_ids.value(), safe) : safe);
       }
       return ret;
     }
@@ -900,9 +926,9 @@ class Graph : public torch::CustomClassHolder {
 
  private:
   torch::Device Device() const {
-    if (csc_) return csc_->indptr.device();
-    if (csr_) return csr_->indptr.device();
-    return coo_->row.device();
+    if (csc_) return DeviceOf(csc_->indptr);
+    if (csr_) return DeviceOf(csr_->indptr);
+    return DeviceOf(coo_->row);
   }
   Tensor DataOrOnes() {
     return data_.has_value() ? data_.value()

@@ -101,8 +101,8 @@ class Graph:
     def _device(self):
         for f in (self.csc_, self.csr_):
             if f is not None:
-                return f.indptr.device
-        return self.coo_.row.device
+                return ops.cuda_device_of(f.indptr)
+        return ops.cuda_device_of(self.coo_.row)
 
     def _data_or_ones(self):
         if self.data_ is not None:
@@ -293,7 +293,7 @@ class Graph:
                                                                        with_coo)
                 new_val_cols = self.val_col_ids_
                 if data is not None:
-                    out_data = data[e_ids[select] if e_ids is not None else select]
+                    out_data = ops.take(data, ops.take(e_ids, select) if e_ids is not None else select)
             if output_format & _CSC:
                 csc_ptr = CSC(indptr, indices)
             if output_format & _COO:
@@ -310,7 +310,7 @@ class Graph:
                                                                        with_coo)
                 new_val_rows = self.val_row_ids_
                 if data is not None:
-                    out_data = data[e_ids[select] if e_ids is not None else select]
+                    out_data = ops.take(data, ops.take(e_ids, select) if e_ids is not None else select)
             else:
                 if self.val_row_ids_ is not None:
                     r = self._compact_col_slicing(self.csr_, self.val_row_ids_, n_ids, with_coo, data, e_ids)
@@ -420,7 +420,7 @@ class Graph:
         n = self.csc_.indptr.numel() - 1
         split_size = int(split_size)
         bounds = list(range(0, n, split_size)) + [n]
-        offsets = torch.tensor(bounds, dtype=torch.int64, device=self.csc_.indptr.device)
+        offsets = torch.tensor(bounds, dtype=torch.int64, device=ops.cuda_device_of(self.csc_.indptr))
         indptrs = ops.indptr_split_by_offset(self.csc_.indptr, offsets)
         edge_bounds = self.csc_.indptr[offsets]
         indices = ops.split_by_offset(self.csc_.indices, edge_bounds)
@@ -493,7 +493,7 @@ class Graph:
             out_data = None
             if data is not None:
                 safe = select.clamp(min=0)
-                out_data = data[e_ids[safe] if e_ids is not None else safe]
+                out_data = ops.take(data, ops.take(e_ids, safe) if e_ids is not None else safe)
         else:
             r = ops.fused_csc_col_slicing_sampling(csc.indptr, csc.indices, column_index, fanout, replace, seed=seed,
                                                    data=data, e_ids=e_ids)
@@ -834,7 +834,7 @@ class _GsOps:
     def __getattr__(self, name):
         table = _batch_ops()
         table.update({"_CAPI_ListSampling": ListSampling, "_CAPI_ListSamplingWithProbs": ListSamplingProbs,
-                      "_CAPI_Unique": Unique, "list_sampling": ListSampling,
+                      "_CAPI_Unique": Unique, "_CAPI_SetSeed": ops.set_seed, "list_sampling": ListSampling,
                       "list_sampling_with_probs": ListSamplingProbs})
         for key in (name, "_CAPI_" + name):
             if key in table:

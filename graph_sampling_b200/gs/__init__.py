@@ -3,17 +3,18 @@
 `gs.utils.SeedGenerator`; `gs.gs_ops` stands in for `torch.ops.gs_ops` (list sampling and the super-batch operators).  Import as `import graph_sampling_b200.gs as gs`.
 
 `gs.jit.compile` traces a function written against `Matrix` and rewrites it onto the fused operators.
-`HeteroMatrix` and the DGL block builders of the reference are framework glue and are not provided;
-`Matrix.to_block` returns a plain DGL-free block description instead of a DGL object.
+`gs.HeteroMatrix` wraps `HeteroGraph` as the reference's does.  `Matrix.to_block` and
+`gs.utils.create_block_from_{csc,coo}` return a plain DGL-free `Block`; with DGL importable the two
+builders hand the same fields to DGL as the reference does.
 """
 from ..graph import Graph, HeteroGraph, ListSampling, ListSamplingProbs, Unique, gs_ops, _COO, _CSC, _CSR, _DCSC, _DCSR
 from ..ops import set_seed
 from . import ops, utils
-from .matrix import Block, Matrix
+from .matrix import Block, HeteroMatrix, Matrix
 from . import jit
 
 list_sampling = ListSampling
 list_sampling_with_probs = ListSamplingProbs
 
-__all__ = ["Graph", "HeteroGraph", "Matrix", "Block", "ops", "utils", "jit", "gs_ops", "set_seed", "list_sampling", "list_sampling_with_probs",
+__all__ = ["Graph", "HeteroGraph", "Matrix", "HeteroMatrix", "Block", "ops", "utils", "jit", "gs_ops", "set_seed", "list_sampling", "list_sampling_with_probs",
            "ListSampling", "ListSamplingProbs", "Unique", "_COO", "_CSC", "_CSR", "_DCSC", "_DCSR"]

@@ -20,7 +20,7 @@ class Block:
     tensor2: torch.Tensor
     num_src: int
     num_dst: int
-    src_ids: torch.Tensor
+    src_ids: Optional[torch.Tensor]
     edge_ids: Optional[torch.Tensor]
     edge_weight: Optional[torch.Tensor]
 
@@ -102,3 +102,33 @@ class Matrix:
     def relabel(self):
         self._graph._CAPI_relabel()
         return self
+
+
+class HeteroMatrix:
+    """Named relations over `HeteroGraph`, method for method the reference's gs.HeteroMatrix
+    (python/gs/matrix_api/hetero_matrix.py:5-30), bound to the registered
+    `_CAPI_*` method names (src/pybind.cc:54-59)."""
+
+    def __init__(self, hetero_graph=None):
+        from ..graph import HeteroGraph
+        self._hetero_graph = hetero_graph if hetero_graph is not None else HeteroGraph()
+
+    def load_from_homo(self, node_types, edge_types, homo_matrices):
+        self._hetero_graph._CAPI_LoadFromHomo(node_types, edge_types, [m._graph for m in homo_matrices])
+
+    def get_homo_matrix(self, etype: str) -> Matrix:
+        return Matrix(self._hetero_graph._CAPI_GetHomoGraph(etype))
+
+    def metapath_random_walk(self, seeds, metapath):
+        """One fused slice + 1-neighbour sample per relation, trace stacked step-major [len(metapath) + 1,
+        num_seeds].  Every walker needs a neighbour at every step: an empty column yields no row, so
+        the steps would differ in length (the fused walk carries -1 instead)."""
+        ret = [seeds]
+        for etype in metapath:
+            sub = self.get_homo_matrix(etype).fused_columnwise_slicing_sampling(seeds, 1, True)
+            seeds = sub.row_indices()
+            ret.append(seeds)
+        return torch.stack(ret)
+
+    def metapath_random_walk_fused(self, seeds, metapath):
+        return self._hetero_graph._CAPI_MetapathRandomWalkFused(seeds, metapath)

@@ -1,6 +1,33 @@
 """Seed batching helper with the semantics of the reference's SeedGenerator
-(python/gs/utils/dataloader.py:4-44)."""
+(python/gs/utils/dataloader.py:4-44) and the block builders of python/gs/utils/to_dgl_block.py:5-25."""
 import torch
+
+
+def create_block_from_csc(indptr, indices, e_ids, num_src, num_dst):
+    """Message-flow block over a relabelled CSC sample.  With DGL importable this is the reference's
+    DGLBlock (python/gs/utils/to_dgl_block.py:5-17); without it, the same fields as a plain `Block`."""
+    try:
+        import dgl
+        from dgl.heterograph import DGLBlock
+    except ImportError:
+        from .matrix import Block
+        return Block("csc", indptr, indices, int(num_src), int(num_dst), None, e_ids, None)
+    hgidx = dgl.heterograph_index.create_unitgraph_from_csr(
+        2, num_src, num_dst, indptr, indices, e_ids, formats=["coo", "csr", "csc"], transpose=True)
+    return DGLBlock(hgidx, (["_N"], ["_N"]), ["_E"])
+
+
+def create_block_from_coo(row, col, num_src, num_dst):
+    """As `create_block_from_csc` for a relabelled COO sample (python/gs/utils/to_dgl_block.py:20-25)."""
+    try:
+        import dgl
+        from dgl.heterograph import DGLBlock
+    except ImportError:
+        from .matrix import Block
+        return Block("coo", row, col, int(num_src), int(num_dst), None, None, None)
+    hgidx = dgl.heterograph_index.create_unitgraph_from_coo(
+        2, num_src, num_dst, row, col, formats=["coo", "csr", "csc"])
+    return DGLBlock(hgidx, (["_N"], ["_N"]), ["_E"])
 
 
 class SeedGenerator:

@@ -99,6 +99,8 @@ class Context:
 
 
 def default_context(device=None):
+    if device is not None and torch.device(device).type != "cuda":       # a pinned host tensor's device
+        device = None
     idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
     ctx = _contexts.get(idx)
     if ctx is None:
@@ -111,14 +113,31 @@ def _stream():
     return c_vp(torch.cuda.current_stream().cuda_stream)
 
 
+def _resident(t):
+    """Memory a kernel can read in place: device memory, or pinned host memory through the unified address
+    space (the reference accepts pinned graph arrays the same way: src/graph_ops.cc:144,226)."""
+    return t.is_cuda or t.is_pinned()
+
+
+def _contiguous(t, name):
+    if not t.is_cuda:
+        raise TypeError(f"{name}: a pinned host tensor must be contiguous")
+    return t.contiguous()
+
+
+def cuda_device_of(t):
+    """Where results derived from `t` are allocated: its own device, or the current one for pinned host memory."""
+    return t.device if t.is_cuda else torch.device("cuda", torch.cuda.current_device())
+
+
 def _i64(t, name, allow_none=False):
     if t is None:
         if allow_none:
             return None
         raise TypeError(f"{name} is required")
-    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.int64):
-        raise TypeError(f"{name} must be an int64 CUDA tensor")
-    return t if t.is_contiguous() else t.contiguous()
+    if not (isinstance(t, torch.Tensor) and _resident(t) and t.dtype == torch.int64):
+        raise TypeError(f"{name} must be an int64 CUDA (or pinned host) tensor")
+    return t if t.is_contiguous() else _contiguous(t, name)
 
 
 def _f32(t, name, allow_none=False):
@@ -126,9 +145,9 @@ def _f32(t, name, allow_none=False):
         if allow_none:
             return None
         raise TypeError(f"{name} is required")
-    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32):
-        raise TypeError(f"{name} must be a float32 CUDA tensor")
-    return t if t.is_contiguous() else t.contiguous()
+    if not (isinstance(t, torch.Tensor) and _resident(t) and t.dtype == torch.float32):
+        raise TypeError(f"{name} must be a float32 CUDA (or pinned host) tensor")
+    return t if t.is_contiguous() else _contiguous(t, name)
 
 
 def _p(t):
@@ -136,7 +155,7 @@ def _p(t):
 
 
 def _empty(n, like, dtype=torch.int64):
-    return torch.empty(int(n), dtype=dtype, device=like.device)
+    return torch.empty(int(n), dtype=dtype, device=cuda_device_of(like))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -345,6 +364,16 @@ def gather_rows(src, index, ctx=None):
 
 
 index_select_cpu_from_gpu = gather_rows
+
+
+def take(src, index):
+    """src[index] for a per-edge array (float32 edge data, int64 edge ids) that lives on the GPU or in pinned host
+    memory, where the GPU reads it in place (src/graph.cc:296-306 does the same through IndexSelectCPUFromGPU)."""
+    if src.is_cuda:
+        return src[index]
+    if src.dtype == torch.int64:                         # copied as rows of two 32-bit words
+        return gather_rows(src.view(torch.float32).view(-1, 2), index).view(torch.int64).view(-1)
+    return gather_rows(src, index)
 
 
 def index_search(origin_data, keys, ctx=None):
@@ -820,8 +849,8 @@ class OutputArena:
     def get(self, key, n, like, dtype=torch.int64):
         n = int(n)
         buf = self._buffers.get(key)
-        if buf is None or buf.numel() < n or buf.device != like.device or buf.dtype != dtype:
-            buf = torch.empty(max(16, n + n // 4), dtype=dtype, device=like.device)
+        if buf is None or buf.numel() < n or buf.device != cuda_device_of(like) or buf.dtype != dtype:
+            buf = torch.empty(max(16, n + n // 4), dtype=dtype, device=cuda_device_of(like))
             self._buffers[key] = buf
         return buf[:n]
 

@@ -188,6 +188,26 @@ def test_fixture_replay_metapath(face, fx):
     assert hg._CAPI_GetHomoGraph("view")._CAPI_GetNumEdges() == 3
 
 
+def test_hetero_matrix_and_block_builders():
+    import graph_sampling_b200.gs as gs
+    follow = gs.Matrix().load_csc(dev(np.array([0, 1, 2, 3, 4])), dev(np.array([1, 2, 3, 0])))     # a 4-cycle
+    view = gs.Matrix().load_csc(dev(np.array([0, 1, 2, 3, 4])), dev(np.array([3, 2, 1, 0])))       # a reversal
+    hm = gs.HeteroMatrix()
+    hm.load_from_homo(["user", "item"], [("user", "follow", "user"), ("user", "view", "item")], [follow, view])
+    seeds, path = dev(np.array([0, 2, 3])), ["follow", "view", "follow"]
+    stepwise = hm.metapath_random_walk(seeds, path)                    # every column has one neighbour: no randomness
+    assert host(stepwise).tolist() == [[0, 2, 3], [1, 3, 0], [2, 0, 3], [3, 1, 0]]
+    fused = hm.metapath_random_walk_fused(seeds, path)
+    assert fused.shape == (3, 4) and same(fused.reshape(-1), host(stepwise).reshape(-1))
+    assert hm.get_homo_matrix("view").get_num_rows() == 4
+    sub = follow.fused_columnwise_slicing_sampling(seeds, 1, False)
+    blk = sub.to_block()
+    built = gs.utils.create_block_from_coo(blk.tensor1, blk.tensor2, blk.num_src, blk.num_dst) if blk.format == "coo" \
+        else gs.utils.create_block_from_csc(blk.tensor1, blk.tensor2, blk.edge_ids, blk.num_src, blk.num_dst)
+    assert (built.format, built.num_src, built.num_dst) == (blk.format, blk.num_src, blk.num_dst)
+    assert built.tensor1 is blk.tensor1 and built.tensor2 is blk.tensor2
+
+
 def test_col_row_slicing_repeated_ids_and_empty_inputs(ops, oracle, small_graph):
     indptr, indices = small_graph
     n = len(indptr) - 1
