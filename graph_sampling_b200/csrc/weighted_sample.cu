@@ -21,6 +21,7 @@
 
 namespace gsb {
 
+using u32 = uint32_t;
 constexpr int kWThreads = 256;
 constexpr int kWTileCols = 64;  // 8 warps x 8 columns each
 
@@ -47,7 +48,12 @@ struct WeightedParams {
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 
-__device__ __forceinline__ bool ranks_before(float ka, i64 ia, float kb, i64 ib) {
+// A list entry / candidate is (key, edge position inside its column).  Positions are 32-bit: a column of more than
+// kMaxScanEnd edges is refused by the kernel (kNoIdx marks an empty entry and ranks after every real position).
+constexpr u32 kNoIdx = 0xffffffffu;
+constexpr u32 kMaxScanEnd = 0xffffff00u;
+
+__device__ __forceinline__ bool ranks_before(float ka, u32 ia, float kb, u32 ib) {
   return ka > kb || (ka == kb && ia < ib);
 }
 
@@ -58,22 +64,26 @@ __device__ __forceinline__ void emit_weighted(const WeightedParams& p, i64 out_p
   if (p.out_data) p.out_data[out_pos] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
 }
 
-// Warp-collective: every lane offers one candidate (key, edge position); the running top-k list (lane j holds
-// the j-th best, empty entries rank last) absorbs the candidates that beat its k-th entry, one at a time.
-__device__ __forceinline__ void topk_offer(float ck, i64 ci, bool valid, int k, unsigned kmask, float& my_key,
-                                           i64& my_idx, float& thr_key, i64& thr_idx) {
-  bool want = valid && ranks_before(ck, ci, thr_key, thr_idx);
+// Warp-collective: every lane offers one candidate; the running top-k list (lane j holds the j-th best, empty
+// entries rank last) absorbs the candidates that beat its k-th entry, one at a time.  The warp's shuffle unit is
+// what bounds this kernel, so an insertion costs four shuffles (candidate key + position, shift of key + position):
+// whether a queued candidate still makes the list is read off its insertion rank, and the k-th entry is broadcast
+// once per call, not once per insertion.
+__device__ __forceinline__ void topk_offer(float ck, u32 ci, bool valid, int k, unsigned kmask, float& my_key,
+                                           u32& my_idx, float& thr_key, u32& thr_idx) {
+  const bool want = valid && ranks_before(ck, ci, thr_key, thr_idx);
   unsigned pending = __ballot_sync(0xffffffffu, want);
+  if (!pending) return;
   while (pending) {
     const int src = __ffs(pending) - 1;
     pending &= pending - 1;
     const float nk = __shfl_sync(0xffffffffu, ck, src);
-    const i64 ni = __shfl_sync(0xffffffffu, ci, src);
-    if (!ranks_before(nk, ni, thr_key, thr_idx)) continue;  // the threshold has moved past it
+    const u32 ni = __shfl_sync(0xffffffffu, ci, src);
     const bool mine_first = ranks_before(my_key, my_idx, nk, ni);
     const int pos = __popc(__ballot_sync(0xffffffffu, mine_first) & kmask);
+    if (pos >= k) continue;  // k entries rank before it by now
     const float up_key = __shfl_up_sync(0xffffffffu, my_key, 1);
-    const i64 up_idx = __shfl_up_sync(0xffffffffu, my_idx, 1);
+    const u32 up_idx = __shfl_up_sync(0xffffffffu, my_idx, 1);
     if (lane_id() > pos) {
       my_key = up_key;
       my_idx = up_idx;
@@ -81,28 +91,27 @@ __device__ __forceinline__ void topk_offer(float ck, i64 ci, bool valid, int k, 
       my_key = nk;
       my_idx = ni;
     }
-    thr_key = __shfl_sync(0xffffffffu, my_key, k - 1);
-    thr_idx = __shfl_sync(0xffffffffu, my_idx, k - 1);
   }
+  thr_key = __shfl_sync(0xffffffffu, my_key, k - 1);
+  thr_idx = __shfl_sync(0xffffffffu, my_idx, k - 1);
 }
 
 // Warp-collective: the first 32 candidates of a column.  The list is empty, so every one of them would be inserted
 // one at a time; a bitonic sort of the 32 (key, position) pairs across the lanes (15 exchange steps) builds the
 // same list directly.  (key, position) is a total order — positions are distinct — so the result does not depend
 // on how it was reached.
-__device__ __forceinline__ void topk_init(float ck, i64 ci, bool valid, int k, float& my_key, i64& my_idx,
-                                          float& thr_key, i64& thr_idx) {
+__device__ __forceinline__ void topk_init(float ck, u32 ci, bool valid, int k, float& my_key, u32& my_idx,
+                                          float& thr_key, u32& thr_idx) {
   const float neg_inf = __uint_as_float(0xFF800000u);
-  const i64 no_idx = 0x7fffffffffffffffll;
   my_key = valid ? ck : neg_inf;
-  my_idx = valid ? ci : no_idx;
+  my_idx = valid ? ci : kNoIdx;
   const int lane = lane_id();
 #pragma unroll
   for (int size = 2; size <= 32; size <<= 1) {
 #pragma unroll
     for (int j = size >> 1; j > 0; j >>= 1) {
       const float ok = __shfl_xor_sync(0xffffffffu, my_key, j);
-      const i64 oi = __shfl_xor_sync(0xffffffffu, my_idx, j);
+      const u32 oi = __shfl_xor_sync(0xffffffffu, my_idx, j);
       const bool descending = (lane & size) == 0;   // direction of this lane's block (the last pass: all descending)
       const bool lower = (lane & j) == 0;
       const bool mine_first = ranks_before(my_key, my_idx, ok, oi);
@@ -116,35 +125,62 @@ __device__ __forceinline__ void topk_init(float ck, i64 ci, bool valid, int k, f
   }
   if (lane >= k) {
     my_key = neg_inf;
-    my_idx = no_idx;
+    my_idx = kNoIdx;
   }
   thr_key = __shfl_sync(0xffffffffu, my_key, k - 1);
   thr_idx = __shfl_sync(0xffffffffu, my_idx, k - 1);
 }
 
-// Top-k of the edges [e_begin, e_end) of one column, scanned by one warp.
-__device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, i64 b, i64 e_begin, i64 e_end, int k,
-                                          unsigned kmask, float& my_key, i64& my_idx) {
+// The ranking key of an edge, or -inf when the key surely ranks after `thr_key` (the list's current k-th key; -inf
+// while the list is not full, which rejects nothing).  Once a long column has filled its list almost every edge
+// fails, and this test spares it the logarithm and the division: log2(u) <= (u - 1)·log2(e) for every u in (0, 1],
+// so key = log2(u) / w <= (u - 1)·log2(e) / w.  The two 1e-4 margins (the bound is pulled towards zero, the
+// threshold pushed away from it) are far wider than the rounding of the key's own arithmetic (< 1e-6 relative), so a
+// key that would tie with or beat thr_key is always evaluated exactly and results do not depend on this shortcut.
+__device__ __forceinline__ float ares_key_if_above(uint32_t r, float w, float thr_key) {
+  const float neg_inf = __uint_as_float(0xFF800000u);
+  if (!(w > 0.0f)) return neg_inf;
+  const float bound = (uniform01(r) - 1.0f) * (1.44269504f * 0.9999f);
+  const float limit = thr_key * w * 1.0001f;
+  if (bound < limit) return neg_inf;
+  return ares_key(r, w);
+}
+
+// Top-k of the edges [e_begin, e_end) of one column (e_begin a multiple of 4, e_end <= kMaxScanEnd), scanned by one
+// warp, 128 edges per iteration.  Keys: a lane evaluates ONE Philox block and uses its four words for four
+// consecutive edges (edge e draws word e & 3 of block e >> 2).  Candidates: the keys are then transposed through
+// `s_keys` (128 floats owned by the warp) so that each offer round holds 32 CONSECUTIVE edges — the first round of a
+// column fills the list from 32 real candidates by the sorting network, and what later rounds insert one at a time
+// is only the few that still beat the k-th entry (about k·ln(d/32) for a column of d edges).
+__device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, i64 b, u32 e_begin, u32 e_end, int k,
+                                          unsigned kmask, float* s_keys, float& my_key, u32& my_idx) {
   const float neg_inf = __uint_as_float(0xFF800000u);
   my_key = neg_inf;
-  my_idx = 0x7fffffffffffffffll;
+  my_idx = kNoIdx;
   float thr_key = neg_inf;
-  i64 thr_idx = 0x7fffffffffffffffll;
-  // 128 edges per iteration: a lane evaluates ONE Philox block and uses its four words for four consecutive
-  // edges (edge e draws word e & 3 of block e >> 2), instead of four lanes computing the same block.
-  const i64 first_block = e_begin >> 2;
+  u32 thr_idx = kNoIdx;
+  const u32 lane = (u32)lane_id();
+  const float* probs = p.probs + b;
   bool empty_list = true;
-  for (i64 blk0 = first_block; (blk0 << 2) < e_end; blk0 += 32) {
-    const i64 blk = blk0 + lane_id();
-    const i64 e4 = blk << 2;
-    U32x4 r;
-    if (e4 < e_end) r = rand_block(p.seed, (u64)col_pos, (u64)blk, STREAM_WEIGHTED);
+  for (u32 e0 = e_begin; e0 < e_end; e0 += 128) {  // e_end <= kMaxScanEnd: e0 + 128 does not wrap
+    const u32 e4 = e0 + 4 * lane;
+    float4 kq = make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
+    if (e4 < e_end) {
+      const U32x4 r = rand_block(p.seed, (u64)col_pos, (u64)(e4 >> 2), STREAM_WEIGHTED);
+      kq.x = ares_key_if_above(r.v[0], __ldg(probs + e4), thr_key);
+      if (e4 + 1 < e_end) kq.y = ares_key_if_above(r.v[1], __ldg(probs + e4 + 1), thr_key);
+      if (e4 + 2 < e_end) kq.z = ares_key_if_above(r.v[2], __ldg(probs + e4 + 2), thr_key);
+      if (e4 + 3 < e_end) kq.w = ares_key_if_above(r.v[3], __ldg(probs + e4 + 3), thr_key);
+    }
+    __syncwarp();  // the previous iteration's reads are done
+    reinterpret_cast<float4*>(s_keys)[lane] = kq;
+    __syncwarp();
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const i64 e = e4 + q;
-      const bool valid = e >= e_begin && e < e_end;
-      float ck = neg_inf;
-      if (valid) ck = ares_key(r.v[q], __ldg(p.probs + b + e));
+    for (u32 q = 0; q < 4; ++q) {
+      if (e0 + 32 * q >= e_end) break;  // uniform across the warp
+      const u32 e = e0 + 32 * q + lane;
+      const bool valid = e < e_end;
+      const float ck = s_keys[32 * q + lane];
       if (empty_list) {
         topk_init(ck, e, valid, k, my_key, my_idx, thr_key, thr_idx);
         empty_list = false;
@@ -166,6 +202,7 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
   __shared__ i64 s_scan[33];
   __shared__ i64 s_base;
   __shared__ int s_next;  // next column of the tile that no warp has taken yet
+  __shared__ __align__(16) float s_keys[kWThreads / 32][128];
   const int tile = blockIdx.x, tid = threadIdx.x;
   const i64 S = p.S, k = p.k;
   const i64 base = (i64)tile * kWTileCols;
@@ -174,14 +211,17 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
   const int ncol = (int)max((i64)0, min((i64)kWTileCols, S - base));
 
   i64 f = 0;
+  bool is_long = false;
   if (tid < ncol) {
     const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
     const i64 b = p.indptr[col];
     const i64 d = p.indptr[col + 1] - b;
     f = p.replace ? (d > 0 ? k : 0) : (d < k ? d : k);
+    is_long = !p.replace && d > kLongColumn && d > k;
     s_in[tid] = b;
     s_deg[tid] = d;
   }
+  const int any_long = __syncthreads_or(is_long);  // does the tile hold a column that the whole CTA scans?
   i64 total;
   const i64 excl = block_exclusive_scan<kWThreads>(f, s_scan, &total);
   if (tid < kWTileCols) s_off[tid] = excl;
@@ -242,34 +282,38 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
     }
     if (d > kLongColumn) continue;  // handled by the whole CTA below
     float my_key;
-    i64 my_idx;
-    topk_scan(p, col_pos, b, 0, d, (int)k, kmask, my_key, my_idx);
-    if (lane < k) emit_weighted(p, o + lane, b + my_idx, col_pos);
+    u32 my_idx;
+    topk_scan(p, col_pos, b, 0u, (u32)d, (int)k, kmask, s_keys[warp], my_key, my_idx);
+    if (lane < k) emit_weighted(p, o + lane, b + (i64)my_idx, col_pos);
   }
 
-  if (p.replace) return;
+  if (!any_long) return;
   // long columns: every warp scans a slice, warp 0 merges the per-warp lists
   __shared__ float s_key[kWarps][32];
-  __shared__ i64 s_idx[kWarps][32];
+  __shared__ u32 s_idx[kWarps][32];
   for (int c = 0; c < ncol; ++c) {
     const i64 d = s_deg[c];
     if (d <= kLongColumn || d <= k) continue;  // uniform across the CTA
+    if (d > (i64)kMaxScanEnd) {                // positions inside a column are 32-bit here
+      if (tid == 0) raise_error(p.counters, GSB_ERR_UNSUPPORTED, d);
+      continue;
+    }
     const i64 b = s_in[c], o = tile_base + s_off[c], col_pos = base + c;
     const i64 chunk = (((d + kWarps - 1) / kWarps) + 31) & ~(i64)31;
     const i64 e_begin = min(d, (i64)warp * chunk), e_end = min(d, (i64)(warp + 1) * chunk);
     float my_key;
-    i64 my_idx;
-    topk_scan(p, col_pos, b, e_begin, e_end, (int)k, kmask, my_key, my_idx);
+    u32 my_idx;
+    topk_scan(p, col_pos, b, (u32)e_begin, (u32)e_end, (int)k, kmask, s_keys[warp], my_key, my_idx);
     s_key[warp][lane] = my_key;
     s_idx[warp][lane] = my_idx;
     __syncthreads();
     if (warp == 0) {
       float thr_key = __shfl_sync(0xffffffffu, my_key, (int)k - 1);
-      i64 thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
+      u32 thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
       for (int w = 1; w < kWarps; ++w)
-        topk_offer(s_key[w][lane], s_idx[w][lane], lane < k && s_idx[w][lane] != 0x7fffffffffffffffll, (int)k, kmask,
-                   my_key, my_idx, thr_key, thr_idx);
-      if (lane < k) emit_weighted(p, o + lane, b + my_idx, col_pos);
+        topk_offer(s_key[w][lane], s_idx[w][lane], lane < k && s_idx[w][lane] != kNoIdx, (int)k, kmask, my_key, my_idx,
+                   thr_key, thr_idx);
+      if (lane < k) emit_weighted(p, o + lane, b + (i64)my_idx, col_pos);
     }
     __syncthreads();
   }

@@ -164,7 +164,9 @@ GSB_API int gsb_random_walk(gsb_ctx* ctx, void* stream, const int64_t* indptr, c
  * descending key order; weights <= 0 rank below every positive weight.  With replacement: k
  * inverse-CDF draws over max(w, 0).  seeds == NULL samples all S columns of the operand; seeds
  * given fuses the column slice (no reference counterpart for the fused form).  Buffers, counts
- * and optional outputs as in gsb_sample_uniform.
+ * and optional outputs as in gsb_sample_uniform.  Without replacement a column may hold at most
+ * 2^32 - 256 edges (positions inside a column are kept in 32 bits); a longer one records
+ * GSB_ERR_UNSUPPORTED.
  */
 GSB_API int gsb_sample_weighted(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
                                 const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
