@@ -246,6 +246,39 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
   const unsigned kmask = k >= 32 ? 0xffffffffu : ((1u << (int)k) - 1u);
   const float neg_inf = __uint_as_float(0xFF800000u);
 
+  // Long columns first: every warp scans a slice, warp 0 merges the per-warp lists.  All warps are still in step
+  // here, so nobody waits at the barriers for a warp that is busy with a column of its own.
+  if (any_long) {
+    __shared__ float s_key[kWarps][32];
+    __shared__ u32 s_idx[kWarps][32];
+    for (int c = 0; c < ncol; ++c) {
+      const i64 d = s_deg[c];
+      if (d <= kLongColumn || d <= k) continue;  // uniform across the CTA
+      if (d > (i64)kMaxScanEnd) {                // positions inside a column are 32-bit here
+        if (tid == 0) raise_error(p.counters, GSB_ERR_UNSUPPORTED, d);
+        continue;
+      }
+      const i64 b = s_in[c], o = tile_base + s_off[c], col_pos = base + c;
+      const i64 chunk = (((d + kWarps - 1) / kWarps) + 31) & ~(i64)31;
+      const i64 e_begin = min(d, (i64)warp * chunk), e_end = min(d, (i64)(warp + 1) * chunk);
+      float my_key;
+      u32 my_idx;
+      topk_scan(p, col_pos, b, (u32)e_begin, (u32)e_end, (int)k, kmask, s_keys[warp], my_key, my_idx);
+      s_key[warp][lane] = my_key;
+      s_idx[warp][lane] = my_idx;
+      __syncthreads();
+      if (warp == 0) {
+        float thr_key = __shfl_sync(0xffffffffu, my_key, (int)k - 1);
+        u32 thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
+        for (int w = 1; w < kWarps; ++w)
+          topk_offer(s_key[w][lane], s_idx[w][lane], lane < k && s_idx[w][lane] != kNoIdx, (int)k, kmask, my_key, my_idx,
+                     thr_key, thr_idx);
+        if (lane < k) emit_weighted(p, o + lane, b + (i64)my_idx, col_pos);
+      }
+      __syncthreads();
+    }
+  }
+
   // warps take columns as they become free: degrees inside a tile differ by orders of magnitude
   for (;;) {
     int c = 0;
@@ -285,37 +318,6 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
     u32 my_idx;
     topk_scan(p, col_pos, b, 0u, (u32)d, (int)k, kmask, s_keys[warp], my_key, my_idx);
     if (lane < k) emit_weighted(p, o + lane, b + (i64)my_idx, col_pos);
-  }
-
-  if (!any_long) return;
-  // long columns: every warp scans a slice, warp 0 merges the per-warp lists
-  __shared__ float s_key[kWarps][32];
-  __shared__ u32 s_idx[kWarps][32];
-  for (int c = 0; c < ncol; ++c) {
-    const i64 d = s_deg[c];
-    if (d <= kLongColumn || d <= k) continue;  // uniform across the CTA
-    if (d > (i64)kMaxScanEnd) {                // positions inside a column are 32-bit here
-      if (tid == 0) raise_error(p.counters, GSB_ERR_UNSUPPORTED, d);
-      continue;
-    }
-    const i64 b = s_in[c], o = tile_base + s_off[c], col_pos = base + c;
-    const i64 chunk = (((d + kWarps - 1) / kWarps) + 31) & ~(i64)31;
-    const i64 e_begin = min(d, (i64)warp * chunk), e_end = min(d, (i64)(warp + 1) * chunk);
-    float my_key;
-    u32 my_idx;
-    topk_scan(p, col_pos, b, (u32)e_begin, (u32)e_end, (int)k, kmask, s_keys[warp], my_key, my_idx);
-    s_key[warp][lane] = my_key;
-    s_idx[warp][lane] = my_idx;
-    __syncthreads();
-    if (warp == 0) {
-      float thr_key = __shfl_sync(0xffffffffu, my_key, (int)k - 1);
-      u32 thr_idx = __shfl_sync(0xffffffffu, my_idx, (int)k - 1);
-      for (int w = 1; w < kWarps; ++w)
-        topk_offer(s_key[w][lane], s_idx[w][lane], lane < k && s_idx[w][lane] != kNoIdx, (int)k, kmask, my_key, my_idx,
-                   thr_key, thr_idx);
-      if (lane < k) emit_weighted(p, o + lane, b + (i64)my_idx, col_pos);
-    }
-    __syncthreads();
   }
 }
 
