@@ -55,8 +55,12 @@ def parse():
     ap.add_argument("--face", default="python", choices=["python", "torchscript"],
                     help="with --group 1: drive the per-batch Graph API through the Python mirror or through the "
                          "TorchScript library (lib/libgs.so)")
-    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels"],
-                    help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale configuration)")
+    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels", "ladies", "adaptive"],
+                    help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale "
+                         "configuration); ladies = layer-wise importance sampling (1 M nodes / 50 M weighted edges); adaptive = "
+                         "SDDMM score -> per-column softmax -> weighted sampling on the products-scale graph; both of the "
+                         "latter run the same TorchScript call sequence on our library or, with --impl reference, on the "
+                         "reference's")
     ap.add_argument("--walkers", type=int, default=10_000_000)
     ap.add_argument("--walk-length", type=int, default=80)
     ap.add_argument("--walk-nodes", type=int, default=111_000_000)
@@ -565,6 +569,136 @@ def run_walk(args):
         dist.destroy_process_group()
 
 
+def _load_face(impl):
+    """torch.classes.gs_classes.Graph and torch.ops.gs_ops of our TorchScript library or of the reference's."""
+    import torch
+    if impl == "reference":
+        torch.classes.load_library(os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so"))
+    else:
+        from graph_sampling_b200 import build as gsb_build
+        torch.classes.load_library(gsb_build.build_glue())
+    return torch.classes.gs_classes.Graph, torch.ops.gs_ops
+
+
+_COO, _CSC, _CSR = 1, 2, 4
+
+
+def ladies_batch(torch, gs_ops, P, seeds, fanouts):
+    """examples/ladies/train_minibatch.py:43-59 spelled with the registered methods that gs.Matrix forwards to
+    (python/gs/matrix_api/matrix.py:66-105): column slice, row probability = sum of squared weights, weighted list
+    sampling, row slice, divide, normalise, frontier + relabel.  Returns the edges of the layer blocks."""
+    edges = 0
+    for fanout in fanouts:
+        U = P._CAPI_Slicing(seeds, 0, _CSC, _COO, False)
+        prob = U._CAPI_Sum(1, 2, _CSR)
+        selected, _ = gs_ops._CAPI_ListSamplingWithProbs(U._CAPI_GetRows(), prob, fanout, False)
+        nodes = torch.cat((seeds, selected)).unique()
+        subU = U._CAPI_Slicing(nodes, 1, _CSR, _COO, False)
+        subU = subU._CAPI_Divide(prob[nodes], 1, _COO)._CAPI_Normalize(0, _CSC)
+        seeds = subU._CAPI_AllValidNode()
+        subU._CAPI_Relabel()
+        edges += int(subU._CAPI_GetNumEdges())
+    return edges
+
+
+def adaptive_batch(torch, gs_ops, A, X, seeds, fanouts):
+    """Adaptive sampling hop by hop: column slice, edge score <x_src, x_dst> / 16 by SDDMM, per-column softmax,
+    weighted sampling without replacement, frontier + relabel.  Returns the sampled edges."""
+    edges = 0
+    for fanout in fanouts:
+        sub = A._CAPI_Slicing(seeds, 0, _CSC, _COO, False)
+        score = torch.zeros(int(sub._CAPI_GetNumEdges()), 1, dtype=torch.float32, device=seeds.device)
+        sub._CAPI_SDDMM("dot", X, X[seeds], score, 0, 2, _COO)
+        sub._CAPI_SetData(torch.exp(score.squeeze(-1) / 16.0))
+        p = sub._CAPI_Normalize(0, _CSC)._CAPI_GetData("default")
+        sampled = sub._CAPI_SamplingWithProbs(0, p, fanout, False, _CSC, _CSC)
+        seeds = sampled._CAPI_AllValidNode()
+        sampled._CAPI_Relabel()
+        edges += int(sampled._CAPI_GetNumEdges())
+    return edges
+
+
+PIPELINES = {
+    "ladies": {"nodes": 1_000_000, "edges": 50_000_000, "batch": 512, "fanouts": [512, 512], "symmetric": False,
+               "text": "layer-wise importance sampling: per layer column-slice 512 seeds, row probability = sum of squared "
+                       "edge weights, 512 rows without replacement by that probability, row-slice, divide + normalise, "
+                       "relabel; 2 layers; R-MAT 1 M nodes / 50 M edges, fp32 weights ~ U(0, 1]",
+               "unit_text": "edges of the row-sliced layer blocks"},
+    "adaptive": {"nodes": NUM_NODES, "edges": NUM_EDGES, "batch": 2048, "fanouts": [10, 10], "symmetric": True,
+                 "text": "adaptive sampling on the products-scale graph, features fp32 [nodes x 256] ~ N(0, 1): per hop "
+                         "column-slice, SDDMM score <x_src, x_dst> / 16, per-column softmax, weighted sampling without "
+                         "replacement (fanout 10), relabel; 2 hops; 2 048 seeds per batch",
+                 "unit_text": "sampled edges"},
+}
+
+
+def run_pipeline(args):
+    """Secondary workloads: the two pipelines around weighted sampling, driven through the registered TorchScript
+    methods, so that `--impl reference` runs the very same Python loop on the reference's own CUDA library.  One GPU;
+    a step is one minibatch; seeds come from pinned host memory inside the timed region."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    import torch
+    from graph_sampling_b200.synthetic import rmat_csc, seed_batches
+    cfg = PIPELINES[args.workload]
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    Graph, gs_ops = _load_face(args.impl)
+    t0 = time.time()
+    kw = {"symmetric": True, "max_degree": MAX_DEGREE} if cfg["symmetric"] else {}
+    graph_seed = GRAPH_SEED if args.workload == "adaptive" else GRAPH_SEED + 3
+    indptr, indices = rmat_csc(cfg["nodes"], cfg["edges"], seed=graph_seed, device=device, **kw)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    n = cfg["nodes"]
+    info = {"nodes": n, "edges": int(indices.numel()), "gen_seconds": round(time.time() - t0, 2)}
+    gen = torch.Generator(device=device)
+    gen.manual_seed(GRAPH_SEED + 11)
+    G = Graph(False)
+    G._CAPI_LoadCSC(indptr, indices)
+    X = None
+    if args.workload == "ladies":
+        w = 1.0 - torch.rand(indices.numel(), generator=gen, device=device)  # (0, 1]
+        G._CAPI_SetData(w)
+    else:
+        X = torch.randn(n, 256, generator=gen, device=device)
+    steps, warmup = max(1, min(args.steps, 200)), max(3, min(args.warmup, 10))
+    batches = seed_batches(n, cfg["batch"], steps + warmup, seed=GRAPH_SEED + 12, device="cpu").pin_memory()
+
+    def fn(host_seeds):
+        seeds = host_seeds.to(device, non_blocking=True)
+        if args.workload == "ladies":
+            return ladies_batch(torch, gs_ops, G, seeds, cfg["fanouts"])
+        return adaptive_batch(torch, gs_ops, G, X, seeds, cfg["fanouts"])
+
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    for b in range(warmup):
+        fn(batches[b])
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    edges = 0
+    ev0.record()
+    for b in range(warmup, warmup + steps):
+        edges += fn(batches[b])
+    ev1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    seconds = ev0.elapsed_time(ev1) / 1e3
+    print(json.dumps({"metric": METRIC, "value": edges / seconds, "unit": UNIT, "n_gpus": 1, "steps": steps,
+                      "warmup": warmup, "ms_per_step": seconds / steps * 1e3, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "int64 ids, f32 weights", "data": "synthetic",
+                      "impl": args.impl,
+                      "config": {"workload": cfg["text"], "graph": info, "batch": cfg["batch"],
+                                 "fanouts": cfg["fanouts"], "counted": cfg["unit_text"],
+                                 "face": "TorchScript classes (same call sequence for both arms)",
+                                 "l2": "graph (and features) larger than L2, read at random"},
+                      "edges_per_step": edges / steps, "clocks": clocks,
+                      "e2e": {"value": edges / seconds, "unit": UNIT, "h2d_bytes_per_step": cfg["batch"] * 8,
+                              "d2h_bytes_per_step": 8 * len(cfg["fanouts"])}}))
+
+
 def run_kernels(args):
     """Per-operator throughput on the products-scale graph: every operator of the hot path once, at a size that
     fills the GPU, timed with CUDA events; achieved = algorithmic bytes / time against the measured HBM peak.
@@ -778,6 +912,8 @@ if __name__ == "__main__":
         run_kernels_reference(a) if a.impl == "reference" else run_kernels(a)
     elif a.workload == "walk":
         run_walk(a)
+    elif a.workload in ("ladies", "adaptive"):
+        run_pipeline(a)
     elif a.impl == "reference":
         run_reference(a)
     else:

@@ -23,7 +23,10 @@ namespace gsb {
 
 using u32 = uint32_t;
 constexpr int kWThreads = 256;
-constexpr int kWTileCols = 64;  // 8 warps x 8 columns each
+// Columns per CTA.  64 (8 per warp) when the call has many columns; 8 (one per warp) when it has few, so that a call
+// with a few thousand long columns — the later hops of adaptive sampling — still fills the GPU.
+constexpr int kWTileColsWide = 64;
+constexpr int kWTileColsNarrow = 8;
 
 struct WeightedParams {
   const i64* indptr;
@@ -195,6 +198,7 @@ __device__ __forceinline__ void topk_scan(const WeightedParams& p, i64 col_pos, 
 // through shared memory): one hub column would otherwise occupy a single warp for hundreds of iterations.
 constexpr i64 kLongColumn = 2048;
 
+template <int kWTileCols>
 __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams p) {
   __shared__ i64 s_in[kWTileCols];
   __shared__ i64 s_deg[kWTileCols];
@@ -334,7 +338,8 @@ extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* i
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(replace || k <= 32, GSB_ERR_UNSUPPORTED);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const int grid = grid_for(S, kWTileCols);
+  const bool narrow = S < (i64)kWTileColsWide * 148 * 6;  // the wide tiles would not fill one wave
+  const int grid = grid_for(S, narrow ? kWTileColsNarrow : kWTileColsWide);
   TileState ts;
   int st = ctx_tile_state(ctx, grid, stream, &ts);
   if (st != GSB_OK) return st;
@@ -342,7 +347,10 @@ extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* i
                    out_indices, out_select, out_coo_col, data,  e_ids, out_data, capacity, ctx_counters(ctx), ts};
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_WEIGHTED, stream);
-    k_sample_weighted<<<grid, kWThreads, 0, stream>>>(p);
+    if (narrow)
+      k_sample_weighted<kWTileColsNarrow><<<grid, kWThreads, 0, stream>>>(p);
+    else
+      k_sample_weighted<kWTileColsWide><<<grid, kWThreads, 0, stream>>>(p);
   }
   GSB_LAUNCH_OK();
   if (nnz_host) {
