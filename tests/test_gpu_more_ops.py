@@ -331,3 +331,42 @@ def test_row_slice_csr_path_against_fixture(ops, oracle, gold):
     assert np.array_equal(host(s_local), gold["rowslice_csr_coo_row"])
     assert np.array_equal(host(s_vals), gold["rowslice_csr_coo_col"])
     assert np.array_equal(gold["slice_data"][host(perm)[host(s_sel)]], gold["rowslice_csr_data"])
+
+
+# ---- kernel variants chosen by the shape of the call -------------------------------------------------
+def test_col_slice_both_fill_kernels(ops, oracle, cfg1_graph):
+    """The slice is copied by column tiles when columns are many and short, by output tiles when they are long or
+    few; every shape below must give the oracle's arrays."""
+    indptr, indices = cfg1_graph
+    rng = np.random.default_rng(12)
+    n = len(indptr) - 1
+    w = rng.random(len(indices)).astype(np.float32)
+    cases = [rng.integers(0, n, 40_000).astype(np.int64),          # many short columns (repeats allowed): column tiles
+             rng.integers(0, n, 700).astype(np.int64)]             # few columns: output tiles
+    for seeds in cases:
+        want = oracle.col_slice(indptr, indices, seeds)
+        got = ops.csc_col_slicing(dev(indptr), dev(indices), dev(seeds), True, data=dev(w))
+        for a, b in zip(want, got):
+            assert np.array_equal(a, host(b))
+        assert np.array_equal(host(got[4]), w[want[3]])
+    # many LONG columns (average degree above 128) with empty ones in between: output tiles although S is large
+    deg = np.diff(indptr)
+    long_cols, empty = np.flatnonzero(deg >= 160), np.flatnonzero(deg == 0)[:8]
+    assert len(long_cols) > 0
+    seeds = np.concatenate([rng.choice(long_cols, 19_500), empty, rng.choice(long_cols, 16)]).astype(np.int64)
+    rng.shuffle(seeds[:19_508])
+    want = oracle.col_slice(indptr, indices, seeds)
+    assert len(seeds) >= 148 * 128 and want[0][-1] >= 128 * len(seeds)
+    got = ops.csc_col_slicing(dev(indptr), dev(indices), dev(seeds), True)
+    for a, b in zip(want, got):
+        assert np.array_equal(a, host(b))
+
+
+def test_weighted_sampling_wide_tiles(ops, oracle, cfg1_graph):
+    """Calls with many columns use 64-column tiles (the other tests, with a few thousand columns, use 8-column ones)."""
+    indptr, indices = cfg1_graph
+    probs = (np.random.default_rng(6).random(len(indices)) + 0.01).astype(np.float32)
+    want = oracle.sample_weighted(indptr, indices, probs, None, 5, False, seed=14)
+    got = ops.csc_col_sampling_probs(dev(indptr), dev(indices), dev(probs), 5, False, with_coo=False, seed=14)
+    assert len(indptr) - 1 >= 64 * 148 * 6
+    assert np.array_equal(want[0], host(got[0])) and np.array_equal(want[3], host(got[3]))
