@@ -1,9 +1,9 @@
 // Generalised SDDMM over the edges of a COO (or CSC) graph: out[eid] = op(lhs[sel_l], rhs[sel_r]).
 //
-// The adaptive-sampling path only needs `dot` with one output per edge: a warp per edge reads the
-// source row (one contiguous F*4-byte segment of the feature matrix, gathered at random) and the
-// destination row (shared by all edges of a column, so it stays in L1/L2) with 128-bit loads and
-// reduces with shuffles.  It is a bandwidth-bound gather (about 0.5 flop per byte), so it runs on
+// The adaptive-sampling path only needs `dot` with one output per edge: a warp takes four edges at a
+// time, reads their source rows (contiguous F*4-byte segments of the feature matrix, gathered at
+// random) and destination rows (shared by all edges of a column, so they stay in L1/L2) with 128-bit
+// loads, all requested before any arithmetic, and reduces with shuffles.  It is a bandwidth-bound gather (about 0.5 flop per byte), so it runs on
 // the FMA pipe, not on tensor cores.  The reference's tree-reduce kernel handles 8 edges per CTA
 // with scalar 4-byte loads (src/cuda/sddmm.cu:66-104).
 //
@@ -52,37 +52,79 @@ __device__ __forceinline__ i64 select_target(int target, i64 src, i64 eid, i64 d
   return target == 0 ? src : (target == 1 ? eid : dst);
 }
 
+// Dot products of up to kDotEdges edges by one warp.  The rows of all of them are requested before any arithmetic:
+// with one edge per step a warp waited out two dependent memory round trips per edge (ids, then rows), and the
+// kernel ran at the pace of latency x resident warps, not of bandwidth.  Per edge the products are accumulated in
+// the same order as before (ascending element, lane-strided, then the xor tree).
+constexpr int kDotEdges = 4;
+
+template <bool VEC4>
+__device__ __forceinline__ void dot_edges(const SddmmParams& p, const i64 (&src)[kDotEdges], const i64 (&dst)[kDotEdges],
+                                          const i64 (&eid)[kDotEdges], int count) {
+  const int lane = threadIdx.x & 31;
+  const i64 F = p.reduce_size;
+  const float* l[kDotEdges];
+  const float* r[kDotEdges];
+  float acc[kDotEdges];
+#pragma unroll
+  for (int u = 0; u < kDotEdges; ++u) {
+    // (the callers fill spare slots, u >= count, with a copy of edge 0; their result is dropped)
+    l[u] = p.lhs + select_target(p.lhs_target, src[u], eid[u], dst[u]) * p.lhs_len;
+    r[u] = p.rhs + select_target(p.rhs_target, src[u], eid[u], dst[u]) * p.rhs_len;
+    acc[u] = 0.f;
+  }
+  if (VEC4) {
+    const i64 n4 = F >> 2;
+    for (i64 q = lane; q < n4; q += 32) {
+      float4 a[kDotEdges], b[kDotEdges];
+#pragma unroll
+      for (int u = 0; u < kDotEdges; ++u) {
+        a[u] = __ldg(reinterpret_cast<const float4*>(l[u]) + q);
+        b[u] = __ldg(reinterpret_cast<const float4*>(r[u]) + q);
+      }
+#pragma unroll
+      for (int u = 0; u < kDotEdges; ++u) {
+        acc[u] = fmaf(a[u].x, b[u].x, acc[u]);
+        acc[u] = fmaf(a[u].y, b[u].y, acc[u]);
+        acc[u] = fmaf(a[u].z, b[u].z, acc[u]);
+        acc[u] = fmaf(a[u].w, b[u].w, acc[u]);
+      }
+    }
+  } else {
+    for (i64 q = lane; q < F; q += 32) {
+      float a[kDotEdges], b[kDotEdges];
+#pragma unroll
+      for (int u = 0; u < kDotEdges; ++u) {
+        a[u] = __ldg(l[u] + q);
+        b[u] = __ldg(r[u] + q);
+      }
+#pragma unroll
+      for (int u = 0; u < kDotEdges; ++u) acc[u] = fmaf(a[u], b[u], acc[u]);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kDotEdges; ++u) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+    if (lane == 0 && u < count) p.out[eid[u]] = acc[u];
+  }
+}
+
 template <bool VEC4>
 __global__ void __launch_bounds__(kSddmmThreads) k_sddmm_dot_warp(SddmmParams p) {
-  const int lane = threadIdx.x & 31;
   const i64 warp_global = ((i64)blockIdx.x * kSddmmThreads + threadIdx.x) >> 5;
   const i64 num_warps = ((i64)gridDim.x * kSddmmThreads) >> 5;
-  const i64 F = p.reduce_size;
-  for (i64 e = warp_global; e < p.E; e += num_warps) {
-    const i64 src = __ldg(p.row + e);
-    const i64 dst = p.col ? __ldg(p.col + e) : column_of_edge(p.indptr, p.num_cols, e);
-    const i64 eid = p.e_ids ? __ldg(p.e_ids + e) : e;
-    const float* l = p.lhs + select_target(p.lhs_target, src, eid, dst) * p.lhs_len;
-    const float* r = p.rhs + select_target(p.rhs_target, src, eid, dst) * p.rhs_len;
-    float acc = 0.f;
-    if (VEC4) {
-      const float4* l4 = reinterpret_cast<const float4*>(l);
-      const float4* r4 = reinterpret_cast<const float4*>(r);
-      const i64 n4 = F >> 2;
-      for (i64 j = lane; j < n4; j += 32) {
-        const float4 a = __ldg(l4 + j);
-        const float4 b = __ldg(r4 + j);
-        acc = fmaf(a.x, b.x, acc);
-        acc = fmaf(a.y, b.y, acc);
-        acc = fmaf(a.z, b.z, acc);
-        acc = fmaf(a.w, b.w, acc);
-      }
-    } else {
-      for (i64 j = lane; j < F; j += 32) acc = fmaf(__ldg(l + j), __ldg(r + j), acc);
-    }
+  for (i64 e0 = warp_global * kDotEdges; e0 < p.E; e0 += num_warps * kDotEdges) {
+    const int count = (int)min((i64)kDotEdges, p.E - e0);
+    i64 src[kDotEdges], dst[kDotEdges], eid[kDotEdges];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) p.out[eid] = acc;
+    for (int u = 0; u < kDotEdges; ++u) {
+      const i64 e = e0 + (u < count ? u : 0);
+      src[u] = __ldg(p.row + e);
+      dst[u] = p.col ? __ldg(p.col + e) : column_of_edge(p.indptr, p.num_cols, e);
+      eid[u] = p.e_ids ? __ldg(p.e_ids + e) : e;
+    }
+    dot_edges<VEC4>(p, src, dst, eid, count);
   }
 }
 

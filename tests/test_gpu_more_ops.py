@@ -370,3 +370,33 @@ def test_weighted_sampling_wide_tiles(ops, oracle, cfg1_graph):
     got = ops.csc_col_sampling_probs(dev(indptr), dev(indices), dev(probs), 5, False, with_coo=False, seed=14)
     assert len(indptr) - 1 >= 64 * 148 * 6
     assert np.array_equal(want[0], host(got[0])) and np.array_equal(want[3], host(got[3]))
+
+
+def test_sddmm_dot_large_call_equals_chunks(ops, oracle, cfg1_graph):
+    """A warp takes four edges per step; how the edges fall into those groups must not change any result: one call
+    over 2 M edges equals, bit for bit, calls over odd-sized chunks of the same edges."""
+    indptr, indices = cfg1_graph
+    rng = np.random.default_rng(64)
+    n, F = len(indptr) - 1, 64
+    row = indices
+    col = np.repeat(np.arange(n, dtype=np.int64), np.diff(indptr))
+    E = len(row)
+    assert E >= (1 << 20)
+    x, y = rng.standard_normal((n, F)).astype(np.float32), rng.standard_normal((n, F)).astype(np.float32)
+    dx, dy, drow, dcol = dev(x), dev(y), dev(row), dev(col)
+    whole = torch.zeros(E, 1, device="cuda")
+    ops.sddmm("dot", dx, dy, whole, 0, 2, drow, dcol)
+    parts = torch.zeros(E, 1, device="cuda")
+    step = (1 << 20) - 1
+    for a in range(0, E, step):
+        ops.sddmm("dot", dx, dy, parts[a:a + step], 0, 2, drow[a:a + step].contiguous(), dcol[a:a + step].contiguous())
+    assert torch.equal(whole, parts)
+    sample = rng.choice(E, 20000, replace=False)
+    want = oracle.sddmm_coo("dot", row[sample], col[sample], x, y)
+    scale = np.abs(x[row[sample]] * y[col[sample]]).sum(1, keepdims=True)
+    assert np.all(np.abs(host(whole)[sample] - want) <= 1e-5 * scale + 1e-7)
+    # the operand gathered by source id on the right-hand side, and edge ids that permute the output
+    perm = rng.permutation(E).astype(np.int64)
+    out = torch.zeros(E, 1, device="cuda")
+    ops.sddmm("dot", dy, dx, out, 2, 0, drow, dcol, e_ids=dev(perm))
+    assert torch.equal(out[dev(perm)], whole)
