@@ -344,6 +344,7 @@ class Graph : public torch::CustomClassHolder {
   }
   void SetCOOByTensor(Tensor row, Tensor col, OptTensor e_ids, bool row_sorted, bool col_sorted) {
     coo_ = std::make_shared<COO>(COO{row, col, e_ids, row_sorted, col_sorted});
+    known_csc_ = nullptr, known_csr_ = nullptr;
   }
   void SetData(Tensor data) { data_ = data; }
   int64_t GetNumRows() { return num_rows_; }
@@ -371,6 +372,10 @@ class Graph : public torch::CustomClassHolder {
         TORCH_CHECK(!val_col_ids_.has_value(), "Require CSC, get DCSC instead");
         return;
       }
+      if (known_csc_) {
+        csc_ = known_csc_;
+        return;
+      }
       if (!coo_) coo_ = AnyToCOO();
       csc_ = FromCOO(*coo_, num_cols_, true);
     } else if (format == kDCSC) {
@@ -385,6 +390,10 @@ class Graph : public torch::CustomClassHolder {
     } else if (format == kCSR) {
       if (csr_) {
         TORCH_CHECK(!val_row_ids_.has_value(), "Require CSR, get DCSR instead");
+        return;
+      }
+      if (known_csr_) {
+        csr_ = known_csr_;
         return;
       }
       if (!coo_) coo_ = AnyToCOO();
@@ -456,7 +465,7 @@ class Graph : public torch::CustomClassHolder {
       new_cols = num_cols_;
       new_rows = n_ids.numel();
     }
-    std::shared_ptr<CSC> csc, csr;
+    std::shared_ptr<CSC> csc, csr, known_csc, known_csr;
     std::shared_ptr<COO> coo;
     OptTensor new_val_cols, new_val_rows;
     Tensor out_data;
@@ -499,6 +508,8 @@ class Graph : public torch::CustomClassHolder {
       }
       if (output_format & (on_csc ? kCSC : kCSR))
         (on_csc ? csc : csr) = std::make_shared<CSC>(CSC{indptr, indices, torch::nullopt});
+      else if (!(on_csc ? new_val_cols : new_val_rows).has_value())
+        (on_csc ? known_csc : known_csr) = std::make_shared<CSC>(CSC{indptr, indices, torch::nullopt});
       if (with_coo)
         coo = on_csc ? std::make_shared<COO>(COO{indices, other, torch::nullopt, false, true})
                      : std::make_shared<COO>(COO{other, indices, torch::nullopt, true, false});
@@ -509,6 +520,10 @@ class Graph : public torch::CustomClassHolder {
     auto ret = c10::make_intrusive<Graph>(true, new_col_ids, new_row_ids, new_cols, new_rows);
     ret->num_edges_ = new_edges;
     ret->csc_ = csc, ret->csr_ = csr, ret->coo_ = coo;
+    // The slice computed these offsets anyway.  The child does not HOLD the format (which formats a graph holds
+    // decides, e.g., what Relabel returns), but a later CreateSparseFormat adopts it instead of converting the COO:
+    // the arrays are exactly what that conversion would produce from a COO sorted along this axis.
+    ret->known_csc_ = known_csc, ret->known_csr_ = known_csr;
     ret->val_col_ids_ = new_val_cols, ret->val_row_ids_ = new_val_rows;
     if (out_data.defined()) ret->data_ = out_data;
     return ret;
@@ -960,6 +975,7 @@ class Graph : public torch::CustomClassHolder {
   bool is_subgraph_ = false;
   int64_t num_cols_ = 0, num_rows_ = 0, num_edges_ = 0;
   std::shared_ptr<CSC> csc_, csr_;
+  std::shared_ptr<CSC> known_csc_, known_csr_;  // offsets a slice computed but the graph does not hold (see Slicing)
   std::shared_ptr<COO> coo_;
   OptTensor data_, col_ids_, row_ids_;
   OptTensor val_col_ids_, val_row_ids_;  // ids that have edges, when csc_ / csr_ is doubly compressed (DCSC / DCSR)

@@ -82,6 +82,7 @@ class Graph:
 
     def SetCOOByTensor(self, row, col, e_ids, row_sorted, col_sorted):
         self.coo_ = COO(row, col, e_ids, bool(row_sorted), bool(col_sorted))
+        self._known_csc = self._known_csr = None
 
     def SetData(self, data):
         self.data_ = data
@@ -188,7 +189,9 @@ class Graph:
                 if self.val_col_ids_ is not None:
                     _fatal("Require CSC, get DCSC instead")
                 return
-            if self.coo_ is not None:
+            if getattr(self, "_known_csc", None) is not None:
+                self.csc_ = self._known_csc
+            elif self.coo_ is not None:
                 self.csc_ = self._coo2csc(self.coo_, self.num_cols_, True)
             else:
                 self.CSR2CSC()
@@ -206,7 +209,9 @@ class Graph:
                 if self.val_row_ids_ is not None:
                     _fatal("Require CSR, get DCSR instead")
                 return
-            if self.coo_ is not None:
+            if getattr(self, "_known_csr", None) is not None:
+                self.csr_ = self._known_csr
+            elif self.coo_ is not None:
                 self.csr_ = self._coo2csc(self.coo_, self.num_rows_, False)
             else:
                 self.CSC2CSR()
@@ -257,6 +262,7 @@ class Graph:
             new_row_ids = self.row_ids_[n_ids] if self.row_ids_ is not None else n_ids
             new_num_cols, new_num_rows = self.num_cols_, n_ids.numel()
         csc_ptr = csr_ptr = coo_ptr = None
+        known_csc = known_csr = None
         out_data = None
         new_val_cols = new_val_rows = None
 
@@ -296,6 +302,8 @@ class Graph:
                     out_data = ops.take(data, ops.take(e_ids, select) if e_ids is not None else select)
             if output_format & _CSC:
                 csc_ptr = CSC(indptr, indices)
+            elif new_val_cols is None:
+                known_csc = CSC(indptr, indices)
             if output_format & _COO:
                 coo_ptr = COO(indices, coo_col, None, False, True)
             new_num_edges = indices.numel()
@@ -324,6 +332,8 @@ class Graph:
                     new_col_ids, new_num_cols = frontier, frontier.numel()
             if output_format & _CSR:
                 csr_ptr = CSC(indptr, indices)
+            elif new_val_rows is None:
+                known_csr = CSC(indptr, indices)
             if output_format & _COO:
                 coo_ptr = COO(coo_row, indices, None, True, False)
             new_num_edges = indices.numel()
@@ -333,6 +343,10 @@ class Graph:
         ret = self._child(new_col_ids, new_row_ids, new_num_cols, new_num_rows)
         ret.num_edges_ = new_num_edges
         ret.coo_, ret.csc_, ret.csr_ = coo_ptr, csc_ptr, csr_ptr
+        # The slice computed these offsets anyway.  The child does not HOLD the format (which formats a graph holds
+        # decides, e.g., what Relabel returns), but a later CreateSparseFormat adopts it instead of converting the COO:
+        # the arrays are exactly what that conversion would produce from a COO sorted along this axis.
+        ret._known_csc, ret._known_csr = known_csc, known_csr
         ret.val_col_ids_, ret.val_row_ids_ = new_val_cols, new_val_rows
         if out_data is not None:
             ret.data_ = out_data

@@ -238,3 +238,26 @@ def test_metapath_walk_edges(ops):
         ops.fused_metapath_random_walk(dev(np.array([0])), [1], g)                 # relation index out of range
     with pytest.raises(Exception):
         ops.fused_metapath_random_walk(dev(np.array([0])), [0] * 300, g)           # longer than the supported path
+
+
+def test_slice_offsets_are_reused_not_held(face, oracle, small_graph):
+    """A column slice with COO output does not HOLD a CSC (Relabel must answer in COO form, as the reference's does),
+    but a later request for the CSC gets the offsets the slice computed — the same arrays a conversion would give."""
+    _COO, _CSC, _CSR = 1, 2, 4
+    indptr, indices = small_graph
+    seeds = np.random.default_rng(2).choice(len(indptr) - 1, 300, replace=False).astype(np.int64)
+    g = face.Graph(False)
+    g._CAPI_LoadCSC(dev(indptr), dev(indices))
+    sub = g._CAPI_Slicing(dev(seeds), 0, _CSC, _COO, False)
+    assert sub._CAPI_Relabel()[6] == "coo"
+    want = oracle.col_slice(indptr, indices, seeds)
+    total = sub._CAPI_Sum(0, 1, _CSC)                       # asks for the CSC
+    assert np.array_equal(host(total), np.diff(want[0]).astype(np.float32))
+    csc = sub._CAPI_GetCSC()
+    assert same(csc[0], want[0]) and same(csc[1], want[2])
+    # the row-wise counterpart: slice the rows of the CSR, COO out, then ask for the CSR
+    rows = np.random.default_rng(3).choice(len(indptr) - 1, 200, replace=False).astype(np.int64)
+    rs = sub._CAPI_Slicing(dev(rows), 1, _CSR, _COO, False)
+    coo = rs._CAPI_COOMetadata()
+    per_row = rs._CAPI_Sum(1, 1, _CSR)
+    assert np.array_equal(host(per_row), np.bincount(host(coo[3]), minlength=len(rows)).astype(np.float32))
