@@ -35,7 +35,6 @@ enum CounterSlot {
   CNT_AUX0 = 4,
   CNT_AUX1 = 5,
   CNT_EPOCH = 6,       // device-side epoch base (pipeline mode)
-  CNT_SCRATCH = 16,    // 8 words of device scratch for tiny offset arrays a call builds for itself
   CNT_NUM = 64
 };
 
