@@ -6,8 +6,9 @@
 // One warp per column keeps the running top-k as a sorted list, one entry per lane (k <= 32, the
 // reference's own limit: sampling_probs.cu:32).  A new key enters the list only if it beats the
 // current k-th entry, which after the first few dozen edges is rare, so a hub column costs one
-// key evaluation per edge plus O(k log(deg/k)) list insertions — no merge network, no shared
-// memory.  Ties rank the smaller edge position first; the output is in descending key order.
+// key evaluation per edge plus O(k log(deg/k)) list insertions — no merge network; shared memory
+// only transposes the keys of an iteration.  Ties rank the smaller edge position first; the output
+// is in descending key order.
 //
 // With replacement: k inverse-CDF draws over max(w, 0), the CDF being the fp32 running sum in
 // edge order (sampling_probs.cu:137-186 builds it with a warp scan into a temporary buffer; here
