@@ -137,6 +137,23 @@ def test_batch_col_slicing(ops, oracle, small_graph, encoding, with_coo):
         assert (w is None and g is None) or np.array_equal(w, host(g))
 
 
+def test_batch_col_slicing_many_columns(ops, oracle, cfg1_graph):
+    """With tens of thousands of short columns the slice is copied by column tiles (the smaller cases above go by
+    output tiles); batch numbers and the encoded row ids must come out the same."""
+    indptr, indices = cfg1_graph
+    n = len(indptr) - 1
+    rng = np.random.default_rng(10)
+    seeds, ps = ragged(rng, 64, 1600, n, 3)
+    assert len(seeds) >= 148 * 128
+    for encoding in (False, True):
+        want = oracle.batch_col_slice(indptr, indices, seeds, ps, n, with_coo=True, encoding=encoding)
+        assert want[0][-1] < 128 * len(seeds)
+        got = ops.batch_csc_col_slicing(dev(indptr), dev(indices), dev(seeds), dev(ps), n, with_coo=True,
+                                        encoding=encoding)
+        for w, g in zip(want, got):
+            assert (w is None and g is None) or np.array_equal(w, host(g))
+
+
 @pytest.mark.parametrize("G,hi,k", [(1, 50, 10), (1, 5, 10), (8, 400, 32), (200, 90, 64), (3, 40000, 4000)])
 def test_batch_list_sampling_matches_oracle(ops, oracle, G, hi, k):
     rng = np.random.default_rng(G + k)
