@@ -3,18 +3,27 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (config "products-scale GraphSAGE 3-hop"): symmetric R-MAT graph, 2,450,000 nodes,
-123,700,000 directed edges, int64 CSC, hub degrees thinned to about 17k; train split = 8% of the
-nodes; one STEP = one minibatch of 1,024 seeds per GPU: per hop (fanouts 15, 10, 5) fused column
-slice + uniform sampling without replacement, then unique + relabel; the frontier is the next hop's
-seeds.  The graph is replicated on every GPU and batches are dealt round-robin to the ranks, so the
-per-GPU work is fixed as N grows (weak scaling); NCCL only reduces the run statistics.
+Workload (config "products-scale GraphSAGE 3-hop"): symmetric R-MAT graph, 2,450,000 nodes, 123,700,000 directed
+edges, int64 CSC, hub degrees thinned to about 17k; train split = 8% of the nodes; minibatches of 1,024 seeds; per hop
+(fanouts 15, 10, 5) fused column slice + uniform sampling without replacement, then unique + relabel; the frontier is
+the next hop's seeds.  One STEP = one pass over the configuration's 1,000 minibatches on every GPU, handed to the
+batched sampler `--group` minibatches per call.  The graph is replicated on every GPU and every GPU has its own 1,000
+minibatches (weak scaling; minibatch b of the 1,000 x N goes to rank b mod N and its random stream is keyed by b, so
+results do not depend on N); NCCL only reduces the run statistics.
 
-Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` goes through the
-public `Graph` API with seeds in pinned host memory and the per-batch edge count read back.
-`--impl reference` times the reference's own implementation of the same loop: its CUDA library
-compiled unmodified for sm_100 (oracle/_ref/libgs_ref.so) if it is present, because the reference has
-no CPU path; otherwise the CPU restatement on the host cores.
+Prints ONE JSON line (rank 0):
+  value       timed with the seeds resident in HBM and per-kernel event timing off: exactly K steps between
+              barrier + synchronize, repeated until the timed work adds up to >= 0.5 s; the median repeat is
+              reported (`timing` carries min / median / max and the total);
+  e2e         the same steps through the public operator (ops.sage_sample_batches -> C ABI) with the seeds copied
+              from pinned host memory every call and the sizes of every hop read back on the host;
+  e2e_dropin  the reference's own super-batch Python loop (its registered TorchScript names) on lib/libgs.so, and
+              e2e_dropin_per_batch its per-minibatch Graph loop: what a user of the reference gets by swapping the library;
+  roofline    per-kernel CUDA-event times from a separate untimed step; algorithmic bytes over the measured HBM peak;
+  secondary   short legs of the other configurations (2-hop small graph, layer-wise, random walk, adaptive).
+`--impl reference` times the reference's own implementation of the same steps: its CUDA library compiled unmodified
+for sm_100 (oracle/_ref/libgs_ref.so) if it is present, because the reference has no CPU path; otherwise the CPU
+restatement on the host cores.
 """
 import argparse
 import json
@@ -33,6 +42,7 @@ NUM_EDGES = 123_700_000
 MAX_DEGREE = 17_000
 TRAIN_FRACTION = 0.08
 GRAPH_SEED = 0x5EED + 2
+RUN_SEED = 2024
 METRIC = "sampled_edges_per_second"
 UNIT = "edges/s"
 
@@ -41,20 +51,29 @@ UNIT = "edges/s"
 # per kernel on a 64-minibatch call of this workload (profiles/k_*_sage3hop_group64.md).  Traffic grows in
 # proportion to the units a launch processes, so a full launch's traffic is this ratio times its algorithmic bytes.
 TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.1, "table_insert": 4.0, "first_compact": 2.9, "relabel": 2.3}
+# the same for the direct-address form of unique + relabel (profiles/k_direct_*_sage3hop_group64.md)
+TRAFFIC_OVER_ALGORITHMIC_DIRECT = {"sample_uniform": 4.1}
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=8192)
-    ap.add_argument("--warmup", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batches-per-step", type=int, default=1000,
+                    help="minibatches every GPU processes per step (the configuration has 1,000)")
+    ap.add_argument("--relabel-path", default=None, choices=["auto", "hash", "direct"],
+                    help="table form of unique + relabel (default: the library's automatic choice)")
+    ap.add_argument("--no-dropin", action="store_true", help="skip the TorchScript drop-in legs")
+    ap.add_argument("--dropin-steps", type=int, default=2)
+    ap.add_argument("--dropin-batches", type=int, default=300)
+    ap.add_argument("--secondary", dest="secondary", action="store_true", default=True,
+                    help="after the headline, short legs of the other configurations (one GPU only)")
+    ap.add_argument("--no-secondary", dest="secondary", action="store_false")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--face", default="python", choices=["python", "torchscript"],
-                    help="with --group 1: drive the per-batch Graph API through the Python mirror or through the "
-                         "TorchScript library (lib/libgs.so)")
     ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels", "ladies", "adaptive"],
                     help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale "
                          "configuration); ladies = layer-wise importance sampling (1 M nodes / 50 M weighted edges); adaptive = "
@@ -65,8 +84,8 @@ def parse():
     ap.add_argument("--walk-length", type=int, default=80)
     ap.add_argument("--walk-nodes", type=int, default=111_000_000)
     ap.add_argument("--walk-edges", type=int, default=1_600_000_000)
-    ap.add_argument("--group", type=int, default=256,
-                    help="minibatches handed to one call of the batched sampler (1 = per-batch Graph API)")
+    ap.add_argument("--group", type=int, default=125,
+                    help="minibatches handed to one call of the batched sampler")
     return ap.parse_args()
 
 
@@ -139,23 +158,38 @@ def dist_env():
     return rank, world, local
 
 
+def graph_info(indptr, indices, gen_seconds):
+    deg = indptr[1:] - indptr[:-1]
+    return {"nodes": int(indptr.numel() - 1), "edges": int(indices.numel()), "max_degree": int(deg.max().item())}, \
+        round(gen_seconds, 2)
+
+
 def make_inputs(args, device, world, rank):
+    """The products-scale graph (replicated) and this rank's share of the configuration's minibatches: every rank
+    processes BATCHES_PER_STEP minibatches per step (weak scaling), dealt round-robin from world x that many, and
+    carries their GLOBAL numbers, which key the random streams."""
     import torch
     from graph_sampling_b200.synthetic import rmat_csc, seed_batches
+    from graph_sampling_b200.sharding import shard_batches, shard_batch_ids
     t0 = time.time()
     indptr, indices = rmat_csc(args.nodes, args.edges, seed=GRAPH_SEED, symmetric=True, max_degree=MAX_DEGREE,
                                device=device)
     torch.cuda.synchronize()
     torch.cuda.empty_cache()  # the generator's temporaries are several GB; keep only the graph resident
-    deg = indptr[1:] - indptr[:-1]
-    info = {"nodes": int(args.nodes), "edges": int(indices.numel()), "max_degree": int(deg.max().item()),
-            "gen_seconds": round(time.time() - t0, 2)}
-    total_batches = (args.steps + args.warmup) * world
-    allb = seed_batches(args.nodes, BATCH, total_batches, seed=GRAPH_SEED + 1, train_fraction=TRAIN_FRACTION,
-                        device="cpu")
-    from graph_sampling_b200.sharding import shard_batches
-    mine = shard_batches(allb, rank, world)  # batch b -> rank b mod world
-    return indptr, indices, mine, info
+    info, gen_s = graph_info(indptr, indices, time.time() - t0)
+    total = args.batches_per_step * world
+    allb = seed_batches(args.nodes, BATCH, total, seed=GRAPH_SEED + 1, train_fraction=TRAIN_FRACTION, device="cpu")
+    return indptr, indices, shard_batches(allb, rank, world), shard_batch_ids(total, rank, world), info, gen_s
+
+
+def workload_config(args, info):
+    """The part of `config` both arms print identically."""
+    return {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, relabel "
+                        "per hop (the products-scale configuration); one step = one pass over the configuration's "
+                        f"{args.batches_per_step} minibatches per GPU, handed to the sampler {args.group} at a time",
+            "graph": info, "batch": BATCH, "fanouts": FANOUTS, "batches_per_step": args.batches_per_step,
+            "group": args.group,
+            "l2": "inputs larger than L2: 1 GB of indices gathered at random, no flush"}
 
 
 def sage_batch_api(graph, seeds, fused_name, relabel_name):
@@ -172,115 +206,93 @@ def sage_batch_api(graph, seeds, fused_name, relabel_name):
     return edges, shapes
 
 
-def sage_group(ops, indptr, indices, seeds_2d, ptr_cache):
-    """G minibatches through the batched sampler (one fused sample + one batched relabel per hop).  Outputs come
-    from a reusable arena (ptr_cache["arena"]): the loop allocates only while the arena is still growing."""
-    G, S0 = seeds_2d.shape
-    ptr = ptr_cache.get(G)
-    if ptr is None:
-        import torch
-        ptr = torch.arange(G + 1, dtype=torch.int64, device=indptr.device) * S0
-        ptr_cache[G] = ptr
-    # one host wait per hop: the exact frontier size sizes the next hop.  Queuing all hops on upper bounds
-    # (sync=False) was measured slower here: bounds overshoot the real sizes 3.5x, which costs more in table
-    # clears and empty CTAs (9.1 G edges/s) than the three waits do (10.0 G).
-    arena = ptr_cache.get("arena")
-    if arena is None:
-        arena = ptr_cache["arena"] = ops.OutputArena()
-    hops = ops.sage_sample_batches(indptr, indices, seeds_2d.reshape(-1), ptr, FANOUTS, replace=False, arena=arena)
-    shapes = [(int(h["seeds"].numel()), int(h["indices"].numel()), int(h["frontier"].numel())) for h in hops]
-    return sum(e for _, e, _ in shapes), shapes
+def superbatch_torchscript(torch, G, seeds, ptr):
+    """The reference's own super-batch loop (examples/graphsage/batching.py:56-90) spelled with the registered
+    TorchScript names: fused sampling over the seeds of all minibatches, per-batch edge offsets from the sampled
+    CSC, gs_ops.BatchCSRRelabel.  Runs unchanged on the reference's library and on lib/libgs.so."""
+    edges, shapes = 0, []
+    for k in FANOUTS:
+        sub = G._CAPI_FusedColumnwiseSlicingSampling(seeds, k, False)
+        sub_indptr, sub_indices, _ = sub._CAPI_GetCSC()
+        indices_ptr = sub_indptr[ptr]
+        uniq, uniq_ptr, rel, _ = torch.ops.gs_ops._CAPI_BatchCSRRelabel(seeds, ptr, sub_indices, indices_ptr)
+        shapes.append((int(seeds.numel()), int(sub_indices.numel()), int(uniq.numel())))
+        edges += int(sub_indices.numel())
+        seeds, ptr = uniq, uniq_ptr
+    return edges, shapes
 
 
-def grouped(batches, group):
-    """Yields consecutive groups of up to `group` batches forever (wraps around)."""
-    n = batches.shape[0]
-    i = 0
-    while True:
-        j = min(n, i + group)
-        yield batches[i:j]
-        i = 0 if j >= n else j
+class Stepper:
+    """One step = one pass over this rank's minibatches, `group` of them per call of `call(seeds_2d, first, step)`
+    (first = index of the group's first minibatch, step = number of the pass).  The source array may live on the
+    device or in pinned host memory; a host source is copied group by group inside the step."""
+
+    def __init__(self, torch, call, source, group, device):
+        self.torch, self.call, self.source, self.group, self.device = torch, call, source, group, device
+        self.step_no = 0
+        self.shapes = []
+        self.keep_shapes = False
+
+    def step(self):
+        n = self.source.shape[0]
+        edges = 0
+        for first in range(0, n, self.group):
+            sb = self.source[first:first + self.group]
+            if not sb.is_cuda:
+                sb = sb.to(self.device, non_blocking=True)
+            e, shapes = self.call(sb, first, self.step_no)
+            edges += e
+            if self.keep_shapes:
+                self.shapes.append(shapes)
+        self.step_no += 1
+        return edges
 
 
-def timed_group_loop(torch, fn, batches, warmup, steps, group, barrier, ctx=None):
-    """Times exactly `steps` minibatches, processed `group` at a time, after `warmup` untimed ones.  With `ctx`,
-    per-kernel event timing and the launch counter cover exactly the timed region."""
-    done = 0
-    while done < warmup:
-        g = min(group, warmup - done)
-        fn(batches[done:done + g])
-        done += g
-    torch.cuda.synchronize()
-    barrier()
-    torch.cuda.synchronize()
-    launches0 = 0
-    if ctx is not None:
-        ctx.profile_reset()
-        ctx.profile_enable(True)
-        launches0 = ctx.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    edges, all_shapes, at = 0, [], warmup
-    end = warmup + steps
-    while at < end:
-        g = min(group, end - at)
-        e, shapes = fn(batches[at:at + g])
-        edges += e
-        all_shapes.append(shapes)
-        at += g
-    ev1.record()
-    torch.cuda.synchronize()
-    if ctx is not None:
-        ctx.profile_enable(False)
-        timed_group_loop.launches = ctx.launch_count() - launches0
-    barrier()
-    return ev0.elapsed_time(ev1) / 1e3, edges, all_shapes
-
-
-def algorithmic_bytes_sample(shapes):
-    # fused slice + uniform sample: 32 B per seed (seed, indptr pair, out offset) + 8 + 24 B per sampled edge
-    return sum(32 * s + 8 + 24 * e for s, e, _ in shapes)
-
-
-def timed_loop(torch, fn, batches_iter, warmup, steps, barrier):
+def timed_steps(torch, stepper, warmup, steps, barrier, reduce_max, min_seconds=0.5, min_repeats=3, max_repeats=25):
+    """`warmup` untimed steps, then the timed region — exactly `steps` steps between barrier + synchronize on both
+    sides, CUDA events on the launching stream — repeated until at least `min_seconds` of timed work and
+    `min_repeats` repeats exist.  Every repeat's time is the max over ranks.  Returns (per-repeat seconds, edges of one
+    repeat on this rank); the caller reports the median repeat."""
     for _ in range(warmup):
-        fn(next(batches_iter))
-    torch.cuda.synchronize()
-    barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
+        stepper.step()
+    seconds = []
     edges = 0
-    all_shapes = []
-    for _ in range(steps):
-        e, shapes = fn(next(batches_iter))
-        edges += e
-        all_shapes.append(shapes)
-    ev1.record()
-    torch.cuda.synchronize()
-    barrier()
-    return ev0.elapsed_time(ev1) / 1e3, edges, all_shapes
+    while len(seconds) < max_repeats and (len(seconds) < min_repeats or sum(seconds) < min_seconds):
+        torch.cuda.synchronize()
+        barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        edges = 0
+        for _ in range(steps):
+            edges += stepper.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        barrier()
+        seconds.append(reduce_max(ev0.elapsed_time(ev1) / 1e3))
+    return seconds, edges
 
 
-def reduce_stats(torch, dist, world, seconds, edges, device):
-    from graph_sampling_b200.sharding import reduce_run_stats
-    return reduce_run_stats(seconds, edges, device=device)
+def median(xs):
+    s = sorted(xs)
+    return s[len(s) // 2] if len(s) % 2 else 0.5 * (s[len(s) // 2 - 1] + s[len(s) // 2])
 
 
-def cpu_baseline(indptr, indices, batches, limit_s=15.0):
-    """Times the CPU restatement of the same batch loop on all host cores, on a bounded sample."""
+def cpu_baseline(indptr, indices, batches, limit_s=10.0, min_s=2.0):
+    """Times the CPU restatement of the same batch loop on all host cores, on a bounded sample: whole minibatches
+    for at least `min_s` and at most `limit_s` seconds, whatever --steps says."""
     from oracle import build as obuild
     obuild.build()
     from oracle import oracle as o
     ip, ix = indptr.cpu().numpy(), indices.cpu().numpy()
     o.sage_batch(ip, ix, batches[0].numpy(), FANOUTS, seed=1)  # warm
     t0, edges, n = time.time(), 0, 0
-    while n < len(batches) and (time.time() - t0) < limit_s:
-        edges += o.sage_batch(ip, ix, batches[n].numpy(), FANOUTS, seed=n)
+    while (time.time() - t0) < min_s or (n < len(batches) and (time.time() - t0) < limit_s):
+        edges += o.sage_batch(ip, ix, batches[n % len(batches)].numpy(), FANOUTS, seed=n, batch_id=n)
         n += 1
     dt = time.time() - t0
     return {"value": edges / dt, "unit": UNIT, "cores": o.num_threads(), "kind": "port",
-            "sample": f"{n} batches of {BATCH} seeds of the same workload ({dt:.1f} s)"}
+            "sample": f"{n} minibatches of {BATCH} seeds of the same workload ({dt:.1f} s)"}
 
 
 def run_ours(args):
@@ -294,80 +306,110 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
 
-    import graph_sampling_b200.gs as gs
+    def reduce_max(x):
+        if world == 1:
+            return float(x)
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x):
+        if world == 1:
+            return int(x)
+        t = torch.tensor([float(x)], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return int(round(t.item()))
+
     from graph_sampling_b200 import ops
-    indptr, indices, batches, info = make_inputs(args, device, world, rank)
-    A = gs.Graph(False)
-    A._CAPI_load_csc(indptr, indices)
+    indptr, indices, batches, batch_ids, info, gen_s = make_inputs(args, device, world, rank)
     ctx = ops.default_context(device)
-    ops.set_seed(2024 + rank)
-
-    # ---- value: seeds resident in HBM --------------------------------------------------------------
-    dev_batches = batches.to(device)
-    sampler = ClockSampler(physical_gpu_index(local), enabled=(rank == 0))
-    group = max(1, min(args.group, args.steps))
+    if args.relabel_path:
+        ctx.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2}[args.relabel_path])
+    group = args.group
+    ids_dev = batch_ids.to(device)
     ptr_cache = {}
-    if group > 1:
-        fn = lambda sb: sage_group(ops, indptr, indices, sb, ptr_cache)
-    elif args.face == "torchscript":
-        from graph_sampling_b200 import build as gsb_build
-        torch.classes.load_library(gsb_build.build_glue())
-        TS = torch.classes.gs_classes.Graph(False)
-        TS._CAPI_LoadCSC(indptr, indices)
-        fn = lambda sb: sage_batch_api(TS, sb[0], "_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_Relabel")
-    else:
-        fn = lambda sb: sage_batch_api(A, sb[0], "_CAPI_fused_columnwise_slicing_sampling", "_CAPI_relabel")
-    for _ in range(3):  # size scratch before anything is timed
-        fn(dev_batches[:group])
+    arena = ops.OutputArena()
+
+    def call_batched(sb, first, step_no):
+        """`group` minibatches through the batched sampler: per hop one call of the C ABI (gsb_sage_hop: fused slice +
+        sample, then unique + relabel of every minibatch), one host wait per hop for the exact sizes (queuing all hops
+        on upper bounds was measured slower: the bounds overshoot 3.5x)."""
+        g, s0 = sb.shape
+        ptr = ptr_cache.get(g)
+        if ptr is None:
+            ptr = ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * s0
+        hops = ops.sage_sample_batches(indptr, indices, sb.reshape(-1), ptr, FANOUTS, replace=False,
+                                       seed=RUN_SEED + 8 * step_no, arena=arena, batch_ids=ids_dev[first:first + g],
+                                       seeds_distinct=True)
+        shapes = [(int(h["seeds"].numel()), int(h["indices"].numel()), int(h["frontier"].numel())) for h in hops]
+        return sum(e for _, e, _ in shapes), shapes
+
+    # ---- value: seeds resident in HBM, per-kernel event timing OFF -----------------------------------------
+    dev_batches = batches.to(device)
+    stepper = Stepper(torch, call_batched, dev_batches, group, device)
+    stepper.step()  # sizes scratch, the output arena and the tables before anything is timed
+    sampler = ClockSampler(physical_gpu_index(local), enabled=(rank == 0))
     sampler.start()
-    seconds, edges, shapes = timed_group_loop(torch, fn, dev_batches, args.warmup, args.steps, group, barrier, ctx)
+    launches0 = ctx.launch_count()
+    steps_before = stepper.step_no
+    seconds, edges = timed_steps(torch, stepper, args.warmup, args.steps, barrier, reduce_max)
+    launches = (ctx.launch_count() - launches0) * args.steps // max(1, stepper.step_no - steps_before)
     clocks = sampler.stop()
-    prof = ctx.profile_read()
-    launches = timed_group_loop.launches
-    seconds_all, edges_all = reduce_stats(torch, dist, world, seconds, edges, device)
+    edges_all = reduce_sum(edges)
+    sec_med = median(seconds)
 
-    # ---- e2e: pinned host seeds -> device, public API, edge count back on the host -------------------
+    # ---- e2e: the same steps with the seeds in pinned host memory; sizes of every hop read back on the host -----
     pinned = batches.pin_memory()
-    h2d_bytes = BATCH * 8
-    d2h_bytes = 8 * 4 * len(FANOUTS)  # per call: the status + size counters read back at each hop
+    e2e_stepper = Stepper(torch, call_batched, pinned, group, device)
+    e2e_seconds, e2e_edges = timed_steps(torch, e2e_stepper, min(args.warmup, 2), args.steps, barrier, reduce_max)
+    e2e_edges_all = reduce_sum(e2e_edges)
+    e2e_med = median(e2e_seconds)
+    calls_per_step = (batches.shape[0] + group - 1) // group
 
-    def fn_e2e(host_seeds):
-        s = host_seeds.to(device, non_blocking=True)
-        return fn(s)
-
-    e2e_seconds, e2e_edges, _ = timed_group_loop(torch, fn_e2e, pinned, args.warmup, args.steps, group, barrier)
-    e2e_seconds_all, e2e_edges_all = reduce_stats(torch, dist, world, e2e_seconds, e2e_edges, device)
+    # ---- per-kernel device time: a separate, untimed pass of one step with event timing on ----------------------
+    prof_stepper = Stepper(torch, call_batched, dev_batches, group, device)
+    prof_stepper.keep_shapes = True
+    ctx.profile_reset()
+    ctx.profile_enable(True)
+    prof_stepper.step()
+    torch.cuda.synchronize()
+    ctx.profile_enable(False)
+    prof = ctx.profile_read()
+    shapes = prof_stepper.shapes
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    # ---- roofline of the dominant kernel (largest share of timed device time) ---------------------------
-    import json as _json
+
+    # ---- drop-in: the reference's own call sequence on lib/libgs.so (one GPU, rank 0) ---------------------------
+    dropin = dropin_torchscript(torch, args, device, indptr, indices, pinned) if not args.no_dropin else None
+
+    # ---- roofline of the dominant kernel (largest share of device time in the profiled step) --------------------
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
-        peak, peak_src = float(_json.load(open(peaks_path))["hbm_gbs"]), "measured"
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak, peak_src = 6650.0, "fallback"
-    # Algorithmic bytes per launch of each hot kernel, from the shapes of the timed calls: (S, E, U) per hop.
+    # Algorithmic bytes per launch of each hot kernel, from the shapes of the profiled calls: (S, E, U) per hop.
     # sample: 32 B per seed column (seed id, indptr pair, output offset) + 24 B per sampled edge (8 read, 16 written);
     # unique + relabel is three passes over N = S + E items: insert reads 8 N; first-occurrence compaction reads 8 N
-    # and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead, not counted).  The sampler that
-    # also records the ids in the tables is charged the sampling bytes only.
+    # and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead, not counted).
     hop_shapes = [h for call in shapes for h in call]
     n_launch = max(1, len(hop_shapes))
     alg = {
         "sample_uniform": sum(32 * s_ + 8 + 24 * e_ for s_, e_, _ in hop_shapes) / n_launch,
-        "sage_sample_insert": sum(32 * s_ + 8 + 24 * e_ for s_, e_, _ in hop_shapes) / n_launch,
         "table_insert": sum(8 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
         "first_compact": sum(8 * (s_ + e_) + 8 * u_ for s_, e_, u_ in hop_shapes) / n_launch,
         "relabel": sum(16 * e_ for s_, e_, _ in hop_shapes) / n_launch,
     }
+    direct = ctx.get_option("relabel_path") != 1
     kernel_names = {"sample_uniform": "k_sample_uniform_tpc (fused count + scan + uniform sample)",
-                    "sage_sample_insert": "k_sample_uniform_tpc<K, fused> (count + scan + uniform sample + table insert)",
-                    "table_insert": "k_batch_insert / k_insert (position-min hash insert)",
-                    "first_compact": "k_batch_compact / k_first_compact (first-occurrence scan + compaction)",
-                    "relabel": "k_batch_relabel / k_relabel (lookup)"}
+                    "table_insert": "k_direct_insert (atomicMin into per-minibatch direct-address tables)" if direct
+                    else "k_batch_insert (position-min hash insert)",
+                    "first_compact": "k_direct_compact (first-occurrence test + scan + compaction)" if direct
+                    else "k_batch_compact (first-occurrence scan + compaction)",
+                    "relabel": "k_direct_fixup (rank look-up of repeated ids)" if direct else "k_batch_relabel (lookup)"}
     total_ms = sum(v[0] for v in prof.values()) or 1.0
     per_kernel = {}
     for name, (ms, n) in prof.items():
@@ -378,17 +420,19 @@ def run_ours(args):
             entry["bytes_per_launch"] = round(alg[name])
             entry["achieved_gbs"] = round(alg[name] / avg_s / 1e9, 2)
             entry["frac"] = round(alg[name] / avg_s / 1e9 / peak, 5)
-            if name in TRAFFIC_OVER_ALGORITHMIC:
-                entry["traffic"] = round(alg[name] * TRAFFIC_OVER_ALGORITHMIC[name])
+            ratio = (TRAFFIC_OVER_ALGORITHMIC_DIRECT if direct else TRAFFIC_OVER_ALGORITHMIC).get(name)
+            if ratio is not None:
+                entry["traffic"] = round(alg[name] * ratio)
         per_kernel[name] = entry
     top = max((k for k in per_kernel if k in alg), key=lambda k: per_kernel[k]["ms"], default=None)
     if top is not None:
         t = per_kernel[top]
         roofline = {"bound": "hbm", "kernel": kernel_names[top], "achieved": t["achieved_gbs"], "peak": peak,
                     "peak_source": peak_src, "unit": "GB/s", "frac": t["frac"], "traffic": t.get("traffic"),
-                    "traffic_source": "ncu capture of a 64-minibatch call, scaled by algorithmic bytes",
+                    "traffic_source": "ncu capture of one launch on a 64-minibatch call, scaled by algorithmic bytes",
                     "bytes_per_launch": t["bytes_per_launch"], "avg_launch_us": t["avg_launch_us"],
-                    "share_of_device_time": t["share"], "kernels": per_kernel}
+                    "share_of_device_time": t["share"],
+                    "measured": "CUDA events around every launch of one untimed step", "kernels": per_kernel}
     else:
         roofline = {"bound": "hbm", "kernel": None, "achieved": None, "peak": peak, "peak_source": peak_src,
                     "unit": "GB/s", "frac": None, "traffic": None, "kernels": per_kernel}
@@ -396,35 +440,102 @@ def run_ours(args):
     if world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(indptr, indices, batches)
     line = {
-        "metric": METRIC, "value": edges_all / seconds_all, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": seconds_all / args.steps * 1e3, "higher_is_better": True,
+        "metric": METRIC, "value": edges_all / sec_med, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec_med / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, "
-                               "relabel per hop (the products-scale configuration)",
-                   "graph": info, "batch": BATCH, "fanouts": FANOUTS, "parallelism": f"replicated graph, dp{world}",
-                   "l2": "inputs larger than L2: 1 GB of indices gathered at random, no flush",
-                   "group": group,
-                   "path": ("batched sampler (gsb_sage_hop): %d minibatches per call; per hop one fused slice+sample launch "
-                            "and a batched unique+relabel (insert, compaction, lookup)" % group) if group > 1 else
-                           "Graph API per batch and hop (fused slice+sample, relabel)"},
+        "config": workload_config(args, info),
+        "arm": {"path": "batched sampler through the C ABI (gsb_sage_hop per hop: fused slice+sample, then unique + "
+                        "relabel of every minibatch with %s)" % ("direct-address tables" if direct else "hash tables"),
+                "parallelism": f"replicated graph, dp{world}; minibatch b of {args.batches_per_step * world} on rank "
+                               "b mod N, random streams keyed by the global minibatch number",
+                "graph_gen_seconds": gen_s, "relabel_path": "direct" if direct else "hash"},
         "edges_per_step": edges_all / args.steps / world,
-        "e2e": {"value": e2e_edges_all / e2e_seconds_all, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes,
-                "d2h_bytes_per_step": d2h_bytes / group, "ms_per_step": e2e_seconds_all / args.steps * 1e3},
+        "timing": {"repeats": len(seconds), "timed_region_s": round(sum(seconds), 4),
+                   "ms_per_step_min_median_max": [round(min(seconds) / args.steps * 1e3, 4),
+                                                  round(sec_med / args.steps * 1e3, 4),
+                                                  round(max(seconds) / args.steps * 1e3, 4)],
+                   "reported": "median repeat; every repeat times exactly `steps` steps, max over ranks"},
+        "e2e": {"value": e2e_edges_all / e2e_med, "unit": UNIT,
+                "h2d_bytes_per_step": batches.shape[0] * BATCH * 8,
+                "d2h_bytes_per_step": calls_per_step * len(FANOUTS) * 32,
+                "ms_per_step": e2e_med / args.steps * 1e3, "repeats": len(e2e_seconds),
+                "path": "ops.sage_sample_batches -> C ABI, seeds from pinned host memory every call, per-hop sizes and "
+                        "status read back; the sampled blocks stay in HBM (as in the reference's API)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roofline,
     }
+    if dropin is not None:
+        line["e2e_dropin"] = dropin["super_batch"]
+        line["e2e_dropin_per_batch"] = dropin["per_batch"]
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if world == 1 and args.secondary:
+        del dev_batches, pinned
+        line["secondary"] = secondary_workloads(args, "ours", device, indptr, indices)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
 
+def dropin_torchscript(torch, args, device, indptr, indices, pinned, lib_path=None):
+    """The reference-facing TorchScript face timed end to end with the reference's own Python loops, seeds from pinned
+    host memory: (1) its super-batch loop (fused sampling, GetCSC offsets, gs_ops.BatchCSRRelabel) on whole steps,
+    (2) its per-minibatch Graph loop on a bounded sample.  `lib_path` None = lib/libgs.so (this repository's library)."""
+    if lib_path is None:
+        from graph_sampling_b200 import build as gsb_build
+        lib_path = gsb_build.build_glue()
+    torch.classes.load_library(lib_path)
+    G = torch.classes.gs_classes.Graph(False)
+    G._CAPI_LoadCSC(indptr, indices)
+    ptr_cache = {}
+
+    def call(sb, first, step_no):
+        g, s0 = sb.shape
+        ptr = ptr_cache.get(g)
+        if ptr is None:
+            ptr = ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * s0
+        return superbatch_torchscript(torch, G, sb.reshape(-1), ptr)
+
+    out = {}
+    best = None
+    for group in sorted({args.group, 250}):
+        st = Stepper(torch, call, pinned, group, device)
+        steps = max(1, min(args.steps, args.dropin_steps))
+        seconds, edges = timed_steps(torch, st, 1, steps, lambda: None, float, min_seconds=0.0, min_repeats=1,
+                                     max_repeats=1)
+        r = {"value": edges / seconds[0], "unit": UNIT, "group": group, "steps": steps,
+             "ms_per_step": seconds[0] / steps * 1e3}
+        if best is None or r["value"] > best["value"]:
+            best = r
+    best["path"] = ("TorchScript classes: _CAPI_FusedColumnwiseSlicingSampling -> _CAPI_GetCSC -> "
+                    "gs_ops._CAPI_BatchCSRRelabel per hop (examples/graphsage/batching.py:56-90)")
+    out["super_batch"] = best
+    n = min(pinned.shape[0], args.dropin_batches)
+    for b in range(5):
+        sage_batch_api(G, pinned[b].to(device, non_blocking=True), "_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_Relabel")
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    edges = 0
+    for b in range(n):
+        e, _ = sage_batch_api(G, pinned[b].to(device, non_blocking=True), "_CAPI_FusedColumnwiseSlicingSampling",
+                              "_CAPI_Relabel")
+        edges += e
+    ev1.record()
+    torch.cuda.synchronize()
+    sec = ev0.elapsed_time(ev1) / 1e3
+    out["per_batch"] = {"value": edges / sec, "unit": UNIT, "minibatches": n, "ms_per_minibatch": sec / n * 1e3,
+                        "path": "TorchScript Graph per minibatch and hop: _CAPI_FusedColumnwiseSlicingSampling, "
+                                "_CAPI_Relabel (examples/graphsage/unbatching_training.py:19-28)"}
+    return out
+
+
 def run_reference(args):
-    """Reference arm.  The reference implements this path in CUDA only (every dispatcher aborts off-GPU),
-    so its own implementation is timed on the GPU through its TorchScript classes; if the compiled
-    library is absent the CPU restatement is timed on the host cores instead."""
+    """Reference arm.  The reference implements this path in CUDA only (every dispatcher aborts off-GPU), so its own
+    implementation — its sources compiled unmodified for sm_100 — is timed on the GPU through its TorchScript classes
+    with its own loops, on the same steps; if the compiled library is absent the CPU restatement is timed on the host
+    cores instead."""
     rank, world, local = dist_env()
     if rank != 0:
         return
@@ -432,67 +543,74 @@ def run_reference(args):
     lib = os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    indptr, indices, batches, info = make_inputs(args, device, 1, 0)
+    indptr, indices, batches, _, info, gen_s = make_inputs(args, device, 1, 0)
     base = {"metric": METRIC, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "impl": "reference",
-            "config": {"workload": "products-scale GraphSAGE 3-hop uniform sampling, fanouts [15,10,5], 1024 seeds/batch, "
-                                   "relabel per hop (the products-scale configuration)", "graph": info, "batch": BATCH,
-                       "fanouts": FANOUTS}}
+            "impl": "reference", "config": workload_config(args, info)}
     if os.path.exists(lib):
+        pinned = batches.pin_memory()
+        sampler = ClockSampler(physical_gpu_index(local))
+        sampler.start()
         torch.classes.load_library(lib)
         G = torch.classes.gs_classes.Graph(False)
         G._CAPI_LoadCSC(indptr, indices)
-        pinned = batches.pin_memory()
-
-        def fn(host_seeds):
-            s = host_seeds.to(device, non_blocking=True)
-            return sage_batch_api(G, s, "_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_Relabel")
-
         ptr_cache = {}
 
-        def fn_batched(host_seeds_2d):
-            """The reference's own super-batch loop (examples/graphsage/batching.py:56-90): fused sampling over the
-            seeds of all minibatches, per-batch edge offsets, gs_ops.BatchCSRRelabel."""
-            g, s0 = host_seeds_2d.shape
-            seeds = host_seeds_2d.to(device, non_blocking=True).reshape(-1)
+        def call(sb, first, step_no):
+            g, s0 = sb.shape
             ptr = ptr_cache.get(g)
             if ptr is None:
-                ptr = torch.arange(g + 1, dtype=torch.int64, device=device) * s0
-                ptr_cache[g] = ptr
-            edges, shapes = 0, []
-            for k in FANOUTS:
-                sub = G._CAPI_FusedColumnwiseSlicingSampling(seeds, k, False)
-                sub_indptr, sub_indices, _ = sub._CAPI_GetCSC()
-                indices_ptr = sub_indptr[ptr]
-                uniq, uniq_ptr, rel, _ = torch.ops.gs_ops._CAPI_BatchCSRRelabel(seeds, ptr, sub_indices, indices_ptr)
-                shapes.append((int(seeds.numel()), int(sub_indices.numel()), int(uniq.numel())))
-                edges += int(sub_indices.numel())
-                seeds, ptr = uniq, uniq_ptr
-            return edges, shapes
+                ptr = ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * s0
+            return superbatch_torchscript(torch, G, sb.reshape(-1), ptr)
 
-        sampler = ClockSampler(physical_gpu_index(local))
-        sampler.start()
-        seconds, edges, _ = timed_loop(torch, fn, iter(pinned), min(args.warmup, 32), min(args.steps, 1024),
-                                       lambda: None)
-        per_batch = edges / seconds
-        group = max(1, min(args.group, args.steps))
-        b_seconds, b_edges, _ = timed_group_loop(torch, fn_batched, pinned, args.warmup, args.steps, group,
-                                                 lambda: None)
-        batched = b_edges / b_seconds
+        # its super-batch loop at this run's group size and at the 256-ish size its examples use: one trial step
+        # each, the faster one is measured in full
+        trial = {}
+        for group in sorted({args.group, 250}):
+            st = Stepper(torch, call, pinned, group, device)
+            sec, e = timed_steps(torch, st, 1, 1, lambda: None, float, min_seconds=0.0, min_repeats=1, max_repeats=1)
+            trial[group] = e / sec[0]
+        group = max(trial, key=trial.get)
+        st = Stepper(torch, call, pinned, group, device)
+        seconds, edges = timed_steps(torch, st, args.warmup, args.steps, lambda: None, float, min_seconds=0.5,
+                                     min_repeats=1, max_repeats=3)
+        sec_med = median(seconds)
+        batched = edges / sec_med
+        # its per-minibatch Graph loop on a bounded sample
+        n = min(pinned.shape[0], 500)
+        for b in range(5):
+            sage_batch_api(G, pinned[b].to(device, non_blocking=True), "_CAPI_FusedColumnwiseSlicingSampling", "_CAPI_Relabel")
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        pb_edges = 0
+        for b in range(n):
+            e, _ = sage_batch_api(G, pinned[b].to(device, non_blocking=True), "_CAPI_FusedColumnwiseSlicingSampling",
+                                  "_CAPI_Relabel")
+            pb_edges += e
+        ev1.record()
+        torch.cuda.synchronize()
+        pb_sec = ev0.elapsed_time(ev1) / 1e3
+        per_batch = pb_edges / pb_sec
         clocks = sampler.stop()
-        v = max(per_batch, batched)
-        seconds = b_seconds if batched >= per_batch else seconds * args.steps / min(args.steps, 1024)
-        base["config"]["reference_paths"] = {
-            "per_batch_graph_api_edges_per_s": per_batch,
-            "super_batch_%d_edges_per_s" % group: batched,
-            "reported": "super-batch" if batched >= per_batch else "per-batch"}
-        base.update({"value": v, "ms_per_step": seconds / args.steps * 1e3, "clocks": clocks,
+        if batched >= per_batch:
+            v, ms_step = batched, sec_med / args.steps * 1e3
+        else:
+            v, ms_step = per_batch, pb_sec / n * args.batches_per_step * 1e3
+        base["arm"] = {"reference_paths": {"per_batch_graph_api_edges_per_s": per_batch,
+                                           "super_batch_edges_per_s": batched, "super_batch_group": group,
+                                           "super_batch_trials_edges_per_s": trial,
+                                           "reported": "super-batch" if batched >= per_batch else "per-batch"},
+                       "graph_gen_seconds": gen_s, "repeats": len(seconds)}
+        base.update({"value": v, "ms_per_step": ms_step, "clocks": clocks,
                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": 0, "kind": "reference",
                                       "sample": "the reference has no CPU path; this is its own CUDA library "
                                                 "(unmodified sources compiled for sm_100) on the same GPU, "
-                                                f"{args.steps} batches"},
+                                                f"{args.steps} steps of {args.batches_per_step} minibatches"},
                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        if args.secondary:
+            del pinned
+            base["secondary"] = secondary_workloads(args, "reference", device, indptr, indices)
     else:
         cpu = cpu_baseline(indptr, indices, batches, limit_s=60.0)
         base.update({"value": cpu["value"], "ms_per_step": None, "cpu_baseline": cpu,
@@ -500,43 +618,32 @@ def run_reference(args):
     print(json.dumps(base))
 
 
-def run_walk(args):
+def measure_walk(torch, args, impl, device, rank=0, world=1, barrier=lambda: None, steps=3, warmup=1):
     """Uniform random walk (papers-scale configuration): one walker per distinct start node, walkers split into
-    contiguous ranges over the ranks, int64 trace [walkers, length + 1].  A step here is one full pass over
-    this rank's walkers.  Secondary workload: prints its own JSON line (metric walker_steps_per_second)."""
-    import torch
-    rank, world, local = dist_env()
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
-    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    contiguous ranges over the ranks, int64 trace [walkers, length + 1].  A step is one full pass over this rank's
+    walkers.  Returns this rank's figures (the caller reduces over ranks)."""
     from graph_sampling_b200.synthetic import rmat_csc, distinct_starts
-    from graph_sampling_b200.sharding import shard_walkers, reduce_run_stats
+    from graph_sampling_b200.sharding import shard_walkers
+    from graph_sampling_b200 import validate
     t0 = time.time()
     indptr, indices = rmat_csc(args.walk_nodes, args.walk_edges, seed=GRAPH_SEED + 4, device=device, permute=True)
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
-    info = {"nodes": args.walk_nodes, "edges": int(indices.numel()), "gen_seconds": round(time.time() - t0, 1)}
+    info = {"nodes": args.walk_nodes, "edges": int(indices.numel())}
+    gen_s = round(time.time() - t0, 1)
     starts = distinct_starts(args.walk_nodes, args.walkers, seed=7, device=device)
     off, cnt = shard_walkers(args.walkers, rank, world)
     mine = starts[off:off + cnt].contiguous()
     L = args.walk_length
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-    if args.impl == "reference":
+    if impl == "reference":
         torch.classes.load_library(os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so"))
         G = torch.classes.gs_classes.Graph(False)
         G._CAPI_LoadCSC(indptr, indices)
         fn = lambda: G._CAPI_RandomWalk(mine, L)
-        layout = "step-major memory (the reference's own)"
     else:
         from graph_sampling_b200 import ops
-        ctx = ops.default_context(device)
-        layout_id = 0  # the reference's own memory order, so both arms write the same layout
-        fn = lambda: ops.fused_random_walk(mine, L, indices, indptr, layout=layout_id, walker_offset=off)
-        layout = "walker-major [walkers, length+1]" if layout_id == 1 else "step-major memory (the reference's own)"
+        # layout 0 = the reference's own memory order, so both arms write the same layout
+        fn = lambda: ops.fused_random_walk(mine, L, indices, indptr, layout=0, walker_offset=off, seed=RUN_SEED)
     for _ in range(warmup):
         out = fn()
     torch.cuda.synchronize()
@@ -548,23 +655,46 @@ def run_walk(args):
     ev1.record()
     torch.cuda.synchronize()
     seconds = ev0.elapsed_time(ev1) / 1e3
-    units = cnt * L * steps
-    seconds_all, units_all = reduce_run_stats(seconds, units, device=device)
+    check = validate.check_walk_trace(indptr, indices, out, cnt, L, step_major=True, sample=100_000)
+    check["ok_start_nodes"] = bool(torch.equal(out.reshape(-1)[:cnt], mine))
     alive = float((out >= 0).float().mean().item()) if out.numel() < (1 << 31) else None
+    del out
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+    alg = (16 * cnt + 32 * cnt * L)  # per pass on this rank
+    ach = alg * steps / seconds / 1e9
+    return {"seconds": seconds, "units": cnt * L * steps, "steps": steps, "warmup": warmup, "graph": info,
+            "graph_gen_seconds": gen_s, "fraction_of_trace_alive": alive, "checked": check,
+            "checks_pass": validate.all_ok(check),
+            "roofline": {"bound": "hbm", "kernel": "k_random_walk", "achieved": round(ach, 2), "peak": peak,
+                         "unit": "GB/s", "frac": round(ach / peak, 5), "traffic": None}}
+
+
+def run_walk(args):
+    """`--workload walk`: prints its own JSON line (metric walker_steps_per_second)."""
+    import torch
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    from graph_sampling_b200.sharding import reduce_run_stats
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    m = measure_walk(torch, args, args.impl, device, rank, world, barrier, steps, warmup)
+    seconds_all, units_all = reduce_run_stats(m["seconds"], m["units"], device=device)
     if rank == 0:
-        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
-        alg = (16 * cnt + 32 * cnt * L)  # per pass on this rank
-        ach = alg * steps / seconds / 1e9
         print(json.dumps({"metric": "walker_steps_per_second", "value": units_all / seconds_all, "unit": "steps/s",
                           "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": seconds_all / steps * 1e3,
                           "higher_is_better": True, "scaling": "strong", "dtype": "int64", "data": "synthetic",
                           "impl": args.impl,
-                          "config": {"workload": "uniform random walk (papers-scale configuration)", "graph": info,
-                                     "walkers": args.walkers, "length": L, "layout": layout,
-                                     "fraction_of_trace_alive": alive},
-                          "roofline": {"bound": "hbm", "kernel": "k_random_walk", "achieved": round(ach, 2), "peak": peak,
-                                       "unit": "GB/s", "frac": round(ach / peak, 5), "traffic": None}}))
+                          "config": {"workload": "uniform random walk (papers-scale configuration)", "graph": m["graph"],
+                                     "walkers": args.walkers, "length": args.walk_length,
+                                     "layout": "step-major memory (the reference's own)",
+                                     "fraction_of_trace_alive": m["fraction_of_trace_alive"]},
+                          "checked": m["checked"], "roofline": m["roofline"]}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -632,48 +762,43 @@ PIPELINES = {
 }
 
 
-def run_pipeline(args):
-    """Secondary workloads: the two pipelines around weighted sampling, driven through the registered TorchScript
-    methods, so that `--impl reference` runs the very same Python loop on the reference's own CUDA library.  One GPU;
-    a step is one minibatch; seeds come from pinned host memory inside the timed region."""
-    rank, world, local = dist_env()
-    if rank != 0:
-        return
-    import torch
+def measure_pipeline(torch, workload, impl, device, steps, warmup, graph=None):
+    """The two pipelines around weighted sampling, driven through the registered TorchScript methods, so that
+    impl="reference" runs the very same Python loop on the reference's own CUDA library.  One GPU; a step is one
+    minibatch; seeds come from pinned host memory inside the timed region.  `graph` = (indptr, indices) to reuse."""
     from graph_sampling_b200.synthetic import rmat_csc, seed_batches
-    cfg = PIPELINES[args.workload]
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    Graph, gs_ops = _load_face(args.impl)
+    cfg = PIPELINES[workload]
+    Graph, gs_ops = _load_face(impl)
     t0 = time.time()
-    kw = {"symmetric": True, "max_degree": MAX_DEGREE} if cfg["symmetric"] else {}
-    graph_seed = GRAPH_SEED if args.workload == "adaptive" else GRAPH_SEED + 3
-    indptr, indices = rmat_csc(cfg["nodes"], cfg["edges"], seed=graph_seed, device=device, **kw)
-    torch.cuda.synchronize()
-    torch.cuda.empty_cache()
-    n = cfg["nodes"]
-    info = {"nodes": n, "edges": int(indices.numel()), "gen_seconds": round(time.time() - t0, 2)}
+    if graph is None:
+        kw = {"symmetric": True, "max_degree": MAX_DEGREE} if cfg["symmetric"] else {}
+        graph_seed = GRAPH_SEED if workload == "adaptive" else GRAPH_SEED + 3
+        indptr, indices = rmat_csc(cfg["nodes"], cfg["edges"], seed=graph_seed, device=device, **kw)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+    else:
+        indptr, indices = graph
+    n = int(indptr.numel() - 1)
+    info = {"nodes": n, "edges": int(indices.numel())}
+    gen_s = round(time.time() - t0, 2)
     gen = torch.Generator(device=device)
     gen.manual_seed(GRAPH_SEED + 11)
     G = Graph(False)
     G._CAPI_LoadCSC(indptr, indices)
     X = None
-    if args.workload == "ladies":
+    if workload == "ladies":
         w = 1.0 - torch.rand(indices.numel(), generator=gen, device=device)  # (0, 1]
         G._CAPI_SetData(w)
     else:
         X = torch.randn(n, 256, generator=gen, device=device)
-    steps, warmup = max(1, min(args.steps, 200)), max(3, min(args.warmup, 10))
     batches = seed_batches(n, cfg["batch"], steps + warmup, seed=GRAPH_SEED + 12, device="cpu").pin_memory()
 
     def fn(host_seeds):
         seeds = host_seeds.to(device, non_blocking=True)
-        if args.workload == "ladies":
+        if workload == "ladies":
             return ladies_batch(torch, gs_ops, G, seeds, cfg["fanouts"])
         return adaptive_batch(torch, gs_ops, G, X, seeds, cfg["fanouts"])
 
-    sampler = ClockSampler(physical_gpu_index(local))
-    sampler.start()
     for b in range(warmup):
         fn(batches[b])
     torch.cuda.synchronize()
@@ -684,19 +809,115 @@ def run_pipeline(args):
         edges += fn(batches[b])
     ev1.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
     seconds = ev0.elapsed_time(ev1) / 1e3
-    print(json.dumps({"metric": METRIC, "value": edges / seconds, "unit": UNIT, "n_gpus": 1, "steps": steps,
-                      "warmup": warmup, "ms_per_step": seconds / steps * 1e3, "higher_is_better": True,
+    return {"value": edges / seconds, "unit": UNIT, "steps": steps, "warmup": warmup, "ms_per_step": seconds / steps * 1e3,
+            "edges_per_step": edges / steps, "graph": info, "graph_gen_seconds": gen_s, "batch": cfg["batch"],
+            "fanouts": cfg["fanouts"], "counted": cfg["unit_text"], "workload": cfg["text"]}
+
+
+def run_pipeline(args):
+    """`--workload ladies|adaptive`: prints its own JSON line."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    import torch
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    steps, warmup = max(1, min(args.steps, 200)), max(3, min(args.warmup, 10))
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    m = measure_pipeline(torch, args.workload, args.impl, device, steps, warmup)
+    clocks = sampler.stop()
+    print(json.dumps({"metric": METRIC, "value": m["value"], "unit": UNIT, "n_gpus": 1, "steps": steps,
+                      "warmup": warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True,
                       "scaling": "weak", "vs_baseline": None, "dtype": "int64 ids, f32 weights", "data": "synthetic",
                       "impl": args.impl,
-                      "config": {"workload": cfg["text"], "graph": info, "batch": cfg["batch"],
-                                 "fanouts": cfg["fanouts"], "counted": cfg["unit_text"],
+                      "config": {"workload": m["workload"], "graph": m["graph"], "batch": m["batch"],
+                                 "fanouts": m["fanouts"], "counted": m["counted"],
                                  "face": "TorchScript classes (same call sequence for both arms)",
                                  "l2": "graph (and features) larger than L2, read at random"},
-                      "edges_per_step": edges / steps, "clocks": clocks,
-                      "e2e": {"value": edges / seconds, "unit": UNIT, "h2d_bytes_per_step": cfg["batch"] * 8,
-                              "d2h_bytes_per_step": 8 * len(cfg["fanouts"])}}))
+                      "edges_per_step": m["edges_per_step"], "clocks": clocks,
+                      "e2e": {"value": m["value"], "unit": UNIT, "h2d_bytes_per_step": m["batch"] * 8,
+                              "d2h_bytes_per_step": 8 * len(m["fanouts"])}}))
+
+
+def measure_small_sage(torch, impl, device, group=125, steps=3):
+    """The small GraphSAGE configuration: R-MAT 100,000 nodes / 2,000,000 directed edges, 1,000 minibatches of 1,024
+    seeds drawn from all nodes, fanouts [10, 5], relabel per hop.  Ours: the batched sampler; reference: its own
+    super-batch loop on its library.  A step is one pass over the 1,000 minibatches."""
+    from graph_sampling_b200.synthetic import rmat_csc, seed_batches
+    indptr, indices = rmat_csc(100_000, 2_000_000, seed=GRAPH_SEED - 1, device=device)
+    batches = seed_batches(100_000, BATCH, 1000, seed=GRAPH_SEED + 20, device="cpu").pin_memory()
+    fan = [10, 5]
+    ptr_cache = {}
+
+    def ptr_for(g, s0):
+        if g not in ptr_cache:
+            ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * s0
+        return ptr_cache[g]
+
+    if impl == "reference":
+        torch.classes.load_library(os.path.join(ROOT, "oracle", "_ref", "libgs_ref.so"))
+        G = torch.classes.gs_classes.Graph(False)
+        G._CAPI_LoadCSC(indptr, indices)
+
+        def call(sb, first, step_no):
+            seeds, ptr = sb.reshape(-1), ptr_for(*sb.shape)
+            edges = 0
+            for k in fan:
+                sub = G._CAPI_FusedColumnwiseSlicingSampling(seeds, k, False)
+                sub_indptr, sub_indices, _ = sub._CAPI_GetCSC()
+                seeds, ptr, _, _ = torch.ops.gs_ops._CAPI_BatchCSRRelabel(seeds, ptr, sub_indices, sub_indptr[ptr])
+                edges += int(sub_indices.numel())
+            return edges, None
+    else:
+        from graph_sampling_b200 import ops
+        arena = ops.OutputArena()
+        ids = torch.arange(1000, dtype=torch.int64, device=device)
+
+        def call(sb, first, step_no):
+            hops = ops.sage_sample_batches(indptr, indices, sb.reshape(-1), ptr_for(*sb.shape), fan, seed=RUN_SEED + 8 * step_no,
+                                           arena=arena, batch_ids=ids[first:first + sb.shape[0]], seeds_distinct=True)
+            return sum(int(h["indices"].numel()) for h in hops), None
+
+    st = Stepper(torch, call, batches, group, device)
+    seconds, edges = timed_steps(torch, st, 1, steps, lambda: None, float, min_seconds=0.0, min_repeats=1, max_repeats=1)
+    return {"value": edges / seconds[0], "unit": UNIT, "steps": steps, "ms_per_step": seconds[0] / steps * 1e3,
+            "edges_per_step": edges / steps, "graph": {"nodes": 100_000, "edges": int(indices.numel())}, "group": group,
+            "workload": "GraphSAGE 2-hop uniform sampling, fanouts [10,5], 1,024 seeds/batch, 100,000-node R-MAT graph, "
+                        "relabel per hop; seeds from pinned host memory; a step = 1,000 minibatches"}
+
+
+def secondary_workloads(args, impl, device, indptr, indices):
+    """Short legs of the other four configurations, after the headline, on one GPU: each arm runs them with its own
+    library (same Python loops).  A leg that fails is reported with its error, never fatal."""
+    import torch
+    out = {}
+
+    def leg(name, fn):
+        t0 = time.time()
+        try:
+            out[name] = fn()
+        except Exception as exc:
+            out[name] = {"error": str(exc).splitlines()[0][:200]}
+        out[name]["wall_seconds"] = round(time.time() - t0, 1)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+
+    leg("small_2hop", lambda: measure_small_sage(torch, impl, device))
+    leg("adaptive", lambda: measure_pipeline(torch, "adaptive", impl, device, 40, 5, graph=(indptr, indices)))
+    leg("layerwise", lambda: measure_pipeline(torch, "ladies", impl, device, 100, 5))
+
+    def walk():
+        m = measure_walk(torch, args, impl, device, steps=3, warmup=1)
+        return {"value": m["units"] / m["seconds"], "unit": "walker steps/s", "ms_per_step": m["seconds"] / m["steps"] * 1e3,
+                "steps": m["steps"], "graph": m["graph"], "graph_gen_seconds": m["graph_gen_seconds"],
+                "walkers": args.walkers, "length": args.walk_length, "checked": m["checked"],
+                "checks_pass": m["checks_pass"], "fraction_of_trace_alive": m["fraction_of_trace_alive"],
+                "roofline": m["roofline"]}
+
+    leg("random_walk", walk)
+    return out
 
 
 def run_kernels(args):

@@ -35,6 +35,32 @@ def declared_symbols(header_path=HEADER_PATH):
     return sorted(set(re.findall(r"GSB_API\s+[\w\s\*]+?\b(gsb_\w+)\s*\(", text)))
 
 
+_CTYPES = {"int": ctypes.c_int, "int64_t": ctypes.c_int64, "uint64_t": ctypes.c_uint64, "size_t": ctypes.c_size_t,
+           "double": ctypes.c_double, "float": ctypes.c_float}
+
+
+def declared_prototypes(header_path=HEADER_PATH):
+    """{name: (restype, [argtypes])} for every GSB_API function of the public header.  Pointers of any kind
+    become c_void_p (callers pass raw device addresses, ctypes arrays or byref objects); `const char*` results
+    become c_char_p.  Binding with explicit argument types makes a call with the wrong number of arguments raise
+    instead of corrupting the stack."""
+    text = re.sub(r"/\*.*?\*/", " ", open(header_path).read(), flags=re.S)
+    protos = {}
+    for ret, name, args in re.findall(r"GSB_API\s+([\w\s\*]+?)\b(gsb_\w+)\s*\(([^)]*)\)\s*;", text):
+        ret = " ".join(ret.split())
+        restype = ctypes.c_char_p if ret == "const char*" else _CTYPES[ret]
+        argtypes = []
+        for a in [x.strip() for x in args.split(",")]:
+            if a in ("void", ""):
+                continue
+            if "*" in a:
+                argtypes.append(ctypes.c_void_p)
+            else:
+                argtypes.append(_CTYPES[a.replace("const ", "").split()[0]])
+        protos[name] = (restype, argtypes)
+    return protos
+
+
 def load():
     """Loads the library once; raises if it is absent (build with `python -m graph_sampling_b200.build`)."""
     global _lib
@@ -49,16 +75,10 @@ def load():
         missing = [s for s in declared_symbols() if not hasattr(lib, s)]
         if missing:
             raise ImportError(f"{LIB_PATH} lacks symbols declared in gsb200.h: {missing}")
-        lib.gsb_status_string.restype = ctypes.c_char_p
-        lib.gsb_last_error_message.restype = ctypes.c_char_p
-        lib.gsb_version.restype = ctypes.c_char_p
-        lib.gsb_launch_count.restype = c_i64
-        lib.gsb_launch_count.argtypes = [c_vp]
-        lib.gsb_ctx_create.argtypes = [c_int, ctypes.POINTER(c_vp)]
-        lib.gsb_ctx_destroy.argtypes = [c_vp]
-        lib.gsb_last_error_message.argtypes = [c_vp]
-        lib.gsb_check_device_status.argtypes = [c_vp, c_vp]
-        lib.gsb_read_counts.argtypes = [c_vp, c_vp, c_i64p, c_i64p]
+        for name, (restype, argtypes) in declared_prototypes().items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
         _lib = lib
         return lib
 

@@ -285,7 +285,8 @@ extern "C" {
 
 int gsb_batch_encode(gsb_ctx* ctx, void* stream_, const int64_t* data, const int64_t* data_ptr, int64_t G, int64_t n,
                      int64_t encoding_size, int64_t* out) {
-  GSB_REQUIRE(ctx && data_ptr && G >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(data_ptr && G >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (n == 0) return GSB_OK;
   GSB_REQUIRE(data && out, GSB_ERR_INVALID_ARGUMENT);
   ScopedKernelTimer timer(ctx, KID_OTHER, (cudaStream_t)stream_);
@@ -297,7 +298,8 @@ int gsb_batch_encode(gsb_ctx* ctx, void* stream_, const int64_t* data, const int
 
 int gsb_batch_decode(gsb_ctx* ctx, void* stream_, const int64_t* data, int64_t n, int64_t encoding_size,
                      int64_t* out) {
-  GSB_REQUIRE(ctx && n >= 0 && encoding_size > 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(n >= 0 && encoding_size > 0, GSB_ERR_INVALID_ARGUMENT);
   if (n == 0) return GSB_OK;
   GSB_REQUIRE(data && out, GSB_ERR_INVALID_ARGUMENT);
   ScopedKernelTimer timer(ctx, KID_OTHER, (cudaStream_t)stream_);
@@ -309,7 +311,8 @@ int gsb_batch_decode(gsb_ctx* ctx, void* stream_, const int64_t* data, int64_t n
 
 int gsb_get_batch_offsets(gsb_ctx* ctx, void* stream_, const int64_t* data, int64_t n, int64_t num_batches,
                           int64_t encoding_size, int64_t* out_ptr, int64_t* out_decoded) {
-  GSB_REQUIRE(ctx && n >= 0 && num_batches >= 0 && encoding_size > 0 && out_ptr, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(n >= 0 && num_batches >= 0 && encoding_size > 0 && out_ptr, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(n == 0 || data, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   {
@@ -325,7 +328,8 @@ int gsb_get_batch_offsets(gsb_ctx* ctx, void* stream_, const int64_t* data, int6
 int gsb_batch_concat(gsb_ctx* ctx, void* stream_, const int64_t* const* data_ptrs_host,
                      const int64_t* const* offset_ptrs_host, const int64_t* lens_host, int num_arrays, int64_t G,
                      int64_t* out, int64_t* out_key, int64_t* out_ptr) {
-  GSB_REQUIRE(ctx && data_ptrs_host && offset_ptrs_host && lens_host && out_ptr && G >= 1, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(data_ptrs_host && offset_ptrs_host && lens_host && out_ptr && G >= 1, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(num_arrays >= 1 && num_arrays <= GSB_MAX_CONCAT, GSB_ERR_UNSUPPORTED);
   PtrTable t{};
   t.n = num_arrays;
@@ -356,7 +360,8 @@ int gsb_batch_concat(gsb_ctx* ctx, void* stream_, const int64_t* const* data_ptr
 
 int gsb_batch_split(gsb_ctx* ctx, void* stream_, const int64_t* data, const int64_t* data_ptr, int64_t n, int64_t G,
                     int64_t* const* out_data_host, const int64_t* const* out_ptr_host, int num_arrays) {
-  GSB_REQUIRE(ctx && data_ptr && out_data_host && out_ptr_host && n >= 0 && G >= 1, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(data_ptr && out_data_host && out_ptr_host && n >= 0 && G >= 1, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(num_arrays >= 1 && num_arrays <= GSB_MAX_CONCAT, GSB_ERR_UNSUPPORTED);
   if (n == 0) return GSB_OK;
   GSB_REQUIRE(data, GSB_ERR_INVALID_ARGUMENT);
@@ -377,7 +382,8 @@ int gsb_batch_split(gsb_ctx* ctx, void* stream_, const int64_t* data, const int6
 int gsb_batch_list_sample(gsb_ctx* ctx, void* stream_, const float* probs, int64_t N, const int64_t* range,
                           int64_t G, int64_t k, uint64_t seed, int64_t* out_idx, int64_t* out_range,
                           int64_t* n_out_host) {
-  GSB_REQUIRE(ctx && range && out_range && N >= 0 && G >= 1 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(range && out_range && N >= 0 && G >= 1 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(N < 0xFFFFFFFFll && G < (1ll << 23), GSB_ERR_UNSUPPORTED);
   GSB_REQUIRE(N == 0 || (probs && (out_idx || k == 0)), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;

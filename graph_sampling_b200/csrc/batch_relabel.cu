@@ -24,31 +24,24 @@
 
 namespace gsb {
 
-constexpr int kBThreads = 256;
-constexpr int kBPerThread = 4;
-constexpr int kBTile = kBThreads * kBPerThread;
-
-struct BatchLayout {
-  const i64* seeds;
-  const i64* seeds_ptr;    // [G + 1]
-  const i64* indices;
-  const i64* indices_ptr;  // [G + 1]
-  i64 G;
-  i64* item_off;    // [G + 1]  seeds_ptr[b] + indices_ptr[b]
-  i64* region_off;  // [G + 1]  slot offsets
-  u64* slots;
-  i64 slot_capacity;
-};
-
 
 // One CTA: per-batch item offsets and / or table regions (exclusive scan over the G region sizes).
 // bound_k < 0: regions sized from the batches' actual item counts (needs indices_ptr); bound_k >= 0:
 // regions sized from the upper bound seeds * (1 + bound_k), which is known before sampling.
 // what & 1: write region_off; what & 2: write item_off.
-__global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters, i64 bound_k, int what) {
+// seeds_bound / edges_bound: what the caller sized grids, scratch and outputs for.  Device-side totals above them
+// record GSB_ERR_CAPACITY and set CNT_ABORT, which makes the kernels that follow in the call return at once.
+__global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters, i64 bound_k, int what,
+                                                            i64 seeds_bound, i64 edges_bound) {
   __shared__ i64 s_scan[33];
   __shared__ i64 s_carry;
-  if (threadIdx.x == 0) s_carry = 0;
+  if (threadIdx.x == 0) {
+    s_carry = 0;
+    const i64 ns = L.seeds_ptr[L.G], ne = L.indices_ptr[L.G];
+    const bool over = ns > seeds_bound || ne > edges_bound || ns < 0 || ne < 0;
+    counters[CNT_ABORT] = over ? 1 : 0;
+    if (over) raise_error(counters, GSB_ERR_CAPACITY, ns > seeds_bound ? ns : ne);
+  }
   __syncthreads();
   for (i64 b0 = 0; b0 < L.G; b0 += kBThreads) {
     const i64 b = b0 + threadIdx.x;
@@ -70,7 +63,10 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
     if (what & 2) L.item_off[L.G] = L.seeds_ptr[L.G] + L.indices_ptr[L.G];
     if (what & 1) {
       L.region_off[L.G] = s_carry;
-      if (s_carry > L.slot_capacity) raise_error(counters, GSB_ERR_CAPACITY, s_carry);
+      if (s_carry > L.slot_capacity) {
+        counters[CNT_ABORT] = 1;
+        raise_error(counters, GSB_ERR_CAPACITY, s_carry);
+      }
     }
   }
 }
@@ -99,38 +95,9 @@ __device__ __forceinline__ ItemRef resolve_item(const BatchLayout& L, i64 g) {
   return r;
 }
 
-// ---- traversal by warp tiles ------------------------------------------------------------------------
-// A warp owns kWarpItems consecutive items, lane-strided so that loads coalesce.  Items are batch-major,
-// so almost every tile lies inside ONE batch: the batch is found once per tile (one binary search per
-// 128 items instead of one per item) and its parameters stay in warp-uniform registers.  The rare tile
-// that straddles a batch boundary resolves each item on its own (resolve_item).  Each lane first issues
-// the loads of its four ids, then the four home-slot probes, so four independent memory round trips are
-// in flight per lane; only a collision enters the probing loop.
-constexpr int kLaneItems = 4;
-constexpr int kWarpItems = 32 * kLaneItems;
-
-struct BatchUniform {
-  i64 batch, begin, next_begin, seeds_begin, num_seeds, edges_begin;
-  u64* region;
-  i64 size;
-};
-
-__device__ __forceinline__ BatchUniform load_batch(const BatchLayout& L, const i64* __restrict__ off, i64 b) {
-  BatchUniform u;
-  u.batch = b;
-  u.begin = __ldg(off + b);
-  u.next_begin = __ldg(off + b + 1);
-  u.seeds_begin = __ldg(L.seeds_ptr + b);
-  u.num_seeds = __ldg(L.seeds_ptr + b + 1) - u.seeds_begin;
-  u.edges_begin = __ldg(L.indices_ptr + b);
-  const i64 ro = __ldg(L.region_off + b);
-  u.region = L.slots + ro;
-  u.size = __ldg(L.region_off + b + 1) - ro;
-  return u;
-}
-
 template <int ITEMS>
 __global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
+  if (counters[CNT_ABORT] != 0) return;
   constexpr int kTileI = 32 * ITEMS;
   const int lane = threadIdx.x & 31;
   const i64 n = L.item_off[L.G];
@@ -188,11 +155,6 @@ __global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* 
   }
 }
 
-struct CompactOut {
-  i64* unique;      // all frontiers back to back
-  i64* unique_ptr;  // [G + 1]
-};
-
 // One CTA per tile of kBTile items; each of its 8 warps covers kWarpItems consecutive items.  First-
 // occurrence flags are ranked with ballots, the 8 warp totals are combined through shared memory (one
 // barrier) and warp 0 fetches the tile prefix from the look-back chain.
@@ -201,6 +163,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
   static_assert(kBTile == (kBThreads / 32) * kWarpItems, "tile geometry");
   __shared__ i64 s_warp_total[kBThreads / 32];
   __shared__ i64 s_base;
+  if (counters[CNT_ABORT] != 0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const i64 n = L.item_off[L.G];
   const int tile = blockIdx.x;
@@ -319,7 +282,8 @@ __global__ void __launch_bounds__(kBThreads) k_batch_compact(BatchLayout L, Comp
 }
 
 __global__ void __launch_bounds__(kBThreads) k_batch_relabel(BatchLayout L, const i64* __restrict__ unique_ptr,
-                                                             i64* __restrict__ out_relabeled) {
+                                                             i64* __restrict__ out_relabeled, const i64* counters) {
+  if (counters[CNT_ABORT] != 0) return;
   const int lane = threadIdx.x & 31;
   const i64 E = L.indices_ptr[L.G];
   const i64 warps = (i64)gridDim.x * (kBThreads / 32);
@@ -374,11 +338,13 @@ __global__ void __launch_bounds__(kBThreads) k_batch_relabel(BatchLayout L, cons
   }
 }
 
+// S = number of entries of sub_indptr minus one; an offset beyond it (a caller's bound that does not hold) is clamped
+// here and reported by the layout kernel that follows.
 __global__ void __launch_bounds__(kBThreads) k_gather_offsets(const i64* __restrict__ sub_indptr,
-                                                              const i64* __restrict__ seeds_ptr, i64 G,
+                                                              const i64* __restrict__ seeds_ptr, i64 G, i64 S,
                                                               i64* __restrict__ out) {
   const i64 b = (i64)blockIdx.x * kBThreads + threadIdx.x;
-  if (b <= G) out[b] = sub_indptr[seeds_ptr[b]];
+  if (b <= G) out[b] = sub_indptr[max((i64)0, min(seeds_ptr[b], S))];
 }
 
 // Per-batch offset arrays cut out of one offset array: batch b receives indptr[offsets[b] .. offsets[b+1]]
@@ -590,7 +556,8 @@ __global__ void k_set_single_batch_ptrs(i64* seeds_ptr, i64* indices_ptr, i64 S,
 
 // Everything k_batch_layout derives, for exactly one batch: offsets, item count and the one table region.
 __global__ void k_single_batch_setup(i64* seeds_ptr, i64* indices_ptr, i64* item_off, i64* region_off, i64 S, i64 E,
-                                     i64 region_size) {
+                                     i64 region_size, i64* counters) {
+  counters[CNT_ABORT] = 0;
   seeds_ptr[0] = 0;
   seeds_ptr[1] = S;
   indices_ptr[0] = 0;
@@ -601,75 +568,77 @@ __global__ void k_single_batch_setup(i64* seeds_ptr, i64* indices_ptr, i64* item
   region_off[1] = region_size;
 }
 
-}  // namespace gsb
-
-using namespace gsb;
-
-extern "C" {
-
-int gsb_split_indptr(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* offsets, int64_t G,
-                     int64_t uniform_size, int64_t* out) {
-  GSB_REQUIRE(ctx && G >= 0 && (offsets || uniform_size >= 0), GSB_ERR_INVALID_ARGUMENT);
-  if (G == 0) return GSB_OK;
-  GSB_REQUIRE(indptr && out, GSB_ERR_INVALID_ARGUMENT);
-  cudaStream_t stream = (cudaStream_t)stream_;
-  ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-  k_split_indptr<<<max(1, min(grid_for(G * 32, kBThreads), kNumSMs * 8)), kBThreads, 0, stream>>>(indptr, offsets, G,
-                                                                                                  uniform_size, out);
-  GSB_LAUNCH_OK();
+// ---- unique + relabel of G minibatches: chooses between direct-address tables and hash-table regions -------------
+static int read_totals(gsb_ctx* ctx, cudaStream_t stream, i64* unique_total_host, i64* edges_total_host) {
+  const i64* c;
+  int st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
+  if (st != GSB_OK) return st;
+  if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
+  if (edges_total_host) *edges_total_host = c[CNT_NNZ];
+  if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
   return GSB_OK;
 }
 
-int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream_, const int64_t* sub_indptr, const int64_t* seeds_ptr,
-                           int64_t G, int64_t* out_indices_ptr) {
-  GSB_REQUIRE(ctx && sub_indptr && seeds_ptr && out_indices_ptr && G >= 0, GSB_ERR_INVALID_ARGUMENT);
-  cudaStream_t stream = (cudaStream_t)stream_;
-  ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-  k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(sub_indptr, seeds_ptr, G, out_indices_ptr);
-  GSB_LAUNCH_OK();
-  return GSB_OK;
-}
-
-int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, const int64_t* seeds_ptr,
-                             int64_t num_seeds, const int64_t* indices, const int64_t* indices_ptr,
-                             int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
-                             int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host) {
-  GSB_REQUIRE(ctx && seeds_ptr && indices_ptr && out_unique_ptr && G >= 1 && num_seeds >= 0 && indices_capacity >= 0,
-              GSB_ERR_INVALID_ARGUMENT);
-  const i64 n_cap = num_seeds + indices_capacity;
-  GSB_REQUIRE(n_cap < (1ll << 31), GSB_ERR_UNSUPPORTED);
-  GSB_REQUIRE(n_cap == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
-  cudaStream_t stream = (cudaStream_t)stream_;
+// L carries seeds / seeds_ptr / indices / indices_ptr / G; scratch fields are filled here.  seeds_bound / edges_bound
+// are what the caller sized the outputs for (the exact counts are read on the device).
+static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 seeds_bound, i64 edges_bound,
+                           i64 num_nodes, int flags, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled) {
+  const i64 G = L.G;
+  const i64 n_cap = seeds_bound + edges_bound;
+  i64* counters = ctx_counters(ctx);
+  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
+  const i64 path = ctx_option(ctx, GSB_OPT_RELABEL_PATH);
+  u64* tables = nullptr;
+  uint32_t epoch = 0;
+  if (path != 1 && num_nodes > 0 && num_nodes < 0xFFFFFFFFll) {
+    int st = ctx_direct_tables(ctx, G, num_nodes, stream, &tables, &epoch);
+    if (st != GSB_OK) return st;
+  }
+  if (path == 2 && !tables) return num_nodes > 0 ? GSB_ERR_OUT_OF_MEMORY : GSB_ERR_INVALID_ARGUMENT;
+  void* ws;
+  if (tables) {
+    const size_t rank_bytes = ((size_t)n_cap * 4 + 255) & ~(size_t)255;
+    int st = ctx_reserve_workspace(ctx, off_bytes + rank_bytes, &ws);
+    if (st != GSB_OK) return st;
+    L.item_off = (i64*)ws;
+    L.region_off = nullptr;
+    L.slots = nullptr;
+    L.slot_capacity = 0;
+    {
+      ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+      k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 2, seeds_bound, edges_bound);
+    }
+    GSB_LAUNCH_OK();
+    DirectTables T;
+    T.words = tables;
+    T.num_nodes = num_nodes;
+    T.epoch_hi = (u64)(~epoch) << 32;
+    T.rank_of_item = (uint32_t*)((char*)ws + off_bytes);
+    T.seeds_distinct = (flags & GSB_SEEDS_DISTINCT) ? 1 : 0;
+    return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr,
+                                        out_relabeled);
+  }
   const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
-  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
-  void* ws;
   int st = ctx_reserve_workspace(ctx, slots_bytes + 2 * off_bytes, &ws);
   if (st != GSB_OK) return st;
-  BatchLayout L;
-  L.seeds = seeds;
-  L.seeds_ptr = seeds_ptr;
-  L.indices = indices;
-  L.indices_ptr = indices_ptr;
-  L.G = G;
   L.slots = (u64*)ws;
   L.item_off = (i64*)((char*)ws + slots_bytes);
   L.region_off = (i64*)((char*)ws + slots_bytes + off_bytes);
   L.slot_capacity = slot_cap;
-  i64* counters = ctx_counters(ctx);
   {
     ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
     GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
   }
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3, seeds_bound, edges_bound);
   }
   GSB_LAUNCH_OK();
   const int wide = kNumSMs * 8;
   {
     ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
-    // one item per lane measured fastest for the insert (more items in flight per lane only add contention
+    // one item per lane measured fastest for the hash insert (more items in flight per lane only add contention
     // on the slots of frequent ids)
     k_batch_insert<1><<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
   }
@@ -684,30 +653,81 @@ int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, 
     k_batch_compact<<<tiles, kBThreads, 0, stream>>>(L, out, counters, ts);
   }
   GSB_LAUNCH_OK();
-  if (indices_capacity > 0 && out_relabeled) {
+  if (edges_bound > 0 && out_relabeled) {
     ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
-    k_batch_relabel<<<max(1, min(grid_for(indices_capacity, kBTile), wide)), kBThreads, 0, stream>>>(
-        L, out_unique_ptr, out_relabeled);
+    k_batch_relabel<<<max(1, min(grid_for(edges_bound, kBTile), wide)), kBThreads, 0, stream>>>(L, out_unique_ptr,
+                                                                                              out_relabeled, counters);
   }
   GSB_LAUNCH_OK();
-  if (unique_total_host || edges_total_host) {
-    const i64* c;
-    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
-    if (st != GSB_OK) return st;
-    if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
-    if (edges_total_host) *edges_total_host = c[CNT_NNZ];
-    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
-  }
   return GSB_OK;
 }
 
-int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, const int64_t* seeds,
-                 const int64_t* seeds_ptr, int64_t G, int64_t S, int64_t k, int replace, uint64_t seed,
-                 int64_t* out_indptr, int64_t* out_indices, int64_t* out_select, int64_t* out_indices_ptr,
-                 int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_relabeled, int64_t* unique_total_host,
-                 int64_t* edges_total_host) {
-  GSB_REQUIRE(ctx && indptr && seeds_ptr && out_indptr && out_indices_ptr && out_unique_ptr && G >= 1 && S >= 0 &&
-                  k >= 0,
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" {
+
+int gsb_split_indptr(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* offsets, int64_t G,
+                     int64_t uniform_size, int64_t* out) {
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(G >= 0 && (offsets || uniform_size >= 0), GSB_ERR_INVALID_ARGUMENT);
+  if (G == 0) return GSB_OK;
+  GSB_REQUIRE(indptr && out, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+  k_split_indptr<<<max(1, min(grid_for(G * 32, kBThreads), kNumSMs * 8)), kBThreads, 0, stream>>>(indptr, offsets, G,
+                                                                                                  uniform_size, out);
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream_, const int64_t* sub_indptr, const int64_t* seeds_ptr,
+                           int64_t G, int64_t* out_indices_ptr) {
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(sub_indptr && seeds_ptr && out_indices_ptr && G >= 0, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+  k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(sub_indptr, seeds_ptr, G,
+                                                                        0x7fffffffffffffffll, out_indices_ptr);
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, const int64_t* seeds_ptr,
+                             int64_t num_seeds, const int64_t* indices, const int64_t* indices_ptr,
+                             int64_t indices_capacity, int64_t G, int64_t num_nodes, int flags, int64_t* out_unique,
+                             int64_t* out_unique_ptr, int64_t* out_relabeled, int64_t* unique_total_host,
+                             int64_t* edges_total_host) {
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(seeds_ptr && indices_ptr && out_unique_ptr && G >= 1 && num_seeds >= 0 && indices_capacity >= 0 &&
+                  num_nodes >= 0,
+              GSB_ERR_INVALID_ARGUMENT);
+  const i64 n_cap = num_seeds + indices_capacity;
+  GSB_REQUIRE(n_cap < (1ll << 30), GSB_ERR_UNSUPPORTED);
+  GSB_REQUIRE(n_cap == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  BatchLayout L;
+  L.seeds = seeds;
+  L.seeds_ptr = seeds_ptr;
+  L.indices = indices;
+  L.indices_ptr = indices_ptr;
+  L.G = G;
+  int st = relabel_batches(ctx, stream, L, num_seeds, indices_capacity, num_nodes, flags, out_unique, out_unique_ptr,
+                           out_relabeled);
+  if (st != GSB_OK) return st;
+  if (unique_total_host || edges_total_host) return read_totals(ctx, stream, unique_total_host, edges_total_host);
+  return GSB_OK;
+}
+
+int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, int64_t num_nodes,
+                 const int64_t* seeds, const int64_t* seeds_ptr, const int64_t* batch_ids, int64_t G, int64_t S,
+                 int64_t k, int replace, uint64_t seed, int flags, int64_t* out_indptr, int64_t* out_indices,
+                 int64_t* out_select, int64_t* out_indices_ptr, int64_t* out_unique, int64_t* out_unique_ptr,
+                 int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host) {
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && seeds_ptr && out_indptr && out_indices_ptr && out_unique_ptr && G >= 1 && S >= 0 && k >= 0 &&
+                  num_nodes >= 0,
               GSB_ERR_INVALID_ARGUMENT);
   const i64 cap = S * k;
   const i64 n_cap = S + cap;
@@ -715,70 +735,26 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
   GSB_REQUIRE(n_cap == 0 || (seeds && out_unique), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(cap == 0 || (indices && out_indices && out_select && out_relabeled), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
-  const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
-  const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
-  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
-  void* ws;
-  int st = ctx_reserve_workspace(ctx, slots_bytes + 2 * off_bytes, &ws);
+  // the exact seed count is seeds_ptr[G] on the device; S only has to bound it (grids, scratch and capacities)
+  int st = sample_uniform_launch(ctx, stream, indptr, indices, num_nodes, seeds, S, k, replace, (u64)seed, out_indptr,
+                                 out_indices, out_select, nullptr, nullptr, nullptr, nullptr, cap, seeds_ptr + G,
+                                 seeds_ptr, batch_ids, G);
   if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(out_indptr, seeds_ptr, G, S,
+                                                                          out_indices_ptr);
+  }
+  GSB_LAUNCH_OK();
   BatchLayout L;
   L.seeds = seeds;
   L.seeds_ptr = seeds_ptr;
   L.indices = out_indices;
   L.indices_ptr = out_indices_ptr;
   L.G = G;
-  L.slots = (u64*)ws;
-  L.item_off = (i64*)((char*)ws + slots_bytes);
-  L.region_off = (i64*)((char*)ws + slots_bytes + off_bytes);
-  L.slot_capacity = slot_cap;
-  i64* counters = ctx_counters(ctx);
-  {
-    ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
-    GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
-  }
-  // the exact seed count is seeds_ptr[G] on the device; S only has to bound it (grids, scratch and capacities)
-  st = sample_uniform_launch(ctx, stream, indptr, indices, seeds, S, k, replace, (u64)seed, out_indptr, out_indices,
-                             out_select, nullptr, nullptr, nullptr, nullptr, cap, seeds_ptr + G);
+  st = relabel_batches(ctx, stream, L, S, cap, num_nodes, flags, out_unique, out_unique_ptr, out_relabeled);
   if (st != GSB_OK) return st;
-  {
-    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(out_indptr, seeds_ptr, G, out_indices_ptr);
-  }
-  GSB_LAUNCH_OK();
-  {
-    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
-  }
-  GSB_LAUNCH_OK();
-  const int wide = kNumSMs * 8;
-  {
-    ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
-    k_batch_insert<1><<<max(1, min(grid_for(n_cap, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters);
-  }
-  GSB_LAUNCH_OK();
-  const int tiles = grid_for(n_cap, kBTile);
-  TileState ts;
-  st = ctx_tile_state(ctx, tiles, stream, &ts);
-  if (st != GSB_OK) return st;
-  CompactOut out{out_unique, out_unique_ptr};
-  {
-    ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
-    k_batch_compact<<<tiles, kBThreads, 0, stream>>>(L, out, counters, ts);
-  }
-  GSB_LAUNCH_OK();
-  if (cap > 0) {
-    ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
-    k_batch_relabel<<<max(1, min(grid_for(cap, kBTile), wide)), kBThreads, 0, stream>>>(L, out_unique_ptr, out_relabeled);
-  }
-  GSB_LAUNCH_OK();
-  if (unique_total_host || edges_total_host) {
-    const i64* c;
-    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
-    if (st != GSB_OK) return st;
-    if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
-    if (edges_total_host) *edges_total_host = c[CNT_NNZ];
-    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
-  }
+  if (unique_total_host || edges_total_host) return read_totals(ctx, stream, unique_total_host, edges_total_host);
   return GSB_OK;
 }
 
@@ -831,7 +807,7 @@ static int build_batch_tables(gsb_ctx* ctx, cudaStream_t stream, const i64* seed
   if (!indices_ptr) GSB_CUDA_OK(cudaMemsetAsync(zero_ptr, 0, off_bytes, stream));
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 3, num_seeds, indices_capacity);
   }
   GSB_LAUNCH_OK();
   const int wide = kNumSMs * 8;
@@ -854,16 +830,6 @@ static int build_batch_tables(gsb_ctx* ctx, cudaStream_t stream, const i64* seed
   return GSB_OK;
 }
 
-static int read_totals(gsb_ctx* ctx, cudaStream_t stream, i64* unique_total_host, i64* edges_total_host) {
-  const i64* c;
-  int st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 4, &c);
-  if (st != GSB_OK) return st;
-  if (unique_total_host) *unique_total_host = c[CNT_UNIQUE];
-  if (edges_total_host) *edges_total_host = c[CNT_NNZ];
-  if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
-  return GSB_OK;
-}
-
 }  // namespace gsb
 
 extern "C" {
@@ -871,7 +837,8 @@ extern "C" {
 int gsb_batch_unique(gsb_ctx* ctx, void* stream_, const int64_t* data, const int64_t* data_ptr, int64_t n, int64_t G,
                      int sorted, int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_unique_key,
                      int64_t* unique_total_host) {
-  GSB_REQUIRE(ctx && data_ptr && out_unique_ptr && G >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(data_ptr && out_unique_ptr && G >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(n == 0 || (data && out_unique), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(n < (1ll << 31) && G < (1ll << 31), GSB_ERR_UNSUPPORTED);
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -926,7 +893,8 @@ int gsb_batch_coo_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, con
                           int64_t num_seeds, const int64_t* coo_col, const int64_t* coo_row, const int64_t* coo_ptr,
                           int64_t num_edges, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_row,
                           int64_t* out_col, int64_t* unique_total_host) {
-  GSB_REQUIRE(ctx && seeds_ptr && coo_ptr && out_unique_ptr && G >= 1 && num_seeds >= 0 && num_edges >= 0,
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(seeds_ptr && coo_ptr && out_unique_ptr && G >= 1 && num_seeds >= 0 && num_edges >= 0,
               GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(num_edges == 0 || (coo_col && coo_row && out_row && out_col), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(num_seeds + num_edges == 0 || out_unique, GSB_ERR_INVALID_ARGUMENT);
@@ -939,13 +907,13 @@ int gsb_batch_coo_relabel(gsb_ctx* ctx, void* stream_, const int64_t* seeds, con
     const int grid = max(1, min(grid_for(num_edges, kBTile), kNumSMs * 8));
     {
       ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
-      k_batch_relabel<<<grid, kBThreads, 0, stream>>>(L, out_unique_ptr, out_row);
+      k_batch_relabel<<<grid, kBThreads, 0, stream>>>(L, out_unique_ptr, out_row, ctx_counters(ctx));
     }
     GSB_LAUNCH_OK();
     L.indices = coo_col;
     {
       ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
-      k_batch_relabel<<<grid, kBThreads, 0, stream>>>(L, out_unique_ptr, out_col);
+      k_batch_relabel<<<grid, kBThreads, 0, stream>>>(L, out_unique_ptr, out_col, ctx_counters(ctx));
     }
     GSB_LAUNCH_OK();
   }
@@ -956,7 +924,8 @@ int gsb_batch_coo_slice(gsb_ctx* ctx, void* stream_, int axis, const int64_t* co
                         const int64_t* edge_ptr, int64_t num_edges, const int64_t* members, const int64_t* members_ptr,
                         int64_t num_members, int64_t G, int64_t* out_row, int64_t* out_col, int64_t* out_ptr,
                         int64_t* n_out_host) {
-  GSB_REQUIRE(ctx && G >= 1 && num_edges >= 0 && num_members >= 0 && out_ptr && (axis == 0 || axis == 1),
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(G >= 1 && num_edges >= 0 && num_members >= 0 && out_ptr && (axis == 0 || axis == 1),
               GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((edge_ptr && members_ptr) || (G == 1 && !edge_ptr && !members_ptr), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(num_edges == 0 || (coo_row && coo_col && out_row && out_col), GSB_ERR_INVALID_ARGUMENT);
@@ -1024,7 +993,7 @@ int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i
   }
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_single_batch_setup<<<1, 1, 0, stream>>>(seeds_ptr, indices_ptr, L.item_off, L.region_off, S, E, region);
+    k_single_batch_setup<<<1, 1, 0, stream>>>(seeds_ptr, indices_ptr, L.item_off, L.region_off, S, E, region, counters);
   }
   GSB_LAUNCH_OK();
   const int wide = kNumSMs * 8;
@@ -1046,7 +1015,8 @@ int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i
   GSB_LAUNCH_OK();
   if (E > 0 && out_relabeled) {
     ScopedKernelTimer timer(ctx, KID_RELABEL, stream);
-    k_batch_relabel<<<max(1, min(grid_for(E, kBTile), wide)), kBThreads, 0, stream>>>(L, L.item_off + 8, out_relabeled);
+    k_batch_relabel<<<max(1, min(grid_for(E, kBTile), wide)), kBThreads, 0, stream>>>(L, L.item_off + 8, out_relabeled,
+                                                                                      counters);
   }
   GSB_LAUNCH_OK();
   const i64* c;

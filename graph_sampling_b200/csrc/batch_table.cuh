@@ -91,15 +91,94 @@ __device__ __forceinline__ void for_each_item_with_batch(const i64* __restrict__
   }
 }
 
+// ---- layout of a super-batch call (shared by the hash-table and the direct-address kernels) ----------------
+constexpr int kBThreads = 256;
+constexpr int kBPerThread = 4;
+constexpr int kBTile = kBThreads * kBPerThread;
+
+struct BatchLayout {
+  const i64* seeds;
+  const i64* seeds_ptr;    // [G + 1]
+  const i64* indices;
+  const i64* indices_ptr;  // [G + 1]
+  i64 G;
+  i64* item_off;    // [G + 1]  seeds_ptr[b] + indices_ptr[b]
+  i64* region_off;  // [G + 1]  slot offsets
+  u64* slots;
+  i64 slot_capacity;
+};
+
+
+// ---- traversal by warp tiles ------------------------------------------------------------------------
+// A warp owns kWarpItems consecutive items, lane-strided so that loads coalesce.  Items are batch-major,
+// so almost every tile lies inside ONE batch: the batch is found once per tile (one binary search per
+// 128 items instead of one per item) and its parameters stay in warp-uniform registers.  The rare tile
+// that straddles a batch boundary resolves each item on its own (resolve_item).  Each lane first issues
+// the loads of its four ids, then the four home-slot probes, so four independent memory round trips are
+// in flight per lane; only a collision enters the probing loop.
+constexpr int kLaneItems = 4;
+constexpr int kWarpItems = 32 * kLaneItems;
+
+struct BatchUniform {
+  i64 batch, begin, next_begin, seeds_begin, num_seeds, edges_begin;
+  u64* region;
+  i64 size;
+};
+
+template <bool WITH_REGION = true>
+__device__ __forceinline__ BatchUniform load_batch(const BatchLayout& L, const i64* __restrict__ off, i64 b) {
+  BatchUniform u;
+  u.batch = b;
+  u.begin = __ldg(off + b);
+  u.next_begin = __ldg(off + b + 1);
+  u.seeds_begin = __ldg(L.seeds_ptr + b);
+  u.num_seeds = __ldg(L.seeds_ptr + b + 1) - u.seeds_begin;
+  u.edges_begin = __ldg(L.indices_ptr + b);
+  u.region = nullptr;
+  u.size = 0;
+  if (WITH_REGION) {
+    const i64 ro = __ldg(L.region_off + b);
+    u.region = L.slots + ro;
+    u.size = __ldg(L.region_off + b + 1) - ro;
+  }
+  return u;
+}
+
+// Direct-address tables of a super-batch call: table b (num_nodes words) belongs to minibatch b.  A word is
+// [~epoch : 32 | key : 32]; atomicMin keeps, per node id, the smallest key of the CURRENT call (a larger epoch gives
+// a smaller upper half, so entries of earlier calls lose against any entry of this one and the tables are never
+// cleared).  Keys grow with the position of an item inside its minibatch: a seed's key is its index among the
+// minibatch's seeds, a sampled neighbour's key is kEdgeKeyBit | its position in the call's edge array.
+struct DirectTables {
+  u64* words;
+  i64 num_nodes;
+  u64 epoch_hi;            // (u64)(~epoch) << 32
+  uint32_t* rank_of_item;  // [items of the call]: frontier position of an item that is a first occurrence
+  int seeds_distinct;      // the caller promises that no id repeats among the seeds of a minibatch
+};
+constexpr uint32_t kEdgeKeyBit = 0x80000000u;
+
+// insert -> first-occurrence compaction -> relabel with direct-address tables (defined in direct_relabel.cu).
+// L.item_off must be valid (k_batch_layout); n_cap / e_cap bound the items / edges of the call.
+int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchLayout& L, const DirectTables& T,
+                                 i64 n_cap, i64 e_cap, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
+
+struct CompactOut {
+  i64* unique;      // all frontiers back to back
+  i64* unique_ptr;  // [G + 1]
+};
+
+
 // Single-batch unique + relabel through the packed-slot batched kernels (defined in batch_relabel.cu).
 int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i64 S, const i64* second, i64 E,
                           i64* out_unique, i64* out_relabeled, i64* unique_host);
 
 // Uniform sampler shared by gsb_sample_uniform and the batched hop (defined in slice_sample.cu).  With S_dev the
 // exact seed count is read on the device and S is an upper bound that sizes the grid.
-int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
-                          i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,
-                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity,
-                          const i64* S_dev = nullptr);
+int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, i64 num_cols,
+                          const i64* seeds, i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices,
+                          i64* out_select, i64* out_coo_col, const float* data, const i64* e_ids, float* out_data,
+                          i64 capacity, const i64* S_dev = nullptr, const i64* batch_ptr = nullptr,
+                          const i64* batch_ids = nullptr, i64 G = 0);
 
 }  // namespace gsb

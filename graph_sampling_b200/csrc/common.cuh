@@ -21,6 +21,12 @@ typedef unsigned long long u64;
     if (!(cond)) return (code); \
   } while (0)
 
+#define GSB_ENTER(ctx)                   \
+  do {                                   \
+    int _st = gsb::ctx_enter(ctx);       \
+    if (_st != GSB_OK) return _st;       \
+  } while (0)
+
 namespace gsb {
 
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
@@ -35,6 +41,8 @@ enum CounterSlot {
   CNT_AUX0 = 4,
   CNT_AUX1 = 5,
   CNT_EPOCH = 6,       // device-side epoch base (pipeline mode)
+  CNT_ABORT = 7,       // set by the layout kernel of a super-batch call whose device-side sizes exceed the caller's
+                       // bounds: the kernels that follow return at once instead of writing past their buffers
   CNT_NUM = 64
 };
 
@@ -45,6 +53,7 @@ struct TileState {
   u64* words;
   uint32_t epoch;
   i64* counters;  // for the error flag
+  int max_polls = 1 << 22;  // polls of one look-back window before the wait is given up (GSB_OPT_MAX_POLLS)
 };
 
 constexpr int kEpochBits = 22;
@@ -87,6 +96,16 @@ int ctx_tile_state(gsb_ctx* ctx, i64 num_tiles, cudaStream_t stream, TileState* 
 i64* ctx_counters(gsb_ctx* ctx);
 i64* ctx_pinned(gsb_ctx* ctx);
 int ctx_device(gsb_ctx* ctx);
+// GSB_OK when `ctx` is usable from the calling thread: non-null and created on the CUDA device that is current.
+// Every entry point starts with it, so a context is never driven from another device's stream by mistake.
+int ctx_enter(gsb_ctx* ctx);
+i64 ctx_option(gsb_ctx* ctx, int option);
+// Direct-address tables of the batched unique + relabel: `count` tables of `num_nodes` 64-bit words each, kept by
+// the context between calls and never cleared: a word is [~epoch : 32 | key : 32] and every call uses a larger
+// epoch, so atomicMin lets a current entry replace any stale one.  *out_table is null when the tables would exceed
+// GSB_OPT_DIRECT_TABLE_BUDGET (the caller then takes the hash path).
+int ctx_direct_tables(gsb_ctx* ctx, i64 count, i64 num_nodes, cudaStream_t stream, u64** out_table,
+                      uint32_t* out_epoch);
 int ctx_check_device_error(gsb_ctx* ctx, cudaStream_t stream);
 // Copies `n` counters starting at `first` to pinned memory, synchronises the stream and returns
 // the pinned pointer.

@@ -26,6 +26,11 @@ struct gsb_ctx {
   size_t ev_used;
   double prof_ms[gsb::KID_NUM];
   i64 prof_launches[gsb::KID_NUM];
+  i64 options[GSB_OPT_NUM];
+  // direct-address tables of the batched unique + relabel (see ctx_direct_tables)
+  u64* direct_tables;
+  size_t direct_bytes;
+  uint32_t direct_epoch;
 };
 
 namespace gsb {
@@ -77,6 +82,53 @@ int ctx_tile_state(gsb_ctx* ctx, i64 num_tiles, cudaStream_t stream, TileState* 
   out->words = ctx->tile_words;
   out->epoch = ctx->epoch;
   out->counters = ctx->counters;
+  out->max_polls = (int)ctx->options[GSB_OPT_MAX_POLLS];
+  return GSB_OK;
+}
+
+int ctx_enter(gsb_ctx* ctx) {
+  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return GSB_ERR_CUDA;
+  if (dev != ctx->device) {
+    snprintf(ctx->message, sizeof(ctx->message),
+             "context belongs to CUDA device %d but device %d is current: nothing was launched", ctx->device, dev);
+    return GSB_ERR_INVALID_ARGUMENT;
+  }
+  return GSB_OK;
+}
+
+i64 ctx_option(gsb_ctx* ctx, int option) { return ctx->options[option]; }
+
+int ctx_direct_tables(gsb_ctx* ctx, i64 count, i64 num_nodes, cudaStream_t stream, u64** out_table,
+                      uint32_t* out_epoch) {
+  *out_table = nullptr;
+  *out_epoch = 0;
+  if (count <= 0 || num_nodes <= 0) return GSB_OK;
+  if ((double)count * (double)num_nodes * 8.0 > (double)ctx->options[GSB_OPT_DIRECT_TABLE_BUDGET]) return GSB_OK;
+  const size_t bytes = (size_t)count * (size_t)num_nodes * sizeof(u64);
+  if (bytes > ctx->direct_bytes) {
+    // Growing synchronises the device; it only happens the first time a (batches x nodes) size is seen.
+    GSB_CUDA_OK(cudaDeviceSynchronize());
+    if (ctx->direct_tables) GSB_CUDA_OK(cudaFree(ctx->direct_tables));
+    ctx->direct_tables = nullptr;
+    ctx->direct_bytes = 0;
+    cudaError_t e = cudaMalloc((void**)&ctx->direct_tables, bytes);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();  // not fatal: the caller falls back to the hash tables
+      return GSB_OK;
+    }
+    ctx->direct_bytes = bytes;
+    GSB_CUDA_OK(cudaMemsetAsync(ctx->direct_tables, 0xFF, bytes, stream));
+    ctx->direct_epoch = 0;
+  }
+  ctx->direct_epoch += 1;
+  if (ctx->direct_epoch >= 0xFFFFFFFEu) {  // the 32-bit epoch is used up: start over from cleared tables
+    GSB_CUDA_OK(cudaMemsetAsync(ctx->direct_tables, 0xFF, ctx->direct_bytes, stream));
+    ctx->direct_epoch = 1;
+  }
+  *out_table = ctx->direct_tables;
+  *out_epoch = ctx->direct_epoch;
   return GSB_OK;
 }
 
@@ -161,6 +213,10 @@ int gsb_ctx_create(int device, gsb_ctx** out_ctx) {
   ctx->ev_begin = new std::vector<cudaEvent_t>();
   ctx->ev_end = new std::vector<cudaEvent_t>();
   ctx->ev_kid = new std::vector<int>();
+  ctx->options[GSB_OPT_MAX_POLLS] = 1 << 22;
+  ctx->options[GSB_OPT_TABLE_SLOTS] = 0;
+  ctx->options[GSB_OPT_RELABEL_PATH] = 0;
+  ctx->options[GSB_OPT_DIRECT_TABLE_BUDGET] = 6ll << 30;
   int prev = 0;
   cudaGetDevice(&prev);
   int st = GSB_OK;
@@ -195,6 +251,7 @@ int gsb_ctx_destroy(gsb_ctx* ctx) {
   cudaDeviceSynchronize();
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->tile_words) cudaFree(ctx->tile_words);
+  if (ctx->direct_tables) cudaFree(ctx->direct_tables);
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   for (size_t i = 0; i < ctx->ev_begin->size(); ++i) {
@@ -227,16 +284,42 @@ const char* gsb_status_string(int status) {
 const char* gsb_last_error_message(gsb_ctx* ctx) { return ctx ? ctx->message : ""; }
 
 int gsb_check_device_status(gsb_ctx* ctx, void* stream) {
-  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  GSB_ENTER(ctx);
   return gsb::ctx_check_device_error(ctx, (cudaStream_t)stream);
 }
 
-const char* gsb_version(void) { return "gsb200 0.1 sm_100a"; }
+const char* gsb_version(void) { return "gsb200 0.2 sm_100a"; }
+
+int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value) {
+  if (!ctx || option < 0 || option >= GSB_OPT_NUM) return GSB_ERR_INVALID_ARGUMENT;
+  switch (option) {
+    case GSB_OPT_MAX_POLLS:
+      if (value < 1 || value > (1ll << 30)) return GSB_ERR_INVALID_ARGUMENT;
+      break;
+    case GSB_OPT_TABLE_SLOTS:
+      if (value < 0) return GSB_ERR_INVALID_ARGUMENT;
+      break;
+    case GSB_OPT_RELABEL_PATH:
+      if (value < 0 || value > 2) return GSB_ERR_INVALID_ARGUMENT;
+      break;
+    case GSB_OPT_DIRECT_TABLE_BUDGET:
+      if (value < 0) return GSB_ERR_INVALID_ARGUMENT;
+      break;
+  }
+  ctx->options[option] = value;
+  return GSB_OK;
+}
+
+int gsb_ctx_get_option(gsb_ctx* ctx, int option, int64_t* value_host) {
+  if (!ctx || !value_host || option < 0 || option >= GSB_OPT_NUM) return GSB_ERR_INVALID_ARGUMENT;
+  *value_host = ctx->options[option];
+  return GSB_OK;
+}
 
 int64_t gsb_launch_count(gsb_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 int gsb_read_counts(gsb_ctx* ctx, void* stream, int64_t* nnz_host, int64_t* unique_host) {
-  if (!ctx) return GSB_ERR_INVALID_ARGUMENT;
+  GSB_ENTER(ctx);
   const i64* c;
   int st = gsb::ctx_fetch_counters(ctx, (cudaStream_t)stream, gsb::CNT_NNZ, 2, &c);
   if (st != GSB_OK) return st;

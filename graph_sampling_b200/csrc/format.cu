@@ -74,7 +74,8 @@ using namespace gsb;
 extern "C" {
 
 int gsb_csc2coo(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int64_t num_cols, int64_t* out_col) {
-  GSB_REQUIRE(ctx && indptr && num_cols >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && num_cols >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (num_cols == 0) return GSB_OK;
   k_csc2coo<<<grid_for(num_cols, kFmtTileCols), kFmtThreads, 0, (cudaStream_t)stream_>>>(indptr, num_cols, out_col);
   GSB_LAUNCH_OK();
@@ -84,7 +85,8 @@ int gsb_csc2coo(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int64_t num_
 
 int gsb_coo2csc(gsb_ctx* ctx, void* stream_, const int64_t* key, const int64_t* other, int64_t E, int64_t num_keys,
                 int key_sorted, int64_t* out_indptr, int64_t* out_other, int64_t* out_perm) {
-  GSB_REQUIRE(ctx && out_indptr && E >= 0 && num_keys >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(out_indptr && E >= 0 && num_keys >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(E == 0 || (key && other && out_other), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(key_sorted || E == 0 || out_perm, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;

@@ -70,7 +70,8 @@ using namespace gsb;
 
 extern "C" int gsb_gather_rows(gsb_ctx* ctx, void* stream_, const float* src, int64_t num_rows, int64_t row_len,
                                const int64_t* index, int64_t n, float* out) {
-  GSB_REQUIRE(ctx && num_rows >= 0 && row_len >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(num_rows >= 0 && row_len >= 1 && n >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (n == 0) return GSB_OK;
   GSB_REQUIRE(src && index && out, GSB_ERR_INVALID_ARGUMENT);
   // `src` may be device memory or page-locked host memory; the kernel gets the address the DEVICE uses for it.

@@ -51,13 +51,22 @@ static const float* FP(const Tensor& t) { return t.defined() && t.numel() ? t.da
 // (the reference accepts the same: src/graph_ops.cc:144,226, src/cuda/slicing.cu:128); results are always allocated
 // on the current device.
 static bool Pinned(const Tensor& t) { return !t.is_cuda() && t.is_pinned(); }
+// Kernels are launched on the CURRENT device's stream with the current device's context: a tensor that lives on
+// another GPU is refused here instead of being dereferenced from the wrong device.
+static void SameDevice(const Tensor& t, const char* name) {
+  TORCH_CHECK(!t.is_cuda() || t.device().index() == c10::cuda::current_device(), name, " is on cuda:",
+              (int)t.device().index(), " while cuda:", (int)c10::cuda::current_device(),
+              " is the current device; set the device (torch.cuda.device) before calling");
+}
 static Tensor Ids(const Tensor& t, const char* name) {
   TORCH_CHECK((t.is_cuda() || Pinned(t)) && t.scalar_type() == torch::kInt64, name, " must be an int64 CUDA (or pinned host) tensor");
+  SameDevice(t, name);
   TORCH_CHECK(t.is_cuda() || t.is_contiguous(), name, ": a pinned host tensor must be contiguous");
   return t.contiguous();
 }
 static Tensor Floats(const Tensor& t, const char* name) {
   TORCH_CHECK((t.is_cuda() || Pinned(t)) && t.scalar_type() == torch::kFloat32, name, " must be a float32 CUDA (or pinned host) tensor");
+  SameDevice(t, name);
   TORCH_CHECK(t.is_cuda() || t.is_contiguous(), name, ": a pinned host tensor must be contiguous");
   return t.contiguous();
 }
@@ -83,6 +92,14 @@ static Tensor Take(const Tensor& src, const Tensor& index) {
   return out;
 }
 
+// Largest node count among the graphs loaded so far (0 = none): the id bound that operators without a graph
+// argument (gs_ops.BatchCSRRelabel) may assume and verify.
+static std::atomic<int64_t> g_node_bound{0};
+static void NoteNodeBound(int64_t n) {
+  int64_t cur = g_node_bound.load();
+  while (n > cur && !g_node_bound.compare_exchange_weak(cur, n)) {
+  }
+}
 static std::atomic<uint64_t> g_seed_base{7777};
 static std::atomic<uint64_t> g_seed_counter{0};
 static uint64_t NextSeed() { return g_seed_base.load() * 0x9E3779B97F4A7C15ull + g_seed_counter.fetch_add(1); }
@@ -108,7 +125,9 @@ static Sliced ColSlice(const CSC& g, const Tensor& ids, bool with_coo, const Opt
   Sliced r;
   r.indptr = EmptyIds(S + 1, g.indptr);
   int64_t nnz = 0;
-  Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), IP(n_ids), S, MP(r.indptr), &nnz), "gsb_col_slice_count");
+  const int64_t num_cols = g.indptr.numel() - 1;
+  Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), num_cols, IP(n_ids), S, MP(r.indptr), &nnz),
+        "gsb_col_slice_count");
   r.indices = EmptyIds(nnz, g.indptr);
   r.select = EmptyIds(nnz, g.indptr);
   if (with_coo) r.coo_other = EmptyIds(nnz, g.indptr);
@@ -118,7 +137,8 @@ static Sliced ColSlice(const CSC& g, const Tensor& ids, bool with_coo, const Opt
     r.data = torch::empty({nnz}, OnDevice(d));
     if (g.e_ids.has_value()) e = g.e_ids.value();
   }
-  Check(gsb_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(n_ids), S, IP(r.indptr), MP(r.indices),
+  Check(gsb_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), num_cols, IP(n_ids), S, IP(r.indptr), nnz,
+                           MP(r.indices),
                            MP(r.select), with_coo ? MP(r.coo_other) : nullptr, FP(d), IP(e),
                            r.data.defined() && nnz ? r.data.data_ptr<float>() : nullptr),
         "gsb_col_slice_fill");
@@ -146,13 +166,15 @@ static Sliced Sample(const CSC& g, const Tensor* seeds, int64_t fanout, bool rep
   if (probs) {
     p = Floats(*probs, "edge probabilities");
     TORCH_CHECK(p.numel() == g.indices.numel(), "edge_probs must have one entry per edge of the operand");
-    Check(gsb_sample_weighted(Ctx(), Stream(), IP(g.indptr), IP(g.indices), FP(p), seeds ? IP(s) : nullptr, S, fanout,
+    Check(gsb_sample_weighted(Ctx(), Stream(), IP(g.indptr), IP(g.indices), g.indptr.numel() - 1, FP(p),
+                              seeds ? IP(s) : nullptr, S, fanout,
                               replace, NextSeed(), MP(r.indptr), MP(r.indices), MP(r.select),
                               with_coo ? MP(r.coo_other) : nullptr, FP(d), IP(e),
                               out_d.defined() && cap ? out_d.data_ptr<float>() : nullptr, cap, &nnz),
           "gsb_sample_weighted");
   } else {
-    Check(gsb_sample_uniform(Ctx(), Stream(), IP(g.indptr), IP(g.indices), seeds ? IP(s) : nullptr, S, fanout, replace,
+    Check(gsb_sample_uniform(Ctx(), Stream(), IP(g.indptr), IP(g.indices), g.indptr.numel() - 1,
+                             seeds ? IP(s) : nullptr, S, fanout, replace,
                              NextSeed(), MP(r.indptr), MP(r.indices), MP(r.select),
                              with_coo ? MP(r.coo_other) : nullptr, FP(d), IP(e),
                              out_d.defined() && cap ? out_d.data_ptr<float>() : nullptr, cap, &nnz),
@@ -321,6 +343,7 @@ class Graph : public torch::CustomClassHolder {
     csc_ = std::make_shared<CSC>(CSC{Ids(indptr, "indptr"), Ids(indices, "indices"), torch::nullopt});
     num_cols_ = num_rows_ = indptr.numel() - 1;
     num_edges_ = indices.numel();
+    NoteNodeBound(num_cols_);
   }
   void LoadCOO(Tensor row, Tensor col) {
     coo_ = std::make_shared<COO>(COO{Ids(row, "row"), Ids(col, "col"), torch::nullopt, false, false});
@@ -551,7 +574,8 @@ class Graph : public torch::CustomClassHolder {
     const CSC& g = *csc_;
     Tensor sub_indptr = EmptyIds(S + 1, g.indptr);
     int64_t nnz = 0;
-    Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), IP(n_ids), S, MP(sub_indptr), &nnz), "gsb_col_slice_count");
+    Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(n_ids), S, MP(sub_indptr), &nnz),
+          "gsb_col_slice_count");
     Tensor indices = EmptyIds(nnz, g.indptr), select = EmptyIds(nnz, g.indptr), offsets = EmptyIds(G + 1, g.indptr);
     Tensor coo_col = with_coo ? EmptyIds(nnz, g.indptr) : Tensor();
     Tensor out_data;
@@ -563,7 +587,8 @@ class Graph : public torch::CustomClassHolder {
       data_out = nnz ? out_data.data_ptr<float>() : nullptr;
     }
     Tensor eids = g.e_ids.value_or(Tensor());
-    Check(gsb_batch_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(n_ids), S, IP(nid_ptr), G,
+    Check(gsb_batch_col_slice_fill(Ctx(), Stream(), IP(g.indptr), IP(g.indices), g.indptr.numel() - 1, IP(n_ids), S,
+                                   IP(nid_ptr), G,
                                    encoding ? num_rows_ : 0, IP(sub_indptr), MP(indices), MP(select), MP(coo_col),
                                    MP(offsets), data_in, IP(eids), data_out),
           "gsb_batch_col_slice_fill");
@@ -595,7 +620,8 @@ class Graph : public torch::CustomClassHolder {
     const int64_t S = col_ids.numel(), R = row_ids.numel(), G = batched ? cp.numel() - 1 : 1;
     Tensor slice_indptr = EmptyIds(S + 1, g.indptr), sub_indptr = EmptyIds(S + 1, g.indptr);
     int64_t D = 0, nnz = 0;
-    Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), IP(col_ids), S, MP(slice_indptr), &D), "gsb_col_slice_count");
+    Check(gsb_col_slice_count(Ctx(), Stream(), IP(g.indptr), g.indptr.numel() - 1, IP(col_ids), S, MP(slice_indptr), &D),
+          "gsb_col_slice_count");
     Tensor indices = EmptyIds(D, g.indptr), select = EmptyIds(D, g.indptr), out_data;
     const float* data_in = nullptr;
     float* data_out = nullptr;
@@ -605,7 +631,8 @@ class Graph : public torch::CustomClassHolder {
       data_out = D ? out_data.data_ptr<float>() : nullptr;
     }
     Tensor eids = g.e_ids.value_or(Tensor());
-    Check(gsb_col_row_slice(Ctx(), Stream(), IP(g.indptr), IP(g.indices), IP(col_ids), S, IP(slice_indptr), D,
+    Check(gsb_col_row_slice(Ctx(), Stream(), IP(g.indptr), IP(g.indices), g.indptr.numel() - 1, IP(col_ids), S,
+                            IP(slice_indptr), D,
                             IP(row_ids), R, IP(cp), IP(rp), G, num_rows_, batched ? 0 : 1, MP(sub_indptr), MP(indices),
                             MP(select), data_in, IP(eids), data_out, &nnz),
           "gsb_col_row_slice");
@@ -731,7 +758,8 @@ class Graph : public torch::CustomClassHolder {
       Tensor seeds = Ids(column_index, "column ids");
       const int64_t S = seeds.numel();
       Tensor indptr = EmptyIds(S + 1, seeds), indices = EmptyIds(S, seeds), select = EmptyIds(S, seeds);
-      Check(gsb_sample_one_keepdim(Ctx(), Stream(), IP(csc_->indptr), IP(csc_->indices), IP(seeds), S, NextSeed(),
+      Check(gsb_sample_one_keepdim(Ctx(), Stream(), IP(csc_->indptr), IP(csc_->indices), csc_->indptr.numel() - 1,
+                                   IP(seeds), S, NextSeed(),
                                    MP(indptr), MP(indices), MP(select)),
             "gsb_sample_one_keepdim");
       ret->csc_ = std::make_shared<CSC>(CSC{indptr, indices, torch::nullopt});
@@ -784,7 +812,8 @@ class Graph : public torch::CustomClassHolder {
     TORCH_CHECK(csc_ != nullptr, "RandomWalk needs a CSC graph");
     Tensor s = Ids(seeds, "seeds");
     Tensor out = EmptyIds(s.numel() * (walk_length + 1), s);
-    Check(gsb_random_walk(Ctx(), Stream(), IP(csc_->indptr), IP(csc_->indices), IP(s), s.numel(), walk_length,
+    Check(gsb_random_walk(Ctx(), Stream(), IP(csc_->indptr), IP(csc_->indices), csc_->indptr.numel() - 1, IP(s),
+                          s.numel(), walk_length,
                           NextSeed(), 0, 0, MP(out)),
           "gsb_random_walk");
     return out.reshape({s.numel(), walk_length + 1});
@@ -1014,12 +1043,13 @@ class HeteroGraph : public torch::CustomClassHolder {
     }
     const int64_t* ip[GSB_MAX_RELATIONS];
     const int64_t* ix[GSB_MAX_RELATIONS];
+    int64_t nn[GSB_MAX_RELATIONS];
     for (size_t i = 0; i < relations_.size(); ++i) {
       const CSC& g = relations_[i]->CscForWalk();
-      ip[i] = IP(g.indptr), ix[i] = IP(g.indices);
+      ip[i] = IP(g.indptr), ix[i] = IP(g.indices), nn[i] = g.indptr.numel() - 1;
     }
     Tensor out = EmptyIds(s.numel() * (L + 1), s);
-    Check(gsb_metapath_random_walk(Ctx(), Stream(), ip, ix, (int)relations_.size(), path.data(), L, IP(s), s.numel(),
+    Check(gsb_metapath_random_walk(Ctx(), Stream(), ip, ix, nn, (int)relations_.size(), path.data(), L, IP(s), s.numel(),
                                    NextSeed(), 0, 0, MP(out)),
           "gsb_metapath_random_walk");
     return out.reshape({s.numel(), L + 1});
@@ -1059,9 +1089,16 @@ static std::tuple<Tensor, Tensor, Tensor, Tensor> BatchCSRRelabel(Tensor seeds, 
   const int64_t G = sp.numel() - 1;
   Tensor uniq = EmptyIds(s.numel() + ix.numel(), s), uniq_ptr = EmptyIds(G + 1, s), rel = EmptyIds(ix.numel(), s);
   int64_t nu = 0, ne = 0;
-  Check(gsb_batch_unique_relabel(Ctx(), Stream(), IP(s), IP(sp), s.numel(), IP(ix), IP(ixp), ix.numel(), G, MP(uniq),
-                                 MP(uniq_ptr), MP(rel), &nu, &ne),
-        "gsb_batch_unique_relabel");
+  // The operator's signature carries no id bound (src/tensor_ops.h), so the largest node count of the graphs loaded
+  // so far serves as a hint: with it first occurrences are found in direct-address tables.  If an id turns out to
+  // lie outside the hint, the device reports GSB_ERR_INDEX_RANGE and the call is redone with hash tables.
+  const int64_t hint = g_node_bound.load();
+  int st = gsb_batch_unique_relabel(Ctx(), Stream(), IP(s), IP(sp), s.numel(), IP(ix), IP(ixp), ix.numel(), G, hint, 0,
+                                    MP(uniq), MP(uniq_ptr), MP(rel), &nu, &ne);
+  if (hint > 0 && (st == GSB_ERR_INDEX_RANGE || st == GSB_ERR_OUT_OF_MEMORY))
+    st = gsb_batch_unique_relabel(Ctx(), Stream(), IP(s), IP(sp), s.numel(), IP(ix), IP(ixp), ix.numel(), G, 0, 0,
+                                  MP(uniq), MP(uniq_ptr), MP(rel), &nu, &ne);
+  Check(st, "gsb_batch_unique_relabel");
   return {uniq.narrow(0, 0, nu), uniq_ptr, rel.narrow(0, 0, ne), ixp};
 }
 static std::vector<Tensor> SplitByOffset(Tensor data, Tensor offset) {  // src/tensor_ops.cc:33-45

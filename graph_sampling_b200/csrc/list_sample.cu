@@ -276,7 +276,8 @@ using namespace gsb;
 extern "C" int gsb_list_sample(gsb_ctx* ctx, void* stream_, const int64_t* data, const float* probs, int64_t N,
                                int64_t k, int replace, uint64_t seed, int64_t* out_data, int64_t* out_index,
                                int64_t* n_out_host) {
-  GSB_REQUIRE(ctx && N >= 0 && k >= 0 && n_out_host, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(N >= 0 && k >= 0 && n_out_host, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(N < 0xFFFFFFFFll, GSB_ERR_UNSUPPORTED);
   cudaStream_t stream = (cudaStream_t)stream_;
   const int wide = kNumSMs * 8;

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(kRowThreads) k_row_indptr(const i64* __restric
 struct ColRowParams {
   const i64* indptr;
   const i64* indices;
+  i64 num_cols;
   const i64* seeds;
   i64 S;
   const i64* sub_indptr;  // [S + 1]
@@ -231,7 +232,12 @@ __global__ void __launch_bounds__(kRowThreads) k_col_row_filter(ColRowParams p) 
   for (int q = 0; q < kCrLane; ++q) {
     if (col_of[q] >= 0) {
       const i64 col = p.seeds ? __ldg(p.seeds + col_of[q]) : col_of[q];
-      start_of[q] = __ldg(p.indptr + col);
+      if ((u64)col < (u64)p.num_cols) {
+        start_of[q] = __ldg(p.indptr + col);
+      } else {  // only reachable when sub_indptr was not counted for these seeds: drop the position
+        raise_error(p.counters, GSB_ERR_INDEX_RANGE, col_of[q]);
+        col_of[q] = -1;
+      }
     }
   }
 #pragma unroll
@@ -354,7 +360,8 @@ extern "C" {
 int gsb_row_slice_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, int64_t num_cols,
                       int64_t E, const int64_t* row_ids, int64_t R, int64_t* out_indptr, int64_t* out_indices,
                       int64_t* out_select, int64_t* out_coo_col, int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && indptr && out_indptr && num_cols >= 0 && E >= 0 && R >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && num_cols >= 0 && E >= 0 && R >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(E == 0 || (indices && out_indices && out_select), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   Table table;
@@ -380,7 +387,8 @@ int gsb_row_slice_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const 
 int gsb_row_slice_coo(gsb_ctx* ctx, void* stream_, const int64_t* coo_row, const int64_t* coo_col, int64_t E,
                       const int64_t* row_ids, int64_t R, int64_t* out_row, int64_t* out_col, int64_t* out_select,
                       int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && E >= 0 && R >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(E >= 0 && R >= 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(E == 0 || (coo_row && coo_col && out_row && out_col && out_select), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   Table table;
@@ -424,13 +432,16 @@ static int col_row_table(gsb_ctx* ctx, cudaStream_t stream, const int64_t* row_i
 
 extern "C" {
 
-int gsb_col_row_slice(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+int gsb_col_row_slice(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, int64_t num_cols,
                       const int64_t* column_ids, int64_t S, const int64_t* sub_indptr, int64_t D,
                       const int64_t* row_ids, int64_t R, const int64_t* col_ptr, const int64_t* row_ptr, int64_t G,
                       int64_t encoding_size, int renumber, int64_t* out_indptr, int64_t* out_indices,
                       int64_t* out_select, const float* data, const int64_t* e_ids, float* out_data,
                       int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && indptr && sub_indptr && out_indptr && S >= 0 && D >= 0 && R >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && sub_indptr && out_indptr && S >= 0 && D >= 0 && R >= 0 && num_cols >= 0 &&
+                  (column_ids || S <= num_cols),
+              GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((col_ptr == nullptr) == (row_ptr == nullptr) && (!col_ptr || G >= 1), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(R == 0 || row_ids, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(D == 0 || (indices && out_indices && out_select), GSB_ERR_INVALID_ARGUMENT);
@@ -448,7 +459,7 @@ int gsb_col_row_slice(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const 
   TileState ts;
   st = ctx_tile_state(ctx, tiles, stream, &ts);
   if (st != GSB_OK) return st;
-  ColRowParams p{indptr, indices, column_ids, S, sub_indptr, D, col_ptr, G, encoding_size, table, renumber ? 1 : 0,
+  ColRowParams p{indptr, indices, num_cols, column_ids, S, sub_indptr, D, col_ptr, G, encoding_size, table, renumber ? 1 : 0,
                  out_indptr, out_indices, out_select, data, e_ids, out_data, ctx_counters(ctx), ts};
   {
     ScopedKernelTimer timer(ctx, KID_ROW_FILTER, stream);
@@ -460,7 +471,8 @@ int gsb_col_row_slice(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const 
 
 int gsb_index_search(gsb_ctx* ctx, void* stream_, const int64_t* origin, int64_t n, const int64_t* keys, int64_t m,
                      int64_t* out) {
-  GSB_REQUIRE(ctx && n >= 0 && m >= 0 && (n == 0 || origin), GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(n >= 0 && m >= 0 && (n == 0 || origin), GSB_ERR_INVALID_ARGUMENT);
   if (m == 0) return GSB_OK;
   GSB_REQUIRE(keys && out, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;

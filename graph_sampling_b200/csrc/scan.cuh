@@ -8,15 +8,13 @@
 // sequence (src/cuda/slicing.cu:133-147, src/cuda/utils.h:17-28).
 //
 // Tiles are numbered by blockIdx.x and rely on CTAs being dispatched in index order, as every
-// single-pass scan does.  The wait on a predecessor is bounded: after kMaxPolls polls the CTA
+// single-pass scan does.  The wait on a predecessor is bounded: after TileState::max_polls polls the CTA
 // records GSB_ERR_LOOKBACK_TIMEOUT in the context's error counter and continues with prefix 0, so
 // a lost predecessor can never hang the GPU.
 #pragma once
 #include "common.cuh"
 
 namespace gsb {
-
-constexpr int kMaxPolls = 1 << 22;
 
 __device__ __forceinline__ u64 tile_word(uint32_t epoch, uint32_t flag, i64 value) {
   return ((u64)(epoch & kEpochMask) << 42) | ((u64)flag << 40) | ((u64)value & kValueMask);
@@ -57,7 +55,7 @@ __device__ __forceinline__ i64 tile_exclusive_prefix(const TileState& ts, int ti
       if (my >= 0) w = ld_volatile_u64(&ts.words[my]);
       ready = ((uint32_t)(w >> 42) == ep) && (((w >> 40) & 3ull) != 0ull);
       if (__all_sync(0xffffffffu, ready)) break;
-      if (++polls > kMaxPolls) {
+      if (++polls > ts.max_polls) {
         if (lane == 0) raise_error(ts.counters, GSB_ERR_LOOKBACK_TIMEOUT, tile);
         if (!ready) w = tile_word(ep, 2, 0);
         break;

@@ -166,7 +166,8 @@ extern "C" int gsb_sddmm(gsb_ctx* ctx, void* stream_, int op, const int64_t* row
                          const float* rhs, float* out, int lhs_target, int rhs_target, int64_t lhs_len,
                          int64_t rhs_len, int64_t out_len, int64_t reduce_size, const int64_t* lhs_off,
                          const int64_t* rhs_off) {
-  GSB_REQUIRE(ctx && E >= 0 && op >= OP_ADD && op <= OP_DOT, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(E >= 0 && op >= OP_ADD && op <= OP_DOT, GSB_ERR_INVALID_ARGUMENT);
   if (E == 0 || out_len == 0) return GSB_OK;
   GSB_REQUIRE(row && (col || indptr) && out, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(lhs_target >= 0 && lhs_target <= 2 && rhs_target >= 0 && rhs_target <= 2, GSB_ERR_INVALID_ARGUMENT);

@@ -265,7 +265,8 @@ extern "C" {
 
 int gsb_segment_sum_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int64_t num_seg, const int64_t* e_ids,
                         const float* data, int64_t powk, float* out) {
-  GSB_REQUIRE(ctx && num_seg >= 0 && powk >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(num_seg >= 0 && powk >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (num_seg == 0) return GSB_OK;
   GSB_REQUIRE(indptr && out, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -290,7 +291,8 @@ int gsb_segment_sum_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int6
 
 int gsb_segment_sum_coo(gsb_ctx* ctx, void* stream_, const int64_t* target, int64_t E, const int64_t* e_ids,
                         const float* data, int64_t powk, int targets_in_runs, float* out_zeroed) {
-  GSB_REQUIRE(ctx && E >= 0 && powk >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(E >= 0 && powk >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (E == 0) return GSB_OK;
   GSB_REQUIRE(target && out_zeroed, GSB_ERR_INVALID_ARGUMENT);
   const int grid = min(grid_for(E, kSegThreads), kNumSMs * 16);
@@ -307,7 +309,8 @@ int gsb_segment_sum_coo(gsb_ctx* ctx, void* stream_, const int64_t* target, int6
 
 int gsb_segment_normalize_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int64_t num_seg,
                               const int64_t* e_ids, const float* data, float* out) {
-  GSB_REQUIRE(ctx && num_seg >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(num_seg >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (num_seg == 0) return GSB_OK;
   GSB_REQUIRE(indptr && data && out, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -330,7 +333,8 @@ int gsb_segment_normalize_csc(gsb_ctx* ctx, void* stream_, const int64_t* indptr
 
 int gsb_edge_div_u_sum(gsb_ctx* ctx, void* stream_, const int64_t* coo_row, const int64_t* coo_col, int64_t E,
                        const float* data, const float* divisor, float* out_data, float* out_sum_zeroed) {
-  GSB_REQUIRE(ctx && E >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(E >= 0, GSB_ERR_INVALID_ARGUMENT);
   if (E == 0) return GSB_OK;
   GSB_REQUIRE(coo_row && coo_col && divisor && out_data && out_sum_zeroed, GSB_ERR_INVALID_ARGUMENT);
   ScopedKernelTimer timer(ctx, KID_SEGMENT, (cudaStream_t)stream_);

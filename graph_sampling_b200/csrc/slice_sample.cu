@@ -29,7 +29,14 @@ __device__ __forceinline__ i64 column_count(i64 d, i64 k, int mode) {
 }
 
 // ---- count + scan only (one column per thread) -------------------------------------------------
-__global__ void __launch_bounds__(kThreads) k_count_scan(const i64* __restrict__ indptr,
+// A seed outside [0, num_cols) counts as an empty column: its offsets are never read, GSB_ERR_INDEX_RANGE is recorded.
+__device__ __forceinline__ bool column_in_range(i64 col, i64 num_cols, i64* counters, i64 where) {
+  if ((u64)col < (u64)num_cols) return true;
+  raise_error(counters, GSB_ERR_INDEX_RANGE, where);
+  return false;
+}
+
+__global__ void __launch_bounds__(kThreads) k_count_scan(const i64* __restrict__ indptr, i64 num_cols,
                                                          const i64* __restrict__ seeds, i64 S, i64 k, int mode,
                                                          i64* __restrict__ out_indptr, i64* counters, TileState ts) {
   __shared__ i64 s_scan[33];
@@ -40,8 +47,10 @@ __global__ void __launch_bounds__(kThreads) k_count_scan(const i64* __restrict__
   i64 f = 0;
   if (i < S) {
     const i64 col = seeds ? seeds[i] : i;
-    const i64 b = indptr[col];
-    f = column_count(indptr[col + 1] - b, k, mode);
+    if (column_in_range(col, num_cols, counters, i)) {
+      const i64 b = indptr[col];
+      f = column_count(indptr[col + 1] - b, k, mode);
+    }
   }
   i64 total;
   const i64 excl = block_exclusive_scan<kThreads>(f, s_scan, &total);
@@ -62,6 +71,7 @@ __global__ void __launch_bounds__(kThreads) k_count_scan(const i64* __restrict__
 struct FillParams {
   const i64* indptr;
   const i64* indices;
+  i64 num_cols;
   const i64* seeds;
   i64 S;
   const i64* out_indptr;
@@ -76,17 +86,18 @@ struct FillParams {
   const i64* nid_ptr;
   i64 G;
   i64 encoding_size;
+  bool host_chose;  // the caller knew the edge total and launched only the kernel that suits the shape
 };
 
 // Which of the two fill kernels copies a slice of S columns with D edges: both are launched and the one whose shape
 // it is not returns at once (the edge total is known on the device only).  Column tiles — offsets and column starts
 // loaded once per column, coalesced — win when there are many short columns; output tiles win when columns are long
 // (D >= 128·S) or too few to give every SM a column tile.
-__device__ __forceinline__ bool fill_by_output_tiles(i64 S, i64 D) { return D >= 128 * S || S < 148 * kTileCols; }
+__host__ __device__ __forceinline__ bool fill_by_output_tiles(i64 S, i64 D) { return D >= 128 * S || S < 148 * kTileCols; }
 
 template <bool ENCODE>
 __global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
-  if (fill_by_output_tiles(p.S, __ldg(p.out_indptr + p.S))) return;
+  if (!p.host_chose && fill_by_output_tiles(p.S, __ldg(p.out_indptr + p.S))) return;
   __shared__ i64 s_in[kTileCols];
   __shared__ i64 s_off[kTileCols + 1];
   __shared__ i64 s_enc[ENCODE ? kTileCols : 1];
@@ -97,7 +108,7 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill(FillParams p) {
   if (tid <= ncol) s_off[tid] = p.out_indptr[base + tid];
   if (tid < ncol) {
     const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
-    s_in[tid] = p.indptr[col];
+    s_in[tid] = (u64)col < (u64)p.num_cols ? p.indptr[col] : 0;  // a bad id has no output positions (count 0)
     if (ENCODE) s_enc[tid] = batch_of(p.nid_ptr, p.G, base + tid) * p.encoding_size;
   }
   __syncthreads();
@@ -186,7 +197,7 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill_edges(FillParams p) {
   __shared__ i64 s_clo, s_chi;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const i64 D = __ldg(p.out_indptr + p.S);
-  if (!fill_by_output_tiles(p.S, D)) return;
+  if (!p.host_chose && !fill_by_output_tiles(p.S, D)) return;
   for (i64 tile_base = (i64)blockIdx.x * kFillTile; tile_base < D; tile_base += (i64)gridDim.x * kFillTile) {
     const i64 tile_end = min(D, tile_base + kFillTile);
     if (warp < 2) {  // the tile's column range: two warp-wide searches side by side
@@ -214,6 +225,10 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill_edges(FillParams p) {
       if (col_of[r] < 0) continue;
       const i64 pos = base + r * 32 + lane;
       const i64 col = p.seeds ? __ldg(p.seeds + col_of[r]) : col_of[r];
+      if ((u64)col >= (u64)p.num_cols) {  // only reachable with offsets that were not counted for these seeds
+        col_of[r] = -1;
+        continue;
+      }
       in_pos[r] = __ldg(p.indptr + col) + (pos - __ldg(p.out_indptr + col_of[r]));
     }
 #pragma unroll
@@ -249,10 +264,21 @@ __global__ void __launch_bounds__(kThreads) k_slice_fill_edges(FillParams p) {
 // One CTA pass covers 2 048 positions; three CTAs per SM (66 registers per thread) hide the searches of one pass behind the copies of another.
 static inline int fill_grid() { return 148 * 3; }
 
+// Launches the copy of a slice: with the edge total known on the host only the kernel that suits the shape, without
+// it both (the one whose shape it is not returns at once).
+template <bool ENCODE>
+static void launch_fill(FillParams p, i64 D, cudaStream_t stream) {
+  p.host_chose = D >= 0;
+  if (D < 0 || !fill_by_output_tiles(p.S, D)) k_slice_fill<ENCODE><<<grid_for(p.S, kTileCols), kThreads, 0, stream>>>(p);
+  if (D < 0 || fill_by_output_tiles(p.S, D)) k_slice_fill_edges<ENCODE><<<fill_grid(), kThreads, 0, stream>>>(p);
+}
+
+
 // ---- fused count + scan + uniform sampling -------------------------------------------------------
 struct SampleParams {
   const i64* indptr;
   const i64* indices;
+  i64 num_cols;
   const i64* seeds;
   i64 S;
   i64 k;
@@ -269,7 +295,19 @@ struct SampleParams {
   i64* counters;
   TileState ts;
   const i64* S_dev;  // when set, the exact seed count lives on the device and S above is only an upper bound
+  // Minibatch form (G > 0): the seeds of minibatch j are seeds[batch_ptr[j] .. batch_ptr[j+1]) and the draws of its
+  // column number c are keyed by (batch_ids[j], c) instead of the column's position in the call, so a minibatch
+  // receives the same sample whichever call, group or GPU processes it.
+  const i64* batch_ptr;
+  const i64* batch_ids;
+  i64 G;
 };
+
+// Random-stream item of the column at position i of the call.
+__device__ __forceinline__ u64 sample_item(const SampleParams& p, i64 i, i64 batch) {
+  if (p.G <= 0) return (u64)i;
+  return ((u64)__ldg(p.batch_ids + batch) << 32) | (u64)(uint32_t)(i - __ldg(p.batch_ptr + batch));
+}
 
 __device__ __forceinline__ void emit_pick(const SampleParams& p, i64 out_pos, i64 in_pos, i64 column_pos) {
   p.out_indices[out_pos] = __ldg(p.indices + in_pos);
@@ -283,6 +321,7 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
   __shared__ i64 s_in[kTileCols];
   __shared__ i64 s_deg[kTileCols];
   __shared__ i64 s_off[kTileCols];
+  __shared__ u64 s_item[kTileCols];
   __shared__ i64 s_scan[33];
   __shared__ i64 s_base;
   const int tile = blockIdx.x;
@@ -296,11 +335,15 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
   i64 f = 0;
   if (tid < ncol) {
     const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
-    const i64 b = p.indptr[col];
-    const i64 d = p.indptr[col + 1] - b;
+    i64 b = 0, d = 0;
+    if (column_in_range(col, p.num_cols, p.counters, base + tid)) {
+      b = p.indptr[col];
+      d = p.indptr[col + 1] - b;
+    }
     f = column_count(d, k, p.replace ? COUNT_WR : COUNT_WOR);
     s_in[tid] = b;
     s_deg[tid] = d;
+    s_item[tid] = sample_item(p, base + tid, p.G > 0 ? batch_of(p.batch_ptr, p.G, base + tid) : 0);
   }
   i64 total;
   const i64 excl = block_exclusive_scan<kThreads>(f, s_scan, &total);
@@ -331,10 +374,11 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
     const i64 b = s_in[c];
     const i64 o = tile_base + s_off[c];
     const i64 col_pos = base + c;
+    const u64 item = s_item[c];
     if (p.replace) {
       if (d == 0) continue;
       for (i64 j = lane; j < k; j += G)
-        emit_pick(p, o + j, b + (i64)rand_bounded(p.seed, (u64)col_pos, (u64)j, STREAM_UNIFORM, (u64)d), col_pos);
+        emit_pick(p, o + j, b + (i64)rand_bounded(p.seed, item, (u64)j, STREAM_UNIFORM, (u64)d), col_pos);
     } else if (d <= k) {
       for (i64 j = lane; j < d; j += G) emit_pick(p, o + j, b + j, col_pos);
     } else if (k <= G) {
@@ -342,7 +386,7 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
       // resolved in slot order (a repeated value is replaced by d-k+j).
       const i64 m = d - k + lane;
       i64 t = 0;
-      if (lane < k) t = (i64)rand_bounded(p.seed, (u64)col_pos, (u64)lane, STREAM_UNIFORM, (u64)(m + 1));
+      if (lane < k) t = (i64)rand_bounded(p.seed, item, (u64)lane, STREAM_UNIFORM, (u64)(m + 1));
       i64 pick = -1;
       for (int j = 0; j < (int)k; ++j) {
         const i64 tj = __shfl_sync(gmask, t, j, G);
@@ -356,7 +400,7 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
       // buffer; membership is checked by the whole warp.
       for (i64 j = 0; j < k; ++j) {
         const i64 m = d - k + j;
-        const i64 tj = b + (i64)rand_bounded(p.seed, (u64)col_pos, (u64)j, STREAM_UNIFORM, (u64)(m + 1));
+        const i64 tj = b + (i64)rand_bounded(p.seed, item, (u64)j, STREAM_UNIFORM, (u64)(m + 1));
         bool dup = false;
         for (i64 q = lane; q < j; q += G) dup |= (p.out_select[o + q] == tj);
         const unsigned any = __ballot_sync(gmask, dup);
@@ -388,8 +432,10 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
   i64 b = 0, d = 0, f = 0, col = 0;
   if (valid) {
     col = p.seeds ? __ldg(p.seeds + i) : i;
-    b = __ldg(p.indptr + col);
-    d = __ldg(p.indptr + col + 1) - b;
+    if (column_in_range(col, p.num_cols, p.counters, i)) {
+      b = __ldg(p.indptr + col);
+      d = __ldg(p.indptr + col + 1) - b;
+    }
     f = column_count(d, k, p.replace ? COUNT_WR : COUNT_WOR);
   }
   i64 inc = f;
@@ -423,11 +469,18 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
   uint32_t pick[KMAX];
   if (n > 0) {
     if (p.replace || d > k) {
+      u64 item = (u64)i;
+      if (p.G > 0) {
+        // batch of the warp's first column by one search; a lane beyond that batch's end searches for itself
+        i64 bt = batch_of(p.batch_ptr, p.G, tile * 32);
+        if (i >= __ldg(p.batch_ptr + bt + 1)) bt = batch_of(p.batch_ptr, p.G, i);
+        item = sample_item(p, i, bt);
+      }
       U32x4 blk;
 #pragma unroll
       for (int j = 0; j < KMAX; ++j) {
         if (j < k) {
-          if ((j & 3) == 0) blk = rand_block(p.seed, (u64)i, (u64)(j >> 2), STREAM_UNIFORM);
+          if ((j & 3) == 0) blk = rand_block(p.seed, item, (u64)(j >> 2), STREAM_UNIFORM);
           const uint32_t word =
               (j & 3) == 0 ? blk.v[0] : (j & 3) == 1 ? blk.v[1] : (j & 3) == 2 ? blk.v[2] : blk.v[3];
           if (p.replace) {
@@ -465,8 +518,9 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
 }
 
 __global__ void __launch_bounds__(kThreads) k_sample_one_keepdim(const i64* __restrict__ indptr,
-                                                                 const i64* __restrict__ indices,
+                                                                 const i64* __restrict__ indices, i64 num_cols,
                                                                  const i64* __restrict__ seeds, i64 S, u64 seed,
+                                                                 i64* counters,
                                                                  i64* __restrict__ out_indptr,
                                                                  i64* __restrict__ out_indices,
                                                                  i64* __restrict__ out_select) {
@@ -475,8 +529,10 @@ __global__ void __launch_bounds__(kThreads) k_sample_one_keepdim(const i64* __re
   out_indptr[i] = i;
   if (i == S) return;
   const i64 col = seeds[i];
-  const i64 b = indptr[col];
-  const i64 d = indptr[col + 1] - b;
+  // -1 is what this operator itself emits for an isolated seed, so a walk may feed it back: it stays -1 silently
+  const bool ok = col == -1 ? false : column_in_range(col, num_cols, counters, i);
+  const i64 b = ok ? indptr[col] : 0;
+  const i64 d = ok ? indptr[col + 1] - b : 0;
   if (d == 0) {
     out_indices[i] = -1;
     out_select[i] = -1;
@@ -493,17 +549,19 @@ static void launch_sample(const SampleParams& p, int grid, cudaStream_t stream) 
 }
 
 
-int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, const i64* seeds,
-                          i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices, i64* out_select,
-                          i64* out_coo_col, const float* data, const i64* e_ids, float* out_data, i64 capacity,
-                          const i64* S_dev) {
+int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, i64 num_cols,
+                          const i64* seeds, i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices,
+                          i64* out_select, i64* out_coo_col, const float* data, const i64* e_ids, float* out_data,
+                          i64 capacity, const i64* S_dev, const i64* batch_ptr, const i64* batch_ids, i64 G) {
   const bool per_thread = k <= 16;  // small fanouts: one lane per column, one warp per tile of 32 columns
   const int grid = per_thread ? grid_for(S, kTpcThreads) : grid_for(S, kTileCols);
   TileState ts;
   int st = ctx_tile_state(ctx, per_thread ? (S + 31) / 32 + 1 : grid, stream, &ts);
   if (st != GSB_OK) return st;
-  SampleParams p{indptr, indices, seeds,  S,        k,        replace,         seed, out_indptr, out_indices,
-                 out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts, S_dev};
+  SampleParams p{indptr,     indices,     num_cols, seeds, S,        k,        replace,           seed, out_indptr,
+                 out_indices, out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts,
+                 S_dev,      batch_ptr,  batch_ids && batch_ptr ? batch_ids : nullptr,
+                 batch_ids && batch_ptr ? G : 0};
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
     if (k <= 4) k_sample_uniform_tpc<4><<<grid, kTpcThreads, 0, stream>>>(p);
@@ -521,9 +579,10 @@ using namespace gsb;
 
 extern "C" {
 
-int gsb_col_slice_count(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* seeds, int64_t S,
-                        int64_t* out_indptr, int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
+int gsb_col_slice_count(gsb_ctx* ctx, void* stream_, const int64_t* indptr, int64_t num_cols, const int64_t* seeds,
+                        int64_t S, int64_t* out_indptr, int64_t* nnz_host) {
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && S >= 0 && num_cols >= 0 && (seeds || S <= num_cols), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   const int grid = grid_for(S, kThreads);
   TileState ts;
@@ -531,42 +590,47 @@ int gsb_col_slice_count(gsb_ctx* ctx, void* stream_, const int64_t* indptr, cons
   if (st != GSB_OK) return st;
   {
     ScopedKernelTimer timer(ctx, KID_COUNT_SCAN, stream);
-    k_count_scan<<<grid, kThreads, 0, stream>>>(indptr, seeds, S, 0, COUNT_DEGREE, out_indptr, ctx_counters(ctx), ts);
+    k_count_scan<<<grid, kThreads, 0, stream>>>(indptr, num_cols, seeds, S, 0, COUNT_DEGREE, out_indptr,
+                                                ctx_counters(ctx), ts);
   }
   GSB_LAUNCH_OK();
   if (nnz_host) {
     const i64* c;
-    st = ctx_fetch_counters(ctx, stream, CNT_NNZ, 1, &c);
+    st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);
     if (st != GSB_OK) return st;
-    *nnz_host = c[0];
+    *nnz_host = c[CNT_NNZ];
+    if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
   }
   return GSB_OK;
 }
 
-int gsb_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
-                       const int64_t* seeds, int64_t S, const int64_t* out_indptr, int64_t* out_indices,
+int gsb_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, int64_t num_cols,
+                       const int64_t* seeds, int64_t S, const int64_t* out_indptr, int64_t D, int64_t* out_indices,
                        int64_t* out_select, int64_t* out_coo_col, const float* data, const int64_t* e_ids,
                        float* out_data) {
   // out_indices / out_select may be null only when the slice is empty (nothing is written then)
-  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
-  if (S == 0) return GSB_OK;
-  FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data,
-               nullptr, 0, 0};
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && S >= 0 && num_cols >= 0 && (seeds || S <= num_cols), GSB_ERR_INVALID_ARGUMENT);
+  if (S == 0 || D == 0) return GSB_OK;
+  GSB_REQUIRE(indices && out_indices && out_select, GSB_ERR_INVALID_ARGUMENT);
+  FillParams p{indptr, indices, num_cols, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids,
+               out_data, nullptr, 0, 0, false};
   {
     ScopedKernelTimer timer(ctx, KID_SLICE_FILL, (cudaStream_t)stream_);
-    k_slice_fill<false><<<grid_for(S, kTileCols), kThreads, 0, (cudaStream_t)stream_>>>(p);
-    k_slice_fill_edges<false><<<fill_grid(), kThreads, 0, (cudaStream_t)stream_>>>(p);
+    launch_fill<false>(p, D, (cudaStream_t)stream_);
   }
   GSB_LAUNCH_OK();
   return GSB_OK;
 }
 
 int gsb_batch_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
-                             const int64_t* seeds, int64_t S, const int64_t* nid_ptr, int64_t G,
+                             int64_t num_cols, const int64_t* seeds, int64_t S, const int64_t* nid_ptr, int64_t G,
                              int64_t encoding_size, const int64_t* out_indptr, int64_t* out_indices,
                              int64_t* out_select, int64_t* out_coo_col, int64_t* out_coo_offsets, const float* data,
                              const int64_t* e_ids, float* out_data) {
-  GSB_REQUIRE(ctx && indptr && out_indptr && nid_ptr && S >= 0 && G >= 1 && encoding_size >= 0,
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && nid_ptr && S >= 0 && G >= 1 && encoding_size >= 0 && num_cols >= 0 &&
+                  (seeds || S <= num_cols),
               GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
   if (out_coo_offsets) {
@@ -574,30 +638,27 @@ int gsb_batch_col_slice_fill(gsb_ctx* ctx, void* stream_, const int64_t* indptr,
     if (st != GSB_OK) return st;
   }
   if (S == 0) return GSB_OK;
-  FillParams p{indptr, indices, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids, out_data,
-               nid_ptr, G, encoding_size};
+  FillParams p{indptr, indices, num_cols, seeds, S, out_indptr, out_indices, out_select, out_coo_col, data, e_ids,
+               out_data, nid_ptr, G, encoding_size, false};
   {
     ScopedKernelTimer timer(ctx, KID_SLICE_FILL, stream);
-    if (encoding_size > 0) {
-      k_slice_fill<true><<<grid_for(S, kTileCols), kThreads, 0, stream>>>(p);
-      k_slice_fill_edges<true><<<fill_grid(), kThreads, 0, stream>>>(p);
-    } else {
-      k_slice_fill<false><<<grid_for(S, kTileCols), kThreads, 0, stream>>>(p);
-      k_slice_fill_edges<false><<<fill_grid(), kThreads, 0, stream>>>(p);
-    }
+    if (encoding_size > 0) launch_fill<true>(p, -1, stream);
+    else launch_fill<false>(p, -1, stream);
   }
   GSB_LAUNCH_OK();
   return GSB_OK;
 }
 
-int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
+int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices, int64_t num_cols,
                        const int64_t* seeds, int64_t S, int64_t k, int replace, uint64_t seed, int64_t* out_indptr,
                        int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col, const float* data,
                        const int64_t* e_ids, float* out_data, int64_t capacity, int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && S >= 0 && k >= 0 && num_cols >= 0 && (seeds || S <= num_cols),
+              GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
-  int st = sample_uniform_launch(ctx, stream, indptr, indices, seeds, S, k, replace, (u64)seed, out_indptr,
+  int st = sample_uniform_launch(ctx, stream, indptr, indices, num_cols, seeds, S, k, replace, (u64)seed, out_indptr,
                                  out_indices, out_select, out_coo_col, data, e_ids, out_data, capacity);
   if (st != GSB_OK) return st;
   if (nnz_host) {
@@ -611,13 +672,14 @@ int gsb_sample_uniform(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const
 }
 
 int gsb_sample_one_keepdim(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
-                           const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
+                           int64_t num_cols, const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
                            int64_t* out_indices, int64_t* out_select) {
-  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && S >= 0 && num_cols >= 0 && (S == 0 || seeds), GSB_ERR_INVALID_ARGUMENT);
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_KEEPDIM, (cudaStream_t)stream_);
     k_sample_one_keepdim<<<grid_for(S + 1, kThreads), kThreads, 0, (cudaStream_t)stream_>>>(
-        indptr, indices, seeds, S, (u64)seed, out_indptr, out_indices, out_select);
+        indptr, indices, num_cols, seeds, S, (u64)seed, ctx_counters(ctx), out_indptr, out_indices, out_select);
   }
   GSB_LAUNCH_OK();
   return GSB_OK;

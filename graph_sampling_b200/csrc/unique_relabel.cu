@@ -147,7 +147,8 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
                                   const int64_t* item_lens_host, int num_item_arrays, int64_t* out_unique,
                                   const int64_t* const* relabel_ptrs_host, const int64_t* relabel_lens_host,
                                   int64_t* const* out_relabel_ptrs_host, int num_relabel, int64_t* unique_host) {
-  GSB_REQUIRE(ctx && num_item_arrays >= 1 && item_ptrs_host && item_lens_host, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(num_item_arrays >= 1 && item_ptrs_host && item_lens_host, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(num_relabel == 0 || (relabel_ptrs_host && relabel_lens_host && out_relabel_ptrs_host),
               GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -164,7 +165,8 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
   // Fast path for the shapes gs::Graph produces — unique(cat(a, b)) with b (or nothing) relabelled, or
   // unique(a) with a relabelled: 8-byte slots and warp-tile kernels, valid for ids below 2^32 - 1.  It needs
   // the read-back (to learn whether an id was too large); if one was, the wide-slot path below redoes the call.
-  if (unique_host && n > 0 && n < (1ll << 30) && num_item_arrays <= 2 && num_relabel <= 1) {
+  const i64 forced_slots = ctx_option(ctx, GSB_OPT_TABLE_SLOTS);
+  if (forced_slots == 0 && unique_host && n > 0 && n < (1ll << 30) && num_item_arrays <= 2 && num_relabel <= 1) {
     const i64* last = item_ptrs_host[num_item_arrays - 1];
     const i64 last_len = item_lens_host[num_item_arrays - 1];
     const bool rel_ok = num_relabel == 0 || (relabel_ptrs_host[0] == last && relabel_lens_host[0] == last_len);
@@ -181,6 +183,12 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
   Table table;
   u64 cap;
   table_geometry(n, &cap, &table.shift);
+  if (forced_slots > 0) {  // a caller-chosen table size (GSB_OPT_TABLE_SLOTS), rounded down to a power of two
+    int bits = 1;
+    while (bits < 40 && (2ull << bits) <= (u64)forced_slots) ++bits;
+    cap = 1ull << bits;
+    table.shift = 64 - bits;
+  }
   table.mask = cap - 1;
   void* ws;
   st = ctx_reserve_workspace(ctx, cap * sizeof(Slot), &ws);
@@ -230,8 +238,11 @@ extern "C" int gsb_unique_relabel(gsb_ctx* ctx, void* stream_, const int64_t* co
 // cudaMalloc (which synchronises the whole device) is forbidden.  gsb_unique_relabel needs a context,
 // and the context grows its scratch with cudaMalloc the first time a size is seen.  The entry point
 // below needs neither: its hash table, look-back words and counters live in file-scope __device__
-// arrays that every GPU loading the library carries until the process exits (about 8.1 MB), which
-// bounds the problem size (GSB_STATIC_MAX_ITEMS items per call).
+// arrays (about 8.1 MB) that a GPU carries from the moment the CUDA runtime loads this module on it — with
+// lazy module loading that is the first call made with that device current, which is therefore the one call
+// that does reserve device memory and may synchronise; make it (n = 0 is enough) before the phase in which
+// nothing may be allocated — until the process exits.  This bounds the problem size (GSB_STATIC_MAX_ITEMS
+// items per call).
 //
 // All calls share these arrays and the arrays keep the previous call's contents, so each call first
 // clears (stream-ordered) everything that must start empty.  Two calls that overlap on the GPU —
@@ -264,9 +275,15 @@ static int static_scratch_for_current_device(StaticScratch** out) {
   StaticScratch* s = &s_static[dev];
   if (!s->ready) {
     void *a = nullptr, *b = nullptr, *c = nullptr;
-    if (cudaGetSymbolAddress(&a, g_static_slots) != cudaSuccess) return GSB_ERR_CUDA;
-    if (cudaGetSymbolAddress(&b, g_static_tile_words) != cudaSuccess) return GSB_ERR_CUDA;
-    if (cudaGetSymbolAddress(&c, g_static_counters) != cudaSuccess) return GSB_ERR_CUDA;
+    // With lazy module loading this is where the arrays come into existence on the device: a failure here is
+    // most likely the device being out of memory for them.
+    cudaError_t e = cudaGetSymbolAddress(&a, g_static_slots);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&b, g_static_tile_words);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&c, g_static_counters);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return e == cudaErrorMemoryAllocation ? GSB_ERR_OUT_OF_MEMORY : GSB_ERR_CUDA;
+    }
     s->slots = (Slot*)a;
     s->tile_words = (u64*)b;
     s->counters = (i64*)c;

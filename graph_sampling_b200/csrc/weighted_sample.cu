@@ -33,6 +33,7 @@ struct WeightedParams {
   const i64* indptr;
   const i64* indices;
   const float* probs;
+  i64 num_cols;
   const i64* seeds;
   i64 S;
   i64 k;
@@ -219,8 +220,13 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
   bool is_long = false;
   if (tid < ncol) {
     const i64 col = p.seeds ? p.seeds[base + tid] : base + tid;
-    const i64 b = p.indptr[col];
-    const i64 d = p.indptr[col + 1] - b;
+    i64 b = 0, d = 0;  // a seed outside the graph counts as an empty column and is never dereferenced
+    if ((u64)col < (u64)p.num_cols) {
+      b = p.indptr[col];
+      d = p.indptr[col + 1] - b;
+    } else {
+      raise_error(p.counters, GSB_ERR_INDEX_RANGE, base + tid);
+    }
     f = p.replace ? (d > 0 ? k : 0) : (d < k ? d : k);
     is_long = !p.replace && d > kLongColumn && d > k;
     s_in[tid] = b;
@@ -331,11 +337,13 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
 using namespace gsb;
 
 extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64_t* indices,
-                                   const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
+                                   int64_t num_cols, const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
                                    uint64_t seed, int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
                                    int64_t* out_coo_col, const float* data, const int64_t* e_ids, float* out_data,
                                    int64_t capacity, int64_t* nnz_host) {
-  GSB_REQUIRE(ctx && indptr && out_indptr && S >= 0 && k >= 0, GSB_ERR_INVALID_ARGUMENT);
+  GSB_ENTER(ctx);
+  GSB_REQUIRE(indptr && out_indptr && S >= 0 && k >= 0 && num_cols >= 0 && (seeds || S <= num_cols),
+              GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(replace || k <= 32, GSB_ERR_UNSUPPORTED);
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -344,7 +352,7 @@ extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* i
   TileState ts;
   int st = ctx_tile_state(ctx, grid, stream, &ts);
   if (st != GSB_OK) return st;
-  WeightedParams p{indptr, indices,    probs,       seeds, S,     k,        replace,  (u64)seed,         out_indptr,
+  WeightedParams p{indptr, indices,    probs, num_cols,      seeds, S,     k,        replace,  (u64)seed,         out_indptr,
                    out_indices, out_select, out_coo_col, data,  e_ids, out_data, capacity, ctx_counters(ctx), ts};
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_WEIGHTED, stream);

@@ -70,6 +70,20 @@ class Context:
     def check_device(self, where="device status"):
         self.check(self.lib.gsb_check_device_status(self.handle, _stream()), where)
 
+    OPTIONS = {"max_polls": 0, "table_slots": 1, "relabel_path": 2, "direct_table_budget": 3}
+
+    def set_option(self, name, value):
+        """gsb_ctx_set_option by name: max_polls, table_slots, relabel_path (0 auto, 1 hash, 2 direct),
+        direct_table_budget (bytes)."""
+        self.check(self.lib.gsb_ctx_set_option(self.handle, c_int(self.OPTIONS[name]), c_i64(int(value))),
+                   "gsb_ctx_set_option")
+
+    def get_option(self, name):
+        v = c_i64(0)
+        self.check(self.lib.gsb_ctx_get_option(self.handle, c_int(self.OPTIONS[name]), ctypes.byref(v)),
+                   "gsb_ctx_get_option")
+        return v.value
+
     def launch_count(self):
         return int(self.lib.gsb_launch_count(self.handle))
 
@@ -170,15 +184,16 @@ def csc_col_slicing(indptr, indices, column_ids, with_coo=True, data=None, e_ids
     S = column_ids.numel() if column_ids is not None else indptr.numel() - 1
     sub_indptr = _empty(S + 1, indptr)
     nnz = c_i64(0)
-    ctx.check(lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), _p(column_ids), c_i64(S), _p(sub_indptr),
-                                      ctypes.byref(nnz)), "gsb_col_slice_count")
+    num_cols = indptr.numel() - 1
+    ctx.check(lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), c_i64(num_cols), _p(column_ids), c_i64(S),
+                                      _p(sub_indptr), ctypes.byref(nnz)), "gsb_col_slice_count")
     n = nnz.value
     sub_indices, select = _empty(n, indptr), _empty(n, indptr)
     coo_col = _empty(n, indptr) if with_coo else None
     out_data = _empty(n, indptr, torch.float32) if data is not None else None
-    ctx.check(lib.gsb_col_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
-                                     _p(sub_indptr), _p(sub_indices), _p(select), _p(coo_col), _p(data), _p(e_ids),
-                                     _p(out_data)), "gsb_col_slice_fill")
+    ctx.check(lib.gsb_col_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(num_cols), _p(column_ids),
+                                     c_i64(S), _p(sub_indptr), c_i64(n), _p(sub_indices), _p(select), _p(coo_col),
+                                     _p(data), _p(e_ids), _p(out_data)), "gsb_col_slice_fill")
     if data is not None:
         return sub_indptr, coo_col, sub_indices, select, out_data
     return sub_indptr, coo_col, sub_indices, select
@@ -196,7 +211,8 @@ def _sample_uniform(indptr, indices, column_ids, fanout, replace, with_coo, seed
     coo_col = _empty(cap, indptr) if with_coo else None
     out_data = _empty(cap, indptr, torch.float32) if data is not None else None
     nnz = c_i64(0)
-    ctx.check(ctx.lib.gsb_sample_uniform(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+    ctx.check(ctx.lib.gsb_sample_uniform(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(indptr.numel() - 1),
+                                         _p(column_ids), c_i64(S),
                                          c_i64(int(fanout)), c_int(int(bool(replace))), c_u64(next_seed(seed)),
                                          _p(sub_indptr), _p(sub_indices), _p(select), _p(coo_col), _p(data), _p(e_ids),
                                          _p(out_data), c_i64(cap), ctypes.byref(nnz)), "gsb_sample_uniform")
@@ -227,7 +243,8 @@ def fused_csc_col_slicing_sampling_one_keepdim(indptr, indices, column_ids, seed
     ctx = ctx or default_context(indptr.device)
     S = column_ids.numel()
     sub_indptr, sub_indices, select = _empty(S + 1, indptr), _empty(S, indptr), _empty(S, indptr)
-    ctx.check(ctx.lib.gsb_sample_one_keepdim(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+    ctx.check(ctx.lib.gsb_sample_one_keepdim(ctx.handle, _stream(), _p(indptr), _p(indices),
+                                             c_i64(indptr.numel() - 1), _p(column_ids), c_i64(S),
                                              c_u64(next_seed(seed)), _p(sub_indptr), _p(sub_indices), _p(select)),
               "gsb_sample_one_keepdim")
     return sub_indptr, sub_indices, select
@@ -280,7 +297,8 @@ def fused_random_walk(seeds, walk_length, indices, indptr, seed=None, layout=0, 
     ctx = ctx or default_context(indptr.device)
     W, L = seeds.numel(), int(walk_length)
     out = _empty(W * (L + 1), indptr)
-    ctx.check(ctx.lib.gsb_random_walk(ctx.handle, _stream(), _p(indptr), _p(indices), _p(seeds), c_i64(W), c_i64(L),
+    ctx.check(ctx.lib.gsb_random_walk(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(indptr.numel() - 1),
+                                      _p(seeds), c_i64(W), c_i64(L),
                                       c_u64(next_seed(seed)), c_int(int(layout)), c_i64(int(walker_offset)), _p(out)),
               "gsb_random_walk")
     return out.reshape(W, L + 1)
@@ -298,7 +316,8 @@ def fused_metapath_random_walk(seeds, metapath, graphs, seed=None, layout=0, wal
     ip = (c_vp * max(1, len(pairs)))(*[a.data_ptr() for a, _ in pairs])
     ix = (c_vp * max(1, len(pairs)))(*[b.data_ptr() for _, b in pairs])
     mp = (c_i64 * max(1, L))(*path)
-    ctx.check(ctx.lib.gsb_metapath_random_walk(ctx.handle, _stream(), ip, ix, c_int(len(pairs)), mp, c_i64(L),
+    nn = (c_i64 * max(1, len(pairs)))(*[a.numel() - 1 for a, _ in pairs])
+    ctx.check(ctx.lib.gsb_metapath_random_walk(ctx.handle, _stream(), ip, ix, nn, c_int(len(pairs)), mp, c_i64(L),
                                                _p(seeds), c_i64(W), c_u64(next_seed(seed)), c_int(int(layout)),
                                                c_i64(int(walker_offset)), _p(out)), "gsb_metapath_random_walk")
     return out.reshape(W, L + 1)
@@ -321,14 +340,16 @@ def csc_col_row_slicing(indptr, indices, column_ids, row_ids, col_ptr=None, row_
     G = 1 if col_ptr is None else col_ptr.numel() - 1
     slice_indptr = _empty(S + 1, indptr)
     d = c_i64(0)
-    ctx.check(ctx.lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), _p(column_ids), c_i64(S),
+    num_cols = indptr.numel() - 1
+    ctx.check(ctx.lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), c_i64(num_cols), _p(column_ids), c_i64(S),
                                           _p(slice_indptr), ctypes.byref(d)), "gsb_col_slice_count")
     D = d.value
     sub_indptr = _empty(S + 1, indptr)
     sub_indices, select = _empty(D, indptr), _empty(D, indptr)
     out_data = _empty(D, indptr, torch.float32) if data is not None else None
     nnz = c_i64(0)
-    ctx.check(ctx.lib.gsb_col_row_slice(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+    ctx.check(ctx.lib.gsb_col_row_slice(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(num_cols),
+                                        _p(column_ids), c_i64(S),
                                         _p(slice_indptr), c_i64(D), _p(row_ids), c_i64(R), _p(col_ptr), _p(row_ptr),
                                         c_i64(G), c_i64(int(encoding_size)), c_int(1 if col_ptr is None else 0),
                                         _p(sub_indptr), _p(sub_indices), _p(select), _p(data), _p(e_ids),
@@ -419,7 +440,8 @@ def csc_col_sampling_probs(indptr, indices, probs, fanout, replace, with_coo=Tru
     coo_col = _empty(cap, indptr) if with_coo else None
     out_data = _empty(cap, indptr, torch.float32) if data is not None else None
     nnz = c_i64(0)
-    ctx.check(ctx.lib.gsb_sample_weighted(ctx.handle, _stream(), _p(indptr), _p(indices), _p(probs), _p(column_ids),
+    ctx.check(ctx.lib.gsb_sample_weighted(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(indptr.numel() - 1),
+                                          _p(probs), _p(column_ids),
                                           c_i64(S), c_i64(int(fanout)), c_int(int(bool(replace))),
                                           c_u64(next_seed(seed)), _p(sub_indptr), _p(sub_indices), _p(select),
                                           _p(coo_col), _p(data), _p(e_ids), _p(out_data), c_i64(cap),
@@ -604,13 +626,15 @@ def coo2csc(row, col, num_cols, col_sorted, ctx=None):
 
 
 # ---- batched ("super-batch") operators --------------------------------------------------------------
-def batch_csr_relabel(seeds, seeds_ptr, indices, indices_ptr, indices_count=None, ctx=None, sync=True):
+def batch_csr_relabel(seeds, seeds_ptr, indices, indices_ptr, indices_count=None, ctx=None, sync=True, num_nodes=0,
+                      seeds_distinct=False):
     """BatchCSRRelabelCUDA (src/cuda/batch_relabel.cu, gs_ops._CAPI_BatchCSRRelabel) →
     (unique_tensor, unique_tensor_ptr, relabeled_indices, indices_ptr): per batch b, the distinct ids of
     cat(seeds[seeds_ptr[b]:seeds_ptr[b+1]], indices[indices_ptr[b]:indices_ptr[b+1]]) in first-occurrence
     order and the batch-local positions of its indices.  `indices` may be longer than the valid edge
     count (indices_ptr[-1]); with sync=False the outputs keep their upper-bound length and the exact
-    sizes stay on the device."""
+    sizes stay on the device.  num_nodes > 0 (every id is below it) allows the direct-address tables;
+    seeds_distinct promises that no id repeats among the seeds of a batch."""
     seeds, seeds_ptr = _i64(seeds, "seeds"), _i64(seeds_ptr, "seeds_ptr")
     indices, indices_ptr = _i64(indices, "indices"), _i64(indices_ptr, "indices_ptr")
     ctx = ctx or default_context(seeds.device)
@@ -621,7 +645,8 @@ def batch_csr_relabel(seeds, seeds_ptr, indices, indices_ptr, indices_count=None
     rel = _empty(cap, seeds)
     nu, ne = c_i64(0), c_i64(0)
     ctx.check(ctx.lib.gsb_batch_unique_relabel(ctx.handle, _stream(), _p(seeds), _p(seeds_ptr), c_i64(seeds.numel()),
-                                               _p(indices), _p(indices_ptr), c_i64(cap), c_i64(G), _p(uniq),
+                                               _p(indices), _p(indices_ptr), c_i64(cap), c_i64(G),
+                                               c_i64(int(num_nodes)), c_int(1 if seeds_distinct else 0), _p(uniq),
                                                _p(uniq_ptr), _p(rel), ctypes.byref(nu) if sync else None,
                                                ctypes.byref(ne) if sync else None), "gsb_batch_unique_relabel")
     if sync:
@@ -683,14 +708,16 @@ def batch_csc_col_slicing(indptr, indices, column_ids, nid_ptr, encoding_size, w
     S, G = column_ids.numel(), nid_ptr.numel() - 1
     sub_indptr = _empty(S + 1, indptr)
     nnz = c_i64(0)
-    ctx.check(ctx.lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), _p(column_ids), c_i64(S), _p(sub_indptr),
-                                          ctypes.byref(nnz)), "gsb_col_slice_count")
+    num_cols = indptr.numel() - 1
+    ctx.check(ctx.lib.gsb_col_slice_count(ctx.handle, _stream(), _p(indptr), c_i64(num_cols), _p(column_ids), c_i64(S),
+                                          _p(sub_indptr), ctypes.byref(nnz)), "gsb_col_slice_count")
     n = nnz.value
     sub_indices, select = _empty(n, indptr), _empty(n, indptr)
     coo_col = _empty(n, indptr) if with_coo else None
     offsets = _empty(G + 1, indptr)
     out_data = _empty(n, indptr, torch.float32) if data is not None else None
-    ctx.check(ctx.lib.gsb_batch_col_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), _p(column_ids), c_i64(S),
+    ctx.check(ctx.lib.gsb_batch_col_slice_fill(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(num_cols),
+                                               _p(column_ids), c_i64(S),
                                                _p(nid_ptr), c_i64(G), c_i64(int(encoding_size) if encoding else 0),
                                                _p(sub_indptr), _p(sub_indices), _p(select), _p(coo_col), _p(offsets),
                                                _p(data), _p(e_ids), _p(out_data)), "gsb_batch_col_slice_fill")
@@ -859,7 +886,7 @@ class OutputArena:
 
 
 def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None, sync=True,
-                        arena=None):
+                        arena=None, batch_ids=None, seeds_distinct=False):
     """Multi-hop GraphSAGE sampling of G minibatches at once (the loop of
     examples/graphsage/batching.py:56-90): per hop one fused slice+sample over the seeds of all batches,
     then one batched unique + relabel; each batch's frontier becomes its seeds for the next hop.
@@ -873,10 +900,21 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
     per hop, so capacities grow by (1+k) per hop), the valid prefixes are given by the offset arrays, and
     every dict carries `counts`, a 3-element device tensor (seeds, edges, frontier) to read when convenient.
 
-    arena: an OutputArena to take the output arrays from (they are then valid until the next call with it)."""
+    arena: an OutputArena to take the output arrays from (they are then valid until the next call with it).
+
+    batch_ids: int64 device tensor with one caller-chosen number (< 2^32) per minibatch, e.g. its index in the
+    epoch.  With it the draws of a minibatch are keyed by (seed, its number, column index inside the minibatch),
+    so the minibatch receives the same sample whichever call, group size or GPU processes it; without it the key
+    is the column's position in the call.
+    seeds_distinct: promise that no id repeats among the seeds of one minibatch (the frontiers that feed hops
+    2, 3, ... are distinct by construction and are always treated so)."""
     ctx = ctx or default_context(indptr.device)
     out = []
     base_seed = next_seed(seed)
+    batch_ids = _i64(batch_ids, "batch_ids", allow_none=True)
+    if batch_ids is not None and batch_ids.numel() != seeds_ptr.numel() - 1:
+        raise ValueError("batch_ids needs one entry per minibatch")
+    num_nodes = indptr.numel() - 1
 
     def alloc(name, hop, n):
         return _empty(n, indptr) if arena is None else arena.get((name, hop), n, indptr)
@@ -890,9 +928,11 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
         indices_ptr, uniq_ptr = alloc("indices_ptr", hop, G + 1), alloc("frontier_ptr", hop, G + 1)
         uniq = alloc("frontier", hop, S + cap)
         nu, ne = c_i64(0), c_i64(0)
-        ctx.check(ctx.lib.gsb_sage_hop(ctx.handle, _stream(), _p(indptr), _p(indices), _p(seeds), _p(seeds_ptr),
-                                       c_i64(G), c_i64(S), c_i64(int(k)), c_int(int(bool(replace))),
-                                       c_u64((base_seed + hop) & (2**64 - 1)), _p(sub_indptr), _p(sub_indices),
+        flags = 1 if (hop > 0 or seeds_distinct) else 0
+        ctx.check(ctx.lib.gsb_sage_hop(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(num_nodes), _p(seeds),
+                                       _p(seeds_ptr), _p(batch_ids), c_i64(G), c_i64(S), c_i64(int(k)),
+                                       c_int(int(bool(replace))), c_u64((base_seed + hop) & (2**64 - 1)),
+                                       c_int(flags), _p(sub_indptr), _p(sub_indices),
                                        _p(select), _p(indices_ptr), _p(uniq), _p(uniq_ptr), _p(rel),
                                        ctypes.byref(nu) if sync else None, ctypes.byref(ne) if sync else None),
                   "gsb_sage_hop")

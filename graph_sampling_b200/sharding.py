@@ -21,6 +21,15 @@ def batch_owner(batch_index: int, world: int) -> int:
     return batch_index % world
 
 
+def shard_batch_ids(num_batches: int, rank: int, world: int) -> torch.Tensor:
+    """Global numbers of the minibatches shard_batches hands to `rank` (int64, on the CPU).  Passed to the batched
+    sampler as `batch_ids`, they key every minibatch's random stream by its GLOBAL number, so the sample a
+    minibatch receives does not depend on the number of ranks or on how a rank groups its minibatches into calls."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of {world}")
+    return torch.arange(rank, int(num_batches), world, dtype=torch.int64)
+
+
 def shard_walkers(num_walkers: int, rank: int, world: int) -> Tuple[int, int]:
     """Contiguous ranges: returns (offset, count) of the walkers of `rank`.  The offset is passed to the
     walk kernel as `walker_offset`, which keys every walker's random stream by its GLOBAL index, so the

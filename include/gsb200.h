@@ -17,6 +17,13 @@
  *    calls sharing a context must be ordered on one stream (use one context per stream/thread).
  *    Scratch grows on demand with cudaMalloc the first time a size is seen (this synchronises the
  *    device once); steady-state calls allocate nothing;
+ *  - a context belongs to the CUDA device it was created on: every entry point checks that this device is
+ *    current and returns GSB_ERR_INVALID_ARGUMENT otherwise, before anything is launched;
+ *  - seed / column / walker ids are checked against `num_cols` (the number of columns of the operand,
+ *    indptr has num_cols + 1 entries) on the device: an id outside [0, num_cols) counts as an empty column
+ *    (or ends a walk with -1), its offsets are never read, and GSB_ERR_INDEX_RANGE is recorded in the context
+ *    (returned by the same call when it waits for the stream, else by gsb_check_device_status).  The reference
+ *    reads indptr[id] unchecked (src/cuda/slicing.cu:133-141, src/cuda/fusion/random_walk.cu:19-36);
  *  - there is no CPU fallback: without a CUDA device gsb_ctx_create fails.
  */
 #ifndef GSB200_H_
@@ -44,7 +51,8 @@ enum gsb_status {
   GSB_ERR_LOOKBACK_TIMEOUT = -5, /* a bounded device-side wait expired */
   GSB_ERR_TABLE_FULL = -6,       /* hash-table probe sequence exhausted */
   GSB_ERR_UNSUPPORTED = -7,
-  GSB_ERR_INDEX_RANGE = -8       /* an id was outside the graph (checked builds / debug mode) */
+  GSB_ERR_INDEX_RANGE = -8       /* a seed / column / walker / node id was outside [0, num_cols): the entry is
+                                    treated as an empty column (or ends the walk) and nothing is read for it */
 };
 
 typedef struct gsb_ctx gsb_ctx;
@@ -62,6 +70,32 @@ GSB_API const char* gsb_last_error_message(gsb_ctx* ctx);
 /* Waits for `stream` and returns the first device-side error recorded by kernels of this context
  * since the last check (GSB_OK if none), then clears it. */
 GSB_API int gsb_check_device_status(gsb_ctx* ctx, void* stream);
+/* Per-context settings.  No counterpart in the reference (its limits are compile-time constants).
+ *  GSB_OPT_MAX_POLLS            polls of one look-back window before a scan gives up waiting for a predecessor
+ *                               tile and records GSB_ERR_LOOKBACK_TIMEOUT (default 2^22; every poll sleeps 20 ns);
+ *  GSB_OPT_TABLE_SLOTS          > 0: gsb_unique_relabel builds its hash table with this many slots (rounded down
+ *                               to a power of two) instead of sizing it from the item count — a table that is too
+ *                               small reports GSB_ERR_TABLE_FULL; 0 (default) = automatic;
+ *  GSB_OPT_RELABEL_PATH         how gsb_sage_hop / gsb_batch_unique_relabel find first occurrences: 0 (default) =
+ *                               direct-address tables when they fit the budget, else hash tables; 1 = hash tables;
+ *                               2 = direct-address tables (GSB_ERR_OUT_OF_MEMORY when they do not fit);
+ *  GSB_OPT_DIRECT_TABLE_BUDGET  bytes the direct-address tables (8 bytes x num_nodes x minibatches per call) may
+ *                               take, default 6 GiB. */
+enum gsb_option {
+  GSB_OPT_MAX_POLLS = 0,
+  GSB_OPT_TABLE_SLOTS = 1,
+  GSB_OPT_RELABEL_PATH = 2,
+  GSB_OPT_DIRECT_TABLE_BUDGET = 3,
+  GSB_OPT_NUM = 4
+};
+GSB_API int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value);
+GSB_API int gsb_ctx_get_option(gsb_ctx* ctx, int option, int64_t* value_host);
+/* Self-test of the bounded wait (no counterpart in the reference): runs the single-pass scan over `tiles` tiles
+ * that each contribute 1, except that tile `silent_tile` never publishes its total (silent_tile < 0: every tile
+ * publishes).  out_prefix[t] (DEVICE, `tiles` entries) receives the exclusive prefix tile t obtained.  With a silent
+ * tile the later tiles give up after GSB_OPT_MAX_POLLS polls, the call waits for the stream and returns
+ * GSB_ERR_LOOKBACK_TIMEOUT; the context stays usable.  tiles <= 4096. */
+GSB_API int gsb_selftest_lookback(gsb_ctx* ctx, void* stream, int tiles, int silent_tile, int64_t* out_prefix);
 /* Library build information: "gsb200 <version> sm_100a". */
 GSB_API const char* gsb_version(void);
 /* Number of kernel launches issued through this context so far (all entry points). */
@@ -87,18 +121,21 @@ GSB_API int gsb_profile_read(gsb_ctx* ctx, int kid, double* total_ms, int64_t* l
  *
  * gsb_col_slice_count: out_indptr[i] = sum of the degrees of seeds[0..i) (S+1 entries), computed
  *   by one kernel; waits for the stream and returns the total in *nnz_host.  seeds == NULL means
- *   "every column 0..S-1".
+ *   "every column 0..S-1" (S <= num_cols).
  * gsb_col_slice_fill: for each seed column copies its index segment in order:
  *   out_indices = GLOBAL row ids, out_select = position in `indices`, out_coo_col (optional) =
  *   position of the seed in `seeds`.  If `data` is given, out_data[j] = data[e_ids ? e_ids[sel] :
  *   sel] (the edge-data gather gs::Graph::Slicing performs afterwards, src/graph.cc:295-308).
+ *   D = out_indptr[S] as reported by gsb_col_slice_count, or -1 if the caller does not know it: with D the
+ *   call launches only the copy kernel that suits the shape (few long columns / many short ones), without
+ *   it both are launched and the device decides.
  */
-GSB_API int gsb_col_slice_count(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* seeds, int64_t S,
-                                int64_t* out_indptr, int64_t* nnz_host);
+GSB_API int gsb_col_slice_count(gsb_ctx* ctx, void* stream, const int64_t* indptr, int64_t num_cols,
+                                const int64_t* seeds, int64_t S, int64_t* out_indptr, int64_t* nnz_host);
 GSB_API int gsb_col_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                               const int64_t* seeds, int64_t S, const int64_t* out_indptr, int64_t* out_indices,
-                               int64_t* out_select, int64_t* out_coo_col, const float* data, const int64_t* e_ids,
-                               float* out_data);
+                               int64_t num_cols, const int64_t* seeds, int64_t S, const int64_t* out_indptr,
+                               int64_t D, int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col,
+                               const float* data, const int64_t* e_ids, float* out_data);
 
 /* ---- uniform per-column sampling ------------------------------------------------------------
  * Replaces gs::impl::CSCColSamplingCUDA (src/cuda/sampling.cu:12-167; seeds == NULL: all S columns
@@ -115,7 +152,7 @@ GSB_API int gsb_col_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr
  * Optional: out_coo_col (position of the column), data/e_ids/out_data as in gsb_col_slice_fill.
  */
 GSB_API int gsb_sample_uniform(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                               const int64_t* seeds, int64_t S, int64_t k, int replace, uint64_t seed,
+                               int64_t num_cols, const int64_t* seeds, int64_t S, int64_t k, int replace, uint64_t seed,
                                int64_t* out_indptr, int64_t* out_indices, int64_t* out_select, int64_t* out_coo_col,
                                const float* data, const int64_t* e_ids, float* out_data, int64_t capacity,
                                int64_t* nnz_host);
@@ -123,7 +160,7 @@ GSB_API int gsb_sample_uniform(gsb_ctx* ctx, void* stream, const int64_t* indptr
 /* Keep-dimension walk step: exactly one draw per seed, -1 / -1 for an isolated seed.  Replaces
  * gs::impl::fusion::FusedCSCColSlicingSamplingOneKeepDimCUDA (src/cuda/fusion/slice_sampling.cu:156-200). */
 GSB_API int gsb_sample_one_keepdim(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                                   const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
+                                   int64_t num_cols, const int64_t* seeds, int64_t S, uint64_t seed, int64_t* out_indptr,
                                    int64_t* out_indices, int64_t* out_select);
 
 /* ---- unique (first-occurrence order) + relabel ------------------------------------------------
@@ -149,10 +186,11 @@ GSB_API int gsb_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* const*
  * any; -1 is absorbing.  layout 0 = the reference's memory order out[step * W + walker]
  * (which it returns shaped [W, L+1] without transposing); layout 1 = walker-major
  * out[walker * (L+1) + step].  The draw for (walker w, step s) is keyed by
- * (seed, walker_offset + w, s), so a sharded run reproduces the unsharded one.
+ * (seed, walker_offset + w, s), so a sharded run reproduces the unsharded one.  A start node or a visited
+ * node outside [0, num_nodes) ends that walk with -1 and records GSB_ERR_INDEX_RANGE.
  */
 GSB_API int gsb_random_walk(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                            const int64_t* seeds, int64_t W, int64_t L, uint64_t seed, int layout,
+                            int64_t num_nodes, const int64_t* seeds, int64_t W, int64_t L, uint64_t seed, int layout,
                             int64_t walker_offset, int64_t* out);
 
 /* ---- weighted per-column sampling -------------------------------------------------------------
@@ -169,7 +207,7 @@ GSB_API int gsb_random_walk(gsb_ctx* ctx, void* stream, const int64_t* indptr, c
  * GSB_ERR_UNSUPPORTED.
  */
 GSB_API int gsb_sample_weighted(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                                const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
+                                int64_t num_cols, const float* probs, const int64_t* seeds, int64_t S, int64_t k, int replace,
                                 uint64_t seed, int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
                                 int64_t* out_coo_col, const float* data, const int64_t* e_ids, float* out_data,
                                 int64_t capacity, int64_t* nnz_host);
@@ -258,10 +296,20 @@ GSB_API int gsb_coo2csc(gsb_ctx* ctx, void* stream, const int64_t* key, const in
  * batch's frontier.  seeds_ptr / indices_ptr / out_unique_ptr are DEVICE arrays of G + 1 entries; the
  * number of edges is read from indices_ptr[G] on the device, so the call can follow a sampling call
  * without a host round trip; `indices_capacity` is an upper bound on it used to size scratch and grids.
- * Ids must be below 2^32 - 1 and num_seeds + indices_capacity below 2^31.  Waits for the stream only if
+ * Ids must be below 2^32 - 1 and num_seeds + indices_capacity below 2^30.  Waits for the stream only if
  * a *_host pointer is given.
+ * num_nodes > 0 promises that every id is in [0, num_nodes): first occurrences are then found in direct-address
+ * tables (one 8-byte word per node and minibatch, kept by the context and never cleared; see GSB_OPT_RELABEL_PATH /
+ * GSB_OPT_DIRECT_TABLE_BUDGET) instead of hash tables — one atomicMin, one load and half a load per item instead of
+ * about 4.5 dependent accesses; an id outside the range records GSB_ERR_INDEX_RANGE and is relabelled -1.
+ * num_nodes == 0 (unknown) always takes the hash tables.  Results are identical.
+ * flags: GSB_SEEDS_DISTINCT promises that no id repeats among the seeds of one minibatch (true for the frontier a
+ * previous hop returned), which spares the table read of every seed.
+ * If seeds_ptr[G] > num_seeds or indices_ptr[G] > indices_capacity on the device, GSB_ERR_CAPACITY is recorded and
+ * the passes that follow do nothing.
  * gsb_batch_edge_offsets: out_indices_ptr[b] = sub_indptr[seeds_ptr[b]] for b in [0, G].
  */
+#define GSB_SEEDS_DISTINCT 1
 /* gsb_split_indptr replaces gs::impl::SplitIndptrByOffsetCUDA / SplitIndptrBySizeCUDA
  * (src/cuda/batch_split.cu:11-104; gs_ops._CAPI_IndptrSplitByOffset / _CAPI_IndptrSplitBySize): cuts one
  * offset array into per-batch offset arrays that start at 0.  Batch b covers columns
@@ -273,8 +321,9 @@ GSB_API int gsb_batch_edge_offsets(gsb_ctx* ctx, void* stream, const int64_t* su
                                    int64_t G, int64_t* out_indices_ptr);
 GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* seeds, const int64_t* seeds_ptr,
                                      int64_t num_seeds, const int64_t* indices, const int64_t* indices_ptr,
-                                     int64_t indices_capacity, int64_t G, int64_t* out_unique, int64_t* out_unique_ptr,
-                                     int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
+                                     int64_t indices_capacity, int64_t G, int64_t num_nodes, int flags,
+                                     int64_t* out_unique, int64_t* out_unique_ptr, int64_t* out_relabeled,
+                                     int64_t* unique_total_host, int64_t* edges_total_host);
 
 /* ---- induced-subgraph slicing, index search, fused divide + sum -------------------------------------------
  * gsb_col_row_slice replaces gs::impl::fusion::CSCColRowSlicingCUDA and BatchCSCColRowSlicingCUDA
@@ -290,7 +339,7 @@ GSB_API int gsb_batch_unique_relabel(gsb_ctx* ctx, void* stream, const int64_t* 
  * positions inside the unmaterialised column slice, which its own data gather then misuses: src/graph.cc:131-137).
  */
 GSB_API int gsb_col_row_slice(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                              const int64_t* column_ids, int64_t S, const int64_t* sub_indptr, int64_t D,
+                              int64_t num_cols, const int64_t* column_ids, int64_t S, const int64_t* sub_indptr, int64_t D,
                               const int64_t* row_ids, int64_t R, const int64_t* col_ptr, const int64_t* row_ptr,
                               int64_t G, int64_t encoding_size, int renumber, int64_t* out_indptr,
                               int64_t* out_indices, int64_t* out_select, const float* data, const int64_t* e_ids,
@@ -320,14 +369,15 @@ GSB_API int gsb_gather_rows(gsb_ctx* ctx, void* stream, const float* src, int64_
 /* gsb_metapath_random_walk replaces gs::impl::fusion::FusedMetapathRandomWalkCUDA
  * (src/cuda/fusion/metapath_random_walk.cu:9-67; HeteroGraph::MetapathRandomWalkFused, src/hetero_graph.cc:58-74):
  * as gsb_random_walk, but step s moves along relation metapath_host[s] — one of num_relations
- * (<= GSB_MAX_RELATIONS) CSC graphs whose DEVICE indptr / indices pointers are listed in the two HOST arrays.
+ * (<= GSB_MAX_RELATIONS) CSC graphs whose DEVICE indptr / indices pointers and node counts are listed in the
+ * three HOST arrays.
  * L (<= GSB_MAX_METAPATH) is the length of metapath_host.  With every entry 0 and one relation the result equals
  * gsb_random_walk for the same seed. */
 #define GSB_MAX_RELATIONS 16
 #define GSB_MAX_METAPATH 256
 GSB_API int gsb_metapath_random_walk(gsb_ctx* ctx, void* stream, const int64_t* const* indptr_host,
-                                     const int64_t* const* indices_host, int num_relations,
-                                     const int64_t* metapath_host, int64_t L, const int64_t* seeds, int64_t W,
+                                     const int64_t* const* indices_host, const int64_t* num_nodes_host,
+                                     int num_relations, const int64_t* metapath_host, int64_t L, const int64_t* seeds, int64_t W,
                                      uint64_t seed, int layout, int64_t walker_offset, int64_t* out);
 
 /* ---- the rest of the super-batch family (gs_ops registry, src/pybind.cc:65-84) ---------------------------
@@ -353,7 +403,7 @@ GSB_API int gsb_get_batch_offsets(gsb_ctx* ctx, void* stream, const int64_t* dat
  * G batches (nid_ptr).  out_indptr comes from gsb_col_slice_count.  encoding_size > 0 writes the row id of an
  * edge of batch b as id + b * encoding_size; out_coo_offsets[b] = out_indptr[nid_ptr[b]] (may be NULL). */
 GSB_API int gsb_batch_col_slice_fill(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                                     const int64_t* seeds, int64_t S, const int64_t* nid_ptr, int64_t G,
+                                     int64_t num_cols, const int64_t* seeds, int64_t S, const int64_t* nid_ptr, int64_t G,
                                      int64_t encoding_size, const int64_t* out_indptr, int64_t* out_indices,
                                      int64_t* out_select, int64_t* out_coo_col, int64_t* out_coo_offsets,
                                      const float* data, const int64_t* e_ids, float* out_data);
@@ -414,8 +464,11 @@ GSB_API int gsb_batch_list_sample(gsb_ctx* ctx, void* stream, const float* probs
  * _CAPI_fused_columnwise_slicing_sampling over the seeds of all batches, GetBatchCSC,
  * gs_ops.BatchCSRRelabel) as ONE call: fused slice + uniform sample over the S seed columns of G
  * minibatches (seeds_ptr: DEVICE, G + 1 offsets), then per batch unique(cat(seeds_b, sampled_b)) in
- * first-occurrence order and batch-local relabelling.  (Recording the ids in the tables from inside the
- * sampling kernel was measured slower than a separate insert pass and is not done.)
+ * first-occurrence order and batch-local relabelling (direct-address or hash tables, flags: see
+ * gsb_batch_unique_relabel; num_nodes = number of columns of the graph, also the bound of the seed range check).
+ * batch_ids (DEVICE, G entries, may be NULL): a caller-chosen number for every minibatch, below 2^32.  When given,
+ * the draws for column c of minibatch j are keyed by (seed, batch_ids[j], c) instead of the column's position in
+ * the call, so a minibatch receives the same sample however minibatches are grouped into calls or dealt to GPUs.
  * Outputs: out_indptr[S + 1] (offsets over all columns), out_indices / out_select / out_relabeled
  * (S * k entries each; global ids, positions in `indices`, batch-local ids), out_indices_ptr[G + 1]
  * (per-batch edge offsets), out_unique (S + S * k entries; all frontiers back to back) and
@@ -427,17 +480,22 @@ GSB_API int gsb_batch_list_sample(gsb_ctx* ctx, void* stream, const float* probs
  * Ids below 2^32 - 1; S * (1 + k) below 2^30.  Waits for the stream only if a *_host pointer is given.
  */
 GSB_API int gsb_sage_hop(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
-                         const int64_t* seeds, const int64_t* seeds_ptr, int64_t G, int64_t S, int64_t k, int replace,
-                         uint64_t seed, int64_t* out_indptr, int64_t* out_indices, int64_t* out_select,
-                         int64_t* out_indices_ptr, int64_t* out_unique, int64_t* out_unique_ptr,
-                         int64_t* out_relabeled, int64_t* unique_total_host, int64_t* edges_total_host);
+                         int64_t num_nodes, const int64_t* seeds, const int64_t* seeds_ptr, const int64_t* batch_ids,
+                         int64_t G, int64_t S, int64_t k, int replace, uint64_t seed, int flags, int64_t* out_indptr,
+                         int64_t* out_indices, int64_t* out_select, int64_t* out_indices_ptr, int64_t* out_unique,
+                         int64_t* out_unique_ptr, int64_t* out_relabeled, int64_t* unique_total_host,
+                         int64_t* edges_total_host);
 
 /* ---- unique + relabel without any allocation ----------------------------------------------------------
  * No counterpart in the reference.  For callers that must not allocate device memory while they
  * run (a host process whose memory budget is fixed up front, a plug-in running under a lock that
  * forbids the device-wide synchronisation cudaMalloc implies): the same result as gsb_unique_relabel
  * for ONE item array, computed with scratch that is compiled into the library as device arrays
- * (about 8.1 MB per GPU, held from library load to process exit) instead of a context's arena.
+ * (about 8.1 MB per GPU) instead of a context's arena.  The arrays come into existence on a GPU when the CUDA
+ * runtime loads this library's module there — with lazy module loading that is the FIRST call made with that
+ * device current, which therefore is the one call that reserves device memory (GSB_ERR_OUT_OF_MEMORY if the
+ * device has none left) and may synchronise.  Make one call per device (n = 0 suffices) during set-up, before
+ * the phase in which nothing may be allocated; the memory is held until the process exits.
  *   - at most GSB_STATIC_MAX_ITEMS items per call; a larger `n` returns GSB_ERR_CAPACITY and
  *     launches nothing;
  *   - no gsb_ctx; nothing is allocated or freed, on the host or the device;

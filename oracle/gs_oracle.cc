@@ -142,10 +142,13 @@ GSO_API i64 gso_sample_uniform_count(const i64* indptr, const i64* seeds, i64 S,
   return exclusive_scan(sub_indptr, S);
 }
 
+/* item_base: the random stream of the column at position i is keyed by item_base + i.  0 keys by the position
+ * in the call; (minibatch number << 32) keys by (minibatch, column index inside the minibatch), which makes a
+ * minibatch's sample independent of how minibatches are grouped into calls. */
 GSO_API void gso_sample_uniform_fill(const i64* indptr, const i64* indices, const i64* seeds,
                                      i64 S, i64 k, int replace, uint64_t seed, int algo,
                                      const i64* sub_indptr, i64* out_indices, i64* out_select,
-                                     i64* out_coo_col /* may be NULL */) {
+                                     i64* out_coo_col /* may be NULL */, uint64_t item_base) {
 #pragma omp parallel
   {
     std::vector<i64> slot((size_t)std::max<i64>(k, 1));
@@ -156,13 +159,13 @@ GSO_API void gso_sample_uniform_fill(const i64* indptr, const i64* indices, cons
       i64 o0 = sub_indptr[i], n = sub_indptr[i + 1] - o0;
       if (replace) {
         for (i64 j = 0; j < n; ++j)
-          slot[j] = (i64)gso_bounded(seed, (uint64_t)i, (uint64_t)j, GSO_STREAM_UNIFORM, (uint64_t)d);
+          slot[j] = (i64)gso_bounded(seed, item_base + (uint64_t)i, (uint64_t)j, GSO_STREAM_UNIFORM, (uint64_t)d);
       } else if (d <= k) {
         for (i64 j = 0; j < n; ++j) slot[j] = j;
       } else if (algo == 0) {
         for (i64 j = 0; j < k; ++j) {
           i64 m = d - k + j;
-          i64 t = (i64)gso_bounded(seed, (uint64_t)i, (uint64_t)j, GSO_STREAM_UNIFORM, (uint64_t)(m + 1));
+          i64 t = (i64)gso_bounded(seed, item_base + (uint64_t)i, (uint64_t)j, GSO_STREAM_UNIFORM, (uint64_t)(m + 1));
           bool seen = false;
           for (i64 q = 0; q < j; ++q) seen |= (slot[q] == t);
           slot[j] = seen ? m : t;
@@ -170,7 +173,7 @@ GSO_API void gso_sample_uniform_fill(const i64* indptr, const i64* indices, cons
       } else {
         for (i64 j = 0; j < k; ++j) slot[j] = j;
         for (i64 idx = k; idx < d; ++idx) {
-          i64 r = (i64)gso_bounded(seed, (uint64_t)i, (uint64_t)idx, GSO_STREAM_UNIFORM | 0x40u,
+          i64 r = (i64)gso_bounded(seed, item_base + (uint64_t)i, (uint64_t)idx, GSO_STREAM_UNIFORM | 0x40u,
                                    (uint64_t)(idx + 1));
           if (r < k) slot[r] = std::max(slot[r], idx);
         }
@@ -701,7 +704,7 @@ GSO_API void gso_coo2csc(const i64* key, const i64* other, i64 E, i64 num_keys, 
  * ------------------------------------------------------------------------------------------ */
 GSO_API i64 gso_sage_batch(const i64* indptr, const i64* indices, const i64* seeds, i64 S,
                            const i64* fanouts, int num_hops, uint64_t seed, i64* frontier_out,
-                           i64 frontier_cap, i64* frontier_len) {
+                           i64 frontier_cap, i64* frontier_len, uint64_t item_base) {
   std::vector<i64> cur(seeds, seeds + S);
   i64 total_edges = 0;
   for (int h = 0; h < num_hops; ++h) {
@@ -712,7 +715,7 @@ GSO_API i64 gso_sage_batch(const i64* indptr, const i64* indices, const i64* see
     std::vector<i64> cat((size_t)(n + E)), sel((size_t)E), rel((size_t)E);
     memcpy(cat.data(), cur.data(), sizeof(i64) * (size_t)n);
     gso_sample_uniform_fill(indptr, indices, cur.data(), n, k, 0, seed + (uint64_t)h, 0,
-                            sub_indptr.data(), cat.data() + n, sel.data(), nullptr);
+                            sub_indptr.data(), cat.data() + n, sel.data(), nullptr, item_base);
     std::vector<i64> uniq((size_t)(n + E));
     i64 U = gso_unique_relabel(cat.data(), n + E, uniq.data(), cat.data() + n, E, rel.data());
     uniq.resize((size_t)U);

@@ -101,8 +101,9 @@ def col_slice(indptr, indices, seeds, with_coo=True):
     return sub_indptr, out_c, out_i, out_s
 
 
-def sample_uniform(indptr, indices, seeds, k, replace, seed=0, algo=0, with_coo=False):
-    """seeds=None → plain Sampling over every column; else fused slice+sample."""
+def sample_uniform(indptr, indices, seeds, k, replace, seed=0, algo=0, with_coo=False, item_base=0):
+    """seeds=None → plain Sampling over every column; else fused slice+sample.  item_base: see
+    gso_sample_uniform_fill (minibatch number << 32 for the minibatch-keyed stream)."""
     indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
     S = len(seeds) if seeds is not None else len(indptr) - 1
     sub_indptr = np.empty(S + 1, dtype=I64)
@@ -112,7 +113,8 @@ def sample_uniform(indptr, indices, seeds, k, replace, seed=0, algo=0, with_coo=
     out_s = np.empty(nnz, dtype=I64)
     out_c = np.empty(nnz, dtype=I64) if with_coo else None
     lib().gso_sample_uniform_fill(_p(indptr), _p(indices), _p(seeds), _c(S), _c(k), ctypes.c_int(int(replace)),
-                                  _u(seed), ctypes.c_int(algo), _p(sub_indptr), _p(out_i), _p(out_s), _p(out_c))
+                                  _u(seed), ctypes.c_int(algo), _p(sub_indptr), _p(out_i), _p(out_s), _p(out_c),
+                                  _u(item_base))
     return sub_indptr, out_c, out_i, out_s
 
 
@@ -299,7 +301,7 @@ def coo2csc(row, col, num_cols, col_sorted=False):
     return indptr, out_row, perm
 
 
-def sage_batch(indptr, indices, seeds, fanouts, seed=0, want_frontier=False):
+def sage_batch(indptr, indices, seeds, fanouts, seed=0, want_frontier=False, batch_id=None):
     indptr, indices, seeds = _i64(indptr), _i64(indices), _i64(seeds)
     f = _i64(np.asarray(fanouts))
     flen = ctypes.c_int64(0)
@@ -311,7 +313,8 @@ def sage_batch(indptr, indices, seeds, fanouts, seed=0, want_frontier=False):
             cap = cap * (1 + int(k))
         fr = np.empty(cap, dtype=I64)
     e = lib().gso_sage_batch(_p(indptr), _p(indices), _p(seeds), _c(len(seeds)), _p(f), ctypes.c_int(len(fanouts)),
-                             _u(seed), _p(fr), _c(cap), ctypes.byref(flen))
+                             _u(seed), _p(fr), _c(cap), ctypes.byref(flen),
+                             _u(0 if batch_id is None else int(batch_id) << 32))
     if want_frontier:
         return int(e), fr[:flen.value].copy()
     return int(e)

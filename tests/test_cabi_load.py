@@ -27,6 +27,23 @@ def test_library_exports_every_declared_symbol(lib):
         assert hasattr(lib, s), s
 
 
+def test_every_entry_point_is_bound_with_its_declared_arity(lib):
+    """The ctypes binding takes its argument lists from the header, so a caller with a stale argument list gets a
+    TypeError instead of a corrupted stack (no kernel is launched: the calls below fail in ctypes)."""
+    protos = cabi.declared_prototypes()
+    assert set(protos) == set(cabi.declared_symbols())
+    for name, (restype, argtypes) in protos.items():
+        fn = getattr(lib, name)
+        assert fn.argtypes is not None and len(fn.argtypes) == len(argtypes), name
+    assert len(protos["gsb_sage_hop"][1]) == 23 and len(protos["gsb_col_slice_count"][1]) == 8
+    assert len(protos["gsb_random_walk"][1]) == 12 and len(protos["gsb_ctx_set_option"][1]) == 3
+    with pytest.raises((TypeError, ctypes.ArgumentError)):
+        lib.gsb_col_slice_count(None, None)
+    # options and the self-test are refused without a context (no device needed)
+    assert lib.gsb_ctx_set_option(None, 0, 5) == -1
+    assert lib.gsb_selftest_lookback(None, None, 4, -1, None) == -1
+
+
 def test_status_strings_and_version(lib):
     assert cabi.status_string(0) == "ok"
     assert "capacity" in cabi.status_string(-4)
@@ -36,7 +53,8 @@ def test_status_strings_and_version(lib):
 def test_no_torch_dependency_in_kernel_library():
     # the boundary is plain C: the kernel library must not link against torch / c10
     out = os.popen(f"ldd {cabi.LIB_PATH}").read()
-    assert "torch" not in out and "c10" not in out
+    names = [line.split()[0] for line in out.splitlines() if line.strip()]   # library names only, not load addresses
+    assert not [n for n in names if "torch" in n or "c10" in n], names
 
 
 def test_ctx_create_fails_cleanly_without_gpu(lib):

@@ -21,6 +21,15 @@ def ops():
     return _ops
 
 
+@pytest.fixture(params=["hash", "direct"])
+def relabel_path(request, ops):
+    """Runs a test once with hash-table regions and once with direct-address tables."""
+    ctx = ops.default_context()
+    ctx.set_option("relabel_path", 1 if request.param == "hash" else 2)
+    yield request.param
+    ctx.set_option("relabel_path", 0)
+
+
 @pytest.mark.parametrize("G,ns,ne", [(1, 5, 40), (3, 1, 0), (7, 100, 3000), (64, 1024, 9000), (300, 17, 200)])
 def test_batch_csr_relabel_matches_per_batch_oracle(ops, oracle, G, ns, ne):
     rng = np.random.default_rng(G * 1000 + ns)
@@ -59,7 +68,7 @@ def test_batch_with_empty_batches(ops, oracle):
 
 
 @pytest.mark.parametrize("fanouts", [[10, 5], [20, 3], [1, 16, 2]])
-def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, fanouts):
+def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, relabel_path, fanouts):
     """The 100k-node configuration, 16 batches of 1,024 seeds at once: sampling equals the oracle's fused
     sampler over the concatenated seeds (same Philox stream), relabel equals the per-batch oracle."""
     indptr, indices = cfg1_graph
@@ -88,6 +97,119 @@ def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, fanouts):
             nxt.append(wu)
             nxt_ptr.append(nxt_ptr[-1] + len(wu))
         cur, cur_ptr = np.concatenate(nxt), np.array(nxt_ptr, dtype=np.int64)
+
+
+@pytest.mark.parametrize("G,ns,ne", [(1, 5, 40), (7, 100, 3000), (64, 1024, 9000), (300, 17, 200)])
+def test_batch_csr_relabel_paths_agree_with_oracle(ops, oracle, relabel_path, G, ns, ne):
+    """Both table forms, with duplicate seeds (no distinctness promise) and ragged / empty batches."""
+    rng = np.random.default_rng(G * 7 + ns)
+    seeds_sizes = rng.integers(0, ns + 1, G)
+    edge_sizes = rng.integers(0, ne + 1, G)
+    edge_sizes[rng.random(G) < 0.15] = 0
+    seeds_ptr = np.concatenate([[0], np.cumsum(seeds_sizes)]).astype(np.int64)
+    indices_ptr = np.concatenate([[0], np.cumsum(edge_sizes)]).astype(np.int64)
+    hi = max(8, (ns + ne) // 2)
+    seeds = rng.integers(0, hi, seeds_ptr[-1]).astype(np.int64)          # repeats inside a batch are allowed
+    indices = rng.integers(0, hi, indices_ptr[-1]).astype(np.int64)
+    uniq, uniq_ptr, rel, _ = ops.batch_csr_relabel(dev(seeds), dev(seeds_ptr), dev(np.concatenate([indices, [3, 3]])),
+                                                   dev(indices_ptr), num_nodes=hi)
+    uniq, uniq_ptr, rel = host(uniq), host(uniq_ptr), host(rel)
+    assert len(rel) == indices_ptr[-1] and uniq_ptr[-1] == len(uniq)
+    for b in range(G):
+        s = seeds[seeds_ptr[b]:seeds_ptr[b + 1]]
+        e = indices[indices_ptr[b]:indices_ptr[b + 1]]
+        wu, (wr,) = oracle.unique_relabel([s, e], [e])
+        assert np.array_equal(uniq[uniq_ptr[b]:uniq_ptr[b + 1]], wu), b
+        assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
+
+
+def test_direct_tables_survive_many_calls_and_a_change_of_shape(ops, oracle):
+    """The direct-address tables are never cleared: stale entries of earlier calls (other ids, other batch counts,
+    another node count) must lose against every entry of the current call."""
+    ctx = ops.default_context()
+    ctx.set_option("relabel_path", 2)
+    try:
+        rng = np.random.default_rng(12)
+        for trial, (G, hi) in enumerate([(4, 500), (4, 500), (9, 300), (2, 2000), (4, 500), (4, 500)] * 3):
+            sizes = rng.integers(1, 200, G)
+            esz = rng.integers(0, 900, G)
+            sp = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+            ep = np.concatenate([[0], np.cumsum(esz)]).astype(np.int64)
+            seeds = np.concatenate([rng.choice(hi, s, replace=False) for s in sizes]).astype(np.int64)
+            idx = rng.integers(0, hi, ep[-1]).astype(np.int64)
+            uniq, uptr, rel, _ = ops.batch_csr_relabel(dev(seeds), dev(sp), dev(idx), dev(ep), num_nodes=hi,
+                                                       seeds_distinct=bool(trial % 2))
+            uniq, uptr, rel = host(uniq), host(uptr), host(rel)
+            for b in range(G):
+                wu, (wr,) = oracle.unique_relabel([seeds[sp[b]:sp[b + 1]], idx[ep[b]:ep[b + 1]]], [idx[ep[b]:ep[b + 1]]])
+                assert np.array_equal(uniq[uptr[b]:uptr[b + 1]], wu), (trial, b)
+                assert np.array_equal(rel[ep[b]:ep[b + 1]], wr), (trial, b)
+    finally:
+        ctx.set_option("relabel_path", 0)
+
+
+def test_direct_tables_fall_back_to_hash_when_over_budget(ops, oracle):
+    ctx = ops.default_context()
+    old = ctx.get_option("direct_table_budget")
+    ctx.set_option("direct_table_budget", 1024)      # nothing fits: automatic mode must take the hash tables
+    try:
+        seeds, sp = dev(np.array([5, 6, 7], dtype=np.int64)), dev(np.array([0, 3], dtype=np.int64))
+        idx, ep = dev(np.array([7, 9, 5, 9], dtype=np.int64)), dev(np.array([0, 4], dtype=np.int64))
+        u, _, r, _ = ops.batch_csr_relabel(seeds, sp, idx, ep, num_nodes=10)
+        assert host(u).tolist() == [5, 6, 7, 9] and host(r).tolist() == [2, 3, 0, 3]
+        ctx.set_option("relabel_path", 2)            # direct tables demanded: refused, not silently replaced
+        from graph_sampling_b200.cabi import GsbError
+        with pytest.raises(GsbError) as e:
+            ops.batch_csr_relabel(seeds, sp, idx, ep, num_nodes=10)
+        assert e.value.status == -3
+    finally:
+        ctx.set_option("relabel_path", 0)
+        ctx.set_option("direct_table_budget", old)
+
+
+@pytest.mark.parametrize("fanouts", [[10, 5], [20, 3]])
+def test_minibatch_keyed_streams_do_not_depend_on_grouping(ops, oracle, cfg1_graph, relabel_path, fanouts):
+    """With batch_ids the sample of a minibatch is keyed by (seed, its number, column index inside it): 12 minibatches
+    in one call, in calls of 5 + 7, or one at a time give the same blocks, equal to the oracle's per-batch sampler
+    with item_base = number << 32."""
+    indptr, indices = cfg1_graph
+    n = len(indptr) - 1
+    G, S0 = 12, 300
+    rng = np.random.default_rng(21)
+    seeds0 = np.concatenate([rng.choice(n, S0, replace=False) for _ in range(G)]).astype(np.int64).reshape(G, S0)
+    ids = np.arange(100, 100 + G, dtype=np.int64) * 3
+    d_indptr, d_indices = dev(indptr), dev(indices)
+
+    def run(sel):
+        ptr = dev((np.arange(len(sel) + 1) * S0).astype(np.int64))
+        return ops.sage_sample_batches(d_indptr, d_indices, dev(seeds0[sel].reshape(-1)), ptr, fanouts, seed=77,
+                                       batch_ids=dev(ids[sel]), seeds_distinct=True)
+
+    whole = run(np.arange(G))
+    parts = [run(np.arange(0, 5)), run(np.arange(5, G))] + [run(np.array([b])) for b in (0, 6, 11)]
+    groups = [np.arange(0, 5), np.arange(5, G), np.array([0]), np.array([6]), np.array([11])]
+    for hop in range(len(fanouts)):
+        w = whole[hop]
+        w_ip, w_fp = host(w["indices_ptr"]), host(w["frontier_ptr"])
+        for part, sel in zip(parts, groups):
+            p = part[hop]
+            p_ip, p_fp = host(p["indices_ptr"]), host(p["frontier_ptr"])
+            for j, b in enumerate(sel):
+                for key, wp, pp in (("indices", w_ip, p_ip), ("relabeled", w_ip, p_ip), ("select_index", w_ip, p_ip),
+                                    ("frontier", w_fp, p_fp)):
+                    assert torch.equal(w[key][wp[b]:wp[b + 1]], p[key][pp[j]:pp[j + 1]]), (hop, key, b)
+    # against the oracle, batch by batch
+    for b in range(G):
+        cur = seeds0[b]
+        for hop, k in enumerate(fanouts):
+            w_indptr, _, w_idx, _ = oracle.sample_uniform(indptr, indices, cur, k, False, seed=77 + hop,
+                                                          item_base=int(ids[b]) << 32)
+            h = whole[hop]
+            ip = host(h["indices_ptr"])
+            assert np.array_equal(host(h["indices"][ip[b]:ip[b + 1]]), w_idx), (b, hop)
+            cur, _ = oracle.unique_relabel([cur, w_idx], [w_idx])
+            fp = host(h["frontier_ptr"])
+            assert np.array_equal(host(h["frontier"][fp[b]:fp[b + 1]]), cur), (b, hop)
 
 
 @pytest.mark.parametrize("fanouts", [[10, 5], [15, 10, 5], [20, 3]])
