@@ -64,6 +64,10 @@ def parse():
                     help="minibatches every GPU processes per step (the configuration has 1,000)")
     ap.add_argument("--relabel-path", default=None, choices=["auto", "hash", "direct"],
                     help="table form of unique + relabel (default: the library's automatic choice)")
+    ap.add_argument("--lanes", type=int, default=1,
+                    help="host threads (each with its own stream and library context) that share the calls of a step")
+    ap.add_argument("--min-timed-seconds", type=float, default=0.5,
+                    help="the timed region is repeated until this much timed work exists (at least 3 repeats)")
     ap.add_argument("--no-dropin", action="store_true", help="skip the TorchScript drop-in legs")
     ap.add_argument("--dropin-steps", type=int, default=2)
     ap.add_argument("--dropin-batches", type=int, default=300)
@@ -223,27 +227,59 @@ def superbatch_torchscript(torch, G, seeds, ptr):
 
 
 class Stepper:
-    """One step = one pass over this rank's minibatches, `group` of them per call of `call(seeds_2d, first, step)`
+    """One step = one pass over this rank's minibatches, `group` of them per call of `call(seeds_2d, first, step, lane)`
     (first = index of the group's first minibatch, step = number of the pass).  The source array may live on the
-    device or in pinned host memory; a host source is copied group by group inside the step."""
+    device or in pinned host memory; a host source is copied group by group inside the step.
 
-    def __init__(self, torch, call, source, group, device):
+    lanes > 1: the groups of a step are dealt to that many host threads, each with its own CUDA stream (and, in the
+    caller's `call`, its own library context and output arena), so that the host waits of one call overlap the device
+    work of another.  Every lane stream starts a step after the work already queued on the current stream and the
+    current stream continues after all lanes, so CUDA events recorded on the current stream bracket the step."""
+
+    def __init__(self, torch, call, source, group, device, lanes=1):
         self.torch, self.call, self.source, self.group, self.device = torch, call, source, group, device
         self.step_no = 0
         self.shapes = []
         self.keep_shapes = False
+        self.lanes = max(1, int(lanes))
+        self.streams, self.pool = [], None
+        if self.lanes > 1:
+            from concurrent.futures import ThreadPoolExecutor
+            self.streams = [torch.cuda.Stream(device=device) for _ in range(self.lanes)]
+            self.pool = ThreadPoolExecutor(max_workers=self.lanes)
+
+    def _run_lane(self, lane, firsts):
+        torch = self.torch
+        edges, shapes_out = 0, []
+        torch.cuda.set_device(self.device)          # the current device is per thread
+        stream = self.streams[lane] if self.streams else torch.cuda.current_stream()
+        with torch.cuda.stream(stream):
+            for first in firsts:
+                sb = self.source[first:first + self.group]
+                if not sb.is_cuda:
+                    sb = sb.to(self.device, non_blocking=True)
+                e, shapes = self.call(sb, first, self.step_no, lane)
+                edges += e
+                shapes_out.append(shapes)
+        return edges, shapes_out
 
     def step(self):
-        n = self.source.shape[0]
-        edges = 0
-        for first in range(0, n, self.group):
-            sb = self.source[first:first + self.group]
-            if not sb.is_cuda:
-                sb = sb.to(self.device, non_blocking=True)
-            e, shapes = self.call(sb, first, self.step_no)
-            edges += e
-            if self.keep_shapes:
-                self.shapes.append(shapes)
+        torch = self.torch
+        firsts = list(range(0, self.source.shape[0], self.group))
+        if self.lanes == 1:
+            edges, shapes = self._run_lane(0, firsts)
+        else:
+            main = torch.cuda.current_stream()
+            for st in self.streams:
+                st.wait_stream(main)
+            futures = [self.pool.submit(self._run_lane, lane, firsts[lane::self.lanes]) for lane in range(self.lanes)]
+            results = [f.result() for f in futures]
+            for st in self.streams:
+                main.wait_stream(st)
+            edges = sum(r[0] for r in results)
+            shapes = [sh for r in results for sh in r[1]]
+        if self.keep_shapes:
+            self.shapes.extend(shapes)
         self.step_no += 1
         return edges
 
@@ -322,15 +358,19 @@ def run_ours(args):
 
     from graph_sampling_b200 import ops
     indptr, indices, batches, batch_ids, info, gen_s = make_inputs(args, device, world, rank)
-    ctx = ops.default_context(device)
+    lanes = max(1, args.lanes)
+    # one library context (scratch, counters) and one output arena per lane: calls of different lanes overlap
+    ctxs = [ops.default_context(device)] + [ops.Context(device) for _ in range(lanes - 1)]
+    ctx = ctxs[0]
     if args.relabel_path:
-        ctx.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2}[args.relabel_path])
+        for c in ctxs:
+            c.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2}[args.relabel_path])
     group = args.group
     ids_dev = batch_ids.to(device)
     ptr_cache = {}
-    arena = ops.OutputArena()
+    arenas = [ops.OutputArena() for _ in range(lanes)]
 
-    def call_batched(sb, first, step_no):
+    def call_batched(sb, first, step_no, lane=0):
         """`group` minibatches through the batched sampler: per hop one call of the C ABI (gsb_sage_hop: fused slice +
         sample, then unique + relabel of every minibatch), one host wait per hop for the exact sizes (queuing all hops
         on upper bounds was measured slower: the bounds overshoot 3.5x)."""
@@ -339,35 +379,39 @@ def run_ours(args):
         if ptr is None:
             ptr = ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * s0
         hops = ops.sage_sample_batches(indptr, indices, sb.reshape(-1), ptr, FANOUTS, replace=False,
-                                       seed=RUN_SEED + 8 * step_no, arena=arena, batch_ids=ids_dev[first:first + g],
-                                       seeds_distinct=True)
+                                       seed=RUN_SEED + 8 * step_no, arena=arenas[lane], ctx=ctxs[lane],
+                                       batch_ids=ids_dev[first:first + g], seeds_distinct=True)
         shapes = [(int(h["seeds"].numel()), int(h["indices"].numel()), int(h["frontier"].numel())) for h in hops]
         return sum(e for _, e, _ in shapes), shapes
 
     # ---- value: seeds resident in HBM, per-kernel event timing OFF -----------------------------------------
     dev_batches = batches.to(device)
-    stepper = Stepper(torch, call_batched, dev_batches, group, device)
-    stepper.step()  # sizes scratch, the output arena and the tables before anything is timed
+    for g in sorted({min(group, batches.shape[0]), batches.shape[0] % group} - {0}):   # offset arrays, made once
+        ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * BATCH
+    stepper = Stepper(torch, call_batched, dev_batches, group, device, lanes)
+    stepper.step()  # sizes scratch, the output arenas and the tables before anything is timed
     sampler = ClockSampler(physical_gpu_index(local), enabled=(rank == 0))
     sampler.start()
-    launches0 = ctx.launch_count()
+    launches0 = sum(c.launch_count() for c in ctxs)
     steps_before = stepper.step_no
-    seconds, edges = timed_steps(torch, stepper, args.warmup, args.steps, barrier, reduce_max)
-    launches = (ctx.launch_count() - launches0) * args.steps // max(1, stepper.step_no - steps_before)
+    seconds, edges = timed_steps(torch, stepper, args.warmup, args.steps, barrier, reduce_max,
+                                 min_seconds=args.min_timed_seconds)
+    launches = (sum(c.launch_count() for c in ctxs) - launches0) * args.steps // max(1, stepper.step_no - steps_before)
     clocks = sampler.stop()
     edges_all = reduce_sum(edges)
     sec_med = median(seconds)
 
     # ---- e2e: the same steps with the seeds in pinned host memory; sizes of every hop read back on the host -----
     pinned = batches.pin_memory()
-    e2e_stepper = Stepper(torch, call_batched, pinned, group, device)
-    e2e_seconds, e2e_edges = timed_steps(torch, e2e_stepper, min(args.warmup, 2), args.steps, barrier, reduce_max)
+    e2e_stepper = Stepper(torch, call_batched, pinned, group, device, lanes)
+    e2e_seconds, e2e_edges = timed_steps(torch, e2e_stepper, min(args.warmup, 2), args.steps, barrier, reduce_max,
+                                         min_seconds=args.min_timed_seconds)
     e2e_edges_all = reduce_sum(e2e_edges)
     e2e_med = median(e2e_seconds)
     calls_per_step = (batches.shape[0] + group - 1) // group
 
     # ---- per-kernel device time: a separate, untimed pass of one step with event timing on ----------------------
-    prof_stepper = Stepper(torch, call_batched, dev_batches, group, device)
+    prof_stepper = Stepper(torch, call_batched, dev_batches, group, device)      # one lane: kernels one after another
     prof_stepper.keep_shapes = True
     ctx.profile_reset()
     ctx.profile_enable(True)
@@ -403,7 +447,7 @@ def run_ours(args):
         "first_compact": sum(8 * (s_ + e_) + 8 * u_ for s_, e_, u_ in hop_shapes) / n_launch,
         "relabel": sum(16 * e_ for s_, e_, _ in hop_shapes) / n_launch,
     }
-    direct = ctx.get_option("relabel_path") != 1
+    direct = ctx.get_option("relabel_path") == 2
     kernel_names = {"sample_uniform": "k_sample_uniform_tpc (fused count + scan + uniform sample)",
                     "table_insert": "k_direct_insert (atomicMin into per-minibatch direct-address tables)" if direct
                     else "k_batch_insert (position-min hash insert)",
@@ -448,7 +492,9 @@ def run_ours(args):
                         "relabel of every minibatch with %s)" % ("direct-address tables" if direct else "hash tables"),
                 "parallelism": f"replicated graph, dp{world}; minibatch b of {args.batches_per_step * world} on rank "
                                "b mod N, random streams keyed by the global minibatch number",
-                "graph_gen_seconds": gen_s, "relabel_path": "direct" if direct else "hash"},
+                "graph_gen_seconds": gen_s, "relabel_path": "direct" if direct else "hash",
+                "lanes": f"{lanes} host thread(s), each with its own CUDA stream, library context and output arena, "
+                         "take alternate calls of a step"},
         "edges_per_step": edges_all / args.steps / world,
         "timing": {"repeats": len(seconds), "timed_region_s": round(sum(seconds), 4),
                    "ms_per_step_min_median_max": [round(min(seconds) / args.steps * 1e3, 4),
@@ -461,7 +507,7 @@ def run_ours(args):
                 "ms_per_step": e2e_med / args.steps * 1e3, "repeats": len(e2e_seconds),
                 "path": "ops.sage_sample_batches -> C ABI, seeds from pinned host memory every call, per-hop sizes and "
                         "status read back; the sampled blocks stay in HBM (as in the reference's API)"},
-        "gpu_launches": int(launches),
+        "gpu_launches": int(launches), "lanes": lanes,
         "clocks": clocks,
         "roofline": roofline,
     }
@@ -490,7 +536,7 @@ def dropin_torchscript(torch, args, device, indptr, indices, pinned, lib_path=No
     G._CAPI_LoadCSC(indptr, indices)
     ptr_cache = {}
 
-    def call(sb, first, step_no):
+    def call(sb, first, step_no, lane=0):
         g, s0 = sb.shape
         ptr = ptr_cache.get(g)
         if ptr is None:
@@ -556,7 +602,7 @@ def run_reference(args):
         G._CAPI_LoadCSC(indptr, indices)
         ptr_cache = {}
 
-        def call(sb, first, step_no):
+        def call(sb, first, step_no, lane=0):
             g, s0 = sb.shape
             ptr = ptr_cache.get(g)
             if ptr is None:
@@ -861,7 +907,7 @@ def measure_small_sage(torch, impl, device, group=125, steps=3):
         G = torch.classes.gs_classes.Graph(False)
         G._CAPI_LoadCSC(indptr, indices)
 
-        def call(sb, first, step_no):
+        def call(sb, first, step_no, lane=0):
             seeds, ptr = sb.reshape(-1), ptr_for(*sb.shape)
             edges = 0
             for k in fan:
@@ -875,7 +921,7 @@ def measure_small_sage(torch, impl, device, group=125, steps=3):
         arena = ops.OutputArena()
         ids = torch.arange(1000, dtype=torch.int64, device=device)
 
-        def call(sb, first, step_no):
+        def call(sb, first, step_no, lane=0):
             hops = ops.sage_sample_batches(indptr, indices, sb.reshape(-1), ptr_for(*sb.shape), fan, seed=RUN_SEED + 8 * step_no,
                                            arena=arena, batch_ids=ids[first:first + sb.shape[0]], seeds_distinct=True)
             return sum(int(h["indices"].numel()) for h in hops), None

@@ -79,6 +79,11 @@ __global__ void __launch_bounds__(kBThreads) k_direct_insert(BatchLayout L, Dire
 // Per item the kernel keeps only the node id, its key, the key found in the table and a few flags; the parameters of
 // the minibatch live in warp-uniform registers (a tile that straddles minibatches — rare: tiles are 128 items, a
 // minibatch has thousands — reloads them per item).
+//
+// HASH = true runs the same compaction over the hash-table regions that k_batch_insert filled (keys there are the
+// item's index inside its minibatch for a seed and edges_begin + that index for a neighbour): the slot is only read —
+// no final position is written back into the table — and the look-up pass is replaced by k_direct_fixup as well.
+template <bool HASH>
 __global__ void __launch_bounds__(kBThreads, 4) k_direct_compact(BatchLayout L, DirectTables T, CompactOut out,
                                                                  i64* __restrict__ out_relabeled, i64 n_bound,
                                                                  i64* counters, TileState ts) {
@@ -100,9 +105,10 @@ __global__ void __launch_bounds__(kBThreads, 4) k_direct_compact(BatchLayout L, 
   BatchUniform u{};
   bool uniform = true;
   if (base < end) {
-    u = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, base));
+    u = load_batch<HASH>(L, L.item_off, batch_of(L.item_off, L.G, base));
     uniform = end <= u.next_begin;
   }
+  uint32_t home[kLaneItems];  // home slot inside the minibatch's region (regions hold fewer than 2^31 slots)
 #pragma unroll
   for (int q = 0; q < kLaneItems; ++q) {
     const i64 g = base + q * 32 + lane;
@@ -111,28 +117,43 @@ __global__ void __launch_bounds__(kBThreads, 4) k_direct_compact(BatchLayout L, 
     found[q] = 0;
     flags[q] = 0;
     boff[q] = 0;
+    home[q] = 0;
     if (g >= end) continue;
     BatchUniform v = u;
-    if (!uniform && g >= u.next_begin) v = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, g));
+    if (!uniform && g >= u.next_begin) v = load_batch<HASH>(L, L.item_off, batch_of(L.item_off, L.G, g));
     const i64 lc = g - v.begin;
     node[q] = item_node(L, v, lc);
-    key[q] = item_key(v, lc);
-    boff[q] = (int)(v.batch - u.batch);
     const bool is_seed = lc < v.num_seeds;
-    const bool in_range = (u64)node[q] < (u64)T.num_nodes;
+    key[q] = HASH ? (uint32_t)(is_seed ? lc : v.edges_begin + lc) : item_key(v, lc);
+    boff[q] = (int)(v.batch - u.batch);
+    const bool in_range = HASH ? valid_id(node[q]) : (u64)node[q] < (u64)T.num_nodes;
     if (!is_seed) flags[q] |= F_EDGE;
     if (in_range) flags[q] |= (is_seed && T.seeds_distinct) ? F_FIRST : F_LOAD;
+    if (HASH && (flags[q] & F_LOAD)) home[q] = (uint32_t)home_slot(node[q], v.size);
   }
   u64 w[kLaneItems];
 #pragma unroll
   for (int q = 0; q < kLaneItems; ++q) {
     w[q] = 0;
-    if (flags[q] & F_LOAD) w[q] = __ldcg(T.words + (u.batch + boff[q]) * T.num_nodes + node[q]);
+    if (flags[q] & F_LOAD) {
+      if (HASH) {
+        const u64* region = boff[q] == 0 ? u.region : L.slots + __ldg(L.region_off + u.batch + boff[q]);
+        w[q] = region[home[q]];
+      } else {
+        w[q] = __ldcg(T.words + (u.batch + boff[q]) * T.num_nodes + node[q]);
+      }
+    }
   }
 #pragma unroll
   for (int q = 0; q < kLaneItems; ++q) {
     if (!(flags[q] & F_LOAD)) continue;
-    if ((w[q] >> 32) != (T.epoch_hi >> 32)) continue;  // no entry of this call (cannot happen after the insert pass)
+    if (HASH) {
+      BatchUniform v = u;
+      if (boff[q] != 0) v = load_batch<true>(L, L.item_off, u.batch + boff[q]);
+      if (find_from(v.region, v.size, home[q], w[q], node[q], &w[q]) == nullptr) continue;  // not inserted: an error was recorded
+    } else if ((w[q] >> 32) != (T.epoch_hi >> 32)) {
+      continue;  // no entry of this call (cannot happen after the insert pass)
+    }
     found[q] = (uint32_t)w[q];
     flags[q] |= found[q] == key[q] ? F_FIRST : F_REF;
   }
@@ -184,7 +205,9 @@ __global__ void __launch_bounds__(kBThreads, 4) k_direct_compact(BatchLayout L, 
       } else if (flags[q] & F_REF) {
         // the earlier occurrence: a seed (its key is its index) or an edge (its key carries its edge position)
         const uint32_t fk = found[q];
-        const i64 first_lc = (fk & kEdgeKeyBit) ? v.num_seeds + ((i64)(fk & ~kEdgeKeyBit) - v.edges_begin) : (i64)fk;
+        const i64 first_lc = HASH ? ((i64)fk < v.num_seeds ? (i64)fk : (i64)fk - v.edges_begin)
+                                  : ((fk & kEdgeKeyBit) ? v.num_seeds + ((i64)(fk & ~kEdgeKeyBit) - v.edges_begin)
+                                                        : (i64)fk);
         val = -2 - (v.begin + first_lc);
       }
       out_relabeled[v.edges_begin + (g - v.begin - v.num_seeds)] = val;
@@ -240,7 +263,8 @@ int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchL
                                  i64 n_cap, i64 e_cap, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled) {
   i64* counters = ctx_counters(ctx);
   const int wide = kNumSMs * 8;
-  {
+  const bool hash = T.words == nullptr;  // the regions of L were filled by k_batch_insert; only compaction + fix-up here
+  if (!hash) {
     ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
     k_direct_insert<2><<<max(1, min(grid_for(n_cap, kBThreads * 2), wide)), kBThreads, 0, stream>>>(L, T, n_cap,
                                                                                                     counters);
@@ -253,7 +277,8 @@ int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchL
   CompactOut out{out_unique, out_unique_ptr};
   {
     ScopedKernelTimer timer(ctx, KID_FIRST_COMPACT, stream);
-    k_direct_compact<<<tiles, kBThreads, 0, stream>>>(L, T, out, out_relabeled, n_cap, counters, ts);
+    if (hash) k_direct_compact<true><<<tiles, kBThreads, 0, stream>>>(L, T, out, out_relabeled, n_cap, counters, ts);
+    else k_direct_compact<false><<<tiles, kBThreads, 0, stream>>>(L, T, out, out_relabeled, n_cap, counters, ts);
   }
   GSB_LAUNCH_OK();
   if (e_cap > 0 && out_relabeled) {

@@ -762,9 +762,9 @@ _NAME_MAP = {
     "CSR2DCSC": ("_CAPI_CSR2DCSC",),
     "BatchSlicing": ("_CAPI_BatchSlicing", "_CAPI_batch_slicing"),
     "BatchFusedBidirSlicing": ("_CAPI_BatchFusionSlicing", "_CAPI_batch_fusion_slicing"),
-    "Split": ("_CAPI_Split",),
-    "Decode": ("_CAPI_Decode",),
-    "EDivUSum": ("_CAPI_EDivUSum",),
+    "Split": ("_CAPI_Split", "_CAPI_split"),
+    "Decode": ("_CAPI_Decode", "_CAPI_decode"),
+    "EDivUSum": ("_CAPI_EDivUSum", "_CAPI_e_div_u_sum"),
 }
 for _method, _aliases in _NAME_MAP.items():
     for _alias in _aliases:

@@ -151,7 +151,7 @@ def test_direct_tables_survive_many_calls_and_a_change_of_shape(ops, oracle):
 def test_direct_tables_fall_back_to_hash_when_over_budget(ops, oracle):
     ctx = ops.default_context()
     old = ctx.get_option("direct_table_budget")
-    ctx.set_option("direct_table_budget", 1024)      # nothing fits: automatic mode must take the hash tables
+    ctx.set_option("direct_table_budget", 8)         # nothing fits: automatic mode must take the hash tables
     try:
         seeds, sp = dev(np.array([5, 6, 7], dtype=np.int64)), dev(np.array([0, 3], dtype=np.int64))
         idx, ep = dev(np.array([7, 9, 5, 9], dtype=np.int64)), dev(np.array([0, 4], dtype=np.int64))
