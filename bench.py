@@ -64,8 +64,16 @@ def parse():
                     help="minibatches every GPU processes per step (the configuration has 1,000)")
     ap.add_argument("--relabel-path", default=None, choices=["auto", "hash", "direct"],
                     help="table form of unique + relabel (default: the library's automatic choice)")
-    ap.add_argument("--lanes", type=int, default=1,
-                    help="host threads (each with its own stream and library context) that share the calls of a step")
+    ap.add_argument("--relabel-chunk-mb", type=int, default=None,
+                    help="chunk size of the batched relabel in MiB of table regions (default: the library's; 0 = off)")
+    ap.add_argument("--lanes", type=int, default=3,
+                    help="CUDA streams (each with its own library context and output arena) that take the calls of a "
+                         "step in turn; with --host-waits every lane is a host thread")
+    ap.add_argument("--host-waits", action="store_true",
+                    help="wait on the host for the exact sizes after every hop (lanes then are host threads) instead of "
+                         "queuing whole steps sized by hints from a first pass")
+    ap.add_argument("--spin-wait", action="store_true",
+                    help="with several lanes: let waiting lanes spin (cudaStreamSynchronize) instead of sleeping on an event")
     ap.add_argument("--min-timed-seconds", type=float, default=0.5,
                     help="the timed region is repeated until this much timed work exists (at least 3 repeats)")
     ap.add_argument("--no-dropin", action="store_true", help="skip the TorchScript drop-in legs")
@@ -78,7 +86,7 @@ def parse():
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels", "ladies", "adaptive"],
+    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels", "ladies", "adaptive", "access"],
                     help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale "
                          "configuration); ladies = layer-wise importance sampling (1 M nodes / 50 M weighted edges); adaptive = "
                          "SDDMM score -> per-column softmax -> weighted sampling on the products-scale graph; both of the "
@@ -236,16 +244,21 @@ class Stepper:
     work of another.  Every lane stream starts a step after the work already queued on the current stream and the
     current stream continues after all lanes, so CUDA events recorded on the current stream bracket the step."""
 
-    def __init__(self, torch, call, source, group, device, lanes=1):
+    def __init__(self, torch, call, source, group, device, lanes=1, queued=None):
         self.torch, self.call, self.source, self.group, self.device = torch, call, source, group, device
         self.step_no = 0
         self.shapes = []
         self.keep_shapes = False
         self.lanes = max(1, int(lanes))
         self.streams, self.pool = [], None
-        if self.lanes > 1:
-            from concurrent.futures import ThreadPoolExecutor
+        # queued = (call_queued, finish): the calls of a step are only QUEUED, by this one host thread, on `lanes`
+        # streams in turn (call_queued(seeds_2d, first, step, lane) returns device-side counts), and finish(list of
+        # those, step) waits once at the end of the step and returns (edges, shapes)
+        self.queued = queued
+        if self.lanes > 1 or queued is not None:
             self.streams = [torch.cuda.Stream(device=device) for _ in range(self.lanes)]
+        if self.lanes > 1 and queued is None:
+            from concurrent.futures import ThreadPoolExecutor
             self.pool = ThreadPoolExecutor(max_workers=self.lanes)
 
     def _run_lane(self, lane, firsts):
@@ -263,10 +276,30 @@ class Stepper:
                 shapes_out.append(shapes)
         return edges, shapes_out
 
+    def _step_queued(self, firsts):
+        torch = self.torch
+        call_queued, finish = self.queued
+        main = torch.cuda.current_stream()
+        for st in self.streams:
+            st.wait_stream(main)
+        pending = []
+        for i, first in enumerate(firsts):
+            lane = i % self.lanes
+            with torch.cuda.stream(self.streams[lane]):
+                sb = self.source[first:first + self.group]
+                if not sb.is_cuda:
+                    sb = sb.to(self.device, non_blocking=True)
+                pending.append(call_queued(sb, first, self.step_no, lane))
+        for st in self.streams:
+            main.wait_stream(st)
+        return finish(pending, self.step_no)
+
     def step(self):
         torch = self.torch
         firsts = list(range(0, self.source.shape[0], self.group))
-        if self.lanes == 1:
+        if self.queued is not None:
+            edges, shapes = self._step_queued(firsts)
+        elif self.lanes == 1:
             edges, shapes = self._run_lane(0, firsts)
         else:
             main = torch.cuda.current_stream()
@@ -362,9 +395,13 @@ def run_ours(args):
     # one library context (scratch, counters) and one output arena per lane: calls of different lanes overlap
     ctxs = [ops.default_context(device)] + [ops.Context(device) for _ in range(lanes - 1)]
     ctx = ctxs[0]
-    if args.relabel_path:
-        for c in ctxs:
+    for c in ctxs:
+        if args.relabel_path:
             c.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2}[args.relabel_path])
+        if args.relabel_chunk_mb is not None:
+            c.set_option("relabel_chunk_bytes", args.relabel_chunk_mb << 20)
+        if args.host_waits and lanes > 1 and not args.spin_wait:
+            c.set_option("blocking_wait", 1)    # a lane that waits for its hop sleeps; the other lanes keep the GPU fed
     group = args.group
     ids_dev = batch_ids.to(device)
     ptr_cache = {}
@@ -384,12 +421,42 @@ def run_ours(args):
         shapes = [(int(h["seeds"].numel()), int(h["indices"].numel()), int(h["frontier"].numel())) for h in hops]
         return sum(e for _, e, _ in shapes), shapes
 
-    # ---- value: seeds resident in HBM, per-kernel event timing OFF -----------------------------------------
+    # ---- size hints: one pass with host waits records the sizes of every call of a step; the timed steps then queue
+    # their calls without waiting, sized by these figures plus a margin (what a training loop has from its previous
+    # epoch).  A call that outgrows its hint reports it and is repeated the slow way.
     dev_batches = batches.to(device)
     for g in sorted({min(group, batches.shape[0]), batches.shape[0] % group} - {0}):   # offset arrays, made once
         ptr_cache[g] = torch.arange(g + 1, dtype=torch.int64, device=device) * BATCH
-    stepper = Stepper(torch, call_batched, dev_batches, group, device, lanes)
-    stepper.step()  # sizes scratch, the output arenas and the tables before anything is timed
+    sized = Stepper(torch, call_batched, dev_batches, group, device, 1)
+    sized.keep_shapes = True
+    sized.step()  # also sizes scratch, the output arenas and the tables before anything is timed
+    firsts = list(range(0, batches.shape[0], group))
+    hints = {first: [(int(s_ * 1.03) + 1024, int(e_ * 1.03) + 1024) for s_, e_, _ in sh]
+             for first, sh in zip(firsts, sized.shapes)}
+    overflow = {"calls": 0}
+
+    def call_queued(sb, first, step_no, lane=0):
+        g, s0 = sb.shape
+        hops = ops.sage_sample_batches(indptr, indices, sb.reshape(-1), ptr_cache[g], FANOUTS, replace=False,
+                                       seed=RUN_SEED + 8 * step_no, arena=arenas[lane], ctx=ctxs[lane], sync=False,
+                                       batch_ids=ids_dev[first:first + g], seeds_distinct=True, size_hints=hints[first])
+        return torch.stack([h["counts"] for h in hops])          # [hops, 3] on the device: seeds, edges, frontier
+
+    def finish_step(pending, step_no):
+        counts = torch.stack(pending).cpu()                       # the one host wait of the step
+        for c in ctxs:
+            try:
+                c.check_device()
+            except ops.GsbError:                                  # a hint was too small: say so (the figures would be wrong)
+                overflow["calls"] += 1
+                raise
+        shapes = [[tuple(int(x) for x in hop) for hop in call] for call in counts]
+        return int(counts[:, :, 1].sum()), shapes
+
+    queued = None if args.host_waits else (call_queued, finish_step)
+    # ---- value: seeds resident in HBM, per-kernel event timing OFF -----------------------------------------
+    stepper = Stepper(torch, call_batched, dev_batches, group, device, lanes, queued)
+    stepper.step()
     sampler = ClockSampler(physical_gpu_index(local), enabled=(rank == 0))
     sampler.start()
     launches0 = sum(c.launch_count() for c in ctxs)
@@ -403,7 +470,7 @@ def run_ours(args):
 
     # ---- e2e: the same steps with the seeds in pinned host memory; sizes of every hop read back on the host -----
     pinned = batches.pin_memory()
-    e2e_stepper = Stepper(torch, call_batched, pinned, group, device, lanes)
+    e2e_stepper = Stepper(torch, call_batched, pinned, group, device, lanes, queued)
     e2e_seconds, e2e_edges = timed_steps(torch, e2e_stepper, min(args.warmup, 2), args.steps, barrier, reduce_max,
                                          min_seconds=args.min_timed_seconds)
     e2e_edges_all = reduce_sum(e2e_edges)
@@ -493,8 +560,12 @@ def run_ours(args):
                 "parallelism": f"replicated graph, dp{world}; minibatch b of {args.batches_per_step * world} on rank "
                                "b mod N, random streams keyed by the global minibatch number",
                 "graph_gen_seconds": gen_s, "relabel_path": "direct" if direct else "hash",
-                "lanes": f"{lanes} host thread(s), each with its own CUDA stream, library context and output arena, "
-                         "take alternate calls of a step"},
+                "lanes": (f"{lanes} host thread(s), each with its own CUDA stream, library context and output arena, take "
+                          "alternate calls of a step; one host wait per hop") if args.host_waits else
+                         (f"one host thread queues the calls of a step on {lanes} CUDA stream(s) in turn (own library "
+                          "context and output arena each), buffers sized by the first pass's sizes + 3 %, one host wait "
+                          "per step"),
+                "hint_overflows": overflow["calls"]},
         "edges_per_step": edges_all / args.steps / world,
         "timing": {"repeats": len(seconds), "timed_region_s": round(sum(seconds), 4),
                    "ms_per_step_min_median_max": [round(min(seconds) / args.steps * 1e3, 4),
@@ -503,10 +574,11 @@ def run_ours(args):
                    "reported": "median repeat; every repeat times exactly `steps` steps, max over ranks"},
         "e2e": {"value": e2e_edges_all / e2e_med, "unit": UNIT,
                 "h2d_bytes_per_step": batches.shape[0] * BATCH * 8,
-                "d2h_bytes_per_step": calls_per_step * len(FANOUTS) * 32,
+                "d2h_bytes_per_step": calls_per_step * len(FANOUTS) * (32 if args.host_waits else 24) +
+                (0 if args.host_waits else lanes * 16),
                 "ms_per_step": e2e_med / args.steps * 1e3, "repeats": len(e2e_seconds),
-                "path": "ops.sage_sample_batches -> C ABI, seeds from pinned host memory every call, per-hop sizes and "
-                        "status read back; the sampled blocks stay in HBM (as in the reference's API)"},
+                "path": "ops.sage_sample_batches -> C ABI, seeds from pinned host memory every call, sizes of every hop "
+                        "and the status read back; the sampled blocks stay in HBM (as in the reference's API)"},
         "gpu_launches": int(launches), "lanes": lanes,
         "clocks": clocks,
         "roofline": roofline,
@@ -966,6 +1038,49 @@ def secondary_workloads(args, impl, device, indptr, indices):
     return out
 
 
+def run_access(args):
+    """`--workload access`: what the sampling launches of ONE call of the batched sampler touch, counted exactly from
+    the call's own outputs (select_index = the positions it gathered): seed columns and how many are distinct, their
+    degrees, the distinct 64-byte lines of `indices` and of `indptr` behind the gathers.  lines x 64 B + the bytes
+    written is the least DRAM traffic an order-preserving sampler can cause for these draws (every line fetched once);
+    the ratio to the algorithmic bytes is the price of 8-byte gathers in 64-byte DRAM lines, whatever the kernel."""
+    import torch
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    from graph_sampling_b200 import ops
+    indptr, indices, batches, batch_ids, info, _ = make_inputs(args, device, 1, 0)
+    G = args.group
+    ptr = torch.arange(G + 1, dtype=torch.int64, device=device) * BATCH
+    hops = ops.sage_sample_batches(indptr, indices, batches[:G].reshape(-1).to(device), ptr, FANOUTS, seed=RUN_SEED,
+                                   batch_ids=batch_ids[:G].to(device), seeds_distinct=True)
+    deg_all = indptr[1:] - indptr[:-1]
+    out = []
+    for k, h in zip(FANOUTS, hops):
+        seeds, sel = h["seeds"], h["select_index"]
+        S, E = int(seeds.numel()), int(sel.numel())
+        d = deg_all[seeds]
+        lines_idx = int(torch.unique(sel // 8).numel())
+        first_line, last_line = (seeds * 8) // 64, (seeds * 8 + 15) // 64        # the indptr pair of a column
+        lines_ptr = int(torch.unique(torch.cat([first_line, last_line])).numel())
+        visits_ptr = S + int((first_line != last_line).sum())
+        alg = 32 * S + 8 + 24 * E
+        written = 8 * (S + 1) + 16 * E
+        seeds_read = 8 * S
+        floor_once = 64 * (lines_idx + lines_ptr) + written + seeds_read          # every line fetched exactly once
+        per_visit = 64 * E + 64 * visits_ptr + written + seeds_read                  # every gather its own line
+        out.append({"fanout": k, "seed_columns": S, "distinct_seed_columns": int(torch.unique(seeds).numel()),
+                    "sampled_edges": E, "mean_degree_of_seed_columns": round(float(d.float().mean()), 1),
+                    "share_of_columns_with_degree_le_fanout": round(float((d <= k).float().mean()), 4),
+                    "share_of_columns_with_degree_le_64": round(float((d <= 64).float().mean()), 4),
+                    "distinct_64B_lines_of_indices": lines_idx, "distinct_64B_lines_of_indptr": lines_ptr,
+                    "algorithmic_bytes": alg, "bytes_if_every_distinct_line_is_fetched_once": floor_once,
+                    "bytes_if_every_gather_fetches_its_line": per_visit,
+                    "floor_over_algorithmic": round(floor_once / alg, 2),
+                    "per_gather_over_algorithmic": round(per_visit / alg, 2)})
+    print(json.dumps({"metric": "sampler_access_pattern", "graph": info, "minibatches_in_call": G, "batch": BATCH,
+                      "hops": out}))
+
+
 def run_kernels(args):
     """Per-operator throughput on the products-scale graph: every operator of the hot path once, at a size that
     fills the GPU, timed with CUDA events; achieved = algorithmic bytes / time against the measured HBM peak.
@@ -1179,6 +1294,8 @@ if __name__ == "__main__":
         run_kernels_reference(a) if a.impl == "reference" else run_kernels(a)
     elif a.workload == "walk":
         run_walk(a)
+    elif a.workload == "access":
+        run_access(a)
     elif a.workload in ("ladies", "adaptive"):
         run_pipeline(a)
     elif a.impl == "reference":

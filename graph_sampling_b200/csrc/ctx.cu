@@ -31,6 +31,7 @@ struct gsb_ctx {
   u64* direct_tables;
   size_t direct_bytes;
   uint32_t direct_epoch;
+  cudaEvent_t wait_event;  // created on first use when GSB_OPT_BLOCKING_WAIT is set
 };
 
 namespace gsb {
@@ -136,10 +137,28 @@ i64* ctx_counters(gsb_ctx* ctx) { return ctx->counters; }
 i64* ctx_pinned(gsb_ctx* ctx) { return ctx->pinned; }
 int ctx_device(gsb_ctx* ctx) { return ctx->device; }
 
+// Waits for `stream`.  By default with cudaStreamSynchronize (the calling thread may spin); with
+// GSB_OPT_BLOCKING_WAIT through an event created with cudaEventBlockingSync, which puts the thread to sleep — what a
+// host that runs several streams from several threads (or several processes per machine) wants.
+static int ctx_wait(gsb_ctx* ctx, cudaStream_t stream) {
+  if (ctx->options[GSB_OPT_BLOCKING_WAIT] == 0) {
+    GSB_CUDA_OK(cudaStreamSynchronize(stream));
+    return GSB_OK;
+  }
+  if (!ctx->wait_event)
+    GSB_CUDA_OK(cudaEventCreateWithFlags(&ctx->wait_event, cudaEventBlockingSync | cudaEventDisableTiming));
+  GSB_CUDA_OK(cudaEventRecord(ctx->wait_event, stream));
+  GSB_CUDA_OK(cudaEventSynchronize(ctx->wait_event));
+  return GSB_OK;
+}
+
 int ctx_fetch_counters(gsb_ctx* ctx, cudaStream_t stream, int first, int n, const i64** out) {
   GSB_CUDA_OK(cudaMemcpyAsync(ctx->pinned + first, ctx->counters + first, sizeof(i64) * (size_t)n,
                               cudaMemcpyDeviceToHost, stream));
-  GSB_CUDA_OK(cudaStreamSynchronize(stream));
+  {
+    int st = ctx_wait(ctx, stream);
+    if (st != GSB_OK) return st;
+  }
   *out = ctx->pinned + first;
   return GSB_OK;
 }
@@ -153,7 +172,10 @@ int ctx_check_device_error(gsb_ctx* ctx, cudaStream_t stream) {
     snprintf(ctx->message, sizeof(ctx->message), "device-side error %d (%s), detail %lld", code,
              gsb_status_string(code), (long long)c[1]);
     GSB_CUDA_OK(cudaMemsetAsync(ctx->counters + CNT_ERROR, 0, 2 * sizeof(i64), stream));
-    GSB_CUDA_OK(cudaStreamSynchronize(stream));
+    {
+      int st2 = ctx_wait(ctx, stream);
+      if (st2 != GSB_OK) return st2;
+    }
     return code;
   }
   return GSB_OK;
@@ -217,6 +239,7 @@ int gsb_ctx_create(int device, gsb_ctx** out_ctx) {
   ctx->options[GSB_OPT_TABLE_SLOTS] = 0;
   ctx->options[GSB_OPT_RELABEL_PATH] = 0;
   ctx->options[GSB_OPT_DIRECT_TABLE_BUDGET] = 6ll << 30;
+  ctx->options[GSB_OPT_RELABEL_CHUNK_BYTES] = 0;  // off: chunked passes were measured slower at every chunk size
   int prev = 0;
   cudaGetDevice(&prev);
   int st = GSB_OK;
@@ -252,6 +275,7 @@ int gsb_ctx_destroy(gsb_ctx* ctx) {
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->tile_words) cudaFree(ctx->tile_words);
   if (ctx->direct_tables) cudaFree(ctx->direct_tables);
+  if (ctx->wait_event) cudaEventDestroy(ctx->wait_event);
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   for (size_t i = 0; i < ctx->ev_begin->size(); ++i) {
@@ -302,7 +326,11 @@ int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value) {
     case GSB_OPT_RELABEL_PATH:
       if (value < 0 || value > 2) return GSB_ERR_INVALID_ARGUMENT;
       break;
+    case GSB_OPT_BLOCKING_WAIT:
+      if (value < 0 || value > 1) return GSB_ERR_INVALID_ARGUMENT;
+      break;
     case GSB_OPT_DIRECT_TABLE_BUDGET:
+    case GSB_OPT_RELABEL_CHUNK_BYTES:
       if (value < 0) return GSB_ERR_INVALID_ARGUMENT;
       break;
   }

@@ -70,11 +70,12 @@ class Context:
     def check_device(self, where="device status"):
         self.check(self.lib.gsb_check_device_status(self.handle, _stream()), where)
 
-    OPTIONS = {"max_polls": 0, "table_slots": 1, "relabel_path": 2, "direct_table_budget": 3}
+    OPTIONS = {"max_polls": 0, "table_slots": 1, "relabel_path": 2, "direct_table_budget": 3,
+               "relabel_chunk_bytes": 4, "blocking_wait": 5}
 
     def set_option(self, name, value):
         """gsb_ctx_set_option by name: max_polls, table_slots, relabel_path (0 auto, 1 hash, 2 direct),
-        direct_table_budget (bytes)."""
+        direct_table_budget (bytes), relabel_chunk_bytes, blocking_wait (0 / 1)."""
         self.check(self.lib.gsb_ctx_set_option(self.handle, c_int(self.OPTIONS[name]), c_i64(int(value))),
                    "gsb_ctx_set_option")
 
@@ -886,7 +887,7 @@ class OutputArena:
 
 
 def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=False, seed=None, ctx=None, sync=True,
-                        arena=None, batch_ids=None, seeds_distinct=False):
+                        arena=None, batch_ids=None, seeds_distinct=False, size_hints=None):
     """Multi-hop GraphSAGE sampling of G minibatches at once (the loop of
     examples/graphsage/batching.py:56-90): per hop one fused slice+sample over the seeds of all batches,
     then one batched unique + relabel; each batch's frontier becomes its seeds for the next hop.
@@ -907,7 +908,14 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
     so the minibatch receives the same sample whichever call, group size or GPU processes it; without it the key
     is the column's position in the call.
     seeds_distinct: promise that no id repeats among the seeds of one minibatch (the frontiers that feed hops
-    2, 3, ... are distinct by construction and are always treated so)."""
+    2, 3, ... are distinct by construction and are always treated so).
+
+    size_hints (with sync=False): one (seed_bound, edge_bound) pair per hop — sizes the caller knows from earlier
+    calls of the same shape, e.g. the sizes of the previous epoch plus a margin — used instead of the worst-case
+    bounds S·(1+k), which overshoot the real sizes several times over and cost grid, clear and scratch work in
+    proportion.  The first hop's seed bound is ignored (its seed count is exact).  If a hop meets more seeds or edges
+    than hinted, the device records GSB_ERR_CAPACITY (ctx.check_device() raises it) and the caller repeats the call
+    without hints; nothing is written out of bounds."""
     ctx = ctx or default_context(indptr.device)
     out = []
     base_seed = next_seed(seed)
@@ -919,10 +927,17 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
     def alloc(name, hop, n):
         return _empty(n, indptr) if arena is None else arena.get((name, hop), n, indptr)
 
+    if size_hints is not None and (sync or len(size_hints) != len(fanouts)):
+        raise ValueError("size_hints needs sync=False and one (seed_bound, edge_bound) pair per hop")
     for hop, k in enumerate(fanouts):
         S = seeds.numel()
         G = seeds_ptr.numel() - 1
         cap = S * int(k)
+        if size_hints is not None:
+            if hop > 0:
+                S = min(S, int(size_hints[hop][0]))
+                seeds = seeds[:S]
+            cap = min(S * int(k), int(size_hints[hop][1]))
         sub_indptr = alloc("sub_indptr", hop, S + 1)
         sub_indices, select, rel = alloc("indices", hop, cap), alloc("select", hop, cap), alloc("relabeled", hop, cap)
         indices_ptr, uniq_ptr = alloc("indices_ptr", hop, G + 1), alloc("frontier_ptr", hop, G + 1)
@@ -930,7 +945,7 @@ def sage_sample_batches(indptr, indices, seeds, seeds_ptr, fanouts, replace=Fals
         nu, ne = c_i64(0), c_i64(0)
         flags = 1 if (hop > 0 or seeds_distinct) else 0
         ctx.check(ctx.lib.gsb_sage_hop(ctx.handle, _stream(), _p(indptr), _p(indices), c_i64(num_nodes), _p(seeds),
-                                       _p(seeds_ptr), _p(batch_ids), c_i64(G), c_i64(S), c_i64(int(k)),
+                                       _p(seeds_ptr), _p(batch_ids), c_i64(G), c_i64(S), c_i64(int(k)), c_i64(cap),
                                        c_int(int(bool(replace))), c_u64((base_seed + hop) & (2**64 - 1)),
                                        c_int(flags), _p(sub_indptr), _p(sub_indices),
                                        _p(select), _p(indices_ptr), _p(uniq), _p(uniq_ptr), _p(rel),

@@ -77,16 +77,29 @@ GSB_API int gsb_check_device_status(gsb_ctx* ctx, void* stream);
  *                               to a power of two) instead of sizing it from the item count — a table that is too
  *                               small reports GSB_ERR_TABLE_FULL; 0 (default) = automatic;
  *  GSB_OPT_RELABEL_PATH         how gsb_sage_hop / gsb_batch_unique_relabel find first occurrences: 0 (default) =
- *                               direct-address tables when they fit the budget, else hash tables; 1 = hash tables;
+ *                               direct-address tables when all tables of the call are L2-sized (32 MiB), else hash
+ *                               tables; 1 = hash tables;
  *                               2 = direct-address tables (GSB_ERR_OUT_OF_MEMORY when they do not fit);
  *  GSB_OPT_DIRECT_TABLE_BUDGET  bytes the direct-address tables (8 bytes x num_nodes x minibatches per call) may
- *                               take, default 6 GiB. */
+ *                               take, default 6 GiB;
+ *  GSB_OPT_RELABEL_CHUNK_BYTES  > 0: the hash-table form of the batched relabel processes a large call in chunks of
+ *                               consecutive items whose table regions (16 bytes per item) add up to about this many
+ *                               bytes, so that clear, insert and compaction of a chunk meet its regions in the L2
+ *                               cache.  Default 0 = the whole call at once: on a B200 the chunked form was slower at
+ *                               every chunk size tried (the passes are not bound by DRAM re-fetches of the regions,
+ *                               and short launches lose more in ramp-up and tail).  Results do not depend on it;
+ *  GSB_OPT_BLOCKING_WAIT        1: calls that wait for their stream (the ones with a *_host result) sleep on an event
+ *                               created with cudaEventBlockingSync instead of calling cudaStreamSynchronize, which
+ *                               may spin — for hosts that drive several streams from several threads, or several
+ *                               processes per machine; default 0. */
 enum gsb_option {
   GSB_OPT_MAX_POLLS = 0,
   GSB_OPT_TABLE_SLOTS = 1,
   GSB_OPT_RELABEL_PATH = 2,
   GSB_OPT_DIRECT_TABLE_BUDGET = 3,
-  GSB_OPT_NUM = 4
+  GSB_OPT_RELABEL_CHUNK_BYTES = 4,
+  GSB_OPT_BLOCKING_WAIT = 5,
+  GSB_OPT_NUM = 6
 };
 GSB_API int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value);
 GSB_API int gsb_ctx_get_option(gsb_ctx* ctx, int option, int64_t* value_host);
@@ -477,12 +490,16 @@ GSB_API int gsb_batch_list_sample(gsb_ctx* ctx, void* stream, const float* probs
  * scratch and the output capacities (S * k, S + S * k).  With the *_host pointers NULL a caller can therefore queue
  * the next hop right away — seeds = out_unique, seeds_ptr = out_unique_ptr, S = this hop's S * (1 + k) — and read all
  * counts (out_indices_ptr[G], out_unique_ptr[G] of every hop) after the last one: no host wait between hops.
+ * edge_capacity > 0 states the size of the edge buffers when it is smaller than S * k, and S may likewise be a bound the
+ * caller knows from earlier calls of the same shape rather than the worst case S' * (1 + k'): grids, scratch and clears
+ * then follow the real sizes.  If the device meets more seeds or edges than stated, GSB_ERR_CAPACITY is recorded, the
+ * passes that follow do nothing, and the caller repeats the call with the worst-case bounds.
  * Ids below 2^32 - 1; S * (1 + k) below 2^30.  Waits for the stream only if a *_host pointer is given.
  */
 GSB_API int gsb_sage_hop(gsb_ctx* ctx, void* stream, const int64_t* indptr, const int64_t* indices,
                          int64_t num_nodes, const int64_t* seeds, const int64_t* seeds_ptr, const int64_t* batch_ids,
-                         int64_t G, int64_t S, int64_t k, int replace, uint64_t seed, int flags, int64_t* out_indptr,
-                         int64_t* out_indices, int64_t* out_select, int64_t* out_indices_ptr, int64_t* out_unique,
+                         int64_t G, int64_t S, int64_t k, int64_t edge_capacity, int replace, uint64_t seed, int flags,
+                         int64_t* out_indptr, int64_t* out_indices, int64_t* out_select, int64_t* out_indices_ptr, int64_t* out_unique,
                          int64_t* out_unique_ptr, int64_t* out_relabeled, int64_t* unique_total_host,
                          int64_t* edges_total_host);
 

@@ -123,6 +123,42 @@ def test_batch_csr_relabel_paths_agree_with_oracle(ops, oracle, relabel_path, G,
         assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
 
 
+@pytest.mark.parametrize("chunk_bytes", [16 * 1024, 48 * 1024, 1 << 20])
+@pytest.mark.parametrize("G,ns,ne", [(7, 100, 3000), (64, 1024, 9000), (300, 17, 200)])
+def test_chunked_hash_relabel_equals_oracle(ops, oracle, chunk_bytes, G, ns, ne):
+    """The hash-table form cut into chunks of 1,024 / 3,072 / 65,536 items: minibatches straddle chunk boundaries,
+    some are empty, some chunks begin with empty minibatches — results must not depend on the chunk size."""
+    ctx = ops.default_context()
+    ctx.set_option("relabel_path", 1)
+    old = ctx.get_option("relabel_chunk_bytes")
+    ctx.set_option("relabel_chunk_bytes", chunk_bytes)
+    try:
+        rng = np.random.default_rng(G + ns + chunk_bytes)
+        seeds_sizes = rng.integers(0, ns + 1, G)
+        edge_sizes = rng.integers(0, ne + 1, G)
+        edge_sizes[rng.random(G) < 0.2] = 0
+        seeds_sizes[rng.random(G) < 0.1] = 0
+        seeds_ptr = np.concatenate([[0], np.cumsum(seeds_sizes)]).astype(np.int64)
+        indices_ptr = np.concatenate([[0], np.cumsum(edge_sizes)]).astype(np.int64)
+        hi = max(8, (ns + ne) // 2)
+        seeds = np.concatenate([rng.choice(hi * 4, s, replace=False) for s in seeds_sizes] + [np.empty(0, np.int64)]).astype(np.int64)
+        indices = rng.integers(0, hi * 4, indices_ptr[-1]).astype(np.int64)
+        for distinct in (False, True):
+            uniq, uniq_ptr, rel, _ = ops.batch_csr_relabel(dev(seeds), dev(seeds_ptr), dev(indices), dev(indices_ptr),
+                                                           seeds_distinct=distinct)
+            uniq, uniq_ptr, rel = host(uniq), host(uniq_ptr), host(rel)
+            assert uniq_ptr[-1] == len(uniq) and len(rel) == indices_ptr[-1]
+            for b in range(G):
+                s_ = seeds[seeds_ptr[b]:seeds_ptr[b + 1]]
+                e = indices[indices_ptr[b]:indices_ptr[b + 1]]
+                wu, (wr,) = oracle.unique_relabel([s_, e], [e])
+                assert np.array_equal(uniq[uniq_ptr[b]:uniq_ptr[b + 1]], wu), b
+                assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
+    finally:
+        ctx.set_option("relabel_chunk_bytes", old)
+        ctx.set_option("relabel_path", 0)
+
+
 def test_direct_tables_survive_many_calls_and_a_change_of_shape(ops, oracle):
     """The direct-address tables are never cleared: stale entries of earlier calls (other ids, other batch counts,
     another node count) must lose against every entry of the current call."""
@@ -235,6 +271,49 @@ def test_sage_sample_batches_without_host_waits(ops, cfg1_graph, fanouts):
             assert torch.equal(g[key][:E], w[key]), key
         assert torch.equal(g["indices_ptr"], w["indices_ptr"]) and torch.equal(g["frontier_ptr"], w["frontier_ptr"])
         assert torch.equal(g["frontier"][:U], w["frontier"])
+
+
+def test_size_hints_give_the_same_blocks_and_too_small_hints_are_reported(ops, cfg1_graph, relabel_path):
+    """Hops queued without host waits on buffers sized by hints (the sizes of an earlier call plus a margin): the valid
+    prefixes equal the hop-by-hop result; a hint that is too small yields GSB_ERR_CAPACITY, nothing out of bounds, and
+    the next call works."""
+    from graph_sampling_b200.cabi import GsbError
+    indptr, indices = cfg1_graph
+    n = len(indptr) - 1
+    G, S0 = 10, 512
+    rng = np.random.default_rng(5)
+    seeds0 = dev(np.concatenate([rng.choice(n, S0, replace=False) for _ in range(G)]).astype(np.int64))
+    ptr0 = dev((np.arange(G + 1) * S0).astype(np.int64))
+    ids = dev(np.arange(G, dtype=np.int64) + 7)
+    fanouts = [10, 5, 3]
+    d_indptr, d_indices = dev(indptr), dev(indices)
+    want = ops.sage_sample_batches(d_indptr, d_indices, seeds0, ptr0, fanouts, seed=5, batch_ids=ids, seeds_distinct=True)
+    sizes = [(w["seeds"].numel(), w["indices"].numel()) for w in want]
+    hints = [(int(s * 1.05) + 8, int(e * 1.05) + 8) for s, e in sizes]
+    got = ops.sage_sample_batches(d_indptr, d_indices, seeds0, ptr0, fanouts, seed=5, batch_ids=ids, seeds_distinct=True,
+                                  sync=False, size_hints=hints)
+    ctx = ops.default_context()
+    ctx.check_device()
+    for w, g, (hs, he) in zip(want, got, hints):
+        S, E, U = g["counts"].tolist()
+        assert (S, E, U) == (w["seeds"].numel(), w["indices"].numel(), w["frontier"].numel())
+        assert g["indices"].numel() <= he and g["frontier"].numel() <= g["seeds"].numel() + he   # hinted capacities
+        for key in ("indices", "relabeled", "select_index"):
+            assert torch.equal(g[key][:E], w[key]), key
+        assert torch.equal(g["frontier"][:U], w["frontier"]) and torch.equal(g["frontier_ptr"], w["frontier_ptr"])
+        assert torch.equal(g["sub_indptr"][:S + 1], w["sub_indptr"])
+    # hints that are too small, for the edges of hop 2 and for the seeds of hop 3
+    for bad in ([hints[0], (hints[1][0], sizes[1][1] - 5), hints[2]], [hints[0], hints[1], (sizes[2][0] - 3, hints[2][1])]):
+        guard = ops.sage_sample_batches(d_indptr, d_indices, seeds0, ptr0, fanouts, seed=5, batch_ids=ids,
+                                        seeds_distinct=True, sync=False, size_hints=bad)
+        with pytest.raises(GsbError) as e:
+            ctx.check_device()
+        assert e.value.status == -4
+        del guard
+    again = ops.sage_sample_batches(d_indptr, d_indices, seeds0, ptr0, fanouts, seed=5, batch_ids=ids, seeds_distinct=True)
+    assert torch.equal(again[2]["frontier"], want[2]["frontier"])
+    with pytest.raises(ValueError):
+        ops.sage_sample_batches(d_indptr, d_indices, seeds0, ptr0, fanouts, size_hints=hints)   # needs sync=False
 
 
 def test_output_arena_reuses_buffers_and_keeps_results_equal(ops, cfg1_graph):
