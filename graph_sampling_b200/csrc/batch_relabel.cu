@@ -17,8 +17,6 @@
 //
 // Replaces gs::impl::BatchCSRRelabelCUDA (src/cuda/batch_relabel.cu:90-320), which keeps two int64
 // arrays per table, three passes with separate prefix-sum calls and a host round trip per pass.
-#include <stdlib.h>
-
 #include "batch_table.cuh"
 #include "common.cuh"
 #include "radix_sort.cuh"
@@ -73,34 +71,6 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
   }
 }
 
-constexpr i64 kAllItems = 0x7fffffffffffffffll;
-
-// Empties the table regions of the minibatches that BEGIN inside items [item_lo, item_hi) (the minibatch that
-// straddles item_lo was emptied with the chunk in which it begins).  Regions are contiguous, so this is one range.
-__global__ void __launch_bounds__(kBThreads) k_clear_chunk_regions(BatchLayout L, const i64* counters, i64 item_lo,
-                                                                   i64 item_hi) {
-  if (counters[CNT_ABORT] != 0) return;
-  const i64 n = L.item_off[L.G];
-  if (item_lo >= n && item_lo > 0) return;
-  i64 b_first = 0;
-  if (item_lo > 0) {
-    b_first = batch_of(L.item_off, L.G, item_lo);
-    if (__ldg(L.item_off + b_first) < item_lo) ++b_first;     // began in an earlier chunk
-    else while (b_first > 0 && __ldg(L.item_off + b_first - 1) == item_lo) --b_first;   // empty minibatches in front
-  }
-  // minibatches beginning before item_hi; at the end of the call all that remain (empty ones included)
-  i64 b_end = L.G;
-  if (item_hi < n) {
-    b_end = batch_of(L.item_off, L.G, item_hi);
-    if (__ldg(L.item_off + b_end) < item_hi) ++b_end;
-    else while (b_end > 0 && __ldg(L.item_off + b_end - 1) == item_hi) --b_end;
-  }
-  if (b_end <= b_first) return;
-  const i64 lo = __ldg(L.region_off + b_first), hi = __ldg(L.region_off + b_end);
-  for (i64 i = lo + (i64)blockIdx.x * kBThreads + threadIdx.x; i < hi; i += (i64)gridDim.x * kBThreads)
-    L.slots[i] = kEmptyWord;
-}
-
 struct ItemRef {
   i64 batch;
   i64 local;   // position among the batch's items (seeds first)
@@ -125,107 +95,53 @@ __device__ __forceinline__ ItemRef resolve_item(const BatchLayout& L, i64 g) {
   return r;
 }
 
-// Items [item_lo, item_hi) of the call (item_lo a multiple of the CTA span); the whole call is [0, max).
-//
-// A warp owns 256 consecutive items (8 rounds of 32, lanes on consecutive items) and a CTA 2 048; CTAs stride over
-// the call, so the items in flight at any moment are a window of a few minibatches whose regions stay in L2.  The
-// minibatch of a warp's span is looked up once (it used to be once per 32 items: a binary search and nine parameter
-// loads in front of every probe — most of the kernel's 316 instructions per 32 items and a chain of dependent loads
-// before the first useful one).  The ids of all eight rounds are loaded first; the home slot of round r + 1 is
-// fetched before round r's atomics are issued, so a lane always has one probe in flight behind the one it resolves.
-// A stale view of a slot is harmless: keys never change once claimed and positions only decrease.
-// ROUNDS = 1: a warp owns 32 items per pass (the form in use); ROUNDS = 8: the span described above.
-constexpr i64 kInsCtaSpan = 32 * 8 * (kBThreads / 32);   // items per CTA pass with ROUNDS = 8; chunk boundaries align to it
-
-constexpr uint32_t kBadId = 0xFFFFFFFFu;  // what an id outside [0, 2^32 - 1) becomes once ids are held in 32 bits
-
-template <int ROUNDS>
-__global__ void __launch_bounds__(kBThreads, ROUNDS == 1 ? 8 : 4) k_batch_insert(BatchLayout L, i64* counters,
-                                                                                 i64 item_lo, i64 item_hi) {
-  constexpr int kInsRounds = ROUNDS;
-  constexpr i64 kInsWarpSpan = 32 * kInsRounds;
-  constexpr i64 kInsCtaSpan = kInsWarpSpan * (kBThreads / 32);
+// A warp takes 32 consecutive items per pass (lanes on consecutive items, one probe chain per lane); warps stride over
+// the call, so the items in flight at any moment are a window of a few minibatches whose regions stay in L2.
+// Measured and dropped: a warp owning 256 consecutive items with the minibatch looked up once per span, the ids of all
+// eight rounds loaded first and the next round's home slot prefetched — 63 registers, half the resident warps, 7.6
+// instead of 6.2 ms per 1 000 minibatches: the number of resident probe chains sets the pace, not the per-tile look-up;
+// more items per lane only add contention on the slots of frequent ids.
+__global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
   if (counters[CNT_ABORT] != 0) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const i64 n = min(L.item_off[L.G], item_hi);
-  for (i64 cbase = item_lo + (i64)blockIdx.x * kInsCtaSpan; cbase < n; cbase += (i64)gridDim.x * kInsCtaSpan) {
-    const i64 wbase = cbase + (i64)warp * kInsWarpSpan;
-    if (wbase >= n) continue;
-    const i64 wend = min(n, wbase + kInsWarpSpan);
-    const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, wbase));
-    if (wend <= u.next_begin) {
-      uint32_t node[kInsRounds];
-#pragma unroll
-      for (int r = 0; r < kInsRounds; ++r) {
-        const i64 g = wbase + r * 32 + lane;
-        const i64 local = g - u.begin;
-        const i64 id = g < wend ? (local < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + local)
-                                                       : __ldg(L.indices + u.edges_begin + (local - u.num_seeds)))
-                                : -1;
-        node[r] = valid_id(id) ? (uint32_t)id : kBadId;
+  const int lane = threadIdx.x & 31;
+  const i64 n = L.item_off[L.G];
+  const i64 warps = (i64)gridDim.x * (kBThreads / 32);
+  for (i64 tile = (i64)blockIdx.x * (kBThreads / 32) + (threadIdx.x >> 5); tile * 32 < n; tile += warps) {
+    const i64 g = tile * 32 + lane;
+    const i64 end = min(n, tile * 32 + 32);
+    const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, tile * 32));
+    if (end <= u.next_begin) {
+      if (g >= end) continue;
+      const i64 lc = g - u.begin;
+      const i64 node = lc < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + lc)
+                                        : __ldg(L.indices + u.edges_begin + (lc - u.num_seeds));
+      if (!valid_id(node)) {
+        raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+        continue;
       }
-      i64 h_next = 0;
-      u64 w_next = 0;
-      if (wbase + lane < wend && node[0] != kBadId) {
-        h_next = home_slot((i64)node[0], u.size);
-        w_next = __ldcg(u.region + h_next);
-      }
-#pragma unroll
-      for (int r = 0; r < kInsRounds; ++r) {
-        const i64 g = wbase + r * 32 + lane;
-        const i64 h = h_next;
-        const u64 w = w_next;
-        if (r + 1 < kInsRounds) {
-          if (g + 32 < wend && node[r + 1] != kBadId) {
-            h_next = home_slot((i64)node[r + 1], u.size);
-            w_next = __ldcg(u.region + h_next);
-          }
-        }
-        if (g >= wend) continue;
-        if (node[r] == kBadId) {
-          raise_error(counters, GSB_ERR_INDEX_RANGE, g);
-          continue;
-        }
-        const i64 lc = g - u.begin;
-        const u64 mine = ((u64)node[r] << 32) | (u64)(uint32_t)(lc < u.num_seeds ? lc : u.edges_begin + lc);
-        if ((w >> 32) == (u64)node[r] && (uint32_t)w <= (uint32_t)mine) continue;  // already there, earlier
-        if (!insert_from(u.region, u.size, h, w, (i64)node[r], mine)) raise_error(counters, GSB_ERR_TABLE_FULL, g);
-      }
+      const i64 h = home_slot(node, u.size);
+      const u64 w = __ldcg(u.region + h);
+      const u64 mine = ((u64)node << 32) | (u64)(uint32_t)(lc < u.num_seeds ? lc : u.edges_begin + lc);
+      if ((w >> 32) == (u64)node && (uint32_t)w <= (uint32_t)mine) continue;  // already there, earlier
+      if (!insert_from(u.region, u.size, h, w, node, mine)) raise_error(counters, GSB_ERR_TABLE_FULL, g);
     } else {
-      // the span straddles minibatches (or holds empty ones): every item finds its own
-      for (int r = 0; r < kInsRounds; ++r) {
-        const i64 g = wbase + r * 32 + lane;
-        if (g >= wend) continue;
-        const ItemRef it = resolve_item(L, g);
-        if (!valid_id(it.node)) {
-          raise_error(counters, GSB_ERR_INDEX_RANGE, g);
-          continue;
-        }
-        const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.key;
-        const i64 h = home_slot(it.node, it.size);
-        if (!insert_from(it.region, it.size, h, __ldcg(it.region + h), it.node, mine))
-          raise_error(counters, GSB_ERR_TABLE_FULL, g);
+      // the tile straddles minibatches (or holds empty ones): every item finds its own
+      if (g >= end) continue;
+      const ItemRef it = resolve_item(L, g);
+      if (!valid_id(it.node)) {
+        raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+        continue;
       }
+      const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.key;
+      const i64 h = home_slot(it.node, it.size);
+      if (!insert_from(it.region, it.size, h, __ldcg(it.region + h), it.node, mine))
+        raise_error(counters, GSB_ERR_TABLE_FULL, g);
     }
   }
 }
 
-static inline void launch_batch_insert(const BatchLayout& L, i64* counters, i64 item_lo, i64 item_hi, i64 items_bound,
-                                       cudaStream_t stream) {
-  const int wide = wide_grid();
-  static const int forced = [] {   // GSB_INSERT_ROUNDS = 1 or 8 pins the variant (for measurements)
-    const char* e = getenv("GSB_INSERT_ROUNDS");
-    return e ? atoi(e) : 0;
-  }();
-  // Measured on the products-scale workload (125 minibatches per call): the eight-round form is SLOWER (7.6 against
-  // 6.2 ms per 1 000 minibatches) — its 63 registers halve the resident warps, and resident probe chains, not the
-  // per-tile look-up, set the pace.  One round is the default; GSB_INSERT_ROUNDS=8 selects the other for measurements.
-  if (forced == 8)   // four resident CTAs per SM
-    k_batch_insert<8><<<max(1, min(grid_for(items_bound, kInsCtaSpan), kNumSMs * 4)), kBThreads, 0, stream>>>(
-        L, counters, item_lo, item_hi);
-  else
-    k_batch_insert<1><<<max(1, min(grid_for(items_bound, kBThreads), wide)), kBThreads, 0, stream>>>(L, counters, item_lo,
-                                                                                                   item_hi);
+static inline void launch_batch_insert(const BatchLayout& L, i64* counters, i64 items_bound, cudaStream_t stream) {
+  k_batch_insert<<<max(1, min(grid_for(items_bound, kBThreads), kNumSMs * 8)), kBThreads, 0, stream>>>(L, counters);
 }
 
 // One CTA per tile of kBTile items; each of its 8 warps covers kWarpItems consecutive items.  First-
@@ -654,35 +570,6 @@ static int read_totals(gsb_ctx* ctx, cudaStream_t stream, i64* unique_total_host
   return GSB_OK;
 }
 
-static int chunked_hash_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchLayout& L, const DirectTables& T,
-                                       i64 n_cap, i64 e_cap, i64 chunk_items, i64* out_unique, i64* out_unique_ptr,
-                                       i64* out_relabeled) {
-  i64* counters = ctx_counters(ctx);
-  const int wide = kNumSMs * 8;
-  TileState ts;  // one epoch for the whole call: a chunk's first tile looks back at the words of the chunk before
-  int st = ctx_tile_state(ctx, grid_for(n_cap, kBTile), stream, &ts);
-  if (st != GSB_OK) return st;
-  for (i64 lo = 0; lo < n_cap || lo == 0; lo += chunk_items) {
-    const i64 hi = min(n_cap, lo + chunk_items);
-    const i64 items = max((i64)1, hi - lo);
-    {
-      ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
-      k_clear_chunk_regions<<<max(1, min(grid_for(2 * items, kBThreads * 4), wide)), kBThreads, 0, stream>>>(
-          L, counters, lo, hi >= n_cap ? kAllItems : hi);
-    }
-    GSB_LAUNCH_OK();
-    {
-      ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
-      launch_batch_insert(L, counters, lo, hi, items, stream);
-    }
-    GSB_LAUNCH_OK();
-    st = hash_compact_chunk_launch(ctx, stream, L, T, lo, hi, ts, out_unique, out_unique_ptr, out_relabeled);
-    if (st != GSB_OK) return st;
-    if (n_cap == 0) break;
-  }
-  return relabel_fixup_launch(ctx, stream, L, T, e_cap, out_unique_ptr, out_relabeled);
-}
-
 // L carries seeds / seeds_ptr / indices / indices_ptr / G; scratch fields are filled here.  seeds_bound / edges_bound
 // are what the caller sized the outputs for (the exact counts are read on the device).
 static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 seeds_bound, i64 edges_bound,
@@ -705,11 +592,9 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
   }
   if (path == 2 && !tables) return num_nodes > 0 ? GSB_ERR_OUT_OF_MEMORY : GSB_ERR_INVALID_ARGUMENT;
   void* ws;
-  const size_t ref_bytes = ((size_t)n_cap * 4 + 255) & ~(size_t)255;
-  const size_t count_bytes = ((size_t)(n_cap / kWarpItems + 3) * 8 + 255) & ~(size_t)255;
   if (tables) {
     const size_t rank_bytes = ((size_t)n_cap * 4 + 255) & ~(size_t)255;
-    int st = ctx_reserve_workspace(ctx, off_bytes + rank_bytes + ref_bytes + count_bytes, &ws);
+    int st = ctx_reserve_workspace(ctx, off_bytes + rank_bytes, &ws);
     if (st != GSB_OK) return st;
     L.item_off = (i64*)ws;
     L.region_off = nullptr;
@@ -725,8 +610,6 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
     T.num_nodes = num_nodes;
     T.epoch_hi = (u64)(~epoch) << 32;
     T.rank_of_item = (uint32_t*)((char*)ws + off_bytes);
-    T.ref = (uint32_t*)((char*)ws + off_bytes + rank_bytes);
-    T.tile_count = (i64*)((char*)ws + off_bytes + rank_bytes + ref_bytes);
     T.seeds_distinct = (flags & GSB_SEEDS_DISTINCT) ? 1 : 0;
     return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr,
                                         out_relabeled);
@@ -734,7 +617,7 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
   const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
   const size_t rank_bytes = ((size_t)n_cap * 4 + 255) & ~(size_t)255;
-  int st = ctx_reserve_workspace(ctx, slots_bytes + 2 * off_bytes + rank_bytes + ref_bytes + count_bytes, &ws);
+  int st = ctx_reserve_workspace(ctx, slots_bytes + 2 * off_bytes + rank_bytes, &ws);
   if (st != GSB_OK) return st;
   L.slots = (u64*)ws;
   L.item_off = (i64*)((char*)ws + slots_bytes);
@@ -750,20 +633,7 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
   T.num_nodes = 0;
   T.epoch_hi = 0;
   T.rank_of_item = (uint32_t*)((char*)ws + slots_bytes + 2 * off_bytes);
-  T.ref = (uint32_t*)((char*)ws + slots_bytes + 2 * off_bytes + rank_bytes);
-  T.tile_count = (i64*)((char*)ws + slots_bytes + 2 * off_bytes + rank_bytes + ref_bytes);
   T.seeds_distinct = (flags & GSB_SEEDS_DISTINCT) ? 1 : 0;
-  // Large calls go through clear -> insert -> compaction in chunks of consecutive items whose table regions fit the
-  // L2 cache together (16 bytes of slots per item): the regions a chunk touches are written by the clear, updated by
-  // the insert and read by the compaction while they are still cache resident, instead of being written out and
-  // fetched from DRAM again by every pass.  Chunks are item ranges, not minibatch ranges — the host does not know where
-  // minibatches begin — which is safe because an item's first-occurrence status depends on earlier items only.
-  const i64 chunk_bytes = ctx_option(ctx, GSB_OPT_RELABEL_CHUNK_BYTES);
-  i64 chunk_items = chunk_bytes > 0 ? (chunk_bytes / 16) / kInsCtaSpan * kInsCtaSpan : 0;
-  if (chunk_items > 0 && chunk_items < kInsCtaSpan) chunk_items = kInsCtaSpan;
-  if (chunk_items > 0 && n_cap > chunk_items + chunk_items / 2)
-    return chunked_hash_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, chunk_items, out_unique, out_unique_ptr,
-                                       out_relabeled);
   {
     ScopedKernelTimer timer(ctx, KID_TABLE_CLEAR, stream);
     GSB_CUDA_OK(cudaMemsetAsync(L.slots, 0xFF, slots_bytes, stream));
@@ -772,7 +642,7 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
     ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
     // one item per lane measured fastest for the hash insert (more items in flight per lane only add contention
     // on the slots of frequent ids)
-    launch_batch_insert(L, counters, 0, kAllItems, n_cap, stream);
+    launch_batch_insert(L, counters, n_cap, stream);
   }
   GSB_LAUNCH_OK();
   // compaction that only READS the slots and leaves, for every neighbour, its frontier rank or a reference to the
@@ -934,7 +804,7 @@ static int build_batch_tables(gsb_ctx* ctx, cudaStream_t stream, const i64* seed
   GSB_LAUNCH_OK();
   {
     ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
-    launch_batch_insert(L, counters, 0, kAllItems, n_cap, stream);
+    launch_batch_insert(L, counters, n_cap, stream);
   }
   GSB_LAUNCH_OK();
   if (out_unique_ptr) {
@@ -1120,7 +990,7 @@ int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i
   const int wide = kNumSMs * 8;
   {
     ScopedKernelTimer timer(ctx, KID_TABLE_INSERT, stream);
-    launch_batch_insert(L, counters, 0, kAllItems, n_cap, stream);
+    launch_batch_insert(L, counters, n_cap, stream);
   }
   GSB_LAUNCH_OK();
   const int tiles = grid_for(n_cap, kBTile);

@@ -155,9 +155,6 @@ struct DirectTables {
   u64 epoch_hi;            // (u64)(~epoch) << 32
   uint32_t* rank_of_item;  // [items of the call]: frontier position of an item that is a first occurrence
   int seeds_distinct;      // the caller promises that no id repeats among the seeds of a minibatch
-  // scratch of the flags -> scan -> emit form of the compaction (null: not provided)
-  uint32_t* ref;           // [items of the call]: index of the item that came first with this item's id
-  i64* tile_count;         // [items / 128 + 2]: first occurrences per warp tile, then their exclusive scan
 };
 constexpr uint32_t kEdgeKeyBit = 0x80000000u;
 
@@ -165,21 +162,10 @@ constexpr uint32_t kEdgeKeyBit = 0x80000000u;
 // L.item_off must be valid (k_batch_layout); n_cap / e_cap bound the items / edges of the call.
 int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchLayout& L, const DirectTables& T,
                                  i64 n_cap, i64 e_cap, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
-// The pieces of the same sequence for a call that is processed in chunks of consecutive items (batch_relabel.cu):
-// compaction of the tiles of items [item_lo, item_hi) over hash regions, and the final fix-up pass.
-int hash_compact_chunk_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchLayout& L, const DirectTables& T, i64 item_lo,
-                              i64 item_hi, const TileState& ts, i64* out_unique, i64* out_unique_ptr,
-                              i64* out_relabeled);
-int relabel_fixup_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchLayout& L, const DirectTables& T, i64 e_cap,
-                         i64* out_unique_ptr, i64* out_relabeled);
-// Grid of the grid-stride kernels of the batched relabel (CTAs per SM x 148; see direct_relabel.cu).
-int wide_grid();
-
 struct CompactOut {
   i64* unique;      // all frontiers back to back
   i64* unique_ptr;  // [G + 1]
 };
-
 
 // Single-batch unique + relabel through the packed-slot batched kernels (defined in batch_relabel.cu).
 int unique_relabel_packed(gsb_ctx* ctx, cudaStream_t stream, const i64* first, i64 S, const i64* second, i64 E,

@@ -239,7 +239,6 @@ int gsb_ctx_create(int device, gsb_ctx** out_ctx) {
   ctx->options[GSB_OPT_TABLE_SLOTS] = 0;
   ctx->options[GSB_OPT_RELABEL_PATH] = 0;
   ctx->options[GSB_OPT_DIRECT_TABLE_BUDGET] = 6ll << 30;
-  ctx->options[GSB_OPT_RELABEL_CHUNK_BYTES] = 0;  // off: chunked passes were measured slower at every chunk size
   int prev = 0;
   cudaGetDevice(&prev);
   int st = GSB_OK;
@@ -330,7 +329,6 @@ int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value) {
       if (value < 0 || value > 1) return GSB_ERR_INVALID_ARGUMENT;
       break;
     case GSB_OPT_DIRECT_TABLE_BUDGET:
-    case GSB_OPT_RELABEL_CHUNK_BYTES:
       if (value < 0) return GSB_ERR_INVALID_ARGUMENT;
       break;
   }

@@ -34,15 +34,25 @@ __device__ __forceinline__ void raise_error(i64* counters, int code, i64 info) {
   if (atomicCAS((u64*)&counters[CNT_ERROR], 0ull, (u64)(i64)code) == 0ull) counters[CNT_ERROR_INFO] = info;
 }
 
+// The two halves of tile_exclusive_prefix, for kernels that have independent work to put between them: a tile first
+// PUBLISHES its aggregate (its successors can then add it up without waiting for this tile's own prefix), issues
+// whatever loads it can, and only then RESOLVES its prefix — the wait for the predecessors overlaps those loads.
+__device__ __forceinline__ void tile_publish_aggregate(const TileState& ts, int tile, i64 aggregate) {
+  if ((threadIdx.x & 31) == 0) st_volatile_u64(&ts.words[tile], tile_word(ts.epoch, tile == 0 ? 2 : 1, aggregate));
+}
+
+__device__ __forceinline__ i64 tile_resolve_prefix(const TileState& ts, int tile, i64 aggregate);
+
 // Called by all 32 lanes of warp 0 of the CTA that owns `tile`.  Returns the sum of the
 // aggregates of tiles [0, tile) and publishes this tile's inclusive prefix.
 __device__ __forceinline__ i64 tile_exclusive_prefix(const TileState& ts, int tile, i64 aggregate) {
+  tile_publish_aggregate(ts, tile, aggregate);
+  return tile_resolve_prefix(ts, tile, aggregate);
+}
+
+__device__ __forceinline__ i64 tile_resolve_prefix(const TileState& ts, int tile, i64 aggregate) {
   const int lane = threadIdx.x & 31;
-  if (tile == 0) {
-    if (lane == 0) st_volatile_u64(&ts.words[0], tile_word(ts.epoch, 2, aggregate));
-    return 0;
-  }
-  if (lane == 0) st_volatile_u64(&ts.words[tile], tile_word(ts.epoch, 1, aggregate));
+  if (tile == 0) return 0;
   i64 exclusive = 0;
   int idx = tile - 1;  // nearest predecessor examined by lane 0
   const uint32_t ep = ts.epoch & kEpochMask;
