@@ -47,12 +47,12 @@ METRIC = "sampled_edges_per_second"
 UNIT = "edges/s"
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) divided by algorithmic bytes, from one ncu capture
-# per kernel on a 64-minibatch call of this workload (profiles/k_*_sage3hop_group64.md).  Traffic grows in
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) divided by algorithmic bytes, from one ncu capture per
+# kernel on hop 3 of a 64-minibatch call of this workload (profiles/k_*_sage3hop_group64.md).  Traffic grows in
 # proportion to the units a launch processes, so a full launch's traffic is this ratio times its algorithmic bytes.
-TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.1, "table_insert": 4.0, "first_compact": 2.9, "relabel": 2.3}
-# the same for the direct-address form of unique + relabel (profiles/k_direct_*_sage3hop_group64.md)
-TRAFFIC_OVER_ALGORITHMIC_DIRECT = {"sample_uniform": 4.1}
+TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.2, "table_insert": 4.1, "first_compact": 3.2, "relabel": 1.04}
+# the same with direct-address tables (profiles/k_direct_insert_sage3hop_group64.md)
+TRAFFIC_OVER_ALGORITHMIC_DIRECT = {"sample_uniform": 4.2, "table_insert": 9.1}
 
 
 def parse():
@@ -64,8 +64,6 @@ def parse():
                     help="minibatches every GPU processes per step (the configuration has 1,000)")
     ap.add_argument("--relabel-path", default=None, choices=["auto", "hash", "direct"],
                     help="table form of unique + relabel (default: the library's automatic choice)")
-    ap.add_argument("--relabel-chunk-mb", type=int, default=None,
-                    help="chunk size of the batched relabel in MiB of table regions (default: the library's; 0 = off)")
     ap.add_argument("--lanes", type=int, default=3,
                     help="CUDA streams (each with its own library context and output arena) that take the calls of a "
                          "step in turn; with --host-waits every lane is a host thread")
@@ -398,8 +396,6 @@ def run_ours(args):
     for c in ctxs:
         if args.relabel_path:
             c.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2}[args.relabel_path])
-        if args.relabel_chunk_mb is not None:
-            c.set_option("relabel_chunk_bytes", args.relabel_chunk_mb << 20)
         if args.host_waits and lanes > 1 and not args.spin_wait:
             c.set_option("blocking_wait", 1)    # a lane that waits for its hop sleeps; the other lanes keep the GPU fed
     group = args.group
@@ -519,8 +515,8 @@ def run_ours(args):
                     "table_insert": "k_direct_insert (atomicMin into per-minibatch direct-address tables)" if direct
                     else "k_batch_insert (position-min hash insert)",
                     "first_compact": "k_direct_compact (first-occurrence test + scan + compaction)" if direct
-                    else "k_batch_compact (first-occurrence scan + compaction)",
-                    "relabel": "k_direct_fixup (rank look-up of repeated ids)" if direct else "k_batch_relabel (lookup)"}
+                    else "k_direct_compact<HASH> (first-occurrence test on hash regions + scan + compaction)",
+                    "relabel": "k_direct_fixup (rank look-up of repeated ids)"}
     total_ms = sum(v[0] for v in prof.values()) or 1.0
     per_kernel = {}
     for name, (ms, n) in prof.items():
@@ -801,6 +797,7 @@ def run_walk(args):
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
     from graph_sampling_b200.sharding import reduce_run_stats
     steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    args.walkers = min(args.walkers, args.walk_nodes)      # one walker per DISTINCT start node
     m = measure_walk(torch, args, args.impl, device, rank, world, barrier, steps, warmup)
     seconds_all, units_all = reduce_run_stats(m["seconds"], m["units"], device=device)
     if rank == 0:
@@ -1132,6 +1129,10 @@ def run_kernels(args):
     items = torch.cat([seeds, sub_row])
     timed("unique + relabel (single table)", lambda: ops.relabel([seeds, sub_row], [sub_row]),
           lambda o: 8 * items.numel() + 8 * o[0].numel() + 8 * D)
+    third = sub_row[:1_000_000].contiguous()
+    timed("unique + relabel (three arrays: 16-byte slots)", lambda: ops.relabel([seeds, sub_row, third], [sub_row]),
+          lambda o: 8 * (items.numel() + third.numel()) + 8 * o[0].numel() + 8 * D,
+          note="the general form of gs::Graph::Relabel; two-array calls take the packed-slot kernels above")
     F = 256
     x = torch.randn(n, F, generator=g, device=device)
     xd = x[seeds]

@@ -100,7 +100,9 @@ __device__ __forceinline__ ItemRef resolve_item(const BatchLayout& L, i64 g) {
 // Measured and dropped: a warp owning 256 consecutive items with the minibatch looked up once per span, the ids of all
 // eight rounds loaded first and the next round's home slot prefetched — 63 registers, half the resident warps, 7.6
 // instead of 6.2 ms per 1 000 minibatches: the number of resident probe chains sets the pace, not the per-tile look-up;
-// more items per lane only add contention on the slots of frequent ids.
+// more items per lane only add contention on the slots of frequent ids.  Prefetching into L2, one pass ahead, the
+// slice of region slots that the next pass will probe (the clear wrote the regions out long before): 6.4 ms — the
+// probes are not waiting for DRAM fetches of the regions either.
 __global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
   if (counters[CNT_ABORT] != 0) return;
   const int lane = threadIdx.x & 31;

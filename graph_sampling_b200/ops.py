@@ -70,12 +70,11 @@ class Context:
     def check_device(self, where="device status"):
         self.check(self.lib.gsb_check_device_status(self.handle, _stream()), where)
 
-    OPTIONS = {"max_polls": 0, "table_slots": 1, "relabel_path": 2, "direct_table_budget": 3,
-               "relabel_chunk_bytes": 4, "blocking_wait": 5}
+    OPTIONS = {"max_polls": 0, "table_slots": 1, "relabel_path": 2, "direct_table_budget": 3, "blocking_wait": 4}
 
     def set_option(self, name, value):
         """gsb_ctx_set_option by name: max_polls, table_slots, relabel_path (0 auto, 1 hash, 2 direct),
-        direct_table_budget (bytes), relabel_chunk_bytes, blocking_wait (0 / 1)."""
+        direct_table_budget (bytes), blocking_wait (0 / 1)."""
         self.check(self.lib.gsb_ctx_set_option(self.handle, c_int(self.OPTIONS[name]), c_i64(int(value))),
                    "gsb_ctx_set_option")
 

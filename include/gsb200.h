@@ -82,12 +82,6 @@ GSB_API int gsb_check_device_status(gsb_ctx* ctx, void* stream);
  *                               2 = direct-address tables (GSB_ERR_OUT_OF_MEMORY when they do not fit);
  *  GSB_OPT_DIRECT_TABLE_BUDGET  bytes the direct-address tables (8 bytes x num_nodes x minibatches per call) may
  *                               take, default 6 GiB;
- *  GSB_OPT_RELABEL_CHUNK_BYTES  > 0: the hash-table form of the batched relabel processes a large call in chunks of
- *                               consecutive items whose table regions (16 bytes per item) add up to about this many
- *                               bytes, so that clear, insert and compaction of a chunk meet its regions in the L2
- *                               cache.  Default 0 = the whole call at once: on a B200 the chunked form was slower at
- *                               every chunk size tried (the passes are not bound by DRAM re-fetches of the regions,
- *                               and short launches lose more in ramp-up and tail).  Results do not depend on it;
  *  GSB_OPT_BLOCKING_WAIT        1: calls that wait for their stream (the ones with a *_host result) sleep on an event
  *                               created with cudaEventBlockingSync instead of calling cudaStreamSynchronize, which
  *                               may spin — for hosts that drive several streams from several threads, or several
@@ -97,9 +91,8 @@ enum gsb_option {
   GSB_OPT_TABLE_SLOTS = 1,
   GSB_OPT_RELABEL_PATH = 2,
   GSB_OPT_DIRECT_TABLE_BUDGET = 3,
-  GSB_OPT_RELABEL_CHUNK_BYTES = 4,
-  GSB_OPT_BLOCKING_WAIT = 5,
-  GSB_OPT_NUM = 6
+  GSB_OPT_BLOCKING_WAIT = 4,
+  GSB_OPT_NUM = 5
 };
 GSB_API int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value);
 GSB_API int gsb_ctx_get_option(gsb_ctx* ctx, int option, int64_t* value_host);

@@ -35,7 +35,7 @@ def test_every_entry_point_is_bound_with_its_declared_arity(lib):
     for name, (restype, argtypes) in protos.items():
         fn = getattr(lib, name)
         assert fn.argtypes is not None and len(fn.argtypes) == len(argtypes), name
-    assert len(protos["gsb_sage_hop"][1]) == 23 and len(protos["gsb_col_slice_count"][1]) == 8
+    assert len(protos["gsb_sage_hop"][1]) == 24 and len(protos["gsb_col_slice_count"][1]) == 8
     assert len(protos["gsb_random_walk"][1]) == 12 and len(protos["gsb_ctx_set_option"][1]) == 3
     with pytest.raises((TypeError, ctypes.ArgumentError)):
         lib.gsb_col_slice_count(None, None)

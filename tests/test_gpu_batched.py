@@ -123,42 +123,6 @@ def test_batch_csr_relabel_paths_agree_with_oracle(ops, oracle, relabel_path, G,
         assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
 
 
-@pytest.mark.parametrize("chunk_bytes", [16 * 1024, 48 * 1024, 1 << 20])
-@pytest.mark.parametrize("G,ns,ne", [(7, 100, 3000), (64, 1024, 9000), (300, 17, 200)])
-def test_chunked_hash_relabel_equals_oracle(ops, oracle, chunk_bytes, G, ns, ne):
-    """The hash-table form cut into chunks of 1,024 / 3,072 / 65,536 items: minibatches straddle chunk boundaries,
-    some are empty, some chunks begin with empty minibatches — results must not depend on the chunk size."""
-    ctx = ops.default_context()
-    ctx.set_option("relabel_path", 1)
-    old = ctx.get_option("relabel_chunk_bytes")
-    ctx.set_option("relabel_chunk_bytes", chunk_bytes)
-    try:
-        rng = np.random.default_rng(G + ns + chunk_bytes)
-        seeds_sizes = rng.integers(0, ns + 1, G)
-        edge_sizes = rng.integers(0, ne + 1, G)
-        edge_sizes[rng.random(G) < 0.2] = 0
-        seeds_sizes[rng.random(G) < 0.1] = 0
-        seeds_ptr = np.concatenate([[0], np.cumsum(seeds_sizes)]).astype(np.int64)
-        indices_ptr = np.concatenate([[0], np.cumsum(edge_sizes)]).astype(np.int64)
-        hi = max(8, (ns + ne) // 2)
-        seeds = np.concatenate([rng.choice(hi * 4, s, replace=False) for s in seeds_sizes] + [np.empty(0, np.int64)]).astype(np.int64)
-        indices = rng.integers(0, hi * 4, indices_ptr[-1]).astype(np.int64)
-        for distinct in (False, True):
-            uniq, uniq_ptr, rel, _ = ops.batch_csr_relabel(dev(seeds), dev(seeds_ptr), dev(indices), dev(indices_ptr),
-                                                           seeds_distinct=distinct)
-            uniq, uniq_ptr, rel = host(uniq), host(uniq_ptr), host(rel)
-            assert uniq_ptr[-1] == len(uniq) and len(rel) == indices_ptr[-1]
-            for b in range(G):
-                s_ = seeds[seeds_ptr[b]:seeds_ptr[b + 1]]
-                e = indices[indices_ptr[b]:indices_ptr[b + 1]]
-                wu, (wr,) = oracle.unique_relabel([s_, e], [e])
-                assert np.array_equal(uniq[uniq_ptr[b]:uniq_ptr[b + 1]], wu), b
-                assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
-    finally:
-        ctx.set_option("relabel_chunk_bytes", old)
-        ctx.set_option("relabel_path", 0)
-
-
 def test_direct_tables_survive_many_calls_and_a_change_of_shape(ops, oracle):
     """The direct-address tables are never cleared: stale entries of earlier calls (other ids, other batch counts,
     another node count) must lose against every entry of the current call."""
