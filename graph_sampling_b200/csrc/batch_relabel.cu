@@ -102,48 +102,87 @@ __device__ __forceinline__ ItemRef resolve_item(const BatchLayout& L, i64 g) {
 // instead of 6.2 ms per 1 000 minibatches: the number of resident probe chains sets the pace, not the per-tile look-up;
 // more items per lane only add contention on the slots of frequent ids.  Prefetching into L2, one pass ahead, the
 // slice of region slots that the next pass will probe (the clear wrote the regions out long before): 6.4 ms — the
-// probes are not waiting for DRAM fetches of the regions either.
-__global__ void __launch_bounds__(kBThreads) k_batch_insert(BatchLayout L, i64* counters) {
+// probes are not waiting for DRAM fetches of the regions either.  Letting the sampler insert the seed and the ids it
+// has just sampled while it still holds them in registers (regions laid out from seeds x (1 + fanout) and cleared
+// before it runs; the home slots of up to eight ids loaded before the first update): 72 / 92 registers instead of
+// 56 / 80, and 13.3 ms for the sampler against 6.5 + 6.1 ms for the two kernels — both phases are bound by the
+// latency of the warps in flight, so putting them into one warp adds their times and costs occupancy on top.
+// ITEMS > 1 (a warp pass of 32 x ITEMS consecutive items, all ids loaded, then all home slots, then the updates) is
+// kept as a template parameter because it was measured more than once: 2 items at 32 registers (a few spilled words)
+// 6.38 ms, 2 items at 40 registers / 6 CTAs 6.23 ms, 4 items at 40 registers 7.24 ms, 4 items at 64 registers / 4 CTAs
+// 7.61 ms, against 6.17 ms for one item per lane at full occupancy.  Asking the L2 for 32-byte instead of 64-byte
+// fetches (cudaLimitMaxL2FetchGranularity, accepted by the device) changes neither this kernel nor the sampler nor
+// the random walk.
+template <int ITEMS, int MIN_CTAS>
+__global__ void __launch_bounds__(kBThreads, MIN_CTAS) k_batch_insert(BatchLayout L, i64* counters) {
   if (counters[CNT_ABORT] != 0) return;
+  constexpr int kSpan = 32 * ITEMS;
   const int lane = threadIdx.x & 31;
   const i64 n = L.item_off[L.G];
   const i64 warps = (i64)gridDim.x * (kBThreads / 32);
-  for (i64 tile = (i64)blockIdx.x * (kBThreads / 32) + (threadIdx.x >> 5); tile * 32 < n; tile += warps) {
-    const i64 g = tile * 32 + lane;
-    const i64 end = min(n, tile * 32 + 32);
-    const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, tile * 32));
+  for (i64 tile = (i64)blockIdx.x * (kBThreads / 32) + (threadIdx.x >> 5); tile * kSpan < n; tile += warps) {
+    const i64 base = tile * kSpan;
+    const i64 end = min(n, base + kSpan);
+    const BatchUniform u = load_batch(L, L.item_off, batch_of(L.item_off, L.G, base));
     if (end <= u.next_begin) {
-      if (g >= end) continue;
-      const i64 lc = g - u.begin;
-      const i64 node = lc < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + lc)
-                                        : __ldg(L.indices + u.edges_begin + (lc - u.num_seeds));
-      if (!valid_id(node)) {
-        raise_error(counters, GSB_ERR_INDEX_RANGE, g);
-        continue;
+      i64 node[ITEMS];
+      uint32_t key[ITEMS];
+#pragma unroll
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        node[q] = -1;
+        key[q] = 0;
+        if (g < end) {
+          const i64 lc = g - u.begin;
+          node[q] = lc < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + lc)
+                                     : __ldg(L.indices + u.edges_begin + (lc - u.num_seeds));
+          key[q] = (uint32_t)(lc < u.num_seeds ? lc : u.edges_begin + lc);
+        }
       }
-      const i64 h = home_slot(node, u.size);
-      const u64 w = __ldcg(u.region + h);
-      const u64 mine = ((u64)node << 32) | (u64)(uint32_t)(lc < u.num_seeds ? lc : u.edges_begin + lc);
-      if ((w >> 32) == (u64)node && (uint32_t)w <= (uint32_t)mine) continue;  // already there, earlier
-      if (!insert_from(u.region, u.size, h, w, node, mine)) raise_error(counters, GSB_ERR_TABLE_FULL, g);
+      uint32_t h[ITEMS];
+      u64 w[ITEMS];
+#pragma unroll
+      for (int q = 0; q < ITEMS; ++q) {
+        h[q] = 0;
+        w[q] = 0;
+        if (valid_id(node[q])) {
+          h[q] = (uint32_t)home_slot(node[q], u.size);
+          w[q] = __ldcg(u.region + h[q]);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        if (g >= end) continue;
+        if (!valid_id(node[q])) {
+          raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+          continue;
+        }
+        const u64 mine = ((u64)node[q] << 32) | (u64)key[q];
+        if ((w[q] >> 32) == (u64)node[q] && (uint32_t)w[q] <= key[q]) continue;  // already there, earlier
+        if (!insert_from(u.region, u.size, h[q], w[q], node[q], mine)) raise_error(counters, GSB_ERR_TABLE_FULL, g);
+      }
     } else {
-      // the tile straddles minibatches (or holds empty ones): every item finds its own
-      if (g >= end) continue;
-      const ItemRef it = resolve_item(L, g);
-      if (!valid_id(it.node)) {
-        raise_error(counters, GSB_ERR_INDEX_RANGE, g);
-        continue;
+      // the span straddles minibatches (or holds empty ones): every item finds its own
+      for (int q = 0; q < ITEMS; ++q) {
+        const i64 g = base + q * 32 + lane;
+        if (g >= end) continue;
+        const ItemRef it = resolve_item(L, g);
+        if (!valid_id(it.node)) {
+          raise_error(counters, GSB_ERR_INDEX_RANGE, g);
+          continue;
+        }
+        const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.key;
+        const i64 h = home_slot(it.node, it.size);
+        if (!insert_from(it.region, it.size, h, __ldcg(it.region + h), it.node, mine))
+          raise_error(counters, GSB_ERR_TABLE_FULL, g);
       }
-      const u64 mine = ((u64)it.node << 32) | (u64)(uint32_t)it.key;
-      const i64 h = home_slot(it.node, it.size);
-      if (!insert_from(it.region, it.size, h, __ldcg(it.region + h), it.node, mine))
-        raise_error(counters, GSB_ERR_TABLE_FULL, g);
     }
   }
 }
 
 static inline void launch_batch_insert(const BatchLayout& L, i64* counters, i64 items_bound, cudaStream_t stream) {
-  k_batch_insert<<<max(1, min(grid_for(items_bound, kBThreads), kNumSMs * 8)), kBThreads, 0, stream>>>(L, counters);
+  k_batch_insert<1, 8><<<max(1, min(grid_for(items_bound, kBThreads), kNumSMs * 8)), kBThreads, 0, stream>>>(L, counters);
 }
 
 // One CTA per tile of kBTile items; each of its 8 warps covers kWarpItems consecutive items.  First-

@@ -93,6 +93,10 @@ struct Workspace {
 };
 int ctx_reserve_workspace(gsb_ctx* ctx, size_t bytes, void** out);
 int ctx_tile_state(gsb_ctx* ctx, i64 num_tiles, cudaStream_t stream, TileState* out);
+// Offsets of a per-column result by the counting kernel alone (defined in slice_sample.cu): mode 0 = degrees,
+// 1 = min(degree, k), 2 = k per non-empty column.  The total is left in the context's counters.
+int count_scan_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, i64 num_cols, const i64* seeds, i64 S, i64 k,
+                      int mode, i64* out_indptr);
 i64* ctx_counters(gsb_ctx* ctx);
 i64* ctx_pinned(gsb_ctx* ctx);
 int ctx_device(gsb_ctx* ctx);

@@ -548,6 +548,22 @@ __global__ void __launch_bounds__(kThreads) k_sample_one_keepdim(const i64* __re
   }
 }
 
+// Offsets of a per-column sample (min(degree, k) without replacement, k per non-empty column with) or of the plain
+// slice (mode 0) by the counting kernel alone; the total lands in the context's counters.
+int count_scan_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, i64 num_cols, const i64* seeds, i64 S, i64 k,
+                      int mode, i64* out_indptr) {
+  const int grid = grid_for(S, kThreads);
+  TileState ts;
+  int st = ctx_tile_state(ctx, grid, stream, &ts);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_COUNT_SCAN, stream);
+    k_count_scan<<<grid, kThreads, 0, stream>>>(indptr, num_cols, seeds, S, k, mode, out_indptr, ctx_counters(ctx), ts);
+  }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
 template <int G>
 static void launch_sample(const SampleParams& p, int grid, cudaStream_t stream) {
   k_sample_uniform<G><<<grid, kThreads, 0, stream>>>(p);

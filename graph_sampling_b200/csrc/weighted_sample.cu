@@ -332,6 +332,129 @@ __global__ void __launch_bounds__(kWThreads, 6) k_sample_weighted(WeightedParams
   }
 }
 
+// ---- fan-outs above 32 (the reference stops at 32: src/cuda/sampling_probs.cu:32) -----------------------------
+// One CTA per column.  A column longer than the fan-out finds the fan-out-th best entry by a most-significant-digit
+// radix select over the 64-bit composite (order-preserving image of the key : 32 | ~position : 32) — composites are
+// distinct, larger = ranks first, so "the k best" is "composite >= threshold" with no tie handling — then gathers
+// the winners into shared memory, sorts them (bitonic, descending) and emits them in the order the list kernel uses.
+// The select stops as soon as a digit's bin is taken whole, which without ties is after the four key digits.  Keys of
+// columns up to kWideCache entries are evaluated once and kept in shared memory, longer columns evaluate them again
+// in every pass.
+constexpr int kWideThreads = 256;
+constexpr int kWideMaxK = 1024;
+constexpr int kWideCache = 6144;
+
+__device__ __forceinline__ u32 sortable_key(float key) {
+  const u32 u = __float_as_uint(key + 0.0f);  // -0 becomes +0: the comparison the list kernel uses cannot tell them apart
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(kWideThreads) k_sample_weighted_wide(WeightedParams p) {
+  __shared__ u32 s_cache[kWideCache];
+  __shared__ u64 s_win[kWideMaxK];
+  __shared__ u32 s_hist[256];
+  __shared__ u64 s_prefix;
+  __shared__ u32 s_need;
+  __shared__ int s_done;
+  __shared__ u32 s_count;
+  const int tid = threadIdx.x;
+  const i64 S = p.S;
+  const int k = (int)p.k;
+  const i64 total = p.out_indptr[S];
+  if (total > p.capacity) {
+    if (blockIdx.x == 0 && tid == 0) raise_error(p.counters, GSB_ERR_CAPACITY, total);
+    return;
+  }
+  for (i64 col_pos = blockIdx.x; col_pos < S; col_pos += gridDim.x) {
+    const i64 col = p.seeds ? p.seeds[col_pos] : col_pos;
+    if ((u64)col >= (u64)p.num_cols) continue;  // recorded by the counting kernel; the column is empty
+    const i64 b = p.indptr[col], d = p.indptr[col + 1] - b, o = p.out_indptr[col_pos];
+    if (d <= k) {
+      for (i64 j = tid; j < d; j += kWideThreads) emit_weighted(p, o + j, b + j, col_pos);
+      continue;
+    }
+    if (d > (i64)kMaxScanEnd) {
+      if (tid == 0) raise_error(p.counters, GSB_ERR_UNSUPPORTED, d);
+      continue;
+    }
+    const u32 n = (u32)d;
+    const bool cached = n <= (u32)kWideCache;
+    const float* probs = p.probs + b;
+    auto key_of = [&](u32 e) -> u32 {
+      const U32x4 r = rand_block(p.seed, (u64)col_pos, (u64)(e >> 2), STREAM_WEIGHTED);
+      return sortable_key(ares_key(r.v[e & 3], __ldg(probs + e)));
+    };
+    __syncthreads();  // the previous column is done with the shared arrays
+    if (cached) {
+      for (u32 e4 = 4 * tid; e4 < n; e4 += 4 * kWideThreads) {
+        const U32x4 r = rand_block(p.seed, (u64)col_pos, (u64)(e4 >> 2), STREAM_WEIGHTED);
+#pragma unroll
+        for (u32 q = 0; q < 4; ++q)
+          if (e4 + q < n) s_cache[e4 + q] = sortable_key(ares_key(r.v[q], __ldg(probs + e4 + q)));
+      }
+    }
+    if (tid == 0) {
+      s_prefix = 0;
+      s_need = (u32)k;
+      s_done = 0;
+      s_count = 0;
+    }
+    u64 mask = 0;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+      s_hist[tid] = 0;
+      __syncthreads();
+      if (s_done) break;  // uniform: written before the barrier of the previous round
+      const u64 prefix = s_prefix;
+      for (u32 e = tid; e < n; e += kWideThreads) {
+        const u64 comp = ((u64)(cached ? s_cache[e] : key_of(e)) << 32) | (u64)(~e);
+        if ((comp & mask) == prefix) atomicAdd(&s_hist[(comp >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        u32 need = s_need, above = 0;
+        int bin = 255;
+        for (; bin > 0; --bin) {
+          if (above + s_hist[bin] >= need) break;
+          above += s_hist[bin];
+        }
+        s_prefix = prefix | ((u64)bin << shift);
+        if (above + s_hist[bin] == need) s_done = 1;  // the bin is taken whole: nothing below this digit matters
+        s_need = need - above;
+      }
+      mask |= (u64)255u << shift;
+      __syncthreads();
+    }
+    const u64 threshold = s_prefix;  // digits below the last decided one are zero
+    for (u32 e = tid; e < n; e += kWideThreads) {
+      const u64 comp = ((u64)(cached ? s_cache[e] : key_of(e)) << 32) | (u64)(~e);
+      if (comp >= threshold) {
+        const u32 at = atomicAdd(&s_count, 1u);
+        if (at < (u32)kWideMaxK) s_win[at] = comp;
+      }
+    }
+    __syncthreads();
+    int width = 32;
+    while (width < k) width <<= 1;
+    for (int j = k + tid; j < width; j += kWideThreads) s_win[j] = 0;  // ranks after every real composite
+    __syncthreads();
+    for (int size = 2; size <= width; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int t = tid; t < width / 2; t += kWideThreads) {
+          const int lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+          const bool descending = (lo & size) == 0;
+          const u64 a = s_win[lo], c = s_win[hi];
+          if ((a < c) == descending) {
+            s_win[lo] = c;
+            s_win[hi] = a;
+          }
+        }
+        __syncthreads();
+      }
+    }
+    for (int j = tid; j < k; j += kWideThreads) emit_weighted(p, o + j, b + (i64)(u32)(~(u32)s_win[j]), col_pos);
+  }
+}
+
 }  // namespace gsb
 
 using namespace gsb;
@@ -345,8 +468,27 @@ extern "C" int gsb_sample_weighted(gsb_ctx* ctx, void* stream_, const int64_t* i
   GSB_REQUIRE(indptr && out_indptr && S >= 0 && k >= 0 && num_cols >= 0 && (seeds || S <= num_cols),
               GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE((out_indices && out_select) || capacity == 0, GSB_ERR_INVALID_ARGUMENT);
-  GSB_REQUIRE(replace || k <= 32, GSB_ERR_UNSUPPORTED);
+  GSB_REQUIRE(replace || k <= kWideMaxK, GSB_ERR_UNSUPPORTED);
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (!replace && k > 32) {
+    int st = count_scan_launch(ctx, stream, indptr, num_cols, seeds, S, k, /*without replacement*/ 1, out_indptr);
+    if (st != GSB_OK) return st;
+    WeightedParams p{indptr, indices,    probs, num_cols,      seeds, S,     k,        replace,  (u64)seed,         out_indptr,
+                     out_indices, out_select, out_coo_col, data,  e_ids, out_data, capacity, ctx_counters(ctx), TileState{}};
+    if (S > 0) {
+      ScopedKernelTimer timer(ctx, KID_SAMPLE_WEIGHTED, stream);
+      k_sample_weighted_wide<<<(int)min(S, (i64)kNumSMs * 8), kWideThreads, 0, stream>>>(p);
+    }
+    GSB_LAUNCH_OK();
+    if (nnz_host) {
+      const i64* c;
+      st = ctx_fetch_counters(ctx, stream, CNT_ERROR, 3, &c);
+      if (st != GSB_OK) return st;
+      *nnz_host = c[CNT_NNZ];
+      if (c[CNT_ERROR] != 0) return ctx_check_device_error(ctx, stream);
+    }
+    return GSB_OK;
+  }
   const bool narrow = S < (i64)kWTileColsWide * 148 * 6;  // the wide tiles would not fill one wave
   const int grid = grid_for(S, narrow ? kWTileColsNarrow : kWTileColsWide);
   TileState ts;

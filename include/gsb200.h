@@ -203,8 +203,10 @@ GSB_API int gsb_random_walk(gsb_ctx* ctx, void* stream, const int64_t* indptr, c
  * Replaces gs::impl::CSCColSamplingProbsCUDA (src/cuda/sampling_probs.cu:23-282; dispatcher
  * gs::CSCColSamplingProbs, src/graph_ops.cc:207-221).  `probs[j]` pairs with `indices[j]` of the
  * operand.  Without replacement: A-Res (Efraimidis-Spirakis), the k entries with the largest
- * u^(1/w) win (ranked through log2(u)/w), k <= 32 like the reference (sampling_probs.cu:32,
- * GSB_ERR_UNSUPPORTED above that); columns with deg <= k are copied; output per column in
+ * u^(1/w) win (ranked through log2(u)/w).  k <= 32 is the reference's range (sampling_probs.cu:32:
+ * it aborts above); here 32 < k <= 1024 is served by a second kernel (one CTA per column, radix
+ * select of the k-th best key) with identical semantics, GSB_ERR_UNSUPPORTED above 1024;
+ * columns with deg <= k are copied; output per column in
  * descending key order; weights <= 0 rank below every positive weight.  With replacement: k
  * inverse-CDF draws over max(w, 0).  seeds == NULL samples all S columns of the operand; seeds
  * given fuses the column slice (no reference counterpart for the fused form).  Buffers, counts

@@ -30,7 +30,7 @@ def gold():
 
 
 # ---- weighted per-column sampling -------------------------------------------------------------------
-@pytest.mark.parametrize("k", [1, 2, 10, 31, 32])
+@pytest.mark.parametrize("k", [1, 2, 10, 31, 32, 33, 64, 100, 1000, 1024])
 def test_weighted_sampling_wor_matches_oracle(ops, oracle, hub_graph, k):
     """fp32 A-Res keys are built from identical IEEE operations on both sides => identical picks."""
     indptr, indices = hub_graph
@@ -95,11 +95,43 @@ def test_weighted_sampling_law(ops):
 
 
 def test_weighted_k_limit(ops, small_graph):
+    """Fan-outs above 32 (where the reference aborts) are served up to 1 024; beyond that the call is refused."""
     from graph_sampling_b200.cabi import GsbError
     indptr, indices = small_graph
     probs = np.ones(len(indices), dtype=np.float32)
-    with pytest.raises(GsbError):
-        ops.csc_col_sampling_probs(dev(indptr), dev(indices), dev(probs), 33, False)
+    with pytest.raises(GsbError) as e:
+        ops.csc_col_sampling_probs(dev(indptr), dev(indices), dev(probs), 1025, False)
+    assert e.value.status == -7
+
+
+@pytest.mark.parametrize("k", [33, 50, 700])
+def test_weighted_sampling_wide_fanout_ties_long_columns_and_seeds(ops, oracle, k):
+    """The kernel for fan-outs above 32 on what its radix select has to get right: columns whose keys tie en masse
+    (zero weights rank last, smaller position first), a column longer than its shared-memory key cache, columns at and
+    just above the fan-out, seed columns given in any order with repeats, edge data gathered along."""
+    rng = np.random.default_rng(k)
+    deg = np.array([0, 1, k - 1, k, k + 1, 2 * k, 5000, 20000, 3 * k, 6144, 6145], dtype=np.int64)
+    n = 21000
+    indptr = np.zeros(n + 1, dtype=np.int64)
+    indptr[1:len(deg) + 1] = np.cumsum(deg)
+    indptr[len(deg) + 1:] = indptr[len(deg)]
+    indices = np.concatenate([np.sort(rng.choice(n, size=int(d), replace=False)) for d in deg]).astype(np.int64)
+    probs = rng.random(len(indices)).astype(np.float32)
+    probs[indptr[5]:indptr[6]] = 0.0                      # every key of this column ties
+    zero = rng.random(len(indices)) < 0.5
+    zero[:indptr[6]] = False
+    zero[indptr[7]:] = False
+    probs[zero] = 0.0                                     # half of the 5 000-entry column ties at the bottom
+    probs[indptr[8]:indptr[9]] = 0.25                     # equal weights, distinct draws
+    seeds = np.array([7, 5, 6, 0, 4, 3, 2, 1, 8, 7, 9, 10, 6], dtype=np.int64)
+    data = rng.random(len(indices)).astype(np.float32)
+    for sd in (None, seeds):
+        want = oracle.sample_weighted(indptr, indices, probs, sd, k, False, seed=77, with_coo=True)
+        got = ops.csc_col_sampling_probs(dev(indptr), dev(indices), dev(probs), k, False, with_coo=True, seed=77,
+                                         column_ids=None if sd is None else dev(sd), data=dev(data))
+        for w, g in zip(want, got[:4]):
+            assert np.array_equal(w, host(g))
+        assert np.array_equal(host(got[4]), data[want[3]])
 
 
 # ---- list sampling ------------------------------------------------------------------------------------
