@@ -62,7 +62,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batches-per-step", type=int, default=1000,
                     help="minibatches every GPU processes per step (the configuration has 1,000)")
-    ap.add_argument("--relabel-path", default=None, choices=["auto", "hash", "direct"],
+    ap.add_argument("--relabel-path", default=None, choices=["auto", "hash", "direct", "partition"],
                     help="table form of unique + relabel (default: the library's automatic choice)")
     ap.add_argument("--lanes", type=int, default=3,
                     help="CUDA streams (each with its own library context and output arena) that take the calls of a "
@@ -395,7 +395,7 @@ def run_ours(args):
     ctx = ctxs[0]
     for c in ctxs:
         if args.relabel_path:
-            c.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2}[args.relabel_path])
+            c.set_option("relabel_path", {"auto": 0, "hash": 1, "direct": 2, "partition": 3}[args.relabel_path])
         if args.host_waits and lanes > 1 and not args.spin_wait:
             c.set_option("blocking_wait", 1)    # a lane that waits for its hop sleeps; the other lanes keep the GPU fed
     group = args.group

@@ -26,8 +26,9 @@ namespace gsb {
 
 
 // One CTA: per-batch item offsets and / or table regions (exclusive scan over the G region sizes).
-// bound_k < 0: regions sized from the batches' actual item counts (needs indices_ptr); bound_k >= 0:
-// regions sized from the upper bound seeds * (1 + bound_k), which is known before sampling.
+// bound_k == -1: regions sized from the batches' actual item counts (needs indices_ptr); bound_k >= 0:
+// regions sized from the upper bound seeds * (1 + bound_k), which is known before sampling; bound_k == -2: region_off
+// receives the first BUCKET of every minibatch instead (partition_relabel.cu), slot_capacity bounds the bucket count.
 // what & 1: write region_off; what & 2: write item_off.
 // seeds_bound / edges_bound: what the caller sized grids, scratch and outputs for.  Device-side totals above them
 // record GSB_ERR_CAPACITY and set CNT_ABORT, which makes the kernels that follow in the call return at once.
@@ -48,8 +49,10 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
     i64 size = 0;
     if (b < L.G) {
       if (what & 2) L.item_off[b] = L.seeds_ptr[b] + L.indices_ptr[b];
+      const i64 items = L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - L.seeds_ptr[b] - L.indices_ptr[b];
       if (bound_k >= 0) size = region_size_for((L.seeds_ptr[b + 1] - L.seeds_ptr[b]) * (1 + bound_k));
-      else size = region_size_for(L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - L.seeds_ptr[b] - L.indices_ptr[b]);
+      else if (bound_k == -2) size = (items + kBucketTarget - 1) / kBucketTarget;  // buckets of the partitioned form
+      else size = region_size_for(items);
     }
     i64 total;
     const i64 excl = block_exclusive_scan<kBThreads>(size, s_scan, &total);
@@ -654,6 +657,22 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
     T.seeds_distinct = (flags & GSB_SEEDS_DISTINCT) ? 1 : 0;
     return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr,
                                         out_relabeled);
+  }
+  if (path == 3) {
+    // partitioned form: shared-memory tables per bucket of items, then ranking by bit vectors
+    int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, G), &ws);
+    if (st != GSB_OK) return st;
+    L.item_off = (i64*)ws;
+    L.region_off = (i64*)((char*)ws + off_bytes);
+    L.slots = nullptr;
+    L.slot_capacity = partition_bucket_capacity(n_cap, G);
+    {
+      ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+      k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -2, 3, seeds_bound, edges_bound);
+    }
+    GSB_LAUNCH_OK();
+    return partition_unique_relabel(ctx, stream, L, n_cap, (char*)ws + 2 * off_bytes, out_unique, out_unique_ptr,
+                                    out_relabeled);
   }
   const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;

@@ -162,6 +162,16 @@ constexpr uint32_t kEdgeKeyBit = 0x80000000u;
 // L.item_off must be valid (k_batch_layout); n_cap / e_cap bound the items / edges of the call.
 int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchLayout& L, const DirectTables& T,
                                  i64 n_cap, i64 e_cap, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
+// Partitioned form of the batched unique + relabel (defined in partition_relabel.cu): shared-memory tables per bucket of
+// items, bit-vector ranking, no fix-up pass.  L carries seeds / seeds_ptr / indices / indices_ptr / G; item_off and
+// region_off (first bucket of every minibatch) must be filled by k_batch_layout with bound_k == -2; `ws` is scratch of
+// partition_workspace_bytes(n_cap, G) bytes.
+size_t partition_workspace_bytes(i64 n_cap, i64 G);
+i64 partition_bucket_capacity(i64 n_cap, i64 G);
+int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, void* ws, i64* out_unique,
+                             i64* out_unique_ptr, i64* out_relabeled);
+constexpr int kBucketTarget = 4096;  // mean items per bucket
+
 struct CompactOut {
   i64* unique;      // all frontiers back to back
   i64* unique_ptr;  // [G + 1]

@@ -81,7 +81,11 @@ enum KernelId {
   KID_LIST_SAMPLE,
   KID_SORT,
   KID_FORMAT,
-  KID_SAGE_SAMPLE_INSERT,
+  KID_PART_COUNT,
+  KID_PART_SCATTER,
+  KID_PART_RESOLVE,
+  KID_FIRST_BITS,
+  KID_RANK_EMIT,
   KID_OTHER,
   KID_NUM
 };

@@ -323,7 +323,7 @@ int gsb_ctx_set_option(gsb_ctx* ctx, int option, int64_t value) {
       if (value < 0) return GSB_ERR_INVALID_ARGUMENT;
       break;
     case GSB_OPT_RELABEL_PATH:
-      if (value < 0 || value > 2) return GSB_ERR_INVALID_ARGUMENT;
+      if (value < 0 || value > 3) return GSB_ERR_INVALID_ARGUMENT;
       break;
     case GSB_OPT_BLOCKING_WAIT:
       if (value < 0 || value > 1) return GSB_ERR_INVALID_ARGUMENT;
@@ -389,8 +389,8 @@ const char* gsb_profile_kernel_name(int kid) {
   static const char* names[gsb::KID_NUM] = {
       "count_scan",     "slice_fill",   "sample_uniform", "sample_keepdim", "sample_weighted", "table_clear",
       "table_insert",   "first_compact", "relabel",       "random_walk",    "sddmm_dot",       "sddmm_generic",
-      "segment",        "row_filter",   "list_sample",    "sort",           "format",          "sage_sample_insert",
-      "other"};
+      "segment",        "row_filter",   "list_sample",    "sort",           "format",          "partition_count",
+      "partition_scatter", "bucket_resolve", "first_bits",  "rank_emit",      "other"};
   return (kid >= 0 && kid < gsb::KID_NUM) ? names[kid] : "";
 }
 

@@ -73,7 +73,7 @@ class Context:
     OPTIONS = {"max_polls": 0, "table_slots": 1, "relabel_path": 2, "direct_table_budget": 3, "blocking_wait": 4}
 
     def set_option(self, name, value):
-        """gsb_ctx_set_option by name: max_polls, table_slots, relabel_path (0 auto, 1 hash, 2 direct),
+        """gsb_ctx_set_option by name: max_polls, table_slots, relabel_path (0 auto, 1 hash regions, 2 direct-address tables, 3 partitioned),
         direct_table_budget (bytes), blocking_wait (0 / 1)."""
         self.check(self.lib.gsb_ctx_set_option(self.handle, c_int(self.OPTIONS[name]), c_i64(int(value))),
                    "gsb_ctx_set_option")

@@ -21,11 +21,12 @@ def ops():
     return _ops
 
 
-@pytest.fixture(params=["hash", "direct"])
+@pytest.fixture(params=["hash", "direct", "partition"])
 def relabel_path(request, ops):
-    """Runs a test once with hash-table regions and once with direct-address tables."""
+    """Runs a test with hash-table regions, with direct-address tables and with the partitioned form (shared-memory
+    tables per bucket of items)."""
     ctx = ops.default_context()
-    ctx.set_option("relabel_path", 1 if request.param == "hash" else 2)
+    ctx.set_option("relabel_path", {"hash": 1, "direct": 2, "partition": 3}[request.param])
     yield request.param
     ctx.set_option("relabel_path", 0)
 

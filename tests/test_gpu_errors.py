@@ -224,9 +224,9 @@ def test_sage_hop_reports_bad_seed_and_survives(ops, cfg1_graph):
     seeds = np.arange(64, dtype=np.int64)
     seeds[10] = n + 3
     ptr = dev(np.array([0, 32, 64], dtype=np.int64))
-    for path in ("hash", "direct"):
+    for path in ("hash", "direct", "partition"):
         ctx = ops.default_context()
-        ctx.set_option("relabel_path", 1 if path == "hash" else 2)
+        ctx.set_option("relabel_path", {"hash": 1, "direct": 2, "partition": 3}[path])
         try:
             with pytest.raises(GsbError) as e:
                 ops.sage_sample_batches(dev(indptr), dev(indices), dev(seeds), ptr, [5, 3], seed=1)
@@ -283,7 +283,7 @@ def test_batched_relabel_with_sizes_beyond_the_callers_bound_writes_nothing(ops)
     ptr = dev(np.array([0, 2, 4], dtype=np.int64))
     indices = dev(np.arange(100, dtype=np.int64))
     iptr = dev(np.array([0, 50, 100], dtype=np.int64))
-    for path in (1, 2):
+    for path in (1, 2, 3):
         ctx.set_option("relabel_path", path)
         try:
             uniq = torch.full((4 + 10 + 8,), -5, dtype=torch.int64, device="cuda")

@@ -53,7 +53,7 @@ def test_products_scale_group_matches_oracle_bit_for_bit(ops, oracle, products):
     ptr0 = dev((np.arange(G + 1) * 1024).astype(np.int64))
     ctx = ops.default_context()
     results = {}
-    for path in (1, 2):
+    for path in (1, 2, 3):
         ctx.set_option("relabel_path", path)
         try:
             results[path] = ops.sage_sample_batches(indptr, indices, batches.reshape(-1).cuda(), ptr0, FANOUTS, seed=123,
@@ -61,9 +61,12 @@ def test_products_scale_group_matches_oracle_bit_for_bit(ops, oracle, products):
         finally:
             ctx.set_option("relabel_path", 0)
     for hop in range(3):
-        a, b = results[1][hop], results[2][hop]
-        for key in ("sub_indptr", "indices", "select_index", "relabeled", "indices_ptr", "frontier", "frontier_ptr"):
-            assert torch.equal(a[key], b[key]), (hop, key)
+        a = results[1][hop]
+        for other in (2, 3):
+            b = results[other][hop]
+            for key in ("sub_indptr", "indices", "select_index", "relabeled", "indices_ptr", "frontier",
+                        "frontier_ptr"):
+                assert torch.equal(a[key], b[key]), (hop, other, key)
         h = results[2][hop]
         rep = validate.check_sampled_block(indptr, indices, h["seeds"], h["sub_indptr"], h["indices"], h["select_index"],
                                            FANOUTS[hop])
