@@ -170,7 +170,7 @@ size_t partition_workspace_bytes(i64 n_cap, i64 G);
 i64 partition_bucket_capacity(i64 n_cap, i64 G);
 int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, void* ws, i64* out_unique,
                              i64* out_unique_ptr, i64* out_relabeled);
-constexpr int kBucketTarget = 4096;  // mean items per bucket
+constexpr int kBucketTarget = 2048;  // mean items per bucket
 
 struct CompactOut {
   i64* unique;      // all frontiers back to back

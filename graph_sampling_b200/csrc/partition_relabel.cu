@@ -1,29 +1,33 @@
 // Batched unique + relabel by partitioning: first occurrences are found in SHARED-MEMORY hash tables.
 //
 // The hash-region form (batch_relabel.cu) gives every minibatch a table region in global memory and pays two random
-// L2 / DRAM accesses per item in its insert pass and one or two more in its compaction.  Measured on a B200, 64-bit
-// atomics on a CTA's own shared memory run at 4 G/s per SM (620 G/s on the whole GPU), ten times what the L2 path
-// sustains (64 G items/s), while atomics on a cluster's distributed shared memory reach only 29 - 33 G/s GPU-wide.
-// So the items of a minibatch are first PARTITIONED by a hash of their id into buckets small enough for one CTA's
-// shared memory, and every bucket is resolved by one CTA on its own:
+// L2 / DRAM accesses per item in its insert pass and one or two more in its compaction, whose look-back chain over
+// tens of thousands of tiles is what that kernel mostly waits for.  Measured on a B200, 64-bit atomics on a CTA's own
+// shared memory run at 4 G/s per SM (620 G/s on the whole GPU), ten times what the L2 path sustains (64 G items/s),
+// while atomics on a cluster's distributed shared memory reach only 29 - 33 G/s GPU-wide.  So the items of a
+// minibatch are first PARTITIONED by a hash of their id into buckets small enough for one CTA's shared memory, and
+// every bucket is resolved by one CTA on its own:
 //
 //   layout    per minibatch: item offset, number of buckets (items / kBucketTarget, rounded up), first bucket;
 //   count     a CTA takes 4 096 consecutive items, counts them per bucket in shared memory, adds its counts to the
 //             bucket sizes (one global atomic per CTA and bucket);
 //   scan      bucket sizes -> bucket starts (one CTA);
-//   scatter   the same tiles again: a CTA reserves, per bucket, a range for its items with one global atomic and
-//             writes (id << 32 | position inside the minibatch) there — the order inside a bucket does not matter,
-//             the table keeps the smallest position per id;
-//   resolve   one CTA per bucket: position-min insert of the bucket's items into a shared-memory table (load <= 0.5),
-//             then every item looks up the first position of its id and writes it to ref[item] — the only scattered
-//             accesses to global memory of the whole sequence, 4 bytes per item into the minibatch's own window;
-//             a bucket with more items than the shared-memory table is sized for (many repeats of a few hub ids, or
-//             an unlucky hash) uses a table in global memory of its own instead, so nothing depends on luck;
+//   scatter   tiles of 2 048 items: sorted by bucket in shared memory, a range reserved per bucket with one global
+//             atomic, whole runs of (id << 32 | position inside the minibatch) copied out — the order inside a bucket
+//             does not matter, the table keeps the smallest position per id;
+//   resolve   one CTA per bucket: the bucket's items stay in registers; position-min insert into a shared-memory
+//             table (load <= 0.5), then every item reads the first position of its id from the slot it ended in and
+//             writes it to ref[item] — the only scattered accesses to global memory of the whole sequence, 4 bytes
+//             per item into the minibatch's own window; a bucket with more items than the shared-memory table is sized
+//             for (many repeats of a few hub ids, or an unlucky hash) uses a table in global memory of its own
+//             instead, so nothing depends on luck;
 //   rank      bit vector of the first occurrences (ref[item] == own position), prefix counts per 32 items, then one
 //             pass that writes the frontier and every neighbour's position in it (see "ranking by bit vectors").
 //
 // Every pass over the items is coalesced except the 4-byte scatter of `ref` and the 8-byte rank look-ups, both inside
-// the minibatch's own window.  Results are identical to the other
+// the minibatch's own window.  All of these kernels are bound by instruction issue, not by memory, so their common
+// case — a tile or warp whose items lie in ONE minibatch — runs on 32-bit positions with the minibatch's parameters
+// in registers; a tile that straddles minibatches takes a general path per item.  Results are identical to the other
 // forms: first-occurrence order is defined by positions, not by the order in which anything is processed.
 #include "batch_table.cuh"
 #include "common.cuh"
@@ -31,103 +35,142 @@
 
 namespace gsb {
 
+typedef uint32_t u32;
+
 constexpr int kPartThreads = 256;
 constexpr int kPartPerThread = 16;
-constexpr int kPartTile = kPartThreads * kPartPerThread;  // items per CTA of the count / scatter passes
+constexpr int kPartTile = kPartThreads * kPartPerThread;        // items per CTA of the count pass
 constexpr int kScatterPerThread = 8;
 constexpr int kScatterTile = kPartThreads * kScatterPerThread;  // items per CTA of the scatter pass
-constexpr int kWindow = 256;                              // buckets a tile counts in shared memory
-constexpr uint32_t kNoBucket = 0xFFFFFFFFu, kBadId = 0xFFFFFFFEu;
-constexpr int kResolveThreads = 512;
-constexpr int kResolvePer = 12;                           // items per thread of a bucket that fits shared memory
-constexpr int kBucketSlots = 12288;                       // shared-memory table of a resolve CTA: 96 KB
-constexpr int kBucketSmemItems = kBucketSlots / 2 - 16;   // largest bucket that is sure to fit it at load <= 0.5
+constexpr int kWindow = 256;                                    // buckets a tile counts in shared memory
+constexpr u32 kNoBucket = 0xFFFFFFFFu;
+constexpr int kResolveThreads = 256;
+constexpr int kResolvePer = 12;                          // items per thread of a bucket that fits shared memory
+constexpr int kBucketSlots = 6144;                       // shared-memory table of a resolve CTA: 48 KB
+constexpr int kBucketSmemItems = kBucketSlots / 2 - 16;  // largest bucket that is sure to fit it at load <= 0.5
 
 struct PartLayout {
-  BatchLayout L;            // region_off holds the first bucket of every minibatch ([G + 1], last = bucket count)
-  uint32_t* bucket_count;   // [buckets + 1]
-  uint32_t* bucket_start;   // [buckets + 1]
-  uint32_t* bucket_cursor;  // [buckets]
-  u64* bucketed;            // [items]   id << 32 | position inside the minibatch, grouped by bucket
-  uint32_t* ref;            // [items]   position inside the minibatch of the first occurrence of the item's id
-  u64* spill;               // tables of the buckets that do not fit shared memory: 2 x start + 32 x bucket
+  BatchLayout L;       // region_off holds the first bucket of every minibatch ([G + 1], last = bucket count)
+  u32* bucket_count;   // [buckets + 1]
+  u32* bucket_start;   // [buckets + 1]
+  u32* bucket_cursor;  // [buckets]
+  u64* bucketed;       // [items]   id << 32 | position inside the minibatch, grouped by bucket
+  u32* ref;            // [items]   position inside the minibatch of the first occurrence of the item's id
+  u64* spill;          // tables of the buckets that do not fit shared memory: 2 x start + 32 x bucket
 };
 
-__device__ __forceinline__ uint32_t bucket_hash(i64 node) {
-  return (uint32_t)(((u64)node * 0x9E3779B97F4A7C15ull) >> 32);
-}
-// independent of bucket_hash: the ids of one bucket must spread over the whole table
-__device__ __forceinline__ uint32_t slot_hash(i64 node) {
-  uint32_t x = (uint32_t)node;
+// Ids are below 2^32 - 1 here (valid_id).  Bucket: Fibonacci hashing, the high bits of id x odd constant, scaled to
+// the bucket count by a multiply-high.  Slot: a second constant and one xor-shift round, so the ids of one bucket —
+// which share the high bits of the first product — still spread over the whole table.
+__device__ __forceinline__ u32 bucket_of_id(u32 id, u32 parts) { return __umulhi(id * 0x9E3779B1u, parts); }
+__device__ __forceinline__ u32 slot_of_id(u32 id, u32 size) {
+  u32 x = id * 0x85EBCA6Bu;
+  x ^= x >> 13;
+  x *= 0xC2B2AE35u;
   x ^= x >> 16;
-  x *= 0x7feb352du;
-  x ^= x >> 15;
-  x *= 0x846ca68bu;
-  x ^= x >> 16;
-  return x;
+  return __umulhi(x, size);
 }
 
+// Parameters of the minibatch that a tile starts in, reduced to what the per-item work needs.
+struct TileBatch {
+  const i64* seeds;  // seeds[lc] for lc < ns
+  const i64* edges;  // edges[lc] for lc >= ns (pointer already shifted by -ns)
+  u32 ns;            // seeds of the minibatch
+  u32 items;         // items of the minibatch
+  u32 bucket0;       // its first bucket
+  u32 parts;         // its bucket count
+};
+
+__device__ __forceinline__ TileBatch tile_batch(const BatchLayout& L, const BatchUniform& u) {
+  TileBatch t;
+  t.seeds = L.seeds + u.seeds_begin;
+  t.edges = L.indices + u.edges_begin - u.num_seeds;
+  t.ns = (u32)u.num_seeds;
+  t.items = (u32)(u.next_begin - u.begin);
+  const i64 b0 = __ldg(L.region_off + u.batch);
+  t.bucket0 = (u32)b0;
+  t.parts = (u32)(__ldg(L.region_off + u.batch + 1) - b0);
+  return t;
+}
+
+__device__ __forceinline__ i64 tile_item(const TileBatch& t, u32 lc) {
+  return __ldg(lc < t.ns ? t.seeds + lc : t.edges + lc);
+}
+
+// Minibatch of item `base` (the first item of a warp or CTA): one thread of the CTA searches for the minibatch of
+// the CTA's first item, everybody walks forward from there (almost always zero steps) — a binary search per warp
+// costs more instructions than the warp's items in the streaming kernels below.  Contains a barrier.
+__device__ __forceinline__ i64 batch_from_cta(const BatchLayout& L, i64 cta_base, i64 base, i64* s_slot) {
+  if (threadIdx.x == 0) *s_slot = batch_of(L.item_off, L.G, cta_base);
+  __syncthreads();
+  i64 b = *s_slot;
+  while (base >= __ldg(L.item_off + b + 1)) ++b;  // base < item_off[G]
+  return b;
+}
+
+// General path: item g of the call, wherever it lies.
 struct Located {
-  i64 batch, begin;     // minibatch and its first item
   i64 node;
-  uint32_t lc;          // position inside the minibatch (seeds first)
-  uint32_t bucket;      // global bucket number
+  u32 lc;      // position inside its minibatch (seeds first)
+  u32 bucket;  // global bucket number
 };
-
-// Item g of the call; `u` describes the minibatch of the tile's first item and serves every item inside it.
-__device__ __forceinline__ Located locate(const BatchLayout& L, const BatchUniform& u, i64 g) {
-  BatchUniform v = u;
-  if (g >= u.next_begin) v = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, g));
+__device__ __forceinline__ Located locate(const BatchLayout& L, i64 g) {
+  const BatchUniform v = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, g));
+  const TileBatch t = tile_batch(L, v);
   Located r;
-  r.batch = v.batch;
-  r.begin = v.begin;
-  const i64 lc = g - v.begin;
-  r.lc = (uint32_t)lc;
-  r.node = lc < v.num_seeds ? __ldg(L.seeds + v.seeds_begin + lc) : __ldg(L.indices + v.edges_begin + (lc - v.num_seeds));
-  const i64 b0 = __ldg(L.region_off + v.batch);
-  const u64 parts = (u64)(__ldg(L.region_off + v.batch + 1) - b0);
-  r.bucket = (uint32_t)(b0 + (i64)(((u64)bucket_hash(r.node) * parts) >> 32));
+  r.lc = (u32)(g - v.begin);
+  r.node = tile_item(t, r.lc);
+  r.bucket = t.bucket0 + bucket_of_id((u32)r.node, t.parts);
   return r;
 }
 
 __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n_bound, i64* counters) {
-  __shared__ uint32_t s_cnt[kWindow];
+  __shared__ u32 s_cnt[kWindow];
   if (counters[CNT_ABORT] != 0) return;
   const BatchLayout& L = P.L;
   const i64 n = min(L.item_off[L.G], n_bound);
   const i64 tile_base = (i64)blockIdx.x * kPartTile;
   if (tile_base >= n) return;
+  __shared__ i64 s_b;
   for (int i = threadIdx.x; i < kWindow; i += kPartThreads) s_cnt[i] = 0;
-  const BatchUniform u = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, tile_base));
-  const uint32_t win0 = (uint32_t)__ldg(L.region_off + u.batch);
-  // all ids of the thread first (independent loads), the shared-memory atomics afterwards
-  uint32_t bucket[kPartPerThread];
+  const BatchUniform u = load_batch<false>(L, L.item_off, batch_from_cta(L, tile_base, tile_base, &s_b));
+  const TileBatch t = tile_batch(L, u);
+  const u32 lc0 = (u32)(tile_base - u.begin);
+  const u32 here = (u32)min((i64)kPartTile, n - tile_base);  // items of this tile
+  const bool uniform = (u64)lc0 + here <= (u64)t.items && t.parts <= (u32)kWindow;
+  if (uniform) {
+    // ids first (independent loads), then the shared-memory atomics
+    i64 node[kPartPerThread];
 #pragma unroll
-  for (int q = 0; q < kPartPerThread; ++q) {
-    const i64 g = tile_base + q * kPartThreads + threadIdx.x;
-    bucket[q] = kNoBucket;
-    if (g < n) {
-      const Located it = locate(L, u, g);
-      bucket[q] = valid_id(it.node) ? it.bucket : kBadId;
+    for (int q = 0; q < kPartPerThread; ++q) {
+      const u32 i = q * kPartThreads + threadIdx.x;
+      node[q] = i < here ? tile_item(t, lc0 + i) : 0;
     }
-  }
-  __syncthreads();
 #pragma unroll
-  for (int q = 0; q < kPartPerThread; ++q) {
-    if (bucket[q] == kNoBucket) continue;
-    const i64 g = tile_base + q * kPartThreads + threadIdx.x;
-    if (bucket[q] == kBadId) {  // never bucketed: marked for the ranking passes
-      raise_error(counters, GSB_ERR_INDEX_RANGE, g);
-      P.ref[g] = 0xFFFFFFFFu;
+    for (int q = 0; q < kPartPerThread; ++q) {
+      const u32 i = q * kPartThreads + threadIdx.x;
+      if (i >= here) continue;
+      if (!valid_id(node[q])) {  // never bucketed: marked for the ranking passes
+        raise_error(counters, GSB_ERR_INDEX_RANGE, tile_base + i);
+        P.ref[tile_base + i] = 0xFFFFFFFFu;
+        continue;
+      }
+      atomicAdd(&s_cnt[bucket_of_id((u32)node[q], t.parts)], 1u);
+    }
+    __syncthreads();
+    for (u32 i = threadIdx.x; i < t.parts; i += kPartThreads)
+      if (s_cnt[i] != 0) atomicAdd(P.bucket_count + t.bucket0 + i, s_cnt[i]);
+    return;
+  }
+  for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
+    const Located it = locate(L, tile_base + i);
+    if (!valid_id(it.node)) {
+      raise_error(counters, GSB_ERR_INDEX_RANGE, tile_base + i);
+      P.ref[tile_base + i] = 0xFFFFFFFFu;
       continue;
     }
-    const uint32_t w = bucket[q] - win0;
-    if (w < (uint32_t)kWindow) atomicAdd(&s_cnt[w], 1u);
-    else atomicAdd(P.bucket_count + bucket[q], 1u);
+    atomicAdd(P.bucket_count + it.bucket, 1u);
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < kWindow; i += kPartThreads)
-    if (s_cnt[i] != 0) atomicAdd(P.bucket_count + win0 + i, s_cnt[i]);
 }
 
 // bucket sizes -> bucket starts, cursors cleared (one CTA of 1 024 threads, 8 buckets per thread and round)
@@ -141,7 +184,7 @@ __global__ void __launch_bounds__(1024) k_part_scan(PartLayout P, i64* counters)
   constexpr int kPer = 8;
   for (i64 base = 0; base < buckets; base += 1024 * kPer) {
     const i64 first = base + (i64)threadIdx.x * kPer;
-    uint32_t c[kPer];
+    u32 c[kPer];
     i64 sum = 0;
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
@@ -153,7 +196,7 @@ __global__ void __launch_bounds__(1024) k_part_scan(PartLayout P, i64* counters)
 #pragma unroll
     for (int j = 0; j < kPer; ++j) {
       if (first + j < buckets) {
-        P.bucket_start[first + j] = (uint32_t)run;
+        P.bucket_start[first + j] = (u32)run;
         P.bucket_cursor[first + j] = 0u;
       }
       run += c[j];
@@ -162,7 +205,7 @@ __global__ void __launch_bounds__(1024) k_part_scan(PartLayout P, i64* counters)
     if (threadIdx.x == 0) s_carry += total;
     __syncthreads();
   }
-  if (threadIdx.x == 0) P.bucket_start[buckets] = (uint32_t)s_carry;
+  if (threadIdx.x == 0) P.bucket_start[buckets] = (u32)s_carry;
 }
 
 // A tile's items are first sorted by bucket in shared memory (their rank inside the tile's share of a bucket is what
@@ -170,181 +213,157 @@ __global__ void __launch_bounds__(1024) k_part_scan(PartLayout P, i64* counters)
 __global__ void __launch_bounds__(kPartThreads) k_part_scatter(PartLayout P, i64 n_bound, i64* counters) {
   __shared__ u64 s_stage[kScatterTile];
   __shared__ uint16_t s_which[kScatterTile];
-  __shared__ uint32_t s_cnt[kWindow];
-  __shared__ uint32_t s_off[kWindow];
-  __shared__ uint32_t s_base[kWindow];
+  __shared__ u32 s_cnt[kWindow];
+  __shared__ u32 s_off[kWindow];
+  __shared__ u32 s_base[kWindow];
   __shared__ i64 s_scan[33];
-  __shared__ uint32_t s_total;
   static_assert(kWindow == kPartThreads, "one window entry per thread in the scan");
   if (counters[CNT_ABORT] != 0) return;
   const BatchLayout& L = P.L;
   const i64 n = min(L.item_off[L.G], n_bound);
   const i64 tile_base = (i64)blockIdx.x * kScatterTile;
   if (tile_base >= n) return;
+  __shared__ i64 s_b;
   s_cnt[threadIdx.x] = 0;
-  const BatchUniform u = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, tile_base));
-  const uint32_t win0 = (uint32_t)__ldg(L.region_off + u.batch);
-  u64 word[kScatterPerThread];
-  uint32_t bucket[kScatterPerThread];
+  const BatchUniform u = load_batch<false>(L, L.item_off, batch_from_cta(L, tile_base, tile_base, &s_b));
+  const TileBatch t = tile_batch(L, u);
+  const u32 lc0 = (u32)(tile_base - u.begin);
+  const u32 here = (u32)min((i64)kScatterTile, n - tile_base);
+  const bool uniform = (u64)lc0 + here <= (u64)t.items && t.parts <= (u32)kWindow;
+  if (!uniform) {  // a tile over several minibatches: every item straight to its place
+    for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
+      const Located it = locate(L, tile_base + i);
+      if (!valid_id(it.node)) continue;  // reported by the counting pass
+      P.bucketed[__ldg(P.bucket_start + it.bucket) + atomicAdd(P.bucket_cursor + it.bucket, 1u)] =
+          ((u64)it.node << 32) | (u64)it.lc;
+    }
+    return;
+  }
+  i64 node[kScatterPerThread];
 #pragma unroll
   for (int q = 0; q < kScatterPerThread; ++q) {
-    const i64 g = tile_base + q * kPartThreads + threadIdx.x;
-    bucket[q] = kNoBucket;
-    word[q] = 0;
-    if (g < n) {
-      const Located it = locate(L, u, g);
-      if (valid_id(it.node)) {  // the others were reported by the counting pass
-        bucket[q] = it.bucket;
-        word[q] = ((u64)it.node << 32) | (u64)it.lc;
-      }
-    }
+    const u32 i = q * kPartThreads + threadIdx.x;
+    node[q] = i < here ? tile_item(t, lc0 + i) : -1;
   }
   __syncthreads();
-  uint32_t rank[kScatterPerThread];
+  u32 where[kScatterPerThread];  // bucket (inside the minibatch) << 16 | rank inside the tile's share of it
 #pragma unroll
   for (int q = 0; q < kScatterPerThread; ++q) {
-    rank[q] = 0;
-    if (bucket[q] == kNoBucket) continue;
-    const uint32_t w = bucket[q] - win0;
-    if (w < (uint32_t)kWindow) {
-      rank[q] = atomicAdd(&s_cnt[w], 1u);
-    } else {  // outside the tile's window of buckets (a tile over many small minibatches): straight to its place
-      P.bucketed[__ldg(P.bucket_start + bucket[q]) + atomicAdd(P.bucket_cursor + bucket[q], 1u)] = word[q];
-      bucket[q] = kNoBucket;
-    }
+    where[q] = kNoBucket;
+    if (!valid_id(node[q])) continue;
+    const u32 w = bucket_of_id((u32)node[q], t.parts);
+    where[q] = (w << 16) | atomicAdd(&s_cnt[w], 1u);  // at most 2 048 items per tile: the rank fits 16 bits
   }
   __syncthreads();
   {
-    const uint32_t c = s_cnt[threadIdx.x];
+    const u32 c = s_cnt[threadIdx.x];
     i64 total;
-    s_off[threadIdx.x] = (uint32_t)block_exclusive_scan<kPartThreads>((i64)c, s_scan, &total);
+    s_off[threadIdx.x] = (u32)block_exclusive_scan<kPartThreads>((i64)c, s_scan, &total);
     if (c != 0)
-      s_base[threadIdx.x] = __ldg(P.bucket_start + win0 + threadIdx.x) + atomicAdd(P.bucket_cursor + win0 + threadIdx.x, c);
-    if (threadIdx.x == 0) s_total = (uint32_t)total;
+      s_base[threadIdx.x] = __ldg(P.bucket_start + t.bucket0 + threadIdx.x) +
+                            atomicAdd(P.bucket_cursor + t.bucket0 + threadIdx.x, c);
   }
   __syncthreads();
-  const uint32_t staged = s_total;
 #pragma unroll
   for (int q = 0; q < kScatterPerThread; ++q) {
-    if (bucket[q] == kNoBucket) continue;
-    const uint32_t w = bucket[q] - win0;
-    const uint32_t at = s_off[w] + rank[q];
-    s_stage[at] = word[q];
+    if (where[q] == kNoBucket) continue;
+    const u32 w = where[q] >> 16;
+    const u32 at = s_off[w] + (where[q] & 0xFFFFu);
+    s_stage[at] = ((u64)node[q] << 32) | (u64)(lc0 + q * kPartThreads + threadIdx.x);
     s_which[at] = (uint16_t)w;
   }
   __syncthreads();
-  for (uint32_t i = threadIdx.x; i < staged; i += kPartThreads) {
-    const uint32_t w = s_which[i];
+  const u32 staged = s_off[kWindow - 1] + s_cnt[kWindow - 1];
+  for (u32 i = threadIdx.x; i < staged; i += kPartThreads) {
+    const u32 w = s_which[i];
     P.bucketed[s_base[w] + (i - s_off[w])] = s_stage[i];
   }
 }
 
 // ---- one CTA per bucket ---------------------------------------------------------------------------------------
-// Generic pointers: the table is the CTA's shared memory or, for an oversized bucket, its own range of `spill`.
-__device__ __forceinline__ bool table_insert_min(u64* table, uint32_t size, uint32_t h, u64 mine) {
-  const u64 id = mine >> 32;
-  for (uint32_t probe = 0; probe < size; ++probe) {
+// Position-min insert; returns the slot the id lives in.  `table` may be shared or global memory.
+__device__ __forceinline__ u32 table_insert_min(u64* table, u32 size, u32 h, u64 mine) {
+  const u32 id = (u32)(mine >> 32);
+  for (u32 probe = 0; probe < size; ++probe) {
     u64 w = *(volatile u64*)(table + h);
     if (w == kEmptyWord) {
       const u64 old = atomicCAS(table + h, kEmptyWord, mine);
-      if (old == kEmptyWord) return true;
+      if (old == kEmptyWord) return h;
       w = old;
     }
-    if ((w >> 32) == id) {
+    if ((u32)(w >> 32) == id) {
       if (w > mine) atomicMin(table + h, mine);
-      return true;
+      return h;
     }
     h = h + 1 == size ? 0 : h + 1;
   }
-  return false;
+  return 0;  // cannot happen: the table has more slots than the bucket has items
 }
 
-__device__ __forceinline__ uint32_t table_first_position(const u64* table, uint32_t size, uint32_t h, u64 id) {
-  for (uint32_t probe = 0; probe < size; ++probe) {
-    const u64 w = table[h];
-    if ((w >> 32) == id) return (uint32_t)w;
-    if (w == kEmptyWord) break;
-    h = h + 1 == size ? 0 : h + 1;
-  }
-  return 0xFFFFFFFFu;
-}
-
-// Shared-memory table: the same two operations with the address space known to the compiler.
-__device__ __forceinline__ void smem_insert_min(u64* table, uint32_t size, uint32_t h, u64 mine) {
-  const u64 id = mine >> 32;
-  for (uint32_t probe = 0; probe < size; ++probe) {
-    u64 w = *(volatile u64*)(table + h);
-    if (w == kEmptyWord) {
-      const u64 old = atomicCAS(table + h, kEmptyWord, mine);
-      if (old == kEmptyWord) return;
-      w = old;
-    }
-    if ((w >> 32) == id) {
-      if (w > mine) atomicMin(table + h, mine);
-      return;
-    }
-    h = h + 1 == size ? 0 : h + 1;
-  }
-}
-
-__global__ void __launch_bounds__(kResolveThreads, 2) k_part_resolve(PartLayout P, i64* counters) {
+__global__ void __launch_bounds__(kResolveThreads, 4) k_part_resolve(PartLayout P, i64* counters) {
   extern __shared__ __align__(16) u64 s_table[];
   static_assert(kResolvePer * kResolveThreads >= kBucketSmemItems, "a bucket that fits the table fits the registers");
   if (counters[CNT_ABORT] != 0) return;
   const BatchLayout& L = P.L;
-  const i64 buckets = L.region_off[L.G];
-  for (i64 k = blockIdx.x; k < buckets; k += gridDim.x) {
-    const uint32_t start = P.bucket_start[k];
-    const uint32_t n = P.bucket_start[k + 1] - start;
+  const u32 buckets = (u32)L.region_off[L.G];
+  for (u32 k = blockIdx.x; k < buckets; k += gridDim.x) {
+    const u32 start = P.bucket_start[k];
+    const u32 n = P.bucket_start[k + 1] - start;
     if (n == 0) continue;
-    const i64 b = batch_of(L.region_off, L.G, k);
-    uint32_t* ref = P.ref + __ldg(L.item_off + b);
+    u32* ref = P.ref + __ldg(L.item_off + batch_of(L.region_off, L.G, (i64)k));
     const u64* items = P.bucketed + start;
-    const uint32_t size = 2 * n + 32;
-    if (n <= (uint32_t)kBucketSmemItems) {
+    const u32 size = 2 * n + 32;
+    if (n <= (u32)kBucketSmemItems) {
       // the bucket's items stay in registers for both passes; their loads are in flight while the table is cleared
       u64 w[kResolvePer];
 #pragma unroll
       for (int q = 0; q < kResolvePer; ++q) {
-        const uint32_t j = q * kResolveThreads + threadIdx.x;
+        const u32 j = q * kResolveThreads + threadIdx.x;
         w[q] = j < n ? __ldg(items + j) : kEmptyWord;
       }
       __syncthreads();  // the previous bucket's look-ups are done
       {
         ulonglong2* t2 = reinterpret_cast<ulonglong2*>(s_table);
         const ulonglong2 e = make_ulonglong2(kEmptyWord, kEmptyWord);
-        for (uint32_t i = threadIdx.x; i < size / 2; i += kResolveThreads) t2[i] = e;  // size is even
+        for (u32 i = threadIdx.x; i < size / 2; i += kResolveThreads) t2[i] = e;  // size is even
       }
       __syncthreads();
-      uint32_t h[kResolvePer];
+      u32 slot[kResolvePer];
 #pragma unroll
       for (int q = 0; q < kResolvePer; ++q) {
-        h[q] = (uint32_t)(((u64)slot_hash((i64)(w[q] >> 32)) * size) >> 32);
-        if (w[q] != kEmptyWord) smem_insert_min(s_table, size, h[q], w[q]);
+        slot[q] = 0;
+        if (w[q] != kEmptyWord) slot[q] = table_insert_min(s_table, size, slot_of_id((u32)(w[q] >> 32), size), w[q]);
       }
       __syncthreads();
 #pragma unroll
       for (int q = 0; q < kResolvePer; ++q)
-        if (w[q] != kEmptyWord) ref[(uint32_t)w[q]] = table_first_position(s_table, size, h[q], w[q] >> 32);
+        if (w[q] != kEmptyWord) ref[(u32)w[q]] = (u32)s_table[slot[q]];
       continue;
     }
     // oversized bucket (many repeats of a few ids): a table of its own in global memory
     u64* table = P.spill + 2 * (u64)start + 32 * (u64)k;
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < size; i += kResolveThreads) table[i] = kEmptyWord;
+    for (u32 i = threadIdx.x; i < size; i += kResolveThreads) table[i] = kEmptyWord;
     __syncthreads();
-    bool full = false;
-    for (uint32_t j = threadIdx.x; j < n; j += kResolveThreads) {
+    for (u32 j = threadIdx.x; j < n; j += kResolveThreads) {
       const u64 w = __ldg(items + j);
-      const uint32_t h = (uint32_t)(((u64)slot_hash((i64)(w >> 32)) * size) >> 32);
-      full |= !table_insert_min(table, size, h, w);
+      table_insert_min(table, size, slot_of_id((u32)(w >> 32), size), w);
     }
-    if (full) raise_error(counters, GSB_ERR_TABLE_FULL, k);
     __syncthreads();
-    for (uint32_t j = threadIdx.x; j < n; j += kResolveThreads) {
+    for (u32 j = threadIdx.x; j < n; j += kResolveThreads) {
       const u64 w = __ldg(items + j);
-      const uint32_t h = (uint32_t)(((u64)slot_hash((i64)(w >> 32)) * size) >> 32);
-      ref[(uint32_t)w] = table_first_position(table, size, h, w >> 32);
+      const u32 id = (u32)(w >> 32);
+      u32 h = slot_of_id(id, size), first = 0xFFFFFFFFu;
+      for (u32 probe = 0; probe < size; ++probe) {
+        const u64 x = __ldcg(table + h);
+        if ((u32)(x >> 32) == id) {
+          first = (u32)x;
+          break;
+        }
+        if (x == kEmptyWord) break;
+        h = h + 1 == size ? 0 : h + 1;
+      }
+      ref[(u32)w] = first;
     }
   }
 }
@@ -359,45 +378,61 @@ __global__ void __launch_bounds__(kResolveThreads, 2) k_part_resolve(PartLayout 
 // 8-byte look-up in an array of 8 bytes per 32 items (62 KB for a minibatch of 250 000 items) instead of a fix-up pass
 // over a rank array.  None of the three kernels waits for anything but the short chain of k_rank_prefix.
 constexpr int kBitsThreads = 256;
-constexpr int kBitsGroups = 8;                                   // 32-item groups per warp
+constexpr int kBitsGroups = 8;                                     // 32-item groups per warp
 constexpr int kBitsTile = (kBitsThreads / 32) * kBitsGroups * 32;  // items per CTA
 constexpr int kEmitGroups = 4;
 constexpr int kEmitTile = (kBitsThreads / 32) * kEmitGroups * 32;
 constexpr int kPrefixThreads = 256;
 constexpr int kPrefixPer = 8;
-constexpr int kPrefixTile = kPrefixThreads * kPrefixPer;         // words per CTA
+constexpr int kPrefixTile = kPrefixThreads * kPrefixPer;  // words per CTA
 
 struct RankArrays {
-  const uint32_t* ref;
-  uint32_t* bits;   // [ceil(items / 32)]
-  u64* packed;      // [ceil(items / 32) + 1]
+  const u32* ref;
+  u32* bits;    // [ceil(items / 32)]
+  u64* packed;  // [ceil(items / 32) + 1]
 };
 
 __global__ void __launch_bounds__(kBitsThreads) k_first_bits(BatchLayout L, RankArrays R, i64 n_bound, i64* counters) {
   if (counters[CNT_ABORT] != 0) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const i64 n = min(L.item_off[L.G], n_bound);
-  const i64 base = (i64)blockIdx.x * kBitsTile + (i64)warp * (kBitsGroups * 32);
-  if (base >= n) return;
-  uint32_t r[kBitsGroups];
+  __shared__ i64 s_b;
+  const i64 cta_base = (i64)blockIdx.x * kBitsTile;
+  if (cta_base >= n) return;
+  const i64 base = cta_base + (i64)warp * (kBitsGroups * 32);
+  const u32 here = base < n ? (u32)min((i64)(kBitsGroups * 32), n - base) : 0u;  // items of this warp
+  const u32* ref = R.ref + base;
+  u32 r[kBitsGroups];
 #pragma unroll
   for (int q = 0; q < kBitsGroups; ++q) {
-    const i64 g = base + q * 32 + lane;
-    r[q] = g < n ? __ldg(R.ref + g) : 0xFFFFFFFFu;
+    const u32 i = q * 32 + lane;
+    r[q] = i < here ? __ldg(ref + i) : 0xFFFFFFFFu;
   }
-  const BatchUniform u = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, base));
+  const i64 b = batch_from_cta(L, cta_base, min(base, n - 1), &s_b);
+  if (here == 0) return;
+  const i64 begin = __ldg(L.item_off + b), next_begin = __ldg(L.item_off + b + 1);
+  u32* bits = R.bits + (base >> 5);
+  if (base + here <= next_begin) {
+    const u32 lc0 = (u32)(base - begin) + lane;
 #pragma unroll
+    for (int q = 0; q < kBitsGroups; ++q) {
+      if ((u32)(q * 32) >= here) break;  // uniform
+      const unsigned bal = __ballot_sync(0xffffffffu, r[q] == lc0 + q * 32);  // lanes beyond `here` hold 0xFFFFFFFF
+      if (lane == 0) bits[q] = bal;
+    }
+    return;
+  }
+#pragma unroll 1
   for (int q = 0; q < kBitsGroups; ++q) {
-    const i64 g = base + q * 32 + lane;
-    if (base + q * 32 >= n) break;  // uniform
+    if ((u32)(q * 32) >= here) break;
+    const u32 i = q * 32 + lane;
     bool first = false;
-    if (g < n) {
-      i64 begin = u.begin;
-      if (g >= u.next_begin) begin = __ldg(L.item_off + batch_of(L.item_off, L.G, g));
-      first = r[q] == (uint32_t)(g - begin);
+    if (i < here) {
+      const i64 g = base + i;
+      first = r[q] == (u32)(g - __ldg(L.item_off + batch_of(L.item_off, L.G, g)));
     }
     const unsigned bal = __ballot_sync(0xffffffffu, first);
-    if (lane == 0) R.bits[(base >> 5) + q] = bal;
+    if (lane == 0) bits[q] = bal;
   }
 }
 
@@ -411,7 +446,7 @@ __global__ void __launch_bounds__(kPrefixThreads) k_rank_prefix(BatchLayout L, R
   const int tile = blockIdx.x;
   const i64 first = (i64)tile * kPrefixTile + (i64)threadIdx.x * kPrefixPer;
   if ((i64)tile * kPrefixTile >= words && !(words == 0 && tile == 0)) return;
-  uint32_t b[kPrefixPer];
+  u32 b[kPrefixPer];
   i64 sum = 0;
 #pragma unroll
   for (int j = 0; j < kPrefixPer; ++j) {
@@ -441,67 +476,71 @@ __global__ void __launch_bounds__(kPrefixThreads) k_rank_prefix(BatchLayout L, R
   }
 }
 
+__device__ __forceinline__ u32 rank_in_word(u64 w, u32 bit) { return (u32)(w >> 32) + __popc((u32)w & ((1u << bit) - 1u)); }
 __device__ __forceinline__ i64 rank_before(const u64* __restrict__ packed, i64 item) {
-  const u64 w = __ldg(packed + (item >> 5));
-  return (i64)(w >> 32) + __popc((uint32_t)w & ((1u << (item & 31)) - 1u));
+  return (i64)rank_in_word(__ldg(packed + (item >> 5)), (u32)item & 31u);
 }
 
 __global__ void __launch_bounds__(kBitsThreads) k_rank_emit(BatchLayout L, RankArrays R, i64 n_bound, CompactOut out,
                                                             i64* __restrict__ out_relabeled, i64* counters) {
   if (counters[CNT_ABORT] != 0) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const i64 n = min(L.item_off[L.G], n_bound);
-  const i64 base = (i64)blockIdx.x * kEmitTile + (i64)warp * (kEmitGroups * 32);
-  if (base >= n) return;
+  __shared__ i64 s_b;
+  const i64 cta_base = (i64)blockIdx.x * kEmitTile;
+  if (cta_base >= n) return;
+  const i64 base = cta_base + (i64)warp * (kEmitGroups * 32);
+  const u32 here = base < n ? (u32)min((i64)(kEmitGroups * 32), n - base) : 0u;
   // loads that depend on nothing first: the refs of the warp's items and the packed words of their own groups
-  uint32_t r[kEmitGroups];
+  const u32* ref = R.ref + base;
+  const u64* own_words = R.packed + (base >> 5);
+  u32 r[kEmitGroups];
   u64 own[kEmitGroups];
 #pragma unroll
   for (int q = 0; q < kEmitGroups; ++q) {
-    const i64 g = base + q * 32 + lane;
-    r[q] = g < n ? __ldg(R.ref + g) : 0xFFFFFFFFu;
-    own[q] = base + q * 32 < n ? __ldg(R.packed + (base >> 5) + q) : 0ull;
+    const u32 i = q * 32 + lane;
+    r[q] = i < here ? __ldg(ref + i) : 0xFFFFFFFFu;
+    own[q] = (u32)(q * 32) < here ? __ldg(own_words + q) : 0ull;
   }
-  const BatchUniform u = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, base));
-  const i64 u_front = rank_before(R.packed, u.begin);
-  const bool uniform = min(n, base + kEmitGroups * 32) <= u.next_begin;
-  if (uniform) {
-    // every item of the warp lies in minibatch u: look-ups of all groups are issued before anything is written
-    const i64 items_in_batch = u.next_begin - u.begin;
+  const i64 b_warp = batch_from_cta(L, cta_base, min(base, n - 1), &s_b);
+  if (here == 0) return;
+  const BatchUniform u = load_batch<false>(L, L.item_off, b_warp);
+  if (base + here <= u.next_begin) {
+    // every item of the warp lies in minibatch u: positions are 32-bit, the look-ups of all groups are issued before
+    // anything is written
+    const u32 items = (u32)(u.next_begin - u.begin), ns = (u32)u.num_seeds;
+    const u32 lc0 = (u32)(base - u.begin) + lane;
+    const u64* win = R.packed + (u.begin >> 5);  // the minibatch's window of packed words
+    const u32 shift = (u32)u.begin & 31u;        // bit of the minibatch's first item inside win[0]
+    const u32 front = rank_in_word(__ldg(win), shift);
+    const i64* seeds = L.seeds + u.seeds_begin;
+    const i64* edges = L.indices + u.edges_begin - ns;
+    i64* rel = out_relabeled ? out_relabeled + u.edges_begin - ns : nullptr;
     u64 wref[kEmitGroups];
     i64 node[kEmitGroups];
 #pragma unroll
     for (int q = 0; q < kEmitGroups; ++q) {
-      const i64 g = base + q * 32 + lane;
-      const i64 lc = g - u.begin;
+      const u32 lc = lc0 + q * 32;
       wref[q] = 0;
       node[q] = 0;
-      if (g >= n) continue;
-      if (lc >= u.num_seeds && (i64)r[q] < items_in_batch) wref[q] = __ldg(R.packed + ((u.begin + (i64)r[q]) >> 5));
-      if (r[q] == (uint32_t)lc)
-        node[q] = lc < u.num_seeds ? __ldg(L.seeds + u.seeds_begin + lc)
-                                   : __ldg(L.indices + u.edges_begin + (lc - u.num_seeds));
+      if (q * 32 + lane >= here) continue;
+      if (lc >= ns && r[q] < items) wref[q] = __ldg(win + ((r[q] + shift) >> 5));
+      if (r[q] == lc) node[q] = __ldg(lc < ns ? seeds + lc : edges + lc);
     }
 #pragma unroll
     for (int q = 0; q < kEmitGroups; ++q) {
-      const i64 g = base + q * 32 + lane;
-      if (g >= n) continue;
-      const i64 lc = g - u.begin;
-      const i64 pos = (i64)(own[q] >> 32) + __popc((uint32_t)own[q] & ((1u << lane) - 1u));
-      if (r[q] == (uint32_t)lc) out.unique[pos] = node[q];
-      if (g == u.begin) {  // the frontier of the minibatch starts here; empty minibatches before it start here too
+      const u32 lc = lc0 + q * 32;
+      if (q * 32 + lane >= here) continue;
+      const u32 pos = rank_in_word(own[q], lane);
+      if (r[q] == lc) out.unique[pos] = node[q];
+      if (lc == 0) {  // the frontier of the minibatch starts here; empty minibatches before it start here too
         out.unique_ptr[u.batch] = pos;
-        for (i64 e = u.batch - 1; e >= 0 && __ldg(L.item_off + e) == g; --e) out.unique_ptr[e] = pos;
+        for (i64 e = u.batch - 1; e >= 0 && __ldg(L.item_off + e) == u.begin; --e) out.unique_ptr[e] = pos;
       }
-      if (lc >= u.num_seeds && out_relabeled) {
-        // an id outside the accepted range was never bucketed and its ref says so; any value that is not a position
-        // of this minibatch is treated alike, so no look-up can leave the rank array
-        const i64 p = u.begin + (i64)r[q];
-        out_relabeled[u.edges_begin + (lc - u.num_seeds)] =
-            (i64)r[q] >= items_in_batch
-                ? -1
-                : (i64)(wref[q] >> 32) + __popc((uint32_t)wref[q] & ((1u << (p & 31)) - 1u)) - u_front;
-      }
+      // an id outside the accepted range was never bucketed and its ref says so; any value that is not a position of
+      // this minibatch is treated alike, so no look-up can leave the rank array
+      if (lc >= ns && rel)
+        rel[lc] = r[q] < items ? (i64)(rank_in_word(wref[q], (r[q] + shift) & 31u) - front) : (i64)-1;
     }
     return;
   }
@@ -510,13 +549,10 @@ __global__ void __launch_bounds__(kBitsThreads) k_rank_emit(BatchLayout L, RankA
     const i64 g = base + q * 32 + lane;
     if (g >= n) continue;
     BatchUniform v = u;
-    i64 front = u_front;
-    if (g >= u.next_begin) {
-      v = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, g));
-      front = rank_before(R.packed, v.begin);
-    }
+    if (g >= u.next_begin) v = load_batch<false>(L, L.item_off, batch_of(L.item_off, L.G, g));
+    const i64 front = rank_before(R.packed, v.begin);
     const i64 lc = g - v.begin;
-    const bool first = r[q] == (uint32_t)lc;
+    const bool first = r[q] == (u32)lc;
     if (first || g == v.begin) {
       const i64 pos = rank_before(R.packed, g);
       if (first) out.unique[pos] = lc < v.num_seeds ? __ldg(L.seeds + v.seeds_begin + lc)
@@ -540,7 +576,7 @@ i64 partition_bucket_capacity(i64 n_cap, i64 G) { return n_cap / kBucketTarget +
 size_t partition_workspace_bytes(i64 n_cap, i64 G) {
   const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
   const size_t words = (size_t)((n_cap + 31) / 32) + 2;
-  return al256(sizeof(uint32_t) * 3 * (size_t)(bucket_cap + 1)) + al256(8 * (size_t)n_cap) + al256(4 * (size_t)n_cap) +
+  return al256(sizeof(u32) * 3 * (size_t)(bucket_cap + 1)) + al256(8 * (size_t)n_cap) + al256(4 * (size_t)n_cap) +
          al256(4 * words) + al256(8 * words) + al256(8 * (2 * (size_t)n_cap + 32 * (size_t)bucket_cap + 64));
 }
 
@@ -552,17 +588,17 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
   char* at = (char*)ws;
   PartLayout P;
   P.L = L;
-  P.bucket_count = (uint32_t*)at;
+  P.bucket_count = (u32*)at;
   P.bucket_start = P.bucket_count + (bucket_cap + 1);
   P.bucket_cursor = P.bucket_count + 2 * (bucket_cap + 1);
-  at += al256(sizeof(uint32_t) * 3 * (size_t)(bucket_cap + 1));
+  at += al256(sizeof(u32) * 3 * (size_t)(bucket_cap + 1));
   P.bucketed = (u64*)at;
   at += al256(8 * (size_t)n_cap);
-  P.ref = (uint32_t*)at;
+  P.ref = (u32*)at;
   at += al256(4 * (size_t)n_cap);
   RankArrays R;
   R.ref = P.ref;
-  R.bits = (uint32_t*)at;
+  R.bits = (u32*)at;
   at += al256(4 * words);
   R.packed = (u64*)at;
   at += al256(8 * words);
@@ -573,12 +609,10 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
     GSB_CUDA_OK(cudaFuncSetAttribute(k_part_resolve, cudaFuncAttributeMaxDynamicSharedMemorySize, kBucketSlots * 8));
     attr_set[dev] = true;
   }
-  GSB_CUDA_OK(cudaMemsetAsync(P.bucket_count, 0, sizeof(uint32_t) * (size_t)(bucket_cap + 1), stream));
-  const int tiles = grid_for(n_cap, kPartTile);
-  const int scatter_tiles = grid_for(n_cap, kScatterTile);
+  GSB_CUDA_OK(cudaMemsetAsync(P.bucket_count, 0, sizeof(u32) * (size_t)(bucket_cap + 1), stream));
   {
     ScopedKernelTimer timer(ctx, KID_PART_COUNT, stream);
-    k_part_count<<<tiles, kPartThreads, 0, stream>>>(P, n_cap, counters);
+    k_part_count<<<grid_for(n_cap, kPartTile), kPartThreads, 0, stream>>>(P, n_cap, counters);
   }
   GSB_LAUNCH_OK();
   {
@@ -588,18 +622,17 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
   GSB_LAUNCH_OK();
   {
     ScopedKernelTimer timer(ctx, KID_PART_SCATTER, stream);
-    k_part_scatter<<<scatter_tiles, kPartThreads, 0, stream>>>(P, n_cap, counters);
+    k_part_scatter<<<grid_for(n_cap, kScatterTile), kPartThreads, 0, stream>>>(P, n_cap, counters);
   }
   GSB_LAUNCH_OK();
   {
     ScopedKernelTimer timer(ctx, KID_PART_RESOLVE, stream);
-    k_part_resolve<<<(int)min(bucket_cap, (i64)kNumSMs * 2 * 4), kResolveThreads, kBucketSlots * 8, stream>>>(P, counters);
+    k_part_resolve<<<(int)min(bucket_cap, (i64)kNumSMs * 4 * 4), kResolveThreads, kBucketSlots * 8, stream>>>(P, counters);
   }
   GSB_LAUNCH_OK();
-  const int bit_tiles = grid_for(n_cap, kBitsTile);
   {
     ScopedKernelTimer timer(ctx, KID_FIRST_BITS, stream);
-    k_first_bits<<<bit_tiles, kBitsThreads, 0, stream>>>(L, R, n_cap, counters);
+    k_first_bits<<<grid_for(n_cap, kBitsTile), kBitsThreads, 0, stream>>>(L, R, n_cap, counters);
   }
   GSB_LAUNCH_OK();
   const int prefix_tiles = grid_for((n_cap + 31) / 32, kPrefixTile);
