@@ -658,8 +658,8 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
     return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr,
                                         out_relabeled);
   }
-  if (path == 3) {
-    // partitioned form: shared-memory tables per bucket of items, then ranking by bit vectors
+  if (path == 3 || path == 0) {
+    // partitioned form (the default when the direct-address tables above were not chosen): shared-memory tables per bucket of items, then ranking by bit vectors
     int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, G), &ws);
     if (st != GSB_OK) return st;
     L.item_off = (i64*)ws;

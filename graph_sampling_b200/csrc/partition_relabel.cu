@@ -300,6 +300,19 @@ __device__ __forceinline__ u32 table_insert_min(u64* table, u32 size, u32 h, u64
   return 0;  // cannot happen: the table has more slots than the bucket has items
 }
 
+// Shared-memory table as two 32-bit arrays — ids and smallest positions — so that the probe loop, which the lanes of
+// a warp leave at different times, is a 32-bit load and two compares per step, and both atomics are native 32-bit
+// shared-memory operations.  Returns the slot of the id.
+__device__ __forceinline__ u32 smem_claim_slot(u32* keys, u32 size, u32 h, u32 id) {
+  for (u32 probe = 0; probe < size; ++probe) {
+    u32 k = *(volatile u32*)(keys + h);
+    if (k == 0xFFFFFFFFu) k = atomicCAS(keys + h, 0xFFFFFFFFu, id);  // ids are below 2^32 - 1
+    if (k == 0xFFFFFFFFu || k == id) return h;
+    h = h + 1 == size ? 0 : h + 1;
+  }
+  return 0;  // cannot happen: the table has more slots than the bucket has items
+}
+
 __global__ void __launch_bounds__(kResolveThreads, 4) k_part_resolve(PartLayout P, i64* counters) {
   extern __shared__ __align__(16) u64 s_table[];
   static_assert(kResolvePer * kResolveThreads >= kBucketSmemItems, "a bucket that fits the table fits the registers");
@@ -322,22 +335,31 @@ __global__ void __launch_bounds__(kResolveThreads, 4) k_part_resolve(PartLayout 
         w[q] = j < n ? __ldg(items + j) : kEmptyWord;
       }
       __syncthreads();  // the previous bucket's look-ups are done
+      u32* keys = reinterpret_cast<u32*>(s_table);  // [size] ids, then [size] smallest positions; size is even
+      u32* first = keys + size;
       {
-        ulonglong2* t2 = reinterpret_cast<ulonglong2*>(s_table);
-        const ulonglong2 e = make_ulonglong2(kEmptyWord, kEmptyWord);
-        for (u32 i = threadIdx.x; i < size / 2; i += kResolveThreads) t2[i] = e;  // size is even
+        uint4* t4 = reinterpret_cast<uint4*>(s_table);
+        const uint4 e = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+        for (u32 i = threadIdx.x; i < size / 2; i += kResolveThreads) t4[i] = e;
       }
       __syncthreads();
       u32 slot[kResolvePer];
 #pragma unroll
       for (int q = 0; q < kResolvePer; ++q) {
         slot[q] = 0;
-        if (w[q] != kEmptyWord) slot[q] = table_insert_min(s_table, size, slot_of_id((u32)(w[q] >> 32), size), w[q]);
+        if ((u32)(q * kResolveThreads) >= n) break;  // uniform
+        if (w[q] != kEmptyWord) {
+          const u32 id = (u32)(w[q] >> 32);
+          slot[q] = smem_claim_slot(keys, size, slot_of_id(id, size), id);
+          atomicMin(first + slot[q], (u32)w[q]);
+        }
       }
       __syncthreads();
 #pragma unroll
-      for (int q = 0; q < kResolvePer; ++q)
-        if (w[q] != kEmptyWord) ref[(u32)w[q]] = (u32)s_table[slot[q]];
+      for (int q = 0; q < kResolvePer; ++q) {
+        if ((u32)(q * kResolveThreads) >= n) break;
+        if (w[q] != kEmptyWord) ref[(u32)w[q]] = first[slot[q]];
+      }
       continue;
     }
     // oversized bucket (many repeats of a few ids): a table of its own in global memory
