@@ -50,7 +50,10 @@ UNIT = "edges/s"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) divided by algorithmic bytes, from one ncu capture per
 # kernel on hop 3 of a 64-minibatch call of this workload (profiles/k_*_sage3hop_group64.md).  Traffic grows in
 # proportion to the units a launch processes, so a full launch's traffic is this ratio times its algorithmic bytes.
-TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.2, "table_insert": 4.1, "first_compact": 3.2, "relabel": 1.04}
+TRAFFIC_OVER_ALGORITHMIC = {"sample_uniform": 4.2, "table_insert": 4.1, "first_compact": 3.2, "relabel": 1.04,
+                            # partitioned form (profiles/k_part_*_sage3hop_group64.md, k_rank_emit_sage3hop_group64.md)
+                            "partition_count": 1.04, "partition_scatter": 0.81, "bucket_resolve": 0.88,
+                            "first_bits": 1.0}
 # the same with direct-address tables (profiles/k_direct_insert_sage3hop_group64.md)
 TRAFFIC_OVER_ALGORITHMIC_DIRECT = {"sample_uniform": 4.2, "table_insert": 9.1}
 
@@ -500,8 +503,11 @@ def run_ours(args):
         peak, peak_src = 6650.0, "fallback"
     # Algorithmic bytes per launch of each hot kernel, from the shapes of the profiled calls: (S, E, U) per hop.
     # sample: 32 B per seed column (seed id, indptr pair, output offset) + 24 B per sampled edge (8 read, 16 written);
-    # unique + relabel is three passes over N = S + E items: insert reads 8 N; first-occurrence compaction reads 8 N
-    # and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead, not counted).
+    # unique + relabel, hash-region / direct-table forms: three passes over N = S + E items: insert reads 8 N;
+    # first-occurrence compaction reads 8 N and writes 8 U; relabel reads 8 E and writes 8 E (table traffic is overhead,
+    # not counted).  Partitioned form: count reads 8 N; scatter reads 8 N and writes 8 N; the per-bucket resolve reads
+    # 8 N and writes 4 N; the bit pass reads 4 N; the emit pass reads 4 N and the 8 U ids of the first occurrences and
+    # writes 8 U + 8 E.
     hop_shapes = [h for call in shapes for h in call]
     n_launch = max(1, len(hop_shapes))
     alg = {
@@ -509,9 +515,24 @@ def run_ours(args):
         "table_insert": sum(8 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
         "first_compact": sum(8 * (s_ + e_) + 8 * u_ for s_, e_, u_ in hop_shapes) / n_launch,
         "relabel": sum(16 * e_ for s_, e_, _ in hop_shapes) / n_launch,
+        "partition_count": sum(8 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
+        "partition_scatter": sum(16 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
+        "bucket_resolve": sum(12 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
+        "first_bits": sum(4 * (s_ + e_) for s_, e_, _ in hop_shapes) / n_launch,
+        "rank_emit": sum(4 * (s_ + e_) + 16 * u_ + 8 * e_ for s_, e_, u_ in hop_shapes) / n_launch,
     }
-    direct = ctx.get_option("relabel_path") == 2
+    # which form of unique + relabel ran is read off the kernels that were launched
+    launched = {name for name, (ms, n) in prof.items() if n}
+    form = "partition" if "bucket_resolve" in launched else "hash" if "table_clear" in launched else "direct"
+    direct = form == "direct"
+    form_text = {"partition": "shared-memory tables per bucket of items (partitioned form)",
+                 "hash": "hash-table regions in global memory", "direct": "direct-address tables"}[form]
     kernel_names = {"sample_uniform": "k_sample_uniform_tpc (fused count + scan + uniform sample)",
+                    "partition_count": "k_part_count (items per bucket)",
+                    "partition_scatter": "k_part_scatter (items grouped by bucket)",
+                    "bucket_resolve": "k_part_resolve (first position per id in a shared-memory table per bucket)",
+                    "first_bits": "k_first_bits (bit vector of first occurrences)",
+                    "rank_emit": "k_rank_emit (frontier and relabelled ids from the rank bit vector)",
                     "table_insert": "k_direct_insert (atomicMin into per-minibatch direct-address tables)" if direct
                     else "k_batch_insert (position-min hash insert)",
                     "first_compact": "k_direct_compact (first-occurrence test + scan + compaction)" if direct
@@ -552,10 +573,10 @@ def run_ours(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
         "config": workload_config(args, info),
         "arm": {"path": "batched sampler through the C ABI (gsb_sage_hop per hop: fused slice+sample, then unique + "
-                        "relabel of every minibatch with %s)" % ("direct-address tables" if direct else "hash tables"),
+                        "relabel of every minibatch with %s)" % form_text,
                 "parallelism": f"replicated graph, dp{world}; minibatch b of {args.batches_per_step * world} on rank "
                                "b mod N, random streams keyed by the global minibatch number",
-                "graph_gen_seconds": gen_s, "relabel_path": "direct" if direct else "hash",
+                "graph_gen_seconds": gen_s, "relabel_path": form,
                 "lanes": (f"{lanes} host thread(s), each with its own CUDA stream, library context and output arena, take "
                           "alternate calls of a step; one host wait per hop") if args.host_waits else
                          (f"one host thread queues the calls of a step on {lanes} CUDA stream(s) in turn (own library "

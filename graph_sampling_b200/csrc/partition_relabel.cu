@@ -54,6 +54,8 @@ struct PartLayout {
   u32* bucket_count;   // [buckets + 1]
   u32* bucket_start;   // [buckets + 1]
   u32* bucket_cursor;  // [buckets]
+  u32* bucket_item0;   // [buckets]  first item of the bucket's minibatch (what its positions count from); written by
+                       //            the counting pass for every bucket that holds an item
   u64* bucketed;       // [items]   id << 32 | position inside the minibatch, grouped by bucket
   u32* ref;            // [items]   position inside the minibatch of the first occurrence of the item's id
   u64* spill;          // tables of the buckets that do not fit shared memory: 2 x start + 32 x bucket
@@ -158,8 +160,12 @@ __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n
       atomicAdd(&s_cnt[bucket_of_id((u32)node[q], t.parts)], 1u);
     }
     __syncthreads();
-    for (u32 i = threadIdx.x; i < t.parts; i += kPartThreads)
-      if (s_cnt[i] != 0) atomicAdd(P.bucket_count + t.bucket0 + i, s_cnt[i]);
+    for (u32 i = threadIdx.x; i < t.parts; i += kPartThreads) {
+      if (s_cnt[i] != 0) {
+        atomicAdd(P.bucket_count + t.bucket0 + i, s_cnt[i]);
+        P.bucket_item0[t.bucket0 + i] = (u32)u.begin;  // every tile of the minibatch writes the same value
+      }
+    }
     return;
   }
   for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
@@ -170,6 +176,7 @@ __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n
       continue;
     }
     atomicAdd(P.bucket_count + it.bucket, 1u);
+    P.bucket_item0[it.bucket] = (u32)(tile_base + i - it.lc);
   }
 }
 
@@ -304,13 +311,12 @@ __device__ __forceinline__ u32 table_insert_min(u64* table, u32 size, u32 h, u64
 // a warp leave at different times, is a 32-bit load and two compares per step, and both atomics are native 32-bit
 // shared-memory operations.  Returns the slot of the id.
 __device__ __forceinline__ u32 smem_claim_slot(u32* keys, u32 size, u32 h, u32 id) {
-  for (u32 probe = 0; probe < size; ++probe) {
+  for (;;) {  // ends: the table has more slots than the bucket has items
     u32 k = *(volatile u32*)(keys + h);
     if (k == 0xFFFFFFFFu) k = atomicCAS(keys + h, 0xFFFFFFFFu, id);  // ids are below 2^32 - 1
     if (k == 0xFFFFFFFFu || k == id) return h;
     h = h + 1 == size ? 0 : h + 1;
   }
-  return 0;  // cannot happen: the table has more slots than the bucket has items
 }
 
 __global__ void __launch_bounds__(kResolveThreads, 4) k_part_resolve(PartLayout P, i64* counters) {
@@ -323,10 +329,11 @@ __global__ void __launch_bounds__(kResolveThreads, 4) k_part_resolve(PartLayout 
     const u32 start = P.bucket_start[k];
     const u32 n = P.bucket_start[k + 1] - start;
     if (n == 0) continue;
-    u32* ref = P.ref + __ldg(L.item_off + batch_of(L.region_off, L.G, (i64)k));
+    u32* ref = P.ref + P.bucket_item0[k];
     const u64* items = P.bucketed + start;
-    const u32 size = 2 * n + 32;
     if (n <= (u32)kBucketSmemItems) {
+      // three slots per item where the table allows it: the lanes of a warp leave the probe loop together more often
+      const u32 size = min(3 * n + 32, (u32)kBucketSlots) & ~1u;
       // the bucket's items stay in registers for both passes; their loads are in flight while the table is cleared
       u64 w[kResolvePer];
 #pragma unroll
@@ -363,6 +370,7 @@ __global__ void __launch_bounds__(kResolveThreads, 4) k_part_resolve(PartLayout 
       continue;
     }
     // oversized bucket (many repeats of a few ids): a table of its own in global memory
+    const u32 size = 2 * n + 32;
     u64* table = P.spill + 2 * (u64)start + 32 * (u64)k;
     __syncthreads();
     for (u32 i = threadIdx.x; i < size; i += kResolveThreads) table[i] = kEmptyWord;
@@ -598,7 +606,7 @@ i64 partition_bucket_capacity(i64 n_cap, i64 G) { return n_cap / kBucketTarget +
 size_t partition_workspace_bytes(i64 n_cap, i64 G) {
   const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
   const size_t words = (size_t)((n_cap + 31) / 32) + 2;
-  return al256(sizeof(u32) * 3 * (size_t)(bucket_cap + 1)) + al256(8 * (size_t)n_cap) + al256(4 * (size_t)n_cap) +
+  return al256(sizeof(u32) * 4 * (size_t)(bucket_cap + 1)) + al256(8 * (size_t)n_cap) + al256(4 * (size_t)n_cap) +
          al256(4 * words) + al256(8 * words) + al256(8 * (2 * (size_t)n_cap + 32 * (size_t)bucket_cap + 64));
 }
 
@@ -613,7 +621,8 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
   P.bucket_count = (u32*)at;
   P.bucket_start = P.bucket_count + (bucket_cap + 1);
   P.bucket_cursor = P.bucket_count + 2 * (bucket_cap + 1);
-  at += al256(sizeof(u32) * 3 * (size_t)(bucket_cap + 1));
+  P.bucket_item0 = P.bucket_count + 3 * (bucket_cap + 1);
+  at += al256(sizeof(u32) * 4 * (size_t)(bucket_cap + 1));
   P.bucketed = (u64*)at;
   at += al256(8 * (size_t)n_cap);
   P.ref = (u32*)at;
