@@ -26,21 +26,24 @@ namespace gsb {
 
 
 // One CTA: per-batch item offsets and / or table regions (exclusive scan over the G region sizes).
-// bound_k == -1: regions sized from the batches' actual item counts (needs indices_ptr); bound_k >= 0:
-// regions sized from the upper bound seeds * (1 + bound_k), which is known before sampling; bound_k == -2: region_off
-// receives the first BUCKET of every minibatch instead (partition_relabel.cu), slot_capacity bounds the bucket count.
-// what & 1: write region_off; what & 2: write item_off.
+// bound_k < 0: regions sized from the batches' actual item counts (needs indices_ptr); bound_k >= 0: regions sized
+// from the upper bound seeds * (1 + bound_k), which is known before sampling.
+// what & 1: write region_off; what & 2: write item_off (indices_ptr is valid); what & 4: keep an abort that an earlier
+// launch of the same call set; what & 8: region_off receives the first BUCKET of every minibatch instead of a table
+// region (partition_relabel.cu; slot_capacity then bounds the bucket count); what & 16: bucket_item0 receives, for
+// every bucket, the first item of its minibatch (needs region_off and indices_ptr).
 // seeds_bound / edges_bound: what the caller sized grids, scratch and outputs for.  Device-side totals above them
 // record GSB_ERR_CAPACITY and set CNT_ABORT, which makes the kernels that follow in the call return at once.
 __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters, i64 bound_k, int what,
-                                                            i64 seeds_bound, i64 edges_bound) {
+                                                            i64 seeds_bound, i64 edges_bound,
+                                                            uint32_t* bucket_item0 = nullptr) {
   __shared__ i64 s_scan[33];
   __shared__ i64 s_carry;
   if (threadIdx.x == 0) {
     s_carry = 0;
-    const i64 ns = L.seeds_ptr[L.G], ne = L.indices_ptr[L.G];
+    const i64 ns = L.seeds_ptr[L.G], ne = (what & 2) ? L.indices_ptr[L.G] : 0;
     const bool over = ns > seeds_bound || ne > edges_bound || ns < 0 || ne < 0;
-    counters[CNT_ABORT] = over ? 1 : 0;
+    if (!(what & 4) || over) counters[CNT_ABORT] = over ? 1 : 0;
     if (over) raise_error(counters, GSB_ERR_CAPACITY, ns > seeds_bound ? ns : ne);
   }
   __syncthreads();
@@ -49,10 +52,13 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
     i64 size = 0;
     if (b < L.G) {
       if (what & 2) L.item_off[b] = L.seeds_ptr[b] + L.indices_ptr[b];
-      const i64 items = L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - L.seeds_ptr[b] - L.indices_ptr[b];
-      if (bound_k >= 0) size = region_size_for((L.seeds_ptr[b + 1] - L.seeds_ptr[b]) * (1 + bound_k));
-      else if (bound_k == -2) size = (items + kBucketTarget - 1) / kBucketTarget;  // buckets of the partitioned form
-      else size = region_size_for(items);
+      const i64 items = bound_k >= 0 ? (L.seeds_ptr[b + 1] - L.seeds_ptr[b]) * (1 + bound_k)
+                                     : L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - L.seeds_ptr[b] - L.indices_ptr[b];
+      size = (what & 8) ? (items + kBucketTarget - 1) / kBucketTarget : region_size_for(items);
+      if (what & 16) {
+        const uint32_t first = (uint32_t)(L.seeds_ptr[b] + L.indices_ptr[b]);
+        for (i64 k = L.region_off[b]; k < L.region_off[b + 1]; ++k) bucket_item0[k] = first;
+      }
     }
     i64 total;
     const i64 excl = block_exclusive_scan<kBThreads>(size, s_scan, &total);
@@ -660,19 +666,20 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
   }
   if (path == 3 || path == 0) {
     // partitioned form (the default when the direct-address tables above were not chosen): shared-memory tables per bucket of items, then ranking by bit vectors
-    int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, G), &ws);
+    const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
+    int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, bucket_cap), &ws);
     if (st != GSB_OK) return st;
     L.item_off = (i64*)ws;
     L.region_off = (i64*)((char*)ws + off_bytes);
     L.slots = nullptr;
-    L.slot_capacity = partition_bucket_capacity(n_cap, G);
+    L.slot_capacity = bucket_cap;
     {
       ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-      k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -2, 3, seeds_bound, edges_bound);
+      k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 1 | 2 | 8, seeds_bound, edges_bound);
     }
     GSB_LAUNCH_OK();
-    return partition_unique_relabel(ctx, stream, L, n_cap, (char*)ws + 2 * off_bytes, out_unique, out_unique_ptr,
-                                    out_relabeled);
+    return partition_unique_relabel(ctx, stream, L, n_cap, bucket_cap, (char*)ws + 2 * off_bytes, false, out_unique,
+                                    out_unique_ptr, out_relabeled);
   }
   const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
@@ -709,6 +716,56 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
   // item that came first, then the fix-up pass over a dense 4-byte array: one random table access fewer per first
   // occurrence and about half a random access per neighbour instead of a second probe of the table
   return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr, out_relabeled);
+}
+
+// One hop of the partitioned form with the per-bucket item counts taken by the sampler itself (fan-outs up to 16): the
+// buckets are laid out from the bound seeds x (1 + fanout), which is known before sampling, the sampler adds every seed
+// and every id it samples to its bucket's count while it holds them, and the counting pass over the items is not run.
+static int sage_hop_sampler_counts(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices,
+                                   i64 num_nodes, const i64* seeds, const i64* seeds_ptr, const i64* batch_ids, i64 G,
+                                   i64 S, i64 k, i64 cap, int replace, u64 seed, i64* out_indptr, i64* out_indices,
+                                   i64* out_select, i64* out_indices_ptr, i64* out_unique, i64* out_unique_ptr,
+                                   i64* out_relabeled) {
+  i64* counters = ctx_counters(ctx);
+  const i64 n_cap = S + cap;
+  const size_t off_bytes = ((size_t)(G + 1) * 8 + 255) & ~(size_t)255;
+  const i64 bucket_cap = partition_bucket_capacity(S * (1 + k), G);
+  void* ws;
+  int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, bucket_cap), &ws);
+  if (st != GSB_OK) return st;
+  void* part_ws = (char*)ws + 2 * off_bytes;
+  BatchLayout L;
+  L.seeds = seeds;
+  L.seeds_ptr = seeds_ptr;
+  L.indices = out_indices;
+  L.indices_ptr = out_indices_ptr;
+  L.G = G;
+  L.item_off = (i64*)ws;
+  L.region_off = (i64*)((char*)ws + off_bytes);
+  L.slots = nullptr;
+  L.slot_capacity = bucket_cap;
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, k, 1 | 8, S, cap);
+  }
+  GSB_LAUNCH_OK();
+  GSB_CUDA_OK(cudaMemsetAsync(partition_bucket_counts(part_ws), 0, sizeof(uint32_t) * (size_t)(bucket_cap + 1), stream));
+  const SamplerCount count{partition_bucket_counts(part_ws), L.region_off};
+  st = sample_uniform_launch(ctx, stream, indptr, indices, num_nodes, seeds, S, k, replace, seed, out_indptr,
+                             out_indices, out_select, nullptr, nullptr, nullptr, nullptr, cap, seeds_ptr + G,
+                             seeds_ptr, batch_ids, G, &count);
+  if (st != GSB_OK) return st;
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(out_indptr, seeds_ptr, G, S,
+                                                                          out_indices_ptr);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, k, 2 | 4 | 16, S, cap,
+                                                partition_bucket_item0(part_ws, bucket_cap));
+  }
+  GSB_LAUNCH_OK();
+  ctx_count_launches(ctx, 1);
+  return partition_unique_relabel(ctx, stream, L, n_cap, bucket_cap, part_ws, true, out_unique, out_unique_ptr,
+                                  out_relabeled);
 }
 
 }  // namespace gsb
@@ -787,8 +844,19 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
   GSB_REQUIRE(n_cap == 0 || (seeds && out_unique), GSB_ERR_INVALID_ARGUMENT);
   GSB_REQUIRE(cap == 0 || (indices && out_indices && out_select && out_relabeled), GSB_ERR_INVALID_ARGUMENT);
   cudaStream_t stream = (cudaStream_t)stream_;
+  int st;
+  const i64 path = ctx_option(ctx, GSB_OPT_RELABEL_PATH);
+  const bool direct_small = (double)G * (double)num_nodes * 8.0 <= (double)kDirectAutoBytes && num_nodes > 0;
+  if (k >= 1 && k <= 16 && n_cap > 0 && (path == 3 || (path == 0 && !direct_small))) {
+    st = sage_hop_sampler_counts(ctx, stream, indptr, indices, num_nodes, seeds, seeds_ptr, batch_ids, G, S, k, cap,
+                                 replace, (u64)seed, out_indptr, out_indices, out_select, out_indices_ptr, out_unique,
+                                 out_unique_ptr, out_relabeled);
+    if (st != GSB_OK) return st;
+    if (unique_total_host || edges_total_host) return read_totals(ctx, stream, unique_total_host, edges_total_host);
+    return GSB_OK;
+  }
   // the exact seed count is seeds_ptr[G] on the device; S only has to bound it (grids, scratch and capacities)
-  int st = sample_uniform_launch(ctx, stream, indptr, indices, num_nodes, seeds, S, k, replace, (u64)seed, out_indptr,
+  st = sample_uniform_launch(ctx, stream, indptr, indices, num_nodes, seeds, S, k, replace, (u64)seed, out_indptr,
                                  out_indices, out_select, nullptr, nullptr, nullptr, nullptr, cap, seeds_ptr + G,
                                  seeds_ptr, batch_ids, G);
   if (st != GSB_OK) return st;

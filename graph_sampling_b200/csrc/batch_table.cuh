@@ -164,12 +164,24 @@ int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchL
                                  i64 n_cap, i64 e_cap, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
 // Partitioned form of the batched unique + relabel (defined in partition_relabel.cu): shared-memory tables per bucket of
 // items, bit-vector ranking, no fix-up pass.  L carries seeds / seeds_ptr / indices / indices_ptr / G; item_off and
-// region_off (first bucket of every minibatch) must be filled by k_batch_layout with bound_k == -2; `ws` is scratch of
-// partition_workspace_bytes(n_cap, G) bytes.
-size_t partition_workspace_bytes(i64 n_cap, i64 G);
-i64 partition_bucket_capacity(i64 n_cap, i64 G);
-int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, void* ws, i64* out_unique,
-                             i64* out_unique_ptr, i64* out_relabeled);
+// region_off (first bucket of every minibatch) must be filled by k_batch_layout; `ws` is scratch of
+// partition_workspace_bytes(n_cap, bucket_cap) bytes and begins with the per-bucket item counts.  counted = true: the
+// counts (and the first item of every bucket's minibatch) are already there — the sampler of the same hop added
+// them — and the counting pass is skipped.
+i64 partition_bucket_capacity(i64 items_bound, i64 G);
+size_t partition_workspace_bytes(i64 n_cap, i64 bucket_cap);
+uint32_t* partition_bucket_counts(void* ws);
+uint32_t* partition_bucket_item0(void* ws, i64 bucket_cap);
+int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
+                             bool counted, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
+// Bucket of an id among the `parts` buckets of its minibatch: Fibonacci hashing (the high bits of id x odd constant),
+// scaled to the bucket count by a multiply-high.  Ids are below 2^32 - 1 wherever this is used.
+__device__ __forceinline__ uint32_t bucket_of_id(uint32_t id, uint32_t parts) { return __umulhi(id * 0x9E3779B1u, parts); }
+// What the uniform sampler needs to count, per bucket, the seeds and the ids it samples (fan-outs up to 16).
+struct SamplerCount {
+  uint32_t* bucket_count;  // [buckets]
+  const i64* bucket_base;  // [G + 1] first bucket of every minibatch
+};
 constexpr int kBucketTarget = 2048;  // mean items per bucket
 
 struct CompactOut {
@@ -187,6 +199,6 @@ int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, 
                           const i64* seeds, i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices,
                           i64* out_select, i64* out_coo_col, const float* data, const i64* e_ids, float* out_data,
                           i64 capacity, const i64* S_dev = nullptr, const i64* batch_ptr = nullptr,
-                          const i64* batch_ids = nullptr, i64 G = 0);
+                          const i64* batch_ids = nullptr, i64 G = 0, const SamplerCount* count = nullptr);
 
 }  // namespace gsb

@@ -61,10 +61,8 @@ struct PartLayout {
   u64* spill;          // tables of the buckets that do not fit shared memory: 2 x start + 32 x bucket
 };
 
-// Ids are below 2^32 - 1 here (valid_id).  Bucket: Fibonacci hashing, the high bits of id x odd constant, scaled to
-// the bucket count by a multiply-high.  Slot: a second constant and one xor-shift round, so the ids of one bucket —
-// which share the high bits of the first product — still spread over the whole table.
-__device__ __forceinline__ u32 bucket_of_id(u32 id, u32 parts) { return __umulhi(id * 0x9E3779B1u, parts); }
+// Slot inside a bucket's table: a constant other than bucket_of_id's and one xor-shift round, so the ids of one
+// bucket — which share the high bits of that product — still spread over the whole table.
 __device__ __forceinline__ u32 slot_of_id(u32 id, u32 size) {
   u32 x = id * 0x85EBCA6Bu;
   x ^= x >> 13;
@@ -152,11 +150,7 @@ __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n
     for (int q = 0; q < kPartPerThread; ++q) {
       const u32 i = q * kPartThreads + threadIdx.x;
       if (i >= here) continue;
-      if (!valid_id(node[q])) {  // never bucketed: marked for the ranking passes
-        raise_error(counters, GSB_ERR_INDEX_RANGE, tile_base + i);
-        P.ref[tile_base + i] = 0xFFFFFFFFu;
-        continue;
-      }
+      if (!valid_id(node[q])) continue;  // never bucketed; reported by the scatter pass
       atomicAdd(&s_cnt[bucket_of_id((u32)node[q], t.parts)], 1u);
     }
     __syncthreads();
@@ -170,11 +164,7 @@ __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n
   }
   for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
     const Located it = locate(L, tile_base + i);
-    if (!valid_id(it.node)) {
-      raise_error(counters, GSB_ERR_INDEX_RANGE, tile_base + i);
-      P.ref[tile_base + i] = 0xFFFFFFFFu;
-      continue;
-    }
+    if (!valid_id(it.node)) continue;
     atomicAdd(P.bucket_count + it.bucket, 1u);
     P.bucket_item0[it.bucket] = (u32)(tile_base + i - it.lc);
   }
@@ -240,7 +230,11 @@ __global__ void __launch_bounds__(kPartThreads) k_part_scatter(PartLayout P, i64
   if (!uniform) {  // a tile over several minibatches: every item straight to its place
     for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
       const Located it = locate(L, tile_base + i);
-      if (!valid_id(it.node)) continue;  // reported by the counting pass
+      if (!valid_id(it.node)) {  // never bucketed: marked for the ranking passes
+        raise_error(counters, GSB_ERR_INDEX_RANGE, tile_base + i);
+        P.ref[tile_base + i] = 0xFFFFFFFFu;
+        continue;
+      }
       P.bucketed[__ldg(P.bucket_start + it.bucket) + atomicAdd(P.bucket_cursor + it.bucket, 1u)] =
           ((u64)it.node << 32) | (u64)it.lc;
     }
@@ -257,7 +251,13 @@ __global__ void __launch_bounds__(kPartThreads) k_part_scatter(PartLayout P, i64
 #pragma unroll
   for (int q = 0; q < kScatterPerThread; ++q) {
     where[q] = kNoBucket;
-    if (!valid_id(node[q])) continue;
+    if (!valid_id(node[q])) {
+      if (q * kPartThreads + threadIdx.x < here) {  // never bucketed: marked for the ranking passes
+        raise_error(counters, GSB_ERR_INDEX_RANGE, tile_base + q * kPartThreads + threadIdx.x);
+        P.ref[tile_base + q * kPartThreads + threadIdx.x] = 0xFFFFFFFFu;
+      }
+      continue;
+    }
     const u32 w = bucket_of_id((u32)node[q], t.parts);
     where[q] = (w << 16) | atomicAdd(&s_cnt[w], 1u);  // at most 2 048 items per tile: the rank fits 16 bits
   }
@@ -601,19 +601,20 @@ __global__ void __launch_bounds__(kBitsThreads) k_rank_emit(BatchLayout L, RankA
 // ---- host sequence ----------------------------------------------------------------------------------------------------
 static inline size_t al256(size_t b) { return (b + 255) & ~(size_t)255; }
 
-i64 partition_bucket_capacity(i64 n_cap, i64 G) { return n_cap / kBucketTarget + G + 1; }
+i64 partition_bucket_capacity(i64 items_bound, i64 G) { return items_bound / kBucketTarget + G + 1; }
 
-size_t partition_workspace_bytes(i64 n_cap, i64 G) {
-  const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
+size_t partition_workspace_bytes(i64 n_cap, i64 bucket_cap) {
   const size_t words = (size_t)((n_cap + 31) / 32) + 2;
   return al256(sizeof(u32) * 4 * (size_t)(bucket_cap + 1)) + al256(8 * (size_t)n_cap) + al256(4 * (size_t)n_cap) +
          al256(4 * words) + al256(8 * words) + al256(8 * (2 * (size_t)n_cap + 32 * (size_t)bucket_cap + 64));
 }
 
-int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, void* ws, i64* out_unique,
-                             i64* out_unique_ptr, i64* out_relabeled) {
+uint32_t* partition_bucket_counts(void* ws) { return (u32*)ws; }
+uint32_t* partition_bucket_item0(void* ws, i64 bucket_cap) { return (u32*)ws + 3 * (bucket_cap + 1); }
+
+int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
+                             bool counted, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled) {
   i64* counters = ctx_counters(ctx);
-  const i64 bucket_cap = partition_bucket_capacity(n_cap, L.G);
   const size_t words = (size_t)((n_cap + 31) / 32) + 2;
   char* at = (char*)ws;
   PartLayout P;
@@ -640,12 +641,14 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
     GSB_CUDA_OK(cudaFuncSetAttribute(k_part_resolve, cudaFuncAttributeMaxDynamicSharedMemorySize, kBucketSlots * 8));
     attr_set[dev] = true;
   }
-  GSB_CUDA_OK(cudaMemsetAsync(P.bucket_count, 0, sizeof(u32) * (size_t)(bucket_cap + 1), stream));
-  {
-    ScopedKernelTimer timer(ctx, KID_PART_COUNT, stream);
-    k_part_count<<<grid_for(n_cap, kPartTile), kPartThreads, 0, stream>>>(P, n_cap, counters);
+  if (!counted) {
+    GSB_CUDA_OK(cudaMemsetAsync(P.bucket_count, 0, sizeof(u32) * (size_t)(bucket_cap + 1), stream));
+    {
+      ScopedKernelTimer timer(ctx, KID_PART_COUNT, stream);
+      k_part_count<<<grid_for(n_cap, kPartTile), kPartThreads, 0, stream>>>(P, n_cap, counters);
+    }
+    GSB_LAUNCH_OK();
   }
-  GSB_LAUNCH_OK();
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
     k_part_scan<<<1, 1024, 0, stream>>>(P, counters);

@@ -302,14 +302,19 @@ struct SampleParams {
   // Minibatch form (G > 0): the seeds of minibatch j are seeds[batch_ptr[j] .. batch_ptr[j+1]) and the draws of its
   // column number c are keyed by (batch_ids[j], c) instead of the column's position in the call, so a minibatch
   // receives the same sample whichever call, group or GPU processes it.
+  // batch_ptr / G alone (batch_ids null) only tell the kernel which minibatch a column belongs to.
   const i64* batch_ptr;
   const i64* batch_ids;
   i64 G;
+  // Per-bucket item counts of the partitioned unique + relabel that follows (thread-per-column kernels only), or null:
+  // every seed and every sampled id adds one to the count of its bucket.
+  uint32_t* bucket_count;
+  const i64* bucket_base;  // [G + 1] first bucket of every minibatch
 };
 
 // Random-stream item of the column at position i of the call.
 __device__ __forceinline__ u64 sample_item(const SampleParams& p, i64 i, i64 batch) {
-  if (p.G <= 0) return (u64)i;
+  if (!p.batch_ids) return (u64)i;
   return ((u64)__ldg(p.batch_ids + batch) << 32) | (u64)(uint32_t)(i - __ldg(p.batch_ptr + batch));
 }
 
@@ -347,7 +352,7 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
     f = column_count(d, k, p.replace ? COUNT_WR : COUNT_WOR);
     s_in[tid] = b;
     s_deg[tid] = d;
-    s_item[tid] = sample_item(p, base + tid, p.G > 0 ? batch_of(p.batch_ptr, p.G, base + tid) : 0);
+    s_item[tid] = sample_item(p, base + tid, p.batch_ids ? batch_of(p.batch_ptr, p.G, base + tid) : 0);
   }
   i64 total;
   const i64 excl = block_exclusive_scan<kThreads>(f, s_scan, &total);
@@ -423,13 +428,33 @@ __global__ void __launch_bounds__(kThreads) k_sample_uniform(SampleParams p) {
 // columns: counts are scanned with shuffles and the tile prefix comes from the same look-back chain,
 // so the kernel has no CTA-wide barrier at all and every lane keeps k independent loads in flight.
 constexpr int kTpcThreads = 128;
+constexpr int kCountWindow = 256;  // buckets a CTA of the counting sampler keeps in shared memory
 
-template <int KMAX>
+// COUNT: the kernel also counts, per bucket of the partitioned unique + relabel, the seeds and sampled ids of its
+// columns — in shared memory, flushed with one global atomic per bucket and CTA — so that no pass over the items is
+// needed for the counts.  A warp whose tile lies beyond the seeds then stays until the CTA's barriers are passed.
+template <int KMAX, bool COUNT>
 __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams p) {
+  __shared__ uint32_t s_cnt[COUNT ? kCountWindow : 1];
+  __shared__ i64 s_win0;
   const int lane = threadIdx.x & 31;
   const i64 tile = (i64)blockIdx.x * (kTpcThreads / 32) + (threadIdx.x >> 5);
   const i64 S = p.S_dev ? min(p.S, __ldg(p.S_dev)) : p.S;
-  if (tile * 32 >= S && !(S == 0 && tile == 0)) return;
+  if (COUNT) {
+    const i64 first = (i64)blockIdx.x * kTpcThreads;  // first column of the CTA
+    if (first >= S && !(S == 0 && blockIdx.x == 0)) return;  // the whole CTA
+    for (int t = threadIdx.x; t < kCountWindow; t += kTpcThreads) s_cnt[t] = 0;
+    if (threadIdx.x == 0) s_win0 = S > 0 ? __ldg(p.bucket_base + batch_of(p.batch_ptr, p.G, first)) : 0;
+    __syncthreads();
+    if (tile * 32 >= S && !(S == 0 && tile == 0)) {  // nothing to sample, but the CTA's flush below needs everybody
+      __syncthreads();
+      for (int t = threadIdx.x; t < kCountWindow; t += kTpcThreads)
+        if (s_cnt[t] != 0) atomicAdd(p.bucket_count + s_win0 + t, s_cnt[t]);
+      return;
+    }
+  } else if (tile * 32 >= S && !(S == 0 && tile == 0)) {
+    return;
+  }
   const i64 i = tile * 32 + lane;
   const bool valid = i < S;
   const int k = (int)p.k;
@@ -455,16 +480,16 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
   const bool too_long = valid && d > 0xFFFFFFFFll;   // positions inside a column are drawn from one 32-bit word
   if (too_long) raise_error(p.counters, GSB_ERR_UNSUPPORTED, i);
   const int n = valid && !too_long ? (int)f : 0;
+  // minibatch of the warp's first column by one search; a lane beyond that minibatch's end searches for itself
+  i64 bt = 0;
+  if (p.batch_ptr && valid) {
+    bt = batch_of(p.batch_ptr, p.G, tile * 32);
+    if (i >= __ldg(p.batch_ptr + bt + 1)) bt = batch_of(p.batch_ptr, p.G, i);
+  }
   uint32_t pick[KMAX];
   if (n > 0) {
     if (p.replace || d > k) {
-      u64 item = (u64)i;
-      if (p.G > 0) {
-        // batch of the warp's first column by one search; a lane beyond that batch's end searches for itself
-        i64 bt = batch_of(p.batch_ptr, p.G, tile * 32);
-        if (i >= __ldg(p.batch_ptr + bt + 1)) bt = batch_of(p.batch_ptr, p.G, i);
-        item = sample_item(p, i, bt);
-      }
+      const u64 item = sample_item(p, i, bt);
       U32x4 blk;
 #pragma unroll
       for (int j = 0; j < KMAX; ++j) {
@@ -506,19 +531,42 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
     p.out_indptr[0] = 0;
     p.counters[CNT_NNZ] = 0;
   }
-  if (prefix + total > p.capacity) {
+  const bool overflow = prefix + total > p.capacity;
+  if (overflow) {
     if (lane == 0) raise_error(p.counters, GSB_ERR_CAPACITY, prefix + total);
-    return;
+    if (!COUNT) return;
   }
+  if (!overflow) {
 #pragma unroll
-  for (int j = 0; j < KMAX; ++j) {
-    if (j < n) {
-      const i64 in_pos = b + pick[j];
-      p.out_indices[o + j] = val[j];
-      p.out_select[o + j] = in_pos;
-      if (p.out_coo_col) p.out_coo_col[o + j] = i;
-      if (p.out_data) p.out_data[o + j] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+    for (int j = 0; j < KMAX; ++j) {
+      if (j < n) {
+        const i64 in_pos = b + pick[j];
+        p.out_indices[o + j] = val[j];
+        p.out_select[o + j] = in_pos;
+        if (p.out_coo_col) p.out_coo_col[o + j] = i;
+        if (p.out_data) p.out_data[o + j] = p.data[p.e_ids ? p.e_ids[in_pos] : in_pos];
+      }
     }
+  }
+  if (COUNT) {
+    if (valid && !overflow) {
+      const i64 b0 = __ldg(p.bucket_base + bt);
+      const uint32_t parts = (uint32_t)(__ldg(p.bucket_base + bt + 1) - b0);
+      const i64 win = b0 - s_win0;  // >= 0: minibatches follow the CTA's first one
+      auto count_id = [&](i64 id) {
+        if (id < 0 || id >= 0xFFFFFFFFll) return;  // never bucketed; reported by the pass that scatters the items
+        const i64 w = win + bucket_of_id((uint32_t)id, parts);
+        if (w < kCountWindow) atomicAdd(&s_cnt[w], 1u);
+        else atomicAdd(p.bucket_count + s_win0 + w, 1u);
+      };
+      count_id(col);
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j)
+        if (j < n) count_id(val[j]);
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < kCountWindow; t += kTpcThreads)
+      if (s_cnt[t] != 0) atomicAdd(p.bucket_count + s_win0 + t, s_cnt[t]);
   }
 }
 
@@ -573,7 +621,8 @@ static void launch_sample(const SampleParams& p, int grid, cudaStream_t stream) 
 int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, const i64* indices, i64 num_cols,
                           const i64* seeds, i64 S, i64 k, int replace, u64 seed, i64* out_indptr, i64* out_indices,
                           i64* out_select, i64* out_coo_col, const float* data, const i64* e_ids, float* out_data,
-                          i64 capacity, const i64* S_dev, const i64* batch_ptr, const i64* batch_ids, i64 G) {
+                          i64 capacity, const i64* S_dev, const i64* batch_ptr, const i64* batch_ids, i64 G,
+                          const SamplerCount* count) {
   const bool per_thread = k <= 16;  // small fanouts: one lane per column, one warp per tile of 32 columns
   const int grid = per_thread ? grid_for(S, kTpcThreads) : grid_for(S, kTileCols);
   TileState ts;
@@ -581,19 +630,30 @@ int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, 
   if (st != GSB_OK) return st;
   SampleParams p{indptr,     indices,     num_cols, seeds, S,        k,        replace,           seed, out_indptr,
                  out_indices, out_select, out_coo_col, data, e_ids, out_data, capacity, ctx_counters(ctx), ts,
-                 S_dev,      batch_ptr,  batch_ids && batch_ptr ? batch_ids : nullptr,
-                 batch_ids && batch_ptr ? G : 0};
+                 S_dev,      batch_ptr,  batch_ptr ? batch_ids : nullptr,
+                 batch_ptr ? G : 0,      nullptr,    nullptr};
+  if (count && count->bucket_count) {
+    if (!per_thread || !batch_ptr || G < 1) return GSB_ERR_INVALID_ARGUMENT;
+    p.bucket_count = count->bucket_count;
+    p.bucket_base = count->bucket_base;
+  }
   {
     ScopedKernelTimer timer(ctx, KID_SAMPLE_UNIFORM, stream);
     // the register count follows the unrolled pick array (48 / 48 / 56 / 64 / 80 registers); the usual fan-outs 5 and
     // 10 get instantiations of their own, which removes the spilled words of <8> and <16> for them.  Measured effect on
     // the 3-hop benchmark: none (6.45 against 6.47 ms per 1 000 minibatches) — the kernel runs at the rate at which
     // DRAM serves random 64-byte accesses, not at the limit of its resident lanes.
-    if (k <= 4) k_sample_uniform_tpc<4><<<grid, kTpcThreads, 0, stream>>>(p);
-    else if (k <= 5) k_sample_uniform_tpc<5><<<grid, kTpcThreads, 0, stream>>>(p);
-    else if (k <= 8) k_sample_uniform_tpc<8><<<grid, kTpcThreads, 0, stream>>>(p);
-    else if (k <= 10) k_sample_uniform_tpc<10><<<grid, kTpcThreads, 0, stream>>>(p);
-    else if (k <= 16) k_sample_uniform_tpc<16><<<grid, kTpcThreads, 0, stream>>>(p);
+    if (p.bucket_count) {
+      if (k <= 4) k_sample_uniform_tpc<4, true><<<grid, kTpcThreads, 0, stream>>>(p);
+      else if (k <= 5) k_sample_uniform_tpc<5, true><<<grid, kTpcThreads, 0, stream>>>(p);
+      else if (k <= 8) k_sample_uniform_tpc<8, true><<<grid, kTpcThreads, 0, stream>>>(p);
+      else if (k <= 10) k_sample_uniform_tpc<10, true><<<grid, kTpcThreads, 0, stream>>>(p);
+      else k_sample_uniform_tpc<16, true><<<grid, kTpcThreads, 0, stream>>>(p);
+    } else if (k <= 4) k_sample_uniform_tpc<4, false><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 5) k_sample_uniform_tpc<5, false><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 8) k_sample_uniform_tpc<8, false><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 10) k_sample_uniform_tpc<10, false><<<grid, kTpcThreads, 0, stream>>>(p);
+    else if (k <= 16) k_sample_uniform_tpc<16, false><<<grid, kTpcThreads, 0, stream>>>(p);
     else launch_sample<32>(p, grid, stream);
   }
   GSB_LAUNCH_OK();
