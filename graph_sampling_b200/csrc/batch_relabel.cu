@@ -31,7 +31,8 @@ namespace gsb {
 // what & 1: write region_off; what & 2: write item_off (indices_ptr is valid); what & 4: keep an abort that an earlier
 // launch of the same call set; what & 8: region_off receives the first BUCKET of every minibatch instead of a table
 // region (partition_relabel.cu; slot_capacity then bounds the bucket count); what & 16: bucket_item0 receives, for
-// every bucket, the first item of its minibatch (needs region_off and indices_ptr).
+// every bucket, the first item of its minibatch (needs region_off and indices_ptr); what & 32: the same pointer is the
+// array of per-bucket counts instead and is cleared (slot_capacity + 1 words).
 // seeds_bound / edges_bound: what the caller sized grids, scratch and outputs for.  Device-side totals above them
 // record GSB_ERR_CAPACITY and set CNT_ABORT, which makes the kernels that follow in the call return at once.
 __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters, i64 bound_k, int what,
@@ -68,6 +69,8 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
     if (threadIdx.x == 0) s_carry = carry + total;
     __syncthreads();
   }
+  if (what & 32)
+    for (i64 k = threadIdx.x; k <= L.slot_capacity; k += kBThreads) bucket_item0[k] = 0u;
   if (threadIdx.x == 0) {
     if (what & 2) L.item_off[L.G] = L.seeds_ptr[L.G] + L.indices_ptr[L.G];
     if (what & 1) {
@@ -746,24 +749,16 @@ static int sage_hop_sampler_counts(gsb_ctx* ctx, cudaStream_t stream, const i64*
   L.slot_capacity = bucket_cap;
   {
     ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, k, 1 | 8, S, cap);
+    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, k, 1 | 8 | 32, S, cap, partition_bucket_counts(part_ws));
   }
   GSB_LAUNCH_OK();
-  GSB_CUDA_OK(cudaMemsetAsync(partition_bucket_counts(part_ws), 0, sizeof(uint32_t) * (size_t)(bucket_cap + 1), stream));
   const SamplerCount count{partition_bucket_counts(part_ws), L.region_off};
   st = sample_uniform_launch(ctx, stream, indptr, indices, num_nodes, seeds, S, k, replace, seed, out_indptr,
                              out_indices, out_select, nullptr, nullptr, nullptr, nullptr, cap, seeds_ptr + G,
                              seeds_ptr, batch_ids, G, &count);
   if (st != GSB_OK) return st;
-  {
-    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_gather_offsets<<<grid_for(G + 1, kBThreads), kBThreads, 0, stream>>>(out_indptr, seeds_ptr, G, S,
-                                                                          out_indices_ptr);
-    k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, k, 2 | 4 | 16, S, cap,
-                                                partition_bucket_item0(part_ws, bucket_cap));
-  }
-  GSB_LAUNCH_OK();
-  ctx_count_launches(ctx, 1);
+  st = partition_after_sampler(ctx, stream, L, n_cap, bucket_cap, part_ws, out_indptr, S, cap, out_indices_ptr);
+  if (st != GSB_OK) return st;
   return partition_unique_relabel(ctx, stream, L, n_cap, bucket_cap, part_ws, true, out_unique, out_unique_ptr,
                                   out_relabeled);
 }

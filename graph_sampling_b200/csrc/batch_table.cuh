@@ -166,14 +166,18 @@ int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchL
 // items, bit-vector ranking, no fix-up pass.  L carries seeds / seeds_ptr / indices / indices_ptr / G; item_off and
 // region_off (first bucket of every minibatch) must be filled by k_batch_layout; `ws` is scratch of
 // partition_workspace_bytes(n_cap, bucket_cap) bytes and begins with the per-bucket item counts.  counted = true: the
-// counts (and the first item of every bucket's minibatch) are already there — the sampler of the same hop added
-// them — and the counting pass is skipped.
+// counts, bucket starts and the first item of every bucket's minibatch are already there (the sampler of the same hop
+// counted, partition_after_sampler did the rest) and the counting and scan passes are skipped.
 i64 partition_bucket_capacity(i64 items_bound, i64 G);
 size_t partition_workspace_bytes(i64 n_cap, i64 bucket_cap);
 uint32_t* partition_bucket_counts(void* ws);
 uint32_t* partition_bucket_item0(void* ws, i64 bucket_cap);
 int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
                              bool counted, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
+// The one-call hop, after its counting sampler: edge offsets of the minibatches (from the sampled block's offsets),
+// item offsets, bound check, bucket starts — everything partition_unique_relabel(counted = true) expects, one launch.
+int partition_after_sampler(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
+                            const i64* sub_indptr, i64 S, i64 edges_bound, i64* out_indices_ptr);
 // Bucket of an id among the `parts` buckets of its minibatch: Fibonacci hashing (the high bits of id x odd constant),
 // scaled to the bucket count by a multiply-high.  Ids are below 2^32 - 1 wherever this is used.
 __device__ __forceinline__ uint32_t bucket_of_id(uint32_t id, uint32_t parts) { return __umulhi(id * 0x9E3779B1u, parts); }

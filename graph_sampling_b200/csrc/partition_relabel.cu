@@ -205,6 +205,66 @@ __global__ void __launch_bounds__(1024) k_part_scan(PartLayout P, i64* counters)
   if (threadIdx.x == 0) P.bucket_start[buckets] = (u32)s_carry;
 }
 
+// The one-call hop, between its sampler and the scatter pass — one CTA does what three small launches did: the edge
+// offset of every minibatch (the sampled block's offset at the minibatch's first seed), the item offsets, the abort
+// check against the caller's bounds, the first item of every bucket's minibatch, and the scan of the bucket sizes that
+// the sampler counted.
+__global__ void __launch_bounds__(1024) k_part_after_sampler(PartLayout P, const i64* __restrict__ sub_indptr, i64 S,
+                                                             i64 edges_bound, i64* indices_ptr, i64* counters) {
+  __shared__ i64 s_scan[33];
+  __shared__ i64 s_carry;
+  __shared__ int s_abort;
+  const BatchLayout& L = P.L;
+  const i64 G = L.G;
+  if (threadIdx.x == 0) {
+    const i64 ns = L.seeds_ptr[G];
+    const i64 ne = sub_indptr[max((i64)0, min(ns, S))];
+    const bool over = ns > S || ne > edges_bound || ns < 0 || ne < 0;
+    if (over) {
+      counters[CNT_ABORT] = 1;
+      raise_error(counters, GSB_ERR_CAPACITY, ns > S ? ns : ne);
+    }
+    s_abort = counters[CNT_ABORT] != 0;
+    s_carry = 0;
+  }
+  __syncthreads();
+  for (i64 b = threadIdx.x; b <= G; b += 1024) {
+    const i64 sp = L.seeds_ptr[b];
+    const i64 ip = sub_indptr[max((i64)0, min(sp, S))];
+    indices_ptr[b] = ip;
+    L.item_off[b] = sp + ip;
+    if (b < G && !s_abort)
+      for (i64 k = L.region_off[b]; k < L.region_off[b + 1]; ++k) P.bucket_item0[k] = (u32)(sp + ip);
+  }
+  if (s_abort) return;
+  const i64 buckets = L.region_off[G];
+  constexpr int kPer = 8;
+  for (i64 base = 0; base < buckets; base += 1024 * kPer) {
+    const i64 first = base + (i64)threadIdx.x * kPer;
+    u32 c[kPer];
+    i64 sum = 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      c[j] = first + j < buckets ? P.bucket_count[first + j] : 0u;
+      sum += c[j];
+    }
+    i64 total;
+    i64 run = s_carry + block_exclusive_scan<1024>(sum, s_scan, &total);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      if (first + j < buckets) {
+        P.bucket_start[first + j] = (u32)run;
+        P.bucket_cursor[first + j] = 0u;
+      }
+      run += c[j];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) P.bucket_start[buckets] = (u32)s_carry;
+}
+
 // A tile's items are first sorted by bucket in shared memory (their rank inside the tile's share of a bucket is what
 // the counting atomic returns), so the copy to global memory writes whole runs of consecutive words.
 __global__ void __launch_bounds__(kPartThreads) k_part_scatter(PartLayout P, i64 n_bound, i64* counters) {
@@ -612,12 +672,16 @@ size_t partition_workspace_bytes(i64 n_cap, i64 bucket_cap) {
 uint32_t* partition_bucket_counts(void* ws) { return (u32*)ws; }
 uint32_t* partition_bucket_item0(void* ws, i64 bucket_cap) { return (u32*)ws + 3 * (bucket_cap + 1); }
 
-int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
-                             bool counted, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled) {
-  i64* counters = ctx_counters(ctx);
+struct PartArrays {
+  PartLayout P;
+  RankArrays R;
+};
+
+static PartArrays carve(const BatchLayout& L, i64 n_cap, i64 bucket_cap, void* ws) {
   const size_t words = (size_t)((n_cap + 31) / 32) + 2;
   char* at = (char*)ws;
-  PartLayout P;
+  PartArrays a;
+  PartLayout& P = a.P;
   P.L = L;
   P.bucket_count = (u32*)at;
   P.bucket_start = P.bucket_count + (bucket_cap + 1);
@@ -628,13 +692,32 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
   at += al256(8 * (size_t)n_cap);
   P.ref = (u32*)at;
   at += al256(4 * (size_t)n_cap);
-  RankArrays R;
-  R.ref = P.ref;
-  R.bits = (u32*)at;
+  a.R.ref = P.ref;
+  a.R.bits = (u32*)at;
   at += al256(4 * words);
-  R.packed = (u64*)at;
+  a.R.packed = (u64*)at;
   at += al256(8 * words);
   P.spill = (u64*)at;
+  return a;
+}
+
+int partition_after_sampler(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
+                            const i64* sub_indptr, i64 S, i64 edges_bound, i64* out_indices_ptr) {
+  const PartArrays a = carve(L, n_cap, bucket_cap, ws);
+  {
+    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+    k_part_after_sampler<<<1, 1024, 0, stream>>>(a.P, sub_indptr, S, edges_bound, out_indices_ptr, ctx_counters(ctx));
+  }
+  GSB_LAUNCH_OK();
+  return GSB_OK;
+}
+
+int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
+                             bool counted, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled) {
+  i64* counters = ctx_counters(ctx);
+  const PartArrays arrays = carve(L, n_cap, bucket_cap, ws);
+  const PartLayout& P = arrays.P;
+  const RankArrays& R = arrays.R;
   static bool attr_set[64] = {};
   const int dev = ctx_device(ctx);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -648,12 +731,12 @@ int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i
       k_part_count<<<grid_for(n_cap, kPartTile), kPartThreads, 0, stream>>>(P, n_cap, counters);
     }
     GSB_LAUNCH_OK();
+    {
+      ScopedKernelTimer timer(ctx, KID_OTHER, stream);
+      k_part_scan<<<1, 1024, 0, stream>>>(P, counters);
+    }
+    GSB_LAUNCH_OK();
   }
-  {
-    ScopedKernelTimer timer(ctx, KID_OTHER, stream);
-    k_part_scan<<<1, 1024, 0, stream>>>(P, counters);
-  }
-  GSB_LAUNCH_OK();
   {
     ScopedKernelTimer timer(ctx, KID_PART_SCATTER, stream);
     k_part_scatter<<<grid_for(n_cap, kScatterTile), kPartThreads, 0, stream>>>(P, n_cap, counters);

@@ -549,7 +549,9 @@ __global__ void __launch_bounds__(kTpcThreads) k_sample_uniform_tpc(SampleParams
     }
   }
   if (COUNT) {
-    if (valid && !overflow) {
+    // a call whose device-side sizes exceed the caller's bounds was flagged by the layout kernel: its bucket layout
+    // may not fit the count array, so nothing is counted (the passes that would use the counts return at once)
+    if (valid && !overflow && p.counters[CNT_ABORT] == 0) {
       const i64 b0 = __ldg(p.bucket_base + bt);
       const uint32_t parts = (uint32_t)(__ldg(p.bucket_base + bt + 1) - b0);
       const i64 win = b0 - s_win0;  // >= 0: minibatches follow the CTA's first one

@@ -100,6 +100,39 @@ def test_sage_sample_batches_matches_oracle(ops, oracle, cfg1_graph, relabel_pat
         cur, cur_ptr = np.concatenate(nxt), np.array(nxt_ptr, dtype=np.int64)
 
 
+@pytest.mark.parametrize("replace", [False, True])
+def test_sage_sample_batches_ragged_minibatches(ops, oracle, hub_graph, relabel_path, replace):
+    """Minibatches of 0, 1, a few and a few hundred seeds in one call on the graph with hubs, isolated and degree-1
+    nodes (with and without replacement): warps, CTAs and tiles of every pass straddle minibatch boundaries."""
+    indptr, indices = hub_graph
+    n = len(indptr) - 1
+    rng = np.random.default_rng(11)
+    sizes = np.concatenate([rng.integers(0, 4, 150), [0, 0, 300, 1, 0, 700], rng.integers(0, 40, 60)])
+    G = len(sizes)
+    seeds0 = np.concatenate([rng.choice(n, int(z), replace=False) for z in sizes] + [np.empty(0, np.int64)]).astype(np.int64)
+    ptr0 = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    fanouts = [4, 3]
+    hops = ops.sage_sample_batches(dev(indptr), dev(indices), dev(seeds0), dev(ptr0), fanouts, seed=5, replace=replace)
+    cur, cur_ptr = seeds0, ptr0
+    for hop, (k, h) in enumerate(zip(fanouts, hops)):
+        w_indptr, _, w_idx, w_sel = oracle.sample_uniform(indptr, indices, cur, k, replace, seed=5 + hop)
+        assert np.array_equal(host(h["sub_indptr"]), w_indptr)
+        assert np.array_equal(host(h["indices"]), w_idx) and np.array_equal(host(h["select_index"]), w_sel)
+        e_ptr = w_indptr[cur_ptr]
+        assert np.array_equal(host(h["indices_ptr"]), e_ptr)
+        fr, fr_ptr, rel = host(h["frontier"]), host(h["frontier_ptr"]), host(h["relabeled"])
+        nxt, nxt_ptr = [], [0]
+        for b in range(G):
+            s = cur[cur_ptr[b]:cur_ptr[b + 1]]
+            e = w_idx[e_ptr[b]:e_ptr[b + 1]]
+            wu, (wr,) = oracle.unique_relabel([s, e], [e])
+            assert np.array_equal(fr[fr_ptr[b]:fr_ptr[b + 1]], wu), (hop, b)
+            assert np.array_equal(rel[e_ptr[b]:e_ptr[b + 1]], wr), (hop, b)
+            nxt.append(wu)
+            nxt_ptr.append(nxt_ptr[-1] + len(wu))
+        cur, cur_ptr = np.concatenate(nxt + [np.empty(0, np.int64)]).astype(np.int64), np.array(nxt_ptr, dtype=np.int64)
+
+
 @pytest.mark.parametrize("G,ns,ne", [(1, 5, 40), (7, 100, 3000), (64, 1024, 9000), (300, 17, 200)])
 def test_batch_csr_relabel_paths_agree_with_oracle(ops, oracle, relabel_path, G, ns, ne):
     """Both table forms, with duplicate seeds (no distinctness promise) and ragged / empty batches."""
@@ -122,6 +155,82 @@ def test_batch_csr_relabel_paths_agree_with_oracle(ops, oracle, relabel_path, G,
         wu, (wr,) = oracle.unique_relabel([s, e], [e])
         assert np.array_equal(uniq[uniq_ptr[b]:uniq_ptr[b + 1]], wu), b
         assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
+
+
+def _check_against_oracle(oracle, seeds, seeds_ptr, indices, indices_ptr, uniq, uniq_ptr, rel):
+    uniq, uniq_ptr, rel = host(uniq), host(uniq_ptr), host(rel)
+    assert len(rel) == indices_ptr[-1] and uniq_ptr[-1] == len(uniq)
+    for b in range(len(seeds_ptr) - 1):
+        s = seeds[seeds_ptr[b]:seeds_ptr[b + 1]]
+        e = indices[indices_ptr[b]:indices_ptr[b + 1]]
+        wu, (wr,) = oracle.unique_relabel([s, e], [e])
+        assert np.array_equal(uniq[uniq_ptr[b]:uniq_ptr[b + 1]], wu), b
+        assert np.array_equal(rel[indices_ptr[b]:indices_ptr[b + 1]], wr), b
+
+
+@pytest.mark.parametrize("case", ["hub_repeats", "one_id", "wide_minibatch", "many_tiny", "all_distinct"])
+def test_partitioned_form_special_paths(ops, oracle, case):
+    """What the partitioned form treats apart from its common case: a bucket with more items than its shared-memory
+    table is sized for (one id repeated thousands of times) gets a table of its own in global memory; a minibatch with
+    more buckets than a tile counts in shared memory, and tiles that span hundreds of tiny or empty minibatches, take
+    the per-item paths; a minibatch without any repeat fills its tables to their design load."""
+    rng = np.random.default_rng(len(case))
+    if case == "hub_repeats":
+        sizes = [(50, 30000), (10, 9000), (0, 5000)]
+        parts = []
+        for ns, ne in sizes:
+            e = rng.integers(0, 40000, ne)
+            e[rng.random(ne) < 0.45] = 777          # thousands of repeats of one id in one bucket
+            e[rng.random(ne) < 0.10] = 12345
+            parts.append((rng.choice(40000, ns, replace=False), e))
+    elif case == "one_id":
+        parts = [(np.array([5]), np.full(20000, 5)), (np.array([], dtype=np.int64), np.full(7000, 9))]
+    elif case == "wide_minibatch":
+        parts = [(rng.choice(1 << 20, 1000, replace=False), rng.integers(0, 1 << 20, 700_000)),
+                 (rng.choice(1 << 20, 10, replace=False), rng.integers(0, 1 << 20, 100))]
+    elif case == "many_tiny":
+        parts = []
+        for b in range(3000):
+            ns, ne = (0, 0) if b % 7 == 0 else (int(rng.integers(0, 4)), int(rng.integers(0, 9)))
+            parts.append((rng.integers(0, 50, ns), rng.integers(0, 50, ne)))
+    else:
+        ids = rng.permutation(200_000)
+        parts = [(ids[:1000], ids[1000:120_000]), (ids[120_000:120_500], ids[120_500:])]
+    seeds = np.concatenate([p[0] for p in parts]).astype(np.int64)
+    indices = np.concatenate([p[1] for p in parts]).astype(np.int64)
+    seeds_ptr = np.concatenate([[0], np.cumsum([len(p[0]) for p in parts])]).astype(np.int64)
+    indices_ptr = np.concatenate([[0], np.cumsum([len(p[1]) for p in parts])]).astype(np.int64)
+    ctx = ops.default_context()
+    ctx.set_option("relabel_path", 3)
+    try:
+        uniq, uniq_ptr, rel, _ = ops.batch_csr_relabel(dev(seeds), dev(seeds_ptr), dev(indices), dev(indices_ptr))
+    finally:
+        ctx.set_option("relabel_path", 0)
+    _check_against_oracle(oracle, seeds, seeds_ptr, indices, indices_ptr, uniq, uniq_ptr, rel)
+
+
+def test_partitioned_form_marks_ids_it_cannot_bucket(ops, oracle):
+    """A negative neighbour id is reported (GSB_ERR_INDEX_RANGE) and relabelled -1; everything else of the call is
+    what the oracle gives without it."""
+    from graph_sampling_b200.cabi import GsbError
+    rng = np.random.default_rng(3)
+    seeds = rng.choice(5000, 300, replace=False).astype(np.int64)
+    indices = rng.integers(0, 5000, 6000).astype(np.int64)
+    bad = np.array([17, 2500, 5999])
+    indices_bad = indices.copy()
+    indices_bad[bad] = -4
+    seeds_ptr = np.array([0, 100, 300], dtype=np.int64)
+    indices_ptr = np.array([0, 2000, 6000], dtype=np.int64)
+    ctx = ops.default_context()
+    ctx.set_option("relabel_path", 3)
+    try:
+        with pytest.raises(GsbError) as e:
+            ops.batch_csr_relabel(dev(seeds), dev(seeds_ptr), dev(indices_bad), dev(indices_ptr))
+        assert e.value.status == -8
+        uniq, uniq_ptr, rel, _ = ops.batch_csr_relabel(dev(seeds), dev(seeds_ptr), dev(indices), dev(indices_ptr))
+    finally:
+        ctx.set_option("relabel_path", 0)
+    _check_against_oracle(oracle, seeds, seeds_ptr, indices, indices_ptr, uniq, uniq_ptr, rel)
 
 
 def test_direct_tables_survive_many_calls_and_a_change_of_shape(ops, oracle):
