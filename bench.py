@@ -97,7 +97,7 @@ def parse():
     ap.add_argument("--walk-length", type=int, default=80)
     ap.add_argument("--walk-nodes", type=int, default=111_000_000)
     ap.add_argument("--walk-edges", type=int, default=1_600_000_000)
-    ap.add_argument("--group", type=int, default=125,
+    ap.add_argument("--group", type=int, default=500,
                     help="minibatches handed to one call of the batched sampler")
     return ap.parse_args()
 
@@ -634,7 +634,7 @@ def dropin_torchscript(torch, args, device, indptr, indices, pinned, lib_path=No
 
     out = {}
     best = None
-    for group in sorted({args.group, 250}):
+    for group in sorted({args.group, 250, 125}):
         st = Stepper(torch, call, pinned, group, device)
         steps = max(1, min(args.steps, args.dropin_steps))
         seconds, edges = timed_steps(torch, st, 1, steps, lambda: None, float, min_seconds=0.0, min_repeats=1,
@@ -701,7 +701,7 @@ def run_reference(args):
         # its super-batch loop at this run's group size and at the 256-ish size its examples use: one trial step
         # each, the faster one is measured in full
         trial = {}
-        for group in sorted({args.group, 250}):
+        for group in sorted({args.group, 250, 125}):
             st = Stepper(torch, call, pinned, group, device)
             sec, e = timed_steps(torch, st, 1, 1, lambda: None, float, min_seconds=0.0, min_repeats=1, max_repeats=1)
             trial[group] = e / sec[0]
