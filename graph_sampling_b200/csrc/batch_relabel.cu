@@ -612,6 +612,10 @@ __global__ void k_single_batch_setup(i64* seeds_ptr, i64* indices_ptr, i64* item
 
 // ---- unique + relabel of G minibatches: chooses between direct-address tables and hash-table regions -------------
 constexpr i64 kDirectAutoBytes = 32ll << 20;
+// Automatic choice between the partitioned form and the hash regions: the partitioned form takes nine launches where
+// the hash regions take five, which a call of a few thousand items (one minibatch relabelled on its own) feels more
+// than the per-item work it saves — about 20 ns per 1 000 items.
+constexpr i64 kPartitionAutoItems = 1ll << 19;
 
 static int read_totals(gsb_ctx* ctx, cudaStream_t stream, i64* unique_total_host, i64* edges_total_host) {
   const i64* c;
@@ -667,8 +671,8 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
     return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr,
                                         out_relabeled);
   }
-  if (path == 3 || path == 0) {
-    // partitioned form (the default when the direct-address tables above were not chosen): shared-memory tables per bucket of items, then ranking by bit vectors
+  if (path == 3 || (path == 0 && n_cap >= kPartitionAutoItems)) {
+    // partitioned form (the default for large calls when the direct-address tables above were not chosen): shared-memory tables per bucket of items, then ranking by bit vectors
     const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
     int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, bucket_cap), &ws);
     if (st != GSB_OK) return st;
@@ -842,7 +846,7 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
   int st;
   const i64 path = ctx_option(ctx, GSB_OPT_RELABEL_PATH);
   const bool direct_small = (double)G * (double)num_nodes * 8.0 <= (double)kDirectAutoBytes && num_nodes > 0;
-  if (k >= 1 && k <= 16 && n_cap > 0 && (path == 3 || (path == 0 && !direct_small))) {
+  if (k >= 1 && k <= 16 && n_cap > 0 && (path == 3 || (path == 0 && !direct_small && n_cap >= kPartitionAutoItems))) {
     st = sage_hop_sampler_counts(ctx, stream, indptr, indices, num_nodes, seeds, seeds_ptr, batch_ids, G, S, k, cap,
                                  replace, (u64)seed, out_indptr, out_indices, out_select, out_indices_ptr, out_unique,
                                  out_unique_ptr, out_relabeled);
