@@ -87,7 +87,7 @@ def parse():
     ap.add_argument("--nodes", type=int, default=NUM_NODES, help="override the graph size (debugging only)")
     ap.add_argument("--edges", type=int, default=NUM_EDGES)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels", "ladies", "adaptive", "access"],
+    ap.add_argument("--workload", default="sage", choices=["sage", "walk", "kernels", "ladies", "adaptive", "access", "atomics"],
                     help="sage = the headline (the products-scale configuration); walk = uniform random walk (papers-scale "
                          "configuration); ladies = layer-wise importance sampling (1 M nodes / 50 M weighted edges); adaptive = "
                          "SDDMM score -> per-column softmax -> weighted sampling on the products-scale graph; both of the "
@@ -1056,6 +1056,29 @@ def secondary_workloads(args, impl, device, indptr, indices):
     return out
 
 
+def run_atomics(args):
+    """`--workload atomics`: the measurement behind the partitioned unique + relabel — random 64-bit atomicMin on a table
+    in a CTA's own shared memory, in the distributed shared memory of clusters of 2 - 16 CTAs, and in L2-resident global
+    memory (gsb_selftest_table_atomics).  One JSON line."""
+    import ctypes
+    import torch
+    torch.cuda.set_device(0)
+    from graph_sampling_b200 import ops
+    ctx = ops.default_context(torch.device("cuda", 0))
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rows = []
+    for where, name, clusters in ((0, "own shared memory", (1,)), (1, "distributed shared memory of a cluster", (2, 4, 8, 16)),
+                                  (2, "global memory, 32 MB table (L2)", (1,))):
+        for c in clusters:
+            out = ctypes.c_double(0.0)
+            ctx.check(ctx.lib.gsb_selftest_table_atomics(ctx.handle, stream, where, c, 2000, ctypes.byref(out)),
+                      "gsb_selftest_table_atomics")
+            rows.append({"table": name, "cluster_size": c, "atomics_per_second": out.value})
+    print(json.dumps({"metric": "random_64bit_atomic_min_per_second", "unit": "operations/s", "rows": rows,
+                      "config": {"workload": "1,024 threads per CTA, one CTA per SM, 200 KB of shared memory per CTA, "
+                                             "2,000 rounds of 4 independent atomicMin per thread"}}))
+
+
 def run_access(args):
     """`--workload access`: what the sampling launches of ONE call of the batched sampler touch, counted exactly from
     the call's own outputs (select_index = the positions it gathered): seed columns and how many are distinct, their
@@ -1318,6 +1341,8 @@ if __name__ == "__main__":
         run_walk(a)
     elif a.workload == "access":
         run_access(a)
+    elif a.workload == "atomics":
+        run_atomics(a)
     elif a.workload in ("ladies", "adaptive"):
         run_pipeline(a)
     elif a.impl == "reference":

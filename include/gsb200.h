@@ -105,6 +105,14 @@ GSB_API int gsb_ctx_get_option(gsb_ctx* ctx, int option, int64_t* value_host);
  * tile the later tiles give up after GSB_OPT_MAX_POLLS polls, the call waits for the stream and returns
  * GSB_ERR_LOOKBACK_TIMEOUT; the context stays usable.  tiles <= 4096. */
 GSB_API int gsb_selftest_lookback(gsb_ctx* ctx, void* stream, int tiles, int silent_tile, int64_t* out_prefix);
+/* Measurement behind the partitioned unique + relabel (no counterpart in the reference): throughput of random 64-bit
+ * atomicMin on a table that lives in (where = 0) each CTA's own shared memory, (1) the distributed shared memory of
+ * thread-block clusters of `cluster_size` CTAs (2, 4, 8 or 16), (2) 32 MB of global memory, i.e. L2.  One CTA of 1 024
+ * threads per SM, `iters` rounds of four independent operations per thread (1 <= iters <= 100000); cluster_size must
+ * be 1 unless where = 1.  Waits for the stream; *ops_per_second_host receives operations per second over the whole
+ * GPU.  Contains no wait on another CTA except the cluster barriers around the loop. */
+GSB_API int gsb_selftest_table_atomics(gsb_ctx* ctx, void* stream, int where, int cluster_size, int iters,
+                                       double* ops_per_second_host);
 /* Library build information: "gsb200 <version> sm_100a". */
 GSB_API const char* gsb_version(void);
 /* Number of kernel launches issued through this context so far (all entry points). */
