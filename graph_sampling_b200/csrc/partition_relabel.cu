@@ -2,21 +2,24 @@
 //
 // The hash-region form (batch_relabel.cu) gives every minibatch a table region in global memory and pays two random
 // L2 / DRAM accesses per item in its insert pass and one or two more in its compaction, whose look-back chain over
-// tens of thousands of tiles is what that kernel mostly waits for.  Measured on a B200, 64-bit atomics on a CTA's own
-// shared memory run at 4 G/s per SM (620 G/s on the whole GPU), ten times what the L2 path sustains (64 G items/s),
-// while atomics on a cluster's distributed shared memory reach only 29 - 33 G/s GPU-wide.  So the items of a
-// minibatch are first PARTITIONED by a hash of their id into buckets small enough for one CTA's shared memory, and
-// every bucket is resolved by one CTA on its own:
+// tens of thousands of tiles is what that kernel mostly waits for.  Measured on a B200 (gsb_selftest_table_atomics),
+// random 64-bit atomics on a CTA's own shared memory run at 4.7 G/s per SM (691 G/s on the whole GPU), ten times what
+// the L2 path sustains (71 G/s; the hash-region insert reaches 64 G items/s), while atomics on a cluster's distributed
+// shared memory reach only 29 - 33 G/s GPU-wide.  So the items of a minibatch are first PARTITIONED by a hash of their
+// id into buckets small enough for one CTA's shared memory, and every bucket is resolved by one CTA on its own:
 //
-//   layout    per minibatch: item offset, number of buckets (items / kBucketTarget, rounded up), first bucket;
+//   layout    per minibatch: item offset, number of buckets (items / kBucketTarget = 2 048, rounded up), first bucket;
 //   count     a CTA takes 4 096 consecutive items, counts them per bucket in shared memory, adds its counts to the
-//             bucket sizes (one global atomic per CTA and bucket);
-//   scan      bucket sizes -> bucket starts (one CTA);
+//             bucket sizes (one global atomic per CTA and bucket).  In the one-call hop (gsb_sage_hop) the uniform
+//             sampler does this counting itself while it holds the ids (slice_sample.cu, COUNT) — the buckets are then
+//             laid out from the bound seeds x (1 + fanout) before it runs — and this pass is not launched;
+//   scan      bucket sizes -> bucket starts (one CTA; in the one-call hop part of k_part_after_sampler);
 //   scatter   tiles of 2 048 items: sorted by bucket in shared memory, a range reserved per bucket with one global
 //             atomic, whole runs of (id << 32 | position inside the minibatch) copied out — the order inside a bucket
 //             does not matter, the table keeps the smallest position per id;
 //   resolve   one CTA per bucket: the bucket's items stay in registers; position-min insert into a shared-memory
-//             table (load <= 0.5), then every item reads the first position of its id from the slot it ended in and
+//             table (48 KB: ids and smallest positions as two 32-bit arrays, three slots per item where that fits, two
+//             otherwise), then every item reads the first position of its id from the slot it ended in and
 //             writes it to ref[item] — the only scattered accesses to global memory of the whole sequence, 4 bytes
 //             per item into the minibatch's own window; a bucket with more items than the shared-memory table is sized
 //             for (many repeats of a few hub ids, or an unlucky hash) uses a table in global memory of its own
@@ -47,7 +50,7 @@ constexpr u32 kNoBucket = 0xFFFFFFFFu;
 constexpr int kResolveThreads = 256;
 constexpr int kResolvePer = 12;                          // items per thread of a bucket that fits shared memory
 constexpr int kBucketSlots = 6144;                       // shared-memory table of a resolve CTA: 48 KB
-constexpr int kBucketSmemItems = kBucketSlots / 2 - 16;  // largest bucket that is sure to fit it at load <= 0.5
+constexpr int kBucketSmemItems = kBucketSlots / 2 - 16;  // largest bucket that fits it at two slots per item
 
 struct PartLayout {
   BatchLayout L;       // region_off holds the first bucket of every minibatch ([G + 1], last = bucket count)
