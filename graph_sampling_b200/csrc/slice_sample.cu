@@ -644,7 +644,9 @@ int sample_uniform_launch(gsb_ctx* ctx, cudaStream_t stream, const i64* indptr, 
     // the register count follows the unrolled pick array (48 / 48 / 56 / 64 / 80 registers); the usual fan-outs 5 and
     // 10 get instantiations of their own, which removes the spilled words of <8> and <16> for them.  Measured effect on
     // the 3-hop benchmark: none (6.45 against 6.47 ms per 1 000 minibatches) — the kernel runs at the rate at which
-    // DRAM serves random 64-byte accesses, not at the limit of its resident lanes.
+    // DRAM serves random 64-byte accesses, not at the limit of its resident lanes.  Gathers through
+    // ld.global.nc.L2::64B (with or without L1::no_allocate) instead of __ldg, to keep the L2 from fetching more than
+    // one 64-byte line per gather: no change either (6.85 / 6.87 against 6.76 ms with the same run-time switch).
     if (p.bucket_count) {
       if (k <= 4) k_sample_uniform_tpc<4, true><<<grid, kTpcThreads, 0, stream>>>(p);
       else if (k <= 5) k_sample_uniform_tpc<5, true><<<grid, kTpcThreads, 0, stream>>>(p);
