@@ -261,6 +261,25 @@ def test_bounded_lookback_wait_runs_out_and_reports(ops):
     assert ops.tensor_unique(dev(np.array([4, 4, 9], dtype=np.int64))).cpu().tolist() == [4, 9]
 
 
+def test_table_atomics_measurement_runs_and_checks_its_arguments(ops):
+    """The measurement behind the partitioned unique + relabel: every table placement returns a rate, a CTA's own
+    shared memory beats a cluster's distributed shared memory, and inconsistent arguments are refused."""
+    ctx = ops.default_context()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rate = {}
+    for where, cluster in ((0, 1), (1, 2), (1, 16), (2, 1)):
+        out = ctypes.c_double(0.0)
+        assert ctx.lib.gsb_selftest_table_atomics(ctx.handle, stream, where, cluster, 50, ctypes.byref(out)) == 0
+        assert out.value > 1e9
+        rate[(where, cluster)] = out.value
+    assert rate[(0, 1)] > 2 * rate[(1, 16)]
+    out = ctypes.c_double(0.0)
+    assert ctx.lib.gsb_selftest_table_atomics(ctx.handle, stream, 0, 4, 50, ctypes.byref(out)) == -1    # clusters only with where = 1
+    assert ctx.lib.gsb_selftest_table_atomics(ctx.handle, stream, 1, 3, 50, ctypes.byref(out)) == -1
+    assert ctx.lib.gsb_selftest_table_atomics(ctx.handle, stream, 3, 1, 50, ctypes.byref(out)) == -1
+    assert ops.tensor_unique(dev(np.array([4, 4, 9], dtype=np.int64))).cpu().tolist() == [4, 9]
+
+
 def test_undersized_hash_table_reports_table_full(ops):
     from graph_sampling_b200.cabi import GsbError
     ctx = ops.default_context()
