@@ -30,7 +30,9 @@
 // Every pass over the items is coalesced except the 4-byte scatter of `ref` and the 8-byte rank look-ups, both inside
 // the minibatch's own window.  All of these kernels are bound by instruction issue, not by memory, so their common
 // case — a tile or warp whose items lie in ONE minibatch — runs on 32-bit positions with the minibatch's parameters
-// in registers; a tile that straddles minibatches takes a general path per item.  Results are identical to the other
+// in registers; a tile that straddles minibatches takes a general path per item (the counting pass handles the part
+// of each minibatch in turn when they are few; doing the same in the scatter pass was measured: 64 instead of 46
+// registers, 1.86 instead of 1.62 ms per 1 000 minibatches of the products-scale benchmark, whose tiles rarely straddle).  Results are identical to the other
 // forms: first-occurrence order is defined by positions, not by the order in which anything is processed.
 #include "batch_table.cuh"
 #include "common.cuh"
@@ -134,6 +136,8 @@ __device__ __forceinline__ Located locate(const BatchLayout& L, i64 g) {
   return r;
 }
 
+constexpr int kMaxSegments = 8;  // minibatches a tile may touch and still be handled segment by segment
+
 __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n_bound, i64* counters) {
   __shared__ u32 s_cnt[kWindow];
   if (counters[CNT_ABORT] != 0) return;
@@ -141,28 +145,48 @@ __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n
   const i64 n = min(L.item_off[L.G], n_bound);
   const i64 tile_base = (i64)blockIdx.x * kPartTile;
   if (tile_base >= n) return;
-  for (int i = threadIdx.x; i < kWindow; i += kPartThreads) s_cnt[i] = 0;
-  const BatchUniform u = load_batch<false>(L, L.item_off, batch_of_warp(L.item_off, L.G, tile_base));
-  __syncthreads();
-  const TileBatch t = tile_batch(L, u);
-  const u32 lc0 = (u32)(tile_base - u.begin);
-  const u32 here = (u32)min((i64)kPartTile, n - tile_base);  // items of this tile
-  const bool uniform = (u64)lc0 + here <= (u64)t.items && t.parts <= (u32)kWindow;
-  if (uniform) {
+  const i64 tile_end = min(n, tile_base + kPartTile);
+  const i64 b_first = batch_of_warp(L.item_off, L.G, tile_base);
+  const i64 b_last = batch_of_warp(L.item_off, L.G, tile_end - 1);
+  if (b_last - b_first >= kMaxSegments) {  // a tile over many small minibatches: every item on its own
+    for (i64 g = tile_base + threadIdx.x; g < tile_end; g += kPartThreads) {
+      const Located it = locate(L, g);
+      if (!valid_id(it.node)) continue;  // never bucketed; reported by the scatter pass
+      atomicAdd(P.bucket_count + it.bucket, 1u);
+      P.bucket_item0[it.bucket] = (u32)(g - it.lc);
+    }
+    return;
+  }
+  // the part of every minibatch that lies in the tile, one after the other
+  for (i64 b = b_first; b <= b_last; ++b) {
+    const BatchUniform u = load_batch<false>(L, L.item_off, b);
+    const i64 seg_begin = max(tile_base, u.begin), seg_end = min(tile_end, u.next_begin);
+    if (seg_end <= seg_begin) continue;  // an empty minibatch
+    const TileBatch t = tile_batch(L, u);
+    const u32 lc0 = (u32)(seg_begin - u.begin), here = (u32)(seg_end - seg_begin);
+    if (t.parts > (u32)kWindow) {  // more buckets than the shared-memory window holds
+      for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
+        const i64 node = tile_item(t, lc0 + i);
+        if (!valid_id(node)) continue;
+        const u32 k = t.bucket0 + bucket_of_id((u32)node, t.parts);
+        atomicAdd(P.bucket_count + k, 1u);
+        P.bucket_item0[k] = (u32)u.begin;
+      }
+      continue;
+    }
+    __syncthreads();  // the previous segment's counts are flushed
+    for (int i = threadIdx.x; i < kWindow; i += kPartThreads) s_cnt[i] = 0;
     // ids first (independent loads), then the shared-memory atomics
     i64 node[kPartPerThread];
 #pragma unroll
     for (int q = 0; q < kPartPerThread; ++q) {
       const u32 i = q * kPartThreads + threadIdx.x;
-      node[q] = i < here ? tile_item(t, lc0 + i) : 0;
+      node[q] = i < here ? tile_item(t, lc0 + i) : -1;
     }
+    __syncthreads();
 #pragma unroll
-    for (int q = 0; q < kPartPerThread; ++q) {
-      const u32 i = q * kPartThreads + threadIdx.x;
-      if (i >= here) continue;
-      if (!valid_id(node[q])) continue;  // never bucketed; reported by the scatter pass
-      atomicAdd(&s_cnt[bucket_of_id((u32)node[q], t.parts)], 1u);
-    }
+    for (int q = 0; q < kPartPerThread; ++q)
+      if (valid_id(node[q])) atomicAdd(&s_cnt[bucket_of_id((u32)node[q], t.parts)], 1u);  // the others: scatter pass
     __syncthreads();
     for (u32 i = threadIdx.x; i < t.parts; i += kPartThreads) {
       if (s_cnt[i] != 0) {
@@ -170,13 +194,6 @@ __global__ void __launch_bounds__(kPartThreads) k_part_count(PartLayout P, i64 n
         P.bucket_item0[t.bucket0 + i] = (u32)u.begin;  // every tile of the minibatch writes the same value
       }
     }
-    return;
-  }
-  for (u32 i = threadIdx.x; i < here; i += kPartThreads) {
-    const Located it = locate(L, tile_base + i);
-    if (!valid_id(it.node)) continue;
-    atomicAdd(P.bucket_count + it.bucket, 1u);
-    P.bucket_item0[it.bucket] = (u32)(tile_base + i - it.lc);
   }
 }
 
