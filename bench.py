@@ -1170,6 +1170,8 @@ def run_kernels(args):
     probs = torch.rand(D, generator=g, device=device) + 0.01
     timed("weighted per-column sample, fanout 10", lambda: ops.csc_col_sampling_probs(sub_indptr, sub_row, probs, 10, False, with_coo=False),
           lambda o: 32 * S + 8 + 4 * D + 24 * o[2].numel())
+    timed("weighted per-column sample, fanout 64", lambda: ops.csc_col_sampling_probs(sub_indptr, sub_row, probs, 64, False, with_coo=False),
+          lambda o: 32 * S + 8 + 4 * D + 24 * o[2].numel(), note="beyond the reference's limit of 32: one CTA per column, radix select")
     items = torch.cat([seeds, sub_row])
     timed("unique + relabel (single table)", lambda: ops.relabel([seeds, sub_row], [sub_row]),
           lambda o: 8 * items.numel() + 8 * o[0].numel() + 8 * D)
@@ -1224,6 +1226,9 @@ def run_kernels(args):
     bcol = seeds[sub_col]
     timed("BatchCOORelabel, 256 batches", lambda: ops.batch_coo_relabel(seeds, sptr, bcol, sub_row, bptr),
           lambda o: 8 * (S + D) + 8 * o[0].numel() + 8 * D + 16 * D)
+    timed("BatchCSRRelabel, 256 batches", lambda: ops.batch_csr_relabel(seeds, sptr, sub_row, bptr),
+          lambda o: 8 * (S + D) + 8 * o[0].numel() + 8 * D,
+          note="the generic entry of the batched unique + relabel: counting pass + partitioned form")
     rptr = torch.arange(G + 1, device=device) * (rows.numel() // G)
     rows_m = rows[:int(rows.numel() // G) * G].contiguous()   # the offsets must cover the whole member array
     timed("BatchCOOSlicing by membership, 256 batches", lambda: ops.batch_coo_slicing(1, sub_row, sub_col, bptr, rows_m, rptr),
@@ -1321,6 +1326,7 @@ def run_kernels_reference(args):
     timed("BatchUnique2 (sorted), 256 batches", lambda: ops._CAPI_BatchUnique2(sub_row, bptr))
     bcol = seeds[sub_col]
     timed("BatchCOORelabel, 256 batches", lambda: ops._CAPI_BatchCOORelabel(seeds, sptr, bcol, sub_row, bptr))
+    timed("BatchCSRRelabel, 256 batches", lambda: ops._CAPI_BatchCSRRelabel(seeds, sptr, sub_row, bptr))
     rptr = torch.arange(G + 1, device=device) * (rows.numel() // G)
     rows_m = rows[:int(rows.numel() // G) * G].contiguous()   # the offsets must cover the whole member array
     timed("BatchCOOSlicing by membership, 256 batches", lambda: ops._CAPI_BatchCOOSlicing(1, sub_row, sub_col, bptr, rows_m, rptr))

@@ -616,6 +616,13 @@ constexpr i64 kDirectAutoBytes = 32ll << 20;
 // the hash regions take five, which a call of a few thousand items (one minibatch relabelled on its own) feels more
 // than the per-item work it saves — about 20 ns per 1 000 items.
 constexpr i64 kPartitionAutoItems = 1ll << 19;
+// ... and a minibatch with more than 256 buckets (above 524 288 items) leaves the fast paths of the partitioning passes
+// (a tile counts and sorts 256 buckets in shared memory), so calls whose AVERAGE minibatch is larger than that keep the
+// hash regions too.
+constexpr i64 kPartitionAutoMaxMinibatch = 256ll * kBucketTarget;
+static inline bool partition_suits(i64 n_cap, i64 G) {
+  return n_cap >= kPartitionAutoItems && n_cap / (G > 0 ? G : 1) <= kPartitionAutoMaxMinibatch;
+}
 
 static int read_totals(gsb_ctx* ctx, cudaStream_t stream, i64* unique_total_host, i64* edges_total_host) {
   const i64* c;
@@ -671,7 +678,7 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
     return direct_unique_relabel_launch(ctx, stream, L, T, n_cap, edges_bound, out_unique, out_unique_ptr,
                                         out_relabeled);
   }
-  if (path == 3 || (path == 0 && n_cap >= kPartitionAutoItems)) {
+  if (path == 3 || (path == 0 && partition_suits(n_cap, G))) {
     // partitioned form (the default for large calls when the direct-address tables above were not chosen): shared-memory tables per bucket of items, then ranking by bit vectors
     const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
     int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, bucket_cap), &ws);
@@ -846,7 +853,7 @@ int gsb_sage_hop(gsb_ctx* ctx, void* stream_, const int64_t* indptr, const int64
   int st;
   const i64 path = ctx_option(ctx, GSB_OPT_RELABEL_PATH);
   const bool direct_small = (double)G * (double)num_nodes * 8.0 <= (double)kDirectAutoBytes && num_nodes > 0;
-  if (k >= 1 && k <= 16 && n_cap > 0 && (path == 3 || (path == 0 && !direct_small && n_cap >= kPartitionAutoItems))) {
+  if (k >= 1 && k <= 16 && n_cap > 0 && (path == 3 || (path == 0 && !direct_small && partition_suits(n_cap, G)))) {
     st = sage_hop_sampler_counts(ctx, stream, indptr, indices, num_nodes, seeds, seeds_ptr, batch_ids, G, S, k, cap,
                                  replace, (u64)seed, out_indptr, out_indices, out_select, out_indices_ptr, out_unique,
                                  out_unique_ptr, out_relabeled);

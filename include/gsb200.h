@@ -79,7 +79,8 @@ GSB_API int gsb_check_device_status(gsb_ctx* ctx, void* stream);
  *  GSB_OPT_RELABEL_PATH         how gsb_sage_hop / gsb_batch_unique_relabel find first occurrences: 0 (default) =
  *                               direct-address tables when all tables of the call are L2-sized (32 MiB), else the
  *                               partitioned form (items bucketed by a hash of their id, one shared-memory table per
- *                               bucket) for calls of at least 2^19 items and hash-table regions below that;
+ *                               bucket) for calls of at least 2^19 items whose minibatches average at most 2^19
+ *                               items, and hash-table regions otherwise;
  *                               1 = hash-table regions in global memory, one per minibatch;
  *                               2 = direct-address tables (GSB_ERR_OUT_OF_MEMORY when they do not fit);
  *                               3 = the partitioned form.  Results are identical;
