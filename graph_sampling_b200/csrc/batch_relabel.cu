@@ -681,20 +681,26 @@ static int relabel_batches(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64
   if (path == 3 || (path == 0 && partition_suits(n_cap, G))) {
     // partitioned form (the default for large calls when the direct-address tables above were not chosen): shared-memory tables per bucket of items, then ranking by bit vectors
     const i64 bucket_cap = partition_bucket_capacity(n_cap, G);
-    int st = ctx_reserve_workspace(ctx, 2 * off_bytes + partition_workspace_bytes(n_cap, bucket_cap), &ws);
+    int st = ctx_reserve_workspace(ctx, 3 * off_bytes + partition_workspace_bytes(n_cap, bucket_cap), &ws);
     if (st != GSB_OK) return st;
     L.item_off = (i64*)ws;
     L.region_off = (i64*)((char*)ws + off_bytes);
     L.slots = nullptr;
     L.slot_capacity = bucket_cap;
+    if (!L.indices_ptr) {  // one array only (batched unique): every minibatch has zero neighbours
+      i64* zeros = (i64*)((char*)ws + 2 * off_bytes);
+      GSB_CUDA_OK(cudaMemsetAsync(zeros, 0, off_bytes, stream));
+      L.indices_ptr = zeros;
+    }
     {
       ScopedKernelTimer timer(ctx, KID_OTHER, stream);
       k_batch_layout<<<1, kBThreads, 0, stream>>>(L, counters, -1, 1 | 2 | 8, seeds_bound, edges_bound);
     }
     GSB_LAUNCH_OK();
-    return partition_unique_relabel(ctx, stream, L, n_cap, bucket_cap, (char*)ws + 2 * off_bytes, false, out_unique,
+    return partition_unique_relabel(ctx, stream, L, n_cap, bucket_cap, (char*)ws + 3 * off_bytes, false, out_unique,
                                     out_unique_ptr, out_relabeled);
   }
+  if (!L.indices_ptr) return GSB_ERR_INVALID_ARGUMENT;  // the forms below expect both arrays
   const i64 slot_cap = region_size_for(n_cap) + 32 * G + 64;
   const size_t slots_bytes = ((size_t)slot_cap * 8 + 255) & ~(size_t)255;
   const size_t rank_bytes = ((size_t)n_cap * 4 + 255) & ~(size_t)255;
@@ -971,8 +977,20 @@ int gsb_batch_unique(gsb_ctx* ctx, void* stream_, const int64_t* data, const int
   const int grid = max(1, min(grid_for(n, kBThreads), wide));
   if (!sorted) {
     BatchLayout L;
-    int st = build_batch_tables(ctx, stream, data, data_ptr, n, nullptr, nullptr, 0, G, out_unique, out_unique_ptr, &L,
-                                0, nullptr);
+    int st;
+    const i64 path = ctx_option(ctx, GSB_OPT_RELABEL_PATH);
+    if (path == 3 || (path == 0 && partition_suits(n, G))) {
+      // large calls: the partitioned form of unique + relabel with no second array (first-occurrence order as well)
+      L.seeds = data;
+      L.seeds_ptr = data_ptr;
+      L.indices = nullptr;
+      L.indices_ptr = nullptr;
+      L.G = G;
+      st = relabel_batches(ctx, stream, L, n, 0, 0, 0, out_unique, out_unique_ptr, nullptr);
+    } else {
+      st = build_batch_tables(ctx, stream, data, data_ptr, n, nullptr, nullptr, 0, G, out_unique, out_unique_ptr, &L,
+                              0, nullptr);
+    }
     if (st != GSB_OK) return st;
     if (out_unique_key && n > 0) {
       ScopedKernelTimer timer(ctx, KID_OTHER, stream);

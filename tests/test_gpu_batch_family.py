@@ -81,6 +81,28 @@ def test_batch_unique(ops, oracle, G, hi, ids, empty, sort):
         assert np.array_equal(w, host(g))
 
 
+@pytest.mark.parametrize("forced", [None, 1, 3])
+def test_batch_unique_large_call_takes_the_partitioned_form_with_the_same_result(ops, oracle, forced):
+    """Above 2^19 items the unsorted BatchUnique runs the partitioned unique (no second array); forced to the hash
+    regions or to the partitioned form it returns the same frontiers, offsets and keys as the oracle."""
+    rng = np.random.default_rng(21)
+    sizes = np.concatenate([rng.integers(20_000, 60_000, 20), [0, 0, 5, 1]])
+    rng.shuffle(sizes)
+    ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    data = rng.integers(0, 30_000, ptr[-1]).astype(np.int64)
+    assert ptr[-1] >= 1 << 19
+    want = oracle.batch_unique(data, ptr, sort=False)
+    ctx = ops.default_context()
+    if forced is not None:
+        ctx.set_option("relabel_path", forced)
+    try:
+        got = ops.batch_unique(dev(data), dev(ptr), sort=False)
+    finally:
+        ctx.set_option("relabel_path", 0)
+    for w, g in zip(want, got):
+        assert np.array_equal(w, host(g))
+
+
 @pytest.mark.parametrize("G,hi,ids,empty", SHAPES)
 def test_batch_coo_relabel(ops, oracle, G, hi, ids, empty):
     rng = np.random.default_rng(G * 7 + hi)
