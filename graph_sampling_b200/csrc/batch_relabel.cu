@@ -30,14 +30,13 @@ namespace gsb {
 // from the upper bound seeds * (1 + bound_k), which is known before sampling.
 // what & 1: write region_off; what & 2: write item_off (indices_ptr is valid); what & 4: keep an abort that an earlier
 // launch of the same call set; what & 8: region_off receives the first BUCKET of every minibatch instead of a table
-// region (partition_relabel.cu; slot_capacity then bounds the bucket count); what & 16: bucket_item0 receives, for
-// every bucket, the first item of its minibatch (needs region_off and indices_ptr); what & 32: the same pointer is the
-// array of per-bucket counts instead and is cleared (slot_capacity + 1 words).
+// region (partition_relabel.cu; slot_capacity then bounds the bucket count); what & 32: bucket_count, the array of
+// per-bucket item counts that the counting sampler will add to, is cleared (slot_capacity + 1 words).
 // seeds_bound / edges_bound: what the caller sized grids, scratch and outputs for.  Device-side totals above them
 // record GSB_ERR_CAPACITY and set CNT_ABORT, which makes the kernels that follow in the call return at once.
 __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* counters, i64 bound_k, int what,
                                                             i64 seeds_bound, i64 edges_bound,
-                                                            uint32_t* bucket_item0 = nullptr) {
+                                                            uint32_t* bucket_count = nullptr) {
   __shared__ i64 s_scan[33];
   __shared__ i64 s_carry;
   if (threadIdx.x == 0) {
@@ -56,10 +55,6 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
       const i64 items = bound_k >= 0 ? (L.seeds_ptr[b + 1] - L.seeds_ptr[b]) * (1 + bound_k)
                                      : L.seeds_ptr[b + 1] + L.indices_ptr[b + 1] - L.seeds_ptr[b] - L.indices_ptr[b];
       size = (what & 8) ? (items + kBucketTarget - 1) / kBucketTarget : region_size_for(items);
-      if (what & 16) {
-        const uint32_t first = (uint32_t)(L.seeds_ptr[b] + L.indices_ptr[b]);
-        for (i64 k = L.region_off[b]; k < L.region_off[b + 1]; ++k) bucket_item0[k] = first;
-      }
     }
     i64 total;
     const i64 excl = block_exclusive_scan<kBThreads>(size, s_scan, &total);
@@ -70,7 +65,7 @@ __global__ void __launch_bounds__(kBThreads) k_batch_layout(BatchLayout L, i64* 
     __syncthreads();
   }
   if (what & 32)
-    for (i64 k = threadIdx.x; k <= L.slot_capacity; k += kBThreads) bucket_item0[k] = 0u;
+    for (i64 k = threadIdx.x; k <= L.slot_capacity; k += kBThreads) bucket_count[k] = 0u;
   if (threadIdx.x == 0) {
     if (what & 2) L.item_off[L.G] = L.seeds_ptr[L.G] + L.indices_ptr[L.G];
     if (what & 1) {

@@ -171,7 +171,6 @@ int direct_unique_relabel_launch(gsb_ctx* ctx, cudaStream_t stream, const BatchL
 i64 partition_bucket_capacity(i64 items_bound, i64 G);
 size_t partition_workspace_bytes(i64 n_cap, i64 bucket_cap);
 uint32_t* partition_bucket_counts(void* ws);
-uint32_t* partition_bucket_item0(void* ws, i64 bucket_cap);
 int partition_unique_relabel(gsb_ctx* ctx, cudaStream_t stream, BatchLayout L, i64 n_cap, i64 bucket_cap, void* ws,
                              bool counted, i64* out_unique, i64* out_unique_ptr, i64* out_relabeled);
 // The one-call hop, after its counting sampler: edge offsets of the minibatches (from the sampled block's offsets),

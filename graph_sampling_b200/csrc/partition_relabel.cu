@@ -689,7 +689,6 @@ size_t partition_workspace_bytes(i64 n_cap, i64 bucket_cap) {
 }
 
 uint32_t* partition_bucket_counts(void* ws) { return (u32*)ws; }
-uint32_t* partition_bucket_item0(void* ws, i64 bucket_cap) { return (u32*)ws + 3 * (bucket_cap + 1); }
 
 struct PartArrays {
   PartLayout P;
